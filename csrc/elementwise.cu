@@ -1,0 +1,365 @@
+// Memory-bound fused ops for sm_100a: (residual add +) RMSNorm fwd/bwd, per-head
+// QK-RMSNorm + RoPE fwd/bwd on packed [T, H, D] tensors, SwiGLU fwd/bwd, embedding
+// gather / scatter-add. One pass over HBM per tensor, 16-byte vector accesses,
+// fp32 math. The same kernels serve the trainer and the rollout engine so both
+// sides round identically (norm is computed from the un-rounded fp32 residual sum).
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_MAX_VEC = 4;  // up to 4 x 8 bf16 per thread cached in registers -> H <= 8192
+
+struct bf16x8 {
+  uint4 u;
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  uint4 u;
+  u.x = pack_bf16x2(f[0], f[1]);
+  u.y = pack_bf16x2(f[2], f[3]);
+  u.z = pack_bf16x2(f[4], f[5]);
+  u.w = pack_bf16x2(f[6], f[7]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
+
+// y = rmsnorm(x (+ res)) * w ; optionally res_out = x + res (bf16) ; rstd[T] saved for backward.
+// H % 8 == 0, H <= 8192. grid = T rows.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  const int nvec = H >> 3;
+  float v[NORM_MAX_VEC][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < NORM_MAX_VEC; ++j) {
+    const int c = threadIdx.x + j * NORM_THREADS;
+    if (c < nvec) {
+      load8(x + row * H + c * 8, v[j]);
+      if (res != nullptr) {
+        float r[8];
+        load8(res + row * H + c * 8, r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[j][i] += r[i];
+      }
+      if (res_out != nullptr) store8(res_out + row * H + c * 8, v[j]);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[j][i] * v[j][i];
+    }
+  }
+  ss = block_sum<NORM_THREADS>(ss, scratch);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd_out != nullptr) rstd_out[row] = rstd;
+#pragma unroll
+  for (int j = 0; j < NORM_MAX_VEC; ++j) {
+    const int c = threadIdx.x + j * NORM_THREADS;
+    if (c < nvec) {
+      float g[8], o[8];
+      load8(w + c * 8, g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = v[j][i] * rstd * g[i];
+      store8(y + row * H + c * 8, o);
+    }
+  }
+}
+
+// Backward of y = rmsnorm(h) * w for a strip of rows per CTA (h = the summed residual input).
+//   dh = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres_in)
+//   dw_partial[cta, :] = sum over the CTA's rows of dy * xhat
+// dw_partial is scratch of shape [gridDim.x, H] fp32, reduced by rmsnorm_dw_reduce_kernel.
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                   const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                   const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dh,
+                   float* __restrict__ dw_partial, int T, int H) {
+  __shared__ float scratch[32];
+  const int nvec = H >> 3;
+  float dwacc[NORM_MAX_VEC][8];
+  float g[NORM_MAX_VEC][8];
+#pragma unroll
+  for (int j = 0; j < NORM_MAX_VEC; ++j) {
+    const int c = threadIdx.x + j * NORM_THREADS;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+    if (c < nvec) load8(w + c * 8, g[j]);
+  }
+  for (size_t row = blockIdx.x; row < static_cast<size_t>(T); row += gridDim.x) {
+    const float rs = rstd[row];
+    float xh[NORM_MAX_VEC][8], dyw[NORM_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_VEC; ++j) {
+      const int c = threadIdx.x + j * NORM_THREADS;
+      if (c < nvec) {
+        float a[8], b[8];
+        load8(dy + row * H + c * 8, a);
+        load8(h + row * H + c * 8, b);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = b[i] * rs;
+          dwacc[j][i] += a[i] * xh[j][i];
+          dyw[j][i] = a[i] * g[j][i];
+          dot += dyw[j][i] * xh[j][i];
+        }
+      }
+    }
+    dot = block_sum<NORM_THREADS>(dot, scratch) / H;
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_VEC; ++j) {
+      const int c = threadIdx.x + j * NORM_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rs * (dyw[j][i] - xh[j][i] * dot);
+        if (dres_in != nullptr) {
+          float r[8];
+          load8(dres_in + row * H + c * 8, r);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o[i] += r[i];
+        }
+        store8(dh + row * H + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NORM_MAX_VEC; ++j) {
+    const int c = threadIdx.x + j * NORM_THREADS;
+    if (c < nvec) {
+      float4* dst = reinterpret_cast<float4*>(dw_partial + static_cast<size_t>(blockIdx.x) * H + c * 8);
+      dst[0] = make_float4(dwacc[j][0], dwacc[j][1], dwacc[j][2], dwacc[j][3]);
+      dst[1] = make_float4(dwacc[j][4], dwacc[j][5], dwacc[j][6], dwacc[j][7]);
+    }
+  }
+}
+
+// dw[c] (+)= sum_p dw_partial[p, c]
+__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, float* __restrict__ dw, int P, int H,
+                                         int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += part[static_cast<size_t>(p) * H + c];
+  dw[c] = accumulate ? dw[c] + s : s;
+}
+
+// ---------------------------------------------------------------- QK-norm + RoPE
+// x: [T, heads_total, D] packed (q heads then k heads then v heads in one qkv row is fine:
+// `row_stride` is the element pitch of a token, `head0` the first head to process, `nheads`
+// how many). One warp per (token, head). Rotate-half convention:
+//   o[i] = a[i] cos - a[i+D/2] sin ; o[i+D/2] = a[i+D/2] cos + a[i] sin
+// with a = x or rmsnorm_D(x) * nw when nw != nullptr. cos/sin table: [max_pos, D/2] fp32.
+// `sign` = +1 forward rotation, -1 inverse rotation (backward of RoPE).
+template <int D>
+__global__ void __launch_bounds__(128)
+rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, const int* __restrict__ pos,
+            const float* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ nw, float* __restrict__ rstd_out,
+            int T, int nheads, int head0, int in_stride, int out_stride, float eps, float sign) {
+  constexpr int PER = D / 64;  // each lane handles PER pairs (i, i + D/2) ... D/2 / 32 lanes
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= T * nheads) return;
+  const int t = warp_global / nheads, hh = warp_global % nheads;
+  const __nv_bfloat16* src = x + static_cast<size_t>(t) * in_stride + static_cast<size_t>(head0 + hh) * D;
+  __nv_bfloat16* dst = out + static_cast<size_t>(t) * out_stride + static_cast<size_t>(head0 + hh) * D;
+  float lo[PER], hi[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    lo[j] = __bfloat162float(src[i]);
+    hi[j] = __bfloat162float(src[i + D / 2]);
+    ss += lo[j] * lo[j] + hi[j] * hi[j];
+  }
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / D + eps);
+    if (rstd_out != nullptr && lane == 0) rstd_out[static_cast<size_t>(t) * nheads + hh] = rs;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = lane + 32 * j;
+      lo[j] = lo[j] * rs * __bfloat162float(nw[i]);
+      hi[j] = hi[j] * rs * __bfloat162float(nw[i + D / 2]);
+    }
+  }
+  const float* cs = cos_sin + static_cast<size_t>(pos[t]) * D;  // [cos(D/2) | sin(D/2)]
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    const float c = cs[i], s = sign * cs[D / 2 + i];
+    dst[i] = __float2bfloat16(lo[j] * c - hi[j] * s);
+    dst[i + D / 2] = __float2bfloat16(hi[j] * c + lo[j] * s);
+  }
+}
+
+// ---------------------------------------------------------------------- SwiGLU
+// gu: [T, 2F] = [gate | up]; act[T, F] = silu(gate) * up
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, size_t T, int F) {
+  const size_t nvec = T * (F >> 3);
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < nvec;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = idx / (F >> 3);
+    const int c = static_cast<int>(idx % (F >> 3)) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = g[i] / (1.f + __expf(-g[i])) * u[i];
+    store8(act + t * F + c, o);
+  }
+}
+
+// dgu = [dact * up * dsilu(gate) | dact * silu(gate)]
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* __restrict__ dgu, size_t T, int F) {
+  const size_t nvec = T * (F >> 3);
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < nvec;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t t = idx / (F >> 3);
+    const int c = static_cast<int>(idx % (F >> 3)) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + t * 2 * F + c, g);
+    load8(gu + t * 2 * F + F + c, u);
+    load8(dact + t * F + c, d);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float sg = 1.f / (1.f + __expf(-g[i]));
+      const float silu = g[i] * sg;
+      dg[i] = d[i] * u[i] * (sg + silu * (1.f - sg));
+      du[i] = d[i] * silu;
+    }
+    store8(dgu + t * 2 * F + c, dg);
+    store8(dgu + t * 2 * F + F + c, du);
+  }
+}
+
+// ------------------------------------------------------------------- embedding
+__global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, int T, int H, int vocab_lo, int vocab_hi) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool mine = id >= vocab_lo && id < vocab_hi;
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(mine ? id - vocab_lo : 0) * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H);
+  for (int c = threadIdx.x; c < (H >> 3); c += blockDim.x) dst[c] = mine ? src[c] : make_uint4(0, 0, 0, 0);
+}
+
+// dtable[id] += dout[t] in fp32 (atomic; rows with repeated ids collide rarely enough at 150k vocab)
+__global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ dtable, int T, int H, int vocab_lo, int vocab_hi) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  if (id < vocab_lo || id >= vocab_hi) return;
+  float* dst = dtable + static_cast<size_t>(id - vocab_lo) * H;
+  const __nv_bfloat16* src = dout + static_cast<size_t>(t) * H;
+  for (int c = threadIdx.x; c < H; c += blockDim.x) atomicAdd(dst + c, __bfloat162float(src[c]));
+}
+
+// out = a + b (bf16), 8-wide
+__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                __nv_bfloat16* __restrict__ out, size_t nvec) {
+  for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < nvec;
+       idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float x[8], y[8];
+    load8(a + idx * 8, x);
+    load8(b + idx * 8, y);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] += y[i];
+    store8(out + idx * 8, x);
+  }
+}
+
+}  // namespace sb
+
+using bf16 = __nv_bfloat16;
+
+extern "C" int sb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* res_out, float* rstd,
+                              int T, int H, float eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
+  sb::rmsnorm_fwd_kernel<<<T, sb::NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                        (bf16*)res_out, rstd, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// dw_partial: scratch [num_ctas, H] fp32 supplied by the caller; dw: [H] fp32.
+extern "C" int sb_rmsnorm_bwd(const void* dy, const void* h, const void* w, const float* rstd, const void* dres_in,
+                              void* dh, float* dw_partial, float* dw, int T, int H, int num_ctas, int accumulate_dw,
+                              cudaStream_t s) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
+  sb::rmsnorm_bwd_kernel<<<num_ctas, sb::NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
+                                                               (const bf16*)dres_in, (bf16*)dh, dw_partial, T, H);
+  sb::rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, dw, num_ctas, H, accumulate_dw);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_rope(const void* x, void* out, const int* pos, const float* cos_sin, const void* nw, float* rstd,
+                       int T, int nheads, int head0, int in_stride, int out_stride, int D, float eps, float sign,
+                       cudaStream_t s) {
+  if (T == 0 || nheads == 0) return 0;
+  const long warps = (long)T * nheads;
+  const int blocks = (int)((warps * 32 + 127) / 128);
+  if (D == 64)
+    sb::rope_kernel<64><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T, nheads,
+                                              head0, in_stride, out_stride, eps, sign);
+  else if (D == 128)
+    sb::rope_kernel<128><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T,
+                                               nheads, head0, in_stride, out_stride, eps, sign);
+  else if (D == 256)
+    sb::rope_kernel<256><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T,
+                                               nheads, head0, in_stride, out_stride, eps, sign);
+  else
+    return (int)cudaErrorInvalidValue;
+  return (int)cudaGetLastError();
+}
+
+static inline int ew_blocks(size_t n, int threads) {
+  size_t b = (n + threads - 1) / threads;
+  return (int)(b > 148 * 16 ? 148 * 16 : (b == 0 ? 1 : b));
+}
+
+extern "C" int sb_swiglu_fwd(const void* gu, void* act, long T, int F, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (F % 8 != 0) return (int)cudaErrorInvalidValue;
+  sb::swiglu_fwd_kernel<<<ew_blocks((size_t)T * (F / 8), 256), 256, 0, s>>>((const bf16*)gu, (bf16*)act, (size_t)T, F);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long T, int F, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (F % 8 != 0) return (int)cudaErrorInvalidValue;
+  sb::swiglu_bwd_kernel<<<ew_blocks((size_t)T * (F / 8), 256), 256, 0, s>>>((const bf16*)gu, (const bf16*)dact,
+                                                                             (bf16*)dgu, (size_t)T, F);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int vlo, int vhi,
+                                cudaStream_t s) {
+  if (T == 0) return 0;
+  sb::embedding_fwd_kernel<<<T, 128, 0, s>>>(ids, (const bf16*)table, (bf16*)out, T, H, vlo, vhi);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int vlo, int vhi,
+                                cudaStream_t s) {
+  if (T == 0) return 0;
+  sb::embedding_bwd_kernel<<<T, 256, 0, s>>>(ids, (const bf16*)dout, dtable, T, H, vlo, vhi);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_add_bf16(const void* a, const void* b, void* out, long n, cudaStream_t s) {
+  if (n == 0) return 0;
+  if (n % 8 != 0) return (int)cudaErrorInvalidValue;
+  sb::add_bf16_kernel<<<ew_blocks((size_t)n / 8, 256), 256, 0, s>>>((const bf16*)a, (const bf16*)b, (bf16*)out,
+                                                                    (size_t)n / 8);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,315 @@
+// bf16 GEMM for sm_100a: TMA-fed, tcgen05.mma with TMEM accumulators, persistent
+// and warp-specialised.
+//
+//   C[M,N] (+)= op(A) * op(B)  (+ bias[N]),   fp32 accumulate, bf16 or fp32 output.
+//
+// op(A) is an M x K matrix given either K-major (row-major [M,K], the activation
+// layout) or MN-major (stored [K,M], i.e. the transpose of a row-major tensor);
+// likewise op(B) is N x K given K-major (row-major [N,K], the nn.Linear weight
+// layout) or MN-major (stored [K,N]). This covers forward (X W^T), dgrad (dY W)
+// and wgrad (dY^T X) without materialising any transpose.
+//
+// CTA = 6 warps: warp 0 issues TMA loads (one lane), warp 1 owns TMEM and issues
+// tcgen05.mma (one lane), warps 2-5 drain the accumulators (tcgen05.ld) and write
+// C. Tile 128 x BN x 64, STAGES-deep smem ring, two TMEM accumulator stages so the
+// epilogue of tile i overlaps the main loop of tile i+1. Grid = min(#tiles, #SMs).
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int GEMM_THREADS = 192;
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
+                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, int accumulate, int* status) {
+  using S = GemmSmem<BN, STAGES>;
+  constexpr int NCOLS = 2 * BN;  // two accumulator stages (power of two: 256 or 512)
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * S::A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + GEMM_BM - 1) / GEMM_BM;
+  const int tiles_n = (N + BN - 1) / BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull[s], 1);
+      mbar_init(&tempty[s], 4);  // one arrival per epilogue warp
+    }
+    *cta_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, NCOLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * GEMM_BM;
+        const int n0 = (tile / tiles_m) * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full[stage], S::STAGE_BYTES);
+          uint8_t* a_dst = sA + stage * S::A_BYTES;
+          uint8_t* b_dst = sB + stage * S::B_BYTES;
+          if constexpr (!A_MN) {
+            tma_load_2d(a_dst, &tmA, &full[stage], kb * GEMM_BK, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < GEMM_BM / 64; ++j)
+              tma_load_2d(a_dst + j * 8192, &tmA, &full[stage], m0 + j * 64, kb * GEMM_BK);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(b_dst, &tmB, &full[stage], kb * GEMM_BK, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n0 + j * 64, kb * GEMM_BK);
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(GEMM_BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, cta_abort, status, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * S::A_BYTES);
+          const uint32_t b_addr = smem_u32(sB + stage * S::B_BYTES);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            // K-major, 128B swizzle: 8-row groups 1024 B apart; a K step of 16 elements is 32 B inside the row.
+            // MN-major, 128B swizzle: 64-element column chunks 8192 B apart (LBO), 8 k-rows = 1024 B (SBO);
+            // a K step of 16 rows is 2048 B.
+            const uint64_t da = A_MN ? make_smem_desc(a_addr + k * 2048, 8192, 1024, UMMA_SWIZZLE_128B)
+                                     : make_smem_desc(a_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B);
+            const uint64_t db = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024, UMMA_SWIZZLE_128B)
+                                     : make_smem_desc(b_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // frees the smem slot once these MMAs retire
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&tfull[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * GEMM_BM;
+      const int n0 = (tile / tiles_m) * BN;
+      bool ok = mbar_wait(&tfull[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+          if (bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
+          }
+          if constexpr (OUT_F32) {
+            float* crow = reinterpret_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+            const bool vec = (col0 + 32 <= N) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
+            if (vec) {
+              float4* c4 = reinterpret_cast<float4*>(crow);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                if (accumulate) {
+                  const float4 p = c4[i];
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                c4[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < N; ++i) crow[i] = accumulate ? crow[i] + v[i] : v[i];
+            }
+          } else {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+            const bool vec = (col0 + 32 <= N) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
+            if (vec) {
+              uint4* c4 = reinterpret_cast<uint4*>(crow);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                uint4 o;
+                o.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
+                o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
+                o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
+                o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
+                c4[i] = o;
+              }
+            } else {
+              for (int i = 0; i < 32 && col0 + i < N; ++i) crow[i] = __float2bfloat16(v[i]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (++acc == 2) {
+        acc = 0;
+        acc_phase ^= 1;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*cta_abort) {
+    // give copies that are still in flight a bounded time to land before the smem goes away
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem_base, NCOLS);
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                               int ldb, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES>;
+  // K-major operand: tensor [rows = M or N, cols = K], box [rows_tile, 64].
+  // MN-major operand: tensor [rows = K, cols = M or N], box [64 k-rows, 64 cols].
+  CUtensorMap tmA = A_MN ? make_tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, size_t(lda) * 2, 64, 64,
+                                        CU_TENSOR_MAP_SWIZZLE_128B)
+                         : make_tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, size_t(lda) * 2, GEMM_BM, GEMM_BK,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+  CUtensorMap tmB = B_MN ? make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, size_t(ldb) * 2, 64, 64,
+                                        CU_TENSOR_MAP_SWIZZLE_128B)
+                         : make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, size_t(ldb) * 2, BN, GEMM_BK,
+                                        CU_TENSOR_MAP_SWIZZLE_128B);
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int grid = tiles < num_sms ? tiles : num_sms;
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
+                                                 accumulate, status);
+  return cudaGetLastError();
+}
+
+template <int BN, int STAGES>
+static cudaError_t dispatch_layout(bool a_mn, bool b_mn, bool out_f32, const void* A, const void* B, void* C,
+                                   const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int accumulate,
+                                   int* status, int num_sms, cudaStream_t stream) {
+#define SB_CASE(AM, BMN, OF)                                                                                      \
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF)                                                                 \
+    return launch_gemm<BN, STAGES, AM, BMN, OF>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, status, num_sms, \
+                                                stream);
+  SB_CASE(false, false, false)
+  SB_CASE(false, false, true)
+  SB_CASE(false, true, false)
+  SB_CASE(false, true, true)
+  SB_CASE(true, false, false)
+  SB_CASE(true, false, true)
+  SB_CASE(true, true, false)
+  SB_CASE(true, true, true)
+#undef SB_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace sb
+
+// C ABI. Leading dimensions are in elements. Returns a cudaError_t value.
+//   a_mn = 0: A is row-major [M, K] (pitch lda);  a_mn = 1: A is stored [K, M] (pitch lda)
+//   b_mn = 0: B is row-major [N, K] (pitch ldb);  b_mn = 1: B is stored [K, N] (pitch ldb)
+// Requirements: base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
+// `status` is a device int that receives a non-zero code if a bounded wait expired.
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* status,
+                            int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  try {
+    if (bn == 256)
+      return (int)sb::dispatch_layout<256, 4>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb, ldc,
+                                              accumulate, status, num_sms, stream);
+    return (int)sb::dispatch_layout<128, 6>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb, ldc,
+                                            accumulate, status, num_sms, stream);
+  } catch (const std::exception&) {
+    return (int)cudaErrorInvalidValue;
+  }
+}

@@ -1,0 +1,489 @@
+"""Fused ops of the training backend and rollout engine.
+
+CUDA tensors run the hand-written sm_100a kernels (``csrc/*.cu`` through
+``_lib``); CPU tensors run the PyTorch definitions in ``reference``. There is no
+silent GPU fallback: a CUDA tensor without the built library raises.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from slime_b200.ops import _lib, reference
+
+P = _lib.ptr
+
+
+def _cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+# ------------------------------------------------------------------------ GEMM
+def _pick_bn(N: int) -> int:
+    w256 = -(-N // 256) * 256
+    w128 = -(-N // 128) * 128
+    return 256 if w256 <= w128 else 128
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, accumulate=False, bn=None):
+    """``out (+)= op(A) @ op(B)^T (+ bias)`` with fp32 accumulation on the tcgen05 tensor cores.
+
+    ``a``: [M, K] row-major, or [K, M] when ``a_mn``; ``b``: [N, K] row-major, or [K, N]
+    when ``b_mn``. bf16 inputs; ``out`` bf16 or fp32 ([M, N], may be a strided row view).
+    """
+    M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
+    assert K == Kb, f"inner dims differ: {K} vs {Kb}"
+    out_dtype = out.dtype if out is not None else (out_dtype or a.dtype)
+    if not _cuda(a):
+        res = reference.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, out_dtype=torch.float32)
+        if out is None:
+            return res.to(out_dtype)
+        if accumulate:
+            out.add_(res.to(out.dtype))
+        else:
+            out.copy_(res.to(out.dtype))
+        return out
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "sm_100a GEMM takes bf16 operands"
+    assert out_dtype in (torch.bfloat16, torch.float32)
+    if a.stride(-1) != 1:
+        a = a.contiguous()
+    if b.stride(-1) != 1:
+        b = b.contiguous()
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    assert out.stride(-1) == 1 and out.shape == (M, N)
+    assert not (accumulate and out.dtype != torch.float32), "accumulate needs an fp32 output"
+    lda, ldb, ldc = a.stride(0), b.stride(0), out.stride(0)
+    assert lda % 8 == 0 and ldb % 8 == 0, "TMA needs 16-byte row pitches (multiples of 8 bf16)"
+    rc = _lib.lib().sb_gemm_bf16(
+        P(a), P(b), P(out), P(bias), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), int(out.dtype == torch.float32),
+        int(accumulate), bn or _pick_bn(N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
+    )  # fmt: skip
+    _lib.check(rc, "sb_gemm_bf16")
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x W^T (+ b). Backward: dx = dy W (B operand MN-major), dW = dy^T x (both MN-major),
+    accumulated straight into ``weight.main_grad`` (fp32) when the parameter has one."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        ctx.has_bias = bias is not None
+        x2 = x.reshape(-1, x.shape[-1])
+        y = gemm(x2, weight, bias=bias)
+        return y.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.stride(-1) != 1 or (dy2.is_cuda and dy2.stride(0) % 8 != 0):
+            dy2 = dy2.contiguous()
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).view_as(x)
+        if ctx.needs_input_grad[1]:
+            main_grad = getattr(weight, "main_grad", None)
+            if main_grad is not None:
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                dw = None
+                weight.grad_added_to_main_grad = True
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy.dtype)
+        return dx, dw, db
+
+
+def linear(x, weight, bias=None):
+    return _Linear.apply(x, weight, bias)
+
+
+# --------------------------------------------------------------------- RMSNorm
+def _norm_ctas(device) -> int:
+    return 2 * _lib.sm_count(device)
+
+
+class _RMSNorm(torch.autograd.Function):
+    """(y, h) = (rmsnorm(x + residual) * w, x + residual). The norm is computed from the
+    un-rounded fp32 sum, matching the rollout engine's fused add+norm."""
+
+    @staticmethod
+    def forward(ctx, x, weight, residual, eps):
+        shape = x.shape
+        H = shape[-1]
+        x2 = x.reshape(-1, H)
+        T = x2.shape[0]
+        if not _cuda(x):
+            y, h, rstd = reference.rmsnorm(x2, weight, eps, None if residual is None else residual.reshape(-1, H))
+            h = x2 if h is None else h
+        else:
+            x2 = x2.contiguous()
+            r2 = None if residual is None else residual.reshape(-1, H).contiguous()
+            y = torch.empty_like(x2)
+            h = torch.empty_like(x2) if r2 is not None else x2
+            rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+            rc = _lib.lib().sb_rmsnorm_fwd(P(x2), P(r2), P(weight), P(y), P(h) if r2 is not None else None, P(rstd), T, H,
+                                           float(eps), _lib.stream())
+            _lib.check(rc, "sb_rmsnorm_fwd")
+        ctx.save_for_backward(h, weight, rstd)
+        ctx.has_res = residual is not None
+        ctx.shape = shape
+        return y.view(shape), h.view(shape)
+
+    @staticmethod
+    def backward(ctx, dy, dh_in):
+        h, weight, rstd = ctx.saved_tensors
+        H = h.shape[-1]
+        T = h.shape[0]
+        dy2 = dy.reshape(-1, H)
+        dres = None if dh_in is None else dh_in.reshape(-1, H)
+        if not _cuda(dy):
+            hf, dyf, wf = h.float(), dy2.float(), weight.float()
+            xhat = hf * rstd[:, None]
+            dyw = dyf * wf
+            dot = (dyw * xhat).mean(-1, keepdim=True)
+            dh = rstd[:, None] * (dyw - xhat * dot)
+            if dres is not None:
+                dh = dh + dres.float()
+            dw = (dyf * xhat).sum(0)
+            dh = dh.to(dy.dtype)
+        else:
+            dy2 = dy2.contiguous()
+            dres = None if dres is None else dres.contiguous()
+            dh = torch.empty_like(h)
+            n = min(_norm_ctas(dy.device), max(T, 1))
+            part = torch.empty(n, H, dtype=torch.float32, device=dy.device)
+            dw = torch.empty(H, dtype=torch.float32, device=dy.device)
+            rc = _lib.lib().sb_rmsnorm_bwd(P(dy2), P(h), P(weight), P(rstd), P(dres), P(dh), P(part), P(dw), T, H, n, 0,
+                                           _lib.stream())
+            _lib.check(rc, "sb_rmsnorm_bwd")
+        main_grad = getattr(weight, "main_grad", None)
+        if main_grad is not None:
+            main_grad.add_(dw)
+            weight.grad_added_to_main_grad = True
+            dw_out = None
+        else:
+            dw_out = dw.to(weight.dtype)
+        dh = dh.view(ctx.shape)
+        return dh, dw_out, (dh if ctx.has_res else None), None
+
+
+def rmsnorm(x, weight, eps=1e-6, residual=None):
+    """Returns ``(normed, summed)`` where ``summed = x + residual`` (or ``x`` itself)."""
+    return _RMSNorm.apply(x, weight, residual, eps)
+
+
+# ------------------------------------------------------------------------ RoPE
+def rope_cos_sin(max_pos, dim, base, device=None, scaling_factor=1.0):
+    return reference.rope_cos_sin(max_pos, dim, base, device=device, scaling_factor=scaling_factor)
+
+
+def _rope_launch(x, out, positions, cos_sin, nw, rstd, nheads, head0, D, eps, sign):
+    T = x.shape[0]
+    rc = _lib.lib().sb_rope(P(x), P(out), P(positions), P(cos_sin), P(nw), P(rstd), T, nheads, head0, x.stride(0),
+                            out.stride(0), D, float(eps), float(sign), _lib.stream())
+    _lib.check(rc, "sb_rope")
+
+
+class _RopeQK(torch.autograd.Function):
+    """In a packed ``[T, (Hq + 2 Hkv) * D]`` qkv row: (per-head RMSNorm +) RoPE on the q and k heads,
+    v copied through. Output is a new tensor of the same layout."""
+
+    @staticmethod
+    def forward(ctx, qkv, positions, cos_sin, q_norm_w, k_norm_w, Hq, Hkv, D, eps):
+        T = qkv.shape[0]
+        has_norm = q_norm_w is not None
+        if not _cuda(qkv):
+            x = qkv.view(T, Hq + 2 * Hkv, D)
+            q = reference.rope(x[:, :Hq], positions, cos_sin, q_norm_w, eps)
+            k = reference.rope(x[:, Hq : Hq + Hkv], positions, cos_sin, k_norm_w, eps)
+            out = torch.cat([q, k, x[:, Hq + Hkv :]], dim=1).reshape(T, -1)
+        else:
+            qkv = qkv.contiguous()
+            out = torch.empty_like(qkv)
+            _rope_launch(qkv, out, positions, cos_sin, q_norm_w, None, Hq, 0, D, eps, 1.0)
+            _rope_launch(qkv, out, positions, cos_sin, k_norm_w, None, Hkv, Hq, D, eps, 1.0)
+            out.view(T, Hq + 2 * Hkv, D)[:, Hq + Hkv :].copy_(qkv.view(T, Hq + 2 * Hkv, D)[:, Hq + Hkv :])
+        ctx.save_for_backward(qkv if has_norm else None, positions, cos_sin, q_norm_w, k_norm_w)
+        ctx.dims = (Hq, Hkv, D, eps)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, positions, cos_sin, q_norm_w, k_norm_w = ctx.saved_tensors
+        Hq, Hkv, D, eps = ctx.dims
+        T = dout.shape[0]
+        dout = dout.contiguous()
+        d3 = dout.view(T, Hq + 2 * Hkv, D)
+        # inverse rotation of the incoming gradient
+        if not _cuda(dout):
+            dq = reference.rope(d3[:, :Hq], positions, cos_sin, None, eps, sign=-1.0)
+            dk = reference.rope(d3[:, Hq : Hq + Hkv], positions, cos_sin, None, eps, sign=-1.0)
+        else:
+            tmp = torch.empty_like(dout)
+            _rope_launch(dout, tmp, positions, cos_sin, None, None, Hq + Hkv, 0, D, eps, -1.0)
+            t3 = tmp.view(T, Hq + 2 * Hkv, D)
+            dq, dk = t3[:, :Hq], t3[:, Hq : Hq + Hkv]
+        dqw = dkw = None
+        if q_norm_w is not None:
+            x3 = qkv.view(T, Hq + 2 * Hkv, D)
+            dq, dqw = _head_norm_bwd(x3[:, :Hq], dq, q_norm_w, eps)
+            dk, dkw = _head_norm_bwd(x3[:, Hq : Hq + Hkv], dk, k_norm_w, eps)
+        dqkv = torch.cat([dq.to(dout.dtype), dk.to(dout.dtype), d3[:, Hq + Hkv :]], dim=1).reshape(T, -1)
+        return dqkv, None, None, dqw, dkw, None, None, None, None
+
+
+def _head_norm_bwd(x, dy, w, eps):
+    """Backward of per-head RMSNorm over the last dim (x: [T, H, D]); fp32 math."""
+    D = x.shape[-1]
+    if x.is_cuda:
+        x2 = x.reshape(-1, D).contiguous()
+        dy2 = dy.reshape(-1, D).contiguous()
+        rows = x2.shape[0]
+        rstd = torch.rsqrt(x2.float().pow(2).mean(-1) + eps)
+        dh = torch.empty_like(x2)
+        n = min(_norm_ctas(x.device), max(rows, 1))
+        part = torch.empty(n, D, dtype=torch.float32, device=x.device)
+        dw = torch.empty(D, dtype=torch.float32, device=x.device)
+        rc = _lib.lib().sb_rmsnorm_bwd(P(dy2), P(x2), P(w), P(rstd), None, P(dh), P(part), P(dw), rows, D, n, 0,
+                                       _lib.stream())
+        _lib.check(rc, "sb_rmsnorm_bwd(head)")
+        dx = dh.view(x.shape)
+    else:
+        xf, dyf = x.float(), dy.float()
+        rstd = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+        xhat = xf * rstd
+        dyw = dyf * w.float()
+        dx = rstd * (dyw - xhat * (dyw * xhat).mean(-1, keepdim=True))
+        dw = (dyf * xhat).sum((0, 1))
+    main_grad = getattr(w, "main_grad", None)
+    if main_grad is not None:
+        main_grad.add_(dw)
+        w.grad_added_to_main_grad = True
+        return dx, None
+    return dx, dw.to(w.dtype)
+
+
+def rope_qk(qkv, positions, cos_sin, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, eps=1e-6):
+    return _RopeQK.apply(qkv, positions, cos_sin, q_norm_w, k_norm_w, Hq, Hkv, D, eps)
+
+
+# ---------------------------------------------------------------------- SwiGLU
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        ctx.save_for_backward(gu)
+        if not _cuda(gu):
+            return reference.swiglu(gu)
+        shape = gu.shape
+        F_ = shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * F_).contiguous()
+        act = torch.empty(g2.shape[0], F_, dtype=gu.dtype, device=gu.device)
+        _lib.check(_lib.lib().sb_swiglu_fwd(P(g2), P(act), g2.shape[0], F_, _lib.stream()), "sb_swiglu_fwd")
+        return act.view(*shape[:-1], F_)
+
+    @staticmethod
+    def backward(ctx, dact):
+        (gu,) = ctx.saved_tensors
+        F_ = gu.shape[-1] // 2
+        if not _cuda(gu):
+            g, u, d = gu[..., :F_].float(), gu[..., F_:].float(), dact.float()
+            sg = torch.sigmoid(g)
+            silu = g * sg
+            return torch.cat([d * u * (sg + silu * (1 - sg)), d * silu], dim=-1).to(gu.dtype)
+        g2 = gu.reshape(-1, 2 * F_).contiguous()
+        d2 = dact.reshape(-1, F_).contiguous()
+        dgu = torch.empty_like(g2)
+        _lib.check(_lib.lib().sb_swiglu_bwd(P(g2), P(d2), P(dgu), g2.shape[0], F_, _lib.stream()), "sb_swiglu_bwd")
+        return dgu.view_as(gu)
+
+
+def swiglu(gu):
+    return _SwiGLU.apply(gu)
+
+
+# ------------------------------------------------------------------- embedding
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, table, vocab_lo):
+        ctx.save_for_backward(ids)
+        ctx.table = table
+        ctx.vocab_lo = vocab_lo
+        V, H = table.shape
+        if not _cuda(table):
+            local = ids.long() - vocab_lo
+            ok = (local >= 0) & (local < V)
+            out = table[local.clamp(0, V - 1)]
+            return torch.where(ok[:, None], out, torch.zeros_like(out))
+        ids32 = ids.to(torch.int32).contiguous()
+        out = torch.empty(ids32.numel(), H, dtype=table.dtype, device=table.device)
+        rc = _lib.lib().sb_embedding_fwd(P(ids32), P(table), P(out), ids32.numel(), H, vocab_lo, vocab_lo + V, _lib.stream())
+        _lib.check(rc, "sb_embedding_fwd")
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        (ids,) = ctx.saved_tensors
+        table = ctx.table
+        V, H = table.shape
+        main_grad = getattr(table, "main_grad", None)
+        target = main_grad if main_grad is not None else torch.zeros(V, H, dtype=torch.float32, device=table.device)
+        if not _cuda(table):
+            local = ids.long() - ctx.vocab_lo
+            ok = (local >= 0) & (local < V)
+            target.index_add_(0, local[ok], dout.float()[ok])
+        else:
+            ids32 = ids.to(torch.int32).contiguous()
+            rc = _lib.lib().sb_embedding_bwd(P(ids32), P(dout.contiguous()), P(target), ids32.numel(), H, ctx.vocab_lo,
+                                             ctx.vocab_lo + V, _lib.stream())
+            _lib.check(rc, "sb_embedding_bwd")
+        if main_grad is not None:
+            table.grad_added_to_main_grad = True
+            return None, None, None
+        return None, target.to(table.dtype), None
+
+
+def embedding(ids, table, vocab_lo: int = 0):
+    return _Embedding.apply(ids.reshape(-1), table, vocab_lo)
+
+
+# ------------------------------------------------------------------- attention
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True):
+    """Packed causal GQA attention. q: [T, Hq, D], k/v: [T, Hkv, D]."""
+    from slime_b200.ops import attention
+
+    return attention.varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale, causal)
+
+
+def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None, out=None, splits=None,
+                           workspace=None):
+    """One query token per request over a paged KV cache. q: [B, Hq, D]; caches [slots, Hkv, D]."""
+    B, Hq, D = q.shape
+    Hkv = k_cache.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if not _cuda(q):
+        return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale)
+    if splits is None:
+        ctas = B * Hkv
+        splits = 1 if ctas >= _lib.sm_count(q.device) else min(16, max(1, (2 * _lib.sm_count(q.device)) // max(ctas, 1)))
+    if out is None:
+        out = torch.empty_like(q)
+    if workspace is None:
+        workspace = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)
+    part_o = workspace[: B * Hq * splits * D]
+    part_ml = workspace[B * Hq * splits * D : B * Hq * splits * (D + 2)]
+    rc = _lib.lib().sb_paged_decode(P(q), P(k_cache), P(v_cache), P(block_table), P(seq_lens), P(out), P(part_o), P(part_ml),
+                                    B, Hq, Hkv, D, page_size, block_table.shape[1], q.stride(0), out.stride(0), splits,
+                                    float(scale), _lib.stream())
+    _lib.check(rc, "sb_paged_decode")
+    return out
+
+
+def kv_write(k, v, slots, k_cache, v_cache):
+    """Scatter rows ``k[t], v[t]`` ([T, Hkv*D] views, possibly strided) into cache slot ``slots[t]``."""
+    row = k_cache.shape[1] * k_cache.shape[2]
+    if not _cuda(k):
+        ok = slots >= 0
+        k_cache.view(-1, row)[slots[ok].long()] = k[ok].reshape(-1, row)
+        v_cache.view(-1, row)[slots[ok].long()] = v[ok].reshape(-1, row)
+        return
+    rc = _lib.lib().sb_kv_write(P(k), P(v), P(slots), P(k_cache), P(v_cache), k.shape[0], row, k.stride(0), v.stride(0),
+                                _lib.stream())
+    _lib.check(rc, "sb_kv_write")
+
+
+# -------------------------------------------------------------------- sampling
+def sample(logits, temperature, top_k=None, top_p=None, min_p=None, seeds=None, positions=None, kept_cap=0):
+    """Draw one token per row. Returns ``(token int32 [B], logprob fp32 [B], kept_ids, kept_count)``.
+
+    ``logprob`` is the log-probability of the drawn token under the temperature-scaled
+    distribution, renormalised over the kept set when top-k/top-p/min-p are active.
+    """
+    B, V = logits.shape
+    dev = logits.device
+    token = torch.empty(B, dtype=torch.int32, device=dev)
+    logprob = torch.empty(B, dtype=torch.float32, device=dev)
+    kept_ids = torch.empty(B, kept_cap, dtype=torch.int32, device=dev) if kept_cap > 0 else None
+    kept_count = torch.zeros(B, dtype=torch.int32, device=dev) if kept_cap > 0 else None
+    if not _cuda(logits):
+        from slime_b200.ops.sampling_ref import sample_reference
+
+        return sample_reference(logits, temperature, top_k, top_p, min_p, seeds, positions, kept_cap)
+    assert logits.stride(-1) == 1
+    rc = _lib.lib().sb_sample(P(logits), int(logits.dtype == torch.bfloat16), logits.stride(0), B, V, P(temperature),
+                              P(top_k), P(top_p), P(min_p), P(seeds), P(positions), P(token), P(logprob), P(kept_ids),
+                              P(kept_count), kept_cap, _lib.stream())
+    _lib.check(rc, "sb_sample")
+    return token, logprob, kept_ids, kept_count
+
+
+# ----------------------------------------------------------------- quantisers
+def block_fp8_quant(x, block=(128, 128), pow2_scale=False):
+    if not _cuda(x):
+        return reference.block_fp8_quant(x, block, pow2_scale)
+    x = x.contiguous()
+    M, N = x.shape
+    q = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(-(-M // block[0]), -(-N // block[1]), dtype=torch.float32, device=x.device)
+    rc = _lib.lib().sb_block_fp8_quant(P(x), P(q), P(s), M, N, x.stride(0), q.stride(0), block[0], block[1],
+                                       int(pow2_scale), _lib.stream())
+    _lib.check(rc, "sb_block_fp8_quant")
+    return q, s
+
+
+def block_fp8_dequant(q, scale_inv, block=(128, 128), dtype=torch.bfloat16):
+    if not _cuda(q):
+        return reference.block_fp8_dequant(q, scale_inv, block, dtype)
+    M, N = q.shape
+    out = torch.empty(M, N, dtype=torch.bfloat16, device=q.device)
+    rc = _lib.lib().sb_block_fp8_dequant(P(q.contiguous()), P(scale_inv.contiguous()), P(out), M, N, block[0], block[1],
+                                         _lib.stream())
+    _lib.check(rc, "sb_block_fp8_dequant")
+    return out.to(dtype)
+
+
+def fake_int4_quant(x, group=(1, 32), symmetric=True):
+    """Quant-dequant to INT4 code values; returns (y, scales, zeros)."""
+    if not _cuda(x):
+        return reference.fake_int4(x, group, symmetric)
+    x = x.contiguous()
+    M, N = x.shape
+    gm, gn = group
+    y = torch.empty_like(x)
+    s = torch.empty(-(-M // gm), -(-N // gn), dtype=torch.float32, device=x.device)
+    z = torch.empty_like(s)
+    rc = _lib.lib().sb_fake_int4(P(x), P(y), P(s), P(z), M, N, gm, gn, int(symmetric), _lib.stream())
+    _lib.check(rc, "sb_fake_int4")
+    return y, s, z
+
+
+class FakeInt4STE(torch.autograd.Function):
+    """Fake INT4 in forward, identity in backward (QAT on expert weights)."""
+
+    @staticmethod
+    def forward(ctx, w, group_size):
+        return fake_int4_quant(w.reshape(-1, w.shape[-1]), (1, group_size), True)[0].view_as(w)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+def router_gemm(x, w):
+    """fp32 router logits ``x @ w^T`` with a batch-invariant reduction order (tokens in chunks of 16)."""
+    if not _cuda(x):
+        return x.float() @ w.float().t()
+    x = x.contiguous()
+    T, K = x.shape
+    E = w.shape[0]
+    out = torch.empty(T, E, dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().sb_router_gemm(P(x), P(w), P(out), T, K, E, _lib.stream()), "sb_router_gemm")
+    return out

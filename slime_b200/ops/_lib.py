@@ -1,0 +1,141 @@
+"""ctypes binding of the sm_100a kernel library (``_kernels.so``).
+
+The library is built in-tree by ``slime_b200.ops.build``. On a machine with a GPU
+the kernels are mandatory: a missing or stale library raises instead of silently
+falling back to PyTorch ops. CPU tensors take the PyTorch reference path in
+``slime_b200.ops`` (that is what the CPU test-suite exercises).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "_kernels.so")
+_lock = threading.Lock()
+_lib = None
+_launches = 0  # number of kernel-library calls issued by this process (bench reports it)
+
+c_void_p, c_int, c_long, c_float, c_ulonglong = (
+    ctypes.c_void_p, ctypes.c_int, ctypes.c_long, ctypes.c_float, ctypes.c_ulonglong,
+)  # fmt: skip
+
+P, I, L, F = c_void_p, c_int, c_long, c_float
+
+_SIGS = {
+    "sb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
+    "sb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "sb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, P],
+    "sb_rope": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
+    "sb_swiglu_fwd": [P, P, L, I, P],
+    "sb_swiglu_bwd": [P, P, P, L, I, P],
+    "sb_embedding_fwd": [P, P, P, I, I, I, I, P],
+    "sb_embedding_bwd": [P, P, P, I, I, I, I, P],
+    "sb_add_bf16": [P, P, P, L, P],
+    "sb_sqnorm": [P, L, I, P, I, P, I, P],
+    "sb_adam": [P, P, P, P, I, P, L, F, F, F, F, F, F, F, F, F, P, I, P],
+    "sb_softmax_stats": [P, P, P, I, I, L, I, F, P],
+    "sb_finalize_logprob": [P, P, P, P, I, P],
+    "sb_dlogits": [P, P, P, P, P, P, P, I, I, L, L, I, F, P],
+    "sb_pg_loss": [P, P, P, P, P, P, P, P, I, F, F, F, I, P],
+    "sb_sample": [P, I, L, I, I, P, P, P, P, P, P, P, P, P, P, I, P],
+    "sb_kv_write": [P, P, P, P, P, I, I, I, I, P],
+    "sb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+    "sb_block_fp8_quant": [P, P, P, I, I, L, L, I, I, I, P],
+    "sb_block_fp8_dequant": [P, P, P, I, I, I, I, P],
+    "sb_fake_int4": [P, P, P, P, I, I, I, I, I, P],
+    "sb_router_gemm": [P, P, P, I, I, I, P],
+}
+
+
+class KernelLibraryMissing(RuntimeError):
+    pass
+
+
+def available() -> bool:
+    return os.path.exists(_SO)
+
+
+def lib():
+    """Load (once) and return the kernel library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(_SO):
+                raise KernelLibraryMissing(
+                    f"{_SO} not found: build it with `python -m slime_b200.ops.build` (CUDA tensors need the sm_100a kernels)"
+                )
+            handle = ctypes.CDLL(_SO)
+            for name, argtypes in _SIGS.items():
+                try:
+                    fn = getattr(handle, name)
+                except AttributeError:
+                    continue  # optional symbol groups are bound by their own modules
+                fn.argtypes = argtypes
+                fn.restype = c_int
+            _lib = handle
+    return _lib
+
+
+def bind(name: str, argtypes, restype=c_int):
+    fn = getattr(lib(), name)
+    fn.argtypes = argtypes
+    fn.restype = restype
+    return fn
+
+
+def ptr(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str):
+    global _launches
+    _launches += 1
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with CUDA error {rc}")
+
+
+def launch_count() -> int:
+    return _launches
+
+
+_status = {}
+
+
+def status_word(device) -> torch.Tensor:
+    """Per-device int32 that kernels with bounded waits write a non-zero code into."""
+    key = torch.device(device).index or 0
+    t = _status.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[key] = t
+    return t
+
+
+def check_status(device) -> None:
+    """Host-side check of the bounded-wait status word (synchronises)."""
+    t = status_word(device)
+    code = int(t.item())
+    if code != 0:
+        t.zero_()
+        raise RuntimeError(f"kernel wait limit expired: code={code & 0xff} cta={code >> 8}")
+
+
+_sm_count = {}
+
+
+def sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _sm_count:
+        _sm_count[key] = torch.cuda.get_device_properties(key).multi_processor_count
+    return _sm_count[key]
