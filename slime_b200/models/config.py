@@ -1,0 +1,220 @@
+"""Model architecture description shared by the trainer and the rollout engine.
+
+Built from CLI args (Megatron flag names, cf. scripts/models/*.sh of the
+reference), from a Hugging Face ``config.json``, or from a named preset.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import json
+import os
+from dataclasses import dataclass
+
+
+@dataclass
+class ModelConfig:
+    num_layers: int
+    hidden_size: int
+    num_attention_heads: int
+    num_query_groups: int
+    ffn_hidden_size: int
+    vocab_size: int
+    kv_channels: int | None = None  # head dim
+    norm_epsilon: float = 1e-6
+    rotary_base: float = 10000.0
+    rotary_scaling_factor: float = 1.0
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = True
+    add_qkv_bias: bool = False
+    qk_layernorm: bool = False
+    post_self_attn_layernorm: bool = False  # GLM-4 sandwich norms
+    post_mlp_layernorm: bool = False
+    # MoE
+    num_experts: int | None = None
+    moe_ffn_hidden_size: int | None = None
+    moe_router_topk: int = 2
+    moe_router_score_function: str = "softmax"  # softmax | sigmoid
+    moe_router_pre_softmax: bool = False
+    moe_router_enable_expert_bias: bool = False
+    moe_router_topk_scaling_factor: float | None = None
+    moe_shared_expert_intermediate_size: int | None = None
+    moe_layer_freq: int | list | None = None
+    moe_aux_loss_coeff: float = 0.0
+    norm_topk_prob: bool = True
+    # multi-token prediction (draft head)
+    mtp_num_layers: int | None = None
+    model_arch: str = "qwen2"
+    padded_vocab_size: int | None = None
+    init_method_std: float = 0.02
+
+    def __post_init__(self):
+        if self.kv_channels is None:
+            self.kv_channels = self.hidden_size // self.num_attention_heads
+        if self.padded_vocab_size is None:
+            self.padded_vocab_size = self.vocab_size
+
+    @property
+    def head_dim(self) -> int:
+        return self.kv_channels
+
+    def is_moe_layer(self, layer: int) -> bool:
+        if self.num_experts is None:
+            return False
+        f = self.moe_layer_freq
+        if f is None:
+            return True
+        if isinstance(f, (list, tuple)):
+            return bool(f[layer])
+        return layer % f == 0
+
+    def num_params(self) -> int:
+        h, d = self.hidden_size, self.head_dim
+        attn = h * d * (self.num_attention_heads + 2 * self.num_query_groups) + self.num_attention_heads * d * h
+        if self.add_qkv_bias:
+            attn += d * (self.num_attention_heads + 2 * self.num_query_groups)
+        total = 0
+        for i in range(self.num_layers):
+            total += attn + 2 * h
+            if self.is_moe_layer(i):
+                total += self.num_experts * 3 * h * self.moe_ffn_hidden_size + self.num_experts * h
+                if self.moe_shared_expert_intermediate_size:
+                    total += 3 * h * self.moe_shared_expert_intermediate_size
+            else:
+                total += 3 * h * self.ffn_hidden_size
+        total += self.vocab_size * h * (1 if self.tie_word_embeddings else 2) + h
+        return total
+
+    # -- constructors ---------------------------------------------------------
+    @classmethod
+    def from_args(cls, args) -> "ModelConfig":
+        names = {f.name for f in dataclasses.fields(cls)}
+        kw = {k: getattr(args, k) for k in names if getattr(args, k, None) is not None}
+        kw["tie_word_embeddings"] = not getattr(args, "untie_embeddings_and_output_weights", False)
+        kw.setdefault("model_arch", getattr(args, "model_arch", None) or "qwen2")
+        for req in ("num_layers", "hidden_size", "num_attention_heads", "vocab_size"):
+            if req not in kw:
+                raise ValueError(f"--{req.replace('_', '-')} is required (or give --hf-checkpoint with a config.json)")
+        kw.setdefault("num_query_groups", kw["num_attention_heads"])
+        kw.setdefault("ffn_hidden_size", 4 * kw["hidden_size"])
+        return cls(**kw)
+
+    @classmethod
+    def from_hf(cls, path_or_dict) -> "ModelConfig":
+        if isinstance(path_or_dict, dict):
+            c = path_or_dict
+        else:
+            with open(os.path.join(path_or_dict, "config.json")) as f:
+                c = json.load(f)
+        c = c.get("text_config", c)
+        arch = (c.get("architectures") or [c.get("model_type", "qwen2")])[0]
+        a = arch.lower()
+        kw = dict(
+            num_layers=c["num_hidden_layers"],
+            hidden_size=c["hidden_size"],
+            num_attention_heads=c["num_attention_heads"],
+            num_query_groups=c.get("num_key_value_heads", c["num_attention_heads"]),
+            ffn_hidden_size=c.get("intermediate_size", 4 * c["hidden_size"]),
+            vocab_size=c["vocab_size"],
+            kv_channels=c.get("head_dim"),
+            norm_epsilon=c.get("rms_norm_eps", 1e-6),
+            rotary_base=c.get("rope_theta", 10000.0),
+            max_position_embeddings=c.get("max_position_embeddings", 32768),
+            tie_word_embeddings=c.get("tie_word_embeddings", False),
+            add_qkv_bias=c.get("attention_bias", a.startswith("qwen2")),
+            qk_layernorm=a.startswith("qwen3"),
+            model_arch=arch,
+        )
+        if c.get("num_experts") or c.get("n_routed_experts"):
+            kw.update(
+                num_experts=c.get("num_experts") or c.get("n_routed_experts"),
+                moe_ffn_hidden_size=c.get("moe_intermediate_size"),
+                moe_router_topk=c.get("num_experts_per_tok", 2),
+                norm_topk_prob=c.get("norm_topk_prob", True),
+            )
+            if c.get("shared_expert_intermediate_size"):
+                kw["moe_shared_expert_intermediate_size"] = c["shared_expert_intermediate_size"]
+        return cls(**kw)
+
+    def to_hf_dict(self) -> dict:
+        moe = self.num_experts is not None
+        arch = self.model_arch if self.model_arch.endswith("ForCausalLM") else {
+            "qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM", "qwen3_moe": "Qwen3MoeForCausalLM",
+            "llama": "LlamaForCausalLM",
+        }.get(self.model_arch, "Qwen2ForCausalLM")  # fmt: skip
+        d = {
+            "architectures": [arch],
+            "model_type": {"Qwen2ForCausalLM": "qwen2", "Qwen3ForCausalLM": "qwen3", "Qwen3MoeForCausalLM": "qwen3_moe",
+                           "LlamaForCausalLM": "llama"}.get(arch, "qwen2"),
+            "num_hidden_layers": self.num_layers,
+            "hidden_size": self.hidden_size,
+            "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_query_groups,
+            "intermediate_size": self.ffn_hidden_size,
+            "vocab_size": self.vocab_size,
+            "head_dim": self.head_dim,
+            "rms_norm_eps": self.norm_epsilon,
+            "rope_theta": self.rotary_base,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": self.add_qkv_bias,
+            "hidden_act": "silu",
+            "torch_dtype": "bfloat16",
+        }  # fmt: skip
+        if moe:
+            d.update(num_experts=self.num_experts, moe_intermediate_size=self.moe_ffn_hidden_size,
+                     num_experts_per_tok=self.moe_router_topk, norm_topk_prob=self.norm_topk_prob)  # fmt: skip
+        return d
+
+
+PRESETS: dict[str, dict] = {
+    # Qwen2.5-0.5B: 24L, hidden 896, 14 Q / 2 KV heads x 64, FFN 4864, tied, qkv bias
+    "qwen2.5-0.5b": dict(num_layers=24, hidden_size=896, num_attention_heads=14, num_query_groups=2, kv_channels=64,
+                         ffn_hidden_size=4864, vocab_size=151936, rotary_base=1e6, norm_epsilon=1e-6,
+                         tie_word_embeddings=True, add_qkv_bias=True, model_arch="Qwen2ForCausalLM"),
+    "qwen3-0.6b": dict(num_layers=28, hidden_size=1024, num_attention_heads=16, num_query_groups=8, kv_channels=128,
+                       ffn_hidden_size=3072, vocab_size=151936, rotary_base=1e6, tie_word_embeddings=True,
+                       qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
+    "qwen3-4b": dict(num_layers=36, hidden_size=2560, num_attention_heads=32, num_query_groups=8, kv_channels=128,
+                     ffn_hidden_size=9728, vocab_size=151936, rotary_base=1e6, tie_word_embeddings=True,
+                     qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
+    "qwen3-8b": dict(num_layers=36, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128,
+                     ffn_hidden_size=12288, vocab_size=151936, rotary_base=1e6, tie_word_embeddings=False,
+                     qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
+    "qwen3-32b": dict(num_layers=64, hidden_size=5120, num_attention_heads=64, num_query_groups=8, kv_channels=128,
+                      ffn_hidden_size=25600, vocab_size=151936, rotary_base=1e6, tie_word_embeddings=False,
+                      qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
+    "qwen3-30b-a3b": dict(num_layers=48, hidden_size=2048, num_attention_heads=32, num_query_groups=4, kv_channels=128,
+                          ffn_hidden_size=6144, vocab_size=151936, rotary_base=1e6, tie_word_embeddings=False,
+                          qk_layernorm=True, num_experts=128, moe_ffn_hidden_size=768, moe_router_topk=8,
+                          model_arch="Qwen3MoeForCausalLM"),
+    "llama-3.2-1b": dict(num_layers=16, hidden_size=2048, num_attention_heads=32, num_query_groups=8, kv_channels=64,
+                         ffn_hidden_size=8192, vocab_size=128256, rotary_base=5e5, tie_word_embeddings=True,
+                         model_arch="LlamaForCausalLM"),
+    "glm4-9b": dict(num_layers=40, hidden_size=4096, num_attention_heads=32, num_query_groups=2, kv_channels=128,
+                    ffn_hidden_size=13696, vocab_size=151552, rotary_base=1e4, tie_word_embeddings=False,
+                    add_qkv_bias=True, post_self_attn_layernorm=True, post_mlp_layernorm=True,
+                    model_arch="Glm4ForCausalLM"),
+    "tiny": dict(num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=64,
+                 ffn_hidden_size=256, vocab_size=512, rotary_base=1e4, tie_word_embeddings=True, add_qkv_bias=True,
+                 model_arch="Qwen2ForCausalLM"),
+    "tiny-moe": dict(num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=64,
+                     ffn_hidden_size=256, vocab_size=512, rotary_base=1e4, tie_word_embeddings=False,
+                     qk_layernorm=True, num_experts=8, moe_ffn_hidden_size=64, moe_router_topk=2,
+                     model_arch="Qwen3MoeForCausalLM"),
+}  # fmt: skip
+
+
+def get_preset(name: str) -> ModelConfig:
+    key = name.lower()
+    if key not in PRESETS:
+        raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
+    return ModelConfig(**PRESETS[key])
+
+
+def apply_to_args(cfg: ModelConfig, args) -> None:
+    """Copy the architecture into an args namespace under the Megatron flag names."""
+    for f in dataclasses.fields(cfg):
+        setattr(args, f.name, getattr(cfg, f.name))
+    args.untie_embeddings_and_output_weights = not cfg.tie_word_embeddings
+    args.swiglu = True
