@@ -1,0 +1,526 @@
+"""Continuous-batching rollout engine (in-process core).
+
+One ``Engine`` owns the weights, the paged KV cache and a scheduler. ``step()`` either admits
+waiting requests and runs a (chunked) prefill over their un-cached tokens, or runs one decode
+step for every running request; finished requests free their pages (complete pages stay
+indexed for prefix reuse). ``generate()`` is the blocking convenience wrapper; the HTTP server
+drives ``step()`` from its scheduler thread.
+
+This is the component that replaces the SGLang server process of the reference
+(slime/backends/sglang_utils/sglang_engine.py:88-503 is only its HTTP client); the control
+surface it must offer is: generate (with logprobs), abort, pause / continue, flush cache,
+release / resume memory by tag (weights | kv_cache | cuda_graph), weight update and versioning.
+"""
+
+from __future__ import annotations
+
+import threading
+import time
+import uuid
+
+import torch
+
+from slime_b200 import ops
+from slime_b200.engine.kv_cache import OutOfPages, PagedKVCache, _hash_block
+from slime_b200.engine.model_runner import EngineWeights, ModelRunner
+from slime_b200.engine.request import ReqState, Request, SamplingParams
+from slime_b200.engine.server_args import ServerArgs
+from slime_b200.models.config import ModelConfig
+
+MEMORY_TAGS = ("weights", "kv_cache", "cuda_graph")
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, server_args: ServerArgs | None = None, device=None, tokenizer=None,
+                 num_pages: int | None = None, tp_group=None, tp_size: int = 1, tp_rank: int = 0):  # fmt: skip
+        self.cfg = cfg
+        self.args = server_args or ServerArgs()
+        self.device = torch.device(device) if device is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        )
+        self.dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
+        self.tokenizer = tokenizer
+        self.eos_ids = set()
+        if tokenizer is not None and getattr(tokenizer, "eos_token_id", None) is not None:
+            self.eos_ids.add(tokenizer.eos_token_id)
+        self.weights = EngineWeights(cfg, self.dtype, self.device, tp_size, tp_rank)
+        self.max_context = self.args.context_length or min(cfg.max_position_embeddings, 32768)
+        self.page_size = self.args.page_size
+        self.max_running = self.args.max_running_requests
+        if num_pages is None:
+            num_pages = self._pages_from_memory()
+        self.num_pages = num_pages
+        self.kv = PagedKVCache(cfg.num_layers, self.weights.hkv, cfg.head_dim, num_pages, self.page_size, self.dtype,
+                               self.device, enable_prefix_cache=not self.args.disable_radix_cache)  # fmt: skip
+        self.runner = ModelRunner(cfg, self.weights, self.kv, self.max_running, self.max_context,
+                                  use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
+        self.runner._alloc_static()
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self.prefilling: list[Request] = []
+        self.paused = False
+        self.released: set[str] = set()
+        self.lock = threading.RLock()
+        self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0, "aborted": 0,
+                      "h2d_bytes": 0, "d2h_bytes": 0}
+        self._deferred_removals = None
+
+    # ----------------------------------------------------------------- sizing
+    def _pages_from_memory(self) -> int:
+        per_page = PagedKVCache.bytes_per_page(self.cfg.num_layers, self.weights.hkv, self.cfg.head_dim, self.page_size, self.dtype)
+        if self.args.max_total_tokens:
+            return max(8, self.args.max_total_tokens // self.page_size)
+        if self.device.type != "cuda":
+            return 512
+        free, total = torch.cuda.mem_get_info(self.device)
+        budget = int(total * self.args.mem_fraction_static) - (total - free)
+        return max(64, budget // per_page)
+
+    # ------------------------------------------------------------------ intake
+    def add_request(self, input_ids, sampling: SamplingParams | dict | None = None, rid: str | None = None, **kw) -> Request:
+        sp = sampling if isinstance(sampling, SamplingParams) else SamplingParams.from_dict(sampling)
+        req = Request(rid=rid or uuid.uuid4().hex, input_ids=list(input_ids), sampling=sp, **kw)
+        req.seed = sp.sampling_seed if sp.sampling_seed is not None else (self.args.random_seed * 1000003 + hash(req.rid)) & 0x7FFFFFFFFFFF
+        room = self.max_context - len(req.input_ids)
+        if room <= 0:
+            self._finish(req, {"type": "length", "length": 0})
+            return req
+        sp.max_new_tokens = max(0, min(sp.max_new_tokens, room))
+        req.weight_version = self.weights.version
+        with self.lock:
+            self.waiting.append(req)
+        return req
+
+    # -------------------------------------------------------------- scheduling
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running or self.prefilling)
+
+    def num_requests(self) -> int:
+        return len(self.waiting) + len(self.running) + len(self.prefilling)
+
+    def step(self) -> list[Request]:
+        """Run one engine iteration; returns requests that finished in it."""
+        with self.lock:
+            if self.paused or "kv_cache" in self.released or "weights" in self.released:
+                return []
+            self.stats["steps"] += 1
+            batch = self._admit()
+            if batch:
+                return self._run_prefill(batch)
+            if self.running:
+                return self._run_decode()
+            return []
+
+    def _admit(self) -> list[tuple[Request, int]]:
+        """Pick requests (and how many of their tokens) for this step's prefill, within the token budget."""
+        budget = self.args.max_prefill_tokens
+        batch: list[tuple[Request, int]] = []
+        pending_first_hash = set()
+        ps = self.page_size
+        # continue chunked prefills first
+        for req in list(self.prefilling):
+            todo = len(req.input_ids) - req.num_computed
+            n = min(todo, budget, self.args.chunked_prefill_size)
+            if n <= 0:
+                break
+            batch.append((req, n))
+            budget -= n
+        still_waiting = []
+        for req in self.waiting:
+            if budget <= 0 or len(self.running) + len(self.prefilling) + len([b for b in batch if b[0].state == ReqState.WAITING]) >= self.max_running:
+                still_waiting.append(req)
+                continue
+            if req.sampling.max_new_tokens == 0 and req.logprob_start_len < 0:
+                self._finish(req, {"type": "length", "length": 0})
+                continue
+            # siblings of a prompt being prefilled right now wait one step and then hit the prefix cache
+            first = _hash_block(b"", req.input_ids[:ps]) if len(req.input_ids) > ps else None
+            if first is not None and first in pending_first_hash:
+                still_waiting.append(req)
+                continue
+            want_cache = req.logprob_start_len < 0  # input log-probs need every position computed
+            pages, chain = self.kv.allocator.match_prefix(req.input_ids) if want_cache else ([], b"")
+            cached = len(pages) * ps
+            need_tokens = len(req.input_ids) - cached
+            total_pages = -(-(len(req.input_ids) + 1) // ps)
+            try:
+                new_pages = self.kv.allocator.alloc(total_pages - len(pages))
+            except OutOfPages:
+                self.kv.allocator.release(pages)
+                still_waiting.append(req)
+                budget = 0
+                continue
+            req.pages = pages + new_pages
+            req.num_cached_tokens = req.num_computed = cached
+            req.committed_pages, req.chain_hash = len(pages), chain
+            req.first_scheduled = time.time()
+            n = min(need_tokens, budget, self.args.chunked_prefill_size)
+            batch.append((req, n))
+            budget -= n
+            self.stats["cached_tokens"] += cached
+            if first is not None and cached == 0:
+                pending_first_hash.add(first)
+        self.waiting = still_waiting
+        return batch
+
+    def _slots(self, req: Request, start: int, end: int) -> list[int]:
+        ps = self.page_size
+        return [req.pages[p // ps] * ps + p % ps for p in range(start, end)]
+
+    def _run_prefill(self, batch) -> list[Request]:
+        dev = self.device
+        ids, pos, slots, cu_q, cu_k, gather, last_rows, samplers = [], [], [], [0], [0], [], [], []
+        fresh, max_q, max_k = True, 0, 0
+        want_all_rows = any(r.logprob_start_len >= 0 for r, _ in batch)
+        for req, n in batch:
+            s, e = req.num_computed, req.num_computed + n
+            ids += req.input_ids[s:e]
+            pos += list(range(s, e))
+            slots += self._slots(req, s, e)
+            cu_q.append(cu_q[-1] + n)
+            cu_k.append(cu_k[-1] + e)
+            gather += self._slots(req, 0, e)
+            fresh &= s == 0
+            max_q, max_k = max(max_q, n), max(max_k, e)
+            if e == len(req.input_ids):
+                last_rows.append(cu_q[-1] - 1)
+                samplers.append(req)
+            if req.state == ReqState.WAITING:
+                req.state = ReqState.RUNNING
+                self.prefilling.append(req)
+        def t(x, dt=torch.int32):
+            host = torch.tensor(x, dtype=dt)
+            self.stats["h2d_bytes"] += host.numel() * host.element_size()
+            if dev.type == "cuda":
+                host = host.pin_memory()
+            return host.to(dev, non_blocking=True)
+
+        rows = None if want_all_rows else t(last_rows, torch.long)
+        logits = self.runner.prefill(t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long),
+                                     t(cu_k), max_q, max_k, rows, fresh)  # fmt: skip
+        self.stats["prefill_tokens"] += len(ids)
+        if want_all_rows:
+            self._record_input_logprobs(batch, logits, cu_q)
+            logits = logits.index_select(0, t(last_rows, torch.long))
+        for req, n in batch:
+            req.num_computed += n
+            self._commit_pages(req)
+        finished = []
+        if samplers:
+            toks, lps, kept_ids, kept_cnt = self._sample_rows(logits, samplers)
+            for i, req in enumerate(samplers):
+                self.prefilling.remove(req)
+                if req.sampling.max_new_tokens == 0:
+                    self._finish(req, {"type": "length", "length": 0})
+                    finished.append(req)
+                    continue
+                req.first_token_time = time.time()
+                if self._append_token(req, toks[i], lps[i], kept_ids, kept_cnt, i):
+                    finished.append(req)
+                else:
+                    self._start_decoding(req)
+        return finished
+
+    def _record_input_logprobs(self, batch, logits, cu_q):
+        lsm = torch.log_softmax(logits.float(), -1)
+        for (req, n), a, b in zip(batch, cu_q[:-1], cu_q[1:]):
+            if req.logprob_start_len < 0:
+                continue
+            s = req.num_computed
+            nxt = torch.tensor(req.input_ids[s + 1 : s + n + 1], device=logits.device, dtype=torch.long)
+            rows = lsm[a : a + nxt.numel()]
+            vals = rows.gather(-1, nxt[:, None]).squeeze(-1).tolist()
+            if req.input_logprobs is None:
+                req.input_logprobs = [None]  # the first token has no conditional probability
+            req.input_logprobs += vals
+
+    def _sample_rows(self, logits, reqs):
+        dev = logits.device
+        n = len(reqs)
+        f = lambda xs, dt: torch.tensor(xs, dtype=dt, device=dev)  # noqa: E731
+        temp = f([r.sampling.temperature for r in reqs], torch.float32)
+        filtered = any(r.sampling.top_k > 0 or r.sampling.top_p < 1.0 or r.sampling.min_p > 0 for r in reqs)
+        cap = 4096 if any(r.sampling.return_top_p_token_ids for r in reqs) and filtered else 0
+        tk = f([max(r.sampling.top_k, 0) for r in reqs], torch.int32) if filtered else None
+        tp = f([r.sampling.top_p for r in reqs], torch.float32) if filtered else None
+        mp = f([r.sampling.min_p for r in reqs], torch.float32) if filtered else None
+        seeds = f([r.seed for r in reqs], torch.int64)
+        pos = f([len(r.output_ids) for r in reqs], torch.int32)
+        tok, lp, kept_ids, kept_cnt = ops.sample(logits[:n], temp, tk, tp, mp, seeds, pos, cap)
+        return tok.tolist(), lp.tolist(), (kept_ids.cpu() if kept_ids is not None else None), (
+            kept_cnt.tolist() if kept_cnt is not None else None
+        )
+
+    # Rows of the decode buffers: ``running[b]`` owns row ``b``. Rows are written in full when a
+    # request starts decoding and advanced with vectorised numpy updates afterwards.
+    def _row_init(self, b: int, r: Request):
+        h = self.runner.host
+        L = r.seq_len
+        h["ids"][b] = r.output_ids[-1] if r.output_ids else r.input_ids[-1]
+        h["positions"][b] = L - 1
+        h["seq_lens"][b] = L
+        h["top_k"][b] = max(r.sampling.top_k, 0)
+        h["out_pos"][b] = len(r.output_ids)
+        h["temperature"][b] = r.sampling.temperature
+        h["top_p"][b] = r.sampling.top_p
+        h["min_p"][b] = r.sampling.min_p
+        h["seeds"][b] = r.seed
+        bt = h["block_table"][b]
+        bt[:] = 0
+        bt[: len(r.pages)] = r.pages
+
+    def _row_clear(self, b: int):
+        h = self.runner.host
+        for k in ("ids", "positions", "top_k", "out_pos"):
+            h[k][b] = 0
+        h["seq_lens"][b] = 1
+        h["block_table"][b, :] = 0
+
+    def _start_decoding(self, r: Request):
+        self._row_init(len(self.running), r)
+        self.running.append(r)
+
+    def _remove_running(self, r: Request):
+        b = self.running.index(r)
+        last = len(self.running) - 1
+        if b != last:
+            mover = self.running[last]
+            self.running[b] = mover
+            self._row_init(b, mover)
+        self.running.pop()
+        self._row_clear(last)
+
+    def _run_decode(self) -> list[Request]:
+        import numpy as np
+
+        finished = []
+        ps = self.page_size
+        h = self.runner.host
+        # a request whose next token starts a new page needs that page now; if the cache is full the
+        # youngest requests are retracted (their KV is recomputed when they are re-admitted)
+        i = 0
+        while i < len(self.running):
+            r = self.running[i]
+            if r.seq_len % ps == 0 and len(r.pages) * ps <= r.seq_len:
+                try:
+                    r.pages += self.kv.allocator.alloc(1)
+                    h["block_table"][i, len(r.pages) - 1] = r.pages[-1]
+                except OutOfPages:
+                    victim = self.running[-1]
+                    self._remove_running(victim)
+                    self._retract(victim)
+                    continue
+            i += 1
+        reqs = self.running
+        n = len(reqs)
+        if n == 0:
+            return finished
+        filtered = bool((h["top_k"][:n] > 0).any() or (h["top_p"][:n] < 1.0).any() or (h["min_p"][:n] > 0).any())
+        cap = 4096 if filtered and any(r.sampling.return_top_p_token_ids for r in reqs) else 0
+        self.runner.upload_static()
+        self.stats["h2d_bytes"] += self.runner._flat_host.numel() * 4
+        tok, lp, kept_ids, kept_cnt = self.runner.decode(n, filtered, cap)
+        toks_t, lps_t = tok[:n].cpu(), lp[:n].cpu()
+        self.stats["d2h_bytes"] += 8 * n
+        toks, lps = toks_t.tolist(), lps_t.tolist()
+        kept_ids = kept_ids[:n].cpu() if kept_ids is not None else None
+        kept_cnt = kept_cnt[:n].tolist() if kept_cnt is not None else None
+        self.stats["decode_tokens"] += n
+        # advance every row: the sampled token becomes the next input
+        h["ids"][:n] = toks_t.numpy()
+        h["positions"][:n] += 1
+        h["seq_lens"][:n] += 1
+        h["out_pos"][:n] += 1
+        # rows are compacted only after every request has taken its token: a row moved into a freed
+        # slot is rebuilt from its request's (by then final) state
+        self._deferred_removals = []
+        for i, r in enumerate(list(reqs)):
+            r.num_computed = r.seq_len  # the fed token's KV is now cached
+            if r.num_computed % ps == 0:
+                self._commit_pages(r)
+            if self._append_token(r, toks[i], lps[i], kept_ids, kept_cnt, i):
+                finished.append(r)
+        deferred, self._deferred_removals = self._deferred_removals, None
+        for r in deferred:
+            self._remove_running(r)
+        return finished
+
+    def _retract(self, req: Request):
+        """Return a running request to the queue (its KV is dropped; tokens so far are kept as prompt)."""
+        self.kv.allocator.release(req.pages)
+        req.pages, req.num_computed, req.committed_pages, req.chain_hash = [], 0, 0, b""
+        req.state = ReqState.WAITING
+        self.waiting.insert(0, req)
+
+    def _commit_pages(self, req: Request):
+        """Index every page that became full and whose KV is written (committed tokens only)."""
+        ps = self.page_size
+        ids = None
+        while (req.committed_pages + 1) * ps <= req.num_computed:
+            ids = ids or req.all_ids()
+            i = req.committed_pages
+            req.chain_hash = self.kv.allocator.commit(req.pages[i], req.chain_hash, ids[i * ps : (i + 1) * ps])
+            req.committed_pages += 1
+
+    def _append_token(self, req: Request, tok: int, lp: float, kept_ids, kept_cnt, row: int) -> bool:
+        req.output_ids.append(int(tok))
+        req.output_logprobs.append(float(lp))
+        if kept_cnt is not None and req.sampling.return_top_p_token_ids:
+            c = max(kept_cnt[row], 0)
+            ids = kept_ids[row, :c].tolist() if kept_ids is not None and c > 0 else []
+            req.kept_ids += ids
+            req.kept_offsets.append(len(req.kept_ids))
+        sp = req.sampling
+        n_out = len(req.output_ids)
+        reason = None
+        if n_out >= sp.min_new_tokens:
+            if not sp.ignore_eos and tok in self.eos_ids:
+                reason = {"type": "stop", "matched": int(tok)}
+            elif sp.stop_token_ids and tok in sp.stop_token_ids:
+                reason = {"type": "stop", "matched": int(tok)}
+            elif sp.stop and self.tokenizer is not None:
+                tail = self.tokenizer.decode(req.output_ids[-32:])
+                for s in sp.stop:
+                    if s in tail:
+                        reason = {"type": "stop", "matched": s}
+                        break
+        if reason is None and n_out >= sp.max_new_tokens:
+            reason = {"type": "length", "length": sp.max_new_tokens}
+        if req.on_token is not None:
+            req.on_token(req)
+        if reason is not None:
+            self._finish(req, reason)
+            return True
+        return False
+
+    def _finish(self, req: Request, reason: dict):
+        req.finish_reason = reason
+        req.state = ReqState.FINISHED
+        req.finish_time = time.time()
+        if req in self.running:
+            if self._deferred_removals is not None:
+                self._deferred_removals.append(req)
+            else:
+                self._remove_running(req)
+        if req in self.prefilling:
+            self.prefilling.remove(req)
+        if req.pages:
+            self.kv.allocator.release(req.pages)
+            req.pages = []
+        if req.done_event is not None:
+            req.done_event.set()
+        if req.on_token is not None and reason.get("type") == "abort":
+            req.on_token(req)
+
+    # ---------------------------------------------------------------- control plane
+    def abort(self, rid: str | None = None, abort_all: bool = False) -> int:
+        with self.lock:
+            victims = [r for r in self.waiting + self.prefilling + self.running if abort_all or r.rid == rid]
+            for r in victims:
+                if r in self.waiting:
+                    self.waiting.remove(r)
+                self._finish(r, {"type": "abort"})
+            self.stats["aborted"] += len(victims)
+            return len(victims)
+
+    def pause_generation(self):
+        self.paused = True
+
+    def continue_generation(self):
+        self.paused = False
+
+    def flush_cache(self) -> bool:
+        with self.lock:
+            if self.running or self.prefilling:
+                return False
+            self.kv.allocator.flush()
+            return True
+
+    def release_memory_occupation(self, tags=None):
+        """Idempotent per tag. ``weights`` keeps a pinned host copy only if asked to
+        (the trainer re-syncs weights after every resume, so by default they are simply dropped)."""
+        with self.lock:
+            for tag in tags or MEMORY_TAGS:
+                if tag in self.released:
+                    continue
+                if tag == "kv_cache":
+                    self.abort(abort_all=True)
+                    self.kv.release()
+                elif tag == "cuda_graph":
+                    self.runner.drop_graphs()
+                elif tag == "weights":
+                    for t in self.weights.tensors():
+                        t.data = torch.empty(0, dtype=t.dtype, device=t.device)
+                self.released.add(tag)
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+
+    def resume_memory_occupation(self, tags=None):
+        with self.lock:
+            for tag in tags or MEMORY_TAGS:
+                if tag not in self.released:
+                    continue
+                if tag == "kv_cache":
+                    self.kv.allocate()
+                elif tag == "weights":
+                    fresh = EngineWeights(self.cfg, self.dtype, self.device, self.weights.tp, self.weights.rank)
+                    fresh.version = self.weights.version
+                    self.weights = fresh
+                    self.runner.w = fresh
+                    self.runner.drop_graphs()
+                self.released.discard(tag)
+
+    def update_weights(self, named_tensors, version: str | None = None, flush_cache: bool = True):
+        with self.lock:
+            missing = self.weights.load_weights(named_tensors, version)
+            if flush_cache:
+                self.kv.allocator.flush()
+            return missing
+
+    def get_weight_version(self) -> str:
+        return self.weights.version
+
+    def loads(self) -> dict:
+        return {"num_running_reqs": len(self.running) + len(self.prefilling), "num_waiting_reqs": len(self.waiting),
+                "num_reqs": self.num_requests(), **self.kv.allocator.stats()}  # fmt: skip
+
+    # ------------------------------------------------------------------- blocking API
+    def generate(self, prompts: list[list[int]], sampling: list[dict | SamplingParams] | dict | SamplingParams | None = None,
+                 **kw) -> list[Request]:
+        if not isinstance(sampling, list):
+            sampling = [sampling] * len(prompts)
+        reqs = [self.add_request(p, SamplingParams.from_dict(s) if isinstance(s, dict) or s is None else s, **kw)
+                for p, s in zip(prompts, sampling)]  # fmt: skip
+        while any(not r.finished() for r in reqs):
+            if not self.has_work():
+                break
+            self.step()
+        return reqs
+
+    def meta_info(self, req: Request) -> dict:
+        """The ``meta_info`` dict of a finished (or streaming) request, in the wire format slime consumes."""
+        from slime_b200.utils.misc import encode_int32_meta_array
+
+        now = req.finish_time or time.time()
+        e2e = now - req.arrival
+        decode_time = max(now - (req.first_token_time or now), 1e-9)
+        m = {
+            "id": req.rid,
+            "finish_reason": req.finish_reason,
+            "prompt_tokens": len(req.input_ids),
+            "completion_tokens": len(req.output_ids),
+            "cached_tokens": req.num_cached_tokens,
+            "weight_version": req.weight_version,
+            "e2e_latency": e2e,
+            "queue_time": (req.first_scheduled or now) - req.arrival,
+            "decode_throughput": max(len(req.output_ids) - 1, 0) / decode_time,
+            "output_token_logprobs": [(lp, t, None) for lp, t in zip(req.output_logprobs, req.output_ids)],
+        }
+        if req.input_logprobs is not None:
+            m["input_token_logprobs"] = [(lp, t, None) for lp, t in zip(req.input_logprobs, req.input_ids)]
+        if req.sampling.return_top_p_token_ids and len(req.kept_offsets) > 1:
+            m["top_p_token_ids"] = encode_int32_meta_array(req.kept_ids)
+            m["top_p_token_offsets"] = encode_int32_meta_array(req.kept_offsets)
+        if req.return_routed_experts and req.routed_experts:
+            m["routed_experts"] = encode_int32_meta_array(torch.cat(req.routed_experts).reshape(-1))
+        return m

@@ -1,0 +1,161 @@
+"""Paged KV cache with hash-based prefix sharing.
+
+Pages hold ``page_size`` tokens; the per-layer K and V tensors are
+``[num_pages * page_size, Hkv, D]`` (slot = page * page_size + offset). A page whose
+tokens form a complete, committed prefix block is indexed by the hash chain of its
+token ids, so requests that share a prompt prefix (the ``n_samples_per_prompt`` siblings
+of a GRPO group, multi-turn continuations) reuse the same physical pages. Only committed
+KV is indexed, so an aborted / partial request never poisons the index. Unreferenced
+indexed pages stay resident until evicted in LRU order.
+
+The allocator hot path (free list, ref counts, hash index) is native C++ when the
+``_engine_native`` extension is built; this module is the same logic in Python and the
+fallback used by CPU tests.
+"""
+
+from __future__ import annotations
+
+import collections
+import hashlib
+import struct
+
+import torch
+
+
+class OutOfPages(RuntimeError):
+    pass
+
+
+def _hash_block(parent: bytes, tokens) -> bytes:
+    h = hashlib.blake2b(parent, digest_size=16)
+    h.update(struct.pack(f"<{len(tokens)}i", *tokens))
+    return h.digest()
+
+
+class PageAllocator:
+    def __init__(self, num_pages: int, page_size: int, enable_prefix_cache: bool = True):
+        self.num_pages, self.page_size = num_pages, page_size
+        self.enable_prefix_cache = enable_prefix_cache
+        self.free = collections.deque(range(num_pages))
+        self.refcnt = [0] * num_pages
+        self.page_hash: list[bytes | None] = [None] * num_pages
+        self.index: dict[bytes, int] = {}
+        self.lru: collections.OrderedDict[int, None] = collections.OrderedDict()  # refcnt==0 indexed pages
+        self.hits = self.queries = 0
+
+    # ---- capacity --------------------------------------------------------------------
+    def available(self) -> int:
+        return len(self.free) + len(self.lru)
+
+    def _take_page(self) -> int:
+        if self.free:
+            return self.free.popleft()
+        if self.lru:
+            page, _ = self.lru.popitem(last=False)
+            self._unindex(page)
+            return page
+        raise OutOfPages("KV cache exhausted")
+
+    def _unindex(self, page: int):
+        h = self.page_hash[page]
+        if h is not None and self.index.get(h) == page:
+            del self.index[h]
+        self.page_hash[page] = None
+
+    def alloc(self, n: int) -> list[int]:
+        if n > self.available():
+            raise OutOfPages(f"need {n} pages, {self.available()} available")
+        out = []
+        for _ in range(n):
+            p = self._take_page()
+            self.refcnt[p] = 1
+            out.append(p)
+        return out
+
+    def retain(self, page: int):
+        if self.refcnt[page] == 0:
+            self.lru.pop(page, None)
+        self.refcnt[page] += 1
+
+    def release(self, pages):
+        for p in pages:
+            self.refcnt[p] -= 1
+            assert self.refcnt[p] >= 0, f"page {p} released too often"
+            if self.refcnt[p] == 0:
+                if self.page_hash[p] is not None:
+                    self.lru[p] = None
+                else:
+                    self.free.append(p)
+
+    # ---- prefix index -------------------------------------------------------------------
+    def match_prefix(self, tokens: list[int]) -> tuple[list[int], bytes]:
+        """Longest chain of indexed full pages matching ``tokens``; pages are retained for the caller.
+        At least one token is always left uncached so the request still produces logits."""
+        pages, parent = [], b""
+        if not self.enable_prefix_cache:
+            return pages, parent
+        ps = self.page_size
+        full = (len(tokens) - 1) // ps
+        self.queries += full
+        for i in range(full):
+            h = _hash_block(parent, tokens[i * ps : (i + 1) * ps])
+            p = self.index.get(h)
+            if p is None:
+                break
+            self.retain(p)
+            pages.append(p)
+            parent = h
+        self.hits += len(pages)
+        return pages, parent
+
+    def commit(self, page: int, parent: bytes, tokens: list[int]) -> bytes:
+        """Index a full page whose KV has been written. Returns its chain hash."""
+        h = _hash_block(parent, tokens)
+        if self.enable_prefix_cache and h not in self.index and self.page_hash[page] is None:
+            self.index[h] = page
+            self.page_hash[page] = h
+        return h
+
+    def flush(self):
+        """Drop the prefix index (weights changed: cached KV is stale)."""
+        for p in list(self.lru):
+            self.free.append(p)
+        self.lru.clear()
+        self.index.clear()
+        self.page_hash = [None] * self.num_pages
+
+    def stats(self):
+        return {"free": len(self.free), "cached": len(self.lru), "hit_rate": self.hits / max(self.queries, 1)}
+
+
+class PagedKVCache:
+    """Device tensors + allocator. Memory tag ``kv_cache``: released / re-created as a whole."""
+
+    def __init__(self, num_layers, num_kv_heads, head_dim, num_pages, page_size, dtype, device, enable_prefix_cache=True):
+        self.num_layers, self.hkv, self.d = num_layers, num_kv_heads, head_dim
+        self.page_size, self.num_pages, self.dtype, self.device = page_size, num_pages, dtype, device
+        self.allocator = PageAllocator(num_pages, page_size, enable_prefix_cache)
+        self.k: list[torch.Tensor] = []
+        self.v: list[torch.Tensor] = []
+        self.allocate()
+
+    def allocate(self):
+        if self.k:
+            return
+        slots = self.num_pages * self.page_size
+        # one slab per kind so a layer's cache is a contiguous view
+        self._k_slab = torch.zeros(self.num_layers, slots, self.hkv, self.d, dtype=self.dtype, device=self.device)
+        self._v_slab = torch.zeros(self.num_layers, slots, self.hkv, self.d, dtype=self.dtype, device=self.device)
+        self.k = [self._k_slab[i] for i in range(self.num_layers)]
+        self.v = [self._v_slab[i] for i in range(self.num_layers)]
+
+    def release(self):
+        self.k, self.v = [], []
+        self._k_slab = self._v_slab = None
+        self.allocator = PageAllocator(self.num_pages, self.page_size, self.allocator.enable_prefix_cache)
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    @staticmethod
+    def bytes_per_page(num_layers, num_kv_heads, head_dim, page_size, dtype=torch.bfloat16) -> int:
+        return 2 * num_layers * page_size * num_kv_heads * head_dim * torch.empty(0, dtype=dtype).element_size()

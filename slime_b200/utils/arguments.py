@@ -707,4 +707,34 @@ def namespace_from_dict(d: dict[str, Any]) -> argparse.Namespace:
     ns = parser.parse_args(["--rollout-batch-size", str(d.get("rollout_batch_size", 1))])
     for k, v in d.items():
         setattr(ns, k, v)
+    return finalize_namespace(ns)
+
+
+def finalize_namespace(ns: argparse.Namespace) -> argparse.Namespace:
+    """Derived attributes that ``slime_validate_args`` would set, for programmatically built namespaces."""
+    ns.use_critic = ns.advantage_estimator == "ppo"
+    if ns.eps_clip_high is None:
+        ns.eps_clip_high = ns.eps_clip
+    ns.offload_train = bool(ns.offload_train)
+    ns.offload_rollout = bool(ns.offload_rollout)
+    ns.rollout_external = ns.rollout_external_engine_addrs is not None
+    if ns.global_batch_size is None:
+        ns.global_batch_size = ns.rollout_batch_size * ns.n_samples_per_prompt // (ns.num_steps_per_rollout or 1)
+    if ns.over_sampling_batch_size is None:
+        ns.over_sampling_batch_size = ns.rollout_batch_size
+    if ns.use_rollout_routing_replay:
+        ns.use_routing_replay = True
+    if ns.eval_function_path is None:
+        ns.eval_function_path = ns.rollout_function_path
+    if ns.start_rollout_id is None and not ns.load:
+        ns.start_rollout_id = 0
+    if getattr(ns, "offload", None) is not None:
+        del ns.offload
+    if not hasattr(ns, "critic_overrides"):
+        ns.critic_overrides = {"kl_coef": 0.0, "untie_embeddings_and_output_weights": True}
+    if ns.microbatch_group_size_per_vp_stage is None:
+        ns.microbatch_group_size_per_vp_stage = ns.pipeline_model_parallel_size
+    if isinstance(getattr(ns, "moe_layer_freq", None), str):
+        ns.moe_layer_freq = int(ns.moe_layer_freq)
+    ns.eval_datasets = getattr(ns, "eval_datasets", [])
     return ns

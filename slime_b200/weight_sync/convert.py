@@ -1,0 +1,231 @@
+"""Trainer (Megatron-named) <-> Hugging Face tensor naming and layout.
+
+Forward direction (``convert_to_hf``): a *TP-gathered* trainer tensor becomes one or more
+HF tensors: fused qkv -> q_proj / k_proj / v_proj, fused fc1 -> gate_proj / up_proj, expert
+``weight{e}`` -> ``experts.{e}.*``. Parity: slime/backends/megatron_utils/megatron_to_hf/
+(qwen2.py:5-71, qwen3moe.py:6-117, llama.py, glm4.py, glm4moe.py, ...).
+Inverse direction (``hf_to_trainer_name``/``merge_*``) is used by the HF loader
+(slime/backends/megatron_utils/hf_to_megatron/common.py:70-134).
+
+In memory this backend keeps fused qkv rows as [q heads | k heads | v heads]; the Megatron
+on-disk layout interleaves per KV group ``[g][q_per_g*d | d | d]``. ``qkv_to_megatron_layout``
+/ ``qkv_from_megatron_layout`` translate for torch_dist checkpoints.
+"""
+
+from __future__ import annotations
+
+import re
+
+import torch
+
+from slime_b200.models.config import ModelConfig
+
+_LAYER = re.compile(r"^decoder\.layers\.(\d+)\.(.+)$")
+_EXPERT = re.compile(r"^mlp\.experts\.linear_fc([12])\.weight(\d+)$")
+_MTP = re.compile(r"^mtp\.layers\.(\d+)\.(.+)$")
+
+
+def split_qkv(cfg: ModelConfig, t: torch.Tensor):
+    """Full (all-TP-ranks) fused tensor [ (Hq+2Hkv)*d , ...] -> (q, k, v)."""
+    d = cfg.head_dim
+    q, k = cfg.num_attention_heads * d, cfg.num_query_groups * d
+    return t[:q], t[q : q + k], t[q + k :]
+
+
+def qkv_to_megatron_layout(cfg: ModelConfig, t: torch.Tensor) -> torch.Tensor:
+    """[q | k | v] rows -> per-KV-group interleave [g][q_per_g*d | d | d]."""
+    d, g = cfg.head_dim, cfg.num_query_groups
+    per = cfg.num_attention_heads // g
+    q, k, v = split_qkv(cfg, t)
+    rest = t.shape[1:]
+    q = q.reshape(g, per * d, *rest)
+    k = k.reshape(g, d, *rest)
+    v = v.reshape(g, d, *rest)
+    return torch.cat([q, k, v], dim=1).reshape(-1, *rest)
+
+
+def qkv_from_megatron_layout(cfg: ModelConfig, t: torch.Tensor) -> torch.Tensor:
+    d, g = cfg.head_dim, cfg.num_query_groups
+    per = cfg.num_attention_heads // g
+    rest = t.shape[1:]
+    x = t.reshape(g, (per + 2) * d, *rest)
+    q = x[:, : per * d].reshape(-1, *rest)
+    k = x[:, per * d : (per + 1) * d].reshape(-1, *rest)
+    v = x[:, (per + 1) * d :].reshape(-1, *rest)
+    return torch.cat([q, k, v], dim=0)
+
+
+def _family(cfg: ModelConfig) -> str:
+    a = (cfg.model_arch or "").lower()
+    for key in ("qwen3_5", "qwen3next", "qwen3moe", "qwen2moe", "qwen3", "qwen2", "glm4moe", "glm4", "llama", "mimo",
+                "deepseek", "minimax"):  # fmt: skip
+        if key in a.replace("_", "").replace("-", "") or key in a:
+            return key
+    return "qwen2"
+
+
+def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
+    """One gathered trainer tensor -> HF (name, tensor) pairs. Names not handled raise."""
+    name = name.removeprefix("module.").removeprefix("module.")
+    if name == "embedding.word_embeddings.weight":
+        return [("model.embed_tokens.weight", t[: cfg.vocab_size])]
+    if name == "output_layer.weight":
+        return [("lm_head.weight", t[: cfg.vocab_size])]
+    if name == "decoder.final_layernorm.weight":
+        return [("model.norm.weight", t)]
+    m = _LAYER.match(name)
+    if m is None:
+        raise ValueError(f"unknown trainer parameter name: {name}")
+    i, sub = m.group(1), m.group(2)
+    p = f"model.layers.{i}"
+    fam = _family(cfg)
+    if sub == "self_attention.linear_qkv.weight":
+        q, k, v = split_qkv(cfg, t)
+        return [(f"{p}.self_attn.q_proj.weight", q), (f"{p}.self_attn.k_proj.weight", k), (f"{p}.self_attn.v_proj.weight", v)]
+    if sub == "self_attention.linear_qkv.bias":
+        q, k, v = split_qkv(cfg, t)
+        return [(f"{p}.self_attn.q_proj.bias", q), (f"{p}.self_attn.k_proj.bias", k), (f"{p}.self_attn.v_proj.bias", v)]
+    if sub == "self_attention.linear_qkv.layer_norm_weight":
+        return [(f"{p}.input_layernorm.weight", t)]
+    if sub == "self_attention.linear_proj.weight":
+        return [(f"{p}.self_attn.o_proj.weight", t)]
+    if sub == "self_attention.q_layernorm.weight":
+        return [(f"{p}.self_attn.q_norm.weight", t)]
+    if sub == "self_attention.k_layernorm.weight":
+        return [(f"{p}.self_attn.k_norm.weight", t)]
+    if sub == "post_self_attn_layernorm.weight":
+        return [(f"{p}.post_self_attn_layernorm.weight", t)]
+    if sub == "post_mlp_layernorm.weight":
+        return [(f"{p}.post_mlp_layernorm.weight", t)]
+    if sub in ("mlp.linear_fc1.layer_norm_weight", "pre_mlp_layernorm.weight", "mlp.pre_mlp_layernorm.weight"):
+        return [(f"{p}.post_attention_layernorm.weight", t)]
+    if sub == "mlp.linear_fc1.weight":
+        if fam == "glm4":
+            return [(f"{p}.mlp.gate_up_proj.weight", t)]
+        half = t.shape[0] // 2
+        return [(f"{p}.mlp.gate_proj.weight", t[:half]), (f"{p}.mlp.up_proj.weight", t[half:])]
+    if sub == "mlp.linear_fc2.weight":
+        return [(f"{p}.mlp.down_proj.weight", t)]
+    if sub == "mlp.router.weight":
+        return [(f"{p}.mlp.gate.weight", t)]
+    if sub == "mlp.router.expert_bias":
+        return [(f"{p}.mlp.gate.e_score_correction_bias", t)]
+    em = _EXPERT.match(sub)
+    if em:
+        which, e = em.group(1), em.group(2)
+        if which == "1":
+            half = t.shape[0] // 2
+            return [(f"{p}.mlp.experts.{e}.gate_proj.weight", t[:half]), (f"{p}.mlp.experts.{e}.up_proj.weight", t[half:])]
+        return [(f"{p}.mlp.experts.{e}.down_proj.weight", t)]
+    if sub == "mlp.shared_experts.linear_fc1.weight":
+        half = t.shape[0] // 2
+        sp = "shared_expert" if fam in ("qwen2moe", "qwen3next", "qwen3_5") else "shared_experts"
+        return [(f"{p}.mlp.{sp}.gate_proj.weight", t[:half]), (f"{p}.mlp.{sp}.up_proj.weight", t[half:])]
+    if sub == "mlp.shared_experts.linear_fc2.weight":
+        sp = "shared_expert" if fam in ("qwen2moe", "qwen3next", "qwen3_5") else "shared_experts"
+        return [(f"{p}.mlp.{sp}.down_proj.weight", t)]
+    raise ValueError(f"unknown trainer parameter name: {name}")
+
+
+# -------------------------------------------------------------------------- TP gather rules
+def gather_dim(name: str, param) -> int | None:
+    """Dimension along which TP shards of ``param`` concatenate (None: replicated)."""
+    if not getattr(param, "tensor_model_parallel", False):
+        return None
+    return getattr(param, "partition_dim", 0)
+
+
+def merge_tp_shards(cfg: ModelConfig, name: str, shards: list[torch.Tensor], partition_dim: int, stride: int) -> torch.Tensor:
+    """Concatenate TP shards into the full tensor honouring fused layouts.
+
+    * fused fc1 (stride 2): each shard is [gate_r ; up_r] -> full is [gate_0..gate_n ; up_0..up_n].
+    * fused qkv: each shard is [q_r | k_r | v_r] -> full is [q_all | k_all | v_all].
+    """
+    if len(shards) == 1:
+        return shards[0]
+    if "linear_qkv" in name and partition_dim == 0:
+        tp = len(shards)
+        d = cfg.head_dim
+        hq, hkv = cfg.num_attention_heads // tp * d, cfg.num_query_groups // tp * d
+        q = torch.cat([s[:hq] for s in shards], dim=0)
+        k = torch.cat([s[hq : hq + hkv] for s in shards], dim=0)
+        v = torch.cat([s[hq + hkv :] for s in shards], dim=0)
+        return torch.cat([q, k, v], dim=0)
+    if stride == 2 and partition_dim == 0:
+        halves = [s.chunk(2, dim=0) for s in shards]
+        return torch.cat([h[0] for h in halves] + [h[1] for h in halves], dim=0)
+    return torch.cat(shards, dim=partition_dim)
+
+
+def shard_for_tp(cfg: ModelConfig, name: str, full: torch.Tensor, partition_dim: int, stride: int, tp: int, rank: int):
+    """Inverse of :func:`merge_tp_shards`: this rank's shard of a full tensor."""
+    if tp == 1:
+        return full
+    if "linear_qkv" in name and partition_dim == 0:
+        q, k, v = split_qkv(cfg, full)
+        return torch.cat([q.chunk(tp, 0)[rank], k.chunk(tp, 0)[rank], v.chunk(tp, 0)[rank]], dim=0)
+    if stride == 2 and partition_dim == 0:
+        g, u = full.chunk(2, dim=0)
+        return torch.cat([g.chunk(tp, 0)[rank], u.chunk(tp, 0)[rank]], dim=0)
+    return full.chunk(tp, dim=partition_dim)[rank]
+
+
+# ---------------------------------------------------------------------- HF -> trainer names
+def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
+    """HF tensor names needed to build trainer tensor ``name`` and the merge rule
+    ('copy' | 'qkv' | 'gate_up')."""
+    if name == "embedding.word_embeddings.weight":
+        return ["model.embed_tokens.weight"], "copy"
+    if name == "output_layer.weight":
+        return ["model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"], "copy"
+    if name == "decoder.final_layernorm.weight":
+        return ["model.norm.weight"], "copy"
+    m = _LAYER.match(name)
+    if m is None:
+        raise ValueError(f"unknown trainer parameter name: {name}")
+    i, sub = m.group(1), m.group(2)
+    p = f"model.layers.{i}"
+    simple = {
+        "self_attention.linear_qkv.layer_norm_weight": "input_layernorm.weight",
+        "self_attention.linear_proj.weight": "self_attn.o_proj.weight",
+        "self_attention.q_layernorm.weight": "self_attn.q_norm.weight",
+        "self_attention.k_layernorm.weight": "self_attn.k_norm.weight",
+        "mlp.linear_fc1.layer_norm_weight": "post_attention_layernorm.weight",
+        "pre_mlp_layernorm.weight": "post_attention_layernorm.weight",
+        "mlp.pre_mlp_layernorm.weight": "post_attention_layernorm.weight",
+        "mlp.linear_fc2.weight": "mlp.down_proj.weight",
+        "mlp.router.weight": "mlp.gate.weight",
+        "mlp.router.expert_bias": "mlp.gate.e_score_correction_bias",
+        "post_self_attn_layernorm.weight": "post_self_attn_layernorm.weight",
+        "post_mlp_layernorm.weight": "post_mlp_layernorm.weight",
+        "mlp.shared_experts.linear_fc2.weight": "mlp.shared_experts.down_proj.weight",
+    }
+    if sub in simple:
+        return [f"{p}.{simple[sub]}"], "copy"
+    if sub == "self_attention.linear_qkv.weight":
+        return [f"{p}.self_attn.{x}_proj.weight" for x in "qkv"], "qkv"
+    if sub == "self_attention.linear_qkv.bias":
+        return [f"{p}.self_attn.{x}_proj.bias" for x in "qkv"], "qkv"
+    if sub == "mlp.linear_fc1.weight":
+        return [f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight"], "gate_up"
+    if sub == "mlp.shared_experts.linear_fc1.weight":
+        return [f"{p}.mlp.shared_experts.gate_proj.weight", f"{p}.mlp.shared_experts.up_proj.weight"], "gate_up"
+    em = _EXPERT.match(sub)
+    if em:
+        which, e = em.group(1), em.group(2)
+        if which == "1":
+            return [f"{p}.mlp.experts.{e}.gate_proj.weight", f"{p}.mlp.experts.{e}.up_proj.weight"], "gate_up"
+        return [f"{p}.mlp.experts.{e}.down_proj.weight"], "copy"
+    raise ValueError(f"unknown trainer parameter name: {name}")
+
+
+def merge_hf_sources(rule: str, tensors: list[torch.Tensor]) -> torch.Tensor:
+    if rule == "copy":
+        return tensors[0]
+    return torch.cat(tensors, dim=0)  # qkv -> [q|k|v], gate_up -> [gate;up]
+
+
+def pad_vocab(t: torch.Tensor, padded: int) -> torch.Tensor:
+    if t.shape[0] >= padded:
+        return t[:padded]
+    return torch.cat([t, t.new_zeros(padded - t.shape[0], *t.shape[1:])], dim=0)
