@@ -294,6 +294,16 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 #include <stdexcept>
 #include <string>
 namespace sb {
+inline char* last_error_buf() {
+  static thread_local char buf[512] = {0};
+  return buf;
+}
+inline void set_last_error(const std::string& msg) {
+  char* b = last_error_buf();
+  size_t n = msg.size() < 511 ? msg.size() : 511;
+  for (size_t i = 0; i < n; ++i) b[i] = msg[i];
+  b[n] = 0;
+}
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -322,11 +332,15 @@ inline CUtensorMap make_tmap_2d(const void* base, CUtensorMapDataType dt, int el
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (row_pitch_bytes & 15) != 0)
-    throw std::runtime_error("TMA operand must be 16-byte aligned with a 16-byte-multiple row pitch");
+    throw std::runtime_error("TMA operand must be 16-byte aligned with a 16-byte-multiple row pitch: base=" +
+                             std::to_string(reinterpret_cast<uintptr_t>(base)) + " pitch=" + std::to_string(row_pitch_bytes));
   CUresult r = get_encode_tiled()(&m, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) throw std::runtime_error("cuTensorMapEncodeTiled failed: " + std::to_string(int(r)));
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled failed: " + std::to_string(int(r)) + " rows=" + std::to_string(rows) +
+                             " cols=" + std::to_string(cols) + " pitch=" + std::to_string(row_pitch_bytes) + " box=" +
+                             std::to_string(box_rows) + "x" + std::to_string(box_cols));
   return m;
 }
 }  // namespace sb

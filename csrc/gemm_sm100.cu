@@ -262,14 +262,19 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) return e;
+    if (e != cudaSuccess) {
+      set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+      return e;
+    }
     configured = true;
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
                                                  accumulate, status);
-  return cudaGetLastError();
+  cudaError_t le = cudaGetLastError();
+  if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
+  return le;
 }
 
 template <int BN, int STAGES>
@@ -309,7 +314,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
                                               accumulate, status, num_sms, stream);
     return (int)sb::dispatch_layout<128, 6>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb, ldc,
                                             accumulate, status, num_sms, stream);
-  } catch (const std::exception&) {
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;
   }
 }
+
+extern "C" const char* sb_last_error() { return sb::last_error_buf(); }

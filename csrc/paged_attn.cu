@@ -242,3 +242,65 @@ extern "C" int sb_paged_decode(const void* q, const void* k_cache, const void* v
   sb::decode_combine_kernel<<<B * Hq, 64, 0, s>>>(part_o, part_ml, (__nv_bfloat16*)out, D, splits, out_stride, Hq);
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------- decode step state
+// Device-owned per-slot decode state (ids, pos, out_pos) lets consecutive decode steps be launched
+// without a host round trip: the sampled token becomes the next input on the device. The host owns
+// the block table, the active mask and "init" records for slots that start decoding this step.
+namespace sb {
+
+__global__ void decode_prepare_kernel(int* __restrict__ ids, int* __restrict__ pos, int* __restrict__ out_pos,
+                                      const int* __restrict__ init_mask, const int* __restrict__ init_ids,
+                                      const int* __restrict__ init_pos, const int* __restrict__ init_out_pos,
+                                      const int* __restrict__ active, const int* __restrict__ block_table,
+                                      int* __restrict__ ids_eff, int* __restrict__ pos_eff, int* __restrict__ seq_lens,
+                                      int* __restrict__ slots, int B, int page_size, int max_pages) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  if (init_mask[b]) {
+    ids[b] = init_ids[b];
+    pos[b] = init_pos[b];
+    out_pos[b] = init_out_pos[b];
+  }
+  if (active[b]) {
+    const int p = pos[b];
+    ids_eff[b] = ids[b];
+    pos_eff[b] = p;
+    seq_lens[b] = p + 1;
+    slots[b] = block_table[static_cast<size_t>(b) * max_pages + p / page_size] * page_size + p % page_size;
+  } else {  // idle slot: one dummy token whose KV lands in the reserved scratch page 0
+    ids_eff[b] = 0;
+    pos_eff[b] = 0;
+    seq_lens[b] = 1;
+    slots[b] = b % page_size;
+  }
+}
+
+__global__ void decode_advance_kernel(int* __restrict__ ids, int* __restrict__ pos, int* __restrict__ out_pos,
+                                      const int* __restrict__ active, const int* __restrict__ sampled, int B) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B || !active[b]) return;
+  ids[b] = sampled[b];
+  pos[b] += 1;
+  out_pos[b] += 1;
+}
+
+}  // namespace sb
+
+extern "C" int sb_decode_prepare(int* ids, int* pos, int* out_pos, const int* init_mask, const int* init_ids,
+                                 const int* init_pos, const int* init_out_pos, const int* active, const int* block_table,
+                                 int* ids_eff, int* pos_eff, int* seq_lens, int* slots, int B, int page_size,
+                                 int max_pages, cudaStream_t s) {
+  if (B == 0) return 0;
+  sb::decode_prepare_kernel<<<(B + 127) / 128, 128, 0, s>>>(ids, pos, out_pos, init_mask, init_ids, init_pos, init_out_pos,
+                                                            active, block_table, ids_eff, pos_eff, seq_lens, slots, B,
+                                                            page_size, max_pages);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_decode_advance(int* ids, int* pos, int* out_pos, const int* active, const int* sampled, int B,
+                                 cudaStream_t s) {
+  if (B == 0) return 0;
+  sb::decode_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(ids, pos, out_pos, active, sampled, B);
+  return (int)cudaGetLastError();
+}

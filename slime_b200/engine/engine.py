@@ -6,6 +6,11 @@ step for every running request; finished requests free their pages (complete pag
 indexed for prefix reuse). ``generate()`` is the blocking convenience wrapper; the HTTP server
 drives ``step()`` from its scheduler thread.
 
+Decode is pipelined: per-slot token / position state lives on the device, so step ``t+1`` is launched
+before the host has looked at step ``t``'s tokens. Sampled tokens and log-probs stream back through a
+pinned history ring; the host processes them one step late (length-based finishes need no token at all,
+EOS / stop-token finishes are detected one step late and the extra token is discarded).
+
 This is the component that replaces the SGLang server process of the reference
 (slime/backends/sglang_utils/sglang_engine.py:88-503 is only its HTTP client); the control
 surface it must offer is: generate (with logprobs), abort, pause / continue, flush cache,
@@ -14,10 +19,12 @@ release / resume memory by tag (weights | kv_cache | cuda_graph), weight update 
 
 from __future__ import annotations
 
+import heapq
 import threading
 import time
 import uuid
 
+import numpy as np
 import torch
 
 from slime_b200 import ops
@@ -40,7 +47,7 @@ class Engine:
         )
         self.dtype = torch.bfloat16 if self.device.type == "cuda" else torch.float32
         self.tokenizer = tokenizer
-        self.eos_ids = set()
+        self.eos_ids: set[int] = set()
         if tokenizer is not None and getattr(tokenizer, "eos_token_id", None) is not None:
             self.eos_ids.add(tokenizer.eos_token_id)
         self.weights = EngineWeights(cfg, self.dtype, self.device, tp_size, tp_rank)
@@ -56,14 +63,14 @@ class Engine:
                                   use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
         self.runner._alloc_static()
         self.waiting: list[Request] = []
-        self.running: list[Request] = []
+        self.running: list[Request] = []  # decoding (own a slot) until their results are finalised
         self.prefilling: list[Request] = []
         self.paused = False
         self.released: set[str] = set()
         self.lock = threading.RLock()
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0, "aborted": 0,
-                      "h2d_bytes": 0, "d2h_bytes": 0}
-        self._deferred_removals = None
+                      "h2d_bytes": 0, "d2h_bytes": 0, "decode_steps": 0}  # fmt: skip
+        self._init_decode_state()
 
     # ----------------------------------------------------------------- sizing
     def _pages_from_memory(self) -> int:
@@ -75,6 +82,28 @@ class Engine:
         free, total = torch.cuda.mem_get_info(self.device)
         budget = int(total * self.args.mem_fraction_static) - (total - free)
         return max(64, budget // per_page)
+
+    def _init_decode_state(self):
+        B = self.max_running
+        self.slot_req: list[Request | None] = [None] * B
+        self.free_slots = list(range(B))
+        heapq.heapify(self.free_slots)
+        self.h_pos = np.zeros(B, dtype=np.int64)  # position of the token the next step feeds
+        self.h_remaining = np.zeros(B, dtype=np.int64)  # tokens still to sample (length limit)
+        self.h_npages = np.zeros(B, dtype=np.int64)
+        self.h_inspect = np.zeros(B, dtype=bool)  # slot needs its tokens looked at (EOS, stop ids, stop strings, stream)
+        self.ring = int(min(max(self.max_context + 8, 64), 8192))
+        pin = self.device.type == "cuda"
+        self.tok_hist = torch.zeros(self.ring, B, dtype=torch.int32, pin_memory=pin)
+        self.lp_hist = torch.zeros(self.ring, B, dtype=torch.float32, pin_memory=pin)
+        self.tok_np, self.lp_np = self.tok_hist.numpy(), self.lp_hist.numpy()
+        self.hist_events: list = [None] * self.ring
+        self.step_no = 0  # decode steps launched so far
+        self.processed = 0  # decode steps whose results the host has consumed
+        self.kept_hist: dict[int, tuple] = {}
+        if 0 in self.kv.allocator.free:  # page 0 is the scratch page idle decode slots write to
+            self.kv.allocator.free.remove(0)
+            self.kv.allocator.refcnt[0] = 1
 
     # ------------------------------------------------------------------ intake
     def add_request(self, input_ids, sampling: SamplingParams | dict | None = None, rid: str | None = None, **kw) -> Request:
@@ -117,32 +146,33 @@ class Engine:
         batch: list[tuple[Request, int]] = []
         pending_first_hash = set()
         ps = self.page_size
-        # continue chunked prefills first
-        for req in list(self.prefilling):
-            todo = len(req.input_ids) - req.num_computed
+        for req in list(self.prefilling):  # continue chunked prefills first
+            todo = len(req.ctx_ids) - req.num_computed
             n = min(todo, budget, self.args.chunked_prefill_size)
             if n <= 0:
                 break
             batch.append((req, n))
             budget -= n
         still_waiting = []
+        admitted = 0
         for req in self.waiting:
-            if budget <= 0 or len(self.running) + len(self.prefilling) + len([b for b in batch if b[0].state == ReqState.WAITING]) >= self.max_running:
+            if budget <= 0 or len(self.running) + len(self.prefilling) + admitted >= self.max_running:
                 still_waiting.append(req)
                 continue
             if req.sampling.max_new_tokens == 0 and req.logprob_start_len < 0:
                 self._finish(req, {"type": "length", "length": 0})
                 continue
+            ctx = req.input_ids + req.output_ids  # a retracted request re-enters with what it generated so far
+            req.ctx_ids = ctx
             # siblings of a prompt being prefilled right now wait one step and then hit the prefix cache
-            first = _hash_block(b"", req.input_ids[:ps]) if len(req.input_ids) > ps else None
+            first = _hash_block(b"", ctx[:ps]) if len(ctx) > ps else None
             if first is not None and first in pending_first_hash:
                 still_waiting.append(req)
                 continue
             want_cache = req.logprob_start_len < 0  # input log-probs need every position computed
-            pages, chain = self.kv.allocator.match_prefix(req.input_ids) if want_cache else ([], b"")
+            pages, chain = self.kv.allocator.match_prefix(ctx) if want_cache else ([], b"")
             cached = len(pages) * ps
-            need_tokens = len(req.input_ids) - cached
-            total_pages = -(-(len(req.input_ids) + 1) // ps)
+            total_pages = -(-(len(ctx) + 1) // ps)
             try:
                 new_pages = self.kv.allocator.alloc(total_pages - len(pages))
             except OutOfPages:
@@ -153,9 +183,10 @@ class Engine:
             req.pages = pages + new_pages
             req.num_cached_tokens = req.num_computed = cached
             req.committed_pages, req.chain_hash = len(pages), chain
-            req.first_scheduled = time.time()
-            n = min(need_tokens, budget, self.args.chunked_prefill_size)
+            req.first_scheduled = req.first_scheduled or time.time()
+            n = min(len(ctx) - cached, budget, self.args.chunked_prefill_size)
             batch.append((req, n))
+            admitted += 1
             budget -= n
             self.stats["cached_tokens"] += cached
             if first is not None and cached == 0:
@@ -167,14 +198,21 @@ class Engine:
         ps = self.page_size
         return [req.pages[p // ps] * ps + p % ps for p in range(start, end)]
 
+    def _to_dev(self, x, dt=torch.int32):
+        host = torch.tensor(x, dtype=dt)
+        self.stats["h2d_bytes"] += host.numel() * host.element_size()
+        if self.device.type == "cuda":
+            host = host.pin_memory()
+        return host.to(self.device, non_blocking=True)
+
     def _run_prefill(self, batch) -> list[Request]:
-        dev = self.device
+        t = self._to_dev
         ids, pos, slots, cu_q, cu_k, gather, last_rows, samplers = [], [], [], [0], [0], [], [], []
         fresh, max_q, max_k = True, 0, 0
         want_all_rows = any(r.logprob_start_len >= 0 for r, _ in batch)
         for req, n in batch:
             s, e = req.num_computed, req.num_computed + n
-            ids += req.input_ids[s:e]
+            ids += req.ctx_ids[s:e]
             pos += list(range(s, e))
             slots += self._slots(req, s, e)
             cu_q.append(cu_q[-1] + n)
@@ -182,19 +220,12 @@ class Engine:
             gather += self._slots(req, 0, e)
             fresh &= s == 0
             max_q, max_k = max(max_q, n), max(max_k, e)
-            if e == len(req.input_ids):
+            if e == len(req.ctx_ids):
                 last_rows.append(cu_q[-1] - 1)
                 samplers.append(req)
             if req.state == ReqState.WAITING:
                 req.state = ReqState.RUNNING
                 self.prefilling.append(req)
-        def t(x, dt=torch.int32):
-            host = torch.tensor(x, dtype=dt)
-            self.stats["h2d_bytes"] += host.numel() * host.element_size()
-            if dev.type == "cuda":
-                host = host.pin_memory()
-            return host.to(dev, non_blocking=True)
-
         rows = None if want_all_rows else t(last_rows, torch.long)
         logits = self.runner.prefill(t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long),
                                      t(cu_k), max_q, max_k, rows, fresh)  # fmt: skip
@@ -204,7 +235,7 @@ class Engine:
             logits = logits.index_select(0, t(last_rows, torch.long))
         for req, n in batch:
             req.num_computed += n
-            self._commit_pages(req)
+            self._commit_pages(req, req.ctx_ids)
         finished = []
         if samplers:
             toks, lps, kept_ids, kept_cnt = self._sample_rows(logits, samplers)
@@ -214,8 +245,9 @@ class Engine:
                     self._finish(req, {"type": "length", "length": 0})
                     finished.append(req)
                     continue
-                req.first_token_time = time.time()
-                if self._append_token(req, toks[i], lps[i], kept_ids, kept_cnt, i):
+                req.first_token_time = req.first_token_time or time.time()
+                self._record_kept(req, kept_ids, kept_cnt, i)
+                if self._append_token(req, toks[i], lps[i]):
                     finished.append(req)
                 else:
                     self._start_decoding(req)
@@ -227,9 +259,8 @@ class Engine:
             if req.logprob_start_len < 0:
                 continue
             s = req.num_computed
-            nxt = torch.tensor(req.input_ids[s + 1 : s + n + 1], device=logits.device, dtype=torch.long)
-            rows = lsm[a : a + nxt.numel()]
-            vals = rows.gather(-1, nxt[:, None]).squeeze(-1).tolist()
+            nxt = torch.tensor(req.ctx_ids[s + 1 : s + n + 1], device=logits.device, dtype=torch.long)
+            vals = lsm[a : a + nxt.numel()].gather(-1, nxt[:, None]).squeeze(-1).tolist()
             if req.input_logprobs is None:
                 req.input_logprobs = [None]  # the first token has no conditional probability
             req.input_logprobs += vals
@@ -247,129 +278,221 @@ class Engine:
         seeds = f([r.seed for r in reqs], torch.int64)
         pos = f([len(r.output_ids) for r in reqs], torch.int32)
         tok, lp, kept_ids, kept_cnt = ops.sample(logits[:n], temp, tk, tp, mp, seeds, pos, cap)
+        self.stats["d2h_bytes"] += 8 * n
         return tok.tolist(), lp.tolist(), (kept_ids.cpu() if kept_ids is not None else None), (
             kept_cnt.tolist() if kept_cnt is not None else None
         )
 
-    # Rows of the decode buffers: ``running[b]`` owns row ``b``. Rows are written in full when a
-    # request starts decoding and advanced with vectorised numpy updates afterwards.
-    def _row_init(self, b: int, r: Request):
+    # ------------------------------------------------------------------ decode slots
+    def _needs_inspection(self, r: Request) -> bool:
+        sp = r.sampling
+        return bool((not sp.ignore_eos and self.eos_ids) or sp.stop_token_ids or sp.stop or r.on_token is not None)
+
+    def _start_decoding(self, r: Request):
+        """Give the request a decode slot; its first input token and position reach the device with the next upload."""
+        b = heapq.heappop(self.free_slots)
         h = self.runner.host
         L = r.seq_len
-        h["ids"][b] = r.output_ids[-1] if r.output_ids else r.input_ids[-1]
-        h["positions"][b] = L - 1
-        h["seq_lens"][b] = L
-        h["top_k"][b] = max(r.sampling.top_k, 0)
-        h["out_pos"][b] = len(r.output_ids)
-        h["temperature"][b] = r.sampling.temperature
-        h["top_p"][b] = r.sampling.top_p
-        h["min_p"][b] = r.sampling.min_p
-        h["seeds"][b] = r.seed
+        r.slot, r.decode_from_step, r.harvested = b, self.step_no, self.step_no
+        self.slot_req[b] = r
+        h["active"][b], h["init_mask"][b] = 1, 1
+        h["init_ids"][b], h["init_pos"][b], h["init_out_pos"][b] = r.output_ids[-1], L - 1, len(r.output_ids)
+        h["top_k"][b], h["temperature"][b] = max(r.sampling.top_k, 0), r.sampling.temperature
+        h["top_p"][b], h["min_p"][b], h["seeds"][b] = r.sampling.top_p, r.sampling.min_p, r.seed
         bt = h["block_table"][b]
         bt[:] = 0
         bt[: len(r.pages)] = r.pages
-
-    def _row_clear(self, b: int):
-        h = self.runner.host
-        for k in ("ids", "positions", "top_k", "out_pos"):
-            h[k][b] = 0
-        h["seq_lens"][b] = 1
-        h["block_table"][b, :] = 0
-
-    def _start_decoding(self, r: Request):
-        self._row_init(len(self.running), r)
+        self.h_pos[b], self.h_npages[b] = L - 1, len(r.pages)
+        self.h_remaining[b] = r.sampling.max_new_tokens - len(r.output_ids)
+        self.h_inspect[b] = self._needs_inspection(r)
+        r.end_step = None  # decode step index (exclusive) up to which this request's tokens count
         self.running.append(r)
 
-    def _remove_running(self, r: Request):
-        b = self.running.index(r)
-        last = len(self.running) - 1
-        if b != last:
-            mover = self.running[last]
-            self.running[b] = mover
-            self._row_init(b, mover)
-        self.running.pop()
-        self._row_clear(last)
+    def _deactivate(self, b: int):
+        self.runner.host["active"][b] = 0
+        self.runner.host["block_table"][b, :] = 0
+
+    def _release_slot(self, r: Request):
+        b = r.slot
+        self._deactivate(b)
+        self.slot_req[b] = None
+        self.h_inspect[b] = False
+        heapq.heappush(self.free_slots, b)
+        r.slot = None
+        if r in self.running:
+            self.running.remove(r)
 
     def _run_decode(self) -> list[Request]:
-        import numpy as np
-
-        finished = []
-        ps = self.page_size
         h = self.runner.host
-        # a request whose next token starts a new page needs that page now; if the cache is full the
-        # youngest requests are retracted (their KV is recomputed when they are re-admitted)
-        i = 0
-        while i < len(self.running):
-            r = self.running[i]
-            if r.seq_len % ps == 0 and len(r.pages) * ps <= r.seq_len:
-                try:
-                    r.pages += self.kv.allocator.alloc(1)
-                    h["block_table"][i, len(r.pages) - 1] = r.pages[-1]
-                except OutOfPages:
-                    victim = self.running[-1]
-                    self._remove_running(victim)
-                    self._retract(victim)
+        ps = self.page_size
+        act = h["active"][: self.max_running].astype(bool)
+        finished: list[Request] = []
+        if not act.any():
+            return self._drain()
+        # a slot whose next token starts a new page needs that page before the launch; when the cache is
+        # full the youngest request is retracted (its KV is rebuilt when it is re-admitted)
+        need = np.nonzero(act & (self.h_pos // ps >= self.h_npages))[0]
+        for b in need:
+            r = self.slot_req[b]
+            if r is None or not h["active"][b]:
+                continue
+            try:
+                r.pages += self.kv.allocator.alloc(1)
+            except OutOfPages:
+                victim = max((x for x in self.running if x.slot is not None and h["active"][x.slot]), key=lambda x: x.arrival)
+                self._sync_results()
+                self._retract(victim)
+                if victim is r:
                     continue
-            i += 1
-        reqs = self.running
-        n = len(reqs)
-        if n == 0:
-            return finished
-        filtered = bool((h["top_k"][:n] > 0).any() or (h["top_p"][:n] < 1.0).any() or (h["min_p"][:n] > 0).any())
-        cap = 4096 if filtered and any(r.sampling.return_top_p_token_ids for r in reqs) else 0
-        self.runner.upload_static()
-        self.stats["h2d_bytes"] += self.runner._flat_host.numel() * 4
+                r.pages += self.kv.allocator.alloc(1)
+            h["block_table"][b, len(r.pages) - 1] = r.pages[-1]
+            self.h_npages[b] = len(r.pages)
+        act = h["active"][: self.max_running].astype(bool)
+        if not act.any():
+            return self._drain()
+        n = int(np.nonzero(act)[0][-1]) + 1
+        filtered = bool((h["top_k"][:n][act[:n]] > 0).any() or (h["top_p"][:n][act[:n]] < 1.0).any() or (h["min_p"][:n][act[:n]] > 0).any())
+        cap = 4096 if filtered and any(r.sampling.return_top_p_token_ids for r in self.running) else 0
+        self.stats["h2d_bytes"] += self.runner.upload_static()
         tok, lp, kept_ids, kept_cnt = self.runner.decode(n, filtered, cap)
-        toks_t, lps_t = tok[:n].cpu(), lp[:n].cpu()
+        # results stream back into the pinned history ring; an event marks their arrival
+        slot = self.step_no % self.ring
+        self.tok_hist[slot, :n].copy_(tok[:n], non_blocking=True)
+        self.lp_hist[slot, :n].copy_(lp[:n], non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self.hist_events[slot] = ev
+        if cap:
+            self.kept_hist[self.step_no] = (kept_ids[:n].cpu(), kept_cnt[:n].cpu())
         self.stats["d2h_bytes"] += 8 * n
-        toks, lps = toks_t.tolist(), lps_t.tolist()
-        kept_ids = kept_ids[:n].cpu() if kept_ids is not None else None
-        kept_cnt = kept_cnt[:n].tolist() if kept_cnt is not None else None
-        self.stats["decode_tokens"] += n
-        # advance every row: the sampled token becomes the next input
-        h["ids"][:n] = toks_t.numpy()
-        h["positions"][:n] += 1
-        h["seq_lens"][:n] += 1
-        h["out_pos"][:n] += 1
-        # rows are compacted only after every request has taken its token: a row moved into a freed
-        # slot is rebuilt from its request's (by then final) state
-        self._deferred_removals = []
-        for i, r in enumerate(list(reqs)):
-            r.num_computed = r.seq_len  # the fed token's KV is now cached
-            if r.num_computed % ps == 0:
-                self._commit_pages(r)
-            if self._append_token(r, toks[i], lps[i], kept_ids, kept_cnt, i):
-                finished.append(r)
-        deferred, self._deferred_removals = self._deferred_removals, None
-        for r in deferred:
-            self._remove_running(r)
+        self.stats["decode_tokens"] += int(act.sum())
+        self.stats["decode_steps"] += 1
+        self.step_no += 1
+        # host mirrors advance without looking at the tokens
+        self.h_pos[act] += 1
+        self.h_remaining[act] -= 1
+        done = np.nonzero(act & (self.h_remaining <= 0))[0]
+        for b in done:
+            r = self.slot_req[b]
+            if r.end_step is None:
+                r.end_step, r.end_reason = self.step_no, {"type": "length", "length": r.sampling.max_new_tokens}
+            self._deactivate(b)
+        # consume the previous step's results while this one runs
+        finished += self._process_until(self.step_no - 1)
+        if self.step_no - min((r.harvested for r in self.running), default=self.step_no) > self.ring // 2:
+            self._sync_results()
+            for r in self.running:
+                self._harvest(r, self.processed)
         return finished
 
+    def _drain(self) -> list[Request]:
+        """No active slot left: consume every outstanding result."""
+        return self._process_until(self.step_no)
+
+    def _sync_results(self):
+        self._process_until(self.step_no, finalize=False)
+
+    def _process_until(self, upto: int, finalize: bool = True) -> list[Request]:
+        """Consume decode results of steps [processed, upto): token inspection (EOS / stop) for the slots that
+        need it, then finalise requests whose end step has been consumed."""
+        finished = []
+        while self.processed < upto:
+            s = self.processed
+            slot = s % self.ring
+            ev = self.hist_events[slot]
+            if ev is not None:
+                ev.synchronize()
+            if self.h_inspect.any():
+                for b in np.nonzero(self.h_inspect)[0]:
+                    r = self.slot_req[b]
+                    if r is None or r.end_step is not None and s >= r.end_step or s < r.decode_from_step:
+                        continue
+                    self._inspect_token(r, s, int(self.tok_np[slot, b]))
+            self.processed += 1
+        if finalize:
+            for r in list(self.running):
+                if r.end_step is not None and r.end_step <= self.processed:
+                    self._harvest(r, r.end_step)
+                    self._release_slot(r)
+                    self._finish(r, r.end_reason)
+                    finished.append(r)
+        return finished
+
+    def _inspect_token(self, r: Request, step: int, tok: int):
+        """Stop conditions that depend on the token value. ``step`` is the decode step that sampled ``tok``."""
+        sp = r.sampling
+        n_out = len(r.output_ids) + (step - r.harvested) + 1
+        reason = None
+        if n_out >= sp.min_new_tokens:
+            if not sp.ignore_eos and tok in self.eos_ids:
+                reason = {"type": "stop", "matched": tok}
+            elif sp.stop_token_ids and tok in sp.stop_token_ids:
+                reason = {"type": "stop", "matched": tok}
+            elif sp.stop and self.tokenizer is not None:
+                self._harvest(r, step + 1)
+                tail = self.tokenizer.decode(r.output_ids[-32:])
+                for s_ in sp.stop:
+                    if s_ in tail:
+                        reason = {"type": "stop", "matched": s_}
+                        break
+        if r.on_token is not None:
+            self._harvest(r, step + 1)
+            r.on_token(r)
+        if reason is not None:
+            r.end_step, r.end_reason = step + 1, reason
+            if r.slot is not None:
+                self._deactivate(r.slot)  # a token sampled after this one is discarded
+
+    def _harvest(self, r: Request, upto: int):
+        """Move the request's tokens of decode steps [harvested, upto) from the history ring into its lists."""
+        if r.slot is None or upto <= r.harvested:
+            return
+        b = r.slot
+        steps = np.arange(r.harvested, upto) % self.ring
+        r.output_ids += self.tok_np[steps, b].tolist()
+        r.output_logprobs += self.lp_np[steps, b].tolist()
+        if r.sampling.return_top_p_token_ids:
+            for s in range(r.harvested, upto):
+                kept = self.kept_hist.get(s)
+                if kept is None:
+                    r.kept_offsets.append(len(r.kept_ids))
+                    continue
+                c = max(int(kept[1][b]), 0)
+                r.kept_ids += kept[0][b, :c].tolist()
+                r.kept_offsets.append(len(r.kept_ids))
+        r.harvested = upto
+        r.num_computed = len(r.input_ids) + len(r.output_ids) - 1
+        self._commit_pages(r, None)
+
     def _retract(self, req: Request):
-        """Return a running request to the queue (its KV is dropped; tokens so far are kept as prompt)."""
+        """Return a decoding request to the queue: tokens generated so far are kept and re-prefilled later."""
+        self._harvest(req, self.processed)
+        self._release_slot(req)
         self.kv.allocator.release(req.pages)
         req.pages, req.num_computed, req.committed_pages, req.chain_hash = [], 0, 0, b""
         req.state = ReqState.WAITING
         self.waiting.insert(0, req)
 
-    def _commit_pages(self, req: Request):
+    def _commit_pages(self, req: Request, ids):
         """Index every page that became full and whose KV is written (committed tokens only)."""
         ps = self.page_size
-        ids = None
-        while (req.committed_pages + 1) * ps <= req.num_computed:
-            ids = ids or req.all_ids()
+        while (req.committed_pages + 1) * ps <= req.num_computed and req.committed_pages < len(req.pages):
+            ids = ids or (req.input_ids + req.output_ids)
             i = req.committed_pages
             req.chain_hash = self.kv.allocator.commit(req.pages[i], req.chain_hash, ids[i * ps : (i + 1) * ps])
             req.committed_pages += 1
 
-    def _append_token(self, req: Request, tok: int, lp: float, kept_ids, kept_cnt, row: int) -> bool:
-        req.output_ids.append(int(tok))
-        req.output_logprobs.append(float(lp))
+    def _record_kept(self, req, kept_ids, kept_cnt, row):
         if kept_cnt is not None and req.sampling.return_top_p_token_ids:
             c = max(kept_cnt[row], 0)
-            ids = kept_ids[row, :c].tolist() if kept_ids is not None and c > 0 else []
-            req.kept_ids += ids
+            req.kept_ids += kept_ids[row, :c].tolist() if kept_ids is not None and c > 0 else []
             req.kept_offsets.append(len(req.kept_ids))
+
+    def _append_token(self, req: Request, tok: int, lp: float) -> bool:
+        """First token (sampled from the prefill logits). Returns True when the request is already finished."""
+        req.output_ids.append(int(tok))
+        req.output_logprobs.append(float(lp))
         sp = req.sampling
         n_out = len(req.output_ids)
         reason = None
@@ -378,12 +501,6 @@ class Engine:
                 reason = {"type": "stop", "matched": int(tok)}
             elif sp.stop_token_ids and tok in sp.stop_token_ids:
                 reason = {"type": "stop", "matched": int(tok)}
-            elif sp.stop and self.tokenizer is not None:
-                tail = self.tokenizer.decode(req.output_ids[-32:])
-                for s in sp.stop:
-                    if s in tail:
-                        reason = {"type": "stop", "matched": s}
-                        break
         if reason is None and n_out >= sp.max_new_tokens:
             reason = {"type": "length", "length": sp.max_new_tokens}
         if req.on_token is not None:
@@ -397,11 +514,6 @@ class Engine:
         req.finish_reason = reason
         req.state = ReqState.FINISHED
         req.finish_time = time.time()
-        if req in self.running:
-            if self._deferred_removals is not None:
-                self._deferred_removals.append(req)
-            else:
-                self._remove_running(req)
         if req in self.prefilling:
             self.prefilling.remove(req)
         if req.pages:
@@ -416,9 +528,14 @@ class Engine:
     def abort(self, rid: str | None = None, abort_all: bool = False) -> int:
         with self.lock:
             victims = [r for r in self.waiting + self.prefilling + self.running if abort_all or r.rid == rid]
+            if any(r in self.running for r in victims):
+                self._sync_results()
             for r in victims:
                 if r in self.waiting:
                     self.waiting.remove(r)
+                if r in self.running:
+                    self._harvest(r, self.processed if r.end_step is None else min(r.end_step, self.processed))
+                    self._release_slot(r)
                 self._finish(r, {"type": "abort"})
             self.stats["aborted"] += len(victims)
             return len(victims)
@@ -437,8 +554,7 @@ class Engine:
             return True
 
     def release_memory_occupation(self, tags=None):
-        """Idempotent per tag. ``weights`` keeps a pinned host copy only if asked to
-        (the trainer re-syncs weights after every resume, so by default they are simply dropped)."""
+        """Idempotent per tag. Weights are dropped, not backed up: the trainer re-syncs them after every resume."""
         with self.lock:
             for tag in tags or MEMORY_TAGS:
                 if tag in self.released:
@@ -462,6 +578,9 @@ class Engine:
                     continue
                 if tag == "kv_cache":
                     self.kv.allocate()
+                    if 0 in self.kv.allocator.free:
+                        self.kv.allocator.free.remove(0)
+                        self.kv.allocator.refcnt[0] = 1
                 elif tag == "weights":
                     fresh = EngineWeights(self.cfg, self.dtype, self.device, self.weights.tp, self.weights.rank)
                     fresh.version = self.weights.version

@@ -1,0 +1,465 @@
+"""HTTP front of the rollout engine, speaking the SGLang-compatible surface the rollout code uses.
+
+Endpoints (callers in the reference: slime/rollout/sglang_rollout.py:152-221,
+slime/backends/sglang_utils/sglang_engine.py:239-492, server_control.py:32-67):
+  POST /generate (JSON or SSE stream)      GET  /health, /health_generate, /get_model_info
+  POST /abort_request {rid|abort_all}      GET  /v1/loads (also /get_load)
+  GET|POST /flush_cache                    POST /pause_generation, /continue_generation
+  POST /release_memory_occupation, /resume_memory_occupation {tags}
+  POST /update_weights_from_tensor, /update_weights_from_disk, /pull_weights
+  POST /init_weights_update_group, /destroy_weights_update_group, /update_weights_from_distributed
+  GET  /get_weight_version, /weight_version   POST /weights_checker {action}
+  POST /post_process_weights               POST /start_profile, /stop_profile
+  GET  /server_info, /get_server_info      GET  /metrics (Prometheus text)
+
+The engine core runs on a dedicated scheduler thread (``Engine.step`` in a loop); aiohttp handlers only
+enqueue requests and await their completion events, so control endpoints never block on a busy scheduler.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import base64
+import io
+import json
+import threading
+import time
+
+import torch
+
+from slime_b200.engine.engine import MEMORY_TAGS, Engine
+from slime_b200.engine.request import SamplingParams
+
+
+class EngineServer:
+    def __init__(self, engine: Engine, host: str = "127.0.0.1", port: int = 30000, tokenizer=None):
+        self.engine, self.host, self.port = engine, host, port
+        self.tokenizer = tokenizer or engine.tokenizer
+        self._stop = threading.Event()
+        self._thread: threading.Thread | None = None
+        self._loop: asyncio.AbstractEventLoop | None = None
+        self._runner = None
+        self._wake = threading.Event()
+        self.started_at = time.time()
+        self._weights_snapshot = None
+        self._update_groups: dict[str, object] = {}
+        self.num_generated = 0
+
+    # ------------------------------------------------------------------ scheduler thread
+    def _scheduler_loop(self):
+        if self.engine.device.type == "cuda":
+            torch.cuda.set_device(self.engine.device)
+        while not self._stop.is_set():
+            if self.engine.has_work() and not self.engine.paused:
+                try:
+                    self.engine.step()
+                except Exception as e:  # noqa: BLE001  surface the failure on every pending request
+                    self.engine.abort(abort_all=True)
+                    self.last_error = repr(e)
+            else:
+                self._wake.wait(timeout=0.002)
+                self._wake.clear()
+
+    # ---------------------------------------------------------------------------- handlers
+    async def _generate(self, request):
+        from aiohttp import web
+
+        body = await request.json()
+        ids = body.get("input_ids")
+        if ids is None:
+            text = body.get("text")
+            if text is None or self.tokenizer is None:
+                return web.json_response({"error": "input_ids (or text with a tokenizer) required"}, status=400)
+            ids = self.tokenizer.encode(text, add_special_tokens=False)
+        batched = bool(ids) and isinstance(ids[0], list)
+        prompts = ids if batched else [ids]
+        sp = body.get("sampling_params") or {}
+        sps = sp if isinstance(sp, list) else [sp] * len(prompts)
+        loop = asyncio.get_running_loop()
+        stream = bool(body.get("stream"))
+        reqs, events, queues = [], [], []
+        for p, s in zip(prompts, sps):
+            ev = asyncio.Event()
+            q: asyncio.Queue = asyncio.Queue()
+
+            class _Done:  # thread-safe bridge from the scheduler thread to the event loop
+                def __init__(self, ev):
+                    self.ev = ev
+
+                def set(self):
+                    loop.call_soon_threadsafe(self.ev.set)
+
+            def on_token(r, q=q):
+                if stream:
+                    loop.call_soon_threadsafe(q.put_nowait, len(r.output_ids))
+
+            req = self.engine.add_request(
+                p, SamplingParams.from_dict(s), rid=body.get("rid"), return_logprob=bool(body.get("return_logprob", False)),
+                logprob_start_len=int(body.get("logprob_start_len", -1) if body.get("return_logprob") else -1),
+                return_routed_experts=bool(body.get("return_routed_experts", False)), stream=stream,
+                on_token=on_token if stream else None, done_event=_Done(ev),
+            )  # fmt: skip
+            if req.finished():
+                ev.set()
+            reqs.append(req)
+            events.append(ev)
+            queues.append(q)
+        self._wake.set()
+        if stream and not batched:
+            resp = web.StreamResponse(headers={"Content-Type": "text/event-stream"})
+            await resp.prepare(request)
+            req, ev, q = reqs[0], events[0], queues[0]
+            while not ev.is_set():
+                try:
+                    await asyncio.wait_for(q.get(), timeout=0.05)
+                except asyncio.TimeoutError:
+                    continue
+                await resp.write(f"data: {json.dumps(self._render(req))}\n\n".encode())
+            await resp.write(f"data: {json.dumps(self._render(req))}\n\n".encode())
+            await resp.write(b"data: [DONE]\n\n")
+            return resp
+        await asyncio.gather(*[e.wait() for e in events])
+        self.num_generated += sum(len(r.output_ids) for r in reqs)
+        out = [self._render(r) for r in reqs]
+        return web.json_response(out if batched else out[0])
+
+    def _render(self, req) -> dict:
+        text = ""
+        if self.tokenizer is not None:
+            text = self.tokenizer.decode(req.output_ids, skip_special_tokens=req.sampling.skip_special_tokens)
+        meta = self.engine.meta_info(req)
+        if not req.return_logprob:
+            meta.pop("output_token_logprobs", None)
+            meta.pop("input_token_logprobs", None)
+        return {"text": text, "output_ids": list(req.output_ids), "meta_info": meta}
+
+    async def _json(self, request) -> dict:
+        try:
+            return await request.json()
+        except Exception:  # noqa: BLE001
+            return {}
+
+    def _ok(self, **kw):
+        from aiohttp import web
+
+        return web.json_response({"success": True, **kw})
+
+    async def _health(self, request):
+        from aiohttp import web
+
+        return web.Response(text="ok")
+
+    async def _health_generate(self, request):
+        from aiohttp import web
+
+        if "weights" in self.engine.released or "kv_cache" in self.engine.released:
+            return web.Response(text="ok (offloaded)")
+        ev = threading.Event()
+        req = self.engine.add_request([0], SamplingParams(max_new_tokens=1, ignore_eos=True), done_event=ev)
+        self._wake.set()
+        ok = await asyncio.get_running_loop().run_in_executor(None, ev.wait, float(request.query.get("timeout", 20)))
+        return web.Response(text="ok") if ok or req.finished() else web.Response(status=503, text="generation stuck")
+
+    async def _abort(self, request):
+        body = await self._json(request)
+        n = self.engine.abort(body.get("rid"), bool(body.get("abort_all", False)))
+        return self._ok(aborted=n)
+
+    async def _loads(self, request):
+        from aiohttp import web
+
+        info = self.engine.loads()
+        inflight = request.query.get("include") == "inflight"
+        if inflight:
+            now = time.time()
+            info["inflight"] = {"running": [now - r.arrival for r in self.engine.running],
+                                "waiting": [now - r.arrival for r in self.engine.waiting]}  # fmt: skip
+        return web.json_response([{"dp_rank": 0, **info}])
+
+    async def _flush(self, request):
+        from aiohttp import web
+
+        ok = self.engine.flush_cache()
+        return web.Response(status=200 if ok else 400, text="Cache flushed." if ok else "Cache not flushed: requests in flight.")
+
+    async def _pause(self, request):
+        self.engine.pause_generation()
+        return self._ok()
+
+    async def _continue(self, request):
+        self.engine.continue_generation()
+        self._wake.set()
+        return self._ok()
+
+    async def _release(self, request):
+        body = await self._json(request)
+        self.engine.flush_cache()
+        self.engine.release_memory_occupation(body.get("tags"))
+        return self._ok()
+
+    async def _resume(self, request):
+        body = await self._json(request)
+        self.engine.resume_memory_occupation(body.get("tags"))
+        return self._ok()
+
+    async def _update_from_tensor(self, request):
+        """Payload: ``serialized_named_tensors`` = base64(torch.save([(name, tensor), ...])) per TP rank, or
+        ``local_handle`` naming tensors registered in-process (colocated fast path)."""
+        body = await self._json(request)
+        blobs = body.get("serialized_named_tensors") or []
+        named = []
+        for blob in blobs[:1]:
+            named += torch.load(io.BytesIO(base64.b64decode(blob)), weights_only=False)
+        missing = self.engine.update_weights(named, body.get("weight_version"), bool(body.get("flush_cache", True)))
+        if self.engine.device.type == "cuda":
+            torch.cuda.synchronize()  # reply only after the copies retired: the producer may reuse its buffer
+        return self._ok(missing=missing)
+
+    async def _update_from_disk(self, request):
+        body = await self._json(request)
+        from slime_b200.checkpoint.hf_loader import SafetensorReader
+
+        reader = SafetensorReader(body["model_path"])
+        with self.engine.lock:
+            idle_deadline = time.time() + 60
+            while (self.engine.running or self.engine.prefilling) and time.time() < idle_deadline:
+                await asyncio.sleep(0.01)
+            missing = self.engine.update_weights(((n, reader.get(n)) for n in reader.keys() if not n.endswith("_scale_inv")),
+                                                 body.get("weight_version"))  # fmt: skip
+        return self._ok(message="weights reloaded", missing=missing)
+
+    async def _pull_weights(self, request):
+        body = await self._json(request)
+        from slime_b200.weight_sync.local_checkpoint import pull_weights
+
+        loop = asyncio.get_running_loop()
+        version_dir = await loop.run_in_executor(None, pull_weights, body["local_checkpoint_dir"], body["source_dir"],
+                                                 int(body["target_version"]), body.get("base_dir"))  # fmt: skip
+        return self._ok(path=version_dir)
+
+    async def _init_group(self, request):
+        body = await self._json(request)
+        from slime_b200.utils.distributed_utils import init_extra_process_group
+
+        def make():
+            return init_extra_process_group(
+                backend=body.get("backend", "nccl"), init_method=f"tcp://{body['master_address']}:{body['master_port']}",
+                world_size=body["world_size"], rank=body["rank_offset"], group_name=body["group_name"],
+            )  # fmt: skip
+
+        self._update_groups[body["group_name"]] = await asyncio.get_running_loop().run_in_executor(None, make)
+        return self._ok()
+
+    async def _destroy_group(self, request):
+        body = await self._json(request)
+        import torch.distributed as dist
+
+        g = self._update_groups.pop(body.get("group_name"), None)
+        if g is not None:
+            dist.destroy_process_group(g)
+        return self._ok()
+
+    async def _update_from_distributed(self, request):
+        body = await self._json(request)
+        import torch.distributed as dist
+
+        group = self._update_groups[body["group_name"]]
+
+        def recv():
+            named = []
+            for n, dt, shape in zip(body["names"], body["dtypes"], body["shapes"]):
+                t = torch.empty(shape, dtype=getattr(torch, dt), device=self.engine.device)
+                dist.broadcast(t, 0, group=group)
+                named.append((n, t))
+            return self.engine.update_weights(named, body.get("weight_version"), bool(body.get("flush_cache", False)))
+
+        missing = await asyncio.get_running_loop().run_in_executor(None, recv)
+        return self._ok(missing=missing)
+
+    async def _weight_version(self, request):
+        from aiohttp import web
+
+        return web.json_response({"weight_version": self.engine.get_weight_version()})
+
+    async def _weights_checker(self, request):
+        """snapshot -> reset_tensors -> compare: verifies that a sync rewrites every weight."""
+        body = await self._json(request)
+        action = body.get("action")
+        w = self.engine.weights
+        if action == "snapshot":
+            self._weights_snapshot = [t.detach().clone() for t in w.tensors()]
+        elif action == "reset_tensors":
+            for t in w.tensors():
+                t.normal_(0, 1) if t.is_floating_point() else t.zero_()
+        elif action == "compare":
+            assert self._weights_snapshot is not None, "no snapshot"
+            bad = [i for i, (a, b) in enumerate(zip(self._weights_snapshot, w.tensors())) if not torch.equal(a, b)]
+            if bad:
+                from aiohttp import web
+
+                return web.json_response({"success": False, "mismatched_tensors": bad}, status=400)
+        else:
+            return self._ok(success=False, message=f"unknown action {action}")
+        return self._ok()
+
+    async def _post_process_weights(self, request):
+        """Quantised engines: restore -> load -> re-pack cycle around a sync; dense bf16 weights need nothing."""
+        return self._ok()
+
+    async def _profile(self, request):
+        body = await self._json(request)
+        if request.path.endswith("start_profile"):
+            self._profiler = torch.profiler.profile(activities=[torch.profiler.ProfilerActivity.CPU, torch.profiler.ProfilerActivity.CUDA])
+            self._profiler.__enter__()
+            self._profile_dir = body.get("output_dir", "/tmp")
+        elif getattr(self, "_profiler", None) is not None:
+            self._profiler.__exit__(None, None, None)
+            self._profiler.export_chrome_trace(f"{self._profile_dir}/engine_{self.port}_{int(time.time())}.json")
+            self._profiler = None
+        return self._ok()
+
+    async def _server_info(self, request):
+        from aiohttp import web
+
+        a = self.engine.args
+        info = {
+            "model_path": a.model_path, "tp_size": a.tp_size, "dp_size": a.dp_size, "pp_size": a.pp_size, "ep_size": a.ep_size,
+            "disaggregation_mode": a.disaggregation_mode, "weight_version": self.engine.get_weight_version(),
+            "max_total_num_tokens": self.engine.num_pages * self.engine.page_size, "version": "slime_b200",
+            "internal_states": [self.engine.loads()],
+        }  # fmt: skip
+        return web.json_response(info)
+
+    async def _metrics(self, request):
+        from aiohttp import web
+
+        st, ld = self.engine.stats, self.engine.loads()
+        lines = [
+            f"sglang:num_running_reqs {ld['num_running_reqs']}", f"sglang:num_queue_reqs {ld['num_waiting_reqs']}",
+            f"sglang:prompt_tokens_total {st['prefill_tokens']}", f"sglang:generation_tokens_total {st['decode_tokens']}",
+            f"sglang:cached_tokens_total {st['cached_tokens']}", f"sglang:cache_hit_rate {ld['hit_rate']}",
+            f"sglang:uptime_seconds {time.time() - self.started_at}",
+        ]  # fmt: skip
+        return web.Response(text="\n".join(lines) + "\n")
+
+    # ------------------------------------------------------------------------------ lifecycle
+    def build_app(self):
+        from aiohttp import web
+
+        app = web.Application(client_max_size=1 << 34)
+        r = app.router
+        r.add_post("/generate", self._generate)
+        for path in ("/health", "/healthz"):
+            r.add_get(path, self._health)
+        r.add_get("/health_generate", self._health_generate)
+        r.add_post("/abort_request", self._abort)
+        for path in ("/v1/loads", "/get_load", "/get_loads"):
+            r.add_get(path, self._loads)
+        r.add_get("/flush_cache", self._flush)
+        r.add_post("/flush_cache", self._flush)
+        r.add_post("/pause_generation", self._pause)
+        r.add_post("/continue_generation", self._continue)
+        r.add_post("/release_memory_occupation", self._release)
+        r.add_post("/resume_memory_occupation", self._resume)
+        r.add_post("/update_weights_from_tensor", self._update_from_tensor)
+        r.add_post("/update_weights_from_disk", self._update_from_disk)
+        r.add_post("/pull_weights", self._pull_weights)
+        r.add_post("/init_weights_update_group", self._init_group)
+        r.add_post("/destroy_weights_update_group", self._destroy_group)
+        r.add_post("/update_weights_from_distributed", self._update_from_distributed)
+        for path in ("/get_weight_version", "/weight_version"):
+            r.add_get(path, self._weight_version)
+        r.add_post("/weights_checker", self._weights_checker)
+        r.add_post("/post_process_weights", self._post_process_weights)
+        r.add_post("/start_profile", self._profile)
+        r.add_post("/stop_profile", self._profile)
+        for path in ("/server_info", "/get_server_info", "/get_model_info"):
+            r.add_get(path, self._server_info)
+        r.add_get("/metrics", self._metrics)
+        return app
+
+    def start(self, block: bool = False):
+        """Start the scheduler thread and the HTTP listener (its own event loop thread unless ``block``)."""
+        from aiohttp import web
+
+        self._thread = threading.Thread(target=self._scheduler_loop, daemon=True, name="engine-scheduler")
+        self._thread.start()
+        ready = threading.Event()
+
+        def serve():
+            self._loop = asyncio.new_event_loop()
+            asyncio.set_event_loop(self._loop)
+            self._runner = web.AppRunner(self.build_app(), access_log=None)
+            self._loop.run_until_complete(self._runner.setup())
+            site = web.TCPSite(self._runner, self.host, self.port)
+            self._loop.run_until_complete(site.start())
+            ready.set()
+            self._loop.run_forever()
+
+        if block:
+            serve()
+        else:
+            self._http_thread = threading.Thread(target=serve, daemon=True, name="engine-http")
+            self._http_thread.start()
+            ready.wait(timeout=30)
+        return self
+
+    def shutdown(self):
+        self._stop.set()
+        self._wake.set()
+        if self._loop is not None:
+            async def _close():
+                await self._runner.cleanup()
+
+            fut = asyncio.run_coroutine_threadsafe(_close(), self._loop)
+            try:
+                fut.result(timeout=5)
+            except Exception:  # noqa: BLE001
+                pass
+            self._loop.call_soon_threadsafe(self._loop.stop)
+
+    @property
+    def url(self) -> str:
+        return f"http://{self.host}:{self.port}"
+
+
+def launch_server(server_args, model_config=None, tokenizer=None, weights_loader=None, block=True) -> EngineServer:
+    """Process entry point: build the engine from ``ServerArgs`` and serve."""
+    from slime_b200.models.config import ModelConfig
+
+    cfg = model_config or ModelConfig.from_hf(server_args.model_path)
+    device = torch.device("cuda", server_args.base_gpu_id) if torch.cuda.is_available() else torch.device("cpu")
+    if device.type == "cuda":
+        torch.cuda.set_device(device)
+    if tokenizer is None and server_args.model_path:
+        try:
+            from slime_b200.utils.processing_utils import load_tokenizer
+
+            tokenizer = load_tokenizer(server_args.tokenizer_path or server_args.model_path)
+        except Exception:  # noqa: BLE001
+            tokenizer = None
+    engine = Engine(cfg, server_args, device=device, tokenizer=tokenizer)
+    if weights_loader is not None:
+        weights_loader(engine)
+    elif server_args.load_format == "dummy" or not server_args.model_path:
+        engine.weights.init_random(server_args.random_seed)
+    else:
+        from slime_b200.checkpoint.hf_loader import SafetensorReader
+
+        reader = SafetensorReader(server_args.model_path)
+        engine.update_weights(((n, reader.get(n)) for n in reader.keys() if not n.endswith("_scale_inv")))
+    return EngineServer(engine, server_args.host, server_args.port, tokenizer).start(block=block)
+
+
+if __name__ == "__main__":
+    import argparse
+    import dataclasses
+
+    from slime_b200.engine.server_args import ServerArgs
+
+    p = argparse.ArgumentParser("slime_b200.engine.http_server")
+    for f in dataclasses.fields(ServerArgs):
+        kind = {"int": int, "float": float, "bool": lambda s: s.lower() in ("1", "true", "yes")}.get(str(f.type).split(" ")[0], str)
+        p.add_argument("--" + f.name.replace("_", "-"), type=kind, default=None)
+    ns = {k: v for k, v in vars(p.parse_args()).items() if v is not None}
+    launch_server(ServerArgs.from_kwargs(**ns), block=True)

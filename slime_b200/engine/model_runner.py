@@ -248,42 +248,25 @@ class ModelRunner:
         return ops.gemm(h, w.lm_head, out_dtype=torch.float32)
 
     # ---------------------------------------------------------------------- decode
-    def _decode_body(self, ids, positions, block_table, seq_lens):
-        cfg, w, d = self.cfg, self.w, self.cfg.head_dim
-        ps = self.kv.page_size
-        B = ids.numel()
-        pos64 = positions.long()
-        slots = (block_table.gather(1, (pos64 // ps)[:, None]).squeeze(1).long() * ps + pos64 % ps).to(torch.int32)
-        x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
-        x = self._tp_reduce(x) if w.tp > 1 else x
-        res = None
-        for li, L in enumerate(w.layers):
-            normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
-            qkv = self._qkv(L, normed, positions)
-            q3 = qkv.view(B, w.hq + 2 * w.hkv, d)
-            k, v = q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
-            ops.kv_write(k.reshape(B, -1), v.reshape(B, -1), slots, self.kv.k[li], self.kv.v[li])
-            ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], block_table, seq_lens, ps, self.scale)
-            x = self._tp_reduce(ops.gemm(ctx.reshape(B, -1), L["o"]))
-            normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
-            x = self._mlp(L, normed)
-        h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
-        return ops.gemm(h, w.lm_head, out_dtype=torch.float32)
+    # Per-slot decode state is device-owned (ids / pos / out_pos): the token sampled in step t is the
+    # input of step t+1 without touching the host, so steps can be launched back to back while the host
+    # lags one step behind reading results. The host owns the block table, the active mask, sampling
+    # parameters and "init" records for slots that start decoding; those live in one flat pinned buffer
+    # (double-buffered) uploaded with a single copy per step.
+    HOST_FIELDS = ("active", "init_mask", "init_ids", "init_pos", "init_out_pos", "top_k", "temperature", "top_p", "min_p")
 
     def _alloc_static(self):
-        """Decode inputs live in ONE flat int32 device buffer mirrored by a pinned host buffer, so a
-        step uploads everything (ids, positions, lengths, sampling parameters, block table) with a
-        single copy. Sections are contiguous arrays of ``max_batch`` entries; float / int64 fields
-        are bit views of the same memory."""
         B, W, dev = self.max_batch, self.max_pages_per_req, self.device
-        fields = ["ids", "positions", "seq_lens", "top_k", "out_pos", "temperature", "top_p", "min_p"]
-        total = (len(fields) + 2) * B + B * W
+        nf = len(self.HOST_FIELDS)
+        total = (nf + 2) * B + B * W
         self._flat_dev = torch.zeros(total, dtype=torch.int32, device=dev)
-        self._flat_host = torch.zeros(total, dtype=torch.int32, pin_memory=(dev.type == "cuda"))
+        self._flat_hosts = [torch.zeros(total, dtype=torch.int32, pin_memory=(dev.type == "cuda")) for _ in range(2)]
+        self._host_events = [None, None]
+        self._host_idx = 0
 
         def views(flat):
             out, off = {}, 0
-            for f in fields:
+            for f in self.HOST_FIELDS:
                 v = flat[off : off + B]
                 out[f] = v.view(torch.float32) if f in ("temperature", "top_p", "min_p") else v
                 off += B
@@ -293,21 +276,102 @@ class ModelRunner:
             return out
 
         self._static = views(self._flat_dev)
-        self.host = {k: v.numpy() for k, v in views(self._flat_host).items()}
+        # the scheduler edits `host` (plain numpy, not pinned); upload copies it into the free pinned buffer
+        import numpy as np
+
+        self._host_np = np.zeros(total, dtype=np.int32)
+        self.host = {k: v.numpy() for k, v in views(torch.from_numpy(self._host_np)).items()}
         self.host["temperature"][:] = 1.0
         self.host["top_p"][:] = 1.0
-        self.host["seq_lens"][:] = 1
+        i32 = lambda *sh: torch.zeros(*sh, dtype=torch.int32, device=dev)  # noqa: E731
+        self._dev_state = dict(ids=i32(B), pos=i32(B), out_pos=i32(B), ids_eff=i32(B), pos_eff=i32(B), seq_lens=i32(B) + 1,
+                               slots=i32(B))  # fmt: skip
 
     def upload_static(self):
-        self._flat_dev.copy_(self._flat_host, non_blocking=True)
+        """Copy the scheduler's host state to the device through a pinned staging buffer that is not in
+        flight (two alternate; an event guards reuse). ``init_mask`` is consumed by the upload."""
+        k = self._host_idx
+        ev = self._host_events[k]
+        if ev is not None:
+            ev.synchronize()
+        stage = self._flat_hosts[k]
+        stage.numpy()[:] = self._host_np
+        self._flat_dev.copy_(stage, non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record()
+            self._host_events[k] = ev
+        self._host_idx = 1 - k
+        self.host["init_mask"][:] = 0
+        return stage.numel() * 4
+
+    def _decode_step(self, n: int, filtered: bool, kept_cap: int):
+        """prepare -> model -> sample -> advance for slots [0, n). Returns (tokens, logprobs, kept_ids, kept_cnt)."""
+        cfg, w, d = self.cfg, self.w, self.cfg.head_dim
+        st, ds = self._static, self._dev_state
+        ps, W = self.kv.page_size, self.max_pages_per_req
+        ids, pos, seq_lens, slots = ds["ids_eff"][:n], ds["pos_eff"][:n], ds["seq_lens"][:n], ds["slots"][:n]
+        bt = st["block_table"][:n]
+        if self.device.type == "cuda":
+            from slime_b200.ops import _lib
+
+            P = _lib.ptr
+            _lib.check(_lib.lib().sb_decode_prepare(
+                P(ds["ids"]), P(ds["pos"]), P(ds["out_pos"]), P(st["init_mask"]), P(st["init_ids"]), P(st["init_pos"]),
+                P(st["init_out_pos"]), P(st["active"]), P(st["block_table"]), P(ds["ids_eff"]), P(ds["pos_eff"]),
+                P(ds["seq_lens"]), P(ds["slots"]), n, ps, W, _lib.stream()), "sb_decode_prepare")  # fmt: skip
+        else:
+            self._prepare_reference(n)
+        x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
+        x = self._tp_reduce(x) if w.tp > 1 else x
+        res = None
+        for li, L in enumerate(w.layers):
+            normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
+            qkv = self._qkv(L, normed, pos)
+            q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
+            k, v = q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
+            ops.kv_write(k.reshape(n, -1), v.reshape(n, -1), slots, self.kv.k[li], self.kv.v[li])
+            ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
+            x = self._tp_reduce(ops.gemm(ctx.reshape(n, -1), L["o"]))
+            normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
+            x = self._mlp(L, normed)
+        h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
+        logits = ops.gemm(h, w.lm_head, out_dtype=torch.float32)
+        tok, lp, kept_ids, kept_cnt = ops.sample(
+            logits, st["temperature"][:n], st["top_k"][:n] if filtered else None, st["top_p"][:n] if filtered else None,
+            st["min_p"][:n] if filtered else None, st["seeds"][:n], ds["out_pos"][:n], kept_cap,
+        )  # fmt: skip
+        if self.device.type == "cuda":
+            _lib.check(_lib.lib().sb_decode_advance(P(ds["ids"]), P(ds["pos"]), P(ds["out_pos"]), P(st["active"]), P(tok), n,
+                                                    _lib.stream()), "sb_decode_advance")  # fmt: skip
+        else:
+            act = st["active"][:n].bool()
+            ds["ids"][:n] = torch.where(act, tok, ds["ids"][:n])
+            ds["pos"][:n] += act.int()
+            ds["out_pos"][:n] += act.int()
+        return tok, lp, kept_ids, kept_cnt
+
+    def _prepare_reference(self, n):
+        st, ds = self._static, self._dev_state
+        ps = self.kv.page_size
+        init = st["init_mask"][:n].bool()
+        for dst, src in (("ids", "init_ids"), ("pos", "init_pos"), ("out_pos", "init_out_pos")):
+            ds[dst][:n] = torch.where(init, st[src][:n], ds[dst][:n])
+        act = st["active"][:n].bool()
+        p = ds["pos"][:n].long()
+        slot = st["block_table"][:n].gather(1, (p // ps)[:, None]).squeeze(1).long() * ps + p % ps
+        idle = torch.arange(n) % ps
+        ds["ids_eff"][:n] = torch.where(act, ds["ids"][:n], torch.zeros_like(ds["ids"][:n]))
+        ds["pos_eff"][:n] = torch.where(act, ds["pos"][:n], torch.zeros_like(ds["pos"][:n]))
+        ds["seq_lens"][:n] = torch.where(act, ds["pos"][:n] + 1, torch.ones_like(ds["pos"][:n]))
+        ds["slots"][:n] = torch.where(act, slot, idle).to(torch.int32)
 
     @torch.no_grad()
     def decode(self, n: int, filtered: bool, kept_cap: int = 0):
-        """One decode step for the first ``n`` rows of the static buffers (filled by the scheduler).
-        Returns ``(tokens, logprobs, kept_ids, kept_count)`` device tensors of length >= n."""
-        st = self._static
+        """One decode step over slots [0, n) (host state must have been uploaded). Under CUDA graphs the
+        step is one replay of the bucket that covers ``n``; extra slots are inactive by construction."""
         if not self.use_cuda_graph or self.cfg.num_experts is not None:
-            return self._decode_eager(n, filtered, kept_cap)
+            return self._decode_step(n, filtered, kept_cap)
         bucket = next(b for b in self.graph_buckets if b >= n)
         key = (bucket, filtered, kept_cap)
         if key not in self.graphs:
@@ -317,34 +381,28 @@ class ModelRunner:
         graph.replay()
         return outs
 
-    def _decode_eager(self, n, filtered, kept_cap):
-        st = self._static
-        logits = self._decode_body(st["ids"][:n], st["positions"][:n], st["block_table"][:n], st["seq_lens"][:n])
-        return self._sample(logits, n, filtered, kept_cap)
-
-    def _sample(self, logits, n, filtered, kept_cap):
-        st = self._static
-        return ops.sample(
-            logits, st["temperature"][:n], st["top_k"][:n] if filtered else None, st["top_p"][:n] if filtered else None,
-            st["min_p"][:n] if filtered else None, st["seeds"][:n], st["out_pos"][:n], kept_cap,
-        )  # fmt: skip
-
     def _capture(self, bucket, filtered, kept_cap):
-        st = self._static
-        # warm up outside capture (lazy kernel attribute setup, allocator pools)
+        """Capture one decode step. Warm-up and capture run with every slot inactive, so they only touch the
+        reserved scratch page and leave the device-owned request state unchanged."""
+        from slime_b200.ops import _lib
+
+        saved_active = self._static["active"].clone()
+        saved_init = self._static["init_mask"].clone()
+        self._static["active"].zero_()
+        self._static["init_mask"].zero_()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                self._decode_eager(bucket, filtered, kept_cap)
+                self._decode_step(bucket, filtered, kept_cap)
         torch.cuda.current_stream().wait_stream(side)
-        from slime_b200.ops import _lib
-
         g = torch.cuda.CUDAGraph()
         before = _lib.launch_count()
         with torch.cuda.graph(g):
-            outs = self._decode_eager(bucket, filtered, kept_cap)
+            outs = self._decode_step(bucket, filtered, kept_cap)
         self.graphs[(bucket, filtered, kept_cap)] = (g, outs, _lib.launch_count() - before)
+        self._static["active"].copy_(saved_active)
+        self._static["init_mask"].copy_(saved_init)
 
     def drop_graphs(self):
         """Memory tag ``cuda_graph``: captured graphs pin their private pools."""

@@ -83,6 +83,13 @@ class Request:
     on_token: Any = None  # callback(req) for streaming
     done_event: Any = None
     text_so_far: str = ""
+    # decode-slot bookkeeping (see Engine._start_decoding)
+    ctx_ids: list[int] = field(default_factory=list)  # tokens to prefill (prompt, plus outputs after a retraction)
+    slot: int | None = None
+    decode_from_step: int = 0
+    harvested: int = 0
+    end_step: int | None = None
+    end_reason: dict | None = None
 
     @property
     def seq_len(self) -> int:

@@ -44,6 +44,8 @@ _SIGS = {
     "sb_pg_loss": [P, P, P, P, P, P, P, P, I, F, F, F, I, P],
     "sb_sample": [P, I, L, I, I, P, P, P, P, P, P, P, P, P, P, I, P],
     "sb_kv_write": [P, P, P, P, P, I, I, I, I, P],
+    "sb_decode_prepare": [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
+    "sb_decode_advance": [P, P, P, P, P, I, P],
     "sb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "sb_block_fp8_quant": [P, P, P, I, I, L, L, I, I, I, P],
     "sb_block_fp8_dequant": [P, P, P, I, I, I, I, P],
@@ -102,7 +104,15 @@ def check(rc: int, what: str):
     global _launches
     _launches += 1
     if rc != 0:
-        raise RuntimeError(f"{what} failed with CUDA error {rc}")
+        detail = ""
+        try:
+            fn = lib().sb_last_error
+            fn.restype = ctypes.c_char_p
+            fn.argtypes = []
+            detail = (fn() or b"").decode(errors="replace")
+        except Exception:  # noqa: BLE001
+            pass
+        raise RuntimeError(f"{what} failed with CUDA error {rc} {detail}")
 
 
 def launch_count() -> int:

@@ -1,0 +1,148 @@
+"""Rollout engine on CPU (fp32 reference ops): scheduling, prefix cache, stop conditions, control plane."""
+
+import numpy as np
+import pytest
+import torch
+
+from slime_b200.engine.engine import Engine
+from slime_b200.engine.kv_cache import PageAllocator
+from slime_b200.engine.server_args import ServerArgs
+from slime_b200.models.config import get_preset
+
+
+def make_engine(pages=96, max_running=8, **kw):
+    cfg = get_preset("tiny")
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=max_running, context_length=128, disable_cuda_graph=True, **kw),
+               device="cpu", num_pages=pages)  # fmt: skip
+    e.weights.init_random(0)
+    return e
+
+
+def teacher_forced(e, ids, n_prompt):
+    rq = e.generate([ids], [dict(max_new_tokens=0)], logprob_start_len=0)[0]
+    return np.array(rq.input_logprobs[n_prompt:])
+
+
+def test_decode_logprobs_match_teacher_forcing_and_prefix_cache():
+    e = make_engine()
+    p = [1, 2, 3, 4, 5, 6, 7, 8, 9, 10]
+    reqs = e.generate([p] * 4 + [[5, 4, 3, 2, 1, 9, 9, 9, 9]], [dict(max_new_tokens=6 + i, ignore_eos=True) for i in range(5)])
+    for i, r in enumerate(reqs):
+        assert len(r.output_ids) == 6 + i and r.finish_reason["type"] == "length"
+        ref = teacher_forced(e, r.input_ids + r.output_ids, len(r.input_ids))
+        assert np.abs(ref - np.array(r.output_logprobs)).max() < 1e-5
+    assert [r.num_cached_tokens for r in reqs[:4]] == [0, 8, 8, 8]  # siblings reuse the first request's full pages
+    assert e.kv.allocator.stats()["hit_rate"] > 0
+    assert not e.has_work() and all(s is None for s in e.slot_req)
+
+
+def test_same_seed_reproduces_and_different_seed_differs():
+    e = make_engine()
+    p = [3, 1, 4, 1, 5, 9, 2, 6]
+    a, b, c = e.generate([p, p, p], [dict(max_new_tokens=12, ignore_eos=True, sampling_seed=s) for s in (7, 7, 8)])
+    assert a.output_ids == b.output_ids
+    assert a.output_ids != c.output_ids
+
+
+def test_eos_and_stop_token_finish_and_discard_overshoot():
+    e = make_engine()
+    p = [1, 2, 3, 4, 5]
+    base = e.generate([p], [dict(max_new_tokens=20, ignore_eos=True, sampling_seed=1)])[0]
+    stop_tok = base.output_ids[6]
+    first = base.output_ids.index(stop_tok)
+    r = e.generate([p], [dict(max_new_tokens=20, ignore_eos=True, sampling_seed=1, stop_token_ids=[stop_tok])])[0]
+    assert r.output_ids == base.output_ids[: first + 1]
+    assert r.finish_reason == {"type": "stop", "matched": stop_tok}
+    e.eos_ids = {stop_tok}
+    r2 = e.generate([p], [dict(max_new_tokens=20, sampling_seed=1)])[0]
+    assert r2.output_ids == base.output_ids[: first + 1] and r2.finish_reason["type"] == "stop"
+    r3 = e.generate([p], [dict(max_new_tokens=20, sampling_seed=1, min_new_tokens=first + 2)])[0]
+    assert len(r3.output_ids) > first + 1
+
+
+def test_abort_pause_flush_and_memory_tags():
+    e = make_engine()
+    r = e.add_request([1, 2, 3], dict(max_new_tokens=50, ignore_eos=True))
+    for _ in range(5):
+        e.step()
+    assert not e.flush_cache()  # busy
+    assert e.abort(r.rid) == 1
+    assert r.finish_reason == {"type": "abort"} and 0 < len(r.output_ids) < 50
+    assert len(r.output_logprobs) == len(r.output_ids)
+    assert e.flush_cache()
+    e.pause_generation()
+    r2 = e.add_request([1, 2, 3], dict(max_new_tokens=3, ignore_eos=True))
+    assert e.step() == [] and not r2.finished()
+    e.continue_generation()
+    while e.has_work():
+        e.step()
+    assert r2.finished()
+    free_before = e.kv.allocator.available()
+    e.release_memory_occupation(["kv_cache"])
+    e.release_memory_occupation(["kv_cache"])  # idempotent
+    assert e.step() == []
+    e.resume_memory_occupation(["kv_cache"])
+    assert e.kv.allocator.available() >= free_before - 1
+    e.release_memory_occupation(["weights"])
+    e.resume_memory_occupation(["weights"])
+    e.weights.init_random(0)
+    assert e.generate([[1, 2, 3]], [dict(max_new_tokens=2, ignore_eos=True)])[0].finished()
+
+
+def test_retraction_when_cache_is_exhausted_keeps_outputs_consistent():
+    e = make_engine(pages=14, max_running=4)  # 13 usable pages of 4 tokens
+    prompts = [[i + 1] * 6 for i in range(4)]
+    reqs = e.generate(prompts, [dict(max_new_tokens=24, ignore_eos=True, sampling_seed=i) for i in range(4)])
+    assert all(len(r.output_ids) == 24 for r in reqs)
+    big = make_engine(pages=200, max_running=4)
+    ref = big.generate(prompts, [dict(max_new_tokens=24, ignore_eos=True, sampling_seed=i) for i in range(4)])
+    for a, b in zip(reqs, ref):
+        assert a.output_ids == b.output_ids  # re-prefill after retraction continues the same sequence
+        assert np.abs(np.array(a.output_logprobs) - np.array(b.output_logprobs)).max() < 1e-4
+
+
+def test_update_weights_changes_outputs_and_version():
+    e = make_engine()
+    p = [2, 7, 1, 8]
+    a = e.generate([p], [dict(max_new_tokens=8, ignore_eos=True, sampling_seed=3)])[0]
+    named = [("model.layers.0.mlp.down_proj.weight", torch.randn(128, 256) * 0.5)]
+    assert e.update_weights(named, version="7") == []
+    assert e.get_weight_version() == "7"
+    b = e.generate([p], [dict(max_new_tokens=8, ignore_eos=True, sampling_seed=3)])[0]
+    assert b.weight_version == "7" and b.num_cached_tokens == 0  # the prefix cache was flushed with the update
+    assert a.output_logprobs != b.output_logprobs
+    assert e.update_weights([("model.layers.0.nonexistent.weight", torch.zeros(1))]) == ["model.layers.0.nonexistent.weight"]
+
+
+def test_top_p_returns_kept_sets_and_renormalised_logprobs():
+    e = make_engine()
+    sp = dict(max_new_tokens=5, ignore_eos=True, top_p=0.3, top_k=20, custom_params={"return_top_p_token_ids": True})
+    r = e.generate([[1, 2, 3, 4]], [sp])[0]
+    assert len(r.kept_offsets) == len(r.output_ids) + 1 and r.kept_offsets[-1] == len(r.kept_ids)
+    for i, tok in enumerate(r.output_ids):
+        kept = r.kept_ids[r.kept_offsets[i] : r.kept_offsets[i + 1]]
+        assert tok in kept and len(kept) <= 20
+    m = e.meta_info(r)
+    from slime_b200.utils.misc import decode_int32_meta_array
+
+    assert decode_int32_meta_array(m, "top_p_token_offsets").tolist() == r.kept_offsets
+    plain = teacher_forced(e, r.input_ids + r.output_ids, 4)
+    assert all(lp >= ref - 1e-5 for lp, ref in zip(r.output_logprobs, plain))  # renormalising can only raise log-probs
+
+
+def test_page_allocator_prefix_index_and_lru():
+    a = PageAllocator(8, 4)
+    toks = list(range(13))
+    pages = a.alloc(4)
+    parent = b""
+    for i in range(3):
+        parent = a.commit(pages[i], parent, toks[i * 4 : (i + 1) * 4])
+    a.release(pages)
+    assert a.available() == 8 and len(a.lru) == 3
+    got, _ = a.match_prefix(toks)
+    assert got == pages[:3]
+    a.release(got)
+    taken = a.alloc(8)  # evicts the cached pages in LRU order
+    assert len(set(taken)) == 8 and not a.index
+    with pytest.raises(Exception):
+        a.alloc(1)
