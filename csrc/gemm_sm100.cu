@@ -10,9 +10,13 @@
 // and wgrad (dY^T X) without materialising any transpose.
 //
 // CTA = 6 warps: warp 0 issues TMA loads (one lane), warp 1 owns TMEM and issues
-// tcgen05.mma (one lane), warps 2-5 drain the accumulators (tcgen05.ld) and write
-// C. Tile 128 x BN x 64, STAGES-deep smem ring, two TMEM accumulator stages so the
-// epilogue of tile i overlaps the main loop of tile i+1. Grid = min(#tiles, #SMs).
+// tcgen05.mma (one lane), warps 2-5 drain the accumulators: tcgen05.ld -> registers ->
+// (bias, cast) -> 128B-swizzled shared staging -> TMA store (or TMA reduce-add when
+// accumulating into an fp32 C, e.g. wgrad into the main-grad buffer). Tile 128 x BN x 64,
+// STAGES-deep smem ring, two TMEM accumulator stages so the epilogue of tile i overlaps
+// the main loop of tile i+1. Grid = min(#tiles, #SMs).
+// When C's pitch or base is not 16-byte aligned the epilogue falls back to direct,
+// bounds-checked global stores.
 #include "common.cuh"
 
 namespace sb {
@@ -20,6 +24,8 @@ namespace sb {
 constexpr int GEMM_BM = 128;
 constexpr int GEMM_BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int GEMM_THREADS = 192;
+constexpr int EPI_BUF_BYTES = 32 * 128;  // 32 rows x 128 B per staging buffer
+constexpr int EPI_BYTES = 4 * 2 * EPI_BUF_BYTES;  // 4 epilogue warps x 2 buffers
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -27,20 +33,22 @@ struct GemmSmem {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int BAR_BYTES = (2 * STAGES + 4) * 8 + 16;
-  static constexpr int TOTAL = STAGES * STAGE_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
 };
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, void* __restrict__ Cv,
-                 const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, int accumulate, int* status) {
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv, const __nv_bfloat16* __restrict__ bias,
+                 int M, int N, int K, int ldc, int accumulate, int* status) {
   using S = GemmSmem<BN, STAGES>;
   constexpr int NCOLS = 2 * BN;  // two accumulator stages (power of two: 256 or 512)
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * S::A_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * S::STAGE_BYTES);
+  uint8_t* sC = smem + STAGES * S::STAGE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sC + EPI_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
@@ -66,6 +74,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     fence_barrier_init();
     tma_prefetch_desc(&tmA);
     tma_prefetch_desc(&tmB);
+    if constexpr (TMA_EPI) tma_prefetch_desc(&tmC);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, NCOLS);
@@ -162,6 +171,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint8_t* stage_buf = sC + q * 2 * EPI_BUF_BYTES;
+    int buf = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
       const int m0 = (tile % tiles_m) * GEMM_BM;
       const int n0 = (tile / tiles_m) * BN;
@@ -169,55 +180,96 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-      const int row = m0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+      if constexpr (TMA_EPI) {
+        // one box = 32 rows x 128 bytes: 64 bf16 columns or 32 fp32 columns
+        constexpr int BOX_COLS = OUT_F32 ? 32 : 64;
+        const int row0 = m0 + q * 32;
 #pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c * 32, r);
-        tmem_ld_wait();
-        const int col0 = n0 + c * 32;
-        if (row < M && col0 < N) {
-          float v[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
-          if (bias != nullptr) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i)
-              if (col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
-          }
+        for (int c = 0; c < BN / BOX_COLS; ++c) {
+          const int col0 = n0 + c * BOX_COLS;
+          uint8_t* dst = stage_buf + buf * EPI_BUF_BYTES;
+          if (lane == 0) bulk_wait_group_read<1>();  // the store that last used this buffer has drained it
+          __syncwarp();
+          uint8_t* my_row = dst + lane * 128;
+          const int sw = lane & 7;  // 128B swizzle: 16-byte chunk j of row r lives at chunk j ^ (r % 8)
           if constexpr (OUT_F32) {
-            float* crow = reinterpret_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + col0;
-            const bool vec = (col0 + 32 <= N) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-            if (vec) {
-              float4* c4 = reinterpret_cast<float4*>(crow);
+            uint32_t r[32];
+            tmem_ld_32x32(t_row + c * 32, r);
+            tmem_ld_wait();
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (accumulate) {
-                  const float4 p = c4[i];
-                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
-                }
-                c4[i] = o;
+            for (int j = 0; j < 8; ++j) {
+              float4 o = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                     __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+              if (bias != nullptr) {
+                const int cc = col0 + 4 * j;
+                if (cc + 0 < N) o.x += __bfloat162float(bias[cc + 0]);
+                if (cc + 1 < N) o.y += __bfloat162float(bias[cc + 1]);
+                if (cc + 2 < N) o.z += __bfloat162float(bias[cc + 2]);
+                if (cc + 3 < N) o.w += __bfloat162float(bias[cc + 3]);
               }
-            } else {
-              for (int i = 0; i < 32 && col0 + i < N; ++i) crow[i] = accumulate ? crow[i] + v[i] : v[i];
+              *reinterpret_cast<float4*>(my_row + ((j ^ sw) << 4)) = o;
             }
           } else {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
-            const bool vec = (col0 + 32 <= N) && ((reinterpret_cast<uintptr_t>(crow) & 15) == 0);
-            if (vec) {
-              uint4* c4 = reinterpret_cast<uint4*>(crow);
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
+            for (int half = 0; half < 2; ++half) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_row + c * 64 + half * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
+                if (bias != nullptr) {
+                  const int cc = col0 + half * 32 + 8 * j;
+#pragma unroll
+                  for (int i = 0; i < 8; ++i)
+                    if (cc + i < N) v[i] += __bfloat162float(bias[cc + i]);
+                }
                 uint4 o;
-                o.x = pack_bf16x2(v[8 * i + 0], v[8 * i + 1]);
-                o.y = pack_bf16x2(v[8 * i + 2], v[8 * i + 3]);
-                o.z = pack_bf16x2(v[8 * i + 4], v[8 * i + 5]);
-                o.w = pack_bf16x2(v[8 * i + 6], v[8 * i + 7]);
-                c4[i] = o;
+                o.x = pack_bf16x2(v[0], v[1]);
+                o.y = pack_bf16x2(v[2], v[3]);
+                o.z = pack_bf16x2(v[4], v[5]);
+                o.w = pack_bf16x2(v[6], v[7]);
+                *reinterpret_cast<uint4*>(my_row + (((half * 4 + j) ^ sw) << 4)) = o;
+              }
+            }
+          }
+          fence_proxy_async();  // generic-proxy writes -> visible to the TMA engine
+          __syncwarp();
+          if (lane == 0 && row0 < M && col0 < N) {
+            if (accumulate)
+              tma_reduce_add_2d(&tmC, dst, col0, row0);
+            else
+              tma_store_2d(&tmC, dst, col0, row0);
+            bulk_commit_group();
+          }
+          buf ^= 1;
+        }
+      } else {
+        const int row = m0 + q * 32 + lane;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 < N) {
+            if constexpr (OUT_F32) {
+              float* crow = reinterpret_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+              for (int i = 0; i < 32 && col0 + i < N; ++i) {
+                float v = __uint_as_float(r[i]);
+                if (bias != nullptr) v += __bfloat162float(bias[col0 + i]);
+                crow[i] = accumulate ? crow[i] + v : v;
               }
             } else {
-              for (int i = 0; i < 32 && col0 + i < N; ++i) crow[i] = __float2bfloat16(v[i]);
+              __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+              for (int i = 0; i < 32 && col0 + i < N; ++i) {
+                float v = __uint_as_float(r[i]);
+                if (bias != nullptr) v += __bfloat162float(bias[col0 + i]);
+                crow[i] = __float2bfloat16(v);
+              }
             }
           }
         }
@@ -229,6 +281,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         acc = 0;
         acc_phase ^= 1;
       }
+    }
+    if constexpr (TMA_EPI) {
+      if (lane == 0) bulk_wait_group_read<0>();  // staging memory must outlive the stores that read it
+      __syncwarp();
     }
   }
 
@@ -244,7 +300,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, NCOLS);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
 static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
                                int ldb, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
@@ -258,7 +314,14 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
                                         CU_TENSOR_MAP_SWIZZLE_128B)
                          : make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, size_t(ldb) * 2, BN, GEMM_BK,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32>;
+  CUtensorMap tmC = tmA;  // placeholder when the direct-store epilogue is used
+  if constexpr (TMA_EPI) {
+    tmC = OUT_F32 ? make_tmap_2d(C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, size_t(ldc) * 4, 32, 32,
+                                 CU_TENSOR_MAP_SWIZZLE_128B)
+                  : make_tmap_2d(C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, size_t(ldc) * 2, 32, 64,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+  }
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32, TMA_EPI>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -270,21 +333,21 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   }
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc,
-                                                 accumulate, status);
+  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmC, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
+                                                 ldc, accumulate, status);
   cudaError_t le = cudaGetLastError();
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
   return le;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool TMA_EPI>
 static cudaError_t dispatch_layout(bool a_mn, bool b_mn, bool out_f32, const void* A, const void* B, void* C,
                                    const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int accumulate,
                                    int* status, int num_sms, cudaStream_t stream) {
-#define SB_CASE(AM, BMN, OF)                                                                                      \
-  if (a_mn == AM && b_mn == BMN && out_f32 == OF)                                                                 \
-    return launch_gemm<BN, STAGES, AM, BMN, OF>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, status, num_sms, \
-                                                stream);
+#define SB_CASE(AM, BMN, OF)                                                                                       \
+  if (a_mn == AM && b_mn == BMN && out_f32 == OF)                                                                  \
+    return launch_gemm<BN, STAGES, AM, BMN, OF, TMA_EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, status, \
+                                                         num_sms, stream);
   SB_CASE(false, false, false)
   SB_CASE(false, false, true)
   SB_CASE(false, true, false)
@@ -299,21 +362,31 @@ static cudaError_t dispatch_layout(bool a_mn, bool b_mn, bool out_f32, const voi
 
 }  // namespace sb
 
-// C ABI. Leading dimensions are in elements. Returns a cudaError_t value.
+// C ABI. Leading dimensions are in elements. Returns a cudaError_t value (0 = ok); sb_last_error() has details.
 //   a_mn = 0: A is row-major [M, K] (pitch lda);  a_mn = 1: A is stored [K, M] (pitch lda)
 //   b_mn = 0: B is row-major [N, K] (pitch ldb);  b_mn = 1: B is stored [K, N] (pitch ldb)
-// Requirements: base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
+// Requirements: A/B base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
 // `status` is a device int that receives a non-zero code if a bounded wait expired.
 extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
                             int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* status,
                             int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const size_t c_elem = out_f32 ? 4 : 2;
+  const bool tma_epi = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * c_elem) % 16 == 0 &&
+                       !(accumulate && !out_f32);
   try {
-    if (bn == 256)
-      return (int)sb::dispatch_layout<256, 4>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb, ldc,
-                                              accumulate, status, num_sms, stream);
-    return (int)sb::dispatch_layout<128, 6>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb, ldc,
-                                            accumulate, status, num_sms, stream);
+    if (bn == 256) {
+      if (tma_epi)
+        return (int)sb::dispatch_layout<256, 4, true>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb,
+                                                      ldc, accumulate, status, num_sms, stream);
+      return (int)sb::dispatch_layout<256, 4, false>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb,
+                                                     ldc, accumulate, status, num_sms, stream);
+    }
+    if (tma_epi)
+      return (int)sb::dispatch_layout<128, 6, true>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb,
+                                                    ldc, accumulate, status, num_sms, stream);
+    return (int)sb::dispatch_layout<128, 6, false>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb,
+                                                   ldc, accumulate, status, num_sms, stream);
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;

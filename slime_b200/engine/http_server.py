@@ -441,7 +441,7 @@ def launch_server(server_args, model_config=None, tokenizer=None, weights_loader
     engine = Engine(cfg, server_args, device=device, tokenizer=tokenizer)
     if weights_loader is not None:
         weights_loader(engine)
-    elif server_args.load_format == "dummy" or not server_args.model_path:
+    elif server_args.load_format == "dummy" or not server_args.model_path or server_args.model_path.startswith("preset:"):
         engine.weights.init_random(server_args.random_seed)
     else:
         from slime_b200.checkpoint.hf_loader import SafetensorReader

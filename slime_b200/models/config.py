@@ -103,6 +103,8 @@ class ModelConfig:
     def from_hf(cls, path_or_dict) -> "ModelConfig":
         if isinstance(path_or_dict, dict):
             c = path_or_dict
+        elif isinstance(path_or_dict, str) and path_or_dict.startswith("preset:"):
+            return get_preset(path_or_dict[len("preset:") :])  # random-weight runs with no checkpoint directory
         else:
             with open(os.path.join(path_or_dict, "config.json")) as f:
                 c = json.load(f)
