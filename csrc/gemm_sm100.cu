@@ -188,6 +188,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 #pragma unroll 1
         for (int c = 0; c < BN / BOX_COLS; ++c) {
           const int col0 = n0 + c * BOX_COLS;
+          // Boxes that lie wholly outside C are skipped as a whole (warp-uniform): every iteration that touches a
+          // staging buffer also commits exactly one bulk group, which is what makes wait_group<1> mean "the store
+          // that last read THIS buffer is done".
+          if (row0 >= M || col0 >= N) break;
           uint8_t* dst = stage_buf + buf * EPI_BUF_BYTES;
           if (lane == 0) bulk_wait_group_read<1>();  // the store that last used this buffer has drained it
           __syncwarp();
@@ -238,7 +242,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           fence_proxy_async();  // generic-proxy writes -> visible to the TMA engine
           __syncwarp();
-          if (lane == 0 && row0 < M && col0 < N) {
+          if (lane == 0) {
             if (accumulate)
               tma_reduce_add_2d(&tmC, dst, col0, row0);
             else

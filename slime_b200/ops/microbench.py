@@ -1,0 +1,204 @@
+"""Kernel micro-benchmarks: ``python -m slime_b200.ops.microbench {gemm,decode,norm} [options]``.
+
+Every number is a CUDA-event time on the launching stream after warm-up, median over ``--iters`` timed
+repetitions with an L2 flush (a 256 MiB memset) between them. One JSON object per line on stdout.
+
+    gemm    tcgen05 GEMM vs cuBLAS (torch.matmul) for forward / dgrad / wgrad layouts
+    decode  each kernel of one rollout decode step at a given batch and context length
+    norm    RMSNorm forward/backward bandwidth
+
+``--small`` shrinks the working set to a case suitable for a profiler capture (a few launches, < 1 GB).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from slime_b200 import ops
+from slime_b200.ops import _lib
+
+_FLUSH = None
+
+
+def _flush_l2():
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    _FLUSH.zero_()
+
+
+def time_ms(fn, iters: int = 20, warmup: int = 3, reps: int = 1, flush: bool = True) -> float:
+    """Median device time of ``reps`` back-to-back calls of ``fn`` (divided by ``reps``)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush:
+            _flush_l2()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e) / reps)
+    times.sort()
+    return times[len(times) // 2]
+
+
+def _emit(**kw):
+    print(json.dumps(kw), flush=True)
+
+
+# ------------------------------------------------------------------------------------ gemm
+GEMM_SHAPES = [(16384, 1152, 896), (16384, 896, 896), (16384, 9728, 896), (16384, 896, 4864), (8192, 8192, 8192),
+               (4096, 151936, 896), (256, 1152, 896), (256, 9728, 896), (256, 151936, 896)]  # fmt: skip
+GRAD_SHAPES = [(16384, 9728, 896), (16384, 896, 4864), (16384, 1152, 896)]  # (tokens, out features, in features)
+
+
+def bench_gemm(a):
+    shapes, grads = (GEMM_SHAPES, GRAD_SHAPES) if not a.small else ([(4096, 4096, 4096)], [])
+    if a.shape:
+        shapes, grads = [tuple(a.shape)], []
+    bf = torch.bfloat16
+    for M, N, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=bf)
+        w = torch.randn(N, K, device="cuda", dtype=bf)
+        fl = 2.0 * M * N * K
+        for bn in (128, 256):
+            t = time_ms(lambda: ops.gemm(x, w, bn=bn), a.iters)
+            _emit(kind="nt", M=M, N=N, K=K, bn=bn, ms=t, tflops=fl / t / 1e9)
+        if not a.no_cublas:
+            t = time_ms(lambda: x @ w.t(), a.iters)
+            _emit(kind="cublas_nt", M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9)
+    for T, O, I in grads:
+        dy = torch.randn(T, O, device="cuda", dtype=bf)
+        w = torch.randn(O, I, device="cuda", dtype=bf)
+        x = torch.randn(T, I, device="cuda", dtype=bf)
+        acc = torch.zeros(O, I, device="cuda", dtype=torch.float32)
+        fl = 2.0 * T * O * I
+        for name, fn, ref in (
+            ("dgrad", lambda: ops.gemm(dy, w, b_mn=True), lambda: dy @ w),
+            ("wgrad", lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=torch.float32), lambda: dy.t() @ x),
+            ("wgrad_accumulate", lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=acc, accumulate=True), None),
+        ):
+            t = time_ms(fn, a.iters)
+            _emit(kind=name, T=T, O=O, I=I, ms=t, tflops=fl / t / 1e9)
+            if ref is not None and not a.no_cublas:
+                t = time_ms(ref, a.iters)
+                _emit(kind="cublas_" + name, T=T, O=O, I=I, ms=t, tflops=fl / t / 1e9)
+    _lib.check_status("cuda")
+
+
+# ---------------------------------------------------------------------------------- decode
+def bench_decode(a):
+    """Times each kernel of a decode step in isolation (back-to-back launches, no L2 flush: in a real step the
+    weights of a 0.5B model stay L2-resident), then one full layer loop, so shares and launch gaps are visible."""
+    from slime_b200.models.config import get_preset
+
+    cfg = get_preset(a.model)
+    B, ctx, ps = a.batch, a.context, 16
+    d, hq, hkv, H, F, V = cfg.head_dim, cfg.num_attention_heads, cfg.num_query_groups, cfg.hidden_size, cfg.ffn_hidden_size, cfg.vocab_size
+    bf, dev = torch.bfloat16, "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: (0.02 * torch.randn(*s, device=dev, generator=g)).to(bf)  # noqa: E731
+    x, res = rnd(B, H), rnd(B, H)
+    ln = torch.ones(H, device=dev, dtype=bf)
+    wqkv, bqkv = rnd((hq + 2 * hkv) * d, H), (rnd((hq + 2 * hkv) * d) if cfg.add_qkv_bias else None)
+    wo, wgu, wdn, wlm = rnd(H, hq * d), rnd(2 * F, H), rnd(H, F), rnd(V, H)
+    pages = B * math.ceil((ctx + 1) / ps) + 1
+    kc, vc = rnd(pages * ps, hkv, d), rnd(pages * ps, hkv, d)
+    per = math.ceil((ctx + 1) / ps)
+    bt = (1 + torch.arange(B * per, device=dev, dtype=torch.int32)).view(B, per).contiguous()
+    seq = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+    pos = seq - 1
+    slots = (bt[:, -1] * ps).to(torch.int32)
+    rope = ops.rope_cos_sin(ctx + 8, d, cfg.rotary_base, device=dev)
+    qn = torch.ones(d, device=dev, dtype=bf) if cfg.qk_layernorm else None
+    temp = torch.ones(B, device=dev)
+    seeds = torch.arange(B, device=dev, dtype=torch.int64)
+    outp = torch.zeros(B, device=dev, dtype=torch.int32)
+
+    qkv = ops.gemm(x, wqkv, bias=bqkv)
+    q3 = qkv.view(B, hq + 2 * hkv, d)
+    attn = ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps)
+    gu = ops.gemm(x, wgu)
+    act = ops.swiglu(gu)
+    logits = ops.gemm(x, wlm, out_dtype=torch.float32)
+    steps = {
+        "rmsnorm_add": lambda: ops.rmsnorm(x, ln, 1e-6, res),
+        "gemm_qkv": lambda: ops.gemm(x, wqkv, bias=bqkv),
+        "rope_qk": lambda: ops.rope_qk(qkv, pos, rope, hq, hkv, d, qn, qn, 1e-6),
+        "kv_write": lambda: ops.kv_write(q3[:, hq : hq + hkv].reshape(B, -1), q3[:, hq + hkv :].reshape(B, -1), slots, kc, vc),
+        "paged_attention": lambda: ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps),
+        "gemm_o": lambda: ops.gemm(attn.reshape(B, -1), wo),
+        "gemm_gate_up": lambda: ops.gemm(x, wgu),
+        "swiglu": lambda: ops.swiglu(gu),
+        "gemm_down": lambda: ops.gemm(act, wdn),
+        "gemm_lm_head": lambda: ops.gemm(x, wlm, out_dtype=torch.float32),
+        "sample": lambda: ops.sample(logits, temp, None, None, None, seeds, outp, 0),
+    }
+    per_layer = ["rmsnorm_add", "gemm_qkv", "rope_qk", "kv_write", "paged_attention", "gemm_o", "rmsnorm_add", "gemm_gate_up",
+                 "swiglu", "gemm_down"]  # fmt: skip
+    t_of = {}
+    for name, fn in steps.items():
+        t_of[name] = time_ms(fn, a.iters, reps=a.reps, flush=False)
+        _emit(kind="decode_kernel", name=name, batch=B, context=ctx, us=1e3 * t_of[name])
+    est = cfg.num_layers * sum(t_of[k] for k in per_layer) + t_of["gemm_lm_head"] + t_of["sample"] + t_of["rmsnorm_add"]
+
+    def layer_loop():
+        for _ in range(cfg.num_layers):
+            for k in per_layer:
+                steps[k]()
+
+    eager = time_ms(layer_loop, max(3, a.iters // 4), flush=False)
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        layer_loop()
+    graphed = time_ms(gr.replay, max(3, a.iters // 4), flush=False)
+    kv_bytes = 2.0 * B * ctx * hkv * d * 2 * cfg.num_layers
+    w_bytes = 2.0 * (cfg.num_params() - (0 if cfg.tie_word_embeddings else V * H))
+    _emit(kind="decode_step", batch=B, context=ctx, model=a.model, sum_of_kernels_ms=est, layers_eager_ms=eager,
+          layers_graph_ms=graphed, kv_bytes=kv_bytes, weight_bytes=w_bytes)
+    _lib.check_status("cuda")
+
+
+# ------------------------------------------------------------------------------------ norm
+def bench_norm(a):
+    for T, H in ((16384, 896), (16384, 4096), (65536, 2560)) if not a.small else ((4096, 4096),):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        t = time_ms(lambda: ops.rmsnorm(x.detach(), w.detach(), 1e-6, r), a.iters)
+        _emit(kind="rmsnorm_fwd", T=T, H=H, ms=t, gbs=4 * T * H * 2 / t / 1e6)  # read x, r; write y, h
+        y, h = ops.rmsnorm(x, w, 1e-6, r)
+        gy, gh = torch.randn_like(y), torch.randn_like(h)
+        t = time_ms(lambda: torch.autograd.grad([y, h], [x], [gy, gh], retain_graph=True), a.iters)
+        _emit(kind="rmsnorm_bwd", T=T, H=H, ms=t, gbs=4 * T * H * 2 / t / 1e6)  # read dy, dres, h; write dh
+
+
+def main(argv=None):
+    p = argparse.ArgumentParser(prog="python -m slime_b200.ops.microbench")
+    p.add_argument("what", choices=["gemm", "decode", "norm"])
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--reps", type=int, default=20, help="back-to-back launches per timed repetition (decode)")
+    p.add_argument("--small", action="store_true")
+    p.add_argument("--no-cublas", action="store_true")
+    p.add_argument("--shape", type=int, nargs=3, metavar=("M", "N", "K"))
+    p.add_argument("--model", default="qwen2.5-0.5b")
+    p.add_argument("--batch", type=int, default=256)
+    p.add_argument("--context", type=int, default=768)
+    a = p.parse_args(argv)
+    from slime_b200.ops import build
+
+    build.build()
+    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm}[a.what](a)
+
+
+if __name__ == "__main__":
+    main()
