@@ -363,3 +363,87 @@ extern "C" int sb_add_bf16(const void* a, const void* b, void* out, long n, cuda
                                                                     (size_t)n / 8);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// RMSNorm backward with library-owned scratch (see rmsnorm_bwd_static.h for the contract). Nothing above this
+// line is changed by it; it launches the same two kernels as sb_rmsnorm_bwd with `dw_partial` pointing into the
+// array below.
+#include <atomic>
+#include <cstdio>
+
+#include "rmsnorm_bwd_static.h"
+
+static_assert(SB_RMSNORM_STATIC_MAX_H == sb::NORM_THREADS * sb::NORM_MAX_VEC * 8,
+              "the static scratch is sized for the widest row the norm kernels accept");
+
+// [SB_RMSNORM_STATIC_MAX_CTAS, SB_RMSNORM_STATIC_MAX_H] fp32, 4.6 MiB. In host code this name is only a host-side
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float g_rmsnorm_bwd_static_scratch[SB_RMSNORM_STATIC_MAX_CTAS * SB_RMSNORM_STATIC_MAX_H];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::atomic<float*> g_static_scratch_addr[kStaticMaxDevices];  // zero-initialised; one slot per device ordinal
+
+// Writes straight into the thread's message buffer: no std::string, no heap.
+template <typename... A>
+void static_fail(const char* fmt, A... a) {
+  std::snprintf(sb::last_error_buf(), 512, fmt, a...);
+}
+
+// Returns the cached device address of the scratch for the current device, looking it up on first use.
+int static_scratch_for_current_device(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    static_fail("sb_rmsnorm_bwd_static: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return (int)e;
+  }
+  if (dev < 0 || dev >= kStaticMaxDevices) {
+    static_fail("sb_rmsnorm_bwd_static: device ordinal %d is outside the supported range [0, %d)", dev, kStaticMaxDevices);
+    return (int)cudaErrorInvalidDevice;
+  }
+  float* p = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    void* sym = nullptr;
+    e = cudaGetSymbolAddress(&sym, g_rmsnorm_bwd_static_scratch);
+    if (e != cudaSuccess || sym == nullptr) {
+      static_fail("sb_rmsnorm_bwd_static: cudaGetSymbolAddress failed on device %d: %s", dev, cudaGetErrorString(e));
+      return e != cudaSuccess ? (int)e : (int)cudaErrorInvalidSymbol;
+    }
+    p = static_cast<float*>(sym);
+    g_static_scratch_addr[dev].store(p, std::memory_order_release);  // a concurrent first call stores the same value
+  }
+  *out = p;
+  return 0;
+}
+}  // namespace
+
+extern "C" int sb_rmsnorm_bwd_static_setup(void) {
+  float* p = nullptr;
+  return static_scratch_for_current_device(&p);
+}
+
+extern "C" int sb_rmsnorm_bwd_static(const void* dy, const void* h, const void* w, const float* rstd, const void* dres_in,
+                                     void* dh, float* dw, int T, int H, int accumulate_dw, cudaStream_t s) {
+  if (T < 0 || H <= 0 || H % 8 != 0 || H > SB_RMSNORM_STATIC_MAX_H) {
+    static_fail("sb_rmsnorm_bwd_static: T=%d H=%d rejected; H must be a positive multiple of 8 and at most %d "
+                "(scratch is %d x %d floats)", T, H, SB_RMSNORM_STATIC_MAX_H, SB_RMSNORM_STATIC_MAX_CTAS,
+                SB_RMSNORM_STATIC_MAX_H);
+    return (int)cudaErrorInvalidValue;
+  }
+  if (T == 0) return 0;
+  if (dy == nullptr || h == nullptr || w == nullptr || rstd == nullptr || dh == nullptr || dw == nullptr) {
+    static_fail("sb_rmsnorm_bwd_static: null pointer among dy/h/w/rstd/dh/dw");
+    return (int)cudaErrorInvalidValue;
+  }
+  float* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  const int num_ctas = T < SB_RMSNORM_STATIC_MAX_CTAS ? T : SB_RMSNORM_STATIC_MAX_CTAS;
+  // Rows of the scratch are packed with pitch H (not MAX_H), exactly like the caller-supplied buffer of sb_rmsnorm_bwd.
+  sb::rmsnorm_bwd_kernel<<<num_ctas, sb::NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
+                                                               (const bf16*)dres_in, (bf16*)dh, scratch, T, H);
+  sb::rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, num_ctas, H, accumulate_dw);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) static_fail("sb_rmsnorm_bwd_static: launch failed: %s", cudaGetErrorString(e));
+  return (int)e;
+}
