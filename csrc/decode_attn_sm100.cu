@@ -1,0 +1,409 @@
+// Paged decode attention on the 5th-gen tensor cores (sm_100a): one query token per request, GQA.
+//
+// Decode attention is bound by streaming the KV cache once, so the kernel is a TMA pipeline with the two
+// small contractions on tcgen05 so that the CUDA cores only do the softmax:
+//
+//   per 128-token tile of one (request, kv head, split):
+//     TMA      K tile [128 tok, D] and V tile [128 tok, D] from the paged cache (one box per page) -> smem, 128B swizzle
+//     tcgen05  S^T[128 tok, 16] = K · Q^T          (A = K tile K-major, B = the G<=16 query heads of this kv head)
+//     threads  one token per thread: tcgen05.ld its 16 scores, tile max / exp / sum per head, P -> smem (bf16)
+//     tcgen05  O[128(G used), D] = P · V            (A = P K-major [head, token], B = V tile MN-major)
+//     warp 0   tcgen05.ld rows 0..G-1 of O, online-softmax merge into the running (m, l, acc) kept in lane g
+//
+//   S^T is double-buffered in TMEM so K·Q^T of tile i+1 overlaps the softmax of tile i; two smem stages keep the
+//   next tile's K/V in flight. Grid = (B, Hkv, splits); with splits > 1 partial (o, m, l) go to a workspace and a
+//   small combine kernel finishes. Every mbarrier wait is bounded (2 s): on expiry the CTA records a status word,
+//   skips its output, lets in-flight copies land, frees its TMEM and returns.
+//
+// Cache layout: k_cache / v_cache = [num_slots, Hkv, D] bf16, slot = page * page_size + offset;
+// block_table[b, i] = page id of the i-th page of request b. page_size must be 16, 32, 64 or 128.
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int DA_TILE = 128;  // tokens per tile = TMEM lanes = threads
+constexpr int DA_THREADS = 128;
+constexpr int DA_STAGES = 2;
+constexpr int DA_MAXG = 16;  // N of the S^T MMA
+
+template <int D>
+struct DecSmem {
+  static constexpr int NCH = D / 64;                      // 128-byte chunks of the head dim
+  static constexpr int KV_TILE = DA_TILE * 128 * NCH;     // bytes of one K (or V) tile
+  static constexpr int STAGE = 2 * KV_TILE;               // K then V
+  static constexpr int P_BYTES = 2 * 128 * 128;           // [128 rows, 2 chunks of 64 tokens] bf16, K-major
+  static constexpr int Q_BYTES = DA_MAXG * 128 * NCH;     // [16 heads, D] bf16, K-major
+  static constexpr int BAR_BYTES = 128;
+  static constexpr int TOTAL = DA_STAGES * STAGE + P_BYTES + Q_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int TMEM_COLS = D == 64 ? 128 : 256;   // S0 @0, S1 @32, O @64..64+D
+};
+
+template <int D, int G>
+__global__ void __launch_bounds__(DA_THREADS)
+decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __nv_bfloat16* __restrict__ q, const int* __restrict__ block_table,
+                   const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int Hq, int Hkv, int page_size, int page_shift, int max_pages,
+                   int q_stride, int out_stride, int splits, float scale, int* status) {
+  using S = DecSmem<D>;
+  constexpr int NCH = S::NCH;
+  static_assert(G <= DA_MAXG, "at most 16 query heads per kv head");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sKV = smem;
+  uint8_t* sP = smem + DA_STAGES * S::STAGE;
+  uint8_t* sQ = sP + S::P_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(sQ + S::Q_BYTES);
+  uint64_t* bar_s = full + DA_STAGES;
+  uint64_t* bar_o = bar_s + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __shared__ float red_m[2][4][DA_MAXG], red_l[2][4][DA_MAXG];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
+  const int len = seq_lens[b];
+  const int per_split = ((len + splits - 1) / splits + DA_TILE - 1) & ~(DA_TILE - 1);
+  const int t_begin = sp * per_split;
+  const int t_end = min(len, t_begin + per_split);
+  const int ntiles = t_end > t_begin ? (t_end - t_begin + DA_TILE - 1) / DA_TILE : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < DA_STAGES; ++s) mbar_init(&full[s], 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
+    mbar_init(bar_o, 1);
+    *cta_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, S::TMEM_COLS);
+    tmem_relinquish();
+  }
+  // P starts as zeros: rows >= G stay zero for the whole kernel, rows < G are rewritten every tile.
+  for (int i = tid; i < S::P_BYTES / 16; i += DA_THREADS) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
+  // Q rows (unscaled bf16; the scale is applied to the fp32 scores) in the canonical K-major 128B-swizzle layout:
+  // 16-byte chunk j of row r sits at chunk position j ^ (r % 8).
+  for (int i = tid; i < DA_MAXG * NCH * 8; i += DA_THREADS) {
+    const int r = i / (NCH * 8), c = (i / 8) % NCH, j = i % 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < G)
+      v = *reinterpret_cast<const uint4*>(q + static_cast<size_t>(b) * q_stride + static_cast<size_t>(kvh * G + r) * D +
+                                          c * 64 + j * 8);
+    *reinterpret_cast<uint4*>(sQ + c * (DA_MAXG * 128) + r * 128 + ((j ^ (r & 7)) << 4)) = v;
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_o = tmem_base + 64;
+
+  const int* bt_row = block_table + static_cast<size_t>(b) * max_pages;
+  // thread 0 only: start the copies of tile i (one box per page and per 64-wide chunk of the head dim)
+  auto issue_tile = [&](int i) {
+    const int s = i % DA_STAGES;
+    const int t0 = t_begin + i * DA_TILE;
+    const int valid = min(DA_TILE, t_end - t0);
+    const int npages = (valid + page_size - 1) >> page_shift;
+    uint8_t* kd = sKV + s * S::STAGE;
+    uint8_t* vd = kd + S::KV_TILE;
+    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128 * NCH * 2));
+    const int* bt = bt_row + (t0 >> page_shift);
+    for (int p = 0; p < npages; ++p) {
+      const int slot0 = bt[p] * page_size;
+#pragma unroll
+      for (int c = 0; c < NCH; ++c) {
+        tma_load_3d(kd + c * (DA_TILE * 128) + p * page_size * 128, &tmK, &full[s], c * 64, kvh, slot0);
+        tma_load_3d(vd + c * (DA_TILE * 128) + p * page_size * 128, &tmV, &full[s], c * 64, kvh, slot0);
+      }
+    }
+  };
+  // thread 0 only: S^T[128 tok, 16] = K_tile · Q^T into S buffer (i & 1)
+  auto issue_s_mma = [&](int i) {
+    constexpr uint32_t idesc = make_idesc(DA_TILE, DA_MAXG, 1, 1, 0, 0);
+    const uint32_t k_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE);
+    const uint32_t q_addr = smem_u32(sQ);
+#pragma unroll
+    for (int c = 0; c < NCH; ++c)
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma_f16(tmem_base + (i & 1) * 32, make_smem_desc(k_addr + c * (DA_TILE * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
+                 make_smem_desc(q_addr + c * (DA_MAXG * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc,
+                 (c | k) != 0 ? 1u : 0u);
+    umma_commit(&bar_s[i & 1]);
+  };
+  // thread 0 only: O[128, D] = P · V_tile (fresh accumulator every tile; the merge happens in registers)
+  auto issue_o_mma = [&](int i) {
+    constexpr uint32_t idesc = make_idesc(128, D, 1, 1, 0, 1);
+    const uint32_t p_addr = smem_u32(sP);
+    const uint32_t v_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE + S::KV_TILE);
+#pragma unroll
+    for (int kc = 0; kc < 2; ++kc)
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        umma_f16(tmem_o, make_smem_desc(p_addr + kc * (128 * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
+                 make_smem_desc(v_addr + (kc * 4 + k) * 2048, DA_TILE * 128, 1024, UMMA_SWIZZLE_128B), idesc,
+                 (kc | k) != 0 ? 1u : 0u);
+    umma_commit(bar_o);
+  };
+
+  bool ok = true;
+  if (tid == 0 && ntiles > 0) {
+    issue_tile(0);
+    if (ntiles > 1) issue_tile(1);
+    ok = mbar_wait(&full[0], 0, cta_abort, status, ERR_WAIT_FULL);
+    if (ok) {
+      tc_fence_after();
+      issue_s_mma(0);
+    }
+  }
+
+  // running softmax state of head g lives in lane g of warp 0
+  float m_run = -INFINITY, l_run = 0.f;
+  float acc[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+
+  for (int i = 0; i < ntiles; ++i) {
+    const int s = i % DA_STAGES, par = i & 1;
+    const int t0 = t_begin + i * DA_TILE;
+    const int valid = min(DA_TILE, t_end - t0);
+    // ---- scores of this thread's token (TMEM lane = tid) for the G heads
+    if (ok) ok = mbar_wait(&bar_s[par], (i >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
+    ok = __all_sync(0xffffffffu, ok);  // the TMEM load below is warp-collective: take one decision per warp
+    tc_fence_after();
+    float sc[G];
+    {
+      uint32_t r[32];
+      if (ok) {
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + par * 32, r);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int g = 0; g < 32; ++g) r[g] = 0;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) sc[g] = (tid < valid) ? __uint_as_float(r[g]) * scale : -INFINITY;
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float wm = warp_max(sc[g]);
+      if (lane == 0) red_m[par][warp][g] = wm;
+    }
+    // P of the previous tile must have been consumed before it is overwritten
+    if (ok && i > 0) ok = mbar_wait(bar_o, (i - 1) & 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY);
+    ok = __syncthreads_and(ok);  // (A) tile maxima visible; everyone agrees whether to go on
+    if (!ok) break;
+
+    // ---- p = exp(s - tile max), rounded to bf16 exactly as the tensor core will see it
+    const int kc = tid >> 6, col = tid & 63;
+    uint8_t* p_col = sP + kc * (128 * 128) + (col & 7) * 2;
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float mt = fmaxf(fmaxf(red_m[par][0][g], red_m[par][1][g]), fmaxf(red_m[par][2][g], red_m[par][3][g]));
+      const float p = (tid < valid) ? __expf(sc[g] - mt) : 0.f;
+      const __nv_bfloat16 pb = __float2bfloat16(p);
+      const float ps = warp_sum(__bfloat162float(pb));
+      if (lane == 0) red_l[par][warp][g] = ps;
+      *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = pb;
+    }
+    if (valid < DA_TILE) {
+      // Last tile: rows past the end of the sequence hold whatever the cache (or an older tile) left there.
+      // Their p is 0, but 0 x NaN would poison O, so the V rows are cleared. Every thread observes the copy's
+      // barrier first so that its plain stores are ordered after the TMA writes.
+      ok = mbar_wait(&full[s], (i / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL);
+      if (ok && tid >= valid) {
+        uint8_t* vrow = sKV + s * S::STAGE + S::KV_TILE + tid * 128;
+#pragma unroll
+        for (int c = 0; c < NCH; ++c)
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            reinterpret_cast<uint4*>(vrow + c * (DA_TILE * 128))[j] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    fence_proxy_async();  // P (and cleared V rows) -> visible to the tensor core's async proxy
+    tc_fence_before();
+    ok = __syncthreads_and(ok);  // (B)
+    if (!ok) break;
+
+    if (tid == 0) {
+      tc_fence_after();
+      issue_o_mma(i);
+      if (i + 1 < ntiles) {
+        if (mbar_wait(&full[(i + 1) % DA_STAGES], ((i + 1) / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL)) {
+          tc_fence_after();
+          issue_s_mma(i + 1);  // overlaps the merge below and the next tile's softmax
+        } else {
+          ok = false;
+        }
+      }
+    }
+    if (warp == 0) {
+      __syncwarp();
+      const bool okw = __all_sync(0xffffffffu, ok && mbar_wait(bar_o, i & 1, cta_abort, status, ERR_WAIT_TMEM_FULL));
+      tc_fence_after();
+      if (okw) {
+        const int gl = lane < G ? lane : 0;
+        const float mt = fmaxf(fmaxf(red_m[par][0][gl], red_m[par][1][gl]), fmaxf(red_m[par][2][gl], red_m[par][3][gl]));
+        const float lt = red_l[par][0][gl] + red_l[par][1][gl] + red_l[par][2][gl] + red_l[par][3][gl];
+        const float nm = fmaxf(m_run, mt);
+        const float a = (m_run == -INFINITY) ? 0.f : __expf(m_run - nm);
+        const float bcf = __expf(mt - nm);
+        l_run = l_run * a + lt * bcf;
+        m_run = nm;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_o + c * 32, r);  // warp 0 owns TMEM lanes 0..31 = O rows (heads) 0..31
+          tmem_ld_wait();
+#pragma unroll
+          for (int d = 0; d < 32; ++d) acc[c * 32 + d] = acc[c * 32 + d] * a + __uint_as_float(r[d]) * bcf;
+        }
+        tc_fence_before();
+      } else {
+        ok = false;
+      }
+      __syncwarp();
+      // the stage of tile i is free now (its V was read by the MMA that bar_o tracks): refill it
+      if (tid == 0 && okw && i + DA_STAGES < ntiles) issue_tile(i + DA_STAGES);
+    }
+  }
+
+  // ---- output: lane g of warp 0 owns head kvh*G + g
+  const bool all_ok = __syncthreads_and(ok) && (*cta_abort == 0);
+  if (all_ok && warp == 0 && lane < G) {
+    const int h = kvh * G + lane;
+    if (splits == 1) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* o = out + static_cast<size_t>(b) * out_stride + static_cast<size_t>(h) * D;
+#pragma unroll
+      for (int d = 0; d < D; d += 8) {
+        uint4 u;
+        u.x = pack_bf16x2(acc[d] * inv, acc[d + 1] * inv);
+        u.y = pack_bf16x2(acc[d + 2] * inv, acc[d + 3] * inv);
+        u.z = pack_bf16x2(acc[d + 4] * inv, acc[d + 5] * inv);
+        u.w = pack_bf16x2(acc[d + 6] * inv, acc[d + 7] * inv);
+        *reinterpret_cast<uint4*>(o + d) = u;
+      }
+    } else {
+      const size_t base = (static_cast<size_t>(b) * Hq + h) * splits + sp;
+      float4* po = reinterpret_cast<float4*>(part_o + base * D);
+#pragma unroll
+      for (int d = 0; d < D; d += 4) po[d / 4] = make_float4(acc[d], acc[d + 1], acc[d + 2], acc[d + 3]);
+      part_ml[base * 2 + 0] = m_run;
+      part_ml[base * 2 + 1] = l_run;
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*cta_abort) {
+    // give copies that are still in flight a bounded time to land before the shared memory goes away
+    const unsigned long long t_a = globaltimer_ns();
+    while (globaltimer_ns() - t_a < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem_base, S::TMEM_COLS);
+}
+
+// out[b, h, :] = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M) over the splits of one (request, head).
+__global__ void decode_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           __nv_bfloat16* __restrict__ out, int D, int splits, int out_stride, int Hq) {
+  const int bh = blockIdx.x, b = bh / Hq, h = bh % Hq;
+  const float* ml = part_ml + static_cast<size_t>(bh) * splits * 2;
+  float gm = -INFINITY;
+  for (int s = 0; s < splits; ++s) gm = fmaxf(gm, ml[2 * s]);
+  float gl = 0.f;
+  for (int s = 0; s < splits; ++s)
+    if (ml[2 * s] != -INFINITY) gl += ml[2 * s + 1] * __expf(ml[2 * s] - gm);
+  const float inv = gl > 0.f ? 1.f / gl : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.f;
+    for (int s = 0; s < splits; ++s)
+      if (ml[2 * s] != -INFINITY) o += part_o[(static_cast<size_t>(bh) * splits + s) * D + d] * __expf(ml[2 * s] - gm);
+    out[static_cast<size_t>(b) * out_stride + static_cast<size_t>(h) * D + d] = __float2bfloat16(o * inv);
+  }
+}
+
+// [num_slots, Hkv, D] bf16 cache as a 3-D tensor map; box = one page of one head, 64 elements (128 B) wide.
+static CUtensorMap make_cache_tmap(const void* base, int num_slots, int Hkv, int D, int page_size) {
+  CUtensorMap m;
+  cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)Hkv, (cuuint64_t)num_slots};
+  cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)Hkv * D * 2};
+  cuuint32_t box[3] = {64, 1, (cuuint32_t)page_size};
+  cuuint32_t estr[3] = {1, 1, 1};
+  static thread_local bool ctx_bound = false;  // the encoder needs the primary context current on this thread
+  if (!ctx_bound) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ctx_bound = true;
+  }
+  CUresult r = get_encode_tiled()(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    throw std::runtime_error("cuTensorMapEncodeTiled (kv cache) failed: " + std::to_string(int(r)) + " slots=" +
+                             std::to_string(num_slots) + " Hkv=" + std::to_string(Hkv) + " D=" + std::to_string(D));
+  return m;
+}
+
+template <int D, int G>
+static int launch_decode_attn(dim3 grid, cudaStream_t s, const CUtensorMap& tk, const CUtensorMap& tv, const __nv_bfloat16* q,
+                              const int* bt, const int* sl, __nv_bfloat16* out, float* po, float* pml, int Hq, int Hkv,
+                              int page_size, int page_shift, int max_pages, int q_stride, int out_stride, int splits,
+                              float scale, int* status) {
+  auto kern = decode_attn_kernel<D, G>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<D>::TOTAL);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  kern<<<grid, DA_THREADS, DecSmem<D>::TOTAL, s>>>(tk, tv, q, bt, sl, out, po, pml, Hq, Hkv, page_size, page_shift, max_pages,
+                                                  q_stride, out_stride, splits, scale, status);
+  return (int)cudaGetLastError();
+}
+
+}  // namespace sb
+
+// Returns 0, a cudaError_t value, or -1 when the shape is outside what this kernel covers (the caller then uses
+// the CUDA-core kernel sb_paged_decode). part_o / part_ml: workspaces [B, Hq, splits, D] / [B, Hq, splits, 2] fp32,
+// only touched when splits > 1.
+extern "C" int sb_paged_decode_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                  const int* seq_lens, void* out, float* part_o, float* part_ml, int B, int Hq, int Hkv,
+                                  int D, int page_size, int max_pages, int num_slots, int q_stride, int out_stride,
+                                  int splits, float scale, int* status, cudaStream_t s) {
+  using bf16 = __nv_bfloat16;
+  if (B == 0) return 0;
+  if (Hkv <= 0 || Hq % Hkv != 0 || (D != 64 && D != 128)) return -1;
+  const int G = Hq / Hkv;
+  int page_shift = 0;
+  while ((1 << page_shift) < page_size) ++page_shift;
+  if ((1 << page_shift) != page_size || page_size < 16 || page_size > 128) return -1;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride & 7) || (reinterpret_cast<uintptr_t>(out) & 15) || (out_stride & 7) ||
+      (reinterpret_cast<uintptr_t>(k_cache) & 127) || (reinterpret_cast<uintptr_t>(v_cache) & 127))
+    return -1;
+  try {
+    const CUtensorMap tk = sb::make_cache_tmap(k_cache, num_slots, Hkv, D, page_size);
+    const CUtensorMap tv = sb::make_cache_tmap(v_cache, num_slots, Hkv, D, page_size);
+    dim3 grid(B, Hkv, splits);
+    int rc = -1;
+#define SB_DA(DV, GV)                                                                                                  \
+  if (D == DV && G == GV)                                                                                              \
+    rc = sb::launch_decode_attn<DV, GV>(grid, s, tk, tv, (const bf16*)q, block_table, seq_lens, (bf16*)out, part_o, part_ml, \
+                                        Hq, Hkv, page_size, page_shift, max_pages, q_stride, out_stride, splits, scale, status);
+    SB_DA(64, 1) SB_DA(64, 2) SB_DA(64, 4) SB_DA(64, 5) SB_DA(64, 6) SB_DA(64, 7) SB_DA(64, 8) SB_DA(64, 16)
+    SB_DA(128, 1) SB_DA(128, 2) SB_DA(128, 4) SB_DA(128, 5) SB_DA(128, 6) SB_DA(128, 7) SB_DA(128, 8) SB_DA(128, 16)
+#undef SB_DA
+    if (rc != 0) return rc;
+    if (splits > 1)
+      sb::decode_attn_combine_kernel<<<B * Hq, 64, 0, s>>>(part_o, part_ml, (bf16*)out, D, splits, out_stride, Hq);
+    return (int)cudaGetLastError();
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
+    return (int)cudaErrorInvalidValue;
+  }
+}

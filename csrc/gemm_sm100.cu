@@ -36,6 +36,22 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
 };
 
+// Tile order. Tiles are walked in panels of GEMM_PANEL_M row-tiles: within a panel the m index runs fastest, then n.
+// The ~148 tiles in flight at any time then share one A panel (kept in L2 while n sweeps) and a few B column
+// blocks, so A is read from HBM once and B once per panel instead of both being re-fetched every wave.
+constexpr int GEMM_PANEL_M = 32;
+
+template <int BN>
+__device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int per_panel = GEMM_PANEL_M * tiles_n;
+  const int panel = tile / per_panel;
+  const int pm0 = panel * GEMM_PANEL_M;
+  const int pm = min(GEMM_PANEL_M, tiles_m - pm0);
+  const int r = tile - panel * per_panel;
+  m0 = (pm0 + r % pm) * GEMM_BM;
+  n0 = (r / pm) * BN;
+}
+
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -92,8 +108,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % tiles_m) * GEMM_BM;
-        const int n0 = (tile / tiles_m) * BN;
+        int m0, n0;
+        tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
             ok = false;
@@ -174,8 +190,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint8_t* stage_buf = sC + q * 2 * EPI_BUF_BYTES;
     int buf = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * GEMM_BM;
-      const int n0 = (tile / tiles_m) * BN;
+      int m0, n0;
+      tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
       bool ok = mbar_wait(&tfull[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;

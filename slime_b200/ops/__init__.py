@@ -21,10 +21,13 @@ def _cuda(t: torch.Tensor) -> bool:
 
 
 # ------------------------------------------------------------------------ GEMM
-def _pick_bn(N: int) -> int:
-    w256 = -(-N // 256) * 256
-    w128 = -(-N // 128) * 128
-    return 256 if w256 <= w128 else 128
+def _pick_bn(M: int, N: int, sms: int = 148) -> int:
+    """Tile width by a wave model: time ~ waves x tile width / MMA efficiency (a 128-wide tile runs the tensor
+    pipe at ~0.7 of a 256-wide one), waves = ceil(tiles / SMs)."""
+    tiles_m = -(-M // 128)
+    cost128 = -(-(tiles_m * -(-N // 128)) // sms) * 128 / 0.7
+    cost256 = -(-(tiles_m * -(-N // 256)) // sms) * 256
+    return 256 if cost256 <= cost128 else 128
 
 
 def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, accumulate=False, bn=None):
@@ -61,7 +64,7 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, a
     assert lda % 8 == 0 and ldb % 8 == 0, "TMA needs 16-byte row pitches (multiples of 8 bf16)"
     rc = _lib.lib().sb_gemm_bf16(
         P(a), P(b), P(out), P(bias), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), int(out.dtype == torch.float32),
-        int(accumulate), bn or _pick_bn(N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
+        int(accumulate), bn or _pick_bn(M, N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
     )  # fmt: skip
     _lib.check(rc, "sb_gemm_bf16")
     return out
@@ -364,7 +367,7 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True):
 
 
 def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None, out=None, splits=None,
-                           workspace=None):
+                           workspace=None, use_tensor_cores=True):
     """One query token per request over a paged KV cache. q: [B, Hq, D]; caches [slots, Hkv, D]."""
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
@@ -374,12 +377,24 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     if splits is None:
         ctas = B * Hkv
         splits = 1 if ctas >= _lib.sm_count(q.device) else min(16, max(1, (2 * _lib.sm_count(q.device)) // max(ctas, 1)))
+        splits = max(1, min(splits, -(-block_table.shape[1] * page_size // 128)))  # never more splits than 128-token tiles
     if out is None:
         out = torch.empty_like(q)
-    if workspace is None:
+    if workspace is None and splits > 1:
         workspace = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)
-    part_o = workspace[: B * Hq * splits * D]
-    part_ml = workspace[B * Hq * splits * D : B * Hq * splits * (D + 2)]
+    part_o = workspace[: B * Hq * splits * D] if splits > 1 else None
+    part_ml = workspace[B * Hq * splits * D : B * Hq * splits * (D + 2)] if splits > 1 else None
+    if use_tensor_cores:
+        # tcgen05 + TMA kernel; -1 = shape outside its coverage (odd head dim / group size / page size / alignment)
+        rc = _lib.lib().sb_paged_decode_tc(P(q), P(k_cache), P(v_cache), P(block_table), P(seq_lens), P(out), P(part_o), P(part_ml),
+                                           B, Hq, Hkv, D, page_size, block_table.shape[1], k_cache.shape[0], q.stride(0),
+                                           out.stride(0), splits, float(scale), P(_lib.status_word(q.device)), _lib.stream())
+        if rc != -1:
+            _lib.check(rc, "sb_paged_decode_tc")
+            return out
+    if splits == 1:
+        workspace = torch.empty(B * Hq * (D + 2), dtype=torch.float32, device=q.device)
+        part_o, part_ml = workspace[: B * Hq * D], workspace[B * Hq * D :]
     rc = _lib.lib().sb_paged_decode(P(q), P(k_cache), P(v_cache), P(block_table), P(seq_lens), P(out), P(part_o), P(part_ml),
                                     B, Hq, Hkv, D, page_size, block_table.shape[1], q.stride(0), out.stride(0), splits,
                                     float(scale), _lib.stream())

@@ -145,9 +145,17 @@ def bench_decode(a):
     }
     per_layer = ["rmsnorm_add", "gemm_qkv", "rope_qk", "kv_write", "paged_attention", "gemm_o", "rmsnorm_add", "gemm_gate_up",
                  "swiglu", "gemm_down"]  # fmt: skip
+    steps["paged_attention_cuda_cores"] = lambda: ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps,
+                                                                             use_tensor_cores=False)
     t_of = {}
     for name, fn in steps.items():
-        t_of[name] = time_ms(fn, a.iters, reps=a.reps, flush=False)
+        # `reps` launches inside one CUDA graph: device time per launch without the host's launch cost
+        fn()
+        gk = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gk):
+            for _ in range(a.reps):
+                fn()
+        t_of[name] = time_ms(gk.replay, a.iters, flush=False) / a.reps
         _emit(kind="decode_kernel", name=name, batch=B, context=ctx, us=1e3 * t_of[name])
     est = cfg.num_layers * sum(t_of[k] for k in per_layer) + t_of["gemm_lm_head"] + t_of["sample"] + t_of["rmsnorm_add"]
 

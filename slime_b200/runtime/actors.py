@@ -16,6 +16,7 @@ around as references.
 
 from __future__ import annotations
 
+import atexit
 import itertools
 import multiprocessing as mp
 import os
@@ -82,6 +83,13 @@ def wait(refs: list[ObjectRef], num_returns: int = 1, timeout: float | None = No
 # ----------------------------------------------------------------------------- server side
 def _serve(cls, args, kwargs, address, env, ready_path, max_concurrency):
     os.environ.update({k: str(v) for k, v in (env or {}).items()})
+    try:  # die with the parent (actors are not daemonic because they may start actors of their own)
+        import ctypes
+        import signal
+
+        ctypes.CDLL("libc.so.6", use_errno=True).prctl(1, signal.SIGKILL)  # PR_SET_PDEATHSIG
+    except Exception:  # noqa: BLE001
+        pass
     try:
         instance = cls(*args, **kwargs)
         init_error = None
@@ -249,7 +257,7 @@ def spawn_actor(cls, args=(), kwargs=None, *, name=None, env=None, max_concurren
     ctx = mp.get_context("spawn")
     address = os.path.join(_SOCK_DIR, f"slb200-{uuid.uuid4().hex[:12]}.sock")
     ready = address + ".ready"
-    proc = ctx.Process(target=_serve, args=(cls, args, kwargs or {}, address, env, ready, max_concurrency), daemon=True,
+    proc = ctx.Process(target=_serve, args=(cls, args, kwargs or {}, address, env, ready, max_concurrency), daemon=False,
                        name=name or cls.__name__)  # fmt: skip
     proc.start()
     deadline = time.time() + start_timeout
@@ -312,6 +320,9 @@ def shutdown():
         if proc.is_alive():
             proc.kill()
         proc.join(5)
+
+
+atexit.register(shutdown)
 
 
 class Lock:

@@ -34,6 +34,8 @@ class EngineProxy:
     the process boundary as a CUDA IPC mapping (the channel pickles with the multiprocessing reducers torch
     registers), so colocated sync never stages weights through the host."""
 
+    weights = None  # marks a remote engine: the updaters take the bucketed path, not the same-process fused copy
+
     def __init__(self, handle, num_gpus: int = 1, gpu_offset: int = 0, parallel_config: dict | None = None):
         self.handle, self.num_gpus, self.gpu_offset = handle, num_gpus, gpu_offset
         self.parallel_config = parallel_config or {}
@@ -94,7 +96,8 @@ class TrainWorker:
 
         return {"dp_size": mpu.get_data_parallel_world_size(False), "cp_size": mpu.get_context_parallel_world_size(),
                 "tp_size": mpu.get_tensor_model_parallel_world_size(), "pp_size": mpu.get_pipeline_model_parallel_world_size(),
-                "vpp_size": getattr(self.args, "virtual_pipeline_model_parallel_size", None) or 1}  # fmt: skip
+                "vpp_size": getattr(self.args, "virtual_pipeline_model_parallel_size", None) or 1,
+                "microbatch_group_size_per_vp_stage": getattr(self.args, "microbatch_group_size_per_vp_stage", None) or 1}  # fmt: skip
 
     def set_rollout_manager(self, rollout_manager):
         """Fetch the updatable engines and the broadcast lock; rank 0 also tells the manager how the trainer is

@@ -383,10 +383,15 @@ def _model_defaults_from_hf(args) -> None:
     check the ones that were given against it (parity: megatron_utils/arguments.py:97-148)."""
     path = getattr(args, "hf_checkpoint", None)
     cfg_file = os.path.join(path, "config.json") if path else None
-    if not cfg_file or not os.path.exists(cfg_file):
+    if path and path.startswith("preset:"):  # a named architecture with random weights, no directory on disk
+        from slime_b200.models.config import get_preset
+
+        cfg, cfg_file = get_preset(path[len("preset:") :]).to_hf_dict(), path
+    elif not cfg_file or not os.path.exists(cfg_file):
         return
-    with open(cfg_file) as f:
-        cfg = json.load(f)
+    else:
+        with open(cfg_file) as f:
+            cfg = json.load(f)
     cfg = cfg.get("text_config", cfg)
     mapping = {
         "num_layers": "num_hidden_layers", "hidden_size": "hidden_size", "ffn_hidden_size": "intermediate_size",

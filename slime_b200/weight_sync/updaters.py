@@ -134,7 +134,8 @@ class UpdateWeightFromTensor(WeightUpdaterBase):
                     for e in self.engines:
                         e.update_weights(bucket, version=str(self.weight_version), flush_cache=False)
         for e in self.engines:
-            e.weights.version = str(self.weight_version) if hasattr(e, "weights") else None
+            if getattr(e, "weights", None) is not None:  # in-process engine object; remote ones get the version per bucket
+                e.weights.version = str(self.weight_version)
         if torch.cuda.is_available():
             torch.cuda.current_stream().synchronize()  # consumers' copies retired before generation resumes
         self._resume()
@@ -145,7 +146,7 @@ class UpdateWeightFromTensor(WeightUpdaterBase):
             return False
         e = self.engines[0]
         return (
-            hasattr(e, "weights") and e.weights.tp == mpu.get_tensor_model_parallel_world_size()
+            getattr(e, "weights", None) is not None and e.weights.tp == mpu.get_tensor_model_parallel_world_size()
             and mpu.get_pipeline_model_parallel_world_size() == 1 and self.model.cfg.num_experts is None
         )  # fmt: skip
 
