@@ -107,6 +107,12 @@ class TrainActor:
                 self.weights_backuper.backup("actor")
         if getattr(args, "offload_train", False) and getattr(args, "sleep_after_init", False):
             self.sleep()
+        self.prof = None
+        if getattr(args, "use_pytorch_profiler", False) or getattr(args, "record_memory_history", False):
+            from slime_b200.observability.profile_utils import TrainProfiler
+
+            self.prof = TrainProfiler(args)
+            self.prof.on_init_end()
         return args.start_rollout_id
 
     def load_other_checkpoint(self, tag: str, path: str):
@@ -191,9 +197,10 @@ class TrainActor:
             self.wake_up()
         with timer("data_preprocess"):
             data = self._get_rollout_data(rollout_data_ref)
-        if self.role == "critic":
-            return self.train_critic(rollout_id, data)
-        return self.train_actor(rollout_id, data, external_data)
+        out = self.train_critic(rollout_id, data) if self.role == "critic" else self.train_actor(rollout_id, data, external_data)
+        if getattr(self, "prof", None) is not None:
+            self.prof.step(rollout_id)
+        return out
 
     def compute_log_prob(self, data_iterator, num_microbatches, store_prefix=""):
         with timer(f"{store_prefix}log_probs"):

@@ -353,7 +353,12 @@ def train(rollout_id, model: TrainModel, data_iterator, num_microbatches: list[i
     for it in data_iterator:
         it.reset()
     history = []
-    for step_id, (nmb, gbs) in enumerate(zip(num_microbatches, global_batch_sizes)):
+    steps = enumerate(zip(num_microbatches, global_batch_sizes))
+    if getattr(args, "use_pytorch_profiler", False):  # --profile-target train_actor: one profiler step per optimizer step
+        from slime_b200.observability.profile_utils import _profile_simple_loop
+
+        steps = _profile_simple_loop(steps, args, "train_actor")
+    for step_id, (nmb, gbs) in steps:
         metrics, grad_norm = train_one_step(args, rollout_id, step_id, data_iterator, model, nmb, gbs)
         history.append((metrics, grad_norm))
     return history
