@@ -6,7 +6,7 @@
 //   per 128-token tile of one (request, kv head, split):
 //     TMA      K tile [128 tok, D] and V tile [128 tok, D] from the paged cache (one box per page) -> smem, 128B swizzle
 //     tcgen05  S^T[128 tok, 16] = K · Q^T          (A = K tile K-major, B = the G<=16 query heads of this kv head)
-//     threads  one token per thread: tcgen05.ld its 16 scores, tile max / exp / sum per head, P -> smem (bf16)
+//     threads  one token per thread: tcgen05.ld its 16 scores, tile max per head, exp, P -> smem (bf16)
 //     tcgen05  O[128(G used), D] = P · V            (A = P K-major [head, token], B = V tile MN-major)
 //     warp 0   tcgen05.ld rows 0..G-1 of O, online-softmax merge into the running (m, l, acc) kept in lane g
 //
@@ -58,7 +58,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* bar_o = bar_s + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ float red_m[2][4][DA_MAXG], red_l[2][4][DA_MAXG];
+  __shared__ float red_m[2][4][DA_MAXG], red_l[4][DA_MAXG];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
@@ -102,7 +102,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const uint32_t tmem_o = tmem_base + 64;
 
   const int* bt_row = block_table + static_cast<size_t>(b) * max_pages;
-  // thread 0 only: start the copies of tile i (one box per page and per 64-wide chunk of the head dim)
+  // warp 0, all lanes: start the copies of tile i. Lane p fetches the block-table entry of page p and issues that
+  // page's boxes (one per 64-wide chunk of the head dim, for K and for V), so the table reads overlap.
   auto issue_tile = [&](int i) {
     const int s = i % DA_STAGES;
     const int t0 = t_begin + i * DA_TILE;
@@ -110,16 +111,17 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const int npages = (valid + page_size - 1) >> page_shift;
     uint8_t* kd = sKV + s * S::STAGE;
     uint8_t* vd = kd + S::KV_TILE;
-    mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128 * NCH * 2));
-    const int* bt = bt_row + (t0 >> page_shift);
-    for (int p = 0; p < npages; ++p) {
-      const int slot0 = bt[p] * page_size;
+    if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128 * NCH * 2));
+    __syncwarp();
+    if (lane < npages) {
+      const int slot0 = bt_row[(t0 >> page_shift) + lane] * page_size;
 #pragma unroll
       for (int c = 0; c < NCH; ++c) {
-        tma_load_3d(kd + c * (DA_TILE * 128) + p * page_size * 128, &tmK, &full[s], c * 64, kvh, slot0);
-        tma_load_3d(vd + c * (DA_TILE * 128) + p * page_size * 128, &tmV, &full[s], c * 64, kvh, slot0);
+        tma_load_3d(kd + c * (DA_TILE * 128) + lane * page_size * 128, &tmK, &full[s], c * 64, kvh, slot0);
+        tma_load_3d(vd + c * (DA_TILE * 128) + lane * page_size * 128, &tmV, &full[s], c * 64, kvh, slot0);
       }
     }
+    __syncwarp();
   };
   // thread 0 only: S^T[128 tok, 16] = K_tile · Q^T into S buffer (i & 1)
   auto issue_s_mma = [&](int i) {
@@ -151,18 +153,29 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   };
 
   bool ok = true;
-  if (tid == 0 && ntiles > 0) {
+  if (warp == 0 && ntiles > 0) {
     issue_tile(0);
     if (ntiles > 1) issue_tile(1);
-    ok = mbar_wait(&full[0], 0, cta_abort, status, ERR_WAIT_FULL);
-    if (ok) {
-      tc_fence_after();
-      issue_s_mma(0);
+    if (lane == 0) {
+      ok = mbar_wait(&full[0], 0, cta_abort, status, ERR_WAIT_FULL);
+      if (ok) {
+        tc_fence_after();
+        issue_s_mma(0);
+      }
     }
+    __syncwarp();
   }
 
-  // running softmax state of head g lives in lane g of warp 0
-  float m_run = -INFINITY, l_run = 0.f;
+  // Running softmax state. The output accumulator of head g lives in lane g of warp 0. The denominator is kept per
+  // thread (each thread sums the p of its own tokens, rescaled like the accumulator) and reduced once at the end,
+  // which takes the per-tile sum reduction off the critical path.
+  float m_run = -INFINITY;
+  float m_thr[G], l_thr[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m_thr[g] = -INFINITY;
+    l_thr[g] = 0.f;
+  }
   float acc[D];
 #pragma unroll
   for (int d = 0; d < D; ++d) acc[d] = 0.f;
@@ -206,8 +219,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const float mt = fmaxf(fmaxf(red_m[par][0][g], red_m[par][1][g]), fmaxf(red_m[par][2][g], red_m[par][3][g]));
       const float p = (tid < valid) ? __expf(sc[g] - mt) : 0.f;
       const __nv_bfloat16 pb = __float2bfloat16(p);
-      const float ps = warp_sum(__bfloat162float(pb));
-      if (lane == 0) red_l[par][warp][g] = ps;
+      const float nm = fmaxf(m_thr[g], mt);  // the same for every thread of the CTA
+      const float keep = (m_thr[g] == -INFINITY) ? 0.f : __expf(m_thr[g] - nm);
+      l_thr[g] = l_thr[g] * keep + __bfloat162float(pb) * __expf(mt - nm);
+      m_thr[g] = nm;
       *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = pb;
     }
     if (valid < DA_TILE) {
@@ -248,11 +263,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if (okw) {
         const int gl = lane < G ? lane : 0;
         const float mt = fmaxf(fmaxf(red_m[par][0][gl], red_m[par][1][gl]), fmaxf(red_m[par][2][gl], red_m[par][3][gl]));
-        const float lt = red_l[par][0][gl] + red_l[par][1][gl] + red_l[par][2][gl] + red_l[par][3][gl];
         const float nm = fmaxf(m_run, mt);
         const float a = (m_run == -INFINITY) ? 0.f : __expf(m_run - nm);
         const float bcf = __expf(mt - nm);
-        l_run = l_run * a + lt * bcf;
         m_run = nm;
 #pragma unroll
         for (int c = 0; c < D / 32; ++c) {
@@ -268,12 +281,20 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
       __syncwarp();
       // the stage of tile i is free now (its V was read by the MMA that bar_o tracks): refill it
-      if (tid == 0 && okw && i + DA_STAGES < ntiles) issue_tile(i + DA_STAGES);
+      if (okw && i + DA_STAGES < ntiles) issue_tile(i + DA_STAGES);
     }
   }
 
+  // ---- denominators: one block reduction per head (all l_thr[g] refer to the same final maximum)
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const float ws = warp_sum(l_thr[g]);
+    if (lane == 0) red_l[warp][g] = ws;
+  }
   // ---- output: lane g of warp 0 owns head kvh*G + g
   const bool all_ok = __syncthreads_and(ok) && (*cta_abort == 0);
+  const int g_out = lane < G ? lane : 0;
+  const float l_run = red_l[0][g_out] + red_l[1][g_out] + red_l[2][g_out] + red_l[3][g_out];
   if (all_ok && warp == 0 && lane < G) {
     const int h = kvh * G + lane;
     if (splits == 1) {

@@ -29,10 +29,16 @@ __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   *reinterpret_cast<uint4*>(p) = u;
 }
 
+__device__ __forceinline__ void load8(const float* p, float (&f)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
 // y = rmsnorm(x (+ res)) * w ; optionally res_out = x + res (bf16) ; rstd[T] saved for backward.
-// H % 8 == 0, H <= 8192. grid = T rows.
+// H % 8 == 0, H <= 8192. grid = T rows. XT = bf16, or float when x is the fp32 sum left by a split-K projection.
+template <typename XT>
 __global__ void __launch_bounds__(NORM_THREADS)
-rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+rmsnorm_fwd_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H, float eps) {
   __shared__ float scratch[32];
@@ -160,7 +166,8 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, float* 
 // `sign` = +1 forward rotation, -1 inverse rotation (backward of RoPE).
 template <int D>
 __global__ void __launch_bounds__(128)
-rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, const int* __restrict__ pos,
+rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* out /* may alias x: a warp reads its head fully before writing */,
+            const int* __restrict__ pos,
             const float* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ nw, float* __restrict__ rstd_out,
             int T, int nheads, int head0, int in_stride, int out_stride, float eps, float sign) {
   constexpr int PER = D / 64;  // each lane handles PER pairs (i, i + D/2) ... D/2 / 32 lanes
@@ -285,8 +292,18 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               int T, int H, float eps, cudaStream_t s) {
   if (T == 0) return 0;
   if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
-  sb::rmsnorm_fwd_kernel<<<T, sb::NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
-                                                        (bf16*)res_out, rstd, H, eps);
+  sb::rmsnorm_fwd_kernel<bf16><<<T, sb::NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                              (bf16*)res_out, rstd, H, eps);
+  return (int)cudaGetLastError();
+}
+
+// Same, with x in fp32 (res, w, y, res_out stay bf16).
+extern "C" int sb_rmsnorm_fwd_f32x(const float* x, const void* res, const void* w, void* y, void* res_out, float* rstd,
+                                   int T, int H, float eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
+  sb::rmsnorm_fwd_kernel<float><<<T, sb::NORM_THREADS, 0, s>>>(x, (const bf16*)res, (const bf16*)w, (bf16*)y,
+                                                               (bf16*)res_out, rstd, H, eps);
   return (int)cudaGetLastError();
 }
 

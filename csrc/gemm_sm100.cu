@@ -76,6 +76,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int tiles_n = (N + BN - 1) / BN;
   const int num_tiles = tiles_m * tiles_n;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  // Split-K: `accumulate` carries the number of K slices in bits 8.. (1 = no split). A work item is (tile, slice); the
+  // slices of a tile are summed by the epilogue's TMA reduce-add, so the caller passes a zeroed C or asks to accumulate.
+  const int splitk = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
+  const bool add_out = (accumulate & 1) != 0 || splitk > 1;
+  const int kb_per = (num_kb + splitk - 1) / splitk;
+  const int num_items = num_tiles * splitk;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -107,10 +113,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const int tile = item / splitk, ks = item - tile * splitk;
         int m0, n0;
         tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int kb_end = min(num_kb, (ks + 1) * kb_per);
+        for (int kb = ks * kb_per; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
             ok = false;
             break;
@@ -146,11 +154,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         if (!mbar_wait(&tempty[acc], acc_phase ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const int ks = item % splitk;
+        const int kb0 = ks * kb_per, kb_end = min(num_kb, (ks + 1) * kb_per);
+        for (int kb = kb0; kb < kb_end; ++kb) {
           if (!mbar_wait(&full[stage], phase, cta_abort, status, ERR_WAIT_FULL)) {
             ok = false;
             break;
@@ -167,7 +177,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                                      : make_smem_desc(a_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B);
             const uint64_t db = B_MN ? make_smem_desc(b_addr + k * 2048, 8192, 1024, UMMA_SWIZZLE_128B)
                                      : make_smem_desc(b_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B);
-            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);  // frees the smem slot once these MMAs retire
           if (++stage == STAGES) {
@@ -189,7 +199,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t acc_phase = 0;
     uint8_t* stage_buf = sC + q * 2 * EPI_BUF_BYTES;
     int buf = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+    const __nv_bfloat16* const bias_all = bias;
+    for (int item = blockIdx.x; item < num_items; item += gridDim.x) {
+      const int tile = item / splitk;
+      const __nv_bfloat16* bias = (item - tile * splitk) == 0 ? bias_all : nullptr;  // one slice adds the bias
       int m0, n0;
       tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
       bool ok = mbar_wait(&tfull[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
@@ -259,7 +272,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async();  // generic-proxy writes -> visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
-            if (accumulate)
+            if (add_out)
               tma_reduce_add_2d(&tmC, dst, col0, row0);
             else
               tma_store_2d(&tmC, dst, col0, row0);
@@ -281,7 +294,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int i = 0; i < 32 && col0 + i < N; ++i) {
                 float v = __uint_as_float(r[i]);
                 if (bias != nullptr) v += __bfloat162float(bias[col0 + i]);
-                crow[i] = accumulate ? crow[i] + v : v;
+                crow[i] = add_out ? crow[i] + v : v;
               }
             } else {
               __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
@@ -351,7 +364,8 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
     }
     configured = true;
   }
-  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  const int splitk = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
+  const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
   const int grid = tiles < num_sms ? tiles : num_sms;
   kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmC, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
                                                  ldc, accumulate, status);
@@ -387,13 +401,26 @@ static cudaError_t dispatch_layout(bool a_mn, bool b_mn, bool out_f32, const voi
 //   b_mn = 0: B is row-major [N, K] (pitch ldb);  b_mn = 1: B is stored [K, N] (pitch ldb)
 // Requirements: A/B base pointers 16-byte aligned, lda/ldb multiples of 8 elements.
 // `status` is a device int that receives a non-zero code if a bounded wait expired.
-extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
-                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* status,
-                            int num_sms, cudaStream_t stream) {
+// `splitk` > 1 cuts K into that many slices whose partial products are summed into C by TMA reduce-add: C must then be
+// fp32, 16-byte aligned, and either zeroed by the caller or meant to be accumulated into (accumulate = 1).
+extern "C" int sb_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                                   int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int splitk,
+                                   int* status, int num_sms, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   const size_t c_elem = out_f32 ? 4 : 2;
   const bool tma_epi = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * c_elem) % 16 == 0 &&
                        !(accumulate && !out_f32);
+  const int num_kb = (K + sb::GEMM_BK - 1) / sb::GEMM_BK;
+  if (splitk > num_kb) splitk = num_kb;
+  if (splitk > 1) {
+    if (!tma_epi || !out_f32) {
+      sb::set_last_error("sb_gemm_bf16_splitk: split-K needs an fp32 C with a 16-byte aligned base and pitch");
+      return (int)cudaErrorInvalidValue;
+    }
+    const int kb_per = (num_kb + splitk - 1) / splitk;
+    splitk = (num_kb + kb_per - 1) / kb_per;  // no empty slice
+  }
+  accumulate = (accumulate ? 1 : 0) | ((splitk > 1 ? splitk : 0) << 8);
   try {
     if (bn == 256) {
       if (tma_epi)
@@ -414,3 +441,10 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
 }
 
 extern "C" const char* sb_last_error() { return sb::last_error_buf(); }
+
+extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
+                            int ldb, int ldc, int a_mn, int b_mn, int out_f32, int accumulate, int bn, int* status,
+                            int num_sms, cudaStream_t stream) {
+  return sb_gemm_bf16_splitk(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, bn, 1, status, num_sms,
+                             stream);
+}

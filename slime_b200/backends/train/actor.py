@@ -180,9 +180,8 @@ class TrainActor:
         data["tokens"] = [t.to(dev, torch.long, non_blocking=True) for t in data["tokens"]]
         data["loss_masks"] = [t.to(dev, torch.int, non_blocking=True) for t in data["loss_masks"]]
         if "rollout_mask_sums" in data:
-            data["rollout_mask_sums"] = [
-                torch.as_tensor(x, dtype=torch.float32).to(dev, non_blocking=True) for x in data["rollout_mask_sums"]
-            ]
+            sums = torch.as_tensor([float(x) for x in data["rollout_mask_sums"]], dtype=torch.float32).to(dev, non_blocking=True)
+            data["rollout_mask_sums"] = list(sums.unbind(0))  # one copy for the batch, per-sample views
         for key in ("rollout_log_probs", "teacher_log_probs"):
             if key in data:
                 data[key] = [

@@ -89,21 +89,35 @@ def get_sum_of_sample_mean(
     (per-rollout token-weighted mean). ``calculate_per_token_loss``: plain masked sum.
     CP-safe: numerators are local, denominators global.
     """
-    if sample_denoms is None:
-        sample_denoms = [m.sum() for m in loss_masks]
     masks, lens = local_loss_masks(total_lengths, response_lengths, loss_masks)
+    n = len(lens)
+    if n == 0:
+        return lambda x: x.new_zeros(())
+    # One concatenated mask and one segment-id vector for the whole micro-batch: the reduction is a masked
+    # multiply, one index_add over samples and one divide, instead of a few kernels per sample.
+    dev = masks[0].device
+    mask_cat = torch.cat([m.reshape(-1) for m in masks]).to(torch.float32)
+    seg = torch.repeat_interleave(torch.arange(n, device=dev), torch.as_tensor(lens, device=dev), output_size=sum(lens))
+    if calculate_per_token_loss:
+        denoms = None
+    elif sample_denoms is None:
+        if mpu.get_context_parallel_world_size() == 1:
+            denoms = torch.zeros(n, dtype=torch.float32, device=dev).index_add_(0, seg, mask_cat)
+        else:  # denominators are global (whole-sample) mask totals, numerators local to this CP rank
+            denoms = torch.stack([m.sum() for m in loss_masks]).to(torch.float32)
+    elif torch.is_tensor(sample_denoms):
+        denoms = sample_denoms.to(torch.float32).reshape(-1)
+    else:
+        denoms = torch.stack([torch.as_tensor(d, dtype=torch.float32, device=dev).reshape(()) for d in sample_denoms])
+    if denoms is not None:
+        denoms = torch.clamp_min(denoms, 1)
 
     def per_sample(x: torch.Tensor) -> torch.Tensor:
-        total = x.new_zeros(())
-        for piece, m, d in zip(x.split(lens, dim=0), masks, sample_denoms):
-            total = total + (piece * m).sum() / torch.clamp_min(d, 1)
-        return total
+        sums = torch.zeros(n, dtype=x.dtype, device=x.device).index_add(0, seg, x * mask_cat.to(x.dtype))
+        return (sums / denoms.to(x.dtype)).sum()
 
     def per_token(x: torch.Tensor) -> torch.Tensor:
-        total = x.new_zeros(())
-        for piece, m in zip(x.split(lens, dim=0), masks):
-            total = total + (piece * m).sum()
-        return total
+        return (x * mask_cat.to(x.dtype)).sum()
 
     return per_token if calculate_per_token_loss else per_sample
 

@@ -214,11 +214,14 @@ def compute_advantages_and_returns(args: Namespace, rollout_data: RolloutBatch) 
     if not mpu.is_pipeline_last_stage():
         return
 
+    # computed on the concatenated batch and handed out as per-sample views (a few kernels, not a few per sample)
     if args.kl_coef == 0 or not log_probs:
         xs = log_probs or rollout_lp or values
-        kl = [torch.zeros_like(x, dtype=torch.float32) for x in xs]
+        lens = [x.numel() for x in xs]
+        kl = list(torch.split(torch.zeros(sum(lens), dtype=torch.float32, device=xs[0].device), lens)) if xs else []
     else:
-        kl = [compute_approx_kl(lp, r, kl_loss_type=args.kl_loss_type) for lp, r in zip(log_probs, ref)]
+        lens = [x.numel() for x in log_probs]
+        kl = list(torch.split(compute_approx_kl(torch.cat(log_probs), torch.cat(ref), kl_loss_type=args.kl_loss_type), lens))
     rollout_data["kl"] = kl
     dev = kl[0].device if kl else "cpu"
 

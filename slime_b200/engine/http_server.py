@@ -233,8 +233,9 @@ class EngineServer:
         from slime_b200.weight_sync.local_checkpoint import pull_weights
 
         loop = asyncio.get_running_loop()
+        base = body.get("base_dir") or getattr(self.engine.args, "model_path", None)  # version 0 = what the engine booted from
         version_dir = await loop.run_in_executor(None, pull_weights, body["local_checkpoint_dir"], body["source_dir"],
-                                                 int(body["target_version"]), body.get("base_dir"))  # fmt: skip
+                                                 int(body["target_version"]), base)  # fmt: skip
         return self._ok(path=version_dir)
 
     async def _init_group(self, request):

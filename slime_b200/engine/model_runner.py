@@ -160,6 +160,10 @@ class ModelRunner:
         self.max_pages_per_req = -(-max_context // kv.page_size)
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         self.tp_group = tp_group
+        # Row-parallel projections (attention output, MLP down) leave their result in fp32 when no cross-rank sum
+        # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
+        # into K slices that the epilogue sums with TMA reduce-add.
+        self._proj_dtype = torch.float32 if (self.device.type == "cuda" and weights.tp == 1) else None
         self.rope = ops.rope_cos_sin(max_context + 1, cfg.head_dim, cfg.rotary_base, device=self.device,
                                      scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
@@ -181,7 +185,7 @@ class ModelRunner:
     def _mlp(self, L, x):
         if "gate_up" in L:
             act = ops.swiglu(ops.gemm(x, L["gate_up"]))
-            return self._tp_reduce(ops.gemm(act, L["down"]))
+            return self._tp_reduce(ops.gemm(act, L["down"], out_dtype=self._proj_dtype))
         return self._moe(L, x)
 
     def _moe(self, L, x):
@@ -239,7 +243,7 @@ class ModelRunner:
                 k_all = self.kv.k[li].index_select(0, kv_gather_slots)
                 v_all = self.kv.v[li].index_select(0, kv_gather_slots)
                 ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale)
-            x = self._tp_reduce(ops.gemm(ctx.reshape(T, -1), L["o"]))
+            x = self._tp_reduce(ops.gemm(ctx.reshape(T, -1), L["o"], out_dtype=self._proj_dtype))
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._mlp(L, normed)
         h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
@@ -332,7 +336,7 @@ class ModelRunner:
             k, v = q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
             ops.kv_write(k.reshape(n, -1), v.reshape(n, -1), slots, self.kv.k[li], self.kv.v[li])
             ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
-            x = self._tp_reduce(ops.gemm(ctx.reshape(n, -1), L["o"]))
+            x = self._tp_reduce(ops.gemm(ctx.reshape(n, -1), L["o"], out_dtype=self._proj_dtype))
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._mlp(L, normed)
         h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)

@@ -91,16 +91,12 @@ class SelfAttention(nn.Module):
         normed, residual = ops.rmsnorm(x, self.linear_qkv.layer_norm_weight, cfg.norm_epsilon, residual)
         inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
         qkv = ops.linear(inp, self.linear_qkv.weight, self.linear_qkv.bias)
-        qkv = ops.rope_qk(
-            qkv, packed.position_ids, rope_table, self.hq, self.hkv, self.d,
+        ctx = ops.rope_attention(
+            qkv, packed.position_ids, rope_table, packed.cu_seqlens, packed.max_seqlen, self.hq, self.hkv, self.d,
             self.q_layernorm.weight if self.q_layernorm is not None else None,
             self.k_layernorm.weight if self.k_layernorm is not None else None, cfg.norm_epsilon,
         )  # fmt: skip
-        T = qkv.shape[0]
-        q3 = qkv.view(T, self.hq + 2 * self.hkv, self.d)
-        q, k, v = q3[:, : self.hq], q3[:, self.hq : self.hq + self.hkv], q3[:, self.hq + self.hkv :]
-        ctx = ops.varlen_attention(q, k, v, packed.cu_seqlens, packed.max_seqlen)
-        out = ops.linear(ctx.reshape(T, self.hq * self.d), self.linear_proj.weight)
+        out = ops.linear(ctx, self.linear_proj.weight)
         out = tp.reduce_scatter_to_sequence_parallel_region(out) if self.sp else tp.reduce_from_tensor_model_parallel_region(out)
         return out, residual
 

@@ -41,9 +41,9 @@ def _masked_mean_list(vals, masks, total_lengths=None, response_lengths=None):
 
     if total_lengths is not None and mpu.get_context_parallel_world_size() > 1:
         masks, _ = local_loss_masks(total_lengths, response_lengths, masks)
-    num = sum(float((v.float() * m.to(v.device).float()).sum()) for v, m in zip(vals, masks))
-    den = sum(float(m.sum()) for m in masks)
-    return num / max(den, 1.0)
+    v = torch.cat([x.reshape(-1).float() for x in vals])
+    m = torch.cat([x.reshape(-1) for x in masks]).to(v.device, torch.float32)
+    return (v * m).sum() / torch.clamp_min(m.sum(), 1.0)  # stays on the device: the caller reads all metrics at once
 
 
 def log_rollout_data(rollout_id, args, rollout_data: dict):
@@ -60,6 +60,10 @@ def log_rollout_data(rollout_id, args, rollout_data: dict):
                 log[key] = _masked_mean_list(vals, masks, tl, rl)
             except RuntimeError:
                 continue
+    if log:  # one device->host read for every tensor metric
+        keys = list(log)
+        for k, v in zip(keys, torch.stack([log[k].reshape(()) for k in keys]).tolist()):
+            log[k] = v
     for key in ("rewards", "local_raw_reward", "response_lengths", "truncated"):
         vals = rollout_data.get(key)
         if vals:

@@ -30,11 +30,23 @@ def _pick_bn(M: int, N: int, sms: int = 148) -> int:
     return 256 if cost256 <= cost128 else 128
 
 
-def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, accumulate=False, bn=None):
+def _pick_splitk(M: int, N: int, K: int, bn: int, sms: int = 148) -> int:
+    """K slices for a GEMM whose output tiles cannot fill the machine (small weight gradients over many tokens,
+    skinny decode projections with a long K): enough slices to occupy the SMs, at least 8 k-blocks of 64 each."""
+    tiles = -(-M // 128) * -(-N // bn)
+    kb = -(-K // 64)
+    if tiles * 2 > sms or kb < 16:
+        return 1
+    return max(1, min(kb // 8, sms // tiles))
+
+
+def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, accumulate=False, bn=None, splitk=None):
     """``out (+)= op(A) @ op(B)^T (+ bias)`` with fp32 accumulation on the tcgen05 tensor cores.
 
     ``a``: [M, K] row-major, or [K, M] when ``a_mn``; ``b``: [N, K] row-major, or [K, N]
     when ``b_mn``. bf16 inputs; ``out`` bf16 or fp32 ([M, N], may be a strided row view).
+    ``splitk``: K slices summed by TMA reduce-add into an fp32 ``out`` (None = choose; used only when the output
+    is fp32 and either accumulated into or allocated here, where zero-filling it is free to arrange).
     """
     M, K = (a.shape[1], a.shape[0]) if a_mn else a.shape
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
@@ -55,16 +67,25 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, a
         a = a.contiguous()
     if b.stride(-1) != 1:
         b = b.contiguous()
+    bn = bn or _pick_bn(M, N)
+    can_split = out_dtype == torch.float32 and (accumulate or out is None)
+    if splitk is None:
+        splitk = _pick_splitk(M, N, K, bn, _lib.sm_count(a.device)) if can_split else 1
     if out is None:
         assert not accumulate
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = (torch.zeros if splitk > 1 else torch.empty)(M, N, dtype=out_dtype, device=a.device)
     assert out.stride(-1) == 1 and out.shape == (M, N)
     assert not (accumulate and out.dtype != torch.float32), "accumulate needs an fp32 output"
+    assert splitk == 1 or out.dtype == torch.float32, "split-K sums fp32 partial products: the output must be fp32"
     lda, ldb, ldc = a.stride(0), b.stride(0), out.stride(0)
     assert lda % 8 == 0 and ldb % 8 == 0, "TMA needs 16-byte row pitches (multiples of 8 bf16)"
-    rc = _lib.lib().sb_gemm_bf16(
+    if splitk > 1 and (out.data_ptr() % 16 or (ldc * 4) % 16):
+        if not accumulate:
+            raise ValueError("split-K needs a 16-byte aligned fp32 output")
+        splitk = 1
+    rc = _lib.lib().sb_gemm_bf16_splitk(
         P(a), P(b), P(out), P(bias), M, N, K, lda, ldb, ldc, int(a_mn), int(b_mn), int(out.dtype == torch.float32),
-        int(accumulate), bn or _pick_bn(M, N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
+        int(accumulate), bn, int(splitk), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
     )  # fmt: skip
     _lib.check(rc, "sb_gemm_bf16")
     return out
@@ -130,11 +151,12 @@ class _RMSNorm(torch.autograd.Function):
         else:
             x2 = x2.contiguous()
             r2 = None if residual is None else residual.reshape(-1, H).contiguous()
-            y = torch.empty_like(x2)
-            h = torch.empty_like(x2) if r2 is not None else x2
+            f32x = x2.dtype == torch.float32  # the fp32 sum a split-K projection leaves behind (inference path)
+            y = torch.empty(T, H, dtype=weight.dtype, device=x.device)
+            h = torch.empty_like(y) if (r2 is not None or f32x) else x2
             rstd = torch.empty(T, dtype=torch.float32, device=x.device)
-            rc = _lib.lib().sb_rmsnorm_fwd(P(x2), P(r2), P(weight), P(y), P(h) if r2 is not None else None, P(rstd), T, H,
-                                           float(eps), _lib.stream())
+            fn = _lib.lib().sb_rmsnorm_fwd_f32x if f32x else _lib.lib().sb_rmsnorm_fwd
+            rc = fn(P(x2), P(r2), P(weight), P(y), P(h) if h is not x2 else None, P(rstd), T, H, float(eps), _lib.stream())
             _lib.check(rc, "sb_rmsnorm_fwd")
         ctx.save_for_backward(h, weight, rstd)
         ctx.has_res = residual is not None
@@ -359,6 +381,14 @@ def embedding(ids, table, vocab_lo: int = 0):
 
 
 # ------------------------------------------------------------------- attention
+def rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, eps=1e-6,
+                   scale=None):
+    """RoPE (+ per-head q/k RMSNorm) and packed causal attention on a fused qkv row, as one autograd node."""
+    from slime_b200.ops import attention
+
+    return attention.rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w, k_norm_w, eps, scale)
+
+
 def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True):
     """Packed causal GQA attention. q: [T, Hq, D], k/v: [T, Hkv, D]."""
     from slime_b200.ops import attention

@@ -28,7 +28,9 @@ P, I, L, F = c_void_p, c_int, c_long, c_float
 
 _SIGS = {
     "sb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
+    "sb_gemm_bf16_splitk": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "sb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
+    "sb_rmsnorm_fwd_f32x": [P, P, P, P, P, P, I, I, F, P],
     "sb_rmsnorm_bwd": [P, P, P, P, P, P, P, P, I, I, I, I, P],
     "sb_rope": [P, P, P, P, P, P, I, I, I, I, I, I, F, F, P],
     "sb_swiglu_fwd": [P, P, L, I, P],

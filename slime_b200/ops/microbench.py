@@ -108,6 +108,7 @@ def bench_decode(a):
     g = torch.Generator(device=dev).manual_seed(0)
     rnd = lambda *s: (0.02 * torch.randn(*s, device=dev, generator=g)).to(bf)  # noqa: E731
     x, res = rnd(B, H), rnd(B, H)
+    x32 = x.float()
     ln = torch.ones(H, device=dev, dtype=bf)
     wqkv, bqkv = rnd((hq + 2 * hkv) * d, H), (rnd((hq + 2 * hkv) * d) if cfg.add_qkv_bias else None)
     wo, wgu, wdn, wlm = rnd(H, hq * d), rnd(2 * F, H), rnd(H, F), rnd(V, H)
@@ -131,15 +132,15 @@ def bench_decode(a):
     act = ops.swiglu(gu)
     logits = ops.gemm(x, wlm, out_dtype=torch.float32)
     steps = {
-        "rmsnorm_add": lambda: ops.rmsnorm(x, ln, 1e-6, res),
+        "rmsnorm_add": lambda: ops.rmsnorm(x32, ln, 1e-6, res),  # reads the fp32 projection output
         "gemm_qkv": lambda: ops.gemm(x, wqkv, bias=bqkv),
         "rope_qk": lambda: ops.rope_qk(qkv, pos, rope, hq, hkv, d, qn, qn, 1e-6),
         "kv_write": lambda: ops.kv_write(q3[:, hq : hq + hkv].reshape(B, -1), q3[:, hq + hkv :].reshape(B, -1), slots, kc, vc),
         "paged_attention": lambda: ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps),
-        "gemm_o": lambda: ops.gemm(attn.reshape(B, -1), wo),
+        "gemm_o": lambda: ops.gemm(attn.reshape(B, -1), wo, out_dtype=torch.float32),
         "gemm_gate_up": lambda: ops.gemm(x, wgu),
         "swiglu": lambda: ops.swiglu(gu),
-        "gemm_down": lambda: ops.gemm(act, wdn),
+        "gemm_down": lambda: ops.gemm(act, wdn, out_dtype=torch.float32),  # split-K, summed in fp32
         "gemm_lm_head": lambda: ops.gemm(x, wlm, out_dtype=torch.float32),
         "sample": lambda: ops.sample(logits, temp, None, None, None, seeds, outp, 0),
     }

@@ -259,7 +259,11 @@ def calculate_log_probs_and_entropy(
 # ------------------------------------------------------------ returns / GAE
 def get_grpo_returns(rewards: torch.Tensor, kl: list[torch.Tensor]) -> list[torch.Tensor]:
     """GRPO: every response token carries the sample's (already normalised) reward."""
-    return [torch.ones_like(k) * rewards[i] for i, k in enumerate(kl)]
+    if not kl:
+        return []
+    lens = [k.numel() for k in kl]  # one broadcast over the concatenated batch, handed back as per-sample views
+    flat = torch.repeat_interleave(rewards.to(kl[0].dtype), torch.as_tensor(lens, device=rewards.device), output_size=sum(lens))
+    return list(torch.split(flat, lens))
 
 
 def _suffix_scan_matrix(width: int, factor: float, device, dtype) -> torch.Tensor:
@@ -382,7 +386,11 @@ def get_reinforce_plus_plus_baseline_advantages(
     kl_coef: float,
 ) -> list[torch.Tensor]:
     """REINFORCE++-baseline: ``(r - group mean)`` broadcast per token minus the KL penalty."""
-    return [torch.ones_like(k) * r - kl_coef * k for k, r in zip(kl, rewards)]
+    if not kl:
+        return []
+    lens = [k.numel() for k in kl]
+    flat = torch.repeat_interleave(rewards.to(kl[0].dtype), torch.as_tensor(lens, device=rewards.device), output_size=sum(lens))
+    return list(torch.split(flat - kl_coef * torch.cat(kl), lens))
 
 
 def get_advantages_and_returns_batch(
