@@ -103,7 +103,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 }
 
 // --------------------------------------------------------------------- TMA
-// 2-D tiled load, no multicast. x = innermost coordinate (elements), y = row.
+// 2-D tiled load into this CTA's shared memory. x = innermost coordinate (elements), y = row.
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -21,7 +21,7 @@ ALIGN = 128  # elements; keeps every shard boundary 256-byte aligned for bf16
 
 class FlatBuffer:
     def __init__(self, params: list[torch.nn.Parameter], names: list[str], group, group_size: int, group_rank: int,
-                 device, grad_dtype=torch.float32, allocator=None):  # fmt: skip
+                 device, grad_dtype=torch.float32, allocator=None, symmetric=False):  # fmt: skip
         self.params, self.names = params, names
         self.group, self.group_size, self.group_rank = group, group_size, group_rank
         self.offsets: list[tuple[int, int]] = []
@@ -35,14 +35,26 @@ class FlatBuffer:
         self.shard_size = self.numel // group_size
         dtype = params[0].dtype if params else torch.bfloat16
         alloc = allocator or (lambda n, dt: torch.zeros(n, dtype=dt, device=device))
-        self.param_data = alloc(self.numel, dtype)
-        self.grad_data = alloc(self.numel, grad_dtype)
+        self.fused = None  # FusedDataParallel when both buffers live in symmetric memory
+        self.param_store = self.grad_store = None
+        if symmetric and grad_dtype == torch.float32:
+            from slime_b200.parallel.fused_dp import FusedDataParallel, SymmetricStorage
+
+            self.param_store = SymmetricStorage(self.numel, dtype, device, group)
+            self.grad_store = SymmetricStorage(self.numel, grad_dtype, device, group)
+            self.param_data, self.grad_data = self.param_store.tensor, self.grad_store.tensor
+            self.fused = FusedDataParallel.__new__(FusedDataParallel)  # finished below, once the views exist
+        else:
+            self.param_data = alloc(self.numel, dtype)
+            self.grad_data = alloc(self.numel, grad_dtype)
         for p, (s, e) in zip(params, self.offsets):
             view = self.param_data[s:e].view(p.shape)
             view.copy_(p.data)
             p.data = view
             p.main_grad = self.grad_data[s:e].view(p.shape)
             p.grad_added_to_main_grad = False
+        if self.fused is not None:
+            self.fused.__init__(self)
 
     # ---- shard views ----------------------------------------------------------------
     def shard_range(self, rank: int | None = None) -> tuple[int, int]:
@@ -72,7 +84,7 @@ class FlatBuffer:
 
     # ---- collectives (NCCL baseline; the fused path lives in parallel/fused_dp.py) ------------
     def reduce_scatter_grads(self, average: bool = False, async_op: bool = False):
-        if self.group_size == 1:
+        if self.group_size == 1 or self.fused is not None:  # fused: the optimizer step reduces over peer memory itself
             return None
         op = dist.ReduceOp.AVG if average else dist.ReduceOp.SUM
         return dist.reduce_scatter_tensor(self.grad_shard(), self.grad_data, op=op, group=self.group, async_op=async_op)
@@ -82,7 +94,7 @@ class FlatBuffer:
             dist.all_reduce(self.grad_data, op=dist.ReduceOp.AVG if average else dist.ReduceOp.SUM, group=self.group)
 
     def all_gather_params(self, async_op: bool = False):
-        if self.group_size == 1:
+        if self.group_size == 1 or self.fused is not None:  # fused: the Adam kernel stored into every rank's buffer
             return None
         return dist.all_gather_into_tensor(self.param_data, self.param_shard().clone(), group=self.group, async_op=async_op)
 

@@ -93,9 +93,17 @@ class TrainModel:
                 dense_names.append(name)
         self.buffers: list[FlatBuffer] = []
         alloc = getattr(self, "_allocator", None)
-        self.dense_buffer = FlatBuffer(dense, dense_names, mpu.get_data_parallel_group(with_context_parallel=True),
-                                       mpu.get_data_parallel_world_size(with_context_parallel=True),
-                                       mpu.get_data_parallel_rank(with_context_parallel=True), self.device, allocator=alloc)  # fmt: skip
+        from slime_b200.parallel.fused_dp import symmetric_memory_usable
+
+        dp = mpu.get_data_parallel_world_size(with_context_parallel=True)
+        # Peer-memory optimizer step: needs buffers that stay mapped, so not with a trainer that releases its memory
+        # between phases, and not with optimizer state on the host.
+        symmetric = (symmetric_memory_usable(dp, self.device) and dp == dist.get_world_size()
+                     and not getattr(self.args, "offload_train", False) and not getattr(self.args, "optimizer_cpu_offload", False)
+                     and getattr(self.args, "fused_dp_step", True))  # fmt: skip
+        self.dense_buffer = FlatBuffer(dense, dense_names, mpu.get_data_parallel_group(with_context_parallel=True), dp,
+                                       mpu.get_data_parallel_rank(with_context_parallel=True), self.device, allocator=alloc,
+                                       symmetric=symmetric)  # fmt: skip
         self.buffers.append(self.dense_buffer)
         self.expert_buffer = None
         if expert:

@@ -105,7 +105,9 @@ class DistributedOptimizer:
         self.ctl[0] = 0.0
         for b in self.buffers:
             g = b.grad_shard()
-            if g.is_cuda:
+            if getattr(b, "fused", None) is not None:
+                b.fused.reduce_shard(self.ctl)  # reduce-scatter over peer memory and the shard's squared norm in one pass
+            elif g.is_cuda:
                 n = min(1024, max(1, g.numel() // 4096))
                 rc = _lib.lib().sb_sqnorm(P(g), g.numel(), int(g.dtype == torch.bfloat16), P(self._partials), n,
                                           P(self.ctl), 1, _lib.stream())
@@ -135,7 +137,10 @@ class DistributedOptimizer:
         self.last_grad_norm = self.ctl[0:1].sqrt() * grad_scale  # device tensor; .item() only when logged
         for b, st in zip(self.buffers, self.state):
             g = b.grad_shard()
-            if g.is_cuda and not self.cpu_offload:
+            if getattr(b, "fused", None) is not None:
+                b.fused.adam_bcast(st, lr=lr, b1=b1, b2=b2, eps=self.eps, wd=self.weight_decay, bc1=bc1, bc2=bc2,
+                                   grad_scale=grad_scale, clip=self.clip_grad, ctl=self.ctl, stateless=self.stateless)
+            elif g.is_cuda and not self.cpu_offload:
                 rc = _lib.lib().sb_adam(
                     P(st["master"]), P(st.get("exp_avg")), P(st.get("exp_avg_sq")), P(g), int(g.dtype == torch.bfloat16),
                     P(b.param_shard()), g.numel(), lr, b1, b2, self.eps, self.weight_decay, bc1, bc2, grad_scale,

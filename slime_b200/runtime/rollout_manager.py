@@ -234,6 +234,17 @@ def _resolve_sglang_config(args) -> SglangConfig:
 def start_rollout_servers(args, pg) -> tuple[dict[str, RolloutServer], list]:
     """Create routers and engine groups for every configured model; engine ``init`` calls are left pending so
     the caller can overlap them with loading the data source."""
+    if getattr(args, "rollout_external_engine_addrs", None):
+        from slime_b200.engine import external
+
+        if getattr(args, "rollout_external_engine_infos", None) is None:
+            external.apply_external_engine_info_to_args(args, logger)
+
+        def make_engine(rank, info):  # HTTP front only: the engine process itself belongs to someone else
+            return EngineActor.options(name=f"external-engine-{rank}", max_concurrency=8).remote(
+                args, rank, info.worker_type, 0, None, None)
+
+        return external.start_external_rollout_servers(args, start_router=_start_router, make_engine=make_engine)
     cfg = _resolve_sglang_config(args)
     servers: dict[str, RolloutServer] = {}
     pending, port_cursor = [], 15000

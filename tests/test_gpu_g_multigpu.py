@@ -1,0 +1,32 @@
+"""Multi-GPU checks, each a torchrun job on one node. Skipped on boxes with fewer GPUs than the check needs."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _torchrun(script, nproc, extra_env=None, timeout=420):
+    env = dict(os.environ, **(extra_env or {}))
+    env.setdefault("MASTER_ADDR", "127.0.0.1")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
+           "--master-port", str(29600 + nproc), os.path.join(ROOT, script)]  # fmt: skip
+    return subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+
+
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_fused_dp_step_matches_nccl(kernels, multimem):
+    _need(2)
+    n = min(torch.cuda.device_count(), 8)
+    r = _torchrun("tests/multigpu/fused_dp_check.py", n, {"SLIME_B200_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]

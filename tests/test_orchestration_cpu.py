@@ -53,6 +53,41 @@ def test_train_async_py_overlaps_rollout_and_training(prompt_file):
 
 
 @pytest.mark.timeout(300)
+def test_external_engine_is_discovered_and_used(prompt_file):
+    """An engine somebody else started: probe it, front it with an actor, route generation through it."""
+    from slime_b200.engine import external
+    from slime_b200.engine.http_server import launch_server
+    from slime_b200.engine.server_args import ServerArgs
+    from slime_b200.runtime import actors
+    from slime_b200.runtime.rollout_manager import RolloutManager
+    from slime_b200.utils.arguments import parse_args
+    from slime_b200.utils.http_utils import find_available_port
+
+    port = find_available_port(17000)
+    server = launch_server(ServerArgs(model_path="preset:tiny", host="127.0.0.1", port=port, load_format="dummy"), block=False)
+    try:
+        infos = external.discover_external_engines([f"127.0.0.1:{port}"])
+        assert infos[0].worker_type == "regular" and infos[0].num_gpus == 1 and infos[0].parallel_config["tp_size"] == 1
+        with pytest.raises(ValueError):
+            external.normalize_external_engine_addr("ftp://x")
+        args = parse_args([*COMMON, "--prompt-data", prompt_file, "--num-rollout", "2", "--debug-rollout-only",
+                           "--rollout-external-engine-addrs", f"127.0.0.1:{port}"])  # fmt: skip
+        mgr = RolloutManager(args, None)
+        try:
+            assert args.rollout_num_engines == 1 and len(mgr.rollout_engines) == 1
+            engines, _lock, num_new, counts, offsets, cfgs = mgr.get_updatable_engines_and_lock()
+            assert num_new == 1 and counts == [1] and offsets == [0] and cfgs[0]["tp_size"] == 1
+            assert actors.get(engines[0].get_url.remote()) == f"http://127.0.0.1:{port}"
+            mgr.generate(0)
+            assert server.engine.stats["steps"] > 0  # the tokens came from the pre-launched engine
+        finally:
+            mgr.dispose()
+            actors.shutdown()
+    finally:
+        server.shutdown()
+
+
+@pytest.mark.timeout(300)
 def test_engine_crash_is_detected_and_recovered(prompt_file):
     from slime_b200.runtime import actors
     from slime_b200.runtime.rollout_manager import RolloutManager
