@@ -718,6 +718,8 @@ def namespace_from_dict(d: dict[str, Any]) -> argparse.Namespace:
 def finalize_namespace(ns: argparse.Namespace) -> argparse.Namespace:
     """Derived attributes that ``slime_validate_args`` would set, for programmatically built namespaces."""
     ns.use_critic = ns.advantage_estimator == "ppo"
+    if getattr(ns, "hf_checkpoint", None):
+        _model_defaults_from_hf(ns)  # model shape from config.json / a preset, as the CLI path does
     if ns.eps_clip_high is None:
         ns.eps_clip_high = ns.eps_clip
     ns.offload_train = bool(ns.offload_train)

@@ -1,0 +1,76 @@
+"""Converter tools on CPU: HF -> torch_dist -> HF is the identity on a tiny model."""
+
+import json
+import os
+
+import torch
+
+
+def _tiny_hf_dir(path):
+    from safetensors.torch import save_file
+
+    from slime_b200.backends.train.model import TrainModel
+    from slime_b200.checkpoint.hf_saver import iter_hf_tensors
+    from slime_b200.models.config import get_preset
+    from slime_b200.utils.arguments import namespace_from_dict
+
+    os.makedirs(path, exist_ok=True)
+    cfg = get_preset("tiny")
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(cfg.to_hf_dict(), f)
+    args = namespace_from_dict(dict(hf_checkpoint=path, num_rollout=0, rollout_batch_size=1, seed=7))
+    model = TrainModel(args, device=torch.device("cpu"), with_optimizer=False)
+    tensors = {n: t.detach().clone().contiguous() for n, t in iter_hf_tensors(model)}
+    save_file(tensors, os.path.join(path, "model.safetensors"))
+    return tensors
+
+
+def test_hf_torch_dist_roundtrip(tmp_path):
+    from safetensors import safe_open
+
+    from slime_b200.tools import convert_hf_to_torch_dist, convert_torch_dist_to_hf
+
+    hf = str(tmp_path / "hf")
+    original = _tiny_hf_dir(hf)
+    native = str(tmp_path / "native")
+    convert_hf_to_torch_dist.main(["--hf-checkpoint", hf, "--save", native, "--device", "cpu"])
+    assert open(os.path.join(native, "latest_checkpointed_iteration.txt")).read().strip() == "release"
+    back = str(tmp_path / "back")
+    convert_torch_dist_to_hf.main(["--input-dir", os.path.join(native, "release"), "--output-dir", back, "--origin-hf-dir", hf,
+                                   "--chunk-size", "200000"])  # fmt: skip
+    index = json.load(open(os.path.join(back, "model.safetensors.index.json")))["weight_map"]
+    assert set(index) == set(original) and len(set(index.values())) > 1  # several shards were written
+    for name, fname in index.items():
+        with safe_open(os.path.join(back, fname), framework="pt") as f:
+            assert torch.equal(f.get_tensor(name), original[name]), name
+    assert os.path.exists(os.path.join(back, "config.json"))
+
+
+def test_fp8_convert_and_cast_back(tmp_path):
+    from safetensors import safe_open
+
+    from slime_b200.tools import convert_hf_to_fp8, fp8_cast_bf16
+
+    hf = str(tmp_path / "hf")
+    original = _tiny_hf_dir(hf)
+    fp8 = str(tmp_path / "fp8")
+    wm = convert_hf_to_fp8.convert(hf, fp8, "block", (128, 128), device="cpu")
+    cfg = json.load(open(os.path.join(fp8, "config.json")))
+    assert cfg["quantization_config"]["weight_block_size"] == [128, 128]
+    q_name = "model.layers.0.mlp.down_proj.weight"
+    assert q_name + "_scale_inv" in wm and "model.embed_tokens.weight_scale_inv" not in wm
+    with safe_open(os.path.join(fp8, wm[q_name]), framework="pt") as f:
+        q, s = f.get_tensor(q_name), f.get_tensor(q_name + "_scale_inv")
+        assert q.dtype == torch.float8_e4m3fn and s.dtype == torch.float32
+        assert s.shape == (-(-q.shape[0] // 128), -(-q.shape[1] // 128))
+        assert f.get_tensor("model.norm.weight").dtype == torch.bfloat16
+    back = str(tmp_path / "bf16")
+    assert fp8_cast_bf16.convert(fp8, back, device="cpu") > 0
+    assert "quantization_config" not in json.load(open(os.path.join(back, "config.json")))
+    with safe_open(os.path.join(back, "model.safetensors"), framework="pt") as f:
+        w = f.get_tensor(q_name).float()
+    ref = original[q_name].float()
+    assert (w - ref).abs().max() <= 0.07 * ref.abs().max()  # e4m3 has 3 mantissa bits
+    for strategy in ("channel", "tensor"):
+        wm2 = convert_hf_to_fp8.convert(hf, str(tmp_path / strategy), strategy, device="cpu")
+        assert q_name + "_scale" in wm2
