@@ -13,6 +13,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <cstdlib>
+#include <utility>
+
 namespace sb {
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
@@ -47,6 +50,15 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+
+// ------------------------------------------------ programmatic dependent launch
+// A kernel launched with sb::launch_pdl may begin while its predecessor in the stream is still running; everything
+// it does before pdl_wait() (shared-memory carve-up, barrier init, TMEM allocation, descriptor prefetch) overlaps
+// the predecessor's tail. pdl_wait() returns once the predecessor grid has completed and its writes are visible, so
+// all global-memory traffic must come after it. Every kernel launched this way calls pdl_wait(), which keeps the
+// chain transitive (kernel N+2 may rely on kernel N's results). pdl_launch_dependents() lets the successor start.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
@@ -318,6 +330,31 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 #include <stdexcept>
 #include <string>
 namespace sb {
+// 1 = launch with the programmatic-stream-serialization attribute (default), 0 = plain stream order.
+inline int& pdl_enabled() {
+  static int v = [] {
+    const char* e = std::getenv("SLIME_B200_PDL");
+    return (e != nullptr && e[0] == '0') ? 0 : 1;
+  }();
+  return v;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 inline char* last_error_buf() {
   static thread_local char buf[512] = {0};
   return buf;

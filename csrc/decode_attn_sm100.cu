@@ -62,11 +62,6 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
-  const int len = seq_lens[b];
-  const int per_split = ((len + splits - 1) / splits + DA_TILE - 1) & ~(DA_TILE - 1);
-  const int t_begin = sp * per_split;
-  const int t_end = min(len, t_begin + per_split);
-  const int ntiles = t_end > t_begin ? (t_end - t_begin + DA_TILE - 1) / DA_TILE : 0;
 
   if (tid == 0) {
     for (int s = 0; s < DA_STAGES; ++s) mbar_init(&full[s], 1);
@@ -84,6 +79,14 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   }
   // P starts as zeros: rows >= G stay zero for the whole kernel, rows < G are rewritten every tile.
   for (int i = tid; i < S::P_BYTES / 16; i += DA_THREADS) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
+  // Up to here nothing depended on the previous kernel (barriers, TMEM, the zero fill); the rest reads its outputs.
+  pdl_wait();
+  pdl_launch_dependents();
+  const int len = seq_lens[b];
+  const int per_split = ((len + splits - 1) / splits + DA_TILE - 1) & ~(DA_TILE - 1);
+  const int t_begin = sp * per_split;
+  const int t_end = min(len, t_begin + per_split);
+  const int ntiles = t_end > t_begin ? (t_end - t_begin + DA_TILE - 1) / DA_TILE : 0;
   // Q rows (unscaled bf16; the scale is applied to the fp32 scores) in the canonical K-major 128B-swizzle layout:
   // 16-byte chunk j of row r sits at chunk position j ^ (r % 8).
   for (int i = tid; i < DA_MAXG * NCH * 8; i += DA_THREADS) {
@@ -334,6 +337,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 // out[b, h, :] = sum_s o_s exp(m_s - M) / sum_s l_s exp(m_s - M) over the splits of one (request, head).
 __global__ void decode_attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            __nv_bfloat16* __restrict__ out, int D, int splits, int out_stride, int Hq) {
+  pdl_wait();
+  pdl_launch_dependents();
   const int bh = blockIdx.x, b = bh / Hq, h = bh % Hq;
   const float* ml = part_ml + static_cast<size_t>(bh) * splits * 2;
   float gm = -INFINITY;
@@ -383,9 +388,8 @@ static int launch_decode_attn(dim3 grid, cudaStream_t s, const CUtensorMap& tk, 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  kern<<<grid, DA_THREADS, DecSmem<D>::TOTAL, s>>>(tk, tv, q, bt, sl, out, po, pml, Hq, Hkv, page_size, page_shift, max_pages,
-                                                  q_stride, out_stride, splits, scale, status);
-  return (int)cudaGetLastError();
+  return (int)launch_pdl(kern, grid, dim3(DA_THREADS), DecSmem<D>::TOTAL, s, tk, tv, q, bt, sl, out, po, pml, Hq, Hkv,
+                         page_size, page_shift, max_pages, q_stride, out_stride, splits, scale, status);
 }
 
 }  // namespace sb
@@ -421,7 +425,8 @@ extern "C" int sb_paged_decode_tc(const void* q, const void* k_cache, const void
 #undef SB_DA
     if (rc != 0) return rc;
     if (splits > 1)
-      sb::decode_attn_combine_kernel<<<B * Hq, 64, 0, s>>>(part_o, part_ml, (bf16*)out, D, splits, out_stride, Hq);
+      return (int)sb::launch_pdl(sb::decode_attn_combine_kernel, dim3(B * Hq), dim3(64), 0, s, part_o, part_ml, (bf16*)out, D,
+                                 splits, out_stride, Hq);
     return (int)cudaGetLastError();
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());

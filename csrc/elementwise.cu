@@ -42,6 +42,8 @@ rmsnorm_fwd_kernel(const XT* __restrict__ x, const __nv_bfloat16* __restrict__ r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int H, float eps) {
   __shared__ float scratch[32];
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const size_t row = blockIdx.x;
   const int nvec = H >> 3;
   float v[NORM_MAX_VEC][8];
@@ -171,6 +173,8 @@ rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* out /* may alias x: a warp re
             const float* __restrict__ cos_sin, const __nv_bfloat16* __restrict__ nw, float* __restrict__ rstd_out,
             int T, int nheads, int head0, int in_stride, int out_stride, float eps, float sign) {
   constexpr int PER = D / 64;  // each lane handles PER pairs (i, i + D/2) ... D/2 / 32 lanes
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp_global >= T * nheads) return;
@@ -210,6 +214,8 @@ rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* out /* may alias x: a warp re
 // ---------------------------------------------------------------------- SwiGLU
 // gu: [T, 2F] = [gate | up]; act[T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, size_t T, int F) {
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const size_t nvec = T * (F >> 3);
   for (size_t idx = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; idx < nvec;
        idx += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -251,6 +257,8 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __
 // ------------------------------------------------------------------- embedding
 __global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                      __nv_bfloat16* __restrict__ out, int T, int H, int vocab_lo, int vocab_hi) {
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool mine = id >= vocab_lo && id < vocab_hi;
@@ -292,9 +300,8 @@ extern "C" int sb_rmsnorm_fwd(const void* x, const void* res, const void* w, voi
                               int T, int H, float eps, cudaStream_t s) {
   if (T == 0) return 0;
   if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
-  sb::rmsnorm_fwd_kernel<bf16><<<T, sb::NORM_THREADS, 0, s>>>((const bf16*)x, (const bf16*)res, (const bf16*)w, (bf16*)y,
-                                                              (bf16*)res_out, rstd, H, eps);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::rmsnorm_fwd_kernel<bf16>, dim3(T), dim3(sb::NORM_THREADS), 0, s, (const bf16*)x,
+                             (const bf16*)res, (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, H, eps);
 }
 
 // Same, with x in fp32 (res, w, y, res_out stay bf16).
@@ -302,9 +309,8 @@ extern "C" int sb_rmsnorm_fwd_f32x(const float* x, const void* res, const void* 
                                    int T, int H, float eps, cudaStream_t s) {
   if (T == 0) return 0;
   if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
-  sb::rmsnorm_fwd_kernel<float><<<T, sb::NORM_THREADS, 0, s>>>(x, (const bf16*)res, (const bf16*)w, (bf16*)y,
-                                                               (bf16*)res_out, rstd, H, eps);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::rmsnorm_fwd_kernel<float>, dim3(T), dim3(sb::NORM_THREADS), 0, s, x, (const bf16*)res,
+                             (const bf16*)w, (bf16*)y, (bf16*)res_out, rstd, H, eps);
 }
 
 // dw_partial: scratch [num_ctas, H] fp32 supplied by the caller; dw: [H] fp32.
@@ -326,14 +332,14 @@ extern "C" int sb_rope(const void* x, void* out, const int* pos, const float* co
   const long warps = (long)T * nheads;
   const int blocks = (int)((warps * 32 + 127) / 128);
   if (D == 64)
-    sb::rope_kernel<64><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T, nheads,
-                                              head0, in_stride, out_stride, eps, sign);
+    return (int)sb::launch_pdl(sb::rope_kernel<64>, dim3(blocks), dim3(128), 0, s, (const bf16*)x, (bf16*)out, pos, cos_sin,
+                               (const bf16*)nw, rstd, T, nheads, head0, in_stride, out_stride, eps, sign);
   else if (D == 128)
-    sb::rope_kernel<128><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T,
-                                               nheads, head0, in_stride, out_stride, eps, sign);
+    return (int)sb::launch_pdl(sb::rope_kernel<128>, dim3(blocks), dim3(128), 0, s, (const bf16*)x, (bf16*)out, pos, cos_sin,
+                               (const bf16*)nw, rstd, T, nheads, head0, in_stride, out_stride, eps, sign);
   else if (D == 256)
-    sb::rope_kernel<256><<<blocks, 128, 0, s>>>((const bf16*)x, (bf16*)out, pos, cos_sin, (const bf16*)nw, rstd, T,
-                                               nheads, head0, in_stride, out_stride, eps, sign);
+    return (int)sb::launch_pdl(sb::rope_kernel<256>, dim3(blocks), dim3(128), 0, s, (const bf16*)x, (bf16*)out, pos, cos_sin,
+                               (const bf16*)nw, rstd, T, nheads, head0, in_stride, out_stride, eps, sign);
   else
     return (int)cudaErrorInvalidValue;
   return (int)cudaGetLastError();
@@ -347,8 +353,8 @@ static inline int ew_blocks(size_t n, int threads) {
 extern "C" int sb_swiglu_fwd(const void* gu, void* act, long T, int F, cudaStream_t s) {
   if (T == 0) return 0;
   if (F % 8 != 0) return (int)cudaErrorInvalidValue;
-  sb::swiglu_fwd_kernel<<<ew_blocks((size_t)T * (F / 8), 256), 256, 0, s>>>((const bf16*)gu, (bf16*)act, (size_t)T, F);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::swiglu_fwd_kernel, dim3(ew_blocks((size_t)T * (F / 8), 256)), dim3(256), 0, s, (const bf16*)gu,
+                             (bf16*)act, (size_t)T, F);
 }
 
 extern "C" int sb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long T, int F, cudaStream_t s) {
@@ -362,8 +368,8 @@ extern "C" int sb_swiglu_bwd(const void* gu, const void* dact, void* dgu, long T
 extern "C" int sb_embedding_fwd(const int* ids, const void* table, void* out, int T, int H, int vlo, int vhi,
                                 cudaStream_t s) {
   if (T == 0) return 0;
-  sb::embedding_fwd_kernel<<<T, 128, 0, s>>>(ids, (const bf16*)table, (bf16*)out, T, H, vlo, vhi);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::embedding_fwd_kernel, dim3(T), dim3(128), 0, s, ids, (const bf16*)table, (bf16*)out, T, H,
+                             vlo, vhi);
 }
 
 extern "C" int sb_embedding_bwd(const int* ids, const void* dout, float* dtable, int T, int H, int vlo, int vhi,

@@ -106,6 +106,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, TMEM, descriptor prefetch) may overlap the previous kernel; operands may not.
+  pdl_wait();
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -367,9 +370,8 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   const int splitk = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
   const int grid = tiles < num_sms ? tiles : num_sms;
-  kern<<<grid, GEMM_THREADS, S::TOTAL, stream>>>(tmA, tmB, tmC, C, reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K,
-                                                 ldc, accumulate, status);
-  cudaError_t le = cudaGetLastError();
+  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, tmC, C,
+                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status);
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
   return le;
 }
@@ -448,3 +450,7 @@ extern "C" int sb_gemm_bf16(const void* A, const void* B, void* C, const void* b
   return sb_gemm_bf16_splitk(A, B, C, bias, M, N, K, lda, ldb, ldc, a_mn, b_mn, out_f32, accumulate, bn, 1, status, num_sms,
                              stream);
 }
+
+// 1: kernels of this library are launched with programmatic dependent launch (default); 0: plain stream order.
+extern "C" void sb_set_pdl(int enabled) { sb::pdl_enabled() = enabled ? 1 : 0; }
+extern "C" int sb_get_pdl(void) { return sb::pdl_enabled(); }

@@ -14,6 +14,8 @@ namespace sb {
 __global__ void kv_write_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
                                 const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache,
                                 __nv_bfloat16* __restrict__ v_cache, int T, int row_elems, int k_stride, int v_stride) {
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int t = blockIdx.x;
   const int slot = slots[t];
   if (slot < 0) return;
@@ -213,9 +215,8 @@ extern "C" int sb_kv_write(const void* k, const void* v, const int* slots, void*
                            int row_elems, int k_stride, int v_stride, cudaStream_t s) {
   if (T == 0) return 0;
   if (row_elems % 8 != 0 || k_stride % 8 != 0 || v_stride % 8 != 0) return (int)cudaErrorInvalidValue;
-  sb::kv_write_kernel<<<T, 128, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, slots, (__nv_bfloat16*)k_cache,
-                                        (__nv_bfloat16*)v_cache, T, row_elems, k_stride, v_stride);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::kv_write_kernel, dim3(T), dim3(128), 0, s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                             slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, row_elems, k_stride, v_stride);
 }
 
 // part_o: scratch [B, Hq, splits, D] fp32; part_ml: scratch [B, Hq, splits, 2] fp32.
@@ -255,6 +256,8 @@ __global__ void decode_prepare_kernel(int* __restrict__ ids, int* __restrict__ p
                                       const int* __restrict__ active, const int* __restrict__ block_table,
                                       int* __restrict__ ids_eff, int* __restrict__ pos_eff, int* __restrict__ seq_lens,
                                       int* __restrict__ slots, int B, int page_size, int max_pages) {
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   if (init_mask[b]) {
@@ -278,6 +281,8 @@ __global__ void decode_prepare_kernel(int* __restrict__ ids, int* __restrict__ p
 
 __global__ void decode_advance_kernel(int* __restrict__ ids, int* __restrict__ pos, int* __restrict__ out_pos,
                                       const int* __restrict__ active, const int* __restrict__ sampled, int B) {
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B || !active[b]) return;
   ids[b] = sampled[b];
@@ -292,15 +297,14 @@ extern "C" int sb_decode_prepare(int* ids, int* pos, int* out_pos, const int* in
                                  int* ids_eff, int* pos_eff, int* seq_lens, int* slots, int B, int page_size,
                                  int max_pages, cudaStream_t s) {
   if (B == 0) return 0;
-  sb::decode_prepare_kernel<<<(B + 127) / 128, 128, 0, s>>>(ids, pos, out_pos, init_mask, init_ids, init_pos, init_out_pos,
-                                                            active, block_table, ids_eff, pos_eff, seq_lens, slots, B,
-                                                            page_size, max_pages);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::decode_prepare_kernel, dim3((B + 127) / 128), dim3(128), 0, s, ids, pos, out_pos, init_mask,
+                             init_ids, init_pos, init_out_pos, active, block_table, ids_eff, pos_eff, seq_lens, slots, B,
+                             page_size, max_pages);
 }
 
 extern "C" int sb_decode_advance(int* ids, int* pos, int* out_pos, const int* active, const int* sampled, int B,
                                  cudaStream_t s) {
   if (B == 0) return 0;
-  sb::decode_advance_kernel<<<(B + 127) / 128, 128, 0, s>>>(ids, pos, out_pos, active, sampled, B);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_pdl(sb::decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, s, ids, pos, out_pos, active,
+                             sampled, B);
 }

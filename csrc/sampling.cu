@@ -97,6 +97,8 @@ sample_kernel(const T* __restrict__ logits, size_t ld, int V, const float* __res
   __shared__ int s_cnt_above;
   __shared__ int s_kept;
 
+  pdl_wait();  // inputs come from the previous kernel in the stream
+  pdl_launch_dependents();
   const int b = blockIdx.x;
   const T* row = logits + static_cast<size_t>(b) * ld;
   const float temp = temperature[b];
@@ -241,12 +243,10 @@ extern "C" int sb_sample(const void* logits, int is_bf16, long ld, int B, int V,
                          cudaStream_t s) {
   if (B == 0) return 0;
   if (is_bf16)
-    sb::sample_kernel<__nv_bfloat16><<<B, sb::SAMPLE_THREADS, 0, s>>>(
-        (const __nv_bfloat16*)logits, (size_t)ld, V, temperature, top_k, top_p, min_p, (const uint64_t*)seeds, positions,
-        token, logprob, kept_ids, kept_count, kept_cap);
-  else
-    sb::sample_kernel<float><<<B, sb::SAMPLE_THREADS, 0, s>>>((const float*)logits, (size_t)ld, V, temperature, top_k,
-                                                             top_p, min_p, (const uint64_t*)seeds, positions, token,
-                                                             logprob, kept_ids, kept_count, kept_cap);
-  return (int)cudaGetLastError();
+    return (int)sb::launch_pdl(sb::sample_kernel<__nv_bfloat16>, dim3(B), dim3(sb::SAMPLE_THREADS), 0, s,
+                               (const __nv_bfloat16*)logits, (size_t)ld, V, temperature, top_k, top_p, min_p,
+                               (const uint64_t*)seeds, positions, token, logprob, kept_ids, kept_count, kept_cap);
+  return (int)sb::launch_pdl(sb::sample_kernel<float>, dim3(B), dim3(sb::SAMPLE_THREADS), 0, s, (const float*)logits, (size_t)ld,
+                             V, temperature, top_k, top_p, min_p, (const uint64_t*)seeds, positions, token, logprob, kept_ids,
+                             kept_count, kept_cap);
 }

@@ -74,3 +74,27 @@ def test_fp8_convert_and_cast_back(tmp_path):
     for strategy in ("channel", "tensor"):
         wm2 = convert_hf_to_fp8.convert(hf, str(tmp_path / strategy), strategy, device="cpu")
         assert q_name + "_scale" in wm2
+
+
+def test_int4_direct_conversion(tmp_path):
+    from safetensors import safe_open
+
+    from slime_b200.tools import convert_hf_to_int4_direct as tool
+
+    hf = str(tmp_path / "hf")
+    original = _tiny_hf_dir(hf)
+    out = str(tmp_path / "int4")
+    assert tool.convert(hf, out, 32, device="cpu")["quantised"] == 0  # dense model: the default list keeps everything bf16
+    stats = tool.convert(hf, out, 32, ignore=[r".*embed.*", r".*norm.*", r".*lm_head.*"], device="cpu")
+    assert stats["quantised"] > 0
+    name = "model.layers.1.mlp.down_proj"
+    with safe_open(os.path.join(out, "model.safetensors"), framework="pt") as f:
+        packed, scale, shape = (f.get_tensor(f"{name}.weight_{k}") for k in ("packed", "scale", "shape"))
+        assert f"{name}.weight" not in f.keys()
+    w = original[name + ".weight"].float()
+    assert shape.tolist() == list(w.shape) and packed.shape == (w.shape[0], w.shape[1] // 8)
+    codes = torch.stack([((packed >> (4 * i)) & 0xF) - 8 for i in range(8)], -1).reshape(w.shape).float()
+    deq = (codes.view(w.shape[0], -1, 32) * scale.float()[..., None]).view(w.shape)
+    assert (deq - w).abs().max() <= w.abs().max() / 7 * 0.51 + 1e-3  # half a quantisation step of the largest group
+    cfg = json.load(open(os.path.join(out, "config.json")))["quantization_config"]
+    assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["group_size"] == 32
