@@ -1,19 +1,23 @@
 // Paged decode attention on the 5th-gen tensor cores (sm_100a): one query token per request, GQA.
 //
-// Decode attention is bound by streaming the KV cache once, so the kernel is a TMA pipeline with the two
-// small contractions on tcgen05 so that the CUDA cores only do the softmax:
+// Decode attention is bound by streaming the KV cache once, so the kernel is a TMA pipeline with the two small
+// contractions on tcgen05 and only the softmax on the CUDA cores:
 //
 //   per 128-token tile of one (request, kv head, split):
-//     TMA      K tile [128 tok, D] and V tile [128 tok, D] from the paged cache (one box per page) -> smem, 128B swizzle
-//     tcgen05  S^T[128 tok, 16] = K · Q^T          (A = K tile K-major, B = the G<=16 query heads of this kv head)
-//     threads  one token per thread: tcgen05.ld its 16 scores, tile max per head, exp, P -> smem (bf16)
-//     tcgen05  O[128(G used), D] = P · V            (A = P K-major [head, token], B = V tile MN-major)
-//     warp 0   tcgen05.ld rows 0..G-1 of O, online-softmax merge into the running (m, l, acc) kept in lane g
+//     TMA      V tile and K tile [128 tok, D] from the paged cache (one box per page) -> smem, 128B swizzle
+//     tcgen05  S^T[128 tok, 16]  = K · Q^T          A = K tile (K-major), B = the G <= 16 query heads of this kv head
+//     threads  one token per thread: tcgen05.ld its 16 scores, tile max per head, exp, P^T -> smem (bf16, 4 KB)
+//     tcgen05  O^T[128(D used), 16] = V^T · P^T     A = V tile read MN-major, B = P^T (K-major)
+//     threads  one output dim per thread: tcgen05.ld its 16 values, online-softmax merge into registers
 //
-//   S^T is double-buffered in TMEM so K·Q^T of tile i+1 overlaps the softmax of tile i; two smem stages keep the
-//   next tile's K/V in flight. Grid = (B, Hkv, splits); with splits > 1 partial (o, m, l) go to a workspace and a
-//   small combine kernel finishes. Every mbarrier wait is bounded (2 s): on expiry the CTA records a status word,
-//   skips its output, lets in-flight copies land, frees its TMEM and returns.
+//   S^T, P^T and O^T are double-buffered: K·Q^T of tile i+1 and V^T·P^T of tile i-1 run underneath the softmax of tile i,
+//   and tile i-2 is merged meanwhile, so the tensor pipe's latency is off the critical path; three
+//   smem stages keep the next tiles' K/V in flight; ~107 KB of smem and 128 TMEM columns per CTA let two CTAs share
+//   an SM (D = 64). For D = 64 the V^T operand needs 128 rows: its upper half is pointed at the K tile that follows V in the
+//   stage; those 64 accumulator rows are never read.
+//   Grid = (B, Hkv, splits); with splits > 1 partial (o, m, l) go to a workspace and a small combine kernel finishes.
+//   Every mbarrier wait is bounded (2 s): on expiry the CTA records a status word, skips its output, lets in-flight
+//   copies land, frees its TMEM and returns.
 //
 // Cache layout: k_cache / v_cache = [num_slots, Hkv, D] bf16, slot = page * page_size + offset;
 // block_table[b, i] = page id of the i-th page of request b. page_size must be 16, 32, 64 or 128.
@@ -23,20 +27,33 @@ namespace sb {
 
 constexpr int DA_TILE = 128;  // tokens per tile = TMEM lanes = threads
 constexpr int DA_THREADS = 128;
-constexpr int DA_STAGES = 2;
-constexpr int DA_MAXG = 16;  // N of the S^T MMA
+constexpr int DA_STAGES = 3;  // K is fetched three tiles ahead, V two: enough bytes in flight to cover HBM latency
+constexpr int DA_BT_CACHE = 256;  // block-table entries of this CTA's token range kept in shared memory
+constexpr int DA_MAXG = 16;  // N of both MMAs
 
 template <int D>
 struct DecSmem {
-  static constexpr int NCH = D / 64;                      // 128-byte chunks of the head dim
-  static constexpr int KV_TILE = DA_TILE * 128 * NCH;     // bytes of one K (or V) tile
-  static constexpr int STAGE = 2 * KV_TILE;               // K then V
-  static constexpr int P_BYTES = 2 * 128 * 128;           // [128 rows, 2 chunks of 64 tokens] bf16, K-major
-  static constexpr int Q_BYTES = DA_MAXG * 128 * NCH;     // [16 heads, D] bf16, K-major
+  static constexpr int NCH = D / 64;                     // 128-byte chunks of the head dim
+  static constexpr int KV_TILE = DA_TILE * 128 * NCH;    // bytes of one K (or V) tile
+  static constexpr int STAGE = 2 * KV_TILE;              // V then K
+  static constexpr int P_BYTES = 2 * DA_MAXG * 128;      // P^T [16 heads, 2 chunks of 64 tokens] bf16, K-major
+  static constexpr int Q_BYTES = DA_MAXG * 128 * NCH;    // [16 heads, D] bf16, K-major
   static constexpr int BAR_BYTES = 128;
-  static constexpr int TOTAL = DA_STAGES * STAGE + P_BYTES + Q_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
-  static constexpr int TMEM_COLS = D == 64 ? 128 : 256;   // S0 @0, S1 @32, O @64..64+D
+  static constexpr int TOTAL = DA_STAGES * STAGE + 2 * P_BYTES + Q_BYTES + BAR_BYTES + 1024;  // +1024: manual alignment
+  static constexpr int TMEM_COLS = 128;                  // S0 @0, S1 @32, O^T @64 (16 used of each 32)
 };
+
+// One-instruction warp maximum (sm_100a: redux.sync on f32).
+__device__ __forceinline__ float warp_max_redux(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
 
 template <int D, int G>
 __global__ void __launch_bounds__(DA_THREADS)
@@ -52,22 +69,30 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sKV = smem;
   uint8_t* sP = smem + DA_STAGES * S::STAGE;
-  uint8_t* sQ = sP + S::P_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(sQ + S::Q_BYTES);
-  uint64_t* bar_s = full + DA_STAGES;
+  uint8_t* sQ = sP + 2 * S::P_BYTES;
+  uint64_t* full_k = reinterpret_cast<uint64_t*>(sQ + S::Q_BYTES);
+  uint64_t* full_v = full_k + DA_STAGES;
+  uint64_t* bar_s = full_v + DA_STAGES;
   uint64_t* bar_o = bar_s + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 2);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ float red_m[2][4][DA_MAXG], red_l[4][DA_MAXG];
+  __shared__ __align__(16) float red_m[2][DA_MAXG][4];  // [S buffer][head][warp]: one 16-byte read per head
+  __shared__ float red_l[4][DA_MAXG];
+  __shared__ int bt_s[DA_BT_CACHE];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float scale_log2 = scale * 1.4426950408889634f;  // scores live in the log2 domain: exp(x) = 2^(x log2 e)
   const int b = blockIdx.x, kvh = blockIdx.y, sp = blockIdx.z;
 
   if (tid == 0) {
-    for (int s = 0; s < DA_STAGES; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < DA_STAGES; ++s) {
+      mbar_init(&full_k[s], 1);
+      mbar_init(&full_v[s], 1);
+    }
     mbar_init(&bar_s[0], 1);
     mbar_init(&bar_s[1], 1);
-    mbar_init(bar_o, 1);
+    mbar_init(&bar_o[0], 1);
+    mbar_init(&bar_o[1], 1);
     *cta_abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmK);
@@ -77,8 +102,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     tmem_alloc(tmem_slot, S::TMEM_COLS);
     tmem_relinquish();
   }
-  // P starts as zeros: rows >= G stay zero for the whole kernel, rows < G are rewritten every tile.
-  for (int i = tid; i < S::P_BYTES / 16; i += DA_THREADS) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
+  // P^T starts as zeros: rows >= G stay zero for the whole kernel, rows < G are rewritten every tile.
+  for (int i = tid; i < 2 * S::P_BYTES / 16; i += DA_THREADS) reinterpret_cast<uint4*>(sP)[i] = make_uint4(0, 0, 0, 0);
   // Up to here nothing depended on the previous kernel (barriers, TMEM, the zero fill); the rest reads its outputs.
   pdl_wait();
   pdl_launch_dependents();
@@ -87,6 +112,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   const int t_begin = sp * per_split;
   const int t_end = min(len, t_begin + per_split);
   const int ntiles = t_end > t_begin ? (t_end - t_begin + DA_TILE - 1) / DA_TILE : 0;
+  const int* bt_row = block_table + static_cast<size_t>(b) * max_pages;
+  // one coalesced read of the page ids this CTA will need, so that issuing a tile's copies does not wait on them
+  const int my_pages = t_end > t_begin ? ((t_end - t_begin + page_size - 1) >> page_shift) : 0;
+  for (int i = tid; i < min(my_pages, DA_BT_CACHE); i += DA_THREADS) bt_s[i] = bt_row[(t_begin >> page_shift) + i];
   // Q rows (unscaled bf16; the scale is applied to the fp32 scores) in the canonical K-major 128B-swizzle layout:
   // 16-byte chunk j of row r sits at chunk position j ^ (r % 8).
   for (int i = tid; i < DA_MAXG * NCH * 8; i += DA_THREADS) {
@@ -102,34 +131,34 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 64;
+  const uint32_t tmem_o = tmem_base + 64;  // O^T buffer (i & 1) at +0 / +32
 
-  const int* bt_row = block_table + static_cast<size_t>(b) * max_pages;
-  // warp 0, all lanes: start the copies of tile i. Lane p fetches the block-table entry of page p and issues that
-  // page's boxes (one per 64-wide chunk of the head dim, for K and for V), so the table reads overlap.
-  auto issue_tile = [&](int i) {
+  // warp 0, all lanes: start the copies of the K (or V) half of tile i. Lane p fetches the block-table entry of page p
+  // and issues that page's boxes (one per 64-wide chunk of the head dim), so the table reads overlap. K and V have
+  // separate barriers because their buffers become free at different times: K once S^T of the tile two back is done,
+  // V once that tile's O^T is done. With three stages K runs three tiles ahead of the softmax and V two.
+  auto issue_half = [&](int i, bool is_k) {
     const int s = i % DA_STAGES;
     const int t0 = t_begin + i * DA_TILE;
     const int valid = min(DA_TILE, t_end - t0);
     const int npages = (valid + page_size - 1) >> page_shift;
-    uint8_t* kd = sKV + s * S::STAGE;
-    uint8_t* vd = kd + S::KV_TILE;
-    if (lane == 0) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128 * NCH * 2));
+    uint8_t* dst = sKV + s * S::STAGE + (is_k ? S::KV_TILE : 0);
+    uint64_t* bar = is_k ? &full_k[s] : &full_v[s];
+    if (lane == 0) mbar_arrive_expect_tx(bar, static_cast<uint32_t>(npages * page_size * 128 * NCH));
     __syncwarp();
     if (lane < npages) {
-      const int slot0 = bt_row[(t0 >> page_shift) + lane] * page_size;
+      const int pi = ((t0 - t_begin) >> page_shift) + lane;  // page index within this CTA's range
+      const int slot0 = (pi < DA_BT_CACHE ? bt_s[pi] : bt_row[(t_begin >> page_shift) + pi]) * page_size;
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) {
-        tma_load_3d(kd + c * (DA_TILE * 128) + lane * page_size * 128, &tmK, &full[s], c * 64, kvh, slot0);
-        tma_load_3d(vd + c * (DA_TILE * 128) + lane * page_size * 128, &tmV, &full[s], c * 64, kvh, slot0);
-      }
+      for (int c = 0; c < NCH; ++c)
+        tma_load_3d(dst + c * (DA_TILE * 128) + lane * page_size * 128, is_k ? &tmK : &tmV, bar, c * 64, kvh, slot0);
     }
     __syncwarp();
   };
   // thread 0 only: S^T[128 tok, 16] = K_tile · Q^T into S buffer (i & 1)
   auto issue_s_mma = [&](int i) {
     constexpr uint32_t idesc = make_idesc(DA_TILE, DA_MAXG, 1, 1, 0, 0);
-    const uint32_t k_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE);
+    const uint32_t k_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE + S::KV_TILE);
     const uint32_t q_addr = smem_u32(sQ);
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
@@ -140,27 +169,31 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
                  (c | k) != 0 ? 1u : 0u);
     umma_commit(&bar_s[i & 1]);
   };
-  // thread 0 only: O[128, D] = P · V_tile (fresh accumulator every tile; the merge happens in registers)
+  // thread 0 only: O^T[128, 16] = V_tile^T · P^T (fresh accumulator every tile; the merge happens in registers).
+  // A is the V tile read MN-major: 64-wide chunks of the head dim are DA_TILE*128 bytes apart; with D = 64 the second
+  // chunk is the K tile, whose 64 product rows are ignored.
   auto issue_o_mma = [&](int i) {
-    constexpr uint32_t idesc = make_idesc(128, D, 1, 1, 0, 1);
-    const uint32_t p_addr = smem_u32(sP);
-    const uint32_t v_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE + S::KV_TILE);
+    constexpr uint32_t idesc = make_idesc(128, DA_MAXG, 1, 1, 1, 0);
+    const uint32_t v_addr = smem_u32(sKV + (i % DA_STAGES) * S::STAGE);
+    const uint32_t p_addr = smem_u32(sP + (i & 1) * S::P_BYTES);
 #pragma unroll
     for (int kc = 0; kc < 2; ++kc)
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        umma_f16(tmem_o, make_smem_desc(p_addr + kc * (128 * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
-                 make_smem_desc(v_addr + (kc * 4 + k) * 2048, DA_TILE * 128, 1024, UMMA_SWIZZLE_128B), idesc,
+        umma_f16(tmem_o + (i & 1) * 32, make_smem_desc(v_addr + (kc * 4 + k) * 2048, DA_TILE * 128, 1024, UMMA_SWIZZLE_128B),
+                 make_smem_desc(p_addr + kc * (DA_MAXG * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc,
                  (kc | k) != 0 ? 1u : 0u);
-    umma_commit(bar_o);
+    umma_commit(&bar_o[i & 1]);
   };
 
   bool ok = true;
   if (warp == 0 && ntiles > 0) {
-    issue_tile(0);
-    if (ntiles > 1) issue_tile(1);
+    for (int t = 0; t < min(ntiles, DA_STAGES); ++t) {
+      issue_half(t, true);
+      issue_half(t, false);
+    }
     if (lane == 0) {
-      ok = mbar_wait(&full[0], 0, cta_abort, status, ERR_WAIT_FULL);
+      ok = mbar_wait(&full_k[0], 0, cta_abort, status, ERR_WAIT_FULL);
       if (ok) {
         tc_fence_after();
         issue_s_mma(0);
@@ -169,19 +202,36 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     __syncwarp();
   }
 
-  // Running softmax state. The output accumulator of head g lives in lane g of warp 0. The denominator is kept per
-  // thread (each thread sums the p of its own tokens, rescaled like the accumulator) and reduced once at the end,
-  // which takes the per-tile sum reduction off the critical path.
-  float m_run = -INFINITY;
-  float m_thr[G], l_thr[G];
+  // Running softmax state. Thread d (< D) owns output dim d of all G heads. The denominator is kept per thread (each
+  // thread sums the p of its own tokens, rescaled like the accumulator) and reduced once at the end. `keep`/`gain`
+  // are the factors a tile's merge applies: acc = acc * keep + o_tile * gain. A tile is merged two iterations after
+  // its softmax (so that the tensor pipe's issue-to-completion latency never stalls the loop), hence two sets.
+  float acc[G], m_thr[G], l_thr[G], keep0[G], gain0[G], keep1[G], gain1[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
+    acc[g] = 0.f;
     m_thr[g] = -INFINITY;
     l_thr[g] = 0.f;
+    keep0[g] = keep1[g] = 1.f;
+    gain0[g] = gain1[g] = 0.f;
   }
-  float acc[D];
+  const bool merges = tid < D;  // warp-uniform: D is 64 or 128
+  // merge tile j (its O^T buffer (j & 1) is ready once that buffer's barrier completes phase j / 2)
+  auto merge_tile = [&](int j) -> bool {
+    bool okm = mbar_wait(&bar_o[j & 1], (j >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
+    okm = __all_sync(0xffffffffu, okm);
+    tc_fence_after();
+    if (okm && merges) {
+      uint32_t r[32];
+      tmem_ld_32x32(tmem_o + (j & 1) * 32 + (static_cast<uint32_t>(warp * 32) << 16), r);
+      tmem_ld_wait();
+      const bool odd = (j & 1) != 0;
 #pragma unroll
-  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+      for (int g = 0; g < G; ++g)
+        acc[g] = acc[g] * (odd ? keep1[g] : keep0[g]) + __uint_as_float(r[g]) * (odd ? gain1[g] : gain0[g]);
+    }
+    return okm;
+  };
 
   for (int i = 0; i < ntiles; ++i) {
     const int s = i % DA_STAGES, par = i & 1;
@@ -189,6 +239,15 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const int valid = min(DA_TILE, t_end - t0);
     // ---- scores of this thread's token (TMEM lane = tid) for the G heads
     if (ok) ok = mbar_wait(&bar_s[par], (i >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
+    if (tid == 0 && ok && i + 1 < ntiles) {
+      // K·Q^T of the next tile goes to the other S^T buffer now, so it runs underneath this tile's softmax
+      if (mbar_wait(&full_k[(i + 1) % DA_STAGES], ((i + 1) / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL)) {
+        tc_fence_after();
+        issue_s_mma(i + 1);
+      } else {
+        ok = false;
+      }
+    }
     ok = __all_sync(0xffffffffu, ok);  // the TMEM load below is warp-collective: take one decision per warp
     tc_fence_after();
     float sc[G];
@@ -202,39 +261,52 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         for (int g = 0; g < 32; ++g) r[g] = 0;
       }
 #pragma unroll
-      for (int g = 0; g < G; ++g) sc[g] = (tid < valid) ? __uint_as_float(r[g]) * scale : -INFINITY;
+      for (int g = 0; g < G; ++g) sc[g] = (tid < valid) ? __uint_as_float(r[g]) * scale_log2 : -INFINITY;
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const float wm = warp_max(sc[g]);
-      if (lane == 0) red_m[par][warp][g] = wm;
+      const float wm = warp_max_redux(sc[g]);
+      if (lane == 0) red_m[par][g][warp] = wm;
     }
-    // P of the previous tile must have been consumed before it is overwritten
-    if (ok && i > 0) ok = mbar_wait(bar_o, (i - 1) & 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY);
     ok = __syncthreads_and(ok);  // (A) tile maxima visible; everyone agrees whether to go on
     if (!ok) break;
+    // S^T of this tile is complete, so nothing reads its K buffer any more: refill it for the tile two ahead
+    if (warp == 0 && i + DA_STAGES < ntiles) issue_half(i + DA_STAGES, true);
+
+    // ---- fold in the product issued two iterations ago (long since complete); that also frees the O^T and P^T
+    //      buffers this iteration is about to reuse
+    if (i > 1) ok = merge_tile(i - 2);
 
     // ---- p = exp(s - tile max), rounded to bf16 exactly as the tensor core will see it
     const int kc = tid >> 6, col = tid & 63;
-    uint8_t* p_col = sP + kc * (128 * 128) + (col & 7) * 2;
+    uint8_t* p_col = sP + par * S::P_BYTES + kc * (DA_MAXG * 128) + (col & 7) * 2;
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      const float mt = fmaxf(fmaxf(red_m[par][0][g], red_m[par][1][g]), fmaxf(red_m[par][2][g], red_m[par][3][g]));
-      const float p = (tid < valid) ? __expf(sc[g] - mt) : 0.f;
+      const float4 wmx = *reinterpret_cast<const float4*>(red_m[par][g]);
+      const float mt = fmaxf(fmaxf(wmx.x, wmx.y), fmaxf(wmx.z, wmx.w));
+      const float p = fast_exp2(sc[g] - mt);  // tokens past the end have sc = -inf -> p = 0
       const __nv_bfloat16 pb = __float2bfloat16(p);
       const float nm = fmaxf(m_thr[g], mt);  // the same for every thread of the CTA
-      const float keep = (m_thr[g] == -INFINITY) ? 0.f : __expf(m_thr[g] - nm);
-      l_thr[g] = l_thr[g] * keep + __bfloat162float(pb) * __expf(mt - nm);
+      const float keep = fast_exp2(m_thr[g] - nm);  // first tile: 2^(-inf) = 0
+      const float gain = fast_exp2(mt - nm);
+      l_thr[g] = l_thr[g] * keep + __bfloat162float(pb) * gain;
       m_thr[g] = nm;
+      if (par) {
+        keep1[g] = keep;
+        gain1[g] = gain;
+      } else {
+        keep0[g] = keep;
+        gain0[g] = gain;
+      }
       *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = pb;
     }
     if (valid < DA_TILE) {
       // Last tile: rows past the end of the sequence hold whatever the cache (or an older tile) left there.
       // Their p is 0, but 0 x NaN would poison O, so the V rows are cleared. Every thread observes the copy's
       // barrier first so that its plain stores are ordered after the TMA writes.
-      ok = mbar_wait(&full[s], (i / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL);
+      if (ok) ok = mbar_wait(&full_v[s], (i / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL);
       if (ok && tid >= valid) {
-        uint8_t* vrow = sKV + s * S::STAGE + S::KV_TILE + tid * 128;
+        uint8_t* vrow = sKV + s * S::STAGE + tid * 128;
 #pragma unroll
         for (int c = 0; c < NCH; ++c)
 #pragma unroll
@@ -242,51 +314,32 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
             reinterpret_cast<uint4*>(vrow + c * (DA_TILE * 128))[j] = make_uint4(0, 0, 0, 0);
       }
     }
-    fence_proxy_async();  // P (and cleared V rows) -> visible to the tensor core's async proxy
-    tc_fence_before();
+    fence_proxy_async();  // P^T (and cleared V rows) -> visible to the tensor core's async proxy
+    tc_fence_before();    // ... and this thread's TMEM reads (scores, previous O^T) are ordered before the next MMAs
     ok = __syncthreads_and(ok);  // (B)
     if (!ok) break;
 
     if (tid == 0) {
-      tc_fence_after();
-      issue_o_mma(i);
-      if (i + 1 < ntiles) {
-        if (mbar_wait(&full[(i + 1) % DA_STAGES], ((i + 1) / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL)) {
-          tc_fence_after();
-          issue_s_mma(i + 1);  // overlaps the merge below and the next tile's softmax
-        } else {
-          ok = false;
-        }
-      }
-    }
-    if (warp == 0) {
-      __syncwarp();
-      const bool okw = __all_sync(0xffffffffu, ok && mbar_wait(bar_o, i & 1, cta_abort, status, ERR_WAIT_TMEM_FULL));
-      tc_fence_after();
-      if (okw) {
-        const int gl = lane < G ? lane : 0;
-        const float mt = fmaxf(fmaxf(red_m[par][0][gl], red_m[par][1][gl]), fmaxf(red_m[par][2][gl], red_m[par][3][gl]));
-        const float nm = fmaxf(m_run, mt);
-        const float a = (m_run == -INFINITY) ? 0.f : __expf(m_run - nm);
-        const float bcf = __expf(mt - nm);
-        m_run = nm;
-#pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_o + c * 32, r);  // warp 0 owns TMEM lanes 0..31 = O rows (heads) 0..31
-          tmem_ld_wait();
-#pragma unroll
-          for (int d = 0; d < 32; ++d) acc[c * 32 + d] = acc[c * 32 + d] * a + __uint_as_float(r[d]) * bcf;
-        }
-        tc_fence_before();
+      if (mbar_wait(&full_v[s], (i / DA_STAGES) & 1, cta_abort, status, ERR_WAIT_FULL)) {
+        tc_fence_after();
+        issue_o_mma(i);
       } else {
         ok = false;
       }
-      __syncwarp();
-      // the stage of tile i is free now (its V was read by the MMA that bar_o tracks): refill it
-      if (okw && i + DA_STAGES < ntiles) issue_tile(i + DA_STAGES);
+    }
+    __syncwarp();
+    // V^T·P^T of the previous tile was issued a whole iteration ago: once it is done its V buffer takes the tile two
+    // ahead (the wait is a pure test of the phase; the merge of that tile tests the same phase again later)
+    if (warp == 0 && i >= 1 && i + 2 < ntiles) {
+      if (mbar_wait(&bar_o[(i - 1) & 1], ((i - 1) >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL))
+        issue_half(i + 2, false);
+      else
+        ok = false;
     }
   }
+  ok = __syncthreads_and(ok);  // one decision for the whole CTA: the merges below contain warp-collective steps
+  if (ok && ntiles > 1) ok = merge_tile(ntiles - 2);
+  if (ok && ntiles > 0) ok = merge_tile(ntiles - 1);
 
   // ---- denominators: one block reduction per head (all l_thr[g] refer to the same final maximum)
 #pragma unroll
@@ -294,31 +347,24 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     const float ws = warp_sum(l_thr[g]);
     if (lane == 0) red_l[warp][g] = ws;
   }
-  // ---- output: lane g of warp 0 owns head kvh*G + g
   const bool all_ok = __syncthreads_and(ok) && (*cta_abort == 0);
-  const int g_out = lane < G ? lane : 0;
-  const float l_run = red_l[0][g_out] + red_l[1][g_out] + red_l[2][g_out] + red_l[3][g_out];
-  if (all_ok && warp == 0 && lane < G) {
-    const int h = kvh * G + lane;
-    if (splits == 1) {
-      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* o = out + static_cast<size_t>(b) * out_stride + static_cast<size_t>(h) * D;
+  // ---- output: thread d writes dim d of each head (consecutive threads -> consecutive addresses)
+  if (all_ok && merges) {
 #pragma unroll
-      for (int d = 0; d < D; d += 8) {
-        uint4 u;
-        u.x = pack_bf16x2(acc[d] * inv, acc[d + 1] * inv);
-        u.y = pack_bf16x2(acc[d + 2] * inv, acc[d + 3] * inv);
-        u.z = pack_bf16x2(acc[d + 4] * inv, acc[d + 5] * inv);
-        u.w = pack_bf16x2(acc[d + 6] * inv, acc[d + 7] * inv);
-        *reinterpret_cast<uint4*>(o + d) = u;
+    for (int g = 0; g < G; ++g) {
+      const float l_run = red_l[0][g] + red_l[1][g] + red_l[2][g] + red_l[3][g];
+      const int h = kvh * G + g;
+      if (splits == 1) {
+        const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+        out[static_cast<size_t>(b) * out_stride + static_cast<size_t>(h) * D + tid] = __float2bfloat16(acc[g] * inv);
+      } else {
+        const size_t base = (static_cast<size_t>(b) * Hq + h) * splits + sp;
+        part_o[base * D + tid] = acc[g];
+        if (tid == 0) {
+          part_ml[base * 2 + 0] = m_thr[g] * 0.6931471805599453f;  // back to the natural-log domain
+          part_ml[base * 2 + 1] = l_run;
+        }
       }
-    } else {
-      const size_t base = (static_cast<size_t>(b) * Hq + h) * splits + sp;
-      float4* po = reinterpret_cast<float4*>(part_o + base * D);
-#pragma unroll
-      for (int d = 0; d < D; d += 4) po[d / 4] = make_float4(acc[d], acc[d + 1], acc[d + 2], acc[d + 3]);
-      part_ml[base * 2 + 0] = m_run;
-      part_ml[base * 2 + 1] = l_run;
     }
   }
 
