@@ -11,7 +11,7 @@ Backends:
                     calls are retried with jittered exponential back-off; a call marked non-idempotent is never
                     replayed, because a severed response does not say whether the command ran.
 
-``exec_and_wait`` runs a long command *detached*: it writes a launcher script, starts it under ``setsid`` with output
+``exec_and_wait`` runs a long command *detached*: it writes a launcher script (the command in a subshell, so even an ``exit`` inside it still leaves the marker), starts it under ``setsid`` with output
 redirected to a file, and polls for an exit-code marker. Every remote call it makes is short and idempotent, so no
 single response stream has to outlive the command, and the polling keeps an idle-collected sandbox alive.
 Parity: slime/agent/sandbox.py:28-399.
@@ -81,7 +81,7 @@ async def exec_and_wait(sb: Sandbox, *, cmd: str, time_budget_sec: float, tag: s
     head = f"cd {shlex.quote(workdir)}\n" if workdir else ""
     if workdir and user != "root":
         head += f"export HOME=/home/{user}\n"
-    await sb.write_file(launcher, f"#!/bin/bash\n{head}{cmd}\necho $? > {done}\n", user=user)
+    await sb.write_file(launcher, f"#!/bin/bash\n{head}(\n{cmd}\n)\necho $? > {done}\n", user=user)
     await sb.exec(f"rm -rf {lock}; rm -f {out_file} {done}", user=user, timeout=30, check=True)
     await sb.exec(f"chmod +x {launcher}; mkdir {lock} 2>/dev/null || exit 0; "
                   f"setsid bash {launcher} < /dev/null > {out_file} 2>&1 &",
