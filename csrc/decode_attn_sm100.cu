@@ -10,8 +10,8 @@
 //     tcgen05  O^T[128(D used), 16] = V^T · P^T     A = V tile read MN-major, B = P^T (K-major)
 //     threads  one output dim per thread: tcgen05.ld its 16 values, online-softmax merge into registers
 //
-//   S^T, P^T and O^T are double-buffered: K·Q^T of tile i+1 and V^T·P^T of tile i-1 run underneath the softmax of tile i,
-//   and tile i-2 is merged meanwhile, so the tensor pipe's latency is off the critical path; three
+//   S^T and P^T are double-buffered: K·Q^T of tile i+1 is issued before the softmax of tile i starts and V^T·P^T of
+//   tile i-1 is merged underneath it, so the tensor pipe's latency is off the critical path; three
 //   smem stages keep the next tiles' K/V in flight; ~107 KB of smem and 128 TMEM columns per CTA let two CTAs share
 //   an SM (D = 64). For D = 64 the V^T operand needs 128 rows: its upper half is pointed at the K tile that follows V in the
 //   stage; those 64 accumulator rows are never read.
@@ -74,7 +74,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* full_v = full_k + DA_STAGES;
   uint64_t* bar_s = full_v + DA_STAGES;
   uint64_t* bar_o = bar_s + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 2);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar_o + 1);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   __shared__ __align__(16) float red_m[2][DA_MAXG][4];  // [S buffer][head][warp]: one 16-byte read per head
   __shared__ float red_l[4][DA_MAXG];
@@ -91,8 +91,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     }
     mbar_init(&bar_s[0], 1);
     mbar_init(&bar_s[1], 1);
-    mbar_init(&bar_o[0], 1);
-    mbar_init(&bar_o[1], 1);
+    mbar_init(bar_o, 1);
     *cta_abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tmK);
@@ -131,7 +130,7 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 64;  // O^T buffer (i & 1) at +0 / +32
+  const uint32_t tmem_o = tmem_base + 64;
 
   // warp 0, all lanes: start the copies of the K (or V) half of tile i. Lane p fetches the block-table entry of page p
   // and issues that page's boxes (one per 64-wide chunk of the head dim), so the table reads overlap. K and V have
@@ -180,10 +179,10 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     for (int kc = 0; kc < 2; ++kc)
 #pragma unroll
       for (int k = 0; k < 4; ++k)
-        umma_f16(tmem_o + (i & 1) * 32, make_smem_desc(v_addr + (kc * 4 + k) * 2048, DA_TILE * 128, 1024, UMMA_SWIZZLE_128B),
+        umma_f16(tmem_o, make_smem_desc(v_addr + (kc * 4 + k) * 2048, DA_TILE * 128, 1024, UMMA_SWIZZLE_128B),
                  make_smem_desc(p_addr + kc * (DA_MAXG * 128) + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc,
                  (kc | k) != 0 ? 1u : 0u);
-    umma_commit(&bar_o[i & 1]);
+    umma_commit(bar_o);
   };
 
   bool ok = true;
@@ -204,32 +203,31 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
 
   // Running softmax state. Thread d (< D) owns output dim d of all G heads. The denominator is kept per thread (each
   // thread sums the p of its own tokens, rescaled like the accumulator) and reduced once at the end. `keep`/`gain`
-  // are the factors a tile's merge applies: acc = acc * keep + o_tile * gain. A tile is merged two iterations after
-  // its softmax (so that the tensor pipe's issue-to-completion latency never stalls the loop), hence two sets.
-  float acc[G], m_thr[G], l_thr[G], keep0[G], gain0[G], keep1[G], gain1[G];
+  // are the factors a tile's merge applies: acc = acc * keep + o_tile * gain. A tile is merged one iteration after
+  // its softmax, underneath the next tile's, so the tensor pipe's latency stays off the critical path.
+  float acc[G], m_thr[G], l_thr[G], keep_prev[G], gain_prev[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     acc[g] = 0.f;
     m_thr[g] = -INFINITY;
     l_thr[g] = 0.f;
-    keep0[g] = keep1[g] = 1.f;
-    gain0[g] = gain1[g] = 0.f;
+    keep_prev[g] = 1.f;
+    gain_prev[g] = 0.f;
   }
   const bool merges = tid < D;  // warp-uniform: D is 64 or 128
-  // merge tile j (its O^T buffer (j & 1) is ready once that buffer's barrier completes phase j / 2)
+  // merge tile j (O^T is ready once bar_o completes phase j); its V buffer is then free for tile j + DA_STAGES
   auto merge_tile = [&](int j) -> bool {
-    bool okm = mbar_wait(&bar_o[j & 1], (j >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
+    bool okm = mbar_wait(bar_o, j & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
     okm = __all_sync(0xffffffffu, okm);
     tc_fence_after();
     if (okm && merges) {
       uint32_t r[32];
-      tmem_ld_32x32(tmem_o + (j & 1) * 32 + (static_cast<uint32_t>(warp * 32) << 16), r);
+      tmem_ld_32x32(tmem_o + (static_cast<uint32_t>(warp * 32) << 16), r);
       tmem_ld_wait();
-      const bool odd = (j & 1) != 0;
 #pragma unroll
-      for (int g = 0; g < G; ++g)
-        acc[g] = acc[g] * (odd ? keep1[g] : keep0[g]) + __uint_as_float(r[g]) * (odd ? gain1[g] : gain0[g]);
+      for (int g = 0; g < G; ++g) acc[g] = acc[g] * keep_prev[g] + __uint_as_float(r[g]) * gain_prev[g];
     }
+    if (okm && warp == 0 && j + DA_STAGES < ntiles) issue_half(j + DA_STAGES, false);
     return okm;
   };
 
@@ -273,9 +271,9 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     // S^T of this tile is complete, so nothing reads its K buffer any more: refill it for the tile two ahead
     if (warp == 0 && i + DA_STAGES < ntiles) issue_half(i + DA_STAGES, true);
 
-    // ---- fold in the product issued two iterations ago (long since complete); that also frees the O^T and P^T
-    //      buffers this iteration is about to reuse
-    if (i > 1) ok = merge_tile(i - 2);
+    // ---- the previous tile's product is done by now (it was issued before this tile's scores were read): fold it
+    //      in, which also frees O^T and the P^T buffer of two tiles ago for reuse below
+    if (i > 0) ok = merge_tile(i - 1);
 
     // ---- p = exp(s - tile max), rounded to bf16 exactly as the tensor core will see it
     const int kc = tid >> 6, col = tid & 63;
@@ -285,19 +283,14 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const float4 wmx = *reinterpret_cast<const float4*>(red_m[par][g]);
       const float mt = fmaxf(fmaxf(wmx.x, wmx.y), fmaxf(wmx.z, wmx.w));
       const float p = fast_exp2(sc[g] - mt);  // tokens past the end have sc = -inf -> p = 0
-      const __nv_bfloat16 pb = __float2bfloat16(p);
+      const __nv_bfloat16 pb = __float2bfloat16(p);  // the denominator sums the unrounded p (rounding is unbiased)
       const float nm = fmaxf(m_thr[g], mt);  // the same for every thread of the CTA
       const float keep = fast_exp2(m_thr[g] - nm);  // first tile: 2^(-inf) = 0
       const float gain = fast_exp2(mt - nm);
-      l_thr[g] = l_thr[g] * keep + __bfloat162float(pb) * gain;
+      l_thr[g] = l_thr[g] * keep + p * gain;
       m_thr[g] = nm;
-      if (par) {
-        keep1[g] = keep;
-        gain1[g] = gain;
-      } else {
-        keep0[g] = keep;
-        gain0[g] = gain;
-      }
+      keep_prev[g] = keep;
+      gain_prev[g] = gain;
       *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = pb;
     }
     if (valid < DA_TILE) {
@@ -328,17 +321,8 @@ decode_attn_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
     __syncwarp();
-    // V^T·P^T of the previous tile was issued a whole iteration ago: once it is done its V buffer takes the tile two
-    // ahead (the wait is a pure test of the phase; the merge of that tile tests the same phase again later)
-    if (warp == 0 && i >= 1 && i + 2 < ntiles) {
-      if (mbar_wait(&bar_o[(i - 1) & 1], ((i - 1) >> 1) & 1, cta_abort, status, ERR_WAIT_TMEM_FULL))
-        issue_half(i + 2, false);
-      else
-        ok = false;
-    }
   }
   ok = __syncthreads_and(ok);  // one decision for the whole CTA: the merges below contain warp-collective steps
-  if (ok && ntiles > 1) ok = merge_tile(ntiles - 2);
   if (ok && ntiles > 0) ok = merge_tile(ntiles - 1);
 
   // ---- denominators: one block reduction per head (all l_thr[g] refer to the same final maximum)

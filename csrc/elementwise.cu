@@ -20,6 +20,11 @@ __device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
   f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
 }
 
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y), c = unpack_bf16x2(u.z), d = unpack_bf16x2(u.w);
+  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
+
 __device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
   uint4 u;
   u.x = pack_bf16x2(f[0], f[1]);
@@ -157,6 +162,106 @@ __global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ part, float* 
   float s = 0.f;
   for (int p = 0; p < P; ++p) s += part[static_cast<size_t>(p) * H + c];
   dw[c] = accumulate ? dw[c] + s : s;
+}
+
+// Same backward for rows of at most 1024 elements: one WARP per row, so a row costs one shuffle reduction and no
+// block barrier, and every warp keeps 2 * VPL independent 16-byte loads in flight. Lane l owns the 8-element
+// vectors l, l + 32, ... (VPL of them). The per-column dw sums of the CTA's 8 warps are combined in shared memory in
+// warp order (deterministic) and written as one partial row per CTA.
+template <int VPL>
+__global__ void __launch_bounds__(NORM_THREADS, 2)
+rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
+                        const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd,
+                        const __nv_bfloat16* __restrict__ dres_in, __nv_bfloat16* __restrict__ dh,
+                        float* __restrict__ dw_partial, int T, int H) {
+  constexpr int WARPS = NORM_THREADS / 32;
+  __shared__ float dw_sh[32 * VPL * 8];
+  const int nvec = H >> 3, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float inv_h = 1.f / static_cast<float>(H);
+  uint4 gw[VPL];  // the weight stays packed (4 registers per vector) and is unpacked where it is used
+  float dwacc[VPL][8];
+#pragma unroll
+  for (int j = 0; j < VPL; ++j) {
+    const int c = lane + 32 * j;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) dwacc[j][i] = 0.f;
+    gw[j] = c < nvec ? *reinterpret_cast<const uint4*>(w + c * 8) : make_uint4(0, 0, 0, 0);
+  }
+  for (size_t row = static_cast<size_t>(blockIdx.x) * WARPS + warp; row < static_cast<size_t>(T);
+       row += static_cast<size_t>(gridDim.x) * WARPS) {
+    const float rs = rstd[row];
+    uint4 ra[VPL], rb[VPL];
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {  // all loads of the row first
+      const int c = lane + 32 * j;
+      ra[j] = rb[j] = make_uint4(0, 0, 0, 0);
+      if (c < nvec) {
+        ra[j] = *reinterpret_cast<const uint4*>(dy + row * H + c * 8);
+        rb[j] = *reinterpret_cast<const uint4*>(h + row * H + c * 8);
+      }
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      float a[8], b[8], g[8];
+      unpack8(ra[j], a);
+      unpack8(rb[j], b);
+      unpack8(gw[j], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = b[i] * rs;
+        dwacc[j][i] += a[i] * xh;
+        dot += a[i] * g[i] * xh;
+      }
+    }
+    dot = warp_sum(dot) * inv_h;
+#pragma unroll
+    for (int j = 0; j < VPL; ++j) {
+      const int c = lane + 32 * j;
+      if (c < nvec) {
+        float a[8], b[8], r[8], g[8], o[8];
+        unpack8(ra[j], a);
+        unpack8(rb[j], b);
+        unpack8(dres_in != nullptr ? *reinterpret_cast<const uint4*>(dres_in + row * H + c * 8) : make_uint4(0, 0, 0, 0), r);
+        unpack8(gw[j], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = rs * (a[i] * g[i] - b[i] * rs * dot) + r[i];
+        store8(dh + row * H + c * 8, o);
+      }
+    }
+  }
+  for (int turn = 0; turn < WARPS; ++turn) {
+    if (warp == turn) {
+#pragma unroll
+      for (int j = 0; j < VPL; ++j)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float* slot = &dw_sh[(lane + 32 * j) * 8 + i];
+          *slot = turn == 0 ? dwacc[j][i] : *slot + dwacc[j][i];
+        }
+    }
+    __syncthreads();
+  }
+  for (int c = threadIdx.x; c < H; c += NORM_THREADS) dw_partial[static_cast<size_t>(blockIdx.x) * H + c] = dw_sh[c];
+}
+
+// Both backward entry points launch through here: the warp-per-row kernel up to H = 1024, the block-per-row
+// kernel above that, then the reduction of the per-CTA dw partials.
+static cudaError_t launch_rmsnorm_bwd(const __nv_bfloat16* dy, const __nv_bfloat16* h, const __nv_bfloat16* w,
+                                      const float* rstd, const __nv_bfloat16* dres_in, __nv_bfloat16* dh,
+                                      float* dw_partial, float* dw, int T, int H, int num_ctas, int accumulate_dw,
+                                      cudaStream_t s) {
+  const int nvec = H >> 3;
+  if (nvec <= 32)
+    rmsnorm_bwd_warp_kernel<1><<<num_ctas, NORM_THREADS, 0, s>>>(dy, h, w, rstd, dres_in, dh, dw_partial, T, H);
+  else if (nvec <= 64)
+    rmsnorm_bwd_warp_kernel<2><<<num_ctas, NORM_THREADS, 0, s>>>(dy, h, w, rstd, dres_in, dh, dw_partial, T, H);
+  else if (nvec <= 128)
+    rmsnorm_bwd_warp_kernel<4><<<num_ctas, NORM_THREADS, 0, s>>>(dy, h, w, rstd, dres_in, dh, dw_partial, T, H);
+  else
+    rmsnorm_bwd_kernel<<<num_ctas, NORM_THREADS, 0, s>>>(dy, h, w, rstd, dres_in, dh, dw_partial, T, H);
+  rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, dw, num_ctas, H, accumulate_dw);
+  return cudaGetLastError();
 }
 
 // ---------------------------------------------------------------- QK-norm + RoPE
@@ -319,10 +424,8 @@ extern "C" int sb_rmsnorm_bwd(const void* dy, const void* h, const void* w, cons
                               cudaStream_t s) {
   if (T == 0) return 0;
   if (H % 8 != 0 || H > sb::NORM_THREADS * sb::NORM_MAX_VEC * 8) return (int)cudaErrorInvalidValue;
-  sb::rmsnorm_bwd_kernel<<<num_ctas, sb::NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
-                                                               (const bf16*)dres_in, (bf16*)dh, dw_partial, T, H);
-  sb::rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(dw_partial, dw, num_ctas, H, accumulate_dw);
-  return (int)cudaGetLastError();
+  return (int)sb::launch_rmsnorm_bwd((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd, (const bf16*)dres_in,
+                                     (bf16*)dh, dw_partial, dw, T, H, num_ctas, accumulate_dw, s);
 }
 
 extern "C" int sb_rope(const void* x, void* out, const int* pos, const float* cos_sin, const void* nw, float* rstd,
@@ -389,7 +492,7 @@ extern "C" int sb_add_bf16(const void* a, const void* b, void* out, long n, cuda
 
 // ------------------------------------------------------------------------------------------------------------
 // RMSNorm backward with library-owned scratch (see rmsnorm_bwd_static.h for the contract). Nothing above this
-// line is changed by it; it launches the same two kernels as sb_rmsnorm_bwd with `dw_partial` pointing into the
+// line is changed by it; it goes through the same launcher as sb_rmsnorm_bwd with `dw_partial` pointing into the
 // array below.
 #include <atomic>
 #include <cstdio>
@@ -463,10 +566,8 @@ extern "C" int sb_rmsnorm_bwd_static(const void* dy, const void* h, const void* 
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
   const int num_ctas = T < SB_RMSNORM_STATIC_MAX_CTAS ? T : SB_RMSNORM_STATIC_MAX_CTAS;
   // Rows of the scratch are packed with pitch H (not MAX_H), exactly like the caller-supplied buffer of sb_rmsnorm_bwd.
-  sb::rmsnorm_bwd_kernel<<<num_ctas, sb::NORM_THREADS, 0, s>>>((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd,
-                                                               (const bf16*)dres_in, (bf16*)dh, scratch, T, H);
-  sb::rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, dw, num_ctas, H, accumulate_dw);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = sb::launch_rmsnorm_bwd((const bf16*)dy, (const bf16*)h, (const bf16*)w, rstd, (const bf16*)dres_in,
+                                         (bf16*)dh, scratch, dw, T, H, num_ctas, accumulate_dw, s);
   if (e != cudaSuccess) static_fail("sb_rmsnorm_bwd_static: launch failed: %s", cudaGetErrorString(e));
   return (int)e;
 }

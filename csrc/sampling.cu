@@ -3,8 +3,9 @@
 // seed, log-prob of the sampled token (renormalised over the kept set when the
 // nucleus is active) and optional emission of the kept-id set for top-p replay.
 //
-// One CTA per request row. Without top-k/top-p the kernel is a single pass over the
-// logits row (online softmax + perturbed arg-max). With a nucleus, the exact cut-off
+// One CTA per request row. Without top-k/top-p the kernel is a single vectorised pass over the
+// logits row (online softmax) followed by a two-stage inverse-CDF draw that uses two uniforms per
+// row and re-reads only one thread's share of the row. With a nucleus, the exact cut-off
 // probability is found by a 4-level radix select over the fp32 bit pattern of p
 // (histograms of mass and count per 8-bit digit), then one more pass draws the token.
 #include "common.cuh"
@@ -78,6 +79,40 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax x, ArgMax* sh) {
   return sh[0];
 }
 
+// Inclusive prefix sum over the block in thread order. `sh` holds >= 32 floats; all threads must call.
+__device__ __forceinline__ float block_scan_incl(float v, float* sh) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  __syncthreads();
+  if (lane == 31) sh[wid] = v;
+  __syncthreads();
+  if (wid == 0) {
+    float w = lane < SAMPLE_THREADS / 32 ? sh[lane] : 0.f;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w += t;
+    }
+    sh[lane] = w;
+  }
+  __syncthreads();
+  return v + (wid > 0 ? sh[wid - 1] : 0.f);
+}
+
+__device__ __forceinline__ int block_min_int(int v, int* sh) {
+  v = __reduce_min_sync(0xffffffffu, v);
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) sh[wid] = v;
+  __syncthreads();
+  int r = lane < SAMPLE_THREADS / 32 ? sh[lane] : 0x7fffffff;
+  return __reduce_min_sync(0xffffffffu, r);
+}
+
 // logits [B, V] (fp32 or bf16). Per row parameters in arrays of length B.
 //   temperature (>0; <=0 means greedy), top_k (<=0: off), top_p (>=1: off), min_p (<=0: off)
 //   seeds[b], positions[b] (decode step index of the request: advances the random stream)
@@ -96,6 +131,8 @@ sample_kernel(const T* __restrict__ logits, size_t ld, int V, const float* __res
   __shared__ float s_mass_above;
   __shared__ int s_cnt_above;
   __shared__ int s_kept;
+  __shared__ float scan_sh[33];
+  __shared__ int red_i[32];
 
   pdl_wait();  // inputs come from the previous kernel in the stream
   pdl_launch_dependents();
@@ -111,42 +148,149 @@ sample_kernel(const T* __restrict__ logits, size_t ld, int V, const float* __res
   const uint64_t seed = seeds != nullptr ? seeds[b] : 0x1234ull + b;
   const uint32_t pos = positions != nullptr ? static_cast<uint32_t>(positions[b]) : 0u;
 
-  // ---- pass 1: online max / sum-exp, and (unfiltered) the Gumbel-perturbed arg-max
+  // Four consecutive logits (scaled by 1/T) starting at `base` (a multiple of 4): one vector load when the row
+  // is aligned for it, scalar loads with -inf past the end otherwise.
+  const bool vec_ok = (ld % 4 == 0) && (reinterpret_cast<uintptr_t>(logits) % (4 * sizeof(T)) == 0);
+  auto load4 = [&](int base, float (&z)[4]) {
+    if (vec_ok && base + 4 <= V) {
+      if constexpr (sizeof(T) == 4) {
+        const float4 v = *reinterpret_cast<const float4*>(row + base);
+        z[0] = v.x; z[1] = v.y; z[2] = v.z; z[3] = v.w;
+      } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(row + base);
+        z[0] = __uint_as_float(v.x << 16); z[1] = __uint_as_float(v.x & 0xffff0000u);
+        z[2] = __uint_as_float(v.y << 16); z[3] = __uint_as_float(v.y & 0xffff0000u);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z[i] *= inv_t;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z[i] = (base + i < V) ? to_float(row[base + i]) * inv_t : -INFINITY;
+    }
+  };
+
+  // ---- pass 1: online max / sum-exp per thread (one rescale per group of four), greedy arg-max on the way
   float mx = -INFINITY, se = 0.f;
   ArgMax best{-INFINITY, 0x7fffffff};
-  for (int base = threadIdx.x * 4; base < V; base += SAMPLE_THREADS * 4) {
-    uint32_t rnd[4] = {0, 0, 0, 0};
-    if (!greedy && !filtered) philox4(seed, pos, static_cast<uint32_t>(base >> 2), rnd);
+  constexpr int UNROLL = 4;  // groups whose loads are issued together, so each thread keeps 64 bytes in flight
+  for (int base0 = threadIdx.x * 4; base0 < V; base0 += SAMPLE_THREADS * 4 * UNROLL) {
+    float z[UNROLL][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int c = base + i;
-      if (c < V) {
-        const float z = to_float(row[c]) * inv_t;
-        if (z > mx) {
-          se *= __expf(mx - z);
-          mx = z;
-        }
-        se += __expf(z - mx);
-        if (!filtered) {
-          const float score = greedy ? z : z + gumbel_from_bits(rnd[i]);
-          best = argmax_combine(best, ArgMax{score, c});
-        }
+    for (int u = 0; u < UNROLL; ++u) {
+      const int base = base0 + u * SAMPLE_THREADS * 4;
+      if (base < V) {
+        load4(base, z[u]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) z[u][i] = -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int base = base0 + u * SAMPLE_THREADS * 4;
+      const float m4 = fmaxf(fmaxf(z[u][0], z[u][1]), fmaxf(z[u][2], z[u][3]));
+      if (m4 == -INFINITY) continue;  // fully masked (or past the end)
+      if (m4 > mx) {
+        se *= __expf(mx - m4);
+        mx = m4;
+      }
+      se += (__expf(z[u][0] - mx) + __expf(z[u][1] - mx)) + (__expf(z[u][2] - mx) + __expf(z[u][3] - mx));
+      if (greedy) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) best = argmax_combine(best, ArgMax{z[u][i], base + i});
       }
     }
   }
   const float gmx = block_max<SAMPLE_THREADS>(mx, scratch);
-  const float gse = block_sum<SAMPLE_THREADS>(mx == -INFINITY ? 0.f : se * __expf(mx - gmx), scratch);
+  const float my_mass = mx == -INFINITY ? 0.f : se * __expf(mx - gmx);  // this thread's share, relative to exp(gmx)
+  const float gse = block_sum<SAMPLE_THREADS>(my_mass, scratch);
   const float lse = __logf(gse) + gmx;
 
-  if (!filtered) {
+  if (greedy) {
     const ArgMax w = block_argmax(best, am);
     if (threadIdx.x == 0) {
       token[b] = w.i;
-      logprob[b] = to_float(row[w.i]) * inv_t - lse;  // greedy: inv_t == 1, log-prob under the unscaled distribution
+      logprob[b] = to_float(row[w.i]) - lse;  // inv_t == 1: log-prob under the unscaled distribution
       if (kept_count != nullptr) {
-        kept_count[b] = greedy ? 1 : 0;  // 0 = "whole vocabulary kept"
-        if (greedy && kept_ids != nullptr && kept_cap > 0) kept_ids[static_cast<size_t>(b) * kept_cap] = w.i;
+        kept_count[b] = 1;
+        if (kept_ids != nullptr && kept_cap > 0) kept_ids[static_cast<size_t>(b) * kept_cap] = w.i;
       }
+    }
+    return;
+  }
+
+  if (!filtered) {
+    // ---- two-stage inverse-CDF draw with two uniforms per row: first the thread whose share of the mass contains
+    //      u1 * total, then, inside that thread's strided set of groups, the group and element containing u2 * share.
+    //      Only the chosen thread's groups (V / 2048 of them) are read again.
+    uint32_t rnd[4];
+    philox4(seed, pos, 0u, rnd);
+    const float u1 = (static_cast<float>(rnd[0] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float u2 = (static_cast<float>(rnd[1] >> 8) + 0.5f) * (1.0f / 16777216.0f);
+    const float incl = block_scan_incl(my_mass, scan_sh);
+    // first thread whose inclusive sum reaches the target; rounding can leave none: then the last thread with mass
+    const float target = u1 * gse;
+    int cand = (my_mass > 0.f && incl >= target) ? static_cast<int>(threadIdx.x) : 0x7fffffff;
+    int last = my_mass > 0.f ? static_cast<int>(threadIdx.x) : -1;
+    cand = block_min_int(cand, red_i);
+    last = -block_min_int(-last, red_i);
+    const int owner = max(cand != 0x7fffffff ? cand : last, 0);
+    // stage 2: thread j handles group j of the owner's set (element base = owner * 4 + j * THREADS * 4)
+    float carry = 0.f;  // mass of the groups before this round of SAMPLE_THREADS groups
+    int found = 0x7fffffff;
+    float found_excl = 0.f;
+    int last_group = -1;
+    const int ngroups = (V - owner * 4 + SAMPLE_THREADS * 4 - 1) / (SAMPLE_THREADS * 4);
+    // share of the owner, recomputed relative to exp(gmx) in the same order the scan below adds it up
+    float share = 0.f;
+    for (int j0 = 0; j0 < ngroups; j0 += SAMPLE_THREADS) {
+      const int j = j0 + threadIdx.x;
+      float z[4], c = 0.f;
+      if (j < ngroups) {
+        load4(owner * 4 + j * SAMPLE_THREADS * 4, z);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c += __expf(z[i] - gmx);
+      }
+      share += block_sum<SAMPLE_THREADS>(c, scratch);
+    }
+    const float target2 = u2 * share;
+    for (int j0 = 0; j0 < ngroups && found == 0x7fffffff; j0 += SAMPLE_THREADS) {
+      const int j = j0 + threadIdx.x;
+      float z[4], c = 0.f;
+      if (j < ngroups) {
+        load4(owner * 4 + j * SAMPLE_THREADS * 4, z);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c += __expf(z[i] - gmx);
+      }
+      const float inc2 = carry + block_scan_incl(c, scan_sh);
+      const int hit = (c > 0.f && inc2 >= target2) ? j : 0x7fffffff;
+      const int lg = c > 0.f ? j : -1;
+      found = block_min_int(hit, red_i);
+      last_group = max(last_group, -block_min_int(-lg, red_i));
+      if (found == j) scan_sh[32] = inc2 - c;  // exclusive sum at the chosen group
+      __syncthreads();
+      if (found != 0x7fffffff) found_excl = scan_sh[32];
+      carry += block_sum<SAMPLE_THREADS>(c, scratch);
+    }
+    if (threadIdx.x == 0) {
+      const bool exact = found != 0x7fffffff;
+      const int g = exact ? found : last_group;
+      const int base = owner * 4 + g * SAMPLE_THREADS * 4;
+      float z[4];
+      load4(base, z);
+      int pick = -1, last_ok = 0;
+      float run = exact ? found_excl : 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float e = __expf(z[i] - gmx);
+        if (e > 0.f) last_ok = i;
+        run += e;
+        if (pick < 0 && exact && e > 0.f && run >= target2) pick = i;
+      }
+      if (pick < 0) pick = last_ok;
+      token[b] = base + pick;
+      logprob[b] = z[pick] - lse;
+      if (kept_count != nullptr) kept_count[b] = 0;  // 0 = "whole vocabulary kept"
     }
     return;
   }

@@ -179,7 +179,7 @@ def bench_decode(a):
 
 # ------------------------------------------------------------------------------------ norm
 def bench_norm(a):
-    for T, H in ((16384, 896), (16384, 4096), (65536, 2560)) if not a.small else ((4096, 4096),):
+    for T, H in ((131072, 896), (1048576, 128), (16384, 4096), (65536, 2560)) if not a.small else ((4096, 4096),):
         x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
         w = torch.ones(H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
