@@ -483,6 +483,14 @@ class RolloutManager:
             for r in refs:
                 object_store.free(r.inner)
         logging_utils.finish_tracking(self.args)
+        # per-process rollout state (router address, semaphores, pending tasks) belongs to this manager's args: a
+        # manager created later in the same process must not inherit it
+        try:
+            from slime_b200.rollout.sglang_rollout import GenerateState
+
+            GenerateState.clear_instances()
+        except Exception:  # noqa: BLE001
+            pass
 
 
 actors.remote(RolloutManager)
