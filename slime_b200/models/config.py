@@ -207,8 +207,21 @@ PRESETS: dict[str, dict] = {
 }  # fmt: skip
 
 
+def _register_more_presets() -> None:
+    from slime_b200.models import presets as more
+
+    for k, v in more.MORE_PRESETS.items():
+        PRESETS.setdefault(k, v)
+
+
 def get_preset(name: str) -> ModelConfig:
+    from slime_b200.models import presets as more
+
+    _register_more_presets()
     key = name.lower()
+    key = more.ALIASES.get(key, key)
+    if key in more.UNSUPPORTED:
+        raise KeyError(f"model preset {name!r} is not supported: {more.UNSUPPORTED[key]}")
     if key not in PRESETS:
         raise KeyError(f"unknown model preset {name!r}; known: {sorted(PRESETS)}")
     return ModelConfig(**PRESETS[key])

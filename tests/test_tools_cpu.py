@@ -98,3 +98,31 @@ def test_int4_direct_conversion(tmp_path):
     assert (deq - w).abs().max() <= w.abs().max() / 7 * 0.51 + 1e-3  # half a quantisation step of the largest group
     cfg = json.load(open(os.path.join(out, "config.json")))["quantization_config"]
     assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["group_size"] == 32
+
+
+def test_model_presets_round_trip_through_flags():
+    """Every supported preset, printed as flags and parsed back, gives the same architecture."""
+    import dataclasses
+
+    from slime_b200.models import presets
+    from slime_b200.models.config import PRESETS, ModelConfig, _register_more_presets, get_preset
+    from slime_b200.utils.arguments import parse_args
+
+    _register_more_presets()
+    assert {"qwen2.5-7b", "qwen3-14b", "qwen3-235b-a22b", "llama3.1-8b-instruct", "mimo-7b-rl"} <= set(PRESETS)
+    for name in sorted(PRESETS):
+        cfg = get_preset(name)
+        args = parse_args(presets.to_flags(cfg) + ["--rollout-batch-size", "1", "--num-rollout", "1", "--debug-train-only"])
+        back = ModelConfig.from_args(args)
+        for f in dataclasses.fields(ModelConfig):
+            if f.name in ("model_arch", "padded_vocab_size", "init_method_std"):
+                continue
+            a, b = getattr(cfg, f.name), getattr(back, f.name)
+            if f.name == "moe_layer_freq" and a is not None:
+                a, b = list(a), list(b) if not isinstance(b, int) else b
+            assert a == b, (name, f.name, a, b)
+    import pytest
+
+    with pytest.raises(KeyError, match="MLA"):
+        get_preset("kimi-k2")
+    assert get_preset("qwen3-235b-a22b").num_params() > 2.3e11
