@@ -123,6 +123,87 @@ class EngineServer:
         out = [self._render(r) for r in reqs]
         return web.json_response(out if batched else out[0])
 
+    # ---------------------------------------------------------------- OpenAI-compatible front end
+    async def _run_one(self, ids: list[int], sampling: dict, rid=None):
+        """Submit one request and wait for it (shared by the chat and completion endpoints)."""
+        loop = asyncio.get_running_loop()
+        ev = asyncio.Event()
+
+        class _Done:
+            def set(self_inner):
+                loop.call_soon_threadsafe(ev.set)
+
+        req = self.engine.add_request(ids, SamplingParams.from_dict(sampling), rid=rid, return_logprob=False, done_event=_Done())
+        if req.finished():
+            ev.set()
+        self._wake.set()
+        await ev.wait()
+        self.num_generated += len(req.output_ids)
+        return req
+
+    @staticmethod
+    def _openai_sampling(body: dict) -> dict:
+        sp = {"max_new_tokens": int(body.get("max_tokens") or body.get("max_completion_tokens") or 128)}
+        for src, dst in (("temperature", "temperature"), ("top_p", "top_p"), ("top_k", "top_k"), ("min_p", "min_p"),
+                         ("stop", "stop"), ("seed", "sampling_seed")):  # fmt: skip
+            if body.get(src) is not None:
+                sp[dst] = body[src]
+        return sp
+
+    def _finish_reason(self, req) -> str:
+        fr = self.engine.meta_info(req).get("finish_reason") or {}
+        return {"length": "length", "abort": "abort"}.get(fr.get("type"), "stop")
+
+    async def _chat_completions(self, request):
+        """``POST /v1/chat/completions``: chat template -> generate -> one choice. ``continue_final_message`` resumes a
+        partial assistant message (what callers send after an abort during a weight update)."""
+        from aiohttp import web
+
+        body = await self._json(request)
+        messages = body.get("messages")
+        if not messages or self.tokenizer is None:
+            return web.json_response({"error": {"message": "messages and a server-side tokenizer are required"}}, status=400)
+        cont = bool(body.get("continue_final_message")) and messages[-1].get("role") == "assistant"
+        kw = {"tools": body["tools"]} if body.get("tools") else {}
+        if cont:
+            text = self.tokenizer.apply_chat_template(messages[:-1], tokenize=False, add_generation_prompt=True, **kw)
+            text += messages[-1].get("content") or ""
+        else:
+            text = self.tokenizer.apply_chat_template(messages, tokenize=False, add_generation_prompt=True, **kw)
+        ids = self.tokenizer.encode(text, add_special_tokens=False)
+        req = await self._run_one(ids, self._openai_sampling(body), rid=body.get("rid"))
+        content = self.tokenizer.decode(req.output_ids, skip_special_tokens=True)
+        return web.json_response({
+            "id": f"chatcmpl-{req.rid}", "object": "chat.completion", "created": int(time.time()),
+            "model": body.get("model") or self.engine.args.model_path or "default",
+            "choices": [{"index": 0, "message": {"role": "assistant", "content": content},
+                         "finish_reason": self._finish_reason(req)}],
+            "usage": {"prompt_tokens": len(ids), "completion_tokens": len(req.output_ids),
+                      "total_tokens": len(ids) + len(req.output_ids)}})  # fmt: skip
+
+    async def _completions(self, request):
+        from aiohttp import web
+
+        body = await self._json(request)
+        prompt = body.get("prompt")
+        if prompt is None or (isinstance(prompt, str) and self.tokenizer is None):
+            return web.json_response({"error": {"message": "prompt (token ids, or text with a tokenizer) is required"}}, status=400)
+        ids = self.tokenizer.encode(prompt, add_special_tokens=False) if isinstance(prompt, str) else list(prompt)
+        req = await self._run_one(ids, self._openai_sampling(body), rid=body.get("rid"))
+        text = self.tokenizer.decode(req.output_ids, skip_special_tokens=True) if self.tokenizer is not None else ""
+        return web.json_response({
+            "id": f"cmpl-{req.rid}", "object": "text_completion", "created": int(time.time()),
+            "model": body.get("model") or self.engine.args.model_path or "default",
+            "choices": [{"index": 0, "text": text, "token_ids": list(req.output_ids), "finish_reason": self._finish_reason(req)}],
+            "usage": {"prompt_tokens": len(ids), "completion_tokens": len(req.output_ids),
+                      "total_tokens": len(ids) + len(req.output_ids)}})  # fmt: skip
+
+    async def _models(self, _request):
+        from aiohttp import web
+
+        name = self.engine.args.model_path or "default"
+        return web.json_response({"object": "list", "data": [{"id": name, "object": "model", "owned_by": "slime_b200"}]})
+
     def _render(self, req) -> dict:
         text = ""
         if self.tokenizer is not None:
@@ -350,6 +431,9 @@ class EngineServer:
         app = web.Application(client_max_size=1 << 34)
         r = app.router
         r.add_post("/generate", self._generate)
+        r.add_post("/v1/chat/completions", self._chat_completions)
+        r.add_post("/v1/completions", self._completions)
+        r.add_get("/v1/models", self._models)
         for path in ("/health", "/healthz"):
             r.add_get(path, self._health)
         r.add_get("/health_generate", self._health_generate)
@@ -394,6 +478,8 @@ class EngineServer:
             self._loop.run_until_complete(self._runner.setup())
             site = web.TCPSite(self._runner, self.host, self.port)
             self._loop.run_until_complete(site.start())
+            if not self.port and self._runner.addresses:  # port 0: the kernel chose
+                self.port = int(self._runner.addresses[0][1])
             ready.set()
             self._loop.run_forever()
 

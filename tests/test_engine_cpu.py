@@ -146,3 +146,45 @@ def test_page_allocator_prefix_index_and_lru():
     assert len(set(taken)) == 8 and not a.index
     with pytest.raises(Exception):
         a.alloc(1)
+
+
+def test_openai_compatible_endpoints():
+    """/v1/chat/completions, /v1/completions and /v1/models on the CPU engine with a word-level tokenizer."""
+    import requests
+
+    from slime_b200.engine.http_server import EngineServer
+
+    class Tok:
+        def encode(self, text, add_special_tokens=False):
+            return [3 + (sum(map(ord, w)) % 500) for w in text.split()]
+
+        def decode(self, ids, skip_special_tokens=True):
+            return " ".join(f"w{i}" for i in ids)
+
+        def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+            text = " ".join(f"<{m['role']}> {m['content']} </s>" for m in messages)
+            return text + (" <assistant> " if add_generation_prompt else "")
+
+    e = make_engine()
+    tok = Tok()
+    srv = EngineServer(e, "127.0.0.1", 0, tok).start(block=False)
+    try:
+        url = f"http://127.0.0.1:{srv.port}"
+        msgs = [{"role": "user", "content": "what is two plus two"}]
+        r = requests.post(url + "/v1/chat/completions", json={"messages": msgs, "max_tokens": 5, "temperature": 0}, timeout=60).json()
+        ch = r["choices"][0]
+        assert r["object"] == "chat.completion" and ch["message"]["role"] == "assistant" and ch["finish_reason"] == "length"
+        assert r["usage"]["completion_tokens"] == 5 and len(ch["message"]["content"].split()) == 5
+        # resuming a partial answer feeds template(prompt) + partial text, so greedy decoding continues the same sequence
+        head = " ".join(ch["message"]["content"].split()[:2])
+        prompt_ids = tok.encode(tok.apply_chat_template(msgs))
+        full = requests.post(url + "/v1/completions", json={"prompt": prompt_ids, "max_tokens": 5, "temperature": 0}, timeout=60).json()
+        assert full["choices"][0]["token_ids"] == [int(w[1:]) for w in ch["message"]["content"].split()]
+        r2 = requests.post(url + "/v1/chat/completions", timeout=60,
+                           json={"messages": msgs + [{"role": "assistant", "content": head}], "max_tokens": 3,
+                                 "temperature": 0, "continue_final_message": True}).json()
+        assert r2["usage"]["prompt_tokens"] == len(prompt_ids) + 2
+        assert requests.get(url + "/v1/models", timeout=10).json()["data"][0]["object"] == "model"
+        assert requests.post(url + "/v1/chat/completions", json={}, timeout=10).status_code == 400
+    finally:
+        srv.shutdown()
