@@ -49,6 +49,28 @@ __global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t
   }
 }
 
+// Same barrier with the epoch kept in device memory (`counter`, advanced by the kernel): the launch arguments are
+// constant, so the barrier still synchronises when it is replayed from a CUDA graph.
+__global__ void symm_barrier_dev_kernel(PeerPtrs pads, int rank, int world, uint32_t* counter, int base, int* status) {
+  const int p = threadIdx.x;
+  if (p < world) {
+    const uint32_t epoch = *counter + 1;
+    __syncwarp((1u << world) - 1u);
+    if (p == 0) *counter = epoch;
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(pads.p[p]) + base + rank, epoch);
+    const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + base + p;
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (p << 8));
+        break;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ float4 multimem_ld_reduce_f32x4(const float* mc_addr) {
   float4 r;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
@@ -178,6 +200,15 @@ extern "C" int sb_symm_barrier(const void* const* pads, int rank, int world, uns
   sb::PeerPtrs pp{};
   for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(pads[i]);
   sb::symm_barrier_kernel<<<1, 32, 0, s>>>(pp, rank, world, epoch, base_word, status);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int sb_symm_barrier_dev(const void* const* pads, int rank, int world, unsigned* counter, int base_word,
+                                   int* status, cudaStream_t s) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || counter == nullptr) return (int)cudaErrorInvalidValue;
+  sb::PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(pads[i]);
+  sb::symm_barrier_dev_kernel<<<1, 32, 0, s>>>(pp, rank, world, counter, base_word, status);
   return (int)cudaGetLastError();
 }
 

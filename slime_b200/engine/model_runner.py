@@ -10,6 +10,7 @@ log-probs agree by construction. Decode runs under CUDA graphs per batch-size bu
 
 from __future__ import annotations
 
+import logging
 import math
 import re
 
@@ -18,6 +19,8 @@ import torch
 from slime_b200 import ops
 from slime_b200.engine.kv_cache import PagedKVCache
 from slime_b200.models.config import ModelConfig
+
+logger = logging.getLogger(__name__)
 
 _LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
 
@@ -164,6 +167,17 @@ class ModelRunner:
         # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
         # into K slices that the epilogue sums with TMA reduce-add.
         self._proj_dtype = torch.float32 if (self.device.type == "cuda" and weights.tp == 1) else None
+        # Tensor-parallel decode: all-reduce + residual add + RMSNorm as one peer-memory kernel when the ranks share an
+        # NVLink domain; otherwise NCCL all-reduce followed by the fused add+norm.
+        self._fused_tp = None
+        if tp_group is not None and weights.tp > 1 and self.device.type == "cuda":
+            from slime_b200.parallel import fused_tp
+
+            if fused_tp.usable(weights.tp, self.device, cfg.hidden_size):
+                try:
+                    self._fused_tp = fused_tp.FusedAllReduceNorm(tp_group, max_batch, cfg.hidden_size, self.device)
+                except Exception as e:  # noqa: BLE001
+                    logger.warning("fused tensor-parallel all-reduce unavailable (%r): using NCCL", e)
         self.rope = ops.rope_cos_sin(max_context + 1, cfg.head_dim, cfg.rotary_base, device=self.device,
                                      scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
@@ -181,6 +195,14 @@ class ModelRunner:
 
             dist.all_reduce(x, group=self.tp_group)
         return x
+
+    def _row_parallel_norm(self, inp, weight, ln, res, T: int):
+        """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual)."""
+        if self._fused_tp is not None and T <= self._fused_tp.max_tokens:
+            ops.gemm(inp, weight, out=self._fused_tp.partial(T))
+            return self._fused_tp(T, res, ln, self.cfg.norm_epsilon)
+        x = self._tp_reduce(ops.gemm(inp, weight, out_dtype=self._proj_dtype))
+        return ops.rmsnorm(x, ln, self.cfg.norm_epsilon, res)
 
     def _mlp(self, L, x):
         if "gate_up" in L:
@@ -326,20 +348,26 @@ class ModelRunner:
                 P(ds["seq_lens"]), P(ds["slots"]), n, ps, W, _lib.stream()), "sb_decode_prepare")  # fmt: skip
         else:
             self._prepare_reference(n)
+        if self._fused_tp is not None:
+            self._fused_tp.begin_forward()
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
-        res = None
+        normed, res = ops.rmsnorm(x, w.layers[0]["ln1"], cfg.norm_epsilon, None)
         for li, L in enumerate(w.layers):
-            normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
             qkv = self._qkv(L, normed, pos)
             q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
             k, v = q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
             ops.kv_write(k.reshape(n, -1), v.reshape(n, -1), slots, self.kv.k[li], self.kv.v[li])
             ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
-            x = self._tp_reduce(ops.gemm(ctx.reshape(n, -1), L["o"], out_dtype=self._proj_dtype))
-            normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
-            x = self._mlp(L, normed)
-        h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
+            normed, res = self._row_parallel_norm(ctx.reshape(n, -1), L["o"], L["ln2"], res, n)
+            # the norm that follows the MLP is the next layer's input norm (or the final norm)
+            next_ln = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.final_norm
+            if "gate_up" in L:
+                act = ops.swiglu(ops.gemm(normed, L["gate_up"]))
+                normed, res = self._row_parallel_norm(act, L["down"], next_ln, res, n)
+            else:
+                normed, res = ops.rmsnorm(self._moe(L, normed), next_ln, cfg.norm_epsilon, res)
+        h = normed
         logits = ops.gemm(h, w.lm_head, out_dtype=torch.float32)
         tok, lp, kept_ids, kept_cnt = ops.sample(
             logits, st["temperature"][:n], st["top_k"][:n] if filtered else None, st["top_p"][:n] if filtered else None,

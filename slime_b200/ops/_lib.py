@@ -29,6 +29,8 @@ P, I, L, F = c_void_p, c_int, c_long, c_float
 _SIGS = {
     "sb_gemm_bf16": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "sb_symm_barrier": [P, I, I, ctypes.c_uint, I, P, P],
+    "sb_symm_barrier_dev": [P, I, I, P, I, P, P],
+    "sb_tp_ar_add_rmsnorm": [P, P, P, P, P, P, P, I, I, F, I, I, I, P, P],
     "sb_dp_reduce_shard": [P, I, I, I, L, L, P, P, P, P],
     "sb_dp_adam_bcast": [P, P, P, P, P, I, I, I, L, L, F, F, F, F, F, F, F, F, F, P, I, P],
     "sb_gemm_bf16_splitk": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, I, P],

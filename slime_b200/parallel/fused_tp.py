@@ -1,0 +1,87 @@
+"""Tensor-parallel all-reduce + residual add + RMSNorm as one kernel over NVLink peer memory (``csrc/tp_fused.cu``).
+
+In a decoder layer every row-parallel projection (attention output, MLP down) is followed by the same three steps:
+sum the partial products over the tensor-parallel ranks, add the residual stream, normalise for the next block.
+``FusedAllReduceNorm`` does them in one launch and without NCCL:
+
+    ar = FusedAllReduceNorm(tp_group, max_tokens, hidden, device)
+    ar.begin_forward()                        # once per forward pass (one bounded barrier)
+    out = ar.partial(T)                       # [T, hidden] bf16 view: the GEMM writes its partial product here
+    ops.gemm(x, w_row_parallel, out=out)
+    normed, residual = ar(T, residual, norm_weight, eps)
+
+The partial products live in two alternating symmetric buffers; a kernel reads the peers' rows directly (plain P2P
+loads summed in rank order, or NVSwitch ``multimem.ld_reduce``), so every rank ends up with identical values. The launch
+arguments never change between calls with the same ``T`` (epochs live in device memory), hence a decode step that
+contains these calls can be captured in a CUDA graph; ``begin_forward`` restarts the alternation, so any number of
+calls per forward pass works. ``usable()`` says whether the fast path exists here; callers fall back to
+``dist.all_reduce`` + ``ops.rmsnorm``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import logging
+import os
+
+import torch
+
+from slime_b200.parallel.fused_dp import SymmetricStorage, symmetric_memory_usable
+
+logger = logging.getLogger(__name__)
+MAX_BLOCKS = 148
+
+
+def usable(group_size: int, device, hidden: int) -> bool:
+    if os.environ.get("SLIME_B200_DISABLE_FUSED_TP") == "1":
+        return False
+    return symmetric_memory_usable(group_size, device) and hidden % 8 == 0 and hidden <= 8192
+
+
+class FusedAllReduceNorm:
+    def __init__(self, group, max_tokens: int, hidden: int, device):
+        from slime_b200.ops import _lib
+
+        self._lib = _lib
+        self.hidden, self.max_tokens, self.device = hidden, max_tokens, torch.device(device)
+        self.bufs = [SymmetricStorage(max_tokens * hidden, torch.bfloat16, device, group) for _ in range(2)]
+        self.flags = SymmetricStorage(MAX_BLOCKS * 8, torch.int32, device, group)
+        self.world, self.rank = self.flags.world, self.flags.rank
+        self.epochs = torch.zeros(MAX_BLOCKS, dtype=torch.int32, device=device)
+        self.use_mc = all(b.mc_ptr for b in self.bufs) and os.environ.get("SLIME_B200_DISABLE_MULTIMEM") != "1"
+        self._flag_ptrs = (ctypes.c_void_p * self.world)(*self.flags.ptrs)
+        self._pads = (ctypes.c_void_p * self.world)(*self.flags.pad_ptrs)
+        self._pad_base = self.flags.pad_words - 32  # away from the data-parallel barrier's words and torch's own
+        self._barrier_counter = torch.zeros(1, dtype=torch.int32, device=device)  # device-side epoch: graph-safe
+        self._which = 0
+        torch.cuda.synchronize(self.device)
+        import torch.distributed as dist
+
+        dist.barrier(group=group)  # every rank's flags and epochs are zero before anyone raises one
+        logger.info("fused tensor-parallel all-reduce+norm: %d ranks, %s", self.world,
+                    "NVSwitch multimem" if self.use_mc else "P2P loads")  # fmt: skip
+
+    def begin_forward(self) -> None:
+        """All ranks have finished the previous forward pass: both partial buffers are free again."""
+        lib, P = self._lib.lib(), self._lib.ptr
+        rc = lib.sb_symm_barrier_dev(self._pads, self.rank, self.world, P(self._barrier_counter), self._pad_base,
+                                     P(self._lib.status_word(self.device)), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_symm_barrier_dev")
+        self._which = 0
+
+    def partial(self, T: int) -> torch.Tensor:
+        assert T <= self.max_tokens, f"{T} tokens exceed the buffer ({self.max_tokens})"
+        return self.bufs[self._which].tensor[: T * self.hidden].view(T, self.hidden)
+
+    def __call__(self, T: int, residual, weight, eps: float, out=None, res_out=None):
+        """(normed, new_residual) from the partial products in the current buffer; then switches buffers."""
+        lib, P = self._lib.lib(), self._lib.ptr
+        buf = self.bufs[self._which]
+        y = out if out is not None else torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        r = res_out if res_out is not None else torch.empty(T, self.hidden, dtype=torch.bfloat16, device=self.device)
+        rc = lib.sb_tp_ar_add_rmsnorm(buf.c_ptrs(self.use_mc), self._flag_ptrs, P(self.epochs), P(residual), P(weight), P(y),
+                                      P(r), T, self.hidden, float(eps), self.rank, self.world, int(self.use_mc),
+                                      P(self._lib.status_word(self.device)), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_tp_ar_add_rmsnorm")
+        self._which ^= 1
+        return y, r

@@ -30,3 +30,11 @@ def test_fused_dp_step_matches_nccl(kernels, multimem):
     n = min(torch.cuda.device_count(), 8)
     r = _torchrun("tests/multigpu/fused_dp_check.py", n, {"SLIME_B200_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
     assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("multimem", ["1", "0"])
+def test_fused_tp_allreduce_norm_matches_nccl(kernels, multimem):
+    _need(2)
+    n = min(torch.cuda.device_count(), 8)
+    r = _torchrun("tests/multigpu/fused_tp_check.py", n, {"SLIME_B200_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
