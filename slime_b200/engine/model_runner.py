@@ -196,6 +196,17 @@ class ModelRunner:
             dist.all_reduce(x, group=self.tp_group)
         return x
 
+    def _gather_logits(self, logits):
+        """Vocab-parallel LM head: [T, V/tp] per rank -> [T, V] on every rank (rank r owns columns r*V/tp ...)."""
+        if self.tp_group is None or self.w.tp == 1:
+            return logits
+        import torch.distributed as dist
+
+        T, vl = logits.shape
+        parts = torch.empty(self.w.tp * T, vl, dtype=logits.dtype, device=logits.device)  # rank-major concatenation
+        dist.all_gather_into_tensor(parts, logits.contiguous(), group=self.tp_group)
+        return parts.view(self.w.tp, T, vl).permute(1, 0, 2).reshape(T, -1)
+
     def _row_parallel_norm(self, inp, weight, ln, res, T: int):
         """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual)."""
         if self._fused_tp is not None and T <= self._fused_tp.max_tokens:
@@ -271,7 +282,7 @@ class ModelRunner:
         h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
         if last_rows is not None:
             h = h.index_select(0, last_rows)
-        return ops.gemm(h, w.lm_head, out_dtype=torch.float32)
+        return self._gather_logits(ops.gemm(h, w.lm_head, out_dtype=torch.float32))
 
     # ---------------------------------------------------------------------- decode
     # Per-slot decode state is device-owned (ids / pos / out_pos): the token sampled in step t is the
@@ -368,7 +379,7 @@ class ModelRunner:
             else:
                 normed, res = ops.rmsnorm(self._moe(L, normed), next_ln, cfg.norm_epsilon, res)
         h = normed
-        logits = ops.gemm(h, w.lm_head, out_dtype=torch.float32)
+        logits = self._gather_logits(ops.gemm(h, w.lm_head, out_dtype=torch.float32))
         tok, lp, kept_ids, kept_cnt = ops.sample(
             logits, st["temperature"][:n], st["top_k"][:n] if filtered else None, st["top_p"][:n] if filtered else None,
             st["min_p"][:n] if filtered else None, st["seeds"][:n], ds["out_pos"][:n], kept_cap,

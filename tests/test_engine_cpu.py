@@ -188,3 +188,17 @@ def test_openai_compatible_endpoints():
         assert requests.post(url + "/v1/chat/completions", json={}, timeout=10).status_code == 400
     finally:
         srv.shutdown()
+
+
+def test_tensor_parallel_engine_on_gloo_matches_single_rank():
+    """Two gloo ranks: TP weight slicing, row-parallel reductions and the vocab-parallel logits gather (host logic)."""
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, ENGINE_TP_CHECK_DEVICE="cpu", MASTER_ADDR="127.0.0.1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29671", os.path.join(root, "tests/multigpu/engine_tp_check.py")],
+                       env=env, cwd=root, capture_output=True, text=True, timeout=280)  # fmt: skip
+    assert r.returncode == 0 and "RESULT ok world=2" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -38,3 +38,9 @@ def test_fused_tp_allreduce_norm_matches_nccl(kernels, multimem):
     n = min(torch.cuda.device_count(), 8)
     r = _torchrun("tests/multigpu/fused_tp_check.py", n, {"SLIME_B200_DISABLE_MULTIMEM": "0" if multimem == "1" else "1"})
     assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_tensor_parallel_engine_matches_single_gpu(kernels):
+    _need(2)
+    r = _torchrun("tests/multigpu/engine_tp_check.py", 2)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout and "fused_tp=True" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
