@@ -63,19 +63,27 @@ def main():
     missing = tp.weights.load_weights(weights)
     assert not missing, missing
     fused = tp.runner._fused_tp is not None
-    out_tp = [r.output_ids for r in tp.generate(prompts, sp)]
+    reqs = tp.generate(prompts, dict(sp, ignore_eos=True))
+    out_tp = [r.output_ids for r in reqs]
+    lp_tp = [r.output_logprobs for r in reqs]
     if not cpu:
         torch.cuda.synchronize()
         _lib.check_status(dev)
     if rank == 0:
         one = Engine(cfg, ServerArgs(**sargs), device=dev, num_pages=128)
         assert not one.weights.load_weights(weights)
-        out_one = [r.output_ids for r in one.generate(prompts, sp)]
-        same = sum(a == b for a, b in zip(out_tp, out_one))
-        # bf16 partial sums are added in a different order under TP: allow a late divergence in at most one sequence
-        first = [next((k for k, (x, y) in enumerate(zip(a, b)) if x != y), len(a)) for a, b in zip(out_tp, out_one)]
-        assert same >= len(prompts) - 1 and min(first) >= 8, (same, first)
-        print(f"RESULT ok world={world} fused_tp={fused} identical={same}/{len(prompts)}", flush=True)
+        if cpu:  # fp32 reference ops on both sides: greedy decoding must agree token for token
+            out_one = [r.output_ids for r in one.generate(prompts, dict(sp, ignore_eos=True))]
+            assert out_tp == out_one, (out_tp, out_one)
+        # The TP engine's own tokens, scored by the single-rank engine with teacher forcing: the log-probs agree to bf16
+        # accuracy (random weights give near-ties, so comparing greedy tokens of two bf16 pipelines would be fragile).
+        worst = 0.0
+        for p, o, lp in zip(prompts, out_tp, lp_tp):
+            rq = one.generate([p + o], [dict(max_new_tokens=0)], logprob_start_len=0)[0]
+            ref = torch.tensor(rq.input_logprobs[len(p):])
+            worst = max(worst, float((ref - torch.tensor(lp)).abs().max()))
+        assert worst < (1e-4 if cpu else 0.08), worst
+        print(f"RESULT ok world={world} fused_tp={fused} max_logprob_diff={worst:.4f}", flush=True)
     dist.barrier()
     dist.destroy_process_group()
 
