@@ -56,7 +56,7 @@ template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv, const __nv_bfloat16* __restrict__ bias,
-                 int M, int N, int K, int ldc, int accumulate, int* status) {
+                 int M, int N, int K, int ldc, int accumulate, int* status, const int* __restrict__ tile_boff) {
   using S = GemmSmem<BN, STAGES>;
   constexpr int NCOLS = 2 * BN;  // two accumulator stages (power of two: 256 or 512)
   extern __shared__ uint8_t smem_raw[];
@@ -120,6 +120,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int tile = item / splitk, ks = item - tile * splitk;
         int m0, n0;
         tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
+        // Grouped GEMM: B is the experts' matrices stacked along its row dimension and every 128-row tile of A belongs
+        // to one expert; tile_boff[m-tile] is the row at which that expert's matrix starts in the stack.
+        const int boff = tile_boff != nullptr ? __ldg(tile_boff + m0 / GEMM_BM) : 0;
         const int kb_end = min(num_kb, (ks + 1) * kb_per);
         for (int kb = ks * kb_per; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
@@ -137,11 +140,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               tma_load_2d(a_dst + j * 8192, &tmA, &full[stage], m0 + j * 64, kb * GEMM_BK);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(b_dst, &tmB, &full[stage], kb * GEMM_BK, n0);
+            tma_load_2d(b_dst, &tmB, &full[stage], kb * GEMM_BK, n0 + boff);
           } else {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n0 + j * 64, kb * GEMM_BK);
+              tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n0 + j * 64, kb * GEMM_BK + boff);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -338,7 +341,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
 static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
-                               int ldb, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream) {
+                               int ldb, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream,
+                               const int* tile_boff = nullptr, int b_stack_rows = 0) {
   using S = GemmSmem<BN, STAGES>;
   // K-major operand: tensor [rows = M or N, cols = K], box [rows_tile, 64].
   // MN-major operand: tensor [rows = K, cols = M or N], box [64 k-rows, 64 cols].
@@ -346,9 +350,11 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
                                         CU_TENSOR_MAP_SWIZZLE_128B)
                          : make_tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, size_t(lda) * 2, GEMM_BM, GEMM_BK,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
-  CUtensorMap tmB = B_MN ? make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, size_t(ldb) * 2, 64, 64,
+  // grouped: the map covers the whole stack (b_stack_rows rows), the kernel adds the expert's row offset
+  const int b_rows = b_stack_rows > 0 ? b_stack_rows : (B_MN ? K : N);
+  CUtensorMap tmB = B_MN ? make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_rows, N, size_t(ldb) * 2, 64, 64,
                                         CU_TENSOR_MAP_SWIZZLE_128B)
-                         : make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, size_t(ldb) * 2, BN, GEMM_BK,
+                         : make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_rows, K, size_t(ldb) * 2, BN, GEMM_BK,
                                         CU_TENSOR_MAP_SWIZZLE_128B);
   CUtensorMap tmC = tmA;  // placeholder when the direct-store epilogue is used
   if constexpr (TMA_EPI) {
@@ -371,7 +377,7 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
   const int grid = tiles < num_sms ? tiles : num_sms;
   cudaError_t le = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, tmC, C,
-                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status);
+                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status, tile_boff);
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
   return le;
 }
@@ -379,11 +385,12 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
 template <int BN, int STAGES, bool TMA_EPI>
 static cudaError_t dispatch_layout(bool a_mn, bool b_mn, bool out_f32, const void* A, const void* B, void* C,
                                    const void* bias, int M, int N, int K, int lda, int ldb, int ldc, int accumulate,
-                                   int* status, int num_sms, cudaStream_t stream) {
+                                   int* status, int num_sms, cudaStream_t stream, const int* tile_boff = nullptr,
+                                   int b_stack_rows = 0) {
 #define SB_CASE(AM, BMN, OF)                                                                                       \
   if (a_mn == AM && b_mn == BMN && out_f32 == OF)                                                                  \
     return launch_gemm<BN, STAGES, AM, BMN, OF, TMA_EPI>(A, B, C, bias, M, N, K, lda, ldb, ldc, accumulate, status, \
-                                                         num_sms, stream);
+                                                         num_sms, stream, tile_boff, b_stack_rows);
   SB_CASE(false, false, false)
   SB_CASE(false, false, true)
   SB_CASE(false, true, false)
@@ -436,6 +443,41 @@ extern "C" int sb_gemm_bf16_splitk(const void* A, const void* B, void* C, const 
                                                     ldc, accumulate, status, num_sms, stream);
     return (int)sb::dispatch_layout<128, 6, false>(a_mn != 0, b_mn != 0, out_f32 != 0, A, B, C, bias, M, N, K, lda, ldb,
                                                    ldc, accumulate, status, num_sms, stream);
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
+    return (int)cudaErrorInvalidValue;
+  }
+}
+
+// Grouped GEMM over experts (M-contiguous layout): A [M, K] row-major holds the tokens sorted by expert, each expert's
+// segment starting at a multiple of 128 rows (the tail of a segment is padding); B is the experts' weights stacked,
+// [E * N, K] row-major (b_mn = 0, C = A * W_e^T) or [E * K, N] (b_mn = 1, C = A * W_e); tile_boff[t] (device, one int
+// per 128-row tile of A) is the first row of that tile's expert in the stack: e * N, resp. e * K. C [M, N] bf16 or fp32.
+// With b_mn = 1, K must be a multiple of 64 (a K tail would read the next expert's rows).
+extern "C" int sb_gemm_bf16_grouped(const void* A, const void* B, void* C, const int* tile_boff, int M, int N, int K,
+                                    int num_experts, int lda, int ldb, int ldc, int b_mn, int out_f32, int bn, int* status,
+                                    int num_sms, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (tile_boff == nullptr || num_experts <= 0 || (b_mn && K % sb::GEMM_BK != 0)) {
+    sb::set_last_error("sb_gemm_bf16_grouped: needs tile_boff, num_experts > 0, and K % 64 == 0 when b_mn");
+    return (int)cudaErrorInvalidValue;
+  }
+  const size_t c_elem = out_f32 ? 4 : 2;
+  const bool tma_epi = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * c_elem) % 16 == 0;
+  const int stack_rows = num_experts * (b_mn ? K : N);
+  try {
+    if (bn == 256) {
+      if (tma_epi)
+        return (int)sb::dispatch_layout<256, 4, true>(false, b_mn != 0, out_f32 != 0, A, B, C, nullptr, M, N, K, lda, ldb, ldc,
+                                                      0, status, num_sms, stream, tile_boff, stack_rows);
+      return (int)sb::dispatch_layout<256, 4, false>(false, b_mn != 0, out_f32 != 0, A, B, C, nullptr, M, N, K, lda, ldb, ldc,
+                                                     0, status, num_sms, stream, tile_boff, stack_rows);
+    }
+    if (tma_epi)
+      return (int)sb::dispatch_layout<128, 6, true>(false, b_mn != 0, out_f32 != 0, A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0,
+                                                    status, num_sms, stream, tile_boff, stack_rows);
+    return (int)sb::dispatch_layout<128, 6, false>(false, b_mn != 0, out_f32 != 0, A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0,
+                                                   status, num_sms, stream, tile_boff, stack_rows);
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;

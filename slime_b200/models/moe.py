@@ -20,6 +20,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from slime_b200 import ops
+from slime_b200.ops import grouped
 from slime_b200.models.config import ModelConfig
 from slime_b200.parallel import state as mpu
 from slime_b200.parallel import tensor_parallel as tp
@@ -114,6 +115,7 @@ class GroupedExperts(nn.Module):
             self.linear_fc1.register_parameter(f"weight{e}", w1)
             self.linear_fc2.register_parameter(f"weight{e}", w2)
         self.int4_qat_group = 0  # >0: fake-INT4 the expert weights in forward (straight-through backward)
+        self.use_grouped_gemm = True  # False: one GEMM pair per expert (kept as the oracle of the grouped path)
 
     def _w(self, mod, e):
         w = getattr(mod, f"weight{e}")
@@ -123,6 +125,13 @@ class GroupedExperts(nn.Module):
 
     def forward(self, x, counts: list[int]):
         """x: [sum(counts), H] rows grouped by local expert."""
+        if self.int4_qat_group == 0 and x.shape[0] > 0 and self.use_grouped_gemm:
+            # one grouped launch per projection instead of a loop over experts (rows padded to the GEMM's row tile)
+            lay = grouped.PaddedLayout(counts, x.device)
+            w1 = [getattr(self.linear_fc1, f"weight{e}") for e in range(self.num_local)]
+            w2 = [getattr(self.linear_fc2, f"weight{e}") for e in range(self.num_local)]
+            act = ops.swiglu(grouped.grouped_linear(lay.pad(x), lay, w1))
+            return lay.unpad(grouped.grouped_linear(act, lay, w2))
         outs, start = [], 0
         for e, n in enumerate(counts):
             if n == 0:

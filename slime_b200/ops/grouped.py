@@ -1,0 +1,142 @@
+"""Grouped (per-expert) linear layers on the tcgen05 GEMM: the MoE expert MLP without a Python loop over experts.
+
+Layout ("M-contiguous"): the tokens routed to this rank's experts arrive sorted by expert; ``PaddedLayout`` places each
+expert's rows at a multiple of 128 (the GEMM's row tile), so every tile belongs to exactly one expert and the kernel
+only needs a per-tile row offset into the stacked weights (``csrc/gemm_sm100.cu``: ``sb_gemm_bf16_grouped``).
+
+    lay = PaddedLayout(counts, device)              # counts: rows per local expert (host ints)
+    xp = lay.pad(x)                                 # [M_pad, H], padding rows are zero
+    h = grouped_linear(xp, lay, fc1_weights)        # fc1_weights: list of E parameters [N, K]
+    y = lay.unpad(grouped_linear(swiglu(h), lay, fc2_weights))
+
+Forward ``y_e = x_e W_e^T`` and the input gradient ``dx_e = dy_e W_e`` are one grouped launch each; the weight
+gradients are one ``dy_e^T x_e`` GEMM per expert over that expert's row range (accumulated straight into
+``main_grad`` when the parameter has one). The experts' weights are used in place when they are adjacent in memory (the
+flat parameter buffer lays them out that way); otherwise they are stacked with a copy.
+On CPU the same functions run a per-expert fp32 loop (the numerics oracle of the GPU path).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from slime_b200.ops import _lib
+
+TILE = 128
+P = _lib.ptr
+
+
+class PaddedLayout:
+    """Row bookkeeping for ``counts[e]`` rows per expert, each segment starting at a multiple of 128."""
+
+    def __init__(self, counts: list[int], device):
+        self.counts = [int(c) for c in counts]
+        self.padded = [-(-c // TILE) * TILE for c in self.counts]
+        self.num_experts, self.rows, self.rows_padded = len(counts), sum(self.counts), sum(self.padded)
+        starts, pstarts, s, ps = [], [], 0, 0
+        for c, pc in zip(self.counts, self.padded):
+            starts.append(s)
+            pstarts.append(ps)
+            s, ps = s + c, ps + pc
+        self.starts, self.padded_starts = starts, pstarts
+        cnt = torch.tensor(self.counts, dtype=torch.long)
+        shift = torch.repeat_interleave(torch.tensor([p - q for p, q in zip(pstarts, starts)], dtype=torch.long), cnt)
+        self.dest = (torch.arange(self.rows, dtype=torch.long) + shift).to(device)  # sorted row -> padded row
+        tiles = torch.tensor([pc // TILE for pc in self.padded], dtype=torch.long)
+        self.tile_expert = torch.repeat_interleave(torch.arange(self.num_experts), tiles).to(device=device, dtype=torch.int32)
+
+    def pad(self, x: torch.Tensor) -> torch.Tensor:
+        return x.new_zeros(self.rows_padded, x.shape[-1]).index_copy(0, self.dest, x)
+
+    def unpad(self, xp: torch.Tensor) -> torch.Tensor:
+        return xp.index_select(0, self.dest)
+
+
+def stacked_view(tensors: list[torch.Tensor]) -> torch.Tensor | None:
+    """``[E, *shape]`` view over ``tensors`` without a copy when they sit back to back in one storage, else None."""
+    t0 = tensors[0]
+    if not all(t.is_contiguous() and t.shape == t0.shape and t.dtype == t0.dtype for t in tensors):
+        return None
+    step = t0.numel() * t0.element_size()
+    base = t0.data_ptr()
+    if any(t.data_ptr() != base + i * step for i, t in enumerate(tensors)):
+        return None
+    try:
+        return torch.empty(0, dtype=t0.dtype, device=t0.device).set_(
+            t0.untyped_storage(), t0.storage_offset(), (len(tensors), *t0.shape))  # fmt: skip
+    except RuntimeError:  # the storage ends before the last tensor: the tensors do not share it after all
+        return None
+
+
+def _stack(weights: list[torch.Tensor]) -> torch.Tensor:
+    datas = [w.detach() for w in weights]
+    v = stacked_view(datas)
+    return v if v is not None else torch.stack(datas)
+
+
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay: PaddedLayout, *, b_mn: bool = False, out_dtype=None) -> torch.Tensor:
+    """``out[rows of e] = a[rows of e] @ w[e]^T`` (``b_mn`` False, w [E, N, K]) or ``@ w[e]`` (``b_mn`` True, w [E, K, N])."""
+    E, R, C = w.shape
+    M, K = a.shape
+    N = C if b_mn else R
+    assert M == lay.rows_padded and E == lay.num_experts and K == (R if b_mn else C)
+    out_dtype = out_dtype or a.dtype
+    if not a.is_cuda:
+        out = torch.zeros(M, N, dtype=torch.float32)
+        for e in range(E):
+            s, n = lay.padded_starts[e], lay.counts[e]
+            we = w[e].float()
+            out[s : s + n] = a[s : s + n].float() @ (we if b_mn else we.t())
+        return out.to(out_dtype)
+    a = a.contiguous()
+    w = w.contiguous()
+    out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if M == 0:
+        return out
+    boff = lay.tile_expert * R  # first row of the tile's expert in the [E * R, C] stack
+    from slime_b200.ops import _pick_bn
+
+    rc = _lib.lib().sb_gemm_bf16_grouped(
+        P(a), P(w), P(out), P(boff), M, N, K, E, a.stride(0), w.stride(1), out.stride(0), int(b_mn),
+        int(out_dtype == torch.float32), _pick_bn(M, N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
+    )  # fmt: skip
+    _lib.check(rc, "sb_gemm_bf16_grouped")
+    return out
+
+
+class _GroupedLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, lay, *weights):
+        ctx.lay, ctx.weights = lay, weights
+        ctx.save_for_backward(x)
+        return grouped_gemm(x, _stack(list(weights)), lay)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from slime_b200.ops import gemm
+
+        (x,) = ctx.saved_tensors
+        lay, weights = ctx.lay, ctx.weights
+        dy = dy.contiguous()
+        dx = grouped_gemm(dy, _stack(list(weights)), lay, b_mn=True) if ctx.needs_input_grad[0] else None
+        dws = []
+        for e, w in enumerate(weights):
+            if not ctx.needs_input_grad[2 + e]:
+                dws.append(None)
+                continue
+            s, n = lay.padded_starts[e], lay.counts[e]
+            main_grad = getattr(w, "main_grad", None)
+            if n == 0:
+                dws.append(None if main_grad is not None else torch.zeros_like(w))
+            elif main_grad is not None:
+                gemm(dy[s : s + n], x[s : s + n], a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+                w.grad_added_to_main_grad = True
+                dws.append(None)
+            else:
+                dws.append(gemm(dy[s : s + n], x[s : s + n], a_mn=True, b_mn=True, out_dtype=w.dtype))
+        return (dx, None, *dws)
+
+
+def grouped_linear(x_padded: torch.Tensor, lay: PaddedLayout, weights: list[torch.Tensor]) -> torch.Tensor:
+    """Differentiable ``y[rows of e] = x[rows of e] @ weights[e]^T`` on the padded layout."""
+    return _GroupedLinear.apply(x_padded, lay, *weights)

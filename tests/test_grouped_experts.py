@@ -1,0 +1,98 @@
+"""Grouped expert MLP: the padded-layout path against the per-expert loop (CPU), and against fp32 math on a GPU."""
+
+import pytest
+import torch
+
+from slime_b200.ops import grouped
+
+
+def _loop_reference(x, counts, w1, w2):
+    outs, s = [], 0
+    for e, n in enumerate(counts):
+        xe = x[s : s + n].float()
+        h = xe @ w1[e].float().t()
+        g, u = h.chunk(2, dim=-1)
+        outs.append((torch.nn.functional.silu(g) * u) @ w2[e].float().t())
+        s += n
+    return torch.cat(outs)
+
+
+def test_padded_layout_and_stacked_view():
+    lay = grouped.PaddedLayout([3, 0, 130, 128], "cpu")
+    assert lay.padded == [128, 0, 256, 128] and lay.rows == 261 and lay.rows_padded == 512
+    assert lay.tile_expert.tolist() == [0, 2, 2, 3] and lay.dest[:4].tolist() == [0, 1, 2, 128]
+    x = torch.arange(261.0)[:, None].repeat(1, 2)
+    assert torch.equal(lay.unpad(lay.pad(x)), x) and lay.pad(x)[3:128].abs().sum() == 0
+    flat = torch.randn(3 * 4 * 5)
+    views = [flat[i * 20 : (i + 1) * 20].view(4, 5) for i in range(3)]
+    st = grouped.stacked_view(views)
+    assert st is not None and st.data_ptr() == flat.data_ptr() and torch.equal(st[2], views[2])
+    assert grouped.stacked_view([views[0], views[2]]) is None
+    assert grouped.stacked_view([torch.randn(4, 5), torch.randn(4, 5).t().contiguous().t()]) is None
+
+
+def test_grouped_experts_module_matches_loop_on_cpu():
+    from slime_b200.models.config import get_preset
+    from slime_b200.models.moe import GroupedExperts
+    from slime_b200.parallel import state as mpu
+
+    if not mpu.model_parallel_is_initialized():
+        mpu.initialize_model_parallel()
+    cfg = get_preset("tiny-moe")
+    torch.manual_seed(0)
+    m = GroupedExperts(cfg, torch.float32, "cpu", 4)
+    counts = [5, 0, 9, 2]
+    x = torch.randn(sum(counts), cfg.hidden_size, requires_grad=True)
+    y = m(x, counts)
+    y.pow(2).sum().backward()
+    gx, gw = x.grad.clone(), [p.grad.clone() for p in m.parameters()]
+    x.grad = None
+    for p in m.parameters():
+        p.grad = None
+    m.use_grouped_gemm = False
+    y2 = m(x, counts)
+    y2.pow(2).sum().backward()
+    torch.testing.assert_close(y, y2, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(gx, x.grad, rtol=1e-4, atol=1e-5)
+    for a, p in zip(gw, m.parameters()):
+        torch.testing.assert_close(a, p.grad if p.grad is not None else torch.zeros_like(p), rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("counts", [[300, 0, 77, 129, 1, 128], [4096, 1000, 2, 3000]])
+def test_grouped_gemm_gpu_matches_fp32(kernels, counts):
+    from slime_b200 import ops
+
+    torch.manual_seed(len(counts))
+    E, H, F = len(counts), 512, 384
+    dev = "cuda"
+    flat1 = (torch.randn(E * 2 * F * H, device=dev) * 0.05).to(torch.bfloat16)  # adjacent experts: the no-copy path
+    w1 = [flat1[e * 2 * F * H : (e + 1) * 2 * F * H].view(2 * F, H).requires_grad_() for e in range(E)]
+    w2 = [(torch.randn(H, F, device=dev) * 0.05).to(torch.bfloat16).requires_grad_() for _ in range(E)]  # stacked by copy
+    x = torch.randn(sum(counts), H, device=dev).to(torch.bfloat16).requires_grad_()
+    lay = grouped.PaddedLayout(counts, dev)
+    assert grouped.stacked_view([w.detach() for w in w1]) is not None
+    h = grouped.grouped_linear(lay.pad(x), lay, w1)
+    y = lay.unpad(grouped.grouped_linear(ops.swiglu(h), lay, w2))
+    ref = _loop_reference(x.detach(), counts, [w.detach() for w in w1], [w.detach() for w in w2])
+    assert (y.float() - ref).abs().max() <= 0.03 * ref.abs().max() + 1e-3
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    xr = x.detach().float().requires_grad_()
+    w1r = [w.detach().float().requires_grad_() for w in w1]
+    w2r = [w.detach().float().requires_grad_() for w in w2]
+    outs, s = [], 0
+    for e, n in enumerate(counts):
+        hh = xr[s : s + n] @ w1r[e].t()
+        g, u = hh.chunk(2, dim=-1)
+        outs.append((torch.nn.functional.silu(g) * u) @ w2r[e].t())
+        s += n
+    torch.cat(outs).backward(gy.float())
+
+    def close(a, b, what):
+        assert (a.float() - b).abs().max() <= 0.04 * b.abs().max() + 1e-3, what
+
+    close(x.grad, xr.grad, "dx")
+    for e in range(E):
+        close(w1[e].grad if w1[e].grad is not None else torch.zeros_like(w1[e]), w1r[e].grad if w1r[e].grad is not None else torch.zeros_like(w1r[e]), f"dw1[{e}]")
+        close(w2[e].grad if w2[e].grad is not None else torch.zeros_like(w2[e]), w2r[e].grad if w2r[e].grad is not None else torch.zeros_like(w2r[e]), f"dw2[{e}]")
