@@ -228,20 +228,13 @@ class ModelRunner:
         topv, idx = torch.topk(logits, k, dim=-1)
         probs = torch.softmax(topv, -1) if cfg.norm_topk_prob else torch.softmax(logits, -1).gather(-1, idx)
         self._last_routed = idx
-        flat = idx.reshape(-1)
-        order = torch.argsort(flat, stable=True)
-        rows = x.index_select(0, order // k)
-        counts = torch.bincount(flat, minlength=cfg.num_experts).tolist()
-        outs, s = [], 0
-        for e, n in enumerate(counts):
-            if n:
-                act = ops.swiglu(ops.gemm(rows[s : s + n], L["w13"][e]))
-                outs.append(ops.gemm(act, L["w2"][e]))
-                s += n
-        y = torch.cat(outs) * probs.reshape(-1).index_select(0, order).to(x.dtype)[:, None]
-        inv = torch.empty_like(order)
-        inv[order] = torch.arange(order.numel(), device=order.device)
-        return y.index_select(0, inv).view(x.shape[0], k, -1).float().sum(1).to(x.dtype)
+        # expert-sorted, tile-padded layout built on the device (no host sync: the step stays graph-capturable), then
+        # one grouped GEMM per projection over all experts
+        from slime_b200.ops import grouped
+
+        lay = grouped.DeviceLayout(idx, L["w13"].shape[0])
+        act = ops.swiglu(grouped.grouped_gemm(lay.pad(x), L["w13"], lay))
+        return lay.combine(grouped.grouped_gemm(act, L["w2"], lay), probs, x.shape[0])
 
     def _qkv(self, L, normed, positions):
         cfg = self.cfg

@@ -52,6 +52,42 @@ class PaddedLayout:
         return xp.index_select(0, self.dest)
 
 
+class DeviceLayout:
+    """The same padded layout built entirely on the device from the router's choices: no host synchronisation, static
+    shapes (the row count is the worst case ``T*k + E*127`` rounded up to a tile), so it can live inside a CUDA graph.
+
+    ``idx``: [T, k] expert ids. Rows of the padded buffer hold token ``order // k`` for the sorted assignment ``order``;
+    tiles past the last used row are zero rows attached to the last expert (they cost a little compute, nothing else).
+    """
+
+    def __init__(self, idx: torch.Tensor, num_experts: int):
+        T, k = idx.shape
+        dev = idx.device
+        flat = idx.reshape(-1).long()
+        self.k, self.num_experts = k, num_experts
+        self.order = torch.argsort(flat, stable=True)  # assignments grouped by expert, token order kept inside a group
+        sorted_e = flat.index_select(0, self.order)
+        counts = torch.bincount(flat, minlength=num_experts)
+        padded = (counts + (TILE - 1)) // TILE * TILE
+        pend = torch.cumsum(padded, 0)
+        shift = (pend - padded) - (torch.cumsum(counts, 0) - counts)
+        self.dest = torch.arange(flat.numel(), device=dev) + shift.index_select(0, sorted_e)
+        self.rows_padded = -(-(flat.numel() + num_experts * (TILE - 1)) // TILE) * TILE
+        tiles = torch.arange(self.rows_padded // TILE, device=dev) * TILE
+        self.tile_expert = torch.searchsorted(pend, tiles, right=True).clamp_(max=num_experts - 1).to(torch.int32)
+        self.token = self.order // k
+
+    def pad(self, x: torch.Tensor) -> torch.Tensor:
+        """[T, H] token activations -> [rows_padded, H] expert-sorted, zero padded."""
+        return x.new_zeros(self.rows_padded, x.shape[-1]).index_copy_(0, self.dest, x.index_select(0, self.token))
+
+    def combine(self, y_padded: torch.Tensor, probs: torch.Tensor, T: int) -> torch.Tensor:
+        """Weighted sum of each token's k expert outputs (fp32 accumulation) -> [T, H]."""
+        w = probs.reshape(-1).index_select(0, self.order).float()
+        y = y_padded.index_select(0, self.dest).float() * w[:, None]
+        return torch.zeros(T, y.shape[-1], dtype=torch.float32, device=y.device).index_add_(0, self.token, y).to(y_padded.dtype)
+
+
 def stacked_view(tensors: list[torch.Tensor]) -> torch.Tensor | None:
     """``[E, *shape]`` view over ``tensors`` without a copy when they sit back to back in one storage, else None."""
     t0 = tensors[0]
@@ -74,7 +110,7 @@ def _stack(weights: list[torch.Tensor]) -> torch.Tensor:
     return v if v is not None else torch.stack(datas)
 
 
-def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay: PaddedLayout, *, b_mn: bool = False, out_dtype=None) -> torch.Tensor:
+def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay, *, b_mn: bool = False, out_dtype=None) -> torch.Tensor:
     """``out[rows of e] = a[rows of e] @ w[e]^T`` (``b_mn`` False, w [E, N, K]) or ``@ w[e]`` (``b_mn`` True, w [E, K, N])."""
     E, R, C = w.shape
     M, K = a.shape
@@ -83,10 +119,9 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay: PaddedLayout, *, b_mn: b
     out_dtype = out_dtype or a.dtype
     if not a.is_cuda:
         out = torch.zeros(M, N, dtype=torch.float32)
-        for e in range(E):
-            s, n = lay.padded_starts[e], lay.counts[e]
+        for t, e in enumerate(lay.tile_expert.tolist()):  # tile by tile: all a layout has to provide is tile -> expert
             we = w[e].float()
-            out[s : s + n] = a[s : s + n].float() @ (we if b_mn else we.t())
+            out[t * TILE : (t + 1) * TILE] = a[t * TILE : (t + 1) * TILE].float() @ (we if b_mn else we.t())
         return out.to(out_dtype)
     a = a.contiguous()
     w = w.contiguous()
