@@ -1,0 +1,244 @@
+// Block-scaled FP8 (e4m3) GEMM for sm_100a: C[M, N] = (A ∘ sa) · (B ∘ sb)^T, bf16 or fp32 out.
+//
+//   A [M, K] e4m3 row-major, one fp32 scale per (row, 128-wide K block):      sa_t [K/128, M]   (K-block major)
+//   B [N, K] e4m3 row-major, one fp32 scale per (128-row, 128-wide K) block:  sb   [ceil(N/128), K/128]
+//   (the layout of a block-quantised checkpoint and of 1x128 activation quantisation)
+//
+// Because the scales change every 128 elements of K, each K block is multiplied on its own: four
+// tcgen05.mma.kind::f8f6f4 (128x128x32) fill a fresh TMEM accumulator, and the epilogue warps fold it into fp32
+// registers as acc += partial * sa[row] * sb[block] ("promotion") while the tensor core already works on the next K
+// block in the other TMEM accumulator. Warp roles: 0 = TMA producer (6-stage ring of 16 KB A + 16 KB B tiles,
+// 128-byte swizzle: one smem row = one K block), 1 = MMA issuer, 2..5 = promotion + store (one TMEM lane quarter each,
+// thread = output row). Persistent over output tiles. Every wait is bounded: on expiry the CTA records a status word,
+// stops issuing, frees its TMEM and returns.
+#include <string>
+
+#include "common.cuh"
+
+namespace sb {
+
+constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128;  // BK in elements = bytes
+constexpr int F8_STAGES = 6;
+constexpr int F8_THREADS = 192;
+constexpr int F8_TILE_BYTES = F8_BM * F8_BK;  // 16 KB (A tile and B tile alike)
+constexpr int F8_SMEM = F8_STAGES * 2 * F8_TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+
+template <bool OUT_F32>
+__global__ void __launch_bounds__(F8_THREADS, 1)
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const float* __restrict__ sa_t, const float* __restrict__ sb, void* __restrict__ Cv, int M, int N,
+                      int K, int ldc, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + F8_STAGES * F8_TILE_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * F8_STAGES * F8_TILE_BYTES);
+  uint64_t* empty = full + F8_STAGES;
+  uint64_t* acc_full = empty + F8_STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + F8_BM - 1) / F8_BM, tiles_n = (N + F8_BN - 1) / F8_BN;
+  const int num_tiles = tiles_m * tiles_n;
+  const int num_kb = K / F8_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F8_STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&acc_full[s], 1);
+      mbar_init(&acc_empty[s], 4);  // one arrival per promotion warp
+    }
+    *cta_abort = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * F8_BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+  pdl_launch_dependents();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        // m fastest: consecutive CTAs share the B tile (weights) through L2
+        const int m0 = (tile % tiles_m) * F8_BM, n0 = (tile / tiles_m) * F8_BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(&full[stage], 2 * F8_TILE_BYTES);
+          tma_load_2d(sA + stage * F8_TILE_BYTES, &tmA, &full[stage], kb * F8_BK, m0);
+          tma_load_2d(sB + stage * F8_TILE_BYTES, &tmB, &full[stage], kb * F8_BK, n0);
+          if (++stage == F8_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(F8_BM, F8_BN, 0, 0, 0, 0);  // e4m3 x e4m3, both K-major
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY) ||
+              !mbar_wait(&full[stage], phase, cta_abort, status, ERR_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(sA + stage * F8_TILE_BYTES), b_addr = smem_u32(sB + stage * F8_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < F8_BK / 32; ++k)  // 32 fp8 elements = 32 bytes along the swizzled row per instruction
+            umma_f8(tmem_base + acc * F8_BN, make_smem_desc(a_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
+                    make_smem_desc(b_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc, k != 0 ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          umma_commit(&acc_full[acc]);
+          if (++stage == F8_STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+          if (++acc == 2) {
+            acc = 0;
+            acc_phase ^= 1;
+          }
+        }
+      }
+    }
+  } else {
+    const int q = warp & 3;  // TMEM lane quarter of this warp
+    const int row_in_tile = q * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % tiles_m) * F8_BM, n0 = (tile / tiles_m) * F8_BN;
+      const int row = m0 + row_in_tile;
+      const float* sb_row = sb + static_cast<size_t>(n0 / F8_BN) * num_kb;
+      float c[F8_BN];
+#pragma unroll
+      for (int i = 0; i < F8_BN; ++i) c[i] = 0.f;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const float s = (row < M ? __ldg(sa_t + static_cast<size_t>(kb) * M + row) : 0.f) * __ldg(sb_row + kb);
+        ok = mbar_wait(&acc_full[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t t = tmem_base + acc * F8_BN + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+        for (int ch = 0; ch < F8_BN / 32; ++ch) {
+          uint32_t r[32];
+          tmem_ld_32x32(t + ch * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) c[ch * 32 + i] = fmaf(__uint_as_float(r[i]), s, c[ch * 32 + i]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[acc]);
+        if (++acc == 2) {
+          acc = 0;
+          acc_phase ^= 1;
+        }
+      }
+      if (ok && row < M) {
+        if constexpr (OUT_F32) {
+          float* dst = static_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + n0;
+          if (n0 + F8_BN <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < F8_BN; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+          } else {
+#pragma unroll
+            for (int i = 0; i < F8_BN; ++i)
+              if (n0 + i < N) dst[i] = c[i];
+          }
+        } else {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + n0;
+          if (n0 + F8_BN <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < F8_BN; i += 8) {
+              uint4 o;
+              o.x = pack_bf16x2(c[i], c[i + 1]); o.y = pack_bf16x2(c[i + 2], c[i + 3]);
+              o.z = pack_bf16x2(c[i + 4], c[i + 5]); o.w = pack_bf16x2(c[i + 6], c[i + 7]);
+              *reinterpret_cast<uint4*>(dst + i) = o;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < F8_BN; ++i)
+              if (n0 + i < N) dst[i] = __float2bfloat16(c[i]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, 2 * F8_BN);
+}
+
+}  // namespace sb
+
+// A, B: e4m3 bytes, row-major with pitches lda / ldb (bytes = elements; multiples of 16). sa_t: [K/128, M] fp32.
+// sb: [ceil(N/128), K/128] fp32. C: [M, N] bf16 (out_f32 = 0) or fp32, pitch ldc elements. K must be a multiple of 128.
+extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t, const float* sb, void* C, int M, int N,
+                                 int K, int lda, int ldb, int ldc, int out_f32, int* status, int num_sms,
+                                 cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K % sb::F8_BK != 0 || lda % 16 != 0 || ldb % 16 != 0) {
+    sb::set_last_error("sb_gemm_fp8_block: K must be a multiple of 128 and the row pitches multiples of 16 bytes");
+    return (int)cudaErrorInvalidValue;
+  }
+  try {
+    CUtensorMap tmA = sb::make_tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, size_t(lda), sb::F8_BM, sb::F8_BK,
+                                       CU_TENSOR_MAP_SWIZZLE_128B);
+    CUtensorMap tmB = sb::make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, size_t(ldb), sb::F8_BN, sb::F8_BK,
+                                       CU_TENSOR_MAP_SWIZZLE_128B);
+    const int tiles = ((M + sb::F8_BM - 1) / sb::F8_BM) * ((N + sb::F8_BN - 1) / sb::F8_BN);
+    const int grid = tiles < num_sms ? tiles : num_sms;
+    cudaError_t e;
+    if (out_f32) {
+      static bool configured = false;
+      if (!configured) {
+        e = cudaFuncSetAttribute(sb::gemm_fp8_block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::F8_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+      }
+      e = sb::launch_pdl(sb::gemm_fp8_block_kernel<true>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB, sa_t,
+                         sb, C, M, N, K, ldc, status);
+    } else {
+      static bool configured = false;
+      if (!configured) {
+        e = cudaFuncSetAttribute(sb::gemm_fp8_block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::F8_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+      }
+      e = sb::launch_pdl(sb::gemm_fp8_block_kernel<false>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB,
+                         sa_t, sb, C, M, N, K, ldc, status);
+    }
+    if (e != cudaSuccess) sb::set_last_error(std::string("fp8 gemm launch: ") + cudaGetErrorString(e));
+    return (int)e;
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
+    return (int)cudaErrorInvalidValue;
+  }
+}

@@ -484,6 +484,31 @@ def block_fp8_quant(x, block=(128, 128), pow2_scale=False):
     return q, s
 
 
+def fp8_block_gemm(a_q, a_scale, b_q, b_scale, out_dtype=torch.bfloat16):
+    """``(a_q * a_scale) @ (b_q * b_scale)^T`` for block-quantised e4m3 operands (W8A8 as block-fp8 checkpoints use it).
+
+    ``a_q`` [M, K] e4m3 with ``a_scale`` [M, K/128] (one scale per row and 128-wide K group: ``block_fp8_quant(x, (1, 128))``);
+    ``b_q`` [N, K] e4m3 with ``b_scale`` [ceil(N/128), K/128] (128 x 128 blocks). On CUDA the product runs on the tcgen05
+    fp8 tensor cores with per-K-block promotion to fp32; on CPU it is the dequantised fp32 product.
+    """
+    M, K = a_q.shape
+    N = b_q.shape[0]
+    assert b_q.shape[1] == K and K % 128 == 0, "K must be a multiple of the 128-wide scale block"
+    assert a_scale.shape == (M, K // 128) and b_scale.shape == (-(-N // 128), K // 128)
+    if not _cuda(a_q):
+        a = a_q.float() * a_scale.float().repeat_interleave(128, dim=1)
+        b = b_q.float() * b_scale.float().repeat_interleave(128, dim=0)[:N].repeat_interleave(128, dim=1)
+        return (a @ b.t()).to(out_dtype)
+    a_q, b_q = a_q.contiguous(), b_q.contiguous()
+    sa_t = a_scale.float().t().contiguous()  # [K/128, M]: the kernel reads one K block's row scales coalesced
+    out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
+    rc = _lib.lib().sb_gemm_fp8_block(P(a_q), P(b_q), P(sa_t), P(b_scale.float().contiguous()), P(out), M, N, K, a_q.stride(0),
+                                      b_q.stride(0), out.stride(0), int(out_dtype == torch.float32),
+                                      P(_lib.status_word(a_q.device)), _lib.sm_count(a_q.device), _lib.stream())  # fmt: skip
+    _lib.check(rc, "sb_gemm_fp8_block")
+    return out
+
+
 def block_fp8_dequant(q, scale_inv, block=(128, 128), dtype=torch.bfloat16):
     if not _cuda(q):
         return reference.block_fp8_dequant(q, scale_inv, block, dtype)
