@@ -5,11 +5,12 @@
 //   (the layout of a block-quantised checkpoint and of 1x128 activation quantisation)
 //
 // Because the scales change every 128 elements of K, each K block is multiplied on its own: four
-// tcgen05.mma.kind::f8f6f4 (128x128x32) fill a fresh TMEM accumulator, and the epilogue warps fold it into fp32
+// tcgen05.mma.kind::f8f6f4 (128x256x32) fill a fresh TMEM accumulator, and the epilogue warps fold it into fp32
 // registers as acc += partial * sa[row] * sb[block] ("promotion") while the tensor core already works on the next K
-// block in the other TMEM accumulator. Warp roles: 0 = TMA producer (6-stage ring of 16 KB A + 16 KB B tiles,
-// 128-byte swizzle: one smem row = one K block), 1 = MMA issuer, 2..5 = promotion + store (one TMEM lane quarter each,
-// thread = output row). Persistent over output tiles. Every wait is bounded: on expiry the CTA records a status word,
+// block in the other TMEM accumulator. Warp roles: 0 = TMA producer (4-stage ring of 16 KB A + 32 KB B tiles,
+// 128-byte swizzle: one smem row = one K block), 1 = MMA issuer, 2..9 = promotion + store (two warps per TMEM lane
+// quarter, one per 128-column half of the 128 x 256 tile, i.e. per B scale block; thread = output row, 128 fp32
+// accumulators in registers). Persistent over output tiles. Every wait is bounded: on expiry the CTA records a status word,
 // stops issuing, frees its TMEM and returns.
 #include <string>
 
@@ -17,11 +18,24 @@
 
 namespace sb {
 
-constexpr int F8_BM = 128, F8_BN = 128, F8_BK = 128;  // BK in elements = bytes
-constexpr int F8_STAGES = 6;
-constexpr int F8_THREADS = 192;
-constexpr int F8_TILE_BYTES = F8_BM * F8_BK;  // 16 KB (A tile and B tile alike)
-constexpr int F8_SMEM = F8_STAGES * 2 * F8_TILE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+constexpr int F8_BM = 128, F8_BN = 256, F8_BK = 128;  // BK in elements = bytes; BN = two 128-wide scale blocks
+constexpr int F8_STAGES = 4;
+constexpr int F8_NACC = 2;     // TMEM accumulators in flight (2 x 256 columns = all of TMEM)
+constexpr int F8_PANEL_M = 16;  // m-tiles per rasterisation panel
+constexpr int F8_THREADS = 320;  // producer warp, MMA warp, 8 promotion warps
+constexpr int F8_A_BYTES = F8_BM * F8_BK, F8_B_BYTES = F8_BN * F8_BK;  // 16 KB + 32 KB per stage
+constexpr int F8_STAGE_BYTES = F8_A_BYTES + F8_B_BYTES;
+constexpr int F8_SMEM = F8_STAGES * F8_STAGE_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+
+// Tiles are walked panel by panel: 16 m-tiles wide, m fastest inside a panel, so the ~148 tiles in flight touch about
+// 16 A row-blocks and 9 B row-blocks (25 x 128 x K bytes, L2-resident) instead of one B block and 148 A blocks.
+__device__ __forceinline__ void f8_tile_origin(int tile, int tiles_m, int tiles_n, int& m0, int& n0) {
+  const int per_panel = F8_PANEL_M * tiles_n;
+  const int panel = tile / per_panel, r = tile - panel * per_panel;
+  const int pm = min(F8_PANEL_M, tiles_m - panel * F8_PANEL_M);  // the last panel may be narrower
+  m0 = (panel * F8_PANEL_M + r % pm) * F8_BM;
+  n0 = (r / pm) * F8_BN;
+}
 
 template <bool OUT_F32>
 __global__ void __launch_bounds__(F8_THREADS, 1)
@@ -31,12 +45,12 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
-  uint8_t* sB = smem + F8_STAGES * F8_TILE_BYTES;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + 2 * F8_STAGES * F8_TILE_BYTES);
+  uint8_t* sB = smem + F8_STAGES * F8_A_BYTES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + F8_STAGES * F8_STAGE_BYTES);
   uint64_t* empty = full + F8_STAGES;
   uint64_t* acc_full = empty + F8_STAGES;
-  uint64_t* acc_empty = acc_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_empty = acc_full + F8_NACC;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + F8_NACC);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -49,9 +63,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < F8_NACC; ++s) {
       mbar_init(&acc_full[s], 1);
-      mbar_init(&acc_empty[s], 4);  // one arrival per promotion warp
+      mbar_init(&acc_empty[s], 8);  // one arrival per promotion warp
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -59,7 +73,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     tma_prefetch_desc(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 2 * F8_BN);
+    tmem_alloc(tmem_slot, F8_NACC * F8_BN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -75,16 +89,16 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        // m fastest: consecutive CTAs share the B tile (weights) through L2
-        const int m0 = (tile % tiles_m) * F8_BM, n0 = (tile / tiles_m) * F8_BN;
+        int m0, n0;
+        f8_tile_origin(tile, tiles_m, tiles_n, m0, n0);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(&full[stage], 2 * F8_TILE_BYTES);
-          tma_load_2d(sA + stage * F8_TILE_BYTES, &tmA, &full[stage], kb * F8_BK, m0);
-          tma_load_2d(sB + stage * F8_TILE_BYTES, &tmB, &full[stage], kb * F8_BK, n0);
+          mbar_arrive_expect_tx(&full[stage], F8_STAGE_BYTES);
+          tma_load_2d(sA + stage * F8_A_BYTES, &tmA, &full[stage], kb * F8_BK, m0);
+          tma_load_2d(sB + stage * F8_B_BYTES, &tmB, &full[stage], kb * F8_BK, n0);
           if (++stage == F8_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -106,7 +120,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             break;
           }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(sA + stage * F8_TILE_BYTES), b_addr = smem_u32(sB + stage * F8_TILE_BYTES);
+          const uint32_t a_addr = smem_u32(sA + stage * F8_A_BYTES), b_addr = smem_u32(sB + stage * F8_B_BYTES);
 #pragma unroll
           for (int k = 0; k < F8_BK / 32; ++k)  // 32 fp8 elements = 32 bytes along the swizzled row per instruction
             umma_f8(tmem_base + acc * F8_BN, make_smem_desc(a_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
@@ -117,7 +131,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             stage = 0;
             phase ^= 1;
           }
-          if (++acc == 2) {
+          if (++acc == F8_NACC) {
             acc = 0;
             acc_phase ^= 1;
           }
@@ -125,57 +139,75 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else {
-    const int q = warp & 3;  // TMEM lane quarter of this warp
+    constexpr int HALF = F8_BN / 2;  // 128 columns = one scale block of B
+    const int q = warp & 3;          // TMEM lane quarter of this warp
+    const int h = (warp - 2) >> 2;   // which 128-column half of the tile
     const int row_in_tile = q * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % tiles_m) * F8_BM, n0 = (tile / tiles_m) * F8_BN;
+      int m0, n0;
+      f8_tile_origin(tile, tiles_m, tiles_n, m0, n0);
       const int row = m0 + row_in_tile;
-      const float* sb_row = sb + static_cast<size_t>(n0 / F8_BN) * num_kb;
-      float c[F8_BN];
+      const int nblk = min(n0 / 128 + h, (N + 127) / 128 - 1);  // a tile's second half may lie past N: its scales are unused
+      const float* sb_row = sb + static_cast<size_t>(nblk) * num_kb;
+      float c[HALF];
 #pragma unroll
-      for (int i = 0; i < F8_BN; ++i) c[i] = 0.f;
+      for (int i = 0; i < HALF; ++i) c[i] = 0.f;
+      // the scales of a K block are fetched two blocks ahead: a global load issued inside the iteration that needs it
+      // would put its full latency on the critical path of every block
+      auto load_scale = [&](int kb) -> float {
+        if (kb >= num_kb) return 0.f;
+        return (row < M ? __ldg(sa_t + static_cast<size_t>(kb) * M + row) : 0.f) * __ldg(sb_row + kb);
+      };
+      float s_cur = load_scale(0), s_next = load_scale(1);
       for (int kb = 0; kb < num_kb; ++kb) {
-        const float s = (row < M ? __ldg(sa_t + static_cast<size_t>(kb) * M + row) : 0.f) * __ldg(sb_row + kb);
+        const float s = s_cur;
+        s_cur = s_next;
+        s_next = load_scale(kb + 2);
         ok = mbar_wait(&acc_full[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t t = tmem_base + acc * F8_BN + (static_cast<uint32_t>(q * 32) << 16);
+        const uint32_t t = tmem_base + acc * F8_BN + h * HALF + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll
-        for (int ch = 0; ch < F8_BN / 32; ++ch) {
-          uint32_t r[32];
-          tmem_ld_32x32(t + ch * 32, r);
+        for (int pass = 0; pass < 2; ++pass) {
+          uint32_t r0[32], r1[32];
+          tmem_ld_32x32(t + pass * 64, r0);  // both loads in flight before the wait
+          tmem_ld_32x32(t + pass * 64 + 32, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) c[ch * 32 + i] = fmaf(__uint_as_float(r[i]), s, c[ch * 32 + i]);
+          for (int i = 0; i < 32; ++i) {
+            c[pass * 64 + i] = fmaf(__uint_as_float(r0[i]), s, c[pass * 64 + i]);
+            c[pass * 64 + 32 + i] = fmaf(__uint_as_float(r1[i]), s, c[pass * 64 + 32 + i]);
+          }
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&acc_empty[acc]);
-        if (++acc == 2) {
+        if (++acc == F8_NACC) {
           acc = 0;
           acc_phase ^= 1;
         }
       }
-      if (ok && row < M) {
+      const int col0 = n0 + h * HALF;
+      if (ok && row < M && col0 < N) {
         if constexpr (OUT_F32) {
-          float* dst = static_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + n0;
-          if (n0 + F8_BN <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          float* dst = static_cast<float*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+          if (col0 + HALF <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-            for (int i = 0; i < F8_BN; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
+            for (int i = 0; i < HALF; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(c[i], c[i + 1], c[i + 2], c[i + 3]);
           } else {
 #pragma unroll
-            for (int i = 0; i < F8_BN; ++i)
-              if (n0 + i < N) dst[i] = c[i];
+            for (int i = 0; i < HALF; ++i)
+              if (col0 + i < N) dst[i] = c[i];
           }
         } else {
-          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + n0;
-          if (n0 + F8_BN <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(Cv) + static_cast<size_t>(row) * ldc + col0;
+          if (col0 + HALF <= N && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
-            for (int i = 0; i < F8_BN; i += 8) {
+            for (int i = 0; i < HALF; i += 8) {
               uint4 o;
               o.x = pack_bf16x2(c[i], c[i + 1]); o.y = pack_bf16x2(c[i + 2], c[i + 3]);
               o.z = pack_bf16x2(c[i + 4], c[i + 5]); o.w = pack_bf16x2(c[i + 6], c[i + 7]);
@@ -183,8 +215,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             }
           } else {
 #pragma unroll
-            for (int i = 0; i < F8_BN; ++i)
-              if (n0 + i < N) dst[i] = __float2bfloat16(c[i]);
+            for (int i = 0; i < HALF; ++i)
+              if (col0 + i < N) dst[i] = __float2bfloat16(c[i]);
           }
         }
       }
@@ -193,7 +225,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) tmem_dealloc(tmem_base, 2 * F8_BN);
+  if (warp == 1) tmem_dealloc(tmem_base, F8_NACC * F8_BN);
 }
 
 }  // namespace sb

@@ -37,6 +37,38 @@ block_fp8_quant_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __res
   }
 }
 
+// 1 x 128 groups (activation quantisation): one warp per group, lane = 4 consecutive elements. Scales go to
+// scale_inv[row, group] and, when scale_t is given, also to scale_t[group, row] (the layout the fp8 GEMM reads).
+__global__ void __launch_bounds__(256)
+group_fp8_quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_e4m3* __restrict__ q, float* __restrict__ scale_inv,
+                             float* __restrict__ scale_t, int M, int groups, size_t ldx, size_t ldq, int pow2_scale) {
+  const int lane = threadIdx.x & 31;
+  const size_t total = static_cast<size_t>(M) * groups;
+  for (size_t g = static_cast<size_t>(blockIdx.x) * 8 + (threadIdx.x >> 5); g < total; g += static_cast<size_t>(gridDim.x) * 8) {
+    const size_t row = g / groups;
+    const int grp = static_cast<int>(g - row * groups);
+    const uint2 u = *reinterpret_cast<const uint2*>(x + row * ldx + grp * 128 + lane * 4);
+    const float2 a = unpack_bf16x2(u.x), b = unpack_bf16x2(u.y);
+    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+    amax = warp_max(amax);
+    float scale = fmaxf(amax, 1e-10f) / 448.f;
+    if (pow2_scale) scale = exp2f(ceilf(log2f(scale)));
+    const float inv = 1.f / scale;
+    if (lane == 0) {
+      scale_inv[g] = scale;
+      if (scale_t != nullptr) scale_t[static_cast<size_t>(grp) * M + row] = scale;
+    }
+    const float v[4] = {a.x * inv, a.y * inv, b.x * inv, b.y * inv};
+    uint32_t packed = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_fp8_e4m3 f(fminf(fmaxf(v[i], -448.f), 448.f));
+      packed |= static_cast<uint32_t>(*reinterpret_cast<const uint8_t*>(&f)) << (8 * i);
+    }
+    *reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(q) + row * ldq + grp * 128 + lane * 4) = packed;
+  }
+}
+
 __global__ void __launch_bounds__(256)
 block_fp8_dequant_kernel(const __nv_fp8_e4m3* __restrict__ q, const float* __restrict__ scale_inv,
                          __nv_bfloat16* __restrict__ out, int M, int N, int BM, int BN, int nbc) {
@@ -136,9 +168,33 @@ router_gemm_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __
 extern "C" int sb_block_fp8_quant(const void* x, void* q, float* scale_inv, int M, int N, long ldx, long ldq, int BM,
                                   int BN, int pow2_scale, cudaStream_t s) {
   if (M == 0 || N == 0) return 0;
+  if (BM == 1 && BN == 128 && N % 128 == 0 && ldx % 4 == 0 && ldq % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
+      (reinterpret_cast<uintptr_t>(q) & 3) == 0) {
+    const long total = (long)M * (N / 128);
+    long blocks = (total + 7) / 8;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    sb::group_fp8_quant_1x128_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)q, scale_inv, nullptr,
+                                                                 M, N / 128, (size_t)ldx, (size_t)ldq, pow2_scale);
+    return (int)cudaGetLastError();
+  }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   sb::block_fp8_quant_kernel<<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)q, scale_inv, M, N, (size_t)ldx,
                                                  (size_t)ldq, BM, BN, pow2_scale);
+  return (int)cudaGetLastError();
+}
+
+// 1 x 128 activation quantisation that also writes the scales K-block major ([N/128, M]) for sb_gemm_fp8_block.
+extern "C" int sb_group_fp8_quant_1x128(const void* x, void* q, float* scale_inv, float* scale_t, int M, int N, long ldx,
+                                        long ldq, int pow2_scale, cudaStream_t s) {
+  if (M == 0 || N == 0) return 0;
+  if (N % 128 != 0 || ldx % 4 != 0 || ldq % 4 != 0 || (reinterpret_cast<uintptr_t>(x) & 7) != 0 ||
+      (reinterpret_cast<uintptr_t>(q) & 3) != 0)
+    return (int)cudaErrorInvalidValue;
+  const long total = (long)M * (N / 128);
+  long blocks = (total + 7) / 8;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  sb::group_fp8_quant_1x128_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_fp8_e4m3*)q, scale_inv, scale_t, M,
+                                                               N / 128, (size_t)ldx, (size_t)ldq, pow2_scale);
   return (int)cudaGetLastError();
 }
 

@@ -484,7 +484,24 @@ def block_fp8_quant(x, block=(128, 128), pow2_scale=False):
     return q, s
 
 
-def fp8_block_gemm(a_q, a_scale, b_q, b_scale, out_dtype=torch.bfloat16):
+def fp8_act_quant(x, pow2_scale=False):
+    """1 x 128 activation quantisation to e4m3 -> (q [M, K], scale [M, K/128], scale_t [K/128, M]); ``scale_t`` is the
+    K-block-major copy the fp8 GEMM reads (pass it as ``a_scale_t`` to skip a transpose)."""
+    M, K = x.shape
+    assert K % 128 == 0
+    if not _cuda(x):
+        q, s = reference.block_fp8_quant(x, (1, 128), pow2_scale)
+        return q, s, s.t().contiguous()
+    x = x.contiguous()
+    q = torch.empty(M, K, dtype=torch.float8_e4m3fn, device=x.device)
+    s = torch.empty(M, K // 128, dtype=torch.float32, device=x.device)
+    st = torch.empty(K // 128, M, dtype=torch.float32, device=x.device)
+    rc = _lib.lib().sb_group_fp8_quant_1x128(P(x), P(q), P(s), P(st), M, K, x.stride(0), q.stride(0), int(pow2_scale), _lib.stream())
+    _lib.check(rc, "sb_group_fp8_quant_1x128")
+    return q, s, st
+
+
+def fp8_block_gemm(a_q, a_scale, b_q, b_scale, out_dtype=torch.bfloat16, a_scale_t=None):
     """``(a_q * a_scale) @ (b_q * b_scale)^T`` for block-quantised e4m3 operands (W8A8 as block-fp8 checkpoints use it).
 
     ``a_q`` [M, K] e4m3 with ``a_scale`` [M, K/128] (one scale per row and 128-wide K group: ``block_fp8_quant(x, (1, 128))``);
@@ -500,7 +517,8 @@ def fp8_block_gemm(a_q, a_scale, b_q, b_scale, out_dtype=torch.bfloat16):
         b = b_q.float() * b_scale.float().repeat_interleave(128, dim=0)[:N].repeat_interleave(128, dim=1)
         return (a @ b.t()).to(out_dtype)
     a_q, b_q = a_q.contiguous(), b_q.contiguous()
-    sa_t = a_scale.float().t().contiguous()  # [K/128, M]: the kernel reads one K block's row scales coalesced
+    # [K/128, M]: the kernel reads one K block's row scales coalesced
+    sa_t = a_scale_t if a_scale_t is not None else a_scale.float().t().contiguous()
     out = torch.empty(M, N, dtype=out_dtype, device=a_q.device)
     rc = _lib.lib().sb_gemm_fp8_block(P(a_q), P(b_q), P(sa_t), P(b_scale.float().contiguous()), P(out), M, N, K, a_q.stride(0),
                                       b_q.stride(0), out.stride(0), int(out_dtype == torch.float32),

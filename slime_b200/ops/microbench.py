@@ -191,9 +191,70 @@ def bench_norm(a):
         _emit(kind="rmsnorm_bwd", T=T, H=H, ms=t, gbs=4 * T * H * 2 / t / 1e6)  # read dy, dres, h; write dh
 
 
+def bench_fp8(a):
+    """Block-scaled fp8 GEMM against this library's bf16 GEMM and torch._scaled_mm (per-tensor scales: a different,
+    cheaper scaling scheme, shown only as the library fp8 ceiling)."""
+    shapes = [(4096, 4096, 7168), (16384, 2048, 7168), (8192, 1536, 2048), (256, 4096, 7168)] if not a.small else [(1024, 1024, 1024)]
+    for M, N, K in shapes:
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.1
+        xq, xs = ops.block_fp8_quant(x, (1, 128))
+        wq, ws = ops.block_fp8_quant(w, (128, 128))
+        fl = 2.0 * M * N * K
+        t = time_ms(lambda: ops.fp8_block_gemm(xq, xs, wq, ws), a.iters)
+        _emit(kind="fp8_block", M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9)
+        t = time_ms(lambda: ops.gemm(x, w), a.iters)
+        _emit(kind="bf16_ours", M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9)
+        t = time_ms(lambda: ops.fp8_act_quant(x), a.iters)
+        _emit(kind="act_quant_1x128", M=M, K=K, ms=t, gbs=3.0 * M * K / t / 1e6)
+        if not a.no_cublas:
+            one = torch.ones((), device="cuda")
+            try:
+                t = time_ms(lambda: torch._scaled_mm(xq, wq.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16), a.iters)
+                _emit(kind="scaled_mm_per_tensor", M=M, N=N, K=K, ms=t, tflops=fl / t / 1e9)
+            except Exception as e:  # noqa: BLE001
+                _emit(kind="scaled_mm_per_tensor", error=repr(e)[:200])
+    _lib.check_status("cuda")
+
+
+def bench_moe(a):
+    """Expert MLP of Qwen3-30B-A3B (hidden 2048, expert FFN 768, 16 local experts of 128 under EP8): grouped GEMMs
+    against the per-expert loop over the same GEMM kernel, for a training-sized and a decode-sized token count."""
+    from slime_b200.ops import grouped
+
+    E, H, F = 16, 2048, 768
+    w13 = torch.randn(E, 2 * F, H, device="cuda", dtype=torch.bfloat16) * 0.02
+    w2 = torch.randn(E, H, F, device="cuda", dtype=torch.bfloat16) * 0.02
+    for rows in ((16384, 2048) if not a.small else (2048,)):
+        g = torch.Generator(device="cuda").manual_seed(rows)
+        cuts = torch.sort(torch.randint(0, rows, (E - 1,), device="cuda", generator=g)).values.tolist()
+        counts = [b - c for c, b in zip([0] + cuts, cuts + [rows])]
+        x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+        lay = grouped.PaddedLayout(counts, "cuda")
+        xp = lay.pad(x)
+
+        def fused():
+            return grouped.grouped_gemm(ops.swiglu(grouped.grouped_gemm(xp, w13, lay)), w2, lay)
+
+        def loop():
+            outs, s = [], 0
+            for e, n in enumerate(counts):
+                if n:
+                    outs.append(ops.gemm(ops.swiglu(ops.gemm(x[s : s + n], w13[e])), w2[e]))
+                    s += n
+            return outs
+
+        fl = 2.0 * rows * (2 * F * H + H * F)
+        t = time_ms(fused, a.iters)
+        _emit(kind="moe_grouped", rows=rows, experts=E, ms=t, tflops=fl / t / 1e9)
+        t = time_ms(loop, a.iters)
+        _emit(kind="moe_expert_loop", rows=rows, experts=E, ms=t, tflops=fl / t / 1e9)
+    _lib.check_status("cuda")
+
+
 def main(argv=None):
     p = argparse.ArgumentParser(prog="python -m slime_b200.ops.microbench")
-    p.add_argument("what", choices=["gemm", "decode", "norm"])
+    p.add_argument("what", choices=["gemm", "decode", "norm", "fp8", "moe"])
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--reps", type=int, default=20, help="back-to-back launches per timed repetition (decode)")
     p.add_argument("--small", action="store_true")
@@ -206,7 +267,7 @@ def main(argv=None):
     from slime_b200.ops import build
 
     build.build()
-    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm}[a.what](a)
+    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm, "fp8": bench_fp8, "moe": bench_moe}[a.what](a)
 
 
 if __name__ == "__main__":
