@@ -126,3 +126,34 @@ def test_model_presets_round_trip_through_flags():
     with pytest.raises(KeyError, match="MLA"):
         get_preset("kimi-k2")
     assert get_preset("qwen3-235b-a22b").num_params() > 2.3e11
+
+
+def test_run_recipes_produce_parseable_command_lines(tmp_path):
+    """Every recipe, in DRY_RUN mode, prints a command line that the argument parser accepts."""
+    import glob
+    import os
+    import subprocess
+
+    ckpt, data = tmp_path / "ckpt", tmp_path / "data"
+    for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist"):
+        (ckpt / d).mkdir(parents=True)
+    for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl"):
+        (data / f).parent.mkdir(parents=True, exist_ok=True)
+        (data / f).write_text("")
+
+    from slime_b200.utils.arguments import parse_args
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    scripts = sorted(glob.glob(os.path.join(root, "recipes", "run-*.sh")))
+    assert len(scripts) >= 4
+    for script in scripts:
+        r = subprocess.run(["bash", script], env=dict(os.environ, DRY_RUN="1", NUM_GPUS="8", CKPT_DIR=str(ckpt), DATA_DIR=str(data)), capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-2000:]
+        argv = r.stdout.strip().split("\n")
+        assert argv[0] in ("train.py", "train_async.py")
+        args = parse_args(argv[1:])
+        assert args.num_layers > 0 and args.rollout_batch_size == 32 and args.n_samples_per_prompt == 8
+        if "30B" in script:
+            assert args.num_experts == 128 and args.expert_model_parallel_size == 8 and args.sglang_ep_size == 8
+        if "async" in script:
+            assert args.rollout_function_path.endswith("generate_rollout_fully_async") and not args.colocate
