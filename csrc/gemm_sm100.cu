@@ -52,11 +52,25 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, 
   n0 = (r / pm) * BN;
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
+// Optional extra kernel parameter. NoExtra: nothing. AllGatherA: the rows of A are spread over up to 8 GPUs (rank r holds
+// rows [r * rows_per_rank, (r + 1) * rows_per_rank) in its own buffer, reachable through peer memory): the producer
+// picks the tensor map of the GPU that owns a tile's rows, so the all-gather of a sequence-parallel activation happens
+// inside the GEMM's operand loads (plain TMA loads from peer memory, no multicast) and is never materialised.
+struct NoExtra {
+  static constexpr bool kAllGather = false;
+};
+struct AllGatherA {
+  static constexpr bool kAllGather = true;
+  CUtensorMap maps[8];
+  int rows_per_rank;
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI, typename Extra = NoExtra>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv, const __nv_bfloat16* __restrict__ bias,
-                 int M, int N, int K, int ldc, int accumulate, int* status, const int* __restrict__ tile_boff) {
+                 int M, int N, int K, int ldc, int accumulate, int* status, const int* __restrict__ tile_boff,
+                 const __grid_constant__ Extra extra) {
   using S = GemmSmem<BN, STAGES>;
   constexpr int NCOLS = 2 * BN;  // two accumulator stages (power of two: 256 or 512)
   extern __shared__ uint8_t smem_raw[];
@@ -132,7 +146,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_arrive_expect_tx(&full[stage], S::STAGE_BYTES);
           uint8_t* a_dst = sA + stage * S::A_BYTES;
           uint8_t* b_dst = sB + stage * S::B_BYTES;
-          if constexpr (!A_MN) {
+          if constexpr (Extra::kAllGather) {
+            static_assert(!Extra::kAllGather || !A_MN, "the gathered operand is row-major [rows, K]");
+            const int owner = m0 / extra.rows_per_rank;  // rows_per_rank is a multiple of the row tile
+            tma_load_2d(a_dst, &extra.maps[owner], &full[stage], kb * GEMM_BK, m0 - owner * extra.rows_per_rank);
+          } else if constexpr (!A_MN) {
             tma_load_2d(a_dst, &tmA, &full[stage], kb * GEMM_BK, m0);
           } else {
 #pragma unroll
@@ -339,10 +357,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 1) tmem_dealloc(tmem_base, NCOLS);
 }
 
-template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI>
+template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI, typename Extra = NoExtra>
 static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda,
                                int ldb, int ldc, int accumulate, int* status, int num_sms, cudaStream_t stream,
-                               const int* tile_boff = nullptr, int b_stack_rows = 0) {
+                               const int* tile_boff = nullptr, int b_stack_rows = 0, const Extra& extra = Extra()) {
   using S = GemmSmem<BN, STAGES>;
   // K-major operand: tensor [rows = M or N, cols = K], box [rows_tile, 64].
   // MN-major operand: tensor [rows = K, cols = M or N], box [64 k-rows, 64 cols].
@@ -363,7 +381,7 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
                   : make_tmap_2d(C, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, N, size_t(ldc) * 2, 32, 64,
                                  CU_TENSOR_MAP_SWIZZLE_128B);
   }
-  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32, TMA_EPI>;
+  auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32, TMA_EPI, Extra>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
@@ -377,7 +395,7 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
   const int grid = tiles < num_sms ? tiles : num_sms;
   cudaError_t le = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, tmC, C,
-                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status, tile_boff);
+                              reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status, tile_boff, extra);
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
   return le;
 }
@@ -478,6 +496,50 @@ extern "C" int sb_gemm_bf16_grouped(const void* A, const void* B, void* C, const
                                                     status, num_sms, stream, tile_boff, stack_rows);
     return (int)sb::dispatch_layout<128, 6, false>(false, b_mn != 0, out_f32 != 0, A, B, C, nullptr, M, N, K, lda, ldb, ldc, 0,
                                                    status, num_sms, stream, tile_boff, stack_rows);
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
+    return (int)cudaErrorInvalidValue;
+  }
+}
+
+// All-gather fused into the GEMM: C[M, N] = gather(A_0 .. A_{world-1}) * B^T (+ bias), where A_r [rows_per_rank, K]
+// (row-major, pitch lda) lives on GPU r and a_ptrs[r] is its address as seen from this GPU (own buffer or peer
+// mapping). M = world * rows_per_rank; rows_per_rank must be a multiple of 128. B [N, K] row-major, C bf16 or fp32.
+// The caller makes sure (barrier) that every A_r is complete before the launch and not rewritten before it ends.
+extern "C" int sb_gemm_bf16_allgather_a(const void* const* a_ptrs, int world, int rows_per_rank, const void* B, void* C,
+                                        const void* bias, int N, int K, int lda, int ldb, int ldc, int out_f32, int bn,
+                                        int* status, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rows_per_rank <= 0 || rows_per_rank % sb::GEMM_BM != 0) {
+    sb::set_last_error("sb_gemm_bf16_allgather_a: 1..8 ranks, rows_per_rank a positive multiple of 128");
+    return (int)cudaErrorInvalidValue;
+  }
+  const int M = world * rows_per_rank;
+  const size_t c_elem = out_f32 ? 4 : 2;
+  const bool tma_epi = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * c_elem) % 16 == 0;
+  try {
+    sb::AllGatherA ex{};
+    ex.rows_per_rank = rows_per_rank;
+    for (int r = 0; r < world; ++r)
+      ex.maps[r] = sb::make_tmap_2d(a_ptrs[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, size_t(lda) * 2,
+                                    sb::GEMM_BM, sb::GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
+    for (int r = world; r < 8; ++r) ex.maps[r] = ex.maps[0];
+    const void* A0 = a_ptrs[0];
+#define SB_AG(BNV, ST, OF, TE)                                                                                            \
+  return (int)sb::launch_gemm<BNV, ST, false, false, OF, TE, sb::AllGatherA>(A0, B, C, bias, M, N, K, lda, ldb, ldc, 0, status, \
+                                                                             num_sms, stream, nullptr, 0, ex);
+    if (bn == 256) {
+      if (out_f32) {
+        if (tma_epi) { SB_AG(256, 4, true, true) } else { SB_AG(256, 4, true, false) }
+      } else {
+        if (tma_epi) { SB_AG(256, 4, false, true) } else { SB_AG(256, 4, false, false) }
+      }
+    }
+    if (out_f32) {
+      if (tma_epi) { SB_AG(128, 6, true, true) } else { SB_AG(128, 6, true, false) }
+    } else {
+      if (tma_epi) { SB_AG(128, 6, false, true) } else { SB_AG(128, 6, false, false) }
+    }
+#undef SB_AG
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;

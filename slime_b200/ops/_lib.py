@@ -35,6 +35,7 @@ _SIGS = {
     "sb_dp_adam_bcast": [P, P, P, P, P, I, I, I, L, L, F, F, F, F, F, F, F, F, F, P, I, P],
     "sb_group_fp8_quant_1x128": [P, P, P, P, I, I, L, L, I, P],
     "sb_gemm_fp8_block": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, P],
+    "sb_gemm_bf16_allgather_a": [P, I, I, P, P, P, I, I, I, I, I, I, I, P, I, P],
     "sb_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "sb_gemm_bf16_splitk": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "sb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],

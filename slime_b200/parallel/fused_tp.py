@@ -85,3 +85,60 @@ class FusedAllReduceNorm:
         self._lib.check(rc, "sb_tp_ar_add_rmsnorm")
         self._which ^= 1
         return y, r
+
+
+class AllGatherGemm:
+    """``gather_rows(x_0 .. x_{n-1}) @ W^T`` with the gather done by the GEMM's own operand loads.
+
+    Sequence-parallel column-parallel linears (QKV, gate/up) take an activation that is sharded by rows over the
+    tensor-parallel ranks. Each rank writes its shard into a symmetric buffer; after one bounded barrier the tcgen05
+    GEMM on every rank reads the row tiles it needs straight from the owning GPU (plain TMA loads over NVLink), so the
+    gathered activation never exists in memory and no NCCL all-gather runs.
+
+        ag = AllGatherGemm(tp_group, max_rows_per_rank, K, device)
+        ag.shard(rows).copy_(x_local)             # or let the producing kernel write there
+        y = ag(rows, weight)                      # [world * rows, N]
+
+    ``rows`` (per rank) must be a multiple of 128. Two buffers alternate, so a rank may refill its shard for the next
+    call while slower ranks still read the previous one; the barrier at the start of every call keeps two calls apart.
+    """
+
+    def __init__(self, group, max_rows_per_rank: int, k: int, device):
+        from slime_b200.ops import _lib
+
+        self._lib = _lib
+        self.k, self.max_rows, self.device = k, max_rows_per_rank, torch.device(device)
+        self.bufs = [SymmetricStorage(max_rows_per_rank * k, torch.bfloat16, device, group) for _ in range(2)]
+        self.world, self.rank = self.bufs[0].world, self.bufs[0].rank
+        self._pads = (ctypes.c_void_p * self.world)(*self.bufs[0].pad_ptrs)
+        self._pad_base = self.bufs[0].pad_words - 48
+        self._counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._which = 0
+        torch.cuda.synchronize(self.device)
+        import torch.distributed as dist
+
+        dist.barrier(group=group)
+
+    def shard(self, rows: int) -> torch.Tensor:
+        assert rows <= self.max_rows and rows % 128 == 0, f"{rows} rows per rank: need a multiple of 128 up to {self.max_rows}"
+        return self.bufs[self._which].tensor[: rows * self.k].view(rows, self.k)
+
+    def __call__(self, rows: int, weight: torch.Tensor, bias=None, out_dtype=torch.bfloat16) -> torch.Tensor:
+        from slime_b200.ops import _pick_bn
+
+        lib, P = self._lib.lib(), self._lib.ptr
+        buf = self.bufs[self._which]
+        rc = lib.sb_symm_barrier_dev(self._pads, self.rank, self.world, P(self._counter), self._pad_base,
+                                     P(self._lib.status_word(self.device)), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_symm_barrier_dev")
+        n = weight.shape[0]
+        m = rows * self.world
+        out = torch.empty(m, n, dtype=out_dtype, device=self.device)
+        ptrs = (ctypes.c_void_p * self.world)(*buf.ptrs)
+        rc = lib.sb_gemm_bf16_allgather_a(ptrs, self.world, rows, P(weight), P(out), P(bias), n, self.k, self.k,
+                                          weight.stride(0), out.stride(0), int(out_dtype == torch.float32), _pick_bn(m, n),
+                                          P(self._lib.status_word(self.device)), self._lib.sm_count(self.device),
+                                          self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_gemm_bf16_allgather_a")
+        self._which ^= 1
+        return out

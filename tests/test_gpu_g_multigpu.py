@@ -46,3 +46,10 @@ def test_tensor_parallel_engine_matches_single_gpu(kernels):
     _need(2)
     r = _torchrun("tests/multigpu/engine_tp_check.py", 2, timeout=180)
     assert r.returncode == 0 and "RESULT ok" in r.stdout and "fused_tp=True" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_allgather_fused_gemm_matches_nccl_path(kernels):
+    _need(2)
+    n = min(torch.cuda.device_count(), 8)
+    r = _torchrun("tests/multigpu/ag_gemm_check.py", n, timeout=240)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
