@@ -27,16 +27,18 @@ def main():
     for step, (rows, dtype, use_bias) in enumerate([(128, torch.bfloat16, False), (384, torch.float32, True), (4096, torch.bfloat16, True)]):
         g = torch.Generator(device=dev).manual_seed(10 * step + rank)
         x = torch.randn(rows, K, device=dev, generator=g).to(torch.bfloat16)
-        ag.shard(rows).copy_(x)
-        y = ag(rows, w, bias if use_bias else None, out_dtype=dtype)
         full = torch.empty(world * rows, K, device=dev, dtype=torch.bfloat16)
         dist.all_gather_into_tensor(full, x)
         ref = ops.gemm(full, w, bias=bias if use_bias else None, out_dtype=dtype)
-        torch.cuda.synchronize()
-        _lib.check_status(dev)
-        assert torch.equal(y, ref), f"step {step}: fused and unfused GEMM differ by {(y.float() - ref.float()).abs().max()}"
         exact = full.float() @ w.float().t() + (bias.float() if use_bias else 0)
-        assert (y.float() - exact).abs().max() <= 0.02 * exact.abs().max()
+        for mode in ("direct", "staged"):
+            ag.shard(rows).copy_(x)
+            y = ag(rows, w, bias if use_bias else None, out_dtype=dtype, mode=mode)
+            torch.cuda.synchronize()
+            _lib.check_status(dev)
+            assert (y.float() - exact).abs().max() <= 0.02 * exact.abs().max(), (step, mode)
+            if mode == "direct":  # same kernel, same tiles: bit-identical to the unfused GEMM
+                assert torch.equal(y, ref), f"step {step}: fused and unfused GEMM differ by {(y.float() - ref.float()).abs().max()}"
 
     rows = 4096
     x = torch.randn(rows, K, device=dev).to(torch.bfloat16)
@@ -61,16 +63,23 @@ def main():
         dist.all_gather_into_tensor(full, x)
         ops.gemm(full, w)
 
-    def fused_path():
+    def fused_path(mode, weight):
         ag.shard(rows).copy_(x)
-        ag(rows, w)
+        ag(rows, weight, mode=mode)
 
-    t_nccl, t_fused, t_gemm = timed(nccl_path), timed(fused_path), timed(lambda: ops.gemm(full, w))
+    t_nccl, t_gemm = timed(nccl_path), timed(lambda: ops.gemm(full, w))
+    t_direct, t_staged = timed(lambda: fused_path("direct", w)), timed(lambda: fused_path("staged", w))
+    w_narrow = w[:256].contiguous()
+
+    def nccl_narrow():
+        dist.all_gather_into_tensor(full, x)
+        ops.gemm(full, w_narrow)
+
+    t_nccl_n, t_direct_n = timed(nccl_narrow), timed(lambda: fused_path("direct", w_narrow))
     _lib.check_status(dev)
     if rank == 0:
-        fl = 2.0 * world * rows * N * K
-        print(f"RESULT ok world={world} M={world * rows} N={N} K={K} nccl_ag_plus_gemm_us={t_nccl:.1f} fused_us={t_fused:.1f} "
-              f"gemm_only_us={t_gemm:.1f} fused_tflops={fl / t_fused / 1e6:.0f}", flush=True)
+        print(f"RESULT ok world={world} M={world * rows} N={N} K={K} nccl_ag_plus_gemm_us={t_nccl:.1f} direct_us={t_direct:.1f} "
+              f"staged_us={t_staged:.1f} gemm_only_us={t_gemm:.1f} | N=256: nccl_us={t_nccl_n:.1f} direct_us={t_direct_n:.1f}", flush=True)
     dist.destroy_process_group()
 
 
