@@ -34,6 +34,9 @@ _SIGS = {
     "sb_dp_reduce_shard": [P, I, I, I, L, L, P, P, P, P],
     "sb_dp_adam_bcast": [P, P, P, P, P, I, I, I, L, L, F, F, F, F, F, F, F, F, F, P, I, P],
     "sb_group_fp8_quant_1x128": [P, P, P, P, I, I, L, L, I, P],
+    "sb_moe_scatter_rows": [P, P, P, L, I, I, P],
+    "sb_moe_gather_sum": [P, P, P, P, L, I, I, I, P],
+    "sb_moe_route_weight_grad": [P, P, P, P, L, I, I, P],
     "sb_gemm_fp8_block": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, P],
     "sb_gemm_bf16_allgather_a": [P, I, I, P, P, P, I, I, I, I, I, I, I, P, I, P],
     "sb_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],

@@ -26,6 +26,92 @@ TILE = 128
 P = _lib.ptr
 
 
+def scatter_rows(x: torch.Tensor, dest: torch.Tensor, k: int, num_rows: int) -> torch.Tensor:
+    """``out[dest[s]] = x[s // k]`` for every route slot ``s`` with ``dest[s] >= 0``; other rows of ``out`` are zero."""
+    out = x.new_zeros(num_rows, x.shape[-1])
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+        rc = _lib.lib().sb_moe_scatter_rows(P(x.contiguous()), P(dest), P(out), dest.numel(), k, x.shape[-1], _lib.stream())
+        _lib.check(rc, "sb_moe_scatter_rows")
+        return out
+    keep = dest >= 0
+    src = torch.arange(dest.numel(), device=dest.device)[keep] // k
+    out[dest[keep].long()] = x[src]
+    return out
+
+
+def gather_sum(rows: torch.Tensor, dest: torch.Tensor, weights: torch.Tensor | None, k: int, round_each: bool = False):
+    """``y[t] = sum_j weights[t*k+j] * rows[dest[t*k+j]]`` in route order ``j = 0..k-1`` (fp32 accumulation, one writer
+    per element: deterministic). Routes with ``dest < 0`` are skipped."""
+    T, H = dest.numel() // k, rows.shape[-1]
+    if rows.is_cuda and rows.dtype == torch.bfloat16 and H % 8 == 0:
+        y = torch.empty(T, H, dtype=rows.dtype, device=rows.device)
+        w = None if weights is None else weights.reshape(-1).float().contiguous()
+        rc = _lib.lib().sb_moe_gather_sum(P(rows.contiguous()), P(dest), P(w), P(y), T, k, H, int(round_each), _lib.stream())
+        _lib.check(rc, "sb_moe_gather_sum")
+        return y
+    d = dest.view(T, k).long()
+    w = torch.ones(T, k, device=rows.device) if weights is None else weights.reshape(T, k).float()
+    acc = torch.zeros(T, H, dtype=torch.float32, device=rows.device)
+    for j in range(k):
+        ok = (d[:, j] >= 0).float()[:, None]
+        acc = acc + ok * w[:, j, None] * rows[d[:, j].clamp_min(0)].float()
+        if round_each:
+            acc = acc.to(rows.dtype).float()
+    return acc.to(rows.dtype)
+
+
+def route_weight_grad(rows: torch.Tensor, dest: torch.Tensor, dy: torch.Tensor, k: int) -> torch.Tensor:
+    """``dw[s] = <rows[dest[s]], dy[s // k]>`` (0 where ``dest[s] < 0``)."""
+    if rows.is_cuda and rows.dtype == torch.bfloat16 and rows.shape[-1] % 8 == 0:
+        dw = torch.empty(dest.numel(), dtype=torch.float32, device=rows.device)
+        rc = _lib.lib().sb_moe_route_weight_grad(P(rows.contiguous()), P(dest), P(dy.contiguous()), P(dw), dest.numel(), k,
+                                                 rows.shape[-1], _lib.stream())  # fmt: skip
+        _lib.check(rc, "sb_moe_route_weight_grad")
+        return dw
+    tok = torch.arange(dest.numel(), device=dest.device) // k
+    return (rows[dest.clamp_min(0).long()].float() * dy[tok].float()).sum(-1) * (dest >= 0).float()
+
+
+class _ScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, dest, k, num_rows):
+        ctx.save_for_backward(dest)
+        ctx.k = k
+        return scatter_rows(x, dest, k, num_rows)
+
+    @staticmethod
+    def backward(ctx, g):
+        (dest,) = ctx.saved_tensors
+        return gather_sum(g.contiguous(), dest, None, ctx.k), None, None, None
+
+
+class _GatherSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, rows, dest, weights, k):
+        ctx.save_for_backward(rows, dest, weights)
+        ctx.k = k
+        return gather_sum(rows, dest, weights, k)
+
+    @staticmethod
+    def backward(ctx, dy):
+        rows, dest, weights = ctx.saved_tensors
+        dy = dy.contiguous()
+        # d rows[dest[s]] = w[s] * dy[s // k]: a scatter of the scaled token gradients (each slot owns its row)
+        scaled = (dy.float().repeat_interleave(ctx.k, dim=0) * weights.reshape(-1, 1).float()).to(dy.dtype)
+        d_rows = scatter_rows(scaled, dest, 1, rows.shape[0])
+        return d_rows, None, route_weight_grad(rows, dest, dy, ctx.k).view_as(weights).to(weights.dtype), None
+
+
+def permute_tokens(x, dest, k: int, num_rows: int):
+    """Differentiable ``scatter_rows`` (gradient: route-ordered ``gather_sum``)."""
+    return _ScatterRows.apply(x, dest, k, num_rows)
+
+
+def combine_routes(rows, dest, weights, k: int):
+    """Differentiable weighted ``gather_sum`` (gradients for the rows and for the routing weights)."""
+    return _GatherSum.apply(rows, dest, weights, k)
+
+
 class PaddedLayout:
     """Row bookkeeping for ``counts[e]`` rows per expert, each segment starting at a multiple of 128."""
 
@@ -72,6 +158,9 @@ class DeviceLayout:
         pend = torch.cumsum(padded, 0)
         shift = (pend - padded) - (torch.cumsum(counts, 0) - counts)
         self.dest = torch.arange(flat.numel(), device=dev) + shift.index_select(0, sorted_e)
+        # the same destinations in slot order (slot s = token s // k, route s % k): what the permutation kernels index by
+        self.slot_dest = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
+        self.slot_dest[self.order] = self.dest.to(torch.int32)
         self.rows_padded = -(-(flat.numel() + num_experts * (TILE - 1)) // TILE) * TILE
         tiles = torch.arange(self.rows_padded // TILE, device=dev) * TILE
         self.tile_expert = torch.searchsorted(pend, tiles, right=True).clamp_(max=num_experts - 1).to(torch.int32)
@@ -79,13 +168,11 @@ class DeviceLayout:
 
     def pad(self, x: torch.Tensor) -> torch.Tensor:
         """[T, H] token activations -> [rows_padded, H] expert-sorted, zero padded."""
-        return x.new_zeros(self.rows_padded, x.shape[-1]).index_copy_(0, self.dest, x.index_select(0, self.token))
+        return scatter_rows(x, self.slot_dest, self.k, self.rows_padded)
 
     def combine(self, y_padded: torch.Tensor, probs: torch.Tensor, T: int) -> torch.Tensor:
-        """Weighted sum of each token's k expert outputs (fp32 accumulation) -> [T, H]."""
-        w = probs.reshape(-1).index_select(0, self.order).float()
-        y = y_padded.index_select(0, self.dest).float() * w[:, None]
-        return torch.zeros(T, y.shape[-1], dtype=torch.float32, device=y.device).index_add_(0, self.token, y).to(y_padded.dtype)
+        """Weighted sum of each token's k expert outputs, in route order with fp32 accumulation -> [T, H]."""
+        return gather_sum(y_padded, self.slot_dest, probs, self.k)
 
 
 def stacked_view(tensors: list[torch.Tensor]) -> torch.Tensor | None:

@@ -140,3 +140,48 @@ def test_moe_engine_decodes_consistently_on_cpu():
     r = e.generate([[1, 2, 3, 4, 5]], [dict(max_new_tokens=6, ignore_eos=True)])[0]
     rq = e.generate([r.input_ids + r.output_ids], [dict(max_new_tokens=0)], logprob_start_len=0)[0]
     assert np.abs(np.array(rq.input_logprobs[5:]) - np.array(r.output_logprobs)).max() < 1e-4
+
+
+def _perm_case(device, dtype):
+    torch.manual_seed(4)
+    T, k, H, R = 33, 3, 64, 150
+    x = torch.randn(T, H, device=device).to(dtype)
+    dest = torch.randperm(R, device=device)[: T * k].to(torch.int32)
+    dest[5] = -1  # a dropped route
+    w = torch.rand(T, k, device=device)
+    return x, dest, w, T, k, H, R
+
+
+def test_route_permutation_ops_and_gradients_cpu():
+    x, dest, w, T, k, H, R = _perm_case("cpu", torch.float32)
+    x.requires_grad_()
+    w.requires_grad_()
+    rows = grouped.permute_tokens(x, dest, k, R)
+    assert torch.equal(rows[dest[7].long()], x[7 // k].detach()) and rows.abs().sum(1).ne(0).sum() == T * k - 1
+    y = grouped.combine_routes(rows * 2.0, dest, w, k)
+    d = dest.view(T, k).long()
+    ok = (d >= 0).float()
+    want = (2.0 * x.detach()[:, None, :] * (w.detach() * ok)[:, :, None]).sum(1)
+    torch.testing.assert_close(y, want, rtol=1e-5, atol=1e-6)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    # d/dx sum_j 2 w_j x = 2 * sum_j w_j * gy ; d/dw_j = <2 x, gy>
+    torch.testing.assert_close(x.grad, 2.0 * (w.detach() * ok).sum(1, keepdim=True) * gy, rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(w.grad, ok * (2.0 * x.detach() * gy).sum(-1, keepdim=True), rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.gpu
+def test_route_permutation_kernels_match_cpu_reference_and_are_deterministic(kernels):
+    x, dest, w, T, k, H, R = _perm_case("cuda", torch.bfloat16)
+    rows = grouped.scatter_rows(x, dest, k, R)
+    assert torch.equal(rows.cpu(), grouped.scatter_rows(x.cpu(), dest.cpu(), k, R))
+    y = grouped.gather_sum(rows, dest, w, k)
+    ref = grouped.gather_sum(rows.cpu(), dest.cpu(), w.cpu(), k)
+    assert (y.cpu().float() - ref.float()).abs().max() <= 2e-2 * ref.float().abs().max()
+    assert torch.equal(grouped.gather_sum(rows, dest, w, k), y)  # same bits every time
+    y2 = grouped.gather_sum(rows, dest, w, k, round_each=True)
+    ref2 = grouped.gather_sum(rows.cpu(), dest.cpu(), w.cpu(), k, round_each=True)
+    assert (y2.cpu().float() - ref2.float()).abs().max() <= 2e-2 * ref2.float().abs().max()
+    dy = torch.randn(T, H, device="cuda").to(torch.bfloat16)
+    dw = grouped.route_weight_grad(rows, dest, dy, k)
+    torch.testing.assert_close(dw.cpu(), grouped.route_weight_grad(rows.cpu(), dest.cpu(), dy.cpu(), k), rtol=2e-3, atol=2e-3)
