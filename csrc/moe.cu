@@ -82,6 +82,96 @@ moe_route_weight_grad_kernel(const __nv_bfloat16* __restrict__ rows, const int* 
   }
 }
 
+// Top-k routing in one pass over the router logits: one warp per token, each lane keeps E / 32 logits in registers.
+//   mode 0  pick the k largest logits; weights = softmax over the picked logits (== renormalised top-k of the softmax)
+//   mode 1  weights = softmax over all experts, pick the k largest, no renormalisation
+//   mode 2  scores = sigmoid(logit); pick by score + bias (bias only steers the choice); weights = picked scores,
+//           divided by their sum when `renorm`
+// then weights *= scale. Ties go to the lower expert index. E <= 512.
+constexpr int TOPK_MAX_PER_LANE = 16;
+__global__ void __launch_bounds__(256)
+moe_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int* __restrict__ idx, float* __restrict__ wts,
+                long T, int E, int k, int mode, int renorm, float scale) {
+  const int lane = threadIdx.x & 31;
+  for (long t = static_cast<long>(blockIdx.x) * 8 + (threadIdx.x >> 5); t < T; t += static_cast<long>(gridDim.x) * 8) {
+    float raw[TOPK_MAX_PER_LANE], sel[TOPK_MAX_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < TOPK_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      raw[i] = e < E ? logits[t * E + e] : -INFINITY;
+      mx = fmaxf(mx, raw[i]);
+    }
+    mx = warp_max(mx);
+    float denom = 0.f;
+    if (mode == 1) {
+#pragma unroll
+      for (int i = 0; i < TOPK_MAX_PER_LANE; ++i) denom += lane + 32 * i < E ? __expf(raw[i] - mx) : 0.f;
+      denom = warp_sum(denom);
+    }
+#pragma unroll
+    for (int i = 0; i < TOPK_MAX_PER_LANE; ++i) {
+      const int e = lane + 32 * i;
+      if (e >= E) {
+        sel[i] = -INFINITY;
+      } else if (mode == 2) {
+        raw[i] = 1.f / (1.f + __expf(-raw[i]));  // from here on "raw" is the score that becomes the weight
+        sel[i] = raw[i] + (bias != nullptr ? bias[e] : 0.f);
+      } else {
+        sel[i] = raw[i];
+      }
+    }
+    float picked_w = 0.f;  // lane j < k ends up holding the weight of the j-th pick
+    int picked_e = 0;
+    float wsum = 0.f;
+    for (int r = 0; r < k; ++r) {
+      float bv = -INFINITY;
+      int be = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < TOPK_MAX_PER_LANE; ++i)
+        if (sel[i] > bv) {  // strict: the lowest index wins inside a lane (indices grow with i)
+          bv = sel[i];
+          be = lane + 32 * i;
+        }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+        if (ov > bv || (ov == bv && oe < be)) {
+          bv = ov;
+          be = oe;
+        }
+      }
+      // the owner of the winner publishes the value the weight is made of and retires the element
+      float val = 0.f;
+      if ((be & 31) == lane) {
+#pragma unroll
+        for (int i = 0; i < TOPK_MAX_PER_LANE; ++i)
+          if (lane + 32 * i == be) {
+            val = raw[i];
+            sel[i] = -INFINITY;
+          }
+      }
+      val = __shfl_sync(0xffffffffu, val, be & 31);
+      float wv;
+      if (mode == 0) wv = __expf(val - mx);          // normalised below by the sum over the picks
+      else if (mode == 1) wv = __expf(val - mx) / denom;
+      else wv = val;
+      wsum += wv;
+      if (lane == r) {
+        picked_w = wv;
+        picked_e = be;
+      }
+    }
+    if (mode == 0) picked_w /= wsum;
+    else if (mode == 2 && renorm) picked_w /= (wsum + 1e-20f);
+    if (lane < k) {
+      idx[t * k + lane] = picked_e;
+      wts[t * k + lane] = picked_w * scale;
+    }
+  }
+}
+
 static inline int moe_blocks(long items) {
   long b = (items + 7) / 8;
   return static_cast<int>(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
@@ -112,5 +202,15 @@ extern "C" int sb_moe_route_weight_grad(const void* rows, const int* dest, const
   if (H % 8 != 0 || k <= 0) return (int)cudaErrorInvalidValue;
   sb::moe_route_weight_grad_kernel<<<sb::moe_blocks(slots), 256, 0, s>>>((const __nv_bfloat16*)rows, dest,
                                                                         (const __nv_bfloat16*)dy, dw, slots, k, H);
+  return (int)cudaGetLastError();
+}
+
+// logits [T, E] fp32 (row-major, contiguous); bias [E] fp32 or null; idx [T, k] int32; weights [T, k] fp32. k <= 32.
+extern "C" int sb_moe_topk(const float* logits, const float* bias, int* idx, float* weights, long T, int E, int k, int mode,
+                           int renorm, float scale, cudaStream_t s) {
+  if (T == 0) return 0;
+  if (E <= 0 || E > 32 * sb::TOPK_MAX_PER_LANE || k <= 0 || k > 32 || k > E || mode < 0 || mode > 2)
+    return (int)cudaErrorInvalidValue;
+  sb::moe_topk_kernel<<<sb::moe_blocks(T), 256, 0, s>>>(logits, bias, idx, weights, T, E, k, mode, renorm, scale);
   return (int)cudaGetLastError();
 }

@@ -224,13 +224,14 @@ class ModelRunner:
     def _moe(self, L, x):
         cfg = self.cfg
         logits = ops.router_gemm(x, L["router"])
-        k = cfg.moe_router_topk
-        topv, idx = torch.topk(logits, k, dim=-1)
-        probs = torch.softmax(topv, -1) if cfg.norm_topk_prob else torch.softmax(logits, -1).gather(-1, idx)
+        from slime_b200.ops import grouped
+
+        probs, idx = grouped.route_topk(logits, cfg.moe_router_topk, score=cfg.moe_router_score_function,
+                                        pre_softmax=cfg.moe_router_pre_softmax, renorm=cfg.norm_topk_prob,
+                                        bias=L.get("router_bias"), scale=cfg.moe_router_topk_scaling_factor)  # fmt: skip
         self._last_routed = idx
         # expert-sorted, tile-padded layout built on the device (no host sync: the step stays graph-capturable), then
         # one grouped GEMM per projection over all experts
-        from slime_b200.ops import grouped
 
         lay = grouped.DeviceLayout(idx, L["w13"].shape[0])
         act = ops.swiglu(grouped.grouped_gemm(lay.pad(x), L["w13"], lay))

@@ -34,6 +34,7 @@ _SIGS = {
     "sb_dp_reduce_shard": [P, I, I, I, L, L, P, P, P, P],
     "sb_dp_adam_bcast": [P, P, P, P, P, I, I, I, L, L, F, F, F, F, F, F, F, F, F, P, I, P],
     "sb_group_fp8_quant_1x128": [P, P, P, P, I, I, L, L, I, P],
+    "sb_moe_topk": [P, P, P, P, L, I, I, I, I, F, P],
     "sb_moe_scatter_rows": [P, P, P, L, I, I, P],
     "sb_moe_gather_sum": [P, P, P, P, L, I, I, I, P],
     "sb_moe_route_weight_grad": [P, P, P, P, L, I, I, P],

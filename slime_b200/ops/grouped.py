@@ -26,6 +26,39 @@ TILE = 128
 P = _lib.ptr
 
 
+def route_topk(logits: torch.Tensor, k: int, *, score: str = "softmax", pre_softmax: bool = False, renorm: bool = True,
+               bias: torch.Tensor | None = None, scale: float | None = None):
+    """Router logits [T, E] (fp32) -> ``(weights [T, k] fp32, indices [T, k] int64)`` in one kernel.
+
+    ``score="softmax"`` with ``renorm`` and not ``pre_softmax``: softmax over the k picked logits; with ``pre_softmax``
+    or ``renorm=False``: full softmax, pick k, keep the probabilities. ``score="sigmoid"``: sigmoid scores, ``bias``
+    steers the choice only, weights are the picked scores (normalised when ``renorm``). ``scale`` multiplies the result.
+    """
+    T, E = logits.shape
+    mode = 2 if score == "sigmoid" else (1 if (pre_softmax or not renorm) else 0)
+    if logits.is_cuda and E <= 512 and k <= 32:
+        lg = logits.float().contiguous()
+        idx = torch.empty(T, k, dtype=torch.int32, device=lg.device)
+        w = torch.empty(T, k, dtype=torch.float32, device=lg.device)
+        b = None if bias is None else bias.float().contiguous()
+        rc = _lib.lib().sb_moe_topk(P(lg), P(b), P(idx), P(w), T, E, k, mode, int(renorm), float(scale or 1.0), _lib.stream())
+        _lib.check(rc, "sb_moe_topk")
+        return w, idx.long()
+    lg = logits.float()
+    if mode == 2:
+        scores = torch.sigmoid(lg)
+        idx = torch.topk(scores + bias.float() if bias is not None else scores, k, dim=-1).indices
+        w = scores.gather(-1, idx)
+        if renorm:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    elif mode == 1:
+        w, idx = torch.topk(torch.softmax(lg, -1), k, dim=-1)
+    else:
+        top, idx = torch.topk(lg, k, dim=-1)
+        w = torch.softmax(top, -1)
+    return w * (scale or 1.0), idx
+
+
 def scatter_rows(x: torch.Tensor, dest: torch.Tensor, k: int, num_rows: int) -> torch.Tensor:
     """``out[dest[s]] = x[s // k]`` for every route slot ``s`` with ``dest[s] >= 0``; other rows of ``out`` are zero."""
     out = x.new_zeros(num_rows, x.shape[-1])

@@ -185,3 +185,20 @@ def test_route_permutation_kernels_match_cpu_reference_and_are_deterministic(ker
     dy = torch.randn(T, H, device="cuda").to(torch.bfloat16)
     dw = grouped.route_weight_grad(rows, dest, dy, k)
     torch.testing.assert_close(dw.cpu(), grouped.route_weight_grad(rows.cpu(), dest.cpu(), dy.cpu(), k), rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("E,k", [(128, 8), (8, 2), (160, 6), (512, 32)])
+def test_route_topk_kernel_matches_torch(kernels, E, k):
+    torch.manual_seed(E)
+    T = 301
+    logits = torch.randn(T, E, device="cuda") * 3
+    bias = torch.randn(E, device="cuda") * 0.5
+    cases = [dict(), dict(pre_softmax=True), dict(renorm=False), dict(score="sigmoid", bias=bias, scale=2.5),
+             dict(score="sigmoid", renorm=False)]
+    for kw in cases:
+        w, idx = grouped.route_topk(logits, k, **kw)
+        kw_cpu = {a: (b.cpu() if torch.is_tensor(b) else b) for a, b in kw.items()}
+        w_ref, idx_ref = grouped.route_topk(logits.cpu(), k, **kw_cpu)
+        assert torch.equal(idx.cpu(), idx_ref), kw  # random logits: no ties, the order of the picks is the same
+        torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-4, atol=1e-6)
