@@ -411,20 +411,23 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
         splits = max(1, min(splits, -(-block_table.shape[1] * page_size // 128)))  # never more splits than 128-token tiles
     if out is None:
         out = torch.empty_like(q)
-    if (use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and os.environ.get("SLIME_B200_DECODE_ATTN_WS", "1") != "0"
-            and (workspace is None or workspace.numel() >= B * Hq * splits * 4 * (D + 2))):
-        # head dim 64: the persistent warp-specialised kernel (four softmax groups per SM); every group of every split
-        # writes a partial result, merged by its combine kernel
+    same_layout = k_cache.stride() == v_cache.stride() and k_cache.stride(2) == 1
+    if (use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and os.environ.get("SLIME_B200_DECODE_ATTN_WS", "0") == "1"
+            and same_layout and (workspace is None or workspace.numel() >= B * Hq * splits * 4 * (D + 2))):
+        # opt-in for head dim 64: the persistent warp-specialised kernel (four softmax groups per SM); every group of
+        # every split writes a partial result, merged by its combine kernel. It measures within 1 % of the default
+        # kernel below on uniform batches, so it is not the default.
         ns = splits * 4
         ws_buf = workspace if workspace is not None else torch.empty(B * Hq * ns * (D + 2), dtype=torch.float32, device=q.device)
         rc = _lib.lib().sb_paged_decode_ws(P(q), P(k_cache), P(v_cache), P(block_table), P(seq_lens), P(out),
                                            P(ws_buf[: B * Hq * ns * D]), P(ws_buf[B * Hq * ns * D : B * Hq * ns * (D + 2)]),
                                            B, Hq, Hkv, D, page_size, block_table.shape[1], k_cache.shape[0], q.stride(0),
                                            out.stride(0), splits, float(scale), P(_lib.status_word(q.device)),
-                                           _lib.sm_count(q.device), _lib.stream())  # fmt: skip
+                                           _lib.sm_count(q.device), k_cache.stride(0), k_cache.stride(1), _lib.stream())  # fmt: skip
         if rc != -1:
             _lib.check(rc, "sb_paged_decode_ws")
             return out
+    assert k_cache.is_contiguous() and v_cache.is_contiguous(), "only the warp-specialised kernel takes a strided KV cache"
     if workspace is None and splits > 1:
         workspace = torch.empty(B * Hq * splits * (D + 2), dtype=torch.float32, device=q.device)
     part_o = workspace[: B * Hq * splits * D] if splits > 1 else None

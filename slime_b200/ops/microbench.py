@@ -15,6 +15,7 @@ from __future__ import annotations
 import argparse
 import json
 import math
+import os
 
 import torch
 
@@ -146,6 +147,15 @@ def bench_decode(a):
     }
     per_layer = ["rmsnorm_add", "gemm_qkv", "rope_qk", "kv_write", "paged_attention", "gemm_o", "rmsnorm_add", "gemm_gate_up",
                  "swiglu", "gemm_down"]  # fmt: skip
+    def attn_ws():  # the opt-in persistent warp-specialised kernel (head dim 64)
+        os.environ["SLIME_B200_DECODE_ATTN_WS"] = "1"
+        try:
+            return ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps)
+        finally:
+            os.environ.pop("SLIME_B200_DECODE_ATTN_WS", None)
+
+    if d == 64:
+        steps["paged_attention_warp_specialised"] = attn_ws
     steps["paged_attention_cuda_cores"] = lambda: ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps,
                                                                              use_tensor_cores=False)
     t_of = {}

@@ -27,8 +27,13 @@ def _reference(q, kc, vc, bt, lens, ps, scale):
 
 @pytest.mark.parametrize("Hq,Hkv,D,ps", [(14, 2, 64, 16), (32, 8, 128, 16), (16, 4, 128, 64), (32, 4, 128, 32), (16, 1, 64, 128),
                                          (2, 2, 64, 16)])  # fmt: skip
-def test_decode_attention_tc(kernels, Hq, Hkv, D, ps):
+@pytest.mark.parametrize("ws", ["0", "1"])
+def test_decode_attention_tc(kernels, monkeypatch, Hq, Hkv, D, ps, ws):
     from slime_b200 import ops
+
+    if ws == "1" and (D != 64 or Hq // Hkv > 8):
+        pytest.skip("the warp-specialised kernel covers head dim 64, group size <= 8")
+    monkeypatch.setenv("SLIME_B200_DECODE_ATTN_WS", ws)
     from slime_b200.ops import _lib
 
     torch.manual_seed(Hq * 7 + D)
@@ -61,9 +66,12 @@ def test_decode_attention_tc(kernels, Hq, Hkv, D, ps):
         torch.testing.assert_close(out.float(), legacy.float(), rtol=2e-2, atol=1.5e-2)
 
 
-def test_decode_attention_tc_strided_q_and_long_context(kernels):
+@pytest.mark.parametrize("ws", ["0", "1"])
+def test_decode_attention_tc_strided_q_and_long_context(kernels, monkeypatch, ws):
     """q as a view into a packed qkv row (the engine's layout) and a context that spans many tiles."""
     from slime_b200 import ops
+
+    monkeypatch.setenv("SLIME_B200_DECODE_ATTN_WS", ws)
     from slime_b200.ops import _lib
 
     torch.manual_seed(3)
