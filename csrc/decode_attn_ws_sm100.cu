@@ -4,39 +4,54 @@
 // reorganised so that an SM keeps FOUR softmax chains in flight instead of two and no softmax thread ever issues a
 // copy or an MMA:
 //
-//   warps 0, 2      TMA producers: warp 0 brings Q of every work item (ring of 6 slots) and K tiles (128 tokens, ring of
-//                   5), warp 2 brings V tiles (ring of 7); lane p fetches page p of a tile
+//   warp 20         scheduler: walks the CTA's work items (WsSched), reads their block-table entries and publishes one
+//                   queue entry per tile (request, kv head, split, group, valid tokens, first / last flags, the cache
+//                   slot of each page). The other four role warps only read entries: the instruction path per tile of
+//                   a single-threaded role is what bounds this kernel, so the bookkeeping lives in a warp of its own
+//   warps 0, 2      TMA producers: warp 0 brings K tiles (128 tokens, ring of 5) and Q when a group starts an item (two
+//                   slots per group), warp 2 brings V tiles (ring of 7); lane p fetches page p of a tile
 //   warps 1, 3      MMA issuers (lane 0 each; one thread cannot issue fast enough for four groups): warp 1 issues S^T(t)
 //                   as soon as K(t) has landed and the owning group has drained its previous S^T (this frees the K
-//                   slot); warp 3 issues O^T(t) as soon as that tile's P^T is ready (this frees the V slot)
-//   warps 4..19     four softmax groups of 128 threads; tile t belongs to group t mod 4, which reads S^T from TMEM,
-//                   forms p = 2^(s - max), writes P^T (bf16) to shared memory and folds the previous tile's O^T into
-//                   registers. Each group keeps its own running (max, sum, accumulator): it is a split of the
-//                   sequence, and writes an un-normalised partial result per work item.
-//   combine kernel  merges the 4 x splits partials of every (request, head).
+//                   slot) and tells the group which tile it is through a small mailbox; warp 3 issues O^T(t) as soon as
+//                   that tile's P^T is ready (this frees the V slot)
+//   warps 4..19     four softmax groups of 128 threads. A group owns one work item (request, kv head, split) at a time,
+//                   from its first tile to its last: it reads S^T from TMEM, forms p = 2^(s - max), writes P^T (bf16) to
+//                   shared memory, folds the previous tile's O^T into registers, and at the end of the item writes the
+//                   output row (or, with splits > 1, an un-normalised partial for the combine kernel).
 //
-// A CTA walks work items (request, kv head, split) blockIdx.x, blockIdx.x + gridDim.x, ...; tiles are numbered through
-// all its items, so the pipeline never drains between items. Every wait is an mbarrier wait with a 2 s bound (also the
-// exchange inside a softmax group): on expiry the CTA records a status word, every role leaves its loop, copies in
-// flight are given time to land, TMEM is freed and the kernel returns.
+// A CTA's work items are blockIdx.x, blockIdx.x + gridDim.x, ...; a group that finishes its item takes the CTA's next
+// one. Tiles flow through the rings round-robin over the groups, so the pipeline never drains between items. Every wait
+// is an mbarrier wait with a 2 s bound (also the exchange inside a softmax group): on expiry the CTA records a status
+// word, every role leaves its loop, copies in flight are given time to land, TMEM is freed and the kernel returns.
 #include "common.cuh"
 
 namespace sb {
 
 // K and V tiles live in separate rings: a K slot is free again as soon as S^T of its tile has been computed, a V slot
 // only after the tile's softmax and O^T product, so V gets the deeper ring and each is loaded by its own warp.
-constexpr int WS_TILE = 128, WS_D = 64, WS_NWG = 4, WS_NK = 5, WS_NV = 7, WS_NQ = 6, WS_MAXG = 8;
-constexpr int WS_THREADS = 128 + 128 * WS_NWG;  // K producer, S^T issuer, V producer, O^T issuer, 4 softmax groups
+constexpr int WS_TILE = 128, WS_D = 64, WS_NWG = 4, WS_NK = 5, WS_NV = 7, WS_NQ = 2 * WS_NWG, WS_MAXG = 8;
+constexpr int WS_THREADS = 128 + 128 * WS_NWG + 32;  // K producer, S^T issuer, V producer, O^T issuer, 4 softmax groups, scheduler
+constexpr int WS_SCHED_WARP = 4 + 4 * WS_NWG;
 constexpr int WS_KV_TILE = WS_TILE * 128;        // one K (or V) tile: 128 tokens x 128 bytes
 constexpr int WS_P_BYTES = 2 * WS_MAXG * 128;    // P^T: 2 chunks of 64 tokens x 8 heads x 128 B
 constexpr int WS_Q_BYTES = 16 * 128;             // 16 rows (heads) x 64 dims
-constexpr int WS_NBAR = 2 * WS_NK + 2 * WS_NV + 6 * WS_NWG + 2 * WS_NQ;
+constexpr int WS_SQ = 16;                         // entries of the tile queue (K producer -> V producer and both issuers)
+constexpr int WS_NBAR = 2 * WS_NK + 2 * WS_NV + 7 * WS_NWG + 2 * WS_NQ + 2 * WS_SQ;
 constexpr int WS_SMEM = (WS_NK + WS_NV) * WS_KV_TILE + WS_NWG * WS_P_BYTES + WS_NQ * WS_Q_BYTES + WS_NBAR * 8 + 64 + 1024;
+// flags of a tile-queue / mailbox word (low 8 bits: valid tokens of the tile; bits 12-13: the group)
+constexpr int WS_F_FIRST = 1 << 8, WS_F_LAST = 1 << 9, WS_F_DONE = 1 << 10, WS_F_GROUP_SHIFT = 12;
 
 __device__ __forceinline__ float ws_warp_max(float v) {
   float r;
   asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
   return r;
+}
+// 32 lanes x 8 columns TMEM -> registers: a thread's row of S^T or O^T for the (at most 8) query heads.
+__device__ __forceinline__ void ws_tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
 }
 __device__ __forceinline__ float ws_exp2(float x) {
   float r;
@@ -48,8 +63,7 @@ struct WsItem {
   int b, kvh, sp, t_begin, t_end, ntiles;
 };
 
-// Sequence length of work item `it` (0 past the end). Every role loads the length of the NEXT item while it works on the
-// current one, so this global load is never on anybody's critical path.
+// Sequence length of work item `it` (0 past the end).
 __device__ __forceinline__ int ws_len(int it, int num_items, int Hkv, int splits, const int* __restrict__ seq_lens) {
   return it < num_items ? __ldg(seq_lens + it / (splits * Hkv)) : 0;
 }
@@ -68,12 +82,119 @@ __device__ __forceinline__ WsItem ws_item(int it, int Hkv, int splits, int len) 
   return w;
 }
 
+// Four values kept in registers and indexed at run time (a chain of selects; no local memory).
+struct WsQuad {
+  int v0, v1, v2, v3;
+  __device__ __forceinline__ int get(int w) const {
+    int r = v0;
+    r = w == 1 ? v1 : r;
+    r = w == 2 ? v2 : r;
+    r = w == 3 ? v3 : r;
+    return r;
+  }
+  __device__ __forceinline__ void set(int w, int x) {
+    v0 = w == 0 ? x : v0;
+    v1 = w == 1 ? x : v1;
+    v2 = w == 2 ? x : v2;
+    v3 = w == 3 ? x : v3;
+  }
+  __device__ __forceinline__ void fill(int x) { v0 = v1 = v2 = v3 = x; }
+};
+
+// The order in which a CTA's tiles pass through the rings. Group w keeps an item until its tiles are used up, then takes
+// the CTA's next item that has any; tiles are emitted round-robin over the groups. Lengths are loaded two items ahead of
+// their use. The loop over the groups is deliberately not unrolled: unrolled four times with its callbacks inlined, the
+// walk ran 1.6x slower (a role that runs at one thread's pace has nothing to hide instruction-cache misses behind).
+struct WsSched {
+  const int* seq_lens;
+  int num_items, Hkv, splits, stride;
+  int next_it, len_a, len_b;  // the next item to hand out, its length, the length of the one after it
+  WsQuad rem, cnt, n;         // per group: tiles left of its item, items taken, tiles emitted
+  WsQuad c_b, c_kvh, c_sp, c_tb, c_te, c_nt;  // per group: its current item
+  int gt;  // tiles emitted by the CTA: the ring position
+
+  __device__ __forceinline__ void init(const int* lens, int num_items_, int Hkv_, int splits_) {
+    seq_lens = lens;
+    num_items = num_items_;
+    Hkv = Hkv_;
+    splits = splits_;
+    stride = gridDim.x;
+    next_it = blockIdx.x;
+    len_a = ws_len(next_it, num_items, Hkv, splits, seq_lens);
+    len_b = ws_len(next_it + stride, num_items, Hkv, splits, seq_lens);
+    gt = 0;
+    rem.fill(0);
+    cnt.fill(0);
+    n.fill(0);
+    c_b.fill(0);
+    c_kvh.fill(0);
+    c_sp.fill(0);
+    c_tb.fill(0);
+    c_te.fill(0);
+    c_nt.fill(0);
+  }
+
+  // on_assign(w, item, ordinal): group w takes a non-empty item, its ordinal-th. on_empty(item): an item without tiles.
+  // on_tile(w, item, r, gt, n, ordinal): tile r of the item, the CTA's gt-th tile and the group's n-th.
+  // A callback that returns false ends the walk (run() then returns false).
+  template <class FA, class FE, class FT>
+  __device__ __forceinline__ bool run(FA&& on_assign, FE&& on_empty, FT&& on_tile) {
+    for (;;) {
+      bool any = false;
+#pragma unroll 1
+      for (int w = 0; w < WS_NWG; ++w) {
+        int left = rem.get(w);
+        if (left == 0) {
+          while (next_it < num_items) {
+            const WsItem x = ws_item(next_it, Hkv, splits, len_a);
+            next_it += stride;
+            len_a = len_b;
+            len_b = ws_len(next_it + stride, num_items, Hkv, splits, seq_lens);
+            if (x.ntiles > 0) {
+              c_b.set(w, x.b);
+              c_kvh.set(w, x.kvh);
+              c_sp.set(w, x.sp);
+              c_tb.set(w, x.t_begin);
+              c_te.set(w, x.t_end);
+              c_nt.set(w, x.ntiles);
+              left = x.ntiles;
+              const int ordinal = cnt.get(w);
+              if (!on_assign(w, x, ordinal)) return false;
+              cnt.set(w, ordinal + 1);
+              break;
+            }
+            if (!on_empty(x)) return false;
+          }
+        }
+        if (left > 0) {
+          any = true;
+          WsItem x;
+          x.b = c_b.get(w);
+          x.kvh = c_kvh.get(w);
+          x.sp = c_sp.get(w);
+          x.t_begin = c_tb.get(w);
+          x.t_end = c_te.get(w);
+          x.ntiles = c_nt.get(w);
+          const int nw = n.get(w);
+          if (!on_tile(w, x, x.ntiles - left, gt, nw, cnt.get(w) - 1)) return false;
+          --left;
+          n.set(w, nw + 1);
+          ++gt;
+        }
+        rem.set(w, left);
+      }
+      if (!any) return true;
+    }
+  }
+};
+
 template <int G>
 __global__ void __launch_bounds__(WS_THREADS, 1)
 decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                       const __grid_constant__ CUtensorMap tmQ, const int* __restrict__ block_table,
-                      const int* __restrict__ seq_lens, float* __restrict__ part_o, float* __restrict__ part_ml, int num_items,
-                      int Hq, int Hkv, int page_size, int page_shift, int max_pages, int splits, float scale, int* status) {
+                      const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, float* __restrict__ part_o,
+                      float* __restrict__ part_ml, int num_items, int Hq, int Hkv, int page_size, int page_shift,
+                      int max_pages, int splits, int out_stride, float scale, int* status, int load_path_only) {
   static_assert(G <= WS_MAXG, "this kernel keeps 8 query heads per kv head at most");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -91,14 +212,20 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint64_t* o_full = p_ready + WS_NWG;
   uint64_t* o_free = o_full + WS_NWG;
   uint64_t* wg_bar = o_free + WS_NWG;
-  uint64_t* q_full = wg_bar + WS_NWG;
+  uint64_t* info_full = wg_bar + WS_NWG;
+  uint64_t* q_full = info_full + WS_NWG;
   uint64_t* q_empty = q_full + WS_NQ;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_empty + WS_NQ);
+  uint64_t* sq_full = q_empty + WS_NQ;
+  uint64_t* sq_empty = sq_full + WS_SQ;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sq_empty + WS_SQ);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __shared__ __align__(16) float red_m[WS_NWG][2][WS_MAXG][4];  // [group][parity][head][warp]
-  __shared__ float red_l[WS_NWG][4][WS_MAXG];
-  constexpr int BT_CACHE = 256, BT_PER_LANE = BT_CACHE / 32;
-  __shared__ int bt_s[2][2][BT_CACHE];  // [K or V producer][item parity][page]
+  __shared__ __align__(16) float red_m[WS_NWG][2][WS_MAXG][4];  // [group][tile parity][head][warp]
+  __shared__ float red_l[WS_NWG][2][4][WS_MAXG];                 // [group][item parity][warp][head]
+  __shared__ __align__(16) int4 info_s[WS_NWG][2];               // mailbox S^T issuer -> group: [group][tile parity]
+  // tile queue: the K producer walks the schedule and publishes, per tile, {request, kv head | split << 16, valid tokens |
+  // flags | group << 12, pages} and the cache slot of each of the tile's pages; the V producer and the issuers read it
+  __shared__ __align__(16) int4 sq_hdr[WS_SQ];
+  __shared__ int sq_slot[WS_SQ][8];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float scale_log2 = scale * 1.4426950408889634f;
@@ -119,10 +246,15 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       mbar_init(&o_full[w], 1);
       mbar_init(&o_free[w], 4);
       mbar_init(&wg_bar[w], 4);
+      mbar_init(&info_full[w], 1);
     }
     for (int s = 0; s < WS_NQ; ++s) {
       mbar_init(&q_full[s], 1);
       mbar_init(&q_empty[s], 1);
+    }
+    for (int e = 0; e < WS_SQ; ++e) {
+      mbar_init(&sq_full[e], 1);
+      mbar_init(&sq_empty[e], 4);  // both producers, both issuers
     }
     *cta_abort = 0;
     fence_barrier_init();
@@ -141,131 +273,203 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   pdl_wait();
   pdl_launch_dependents();
 
-  // ------------------------------------------------------------------------------------------ TMA producers
-  // Run by warp 0 for K (and Q) and by warp 2 for V. Block-table entries are staged in shared memory one item ahead
-  // (lane l keeps entries l, l + 32, ... of the NEXT item in registers while the current item's tiles are issued, and
-  // stores them afterwards), sequence lengths two items ahead: no global load sits between two tile issues.
-  auto produce = [&](const bool is_k) {
+  // ------------------------------------------------------------------------------------------ roles
+  if (warp == WS_SCHED_WARP) {
+    // ---- scheduler. It walks the schedule (WsSched) and publishes every tile to the queue, with the cache slots of
+    // the tile's pages. Lane l keeps block-table entry l of a 32-entry window per group in registers (the window in use
+    // and the next one), and the first two windows of the item that will be handed out next: no global load sits
+    // between two tiles.
+    const int ppt = WS_TILE >> page_shift;  // pages per tile: 8, 4, 2 or 1
+    WsSched sc;
+    sc.init(seq_lens, num_items, Hkv, splits);
+    WsQuad bt0, bt1;
+    bt0.fill(0);
+    bt1.fill(0);
+    int pre0 = 0, pre1 = 0, pre_it = -1;
+    auto bt_load = [&](const WsItem& x, int window) -> int {  // entries [32 window, 32 window + 32) of the item's pages
+      const int npages = (x.t_end - x.t_begin + page_size - 1) >> page_shift;
+      const int e = window * 32 + lane;
+      return e < npages ? __ldg(block_table + static_cast<size_t>(x.b) * max_pages + (x.t_begin >> page_shift) + e) : 0;
+    };
+    auto prefetch_next = [&]() {  // for the item the walk will look at next (its length has landed long ago)
+      if (sc.next_it < num_items) {
+        const WsItem nx = ws_item(sc.next_it, Hkv, splits, sc.len_a);
+        pre0 = bt_load(nx, 0);
+        pre1 = bt_load(nx, 1);
+        pre_it = sc.next_it;
+      }
+    };
+    prefetch_next();
+    auto on_assign = [&](int w, const WsItem& x, int) -> bool {
+      const int this_it = sc.next_it - sc.stride;
+      if (pre_it == this_it) {
+        bt0.set(w, pre0);
+        bt1.set(w, pre1);
+      } else {  // an item without tiles came in between: fetch directly
+        bt0.set(w, bt_load(x, 0));
+        bt1.set(w, bt_load(x, 1));
+      }
+      prefetch_next();
+      return true;
+    };
+    auto on_empty = [&](const WsItem& x) -> bool {  // nobody else looks at an item without tiles: its result is written here
+      if (splits == 1) {
+        __nv_bfloat16* o = out + static_cast<size_t>(x.b) * out_stride + static_cast<size_t>(x.kvh) * G * WS_D;
+        for (int i = lane; i < G * WS_D; i += 32) o[i] = __float2bfloat16(0.f);
+      } else if (lane < G) {
+        const size_t idx = (static_cast<size_t>(x.b) * Hq + x.kvh * G + lane) * splits + x.sp;
+        part_ml[idx * 2 + 0] = -INFINITY;
+        part_ml[idx * 2 + 1] = 0.f;
+      }
+      return true;
+    };
+    auto publish = [&](int gt, const int4& hdr, int slot0) -> bool {
+      const int e = gt & (WS_SQ - 1);
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(&sq_empty[e], ((gt / WS_SQ) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) return false;
+      if (lane == 0) sq_hdr[e] = hdr;
+      if (lane < 8) sq_slot[e][lane] = slot0;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sq_full[e]);
+      return true;
+    };
+    auto on_tile = [&](int w, const WsItem& x, int r, int gt, int, int) -> bool {
+      const int e0 = r * ppt;  // the tile's first block-table entry within the item
+      if (r > 0 && (e0 & 31) == 0) {
+        bt0.set(w, bt1.get(w));
+        bt1.set(w, bt_load(x, (e0 >> 5) + 1));
+      }
+      const int valid = min(WS_TILE, x.t_end - (x.t_begin + r * WS_TILE));
+      const int npages = (valid + page_size - 1) >> page_shift;
+      const int slot0 = __shfl_sync(0xffffffffu, bt0.get(w), (e0 & 31) + (lane & (ppt - 1))) * page_size;
+      const int flags = (r == 0 ? WS_F_FIRST : 0) | (r == x.ntiles - 1 ? WS_F_LAST : 0) | (w << WS_F_GROUP_SHIFT);
+      return publish(gt, make_int4(x.b, x.kvh | (x.sp << 16), valid | flags, npages), lane < npages ? slot0 : 0);
+    };
+    if (sc.run(on_assign, on_empty, on_tile)) publish(sc.gt, make_int4(0, 0, WS_F_DONE, 0), 0);
+  } else if (warp == 0 || warp == 2) {
+    // ---- K producer (warp 0; also brings Q when a group starts an item) and V producer (warp 2): tile by tile from
+    // the queue, lane p copies page p
+    const bool is_k = warp == 0;
     const int ring = is_k ? WS_NK : WS_NV;
     uint64_t* full = is_k ? full_k : full_v;
     uint64_t* emp = is_k ? k_empty : v_empty;
     uint8_t* base = is_k ? sK : sV;
     const CUtensorMap* map = is_k ? &tmK : &tmV;
-    int (*bt_mine)[BT_CACHE] = bt_s[is_k ? 0 : 1];
-    int gt = 0, iq = -1;  // iq counts the items that have tiles: only those use a Q slot
-    bool ok = true;
-    auto bt_fetch = [&](const WsItem& x, int (&regs)[BT_PER_LANE]) {
-      const int* row = block_table + static_cast<size_t>(x.b) * max_pages + (x.t_begin >> page_shift);
-      const int n = x.ntiles > 0 ? min(BT_CACHE, ((x.t_end - x.t_begin + page_size - 1) >> page_shift)) : 0;
-#pragma unroll
-      for (int j = 0; j < BT_PER_LANE; ++j) regs[j] = lane + 32 * j < n ? __ldg(row + lane + 32 * j) : 0;
-    };
-    auto bt_store = [&](int buf, const int (&regs)[BT_PER_LANE]) {
-#pragma unroll
-      for (int j = 0; j < BT_PER_LANE; ++j) bt_mine[buf][lane + 32 * j] = regs[j];
+    WsQuad oq;  // per group: items started (K producer only)
+    oq.fill(0);
+    for (int gt = 0, s = 0, lap = 0;; ++gt) {
+      const int e = gt & (WS_SQ - 1);
+      bool ok = mbar_wait(&sq_full[e], (gt / WS_SQ) & 1, cta_abort, status, ERR_WAIT_FULL);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      const int4 h = sq_hdr[e];
+      const int slot0 = sq_slot[e][lane & 7];
       __syncwarp();
-    };
-    int it = blockIdx.x;
-    int len_cur = ws_len(it, num_items, Hkv, splits, seq_lens);
-    int len_next = ws_len(it + gridDim.x, num_items, Hkv, splits, seq_lens);
-    int regs[BT_PER_LANE];
-    if (it < num_items) {
-      bt_fetch(ws_item(it, Hkv, splits, len_cur), regs);
-      bt_store(0, regs);
-    }
-    for (int k = 0; it < num_items && ok; it += gridDim.x, ++k) {
-      const WsItem w = ws_item(it, Hkv, splits, len_cur);
-      const int it_n = it + gridDim.x;
-      const WsItem wn = ws_item(it_n < num_items ? it_n : it, Hkv, splits, it_n < num_items ? len_next : 0);
-      const int len_after = ws_len(it_n + gridDim.x, num_items, Hkv, splits, seq_lens);  // consumed two items from now
-      if (it_n < num_items) bt_fetch(wn, regs);                                          // consumed one item from now
-      const int* bt_cur = bt_mine[k & 1];
-      if (w.ntiles > 0) {
-        ++iq;
-        if (is_k) {
-          const int qs = iq % WS_NQ;
-          if (lane == 0) {
-            ok = mbar_wait(&q_empty[qs], ((iq / WS_NQ) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
-            if (ok) {
-              mbar_arrive_expect_tx(&q_full[qs], WS_Q_BYTES);
-              tma_load_3d(sQ + qs * WS_Q_BYTES, &tmQ, &q_full[qs], 0, w.kvh * G, w.b);
-            }
+      if (lane == 0) mbar_arrive(&sq_empty[e]);
+      if (h.z & WS_F_DONE) break;
+      const int npages = h.w, kvh = h.y & 0xffff;
+      if (lane == 0) {
+        if (is_k && (h.z & WS_F_FIRST)) {
+          const int w = (h.z >> WS_F_GROUP_SHIFT) & 3, ordinal = oq.get(w), qs = w * 2 + (ordinal & 1);
+          oq.set(w, ordinal + 1);
+          ok = mbar_wait(&q_empty[qs], ((ordinal >> 1) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
+          if (ok) {
+            mbar_arrive_expect_tx(&q_full[qs], WS_Q_BYTES);
+            tma_load_3d(sQ + qs * WS_Q_BYTES, &tmQ, &q_full[qs], 0, kvh * G, h.x);
           }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
         }
-        const int* bt_row = block_table + static_cast<size_t>(w.b) * max_pages + (w.t_begin >> page_shift);
-        for (int i = 0; i < w.ntiles && ok; ++i, ++gt) {
-          const int s = gt % ring;
-          const int valid = min(WS_TILE, w.t_end - (w.t_begin + i * WS_TILE));
-          const int npages = (valid + page_size - 1) >> page_shift;
-          const int pi = ((i * WS_TILE) >> page_shift) + lane;  // page index within the item's range
-          int slot0 = 0;
-          if (lane < npages) slot0 = (pi < BT_CACHE ? bt_cur[pi] : __ldg(bt_row + pi)) * page_size;
-          if (lane == 0) {
-            ok = mbar_wait(&emp[s], ((gt / ring) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
-            if (ok) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128));
-          }
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (ok && lane < npages)
-            tma_load_3d(base + s * WS_KV_TILE + lane * page_size * 128, map, &full[s], 0, w.kvh, slot0);
-          __syncwarp();
-        }
+        ok = ok && mbar_wait(&emp[s], (lap & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
+        if (ok) mbar_arrive_expect_tx(&full[s], static_cast<uint32_t>(npages * page_size * 128));
       }
-      if (it_n < num_items) bt_store((k + 1) & 1, regs);
-      len_cur = len_next;
-      len_next = len_after;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane < npages) tma_load_3d(base + s * WS_KV_TILE + lane * page_size * 128, map, &full[s], 0, kvh, slot0);
+      __syncwarp();
+      if (++s == ring) {
+        s = 0;
+        ++lap;
+      }
     }
-  };
-
-  if (warp == 0) {
-    produce(true);
-  } else if (warp == 2) {
-    produce(false);
   } else if (warp == 1) {
-    // ------------------------------------------------------------------------------------------ S^T issuer
+    // ---- S^T issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc(WS_TILE, 16, 1, 1, 0, 0);  // A = K tile (K-major), B = Q (K-major)
-      bool ok = true;
-      int gt = 0, iq = -1;
-      int len_cur = ws_len(blockIdx.x, num_items, Hkv, splits, seq_lens);
-      for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
-        const WsItem wi = ws_item(it, Hkv, splits, len_cur);
-        len_cur = ws_len(it + gridDim.x, num_items, Hkv, splits, seq_lens);  // for the next item; lands during this one
-        if (wi.ntiles == 0) continue;
-        ++iq;
-        const int qs = iq % WS_NQ;
-        ok = mbar_wait(&q_full[qs], (iq / WS_NQ) & 1, cta_abort, status, ERR_WAIT_FULL);
-        for (int i = 0; i < wi.ntiles && ok; ++i, ++gt) {
-          const int w = gt % WS_NWG, n = gt / WS_NWG, s = gt % WS_NK;
-          if (!mbar_wait(&full_k[s], (gt / WS_NK) & 1, cta_abort, status, ERR_WAIT_FULL) ||
-              !mbar_wait(&s_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t k_addr = smem_u32(sK + s * WS_KV_TILE);
-          const uint32_t q_addr = smem_u32(sQ + qs * WS_Q_BYTES);
+      WsQuad nq, oq;  // per group: tiles issued, items started
+      nq.fill(0);
+      oq.fill(0);
+      bool done = false;
+      for (int gt = 0;; ++gt) {
+        const int e = gt & (WS_SQ - 1), s = gt % WS_NK;
+        if (!mbar_wait(&sq_full[e], (gt / WS_SQ) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        const int4 h = sq_hdr[e];
+        mbar_arrive(&sq_empty[e]);
+        if (h.z & WS_F_DONE) {
+          done = true;
+          break;
+        }
+        const int w = (h.z >> WS_F_GROUP_SHIFT) & 3;
+        const bool first = (h.z & WS_F_FIRST) != 0, last = (h.z & WS_F_LAST) != 0;
+        const int n = nq.get(w);
+        const int started = oq.get(w) + (first ? 1 : 0), ordinal = started - 1;
+        oq.set(w, started);
+        nq.set(w, n + 1);
+        const int qs = w * 2 + (ordinal & 1);
+        if (!mbar_wait(&full_k[s], (gt / WS_NK) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        if (first && !mbar_wait(&q_full[qs], (ordinal >> 1) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        if (load_path_only) {  // measurement mode: hand the slots straight back to the producers
+          mbar_arrive(&k_empty[s]);
+          if (last) mbar_arrive(&q_empty[qs]);
+          continue;
+        }
+        // the group has drained S^T of its previous tile (and is therefore done with the mailbox slot of the one before)
+        if (!mbar_wait(&s_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
+        info_s[w][n & 1] = make_int4(h.x, h.y, h.z, gt);
+        mbar_arrive(&info_full[w]);
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sK + s * WS_KV_TILE);
+        const uint32_t q_addr = smem_u32(sQ + qs * WS_Q_BYTES);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_f16(tmem_base + w * 64, make_smem_desc(k_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
-                     make_smem_desc(q_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc_s, k != 0 ? 1u : 0u);
-          umma_commit(&s_full[w]);
-          umma_commit(&k_empty[s]);  // the K slot is free once S^T exists
-          if (i == wi.ntiles - 1) umma_commit(&q_empty[qs]);  // the item's last use of its Q slot
+        for (int k = 0; k < 4; ++k)
+          umma_f16(tmem_base + w * 64, make_smem_desc(k_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B),
+                   make_smem_desc(q_addr + k * 32, 16, 1024, UMMA_SWIZZLE_128B), idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(&s_full[w]);
+        umma_commit(&k_empty[s]);             // the K slot is free once S^T exists
+        if (last) umma_commit(&q_empty[qs]);  // the item's last use of its Q slot
+      }
+      if (done && !load_path_only) {
+        for (int w = 0; w < WS_NWG; ++w) {  // tell every group that nothing more will come
+          const int n = nq.get(w);
+          if (!mbar_wait(&s_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
+          info_s[w][n & 1] = make_int4(0, 0, WS_F_DONE, 0);
+          mbar_arrive(&info_full[w]);
         }
       }
     }
   } else if (warp == 3) {
-    // ------------------------------------------------------------------------------------------ O^T issuer
+    // ---- O^T issuer
     if (lane == 0) {
       constexpr uint32_t idesc_o = make_idesc(128, 16, 1, 1, 1, 0);  // A = V tile read MN-major, B = P^T
-      bool ok = true;
-      auto issue_o = [&](int gt) -> bool {
-        const int w = gt % WS_NWG, n = gt / WS_NWG, s = gt % WS_NV;
+      WsQuad nq;
+      nq.fill(0);
+      for (int gt = 0;; ++gt) {
+        const int e = gt & (WS_SQ - 1), s = gt % WS_NV;
+        if (!mbar_wait(&sq_full[e], (gt / WS_SQ) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        const int flags = sq_hdr[e].z;
+        mbar_arrive(&sq_empty[e]);
+        if (flags & WS_F_DONE) break;
+        const int w = (flags >> WS_F_GROUP_SHIFT) & 3;
+        const int n = nq.get(w);
+        nq.set(w, n + 1);
+        if (load_path_only) {
+          if (!mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+          mbar_arrive(&v_empty[s]);
+          continue;
+        }
         if (!mbar_wait(&p_ready[w], n & 1, cta_abort, status, ERR_WAIT_FULL) ||
             !mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL) ||
             !mbar_wait(&o_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY))
-          return false;
+          break;
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + s * WS_KV_TILE);
         const uint32_t p_addr = smem_u32(sP + w * WS_P_BYTES);
@@ -280,17 +484,9 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
                      (kc | k) != 0 ? 1u : 0u);
         umma_commit(&o_full[w]);
         umma_commit(&v_empty[s]);
-        return true;
-      };
-      int gt = 0;
-      int len_cur = ws_len(blockIdx.x, num_items, Hkv, splits, seq_lens);
-      for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
-        const WsItem wi = ws_item(it, Hkv, splits, len_cur);
-        len_cur = ws_len(it + gridDim.x, num_items, Hkv, splits, seq_lens);
-        for (int i = 0; i < wi.ntiles && ok; ++i, ++gt) ok = issue_o(gt);
       }
     }
-  } else {
+  } else if (!load_path_only) {
     // --------------------------------------------------------------------------------------- softmax groups
     const int w = (warp - 4) >> 2;   // group
     const int q = warp & 3;          // TMEM lane quarter this warp may touch
@@ -307,139 +503,145 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       ++xph;
       return __all_sync(0xffffffffu, r);
     };
-    int gt = 0;
-    bool ok = true;
-    int len_cur = ws_len(blockIdx.x, num_items, Hkv, splits, seq_lens);
-    for (int it = blockIdx.x; it < num_items && ok; it += gridDim.x) {
-      const WsItem wi = ws_item(it, Hkv, splits, len_cur);
-      len_cur = ws_len(it + gridDim.x, num_items, Hkv, splits, seq_lens);  // for the next item; lands during this one
-      float acc[G], m_run[G], l_thr[G], keep_prev[G], gain_prev[G];
+    float acc[G], m_run[G], l_thr[G], keep_prev[G], gain_prev[G];
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        acc[g] = 0.f;
-        m_run[g] = -INFINITY;
-        l_thr[g] = 0.f;
-        keep_prev[g] = 1.f;
-        gain_prev[g] = 0.f;
+    for (int g = 0; g < G; ++g) acc[g] = m_run[g] = l_thr[g] = keep_prev[g] = gain_prev[g] = 0.f;
+    auto merge = [&](int n) -> bool {  // fold the O^T of the group's tile number n into the accumulator
+      bool r = mbar_wait(&o_full[w], n & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
+      r = __all_sync(0xffffffffu, r);
+      if (!r) return false;
+      tc_fence_after();
+      if (merges) {
+        uint32_t o[8];
+        ws_tmem_ld_32x8(t_o, o);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < G; ++g) acc[g] = acc[g] * keep_prev[g] + __uint_as_float(o[g]) * gain_prev[g];
       }
-      // own tiles of this item: global numbers gt + i with (gt + i) % NWG == w
-      const int first = (w - gt % WS_NWG + WS_NWG) % WS_NWG;
-      const int mine = first < wi.ntiles ? (wi.ntiles - first + WS_NWG - 1) / WS_NWG : 0;
-      auto merge = [&](int n) -> bool {  // fold the O^T of own tile number n (of this group) into the accumulator
-        bool r = mbar_wait(&o_full[w], n & 1, cta_abort, status, ERR_WAIT_TMEM_FULL);
-        r = __all_sync(0xffffffffu, r);
-        if (!r) return false;
-        tc_fence_after();
-        if (merges) {
-          uint32_t o[32];
-          tmem_ld_32x32(t_o, o);
-          tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&o_free[w]);
+      return true;
+    };
+    int b = 0, kvh = 0, sp = 0, items_done = 0;
+    bool ok = true;
+    for (int n = 0; ok; ++n) {  // the group's tiles, in the order the S^T issuer announces them
+      const int par = n & 1;
+      ok = mbar_wait(&info_full[w], par, cta_abort, status, ERR_WAIT_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      const int4 inf = info_s[w][par];
+      if (inf.z & WS_F_DONE) break;
+      const int valid = inf.z & 0xff;
+      const bool first = (inf.z & WS_F_FIRST) != 0, last = (inf.z & WS_F_LAST) != 0;
+      const int g_t = inf.w, s = g_t % WS_NV;
+      if (first) {
+        b = inf.x;
+        kvh = inf.y & 0xffff;
+        sp = inf.y >> 16;
 #pragma unroll
-          for (int g = 0; g < G; ++g) acc[g] = acc[g] * keep_prev[g] + __uint_as_float(o[g]) * gain_prev[g];
+        for (int g = 0; g < G; ++g) {
+          acc[g] = 0.f;
+          m_run[g] = -INFINITY;
+          l_thr[g] = 0.f;
+          keep_prev[g] = 1.f;
+          gain_prev[g] = 0.f;
         }
+      }
+      // ---- scores of this thread's token for the G heads
+      ok = mbar_wait(&s_full[w], par, cta_abort, status, ERR_WAIT_TMEM_FULL);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float sc[G];
+      {
+        uint32_t r[8];
+        ws_tmem_ld_32x8(t_s, r);
+        tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&o_free[w]);
-        return true;
-      };
-      for (int j = 0; j < mine && ok; ++j) {
-        const int g_t = gt + first + j * WS_NWG;  // global tile number
-        const int n = g_t / WS_NWG, s = g_t % WS_NV, par = n & 1;
-        const int t0 = wi.t_begin + (first + j * WS_NWG) * WS_TILE;
-        const int valid = min(WS_TILE, wi.t_end - t0);
-        // ---- scores of this thread's token for the G heads
-        ok = mbar_wait(&s_full[w], par, cta_abort, status, ERR_WAIT_TMEM_FULL);
+        if (lane == 0) mbar_arrive(&s_free[w]);  // S^T is in registers: the next product may overwrite it
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[g] = (wt < valid) ? __uint_as_float(r[g]) * scale_log2 : -INFINITY;
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float wm = ws_warp_max(sc[g]);
+        if (lane == 0) red_m[w][par][g][q] = wm;
+      }
+      ok = group_sync();
+      if (!ok) break;
+      // ---- the previous tile's product is long done: fold it in (this also frees P^T and O^T of the group)
+      if (!first) {
+        ok = merge(n - 1);
+        if (!ok) break;
+      }
+      // ---- p = 2^(s - tile max), running max / sum bookkeeping, P^T to shared memory
+      const int kc = wt >> 6, col = wt & 63;
+      uint8_t* p_col = sP + w * WS_P_BYTES + kc * (WS_MAXG * 128) + (col & 7) * 2;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const float4 wmx = *reinterpret_cast<const float4*>(red_m[w][par][g]);
+        const float mt = fmaxf(fmaxf(wmx.x, wmx.y), fmaxf(wmx.z, wmx.w));
+        const float p = ws_exp2(sc[g] - mt);
+        const float nm = fmaxf(m_run[g], mt);
+        const float keep = ws_exp2(m_run[g] - nm);
+        const float gain = ws_exp2(mt - nm);
+        l_thr[g] = l_thr[g] * keep + p * gain;
+        m_run[g] = nm;
+        keep_prev[g] = keep;
+        gain_prev[g] = gain;
+        *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = __float2bfloat16(p);
+      }
+      if (valid < WS_TILE) {
+        // rows past the end of the sequence hold whatever an older tile left there: p is 0 for them, but 0 x NaN
+        // would poison O^T, so they are cleared once the copy of this tile's V has landed
+        ok = mbar_wait(&full_v[s], (g_t / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        tc_fence_after();
-        float sc[G];
-        {
-          uint32_t r[32];
-          tmem_ld_32x32(t_s, r);
-          tmem_ld_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&s_free[w]);  // S^T is in registers: the next product may overwrite it
+        if (wt >= valid) {
+          uint4* vrow = reinterpret_cast<uint4*>(sV + s * WS_KV_TILE + wt * 128);
 #pragma unroll
-          for (int g = 0; g < G; ++g) sc[g] = (wt < valid) ? __uint_as_float(r[g]) * scale_log2 : -INFINITY;
+          for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float wm = ws_warp_max(sc[g]);
-          if (lane == 0) red_m[w][par][g][q] = wm;
-        }
-        ok = group_sync();
-        if (!ok) break;
-        // ---- the previous own tile's product is long done: fold it in (this also frees P^T and O^T of the group)
-        if (j > 0) {
-          ok = merge(n - 1);
-          if (!ok) break;
-        }
-        // ---- p = 2^(s - tile max), running max / sum bookkeeping, P^T to shared memory
-        const int kc = wt >> 6, col = wt & 63;
-        uint8_t* p_col = sP + w * WS_P_BYTES + kc * (WS_MAXG * 128) + (col & 7) * 2;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float4 wmx = *reinterpret_cast<const float4*>(red_m[w][par][g]);
-          const float mt = fmaxf(fmaxf(wmx.x, wmx.y), fmaxf(wmx.z, wmx.w));
-          const float p = ws_exp2(sc[g] - mt);
-          const float nm = fmaxf(m_run[g], mt);
-          const float keep = ws_exp2(m_run[g] - nm);
-          const float gain = ws_exp2(mt - nm);
-          l_thr[g] = l_thr[g] * keep + p * gain;
-          m_run[g] = nm;
-          keep_prev[g] = keep;
-          gain_prev[g] = gain;
-          *reinterpret_cast<__nv_bfloat16*>(p_col + g * 128 + (((col >> 3) ^ (g & 7)) << 4)) = __float2bfloat16(p);
-        }
-        if (valid < WS_TILE) {
-          // rows past the end of the sequence hold whatever an older tile left there: p is 0 for them, but 0 x NaN
-          // would poison O^T, so they are cleared once the copy of this tile's V has landed
-          ok = mbar_wait(&full_v[s], (g_t / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          if (wt >= valid) {
-            uint4* vrow = reinterpret_cast<uint4*>(sV + s * WS_KV_TILE + wt * 128);
-#pragma unroll
-            for (int c = 0; c < 8; ++c) vrow[c] = make_uint4(0, 0, 0, 0);
-          }
-        }
-        fence_proxy_async();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&p_ready[w]);
-        if (j == mine - 1) ok = merge(n);  // last own tile of the item: wait for its product right away
       }
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[w]);
+      if (!last) continue;
+      // ---- last tile of the item: wait for its product right away, then write the item's result
+      ok = merge(n);
       if (!ok) break;
-      // ---- partial result of this group for the item (an empty marker if it had no tile)
-      float l_tot[G];
-#pragma unroll
-      for (int g = 0; g < G; ++g) l_tot[g] = 0.f;
-      if (mine > 0) {
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float ws = warp_sum(l_thr[g]);
-          if (lane == 0) red_l[w][q][g] = ws;
-        }
-        ok = group_sync();
-        if (!ok) break;
-#pragma unroll
-        for (int g = 0; g < G; ++g) l_tot[g] = (red_l[w][0][g] + red_l[w][1][g]) + (red_l[w][2][g] + red_l[w][3][g]);
-        ok = group_sync();  // red_l is read before the next item may overwrite it
-        if (!ok) break;
-      }
-      const int nsplit = splits * WS_NWG;
+      const int ip = items_done & 1;  // red_l is double-buffered: the exchange of the next item cannot overtake a reader
+      ++items_done;
 #pragma unroll
       for (int g = 0; g < G; ++g) {
-        const int h = wi.kvh * G + g;
-        const size_t base = (static_cast<size_t>(wi.b) * Hq + h) * nsplit + wi.sp * WS_NWG + w;
-        if (mine > 0 && merges) part_o[base * WS_D + wt] = acc[g];
-        if (wt == 0) {
-          part_ml[base * 2 + 0] = mine > 0 ? m_run[g] * 0.6931471805599453f : -INFINITY;  // natural-log domain
-          part_ml[base * 2 + 1] = mine > 0 ? l_tot[g] : 0.f;
+        const float ws = warp_sum(l_thr[g]);
+        if (lane == 0) red_l[w][ip][q][g] = ws;
+      }
+      ok = group_sync();
+      if (!ok) break;
+      float l_tot[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) l_tot[g] = (red_l[w][ip][0][g] + red_l[w][ip][1][g]) + (red_l[w][ip][2][g] + red_l[w][ip][3][g]);
+      if (splits == 1) {
+        if (merges) {
+          __nv_bfloat16* o = out + static_cast<size_t>(b) * out_stride + static_cast<size_t>(kvh) * G * WS_D + wt;
+#pragma unroll
+          for (int g = 0; g < G; ++g) o[g * WS_D] = __float2bfloat16(acc[g] / l_tot[g]);
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const size_t idx = (static_cast<size_t>(b) * Hq + kvh * G + g) * splits + sp;
+          if (merges) part_o[idx * WS_D + wt] = acc[g];
+          if (wt == 0) {
+            part_ml[idx * 2 + 0] = m_run[g] * 0.6931471805599453f;  // natural-log domain
+            part_ml[idx * 2 + 1] = l_tot[g];
+          }
         }
       }
-      gt += wi.ntiles;
     }
   }
 
@@ -511,8 +713,8 @@ __global__ void decode_attn_ws_combine_kernel(const float* __restrict__ part_o, 
 
 template <int G>
 static int ws_launch(int grid, cudaStream_t s, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tq, const int* bt,
-                     const int* sl, float* po, float* pml, int num_items, int Hq, int Hkv, int page_size, int page_shift,
-                     int max_pages, int splits, float scale, int* status) {
+                     const int* sl, __nv_bfloat16* out, float* po, float* pml, int num_items, int Hq, int Hkv, int page_size,
+                     int page_shift, int max_pages, int splits, int out_stride, float scale, int* status, int load_path_only) {
   auto kern = decode_attn_ws_kernel<G>;
   static bool configured = false;
   if (!configured) {
@@ -520,14 +722,20 @@ static int ws_launch(int grid, cudaStream_t s, const CUtensorMap& tk, const CUte
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  return (int)launch_pdl(kern, dim3(grid), dim3(WS_THREADS), WS_SMEM, s, tk, tv, tq, bt, sl, po, pml, num_items, Hq, Hkv, page_size,
-                         page_shift, max_pages, splits, scale, status);
+  return (int)launch_pdl(kern, dim3(grid), dim3(WS_THREADS), WS_SMEM, s, tk, tv, tq, bt, sl, out, po, pml, num_items, Hq, Hkv,
+                         page_size, page_shift, max_pages, splits, out_stride, scale, status, load_path_only);
 }
+
+static int g_ws_load_path_only = 0;
 
 }  // namespace sb
 
-// Head dim 64, at most 8 query heads per kv head. part_o / part_ml: workspaces [B, Hq, 4 * splits, 64] and
-// [B, Hq, 4 * splits, 2] fp32 (always used). Returns 0, a cudaError_t value, or -1 for shapes this kernel does not cover.
+// Measurement switch: with a non-zero value the kernel's producers run as usual and every landed tile is handed straight
+// back (no products, no softmax, no output): its duration is what the copy path alone costs for a given batch.
+extern "C" void sb_paged_decode_ws_load_path_only(int on) { sb::g_ws_load_path_only = on; }
+
+// Head dim 64, at most 8 query heads per kv head. part_o / part_ml: workspaces [B, Hq, splits, 64] and [B, Hq, splits, 2]
+// fp32, used (with the combine kernel) when splits > 1; with one split the kernel writes `out` itself. Returns 0, a cudaError_t value, or -1 for shapes this kernel does not cover.
 extern "C" int sb_paged_decode_ws(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
                                   const int* seq_lens, void* out, float* part_o, float* part_ml, int B, int Hq, int Hkv, int D,
                                   int page_size, int max_pages, int num_slots, int q_stride, int out_stride, int splits,
@@ -550,15 +758,15 @@ extern "C" int sb_paged_decode_ws(const void* q, const void* k_cache, const void
     const int num_items = B * Hkv * splits;
     const int grid = num_items < num_sms ? num_items : num_sms;
     int rc = -1;
-#define SB_WS(GV)                                                                                                         \
-  if (G == GV)                                                                                                             \
-    rc = sb::ws_launch<GV>(grid, s, tk, tv, tq, block_table, seq_lens, part_o, part_ml, num_items, Hq, Hkv, page_size, page_shift, \
-                           max_pages, splits, scale, status);
+#define SB_WS(GV)                                                                                                        \
+  if (G == GV)                                                                                                            \
+    rc = sb::ws_launch<GV>(grid, s, tk, tv, tq, block_table, seq_lens, (__nv_bfloat16*)out, part_o, part_ml, num_items, Hq, Hkv, \
+                           page_size, page_shift, max_pages, splits, out_stride, scale, status, sb::g_ws_load_path_only);
     SB_WS(1) SB_WS(2) SB_WS(3) SB_WS(4) SB_WS(5) SB_WS(6) SB_WS(7) SB_WS(8)
 #undef SB_WS
-    if (rc != 0) return rc;
+    if (rc != 0 || splits == 1 || sb::g_ws_load_path_only) return rc;
     return (int)sb::launch_pdl(sb::decode_attn_ws_combine_kernel, dim3(B * Hq), dim3(sb::WS_D), 0, s, (const float*)part_o,
-                               (const float*)part_ml, (__nv_bfloat16*)out, splits * sb::WS_NWG, out_stride, Hq);
+                               (const float*)part_ml, (__nv_bfloat16*)out, splits, out_stride, Hq);
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;

@@ -405,6 +405,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if not _cuda(q):
         return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale)
+    caller_splits = splits
     if splits is None:
         ctas = B * Hkv
         splits = 1 if ctas >= _lib.sm_count(q.device) else min(16, max(1, (2 * _lib.sm_count(q.device)) // max(ctas, 1)))
@@ -412,17 +413,26 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     if out is None:
         out = torch.empty_like(q)
     same_layout = k_cache.stride() == v_cache.stride() and k_cache.stride(2) == 1
-    if (use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and os.environ.get("SLIME_B200_DECODE_ATTN_WS", "0") == "1"
-            and same_layout and (workspace is None or workspace.numel() >= B * Hq * splits * 4 * (D + 2))):
-        # opt-in for head dim 64: the persistent warp-specialised kernel (four softmax groups per SM); every group of
-        # every split writes a partial result, merged by its combine kernel. It measures within 1 % of the default
-        # kernel below on uniform batches, so it is not the default.
-        ns = splits * 4
-        ws_buf = workspace if workspace is not None else torch.empty(B * Hq * ns * (D + 2), dtype=torch.float32, device=q.device)
+    # Head dim 64: the persistent warp-specialised kernel (four softmax groups per SM, one work item each) wins once every
+    # SM has several (request, kv head) items to walk through (measured: 57 against 74 us at 512 requests x 2 kv heads,
+    # context 768; 137 against 158 us at 256 x 2, context 4096) and loses a little below that, so it is chosen from the
+    # item count. SLIME_B200_DECODE_ATTN_WS=1 / 0 forces it on / off.
+    ws_env = os.environ.get("SLIME_B200_DECODE_ATTN_WS", "")
+    ws_ok = use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and same_layout and ws_env != "0"
+    if ws_ok and (ws_env == "1" or B * Hkv >= 3 * _lib.sm_count(q.device)):
+        ns = splits
+        if caller_splits is None:
+            # its own split rule: enough items for the 4 x SMs groups, at least 8 tiles of 128 tokens per split
+            tiles = -(-block_table.shape[1] * page_size // 128)
+            ns = max(1, min(16, (4 * _lib.sm_count(q.device)) // max(B * Hkv, 1), tiles // 8))
+        if workspace is not None and workspace.numel() >= B * Hq * ns * (D + 2):
+            ws_buf = workspace
+        else:
+            ws_buf = torch.empty(B * Hq * ns * (D + 2) if ns > 1 else 2, dtype=torch.float32, device=q.device)
         rc = _lib.lib().sb_paged_decode_ws(P(q), P(k_cache), P(v_cache), P(block_table), P(seq_lens), P(out),
                                            P(ws_buf[: B * Hq * ns * D]), P(ws_buf[B * Hq * ns * D : B * Hq * ns * (D + 2)]),
                                            B, Hq, Hkv, D, page_size, block_table.shape[1], k_cache.shape[0], q.stride(0),
-                                           out.stride(0), splits, float(scale), P(_lib.status_word(q.device)),
+                                           out.stride(0), ns, float(scale), P(_lib.status_word(q.device)),
                                            _lib.sm_count(q.device), k_cache.stride(0), k_cache.stride(1), _lib.stream())  # fmt: skip
         if rc != -1:
             _lib.check(rc, "sb_paged_decode_ws")

@@ -64,6 +64,7 @@ _SIGS = {
     "sb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
     "sb_paged_decode_tc": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
     "sb_paged_decode_ws": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, I, L, L, P],
+    "sb_paged_decode_ws_load_path_only": [I],
     "sb_block_fp8_quant": [P, P, P, I, I, L, L, I, I, I, P],
     "sb_block_fp8_dequant": [P, P, P, I, I, I, I, P],
     "sb_fake_int4": [P, P, P, P, I, I, I, I, I, P],

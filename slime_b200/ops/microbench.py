@@ -147,15 +147,27 @@ def bench_decode(a):
     }
     per_layer = ["rmsnorm_add", "gemm_qkv", "rope_qk", "kv_write", "paged_attention", "gemm_o", "rmsnorm_add", "gemm_gate_up",
                  "swiglu", "gemm_down"]  # fmt: skip
-    def attn_ws():  # the opt-in persistent warp-specialised kernel (head dim 64)
-        os.environ["SLIME_B200_DECODE_ATTN_WS"] = "1"
+    def attn_forced(flag, **kw):  # SLIME_B200_DECODE_ATTN_WS = "1": warp-specialised kernel, "0": the two-chain kernel
+        os.environ["SLIME_B200_DECODE_ATTN_WS"] = flag
         try:
-            return ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps)
+            return ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps, **kw)
         finally:
             os.environ.pop("SLIME_B200_DECODE_ATTN_WS", None)
 
+    def attn_ws():
+        return attn_forced("1", splits=a.splits)
+
+    def attn_ws_loads():  # the same kernel with every landed tile handed straight back: the cost of its copy path alone
+        _lib.lib().sb_paged_decode_ws_load_path_only(1)
+        try:
+            return attn_ws()
+        finally:
+            _lib.lib().sb_paged_decode_ws_load_path_only(0)
+
     if d == 64:
         steps["paged_attention_warp_specialised"] = attn_ws
+        steps["paged_attention_two_chain"] = lambda: attn_forced("0")
+        steps["paged_attention_warp_specialised_load_path"] = attn_ws_loads
     steps["paged_attention_cuda_cores"] = lambda: ops.paged_decode_attention(q3[:, :hq], kc, vc, bt, seq, ps,
                                                                              use_tensor_cores=False)
     t_of = {}
@@ -273,6 +285,7 @@ def main(argv=None):
     p.add_argument("--model", default="qwen2.5-0.5b")
     p.add_argument("--batch", type=int, default=256)
     p.add_argument("--context", type=int, default=768)
+    p.add_argument("--splits", type=int, default=None, help="sequence splits of the warp-specialised decode attention")
     a = p.parse_args(argv)
     from slime_b200.ops import build
 
