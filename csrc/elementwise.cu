@@ -316,6 +316,75 @@ rope_kernel(const __nv_bfloat16* x, __nv_bfloat16* out /* may alias x: a warp re
   }
 }
 
+// Inference form of the above, fused with the KV-cache write: one launch per layer instead of four. One warp per
+// (token, head) of a packed qkv row [T, (Hq + 2 Hkv) * D]:
+//   q heads  (per-head RMSNorm +) RoPE in place
+//   k heads  the same, written in place (prefill attends over the row itself) and to k_cache[slot[t], head]
+//   v heads  copied to v_cache[slot[t], head]
+// Caches are [slots, Hkv, D] contiguous; a negative slot skips the cache write (padding rows).
+template <int D>
+__global__ void __launch_bounds__(128)
+rope_kv_write_kernel(__nv_bfloat16* qkv, const int* __restrict__ pos, const float* __restrict__ cos_sin,
+                     const __nv_bfloat16* __restrict__ q_nw, const __nv_bfloat16* __restrict__ k_nw,
+                     const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                     int T, int Hq, int Hkv, int row_stride, float eps) {
+  constexpr int PER = D / 64;
+  pdl_wait();
+  pdl_launch_dependents();
+  const int heads = Hq + 2 * Hkv;
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (warp_global >= T * heads) return;
+  const int t = warp_global / heads, h = warp_global % heads;
+  __nv_bfloat16* row = qkv + static_cast<size_t>(t) * row_stride + static_cast<size_t>(h) * D;
+  if (h >= Hq + Hkv) {  // v: copy to the cache
+    const int slot = slots[t];
+    if (slot < 0) return;
+    __nv_bfloat16* dst = v_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq - Hkv)) * D;
+    const uint32_t* s32 = reinterpret_cast<const uint32_t*>(row);
+    uint32_t* d32 = reinterpret_cast<uint32_t*>(dst);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) d32[lane + 32 * j] = s32[lane + 32 * j];
+    return;
+  }
+  const bool is_k = h >= Hq;
+  const __nv_bfloat16* nw = is_k ? k_nw : q_nw;
+  float lo[PER], hi[PER];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    lo[j] = __bfloat162float(row[i]);
+    hi[j] = __bfloat162float(row[i + D / 2]);
+    ss += lo[j] * lo[j] + hi[j] * hi[j];
+  }
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float rs = rsqrtf(ss / D + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = lane + 32 * j;
+      lo[j] = lo[j] * rs * __bfloat162float(nw[i]);
+      hi[j] = hi[j] * rs * __bfloat162float(nw[i + D / 2]);
+    }
+  }
+  const float* cs = cos_sin + static_cast<size_t>(pos[t]) * D;  // [cos(D/2) | sin(D/2)]
+  const int slot = is_k ? slots[t] : -1;
+  __nv_bfloat16* cache = slot >= 0 ? k_cache + (static_cast<size_t>(slot) * Hkv + (h - Hq)) * D : nullptr;
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = lane + 32 * j;
+    const float c = cs[i], sn = cs[D / 2 + i];
+    const __nv_bfloat16 a = __float2bfloat16(lo[j] * c - hi[j] * sn), b = __float2bfloat16(hi[j] * c + lo[j] * sn);
+    row[i] = a;
+    row[i + D / 2] = b;
+    if (cache != nullptr) {
+      cache[i] = a;
+      cache[i + D / 2] = b;
+    }
+  }
+}
+
 // ---------------------------------------------------------------------- SwiGLU
 // gu: [T, 2F] = [gate | up]; act[T, F] = silu(gate) * up
 __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act, size_t T, int F) {
@@ -446,6 +515,23 @@ extern "C" int sb_rope(const void* x, void* out, const int* pos, const float* co
   else
     return (int)cudaErrorInvalidValue;
   return (int)cudaGetLastError();
+}
+
+extern "C" int sb_rope_kv_write(void* qkv, const int* pos, const float* cos_sin, const void* q_nw, const void* k_nw,
+                                const int* slots, void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D, int row_stride,
+                                float eps, cudaStream_t s) {
+  if (T == 0) return 0;
+  if ((row_stride & 1) || (reinterpret_cast<uintptr_t>(qkv) & 3)) return (int)cudaErrorInvalidValue;
+  const long warps = (long)T * (Hq + 2 * Hkv);
+  const int blocks = (int)((warps * 32 + 127) / 128);
+#define SB_RKW(DV)                                                                                                     \
+  if (D == DV)                                                                                                         \
+    return (int)sb::launch_pdl(sb::rope_kv_write_kernel<DV>, dim3(blocks), dim3(128), 0, s, (bf16*)qkv, pos, cos_sin,  \
+                               (const bf16*)q_nw, (const bf16*)k_nw, slots, (bf16*)k_cache, (bf16*)v_cache, T, Hq, Hkv, \
+                               row_stride, eps);
+  SB_RKW(64) SB_RKW(128) SB_RKW(256)
+#undef SB_RKW
+  return (int)cudaErrorInvalidValue;
 }
 
 static inline int ew_blocks(size_t n, int threads) {

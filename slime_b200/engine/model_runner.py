@@ -237,11 +237,13 @@ class ModelRunner:
         act = ops.swiglu(grouped.grouped_gemm(lay.pad(x), L["w13"], lay))
         return lay.combine(grouped.grouped_gemm(act, L["w2"], lay), probs, x.shape[0])
 
-    def _qkv(self, L, normed, positions):
+    def _qkv(self, L, normed, positions, slots, li):
+        """Packed q / k / v of the new tokens, rotated (and per-head normalised) in place, k and v also written to
+        their cache slots of layer ``li``: one GEMM and one fused launch."""
         cfg = self.cfg
         qkv = ops.gemm(normed, L["qkv"], bias=L["qkv_bias"])
-        return ops.rope_qk(qkv, positions, self.rope, self.w.hq, self.w.hkv, cfg.head_dim, L["q_norm"], L["k_norm"],
-                           cfg.norm_epsilon)  # fmt: skip
+        return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[li], self.kv.v[li], self.w.hq, self.w.hkv,
+                                 cfg.head_dim, L["q_norm"], L["k_norm"], cfg.norm_epsilon)  # fmt: skip
 
     # --------------------------------------------------------------------- prefill
     @torch.no_grad()
@@ -260,10 +262,9 @@ class ModelRunner:
         T = ids.numel()
         for li, L in enumerate(w.layers):
             normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
-            qkv = self._qkv(L, normed, positions)
+            qkv = self._qkv(L, normed, positions, slots, li)
             q3 = qkv.view(T, w.hq + 2 * w.hkv, d)
             q, k, v = q3[:, : w.hq], q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
-            ops.kv_write(k.reshape(T, -1), v.reshape(T, -1), slots, self.kv.k[li], self.kv.v[li])
             if fresh:
                 ctx = ops.varlen_attention(q, k, v, cu_q, max_q, self.scale)
             else:
@@ -359,10 +360,8 @@ class ModelRunner:
         x = self._tp_reduce(x) if w.tp > 1 else x
         normed, res = ops.rmsnorm(x, w.layers[0]["ln1"], cfg.norm_epsilon, None)
         for li, L in enumerate(w.layers):
-            qkv = self._qkv(L, normed, pos)
+            qkv = self._qkv(L, normed, pos, slots, li)
             q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
-            k, v = q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
-            ops.kv_write(k.reshape(n, -1), v.reshape(n, -1), slots, self.kv.k[li], self.kv.v[li])
             ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
             normed, res = self._row_parallel_norm(ctx.reshape(n, -1), L["o"], L["ln2"], res, n)
             # the norm that follows the MLP is the next layer's input norm (or the final norm)

@@ -302,6 +302,23 @@ def rope_qk(qkv, positions, cos_sin, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, e
     return _RopeQK.apply(qkv, positions, cos_sin, q_norm_w, k_norm_w, Hq, Hkv, D, eps)
 
 
+def rope_kv_write(qkv, positions, cos_sin, slots, k_cache, v_cache, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, eps=1e-6):
+    """Inference path: (per-head RMSNorm +) RoPE on the q and k heads of a packed qkv row IN PLACE, and the new k / v
+    rows scattered into cache slot ``slots[t]`` (negative: skipped), as one launch. Returns ``qkv``."""
+    T = qkv.shape[0]
+    if not _cuda(qkv):
+        x = qkv.view(T, Hq + 2 * Hkv, D)
+        x[:, :Hq] = reference.rope(x[:, :Hq], positions, cos_sin, q_norm_w, eps)
+        x[:, Hq : Hq + Hkv] = reference.rope(x[:, Hq : Hq + Hkv], positions, cos_sin, k_norm_w, eps)
+        kv_write(x[:, Hq : Hq + Hkv].reshape(T, -1), x[:, Hq + Hkv :].reshape(T, -1), slots, k_cache, v_cache)
+        return qkv
+    assert qkv.stride(1) == 1 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    rc = _lib.lib().sb_rope_kv_write(P(qkv), P(positions), P(cos_sin), P(q_norm_w), P(k_norm_w), P(slots), P(k_cache),
+                                     P(v_cache), T, Hq, Hkv, D, qkv.stride(0), float(eps), _lib.stream())
+    _lib.check(rc, "sb_rope_kv_write")
+    return qkv
+
+
 # ---------------------------------------------------------------------- SwiGLU
 class _SwiGLU(torch.autograd.Function):
     @staticmethod

@@ -59,6 +59,7 @@ _SIGS = {
     "sb_pg_loss": [P, P, P, P, P, P, P, P, I, F, F, F, I, P],
     "sb_sample": [P, I, L, I, I, P, P, P, P, P, P, P, P, P, P, I, P],
     "sb_kv_write": [P, P, P, P, P, I, I, I, I, P],
+    "sb_rope_kv_write": [P, P, P, P, P, P, P, P, I, I, I, I, I, F, P],
     "sb_decode_prepare": [P, P, P, P, P, P, P, P, P, P, P, P, P, I, I, I, P],
     "sb_decode_advance": [P, P, P, P, P, I, P],
     "sb_paged_decode": [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],

@@ -286,3 +286,37 @@ def test_quantisers_and_router(kernels):
     # batch invariance: a token's logits do not depend on which other tokens share the launch
     out1 = ops.router_gemm(xr[5:6].contiguous(), wr)
     assert torch.equal(out1[0], out[5])
+
+
+@pytest.mark.parametrize("Hq,Hkv,D,norm", [(14, 2, 64, False), (8, 2, 128, True)])
+def test_rope_kv_write_matches_separate_ops(kernels, Hq, Hkv, D, norm):
+    """The fused inference kernel against fp32 PyTorch: rotated q / k in place, k / v rows in their cache slots."""
+    from slime_b200 import ops
+    from slime_b200.ops import reference
+
+    torch.manual_seed(5)
+    T, slots_n = 37, 64
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    cs = ops.rope_cos_sin(512, D, 10000.0, device="cuda")
+    slots = torch.randperm(slots_n, device="cuda")[:T].to(torch.int32)
+    slots[3] = -1  # a padding row: rotated in place, not written to the cache
+    qw = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16) if norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda")).to(torch.bfloat16) if norm else None
+    kc = torch.zeros(slots_n, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    x = qkv.float().view(T, Hq + 2 * Hkv, D)
+    q_ref = reference.rope(x[:, :Hq], pos, cs, qw.float() if norm else None, 1e-6)
+    k_ref = reference.rope(x[:, Hq : Hq + Hkv], pos, cs, kw.float() if norm else None, 1e-6)
+    v_ref = x[:, Hq + Hkv :]
+    out = ops.rope_kv_write(qkv.clone(), pos, cs, slots, kc, vc, Hq, Hkv, D, qw, kw, 1e-6).view(T, Hq + 2 * Hkv, D)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(out[:, :Hq].float(), q_ref.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:, Hq : Hq + Hkv].float(), k_ref.float(), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out[:, Hq + Hkv :].float(), v_ref)
+    ok = slots >= 0
+    torch.testing.assert_close(kc[slots[ok].long()].float(), k_ref.float()[ok], rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(vc[slots[ok].long()].float(), v_ref[ok])
+    unused = torch.ones(slots_n, dtype=torch.bool, device="cuda")
+    unused[slots[ok].long()] = False
+    assert (kc[unused] == 0).all() and (vc[unused] == 0).all()
