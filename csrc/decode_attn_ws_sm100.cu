@@ -63,6 +63,32 @@ struct WsItem {
   int b, kvh, sp, t_begin, t_end, ntiles;
 };
 
+// Optional measurement build (-DSB_WS_CHAIN_TIMING): one thread of softmax group 0 of every CTA clocks the segments of
+// its per-tile chain and adds them up in ws_chain_ticks: [0] wait for the mailbox and S^T, [1] TMEM read + row maxima,
+// [2] exchange inside the group, [3] merge of the previous product (wait for O^T + TMEM read), [4] exp / P^T / fences,
+// [5] end of item (last merge, sum exchange, output), [6] tiles counted. ws_issue_ticks, by the two MMA issuers:
+// S^T issuer [0] queue entry, [1] K tile landed, [2] group drained its S^T, [3] issue; O^T issuer [4] P^T ready,
+// [5] V tile landed, [6] group merged its previous O^T, [7] issue.
+#ifdef SB_WS_CHAIN_TIMING
+__device__ unsigned long long ws_chain_ticks[8];
+__device__ unsigned long long ws_issue_ticks[8];
+#define WS_ITICK(slot)                 \
+  {                                    \
+    const long long now_ = clock64();  \
+    itick[slot] += now_ - itick_last;  \
+    itick_last = now_;                 \
+  }
+#define WS_TICK(slot)                                   \
+  if (timing) {                                         \
+    const long long now_ = clock64();                   \
+    tick_acc[slot] += now_ - tick_last;                 \
+    tick_last = now_;                                   \
+  }
+#else
+#define WS_TICK(slot)
+#define WS_ITICK(slot)
+#endif
+
 // Sequence length of work item `it` (0 past the end).
 __device__ __forceinline__ int ws_len(int it, int num_items, int Hkv, int splits, const int* __restrict__ seq_lens) {
   return it < num_items ? __ldg(seq_lens + it / (splits * Hkv)) : 0;
@@ -99,93 +125,6 @@ struct WsQuad {
     v3 = w == 3 ? x : v3;
   }
   __device__ __forceinline__ void fill(int x) { v0 = v1 = v2 = v3 = x; }
-};
-
-// The order in which a CTA's tiles pass through the rings. Group w keeps an item until its tiles are used up, then takes
-// the CTA's next item that has any; tiles are emitted round-robin over the groups. Lengths are loaded two items ahead of
-// their use. The loop over the groups is deliberately not unrolled: unrolled four times with its callbacks inlined, the
-// walk ran 1.6x slower (a role that runs at one thread's pace has nothing to hide instruction-cache misses behind).
-struct WsSched {
-  const int* seq_lens;
-  int num_items, Hkv, splits, stride;
-  int next_it, len_a, len_b;  // the next item to hand out, its length, the length of the one after it
-  WsQuad rem, cnt, n;         // per group: tiles left of its item, items taken, tiles emitted
-  WsQuad c_b, c_kvh, c_sp, c_tb, c_te, c_nt;  // per group: its current item
-  int gt;  // tiles emitted by the CTA: the ring position
-
-  __device__ __forceinline__ void init(const int* lens, int num_items_, int Hkv_, int splits_) {
-    seq_lens = lens;
-    num_items = num_items_;
-    Hkv = Hkv_;
-    splits = splits_;
-    stride = gridDim.x;
-    next_it = blockIdx.x;
-    len_a = ws_len(next_it, num_items, Hkv, splits, seq_lens);
-    len_b = ws_len(next_it + stride, num_items, Hkv, splits, seq_lens);
-    gt = 0;
-    rem.fill(0);
-    cnt.fill(0);
-    n.fill(0);
-    c_b.fill(0);
-    c_kvh.fill(0);
-    c_sp.fill(0);
-    c_tb.fill(0);
-    c_te.fill(0);
-    c_nt.fill(0);
-  }
-
-  // on_assign(w, item, ordinal): group w takes a non-empty item, its ordinal-th. on_empty(item): an item without tiles.
-  // on_tile(w, item, r, gt, n, ordinal): tile r of the item, the CTA's gt-th tile and the group's n-th.
-  // A callback that returns false ends the walk (run() then returns false).
-  template <class FA, class FE, class FT>
-  __device__ __forceinline__ bool run(FA&& on_assign, FE&& on_empty, FT&& on_tile) {
-    for (;;) {
-      bool any = false;
-#pragma unroll 1
-      for (int w = 0; w < WS_NWG; ++w) {
-        int left = rem.get(w);
-        if (left == 0) {
-          while (next_it < num_items) {
-            const WsItem x = ws_item(next_it, Hkv, splits, len_a);
-            next_it += stride;
-            len_a = len_b;
-            len_b = ws_len(next_it + stride, num_items, Hkv, splits, seq_lens);
-            if (x.ntiles > 0) {
-              c_b.set(w, x.b);
-              c_kvh.set(w, x.kvh);
-              c_sp.set(w, x.sp);
-              c_tb.set(w, x.t_begin);
-              c_te.set(w, x.t_end);
-              c_nt.set(w, x.ntiles);
-              left = x.ntiles;
-              const int ordinal = cnt.get(w);
-              if (!on_assign(w, x, ordinal)) return false;
-              cnt.set(w, ordinal + 1);
-              break;
-            }
-            if (!on_empty(x)) return false;
-          }
-        }
-        if (left > 0) {
-          any = true;
-          WsItem x;
-          x.b = c_b.get(w);
-          x.kvh = c_kvh.get(w);
-          x.sp = c_sp.get(w);
-          x.t_begin = c_tb.get(w);
-          x.t_end = c_te.get(w);
-          x.ntiles = c_nt.get(w);
-          const int nw = n.get(w);
-          if (!on_tile(w, x, x.ntiles - left, gt, nw, cnt.get(w) - 1)) return false;
-          --left;
-          n.set(w, nw + 1);
-          ++gt;
-        }
-        rem.set(w, left);
-      }
-      if (!any) return true;
-    }
-  }
 };
 
 template <int G>
@@ -275,79 +214,81 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
 
   // ------------------------------------------------------------------------------------------ roles
   if (warp == WS_SCHED_WARP) {
-    // ---- scheduler. It walks the schedule (WsSched) and publishes every tile to the queue, with the cache slots of
-    // the tile's pages. Lane l keeps block-table entry l of a 32-entry window per group in registers (the window in use
-    // and the next one), and the first two windows of the item that will be handed out next: no global load sits
-    // between two tiles.
+    // ---- scheduler. Lanes 8g .. 8g+7 look after softmax group g (its item and how far it is; the same values in all
+    // eight lanes), lane 8g+p after page p of the group's next tile. One round hands items to the groups that ran out
+    // (the CTA's next items, in group order), then publishes the next tile of every group that has one, in group
+    // order: up to four queue entries per round, with the block-table lookups of all of them in flight together.
+    const int g = lane >> 3, p = lane & 7;
     const int ppt = WS_TILE >> page_shift;  // pages per tile: 8, 4, 2 or 1
-    WsSched sc;
-    sc.init(seq_lens, num_items, Hkv, splits);
-    WsQuad bt0, bt1;
-    bt0.fill(0);
-    bt1.fill(0);
-    int pre0 = 0, pre1 = 0, pre_it = -1;
-    auto bt_load = [&](const WsItem& x, int window) -> int {  // entries [32 window, 32 window + 32) of the item's pages
-      const int npages = (x.t_end - x.t_begin + page_size - 1) >> page_shift;
-      const int e = window * 32 + lane;
-      return e < npages ? __ldg(block_table + static_cast<size_t>(x.b) * max_pages + (x.t_begin >> page_shift) + e) : 0;
-    };
-    auto prefetch_next = [&]() {  // for the item the walk will look at next (its length has landed long ago)
-      if (sc.next_it < num_items) {
-        const WsItem nx = ws_item(sc.next_it, Hkv, splits, sc.len_a);
-        pre0 = bt_load(nx, 0);
-        pre1 = bt_load(nx, 1);
-        pre_it = sc.next_it;
+    const unsigned seg_mask = 0xffu << (g * 8);
+    int next_it = blockIdx.x, gt = 0;
+    int rem = 0, nt = 0, ib = 0, ikvh = 0, isp = 0, tb = 0, te = 0;
+    bool ok = true;
+    for (;;) {
+      // -- items for the groups that have none
+      const bool needy = rem == 0;
+      const unsigned need4 = __ballot_sync(0xffffffffu, needy && p == 0);  // bits 0, 8, 16, 24
+      const int before = __popc(need4 & ((1u << (g * 8)) - 1u));
+      const int cand = next_it + before * static_cast<int>(gridDim.x);
+      if (needy && cand < num_items) {
+        const WsItem x = ws_item(cand, Hkv, splits, ws_len(cand, num_items, Hkv, splits, seq_lens));
+        if (x.ntiles > 0) {
+          rem = nt = x.ntiles;
+          ib = x.b;
+          ikvh = x.kvh;
+          isp = x.sp;
+          tb = x.t_begin;
+          te = x.t_end;
+        } else if (splits == 1) {  // nobody else looks at an item without tiles: its (empty) result is written here
+          __nv_bfloat16* o = out + static_cast<size_t>(x.b) * out_stride + static_cast<size_t>(x.kvh) * G * WS_D;
+          for (int i = p; i < G * WS_D; i += 8) o[i] = __float2bfloat16(0.f);
+        } else if (p < G) {
+          const size_t idx = (static_cast<size_t>(x.b) * Hq + x.kvh * G + p) * splits + x.sp;
+          part_ml[idx * 2 + 0] = -INFINITY;
+          part_ml[idx * 2 + 1] = 0.f;
+        }
       }
-    };
-    prefetch_next();
-    auto on_assign = [&](int w, const WsItem& x, int) -> bool {
-      const int this_it = sc.next_it - sc.stride;
-      if (pre_it == this_it) {
-        bt0.set(w, pre0);
-        bt1.set(w, pre1);
-      } else {  // an item without tiles came in between: fetch directly
-        bt0.set(w, bt_load(x, 0));
-        bt1.set(w, bt_load(x, 1));
+      const int handed = min(__popc(need4), max(0, (num_items - next_it + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x)));
+      next_it += handed * static_cast<int>(gridDim.x);
+      // -- the next tile of every group that has one
+      const bool active = rem > 0;
+      const unsigned act4 = __ballot_sync(0xffffffffu, active && p == 0);
+      if (act4 == 0) {
+        if (next_it >= num_items) break;
+        continue;  // only items without tiles this round
       }
-      prefetch_next();
-      return true;
-    };
-    auto on_empty = [&](const WsItem& x) -> bool {  // nobody else looks at an item without tiles: its result is written here
-      if (splits == 1) {
-        __nv_bfloat16* o = out + static_cast<size_t>(x.b) * out_stride + static_cast<size_t>(x.kvh) * G * WS_D;
-        for (int i = lane; i < G * WS_D; i += 32) o[i] = __float2bfloat16(0.f);
-      } else if (lane < G) {
-        const size_t idx = (static_cast<size_t>(x.b) * Hq + x.kvh * G + lane) * splits + x.sp;
-        part_ml[idx * 2 + 0] = -INFINITY;
-        part_ml[idx * 2 + 1] = 0.f;
+      const int my_gt = gt + __popc(act4 & ((1u << (g * 8)) - 1u));
+      const int e = my_gt & (WS_SQ - 1);
+      int slot0 = 0;
+      int4 hdr = make_int4(0, 0, 0, 0);
+      if (active) {
+        const int r = nt - rem;
+        const int valid = min(WS_TILE, te - (tb + r * WS_TILE));
+        const int npages = (valid + page_size - 1) >> page_shift;
+        if (p < npages)
+          slot0 = __ldg(block_table + static_cast<size_t>(ib) * max_pages + (tb >> page_shift) + r * ppt + p) * page_size;
+        const int flags = (r == 0 ? WS_F_FIRST : 0) | (rem == 1 ? WS_F_LAST : 0) | (g << WS_F_GROUP_SHIFT);
+        hdr = make_int4(ib, ikvh | (isp << 16), valid | flags, npages);
+        ok = mbar_wait(&sq_empty[e], ((my_gt / WS_SQ) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
       }
-      return true;
-    };
-    auto publish = [&](int gt, const int4& hdr, int slot0) -> bool {
+      if (!__all_sync(0xffffffffu, ok)) break;
+      if (active) {
+        if (p == 0) sq_hdr[e] = hdr;
+        sq_slot[e][p] = slot0;
+        __syncwarp(seg_mask);
+        if (p == 0) mbar_arrive(&sq_full[e]);
+        --rem;
+      }
+      gt += __popc(act4);
+    }
+    if (__all_sync(0xffffffffu, ok)) {  // end of the stream
       const int e = gt & (WS_SQ - 1);
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(&sq_empty[e], ((gt / WS_SQ) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
-      ok = __shfl_sync(0xffffffffu, ok, 0);
-      if (!ok) return false;
-      if (lane == 0) sq_hdr[e] = hdr;
-      if (lane < 8) sq_slot[e][lane] = slot0;
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sq_full[e]);
-      return true;
-    };
-    auto on_tile = [&](int w, const WsItem& x, int r, int gt, int, int) -> bool {
-      const int e0 = r * ppt;  // the tile's first block-table entry within the item
-      if (r > 0 && (e0 & 31) == 0) {
-        bt0.set(w, bt1.get(w));
-        bt1.set(w, bt_load(x, (e0 >> 5) + 1));
+      ok = mbar_wait(&sq_empty[e], ((gt / WS_SQ) & 1) ^ 1, cta_abort, status, ERR_WAIT_EMPTY);
+      if (__all_sync(0xffffffffu, ok) && lane == 0) {
+        sq_hdr[e] = make_int4(0, 0, WS_F_DONE, 0);
+        mbar_arrive(&sq_full[e]);
       }
-      const int valid = min(WS_TILE, x.t_end - (x.t_begin + r * WS_TILE));
-      const int npages = (valid + page_size - 1) >> page_shift;
-      const int slot0 = __shfl_sync(0xffffffffu, bt0.get(w), (e0 & 31) + (lane & (ppt - 1))) * page_size;
-      const int flags = (r == 0 ? WS_F_FIRST : 0) | (r == x.ntiles - 1 ? WS_F_LAST : 0) | (w << WS_F_GROUP_SHIFT);
-      return publish(gt, make_int4(x.b, x.kvh | (x.sp << 16), valid | flags, npages), lane < npages ? slot0 : 0);
-    };
-    if (sc.run(on_assign, on_empty, on_tile)) publish(sc.gt, make_int4(0, 0, WS_F_DONE, 0), 0);
+    }
   } else if (warp == 0 || warp == 2) {
     // ---- K producer (warp 0; also brings Q when a group starts an item) and V producer (warp 2): tile by tile from
     // the queue, lane p copies page p
@@ -399,9 +340,13 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       nq.fill(0);
       oq.fill(0);
       bool done = false;
+#ifdef SB_WS_CHAIN_TIMING
+      long long itick[4] = {0, 0, 0, 0}, itick_last = clock64();
+#endif
       for (int gt = 0;; ++gt) {
         const int e = gt & (WS_SQ - 1), s = gt % WS_NK;
         if (!mbar_wait(&sq_full[e], (gt / WS_SQ) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        WS_ITICK(0)
         const int4 h = sq_hdr[e];
         mbar_arrive(&sq_empty[e]);
         if (h.z & WS_F_DONE) {
@@ -417,6 +362,7 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         const int qs = w * 2 + (ordinal & 1);
         if (!mbar_wait(&full_k[s], (gt / WS_NK) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
         if (first && !mbar_wait(&q_full[qs], (ordinal >> 1) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        WS_ITICK(1)
         if (load_path_only) {  // measurement mode: hand the slots straight back to the producers
           mbar_arrive(&k_empty[s]);
           if (last) mbar_arrive(&q_empty[qs]);
@@ -424,6 +370,7 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         }
         // the group has drained S^T of its previous tile (and is therefore done with the mailbox slot of the one before)
         if (!mbar_wait(&s_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
+        WS_ITICK(2)
         info_s[w][n & 1] = make_int4(h.x, h.y, h.z, gt);
         mbar_arrive(&info_full[w]);
         tc_fence_after();
@@ -436,7 +383,11 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         umma_commit(&s_full[w]);
         umma_commit(&k_empty[s]);             // the K slot is free once S^T exists
         if (last) umma_commit(&q_empty[qs]);  // the item's last use of its Q slot
+        WS_ITICK(3)
       }
+#ifdef SB_WS_CHAIN_TIMING
+      for (int i = 0; i < 4; ++i) atomicAdd(&ws_issue_ticks[i], static_cast<unsigned long long>(itick[i]));
+#endif
       if (done && !load_path_only) {
         for (int w = 0; w < WS_NWG; ++w) {  // tell every group that nothing more will come
           const int n = nq.get(w);
@@ -452,6 +403,9 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       constexpr uint32_t idesc_o = make_idesc(128, 16, 1, 1, 1, 0);  // A = V tile read MN-major, B = P^T
       WsQuad nq;
       nq.fill(0);
+#ifdef SB_WS_CHAIN_TIMING
+      long long itick[4] = {0, 0, 0, 0}, itick_last = clock64();
+#endif
       for (int gt = 0;; ++gt) {
         const int e = gt & (WS_SQ - 1), s = gt % WS_NV;
         if (!mbar_wait(&sq_full[e], (gt / WS_SQ) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
@@ -466,10 +420,12 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           mbar_arrive(&v_empty[s]);
           continue;
         }
-        if (!mbar_wait(&p_ready[w], n & 1, cta_abort, status, ERR_WAIT_FULL) ||
-            !mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL) ||
-            !mbar_wait(&o_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY))
-          break;
+        if (!mbar_wait(&p_ready[w], n & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        WS_ITICK(0)
+        if (!mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+        WS_ITICK(1)
+        if (!mbar_wait(&o_free[w], (n & 1) ^ 1, cta_abort, status, ERR_WAIT_TMEM_EMPTY)) break;
+        WS_ITICK(2)
         tc_fence_after();
         const uint32_t v_addr = smem_u32(sV + s * WS_KV_TILE);
         const uint32_t p_addr = smem_u32(sP + w * WS_P_BYTES);
@@ -484,7 +440,11 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
                      (kc | k) != 0 ? 1u : 0u);
         umma_commit(&o_full[w]);
         umma_commit(&v_empty[s]);
+        WS_ITICK(3)
       }
+#ifdef SB_WS_CHAIN_TIMING
+      for (int i = 0; i < 4; ++i) atomicAdd(&ws_issue_ticks[4 + i], static_cast<unsigned long long>(itick[i]));
+#endif
     }
   } else if (!load_path_only) {
     // --------------------------------------------------------------------------------------- softmax groups
@@ -525,6 +485,10 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
     };
     int b = 0, kvh = 0, sp = 0, items_done = 0;
     bool ok = true;
+#ifdef SB_WS_CHAIN_TIMING
+    const bool timing = w == 0 && q == 0 && lane == 0;
+    long long tick_acc[7] = {0, 0, 0, 0, 0, 0, 0}, tick_last = clock64();
+#endif
     for (int n = 0; ok; ++n) {  // the group's tiles, in the order the S^T issuer announces them
       const int par = n & 1;
       ok = mbar_wait(&info_full[w], par, cta_abort, status, ERR_WAIT_FULL);
@@ -552,6 +516,7 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       ok = mbar_wait(&s_full[w], par, cta_abort, status, ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
+      WS_TICK(0)
       tc_fence_after();
       float sc[G];
       {
@@ -569,13 +534,16 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
         const float wm = ws_warp_max(sc[g]);
         if (lane == 0) red_m[w][par][g][q] = wm;
       }
+      WS_TICK(1)
       ok = group_sync();
       if (!ok) break;
+      WS_TICK(2)
       // ---- the previous tile's product is long done: fold it in (this also frees P^T and O^T of the group)
       if (!first) {
         ok = merge(n - 1);
         if (!ok) break;
       }
+      WS_TICK(3)
       // ---- p = 2^(s - tile max), running max / sum bookkeeping, P^T to shared memory
       const int kc = wt >> 6, col = wt & 63;
       uint8_t* p_col = sP + w * WS_P_BYTES + kc * (WS_MAXG * 128) + (col & 7) * 2;
@@ -609,6 +577,10 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[w]);
+      WS_TICK(4)
+#ifdef SB_WS_CHAIN_TIMING
+      tick_acc[6] += 1;
+#endif
       if (!last) continue;
       // ---- last tile of the item: wait for its product right away, then write the item's result
       ok = merge(n);
@@ -642,7 +614,12 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           }
         }
       }
+      WS_TICK(5)
     }
+#ifdef SB_WS_CHAIN_TIMING
+    if (timing)
+      for (int i = 0; i < 7; ++i) atomicAdd(&ws_chain_ticks[i], static_cast<unsigned long long>(tick_acc[i]));
+#endif
   }
 
   // ---- teardown
@@ -733,6 +710,20 @@ static int g_ws_load_path_only = 0;
 // Measurement switch: with a non-zero value the kernel's producers run as usual and every landed tile is handed straight
 // back (no products, no softmax, no output): its duration is what the copy path alone costs for a given batch.
 extern "C" void sb_paged_decode_ws_load_path_only(int on) { sb::g_ws_load_path_only = on; }
+
+#ifdef SB_WS_CHAIN_TIMING
+// Reads (and with `reset` clears) the counters of a measurement build into out[16]: chain, then issuers.
+extern "C" int sb_paged_decode_ws_chain_ticks(unsigned long long* out, int reset) {
+  cudaError_t e = cudaMemcpyFromSymbol(out, sb::ws_chain_ticks, sizeof(unsigned long long) * 8);
+  if (e == cudaSuccess) e = cudaMemcpyFromSymbol(out + 8, sb::ws_issue_ticks, sizeof(unsigned long long) * 8);
+  if (e == cudaSuccess && reset) {
+    const unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    e = cudaMemcpyToSymbol(sb::ws_chain_ticks, zero, sizeof(zero));
+    if (e == cudaSuccess) e = cudaMemcpyToSymbol(sb::ws_issue_ticks, zero, sizeof(zero));
+  }
+  return (int)e;
+}
+#endif
 
 // Head dim 64, at most 8 query heads per kv head. part_o / part_ml: workspaces [B, Hq, splits, 64] and [B, Hq, splits, 2]
 // fp32, used (with the combine kernel) when splits > 1; with one split the kernel writes `out` itself. Returns 0, a cudaError_t value, or -1 for shapes this kernel does not cover.

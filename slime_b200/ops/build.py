@@ -25,6 +25,8 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v",
 ]  # fmt: skip
+# extra compiler flags, e.g. SLIME_B200_NVCC_EXTRA="-DSB_WS_CHAIN_TIMING" for a measurement build
+NVCC_FLAGS += os.environ.get("SLIME_B200_NVCC_EXTRA", "").split()
 
 
 def _nvcc() -> str:

@@ -182,6 +182,27 @@ def bench_decode(a):
                 fn()
         t_of[name] = time_ms(gk.replay, a.iters, flush=False) / a.reps
         _emit(kind="decode_kernel", name=name, batch=B, context=ctx, us=1e3 * t_of[name])
+    try:  # a measurement build (-DSB_WS_CHAIN_TIMING) also reports where a softmax group's time per tile goes
+        import ctypes
+
+        ticks_fn = _lib.bind("sb_paged_decode_ws_chain_ticks", [ctypes.c_void_p, ctypes.c_int])
+    except AttributeError:
+        ticks_fn = None
+    if ticks_fn is not None and d == 64:
+        buf = (ctypes.c_ulonglong * 16)()
+        torch.cuda.synchronize()
+        ticks_fn(ctypes.addressof(buf), 1)
+        attn_ws()
+        torch.cuda.synchronize()
+        ticks_fn(ctypes.addressof(buf), 0)
+        tiles = max(1, buf[6])
+        names = ["wait_s", "tmem_ld_max", "group_exchange", "merge_prev", "exp_p_fence", "end_of_item"]
+        _emit(kind="decode_attn_ws_chain", batch=B, context=ctx, tiles=int(buf[6]),
+              cycles_per_tile={k: buf[i] / tiles for i, k in enumerate(names)})
+        inames = ["s_queue", "s_wait_k", "s_wait_group", "s_issue", "o_wait_p", "o_wait_v", "o_wait_group", "o_issue"]
+        # the issuers handle the tiles of all four groups: per tile of the CTA (4 x the tiles the clocked group saw)
+        _emit(kind="decode_attn_ws_issuers", batch=B, context=ctx,
+              cycles_per_cta_tile={k: buf[8 + i] / (4 * tiles) for i, k in enumerate(inames)})
     est = cfg.num_layers * sum(t_of[k] for k in per_layer) + t_of["gemm_lm_head"] + t_of["sample"] + t_of["rmsnorm_add"]
 
     def layer_loop():
