@@ -36,7 +36,7 @@ constexpr int WS_KV_TILE = WS_TILE * 128;        // one K (or V) tile: 128 token
 constexpr int WS_P_BYTES = 2 * WS_MAXG * 128;    // P^T: 2 chunks of 64 tokens x 8 heads x 128 B
 constexpr int WS_Q_BYTES = 16 * 128;             // 16 rows (heads) x 64 dims
 constexpr int WS_SQ = 16;                         // entries of the tile queue (K producer -> V producer and both issuers)
-constexpr int WS_NBAR = 2 * WS_NK + 2 * WS_NV + 7 * WS_NWG + 2 * WS_NQ + 2 * WS_SQ;
+constexpr int WS_NBAR = 2 * WS_NK + 2 * WS_NV + 8 * WS_NWG + 2 * WS_NQ + 2 * WS_SQ;
 constexpr int WS_SMEM = (WS_NK + WS_NV) * WS_KV_TILE + WS_NWG * WS_P_BYTES + WS_NQ * WS_Q_BYTES + WS_NBAR * 8 + 64 + 1024;
 // flags of a tile-queue / mailbox word (low 8 bits: valid tokens of the tile; bits 12-13: the group)
 constexpr int WS_F_FIRST = 1 << 8, WS_F_LAST = 1 << 9, WS_F_DONE = 1 << 10, WS_F_GROUP_SHIFT = 12;
@@ -152,7 +152,8 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
   uint64_t* o_free = o_full + WS_NWG;
   uint64_t* wg_bar = o_free + WS_NWG;
   uint64_t* info_full = wg_bar + WS_NWG;
-  uint64_t* q_full = info_full + WS_NWG;
+  uint64_t* v_landed = info_full + WS_NWG;
+  uint64_t* q_full = v_landed + WS_NWG;
   uint64_t* q_empty = q_full + WS_NQ;
   uint64_t* sq_full = q_empty + WS_NQ;
   uint64_t* sq_empty = sq_full + WS_SQ;
@@ -186,6 +187,7 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       mbar_init(&o_free[w], 4);
       mbar_init(&wg_bar[w], 4);
       mbar_init(&info_full[w], 1);
+      mbar_init(&v_landed[w], 1);
     }
     for (int s = 0; s < WS_NQ; ++s) {
       mbar_init(&q_full[s], 1);
@@ -420,6 +422,13 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
           mbar_arrive(&v_empty[s]);
           continue;
         }
+        if ((flags & 0xff) < WS_TILE) {
+          // a tile that ends inside the sequence: its group clears the V rows past the end before it announces P^T, and
+          // may only do so once the copy has landed. This thread sees every V tile land, in order, so it can tell; a
+          // group that looked at full_v itself could be a whole lap of the ring away from what the parity bit means.
+          if (!mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
+          mbar_arrive(&v_landed[w]);
+        }
         if (!mbar_wait(&p_ready[w], n & 1, cta_abort, status, ERR_WAIT_FULL)) break;
         WS_ITICK(0)
         if (!mbar_wait(&full_v[s], (gt / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL)) break;
@@ -483,7 +492,7 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       if (lane == 0) mbar_arrive(&o_free[w]);
       return true;
     };
-    int b = 0, kvh = 0, sp = 0, items_done = 0;
+    int b = 0, kvh = 0, sp = 0, items_done = 0, npartial = 0;
     bool ok = true;
 #ifdef SB_WS_CHAIN_TIMING
     const bool timing = w == 0 && q == 0 && lane == 0;
@@ -563,8 +572,9 @@ decode_attn_ws_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_cons
       }
       if (valid < WS_TILE) {
         // rows past the end of the sequence hold whatever an older tile left there: p is 0 for them, but 0 x NaN
-        // would poison O^T, so they are cleared once the copy of this tile's V has landed
-        ok = mbar_wait(&full_v[s], (g_t / WS_NV) & 1, cta_abort, status, ERR_WAIT_FULL);
+        // would poison O^T, so they are cleared once the copy of this tile's V has landed (the O^T issuer says when)
+        ok = mbar_wait(&v_landed[w], npartial & 1, cta_abort, status, ERR_WAIT_FULL);  // from the O^T issuer
+        ++npartial;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (wt >= valid) {
