@@ -432,8 +432,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     same_layout = k_cache.stride() == v_cache.stride() and k_cache.stride(2) == 1
     # Head dim 64: the persistent warp-specialised kernel (four softmax groups per SM, one work item each). Measured
     # against the two-chain kernel below: 28.7 / 36.1 us at 256 requests x 2 kv heads and context 768, 50.4 / 74.0 us at
-    # 512 requests, 112.7 / 158.1 us at context 4096, 12.8 / 12.8 us at 64 requests; below that it is not measured and
-    # the two-chain kernel stays. SLIME_B200_DECODE_ATTN_WS=1 / 0 forces it on / off.
+    # 512 requests, 21.6 / 33.6 us at 192, 16.0 / 17.0 us at 96, 112.7 / 158.1 us at context 4096, 13.3 / 12.9 us at 64
+    # requests; below half an item per SM the two-chain kernel stays. SLIME_B200_DECODE_ATTN_WS=1 / 0 forces it on / off.
     ws_env = os.environ.get("SLIME_B200_DECODE_ATTN_WS", "")
     ws_ok = use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and same_layout and ws_env != "0"
     if ws_ok and (ws_env == "1" or 2 * B * Hkv >= _lib.sm_count(q.device)):
