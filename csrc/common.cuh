@@ -327,9 +327,39 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 // Host side: driver entry point for cuTensorMapEncodeTiled resolved through the
 // runtime so the extension does not link against libcuda.
 #ifndef __CUDACC_RTC__
+#include <mutex>
+#include <set>
 #include <stdexcept>
 #include <string>
 namespace sb {
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel, so "already raised" is remembered
+// per (device, kernel) pair; the table is shared by every translation unit of the library and guarded by a mutex
+// because actor threads and autograd's backward threads launch concurrently.
+inline cudaError_t ensure_dynamic_smem(const void* kernel, int bytes) {
+  static std::mutex mu;
+  static std::set<std::pair<int, const void*>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({dev, kernel})) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({dev, kernel});
+  return e;
+}
+
+// How long a kernel of this library waits for another GPU (signal-pad barriers, per-CTA peer flags) before it gives
+// up, records ERR_WAIT_PEER in the status word and returns. A launch argument, not a constant: tests make it a few
+// milliseconds, production keeps seconds. SLIME_B200_PEER_WAIT_MS sets the initial value.
+inline unsigned long long& peer_wait_limit_ns() {
+  static unsigned long long v = [] {
+    const char* e = std::getenv("SLIME_B200_PEER_WAIT_MS");
+    const long long ms = e != nullptr ? std::atoll(e) : 0;
+    return ms > 0 ? static_cast<unsigned long long>(ms) * 1000000ull : WAIT_LIMIT_NS;
+  }();
+  return v;
+}
+
 // 1 = launch with the programmatic-stream-serialization attribute (default), 0 = plain stream order.
 inline int& pdl_enabled() {
   static int v = [] {

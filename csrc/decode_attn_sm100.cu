@@ -412,12 +412,7 @@ static int launch_decode_attn(dim3 grid, cudaStream_t s, const CUtensorMap& tk, 
                               int page_size, int page_shift, int max_pages, int q_stride, int out_stride, int splits,
                               float scale, int* status) {
   auto kern = decode_attn_kernel<D, G>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<D>::TOTAL);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), DecSmem<D>::TOTAL); e != cudaSuccess) return (int)e;
   return (int)launch_pdl(kern, grid, dim3(DA_THREADS), DecSmem<D>::TOTAL, s, tk, tv, q, bt, sl, out, po, pml, Hq, Hkv,
                          page_size, page_shift, max_pages, q_stride, out_stride, splits, scale, status);
 }

@@ -703,12 +703,7 @@ static int ws_launch(int grid, cudaStream_t s, const CUtensorMap& tk, const CUte
                      const int* sl, __nv_bfloat16* out, float* po, float* pml, int num_items, int Hq, int Hkv, int page_size,
                      int page_shift, int max_pages, int splits, int out_stride, float scale, int* status, int load_path_only) {
   auto kern = decode_attn_ws_kernel<G>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, WS_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), WS_SMEM); e != cudaSuccess) return (int)e;
   return (int)launch_pdl(kern, dim3(grid), dim3(WS_THREADS), WS_SMEM, s, tk, tv, tq, bt, sl, out, po, pml, num_items, Hq, Hkv,
                          page_size, page_shift, max_pages, splits, out_stride, scale, status, load_path_only);
 }

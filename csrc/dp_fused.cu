@@ -8,7 +8,14 @@
 //                        all-gather: the new bf16 parameters are stored straight into every rank's parameter buffer
 //                        (P2P stores, or one multimem.st that the switch replicates).
 //   sb_symm_barrier      all ranks meet; signal words live in each rank's symmetric signal pad. The wait is bounded
-//                        (2 s): on expiry the kernel records a status word and returns, it never spins forever.
+//                        (sb_set_peer_wait_limit_ns, 2 s unless changed): on expiry the kernel records ERR_WAIT_PEER in
+//                        the status word and returns, it never spins forever.
+//
+// A non-zero status word is sticky until the host clears it. Every kernel here looks at it first: a barrier still
+// raises its own flag (so the peers are not held up) but does not wait; the reduce and the Adam kernel touch no data;
+// the partial-sum kernel turns it into the "skip this step" flag ctl[1], which the caller all-reduces together with
+// the squared norm, so that after one expired wait EVERY rank skips the update and the parameters stay unchanged and
+// identical. The host reads the status word where it reads the gradient norm and raises.
 //
 // Order per step:  barrier -> reduce_shard -> (all-reduce of one scalar: the squared norm) -> adam_bcast -> barrier.
 // The gradient traffic is what an NCCL reduce-scatter moves, and the parameter traffic what an all-gather moves, but
@@ -32,16 +39,19 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* addr) {
 }
 
 // One block, one thread per peer. Slot layout in every rank's pad: words [base + r] = last epoch rank r announced here.
-__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int base, int* status) {
+__global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t epoch, int base, int* status,
+                                    unsigned long long limit_ns) {
   const int p = threadIdx.x;
   if (p < world) {
+    const bool failed = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
     __threadfence_system();  // everything this GPU wrote before the barrier is visible to peers that see the flag
     st_release_sys(static_cast<uint32_t*>(pads.p[p]) + base + rank, epoch);
+    if (failed) return;  // an earlier wait expired: announce, do not wait again
     const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + base + p;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t it = 0;
     while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (p << 8));
         break;
       }
@@ -51,19 +61,22 @@ __global__ void symm_barrier_kernel(PeerPtrs pads, int rank, int world, uint32_t
 
 // Same barrier with the epoch kept in device memory (`counter`, advanced by the kernel): the launch arguments are
 // constant, so the barrier still synchronises when it is replayed from a CUDA graph.
-__global__ void symm_barrier_dev_kernel(PeerPtrs pads, int rank, int world, uint32_t* counter, int base, int* status) {
+__global__ void symm_barrier_dev_kernel(PeerPtrs pads, int rank, int world, uint32_t* counter, int base, int* status,
+                                        unsigned long long limit_ns) {
   const int p = threadIdx.x;
   if (p < world) {
+    const bool failed = status != nullptr && *reinterpret_cast<volatile int*>(status) != 0;
     const uint32_t epoch = *counter + 1;
     __syncwarp((1u << world) - 1u);
     if (p == 0) *counter = epoch;
     __threadfence_system();
     st_release_sys(static_cast<uint32_t*>(pads.p[p]) + base + rank, epoch);
+    if (failed) return;
     const uint32_t* mine = static_cast<const uint32_t*>(pads.p[rank]) + base + p;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t it = 0;
     while (static_cast<int32_t>(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (p << 8));
         break;
       }
@@ -91,9 +104,13 @@ __device__ __forceinline__ void multimem_st_b32x4(void* mc_addr, uint4 v) {
 template <bool MC>
 __global__ void __launch_bounds__(256)
 dp_reduce_shard_kernel(PeerPtrs grads, int world, int rank, size_t off, size_t n, float* __restrict__ out,
-                       float* __restrict__ partials) {
+                       float* __restrict__ partials, const int* __restrict__ status) {
   __shared__ float scratch[32];
   float ss = 0.f;
+  if (status != nullptr && *status != 0) {  // the barrier before this kernel gave up: the peers' buffers may be unfinished
+    if (threadIdx.x == 0) partials[blockIdx.x] = 0.f;
+    return;
+  }
   const size_t nvec = n >> 2;
   for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -117,12 +134,16 @@ dp_reduce_shard_kernel(PeerPtrs grads, int world, int rank, size_t off, size_t n
 }
 
 // ctl[slot] += sum(partials[0..n)) in a fixed order (one block), so the norm does not depend on scheduling.
-__global__ void dp_sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ ctl, int slot) {
+__global__ void dp_sum_partials_kernel(const float* __restrict__ partials, int n, float* __restrict__ ctl, int slot,
+                                       const int* __restrict__ status) {
   __shared__ float scratch[32];
   float s = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) s += partials[i];
   s = block_sum<256>(s, scratch);
-  if (threadIdx.x == 0) ctl[slot] += s;
+  if (threadIdx.x == 0) {
+    ctl[slot] += s;
+    if (status != nullptr && *status != 0) ctl[1] += 1.f;  // summed over ranks by the caller: everyone skips the step
+  }
 }
 
 struct DpAdamArgs {
@@ -136,7 +157,8 @@ __global__ void __launch_bounds__(256)
 dp_adam_bcast_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v, const float* __restrict__ g,
                      PeerPtrs params, int world, int rank, size_t off, size_t n, DpAdamArgs a,
                      const float* __restrict__ ctl, int stateless) {
-  if (ctl != nullptr && ctl[1] != 0.f) return;  // non-finite gradients: the whole step is skipped on every rank
+  // non-finite gradients, or a wait that expired on some rank: the whole step is skipped on every rank
+  if (ctl != nullptr && ctl[1] != 0.f) return;
   float coef = a.grad_scale;
   if (ctl != nullptr && a.max_norm > 0.f) {
     const float norm = sqrtf(ctl[0]) * a.grad_scale;
@@ -194,12 +216,16 @@ dp_adam_bcast_kernel(float* __restrict__ p, float* __restrict__ m, float* __rest
 
 }  // namespace sb
 
+// Wait limit of every kernel that waits for another GPU, in nanoseconds (0 restores the 2 s default). Process-wide.
+extern "C" void sb_set_peer_wait_limit_ns(unsigned long long ns) { sb::peer_wait_limit_ns() = ns ? ns : sb::WAIT_LIMIT_NS; }
+extern "C" unsigned long long sb_get_peer_wait_limit_ns(void) { return sb::peer_wait_limit_ns(); }
+
 extern "C" int sb_symm_barrier(const void* const* pads, int rank, int world, unsigned epoch, int base_word, int* status,
                                cudaStream_t s) {
   if (world < 1 || world > 8 || rank < 0 || rank >= world) return (int)cudaErrorInvalidValue;
   sb::PeerPtrs pp{};
   for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(pads[i]);
-  sb::symm_barrier_kernel<<<1, 32, 0, s>>>(pp, rank, world, epoch, base_word, status);
+  sb::symm_barrier_kernel<<<1, 32, 0, s>>>(pp, rank, world, epoch, base_word, status, sb::peer_wait_limit_ns());
   return (int)cudaGetLastError();
 }
 
@@ -208,15 +234,16 @@ extern "C" int sb_symm_barrier_dev(const void* const* pads, int rank, int world,
   if (world < 1 || world > 8 || rank < 0 || rank >= world || counter == nullptr) return (int)cudaErrorInvalidValue;
   sb::PeerPtrs pp{};
   for (int i = 0; i < world; ++i) pp.p[i] = const_cast<void*>(pads[i]);
-  sb::symm_barrier_dev_kernel<<<1, 32, 0, s>>>(pp, rank, world, counter, base_word, status);
+  sb::symm_barrier_dev_kernel<<<1, 32, 0, s>>>(pp, rank, world, counter, base_word, status, sb::peer_wait_limit_ns());
   return (int)cudaGetLastError();
 }
 
 // grads: `world` pointers to every rank's fp32 gradient buffer (own included), or, with multicast != 0, one multicast
 // address in grads[0]. out: where this rank keeps the reduced shard (usually its own buffer at `off`). partials: scratch
 // of at least 1184 floats. ctl[0] accumulates the shard's squared norm.
+// status: the device status word (may be null); when it is non-zero the kernel reads nothing and ctl[1] is raised.
 extern "C" int sb_dp_reduce_shard(const void* const* grads, int world, int rank, int multicast, long off, long n, float* out,
-                                  float* partials, float* ctl, cudaStream_t s) {
+                                  float* partials, float* ctl, const int* status, cudaStream_t s) {
   if (n == 0) return 0;
   if (world < 1 || world > 8 || (n & 3) || (off & 3)) return (int)cudaErrorInvalidValue;
   sb::PeerPtrs pp{};
@@ -224,10 +251,10 @@ extern "C" int sb_dp_reduce_shard(const void* const* grads, int world, int rank,
   long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (multicast)
-    sb::dp_reduce_shard_kernel<true><<<(int)blocks, 256, 0, s>>>(pp, world, rank, (size_t)off, (size_t)n, out, partials);
+    sb::dp_reduce_shard_kernel<true><<<(int)blocks, 256, 0, s>>>(pp, world, rank, (size_t)off, (size_t)n, out, partials, status);
   else
-    sb::dp_reduce_shard_kernel<false><<<(int)blocks, 256, 0, s>>>(pp, world, rank, (size_t)off, (size_t)n, out, partials);
-  sb::dp_sum_partials_kernel<<<1, 256, 0, s>>>(partials, (int)blocks, ctl, 0);
+    sb::dp_reduce_shard_kernel<false><<<(int)blocks, 256, 0, s>>>(pp, world, rank, (size_t)off, (size_t)n, out, partials, status);
+  sb::dp_sum_partials_kernel<<<1, 256, 0, s>>>(partials, (int)blocks, ctl, 0, status);
   return (int)cudaGetLastError();
 }
 

@@ -648,6 +648,16 @@ extern "C" int sb_rmsnorm_bwd_static(const void* dy, const void* h, const void* 
     static_fail("sb_rmsnorm_bwd_static: null pointer among dy/h/w/rstd/dh/dw");
     return (int)cudaErrorInvalidValue;
   }
+  // The kernels move 16 bytes at a time through dy, h, w, dres_in and dh (rows are H * 2 bytes, a multiple of 16
+  // because H % 8 == 0) and 4 bytes through rstd and dw: a base pointer off those boundaries would fault on the device,
+  // so it is turned away here.
+  auto misaligned = [](const void* p, uintptr_t a) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) & (a - 1)) != 0; };
+  if (misaligned(dy, 16) || misaligned(h, 16) || misaligned(w, 16) || misaligned(dres_in, 16) || misaligned(dh, 16) ||
+      misaligned(rstd, 4) || misaligned(dw, 4)) {
+    static_fail("sb_rmsnorm_bwd_static: misaligned pointer; dy, h, w, dres_in and dh must be 16-byte aligned, rstd and dw "
+                "4-byte aligned (H <= %d)", SB_RMSNORM_STATIC_MAX_H);
+    return (int)cudaErrorInvalidValue;
+  }
   float* scratch = nullptr;
   if (int rc = static_scratch_for_current_device(&scratch)) return rc;
   const int num_ctas = T < SB_RMSNORM_STATIC_MAX_CTAS ? T : SB_RMSNORM_STATIC_MAX_CTAS;

@@ -249,21 +249,13 @@ extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t
     const int grid = tiles < num_sms ? tiles : num_sms;
     cudaError_t e;
     if (out_f32) {
-      static bool configured = false;
-      if (!configured) {
-        e = cudaFuncSetAttribute(sb::gemm_fp8_block_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::F8_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-      }
+      e = sb::ensure_dynamic_smem(reinterpret_cast<const void*>(sb::gemm_fp8_block_kernel<true>), sb::F8_SMEM);
+      if (e != cudaSuccess) return (int)e;
       e = sb::launch_pdl(sb::gemm_fp8_block_kernel<true>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB, sa_t,
                          sb, C, M, N, K, ldc, status);
     } else {
-      static bool configured = false;
-      if (!configured) {
-        e = cudaFuncSetAttribute(sb::gemm_fp8_block_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, sb::F8_SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-      }
+      e = sb::ensure_dynamic_smem(reinterpret_cast<const void*>(sb::gemm_fp8_block_kernel<false>), sb::F8_SMEM);
+      if (e != cudaSuccess) return (int)e;
       e = sb::launch_pdl(sb::gemm_fp8_block_kernel<false>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB,
                          sa_t, sb, C, M, N, K, ldc, status);
     }

@@ -382,14 +382,9 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
                                  CU_TENSOR_MAP_SWIZZLE_128B);
   }
   auto kern = gemm_bf16_kernel<BN, STAGES, A_MN, B_MN, OUT_F32, TMA_EPI, Extra>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::TOTAL);
-    if (e != cudaSuccess) {
-      set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
-      return e;
-    }
-    configured = true;
+  if (cudaError_t e = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), S::TOTAL); e != cudaSuccess) {
+    set_last_error(std::string("cudaFuncSetAttribute: ") + cudaGetErrorString(e));
+    return e;
   }
   const int splitk = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;

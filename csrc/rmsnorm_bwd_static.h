@@ -16,8 +16,12 @@
 // array has to be zero at entry and nothing is cleared between calls.
 //
 // Limits. H must be a multiple of 8 and at most SB_RMSNORM_STATIC_MAX_H; T is unbounded (rows are strided over at
-// most SB_RMSNORM_STATIC_MAX_CTAS CTAs). A call outside the limits launches nothing, returns
-// cudaErrorInvalidValue (1) and leaves the reason in sb_last_error().
+// most SB_RMSNORM_STATIC_MAX_CTAS CTAs). dy, h, w, dres_in and dh must be 16-byte aligned (the kernels move eight
+// bf16 values per access; with H a multiple of 8 every row then is too), rstd and dw 4-byte aligned. A call outside
+// these limits launches nothing, returns cudaErrorInvalidValue (1) and leaves the reason in sb_last_error().
+// sb_last_error() returns a buffer that belongs to the calling host thread: read it on the thread that made the
+// failing call. The return value of a successful launch is whatever cudaGetLastError() reports after the second
+// kernel has been queued, so an asynchronous error raised by unrelated earlier work on the device can surface here.
 //
 // Set-up. The array's device address is looked up once per device (cudaGetSymbolAddress) and cached. Call
 // sb_rmsnorm_bwd_static_setup() with the device current to do that explicitly; otherwise the first

@@ -15,7 +15,8 @@
 //
 // The caller alternates between two partial buffers and places one full barrier (sb_symm_barrier) at the start of each
 // forward pass; that is what makes it safe for a fast rank to start the next GEMM while a slow one is still reading.
-// Every wait is bounded (2 s): on expiry the CTA records a status word, skips its rows and returns.
+// Every wait is bounded (sb_set_peer_wait_limit_ns, 2 s unless changed): on expiry the CTA records a status word, skips
+// its rows and returns; later launches see the status word and return at once (see the kernel).
 #include "common.cuh"
 
 namespace sb {
@@ -53,12 +54,15 @@ __global__ void __launch_bounds__(TP_THREADS)
 tp_ar_add_rmsnorm_kernel(TpPeerPtrs partial, TpPeerPtrs flags, uint32_t* __restrict__ epochs,
                          const __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ w,
                          __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ res_out, int T, int H, float eps,
-                         int rank, int world, int* status) {
+                         int rank, int world, int* status, unsigned long long limit_ns) {
   __shared__ float scratch[32];
   __shared__ int s_ok;
   const int b = blockIdx.x, tid = threadIdx.x;
-  if (tid == 0) s_ok = 1;
+  // A non-zero status word (an earlier wait of this process gave up) is sticky: the flag is still raised so that the
+  // peers are not held up, but this CTA neither waits nor produces rows; the host sees the status and raises.
+  if (tid == 0) s_ok = (status == nullptr || *reinterpret_cast<volatile int*>(status) == 0) ? 1 : 0;
   __syncthreads();
+  const bool failed = s_ok == 0;
   if (tid < world) {
     const uint32_t epoch = epochs[b] + 1;  // every thread < world reads the old value before thread 0 stores the new one
     __syncwarp((1u << world) - 1u);
@@ -68,8 +72,8 @@ tp_ar_add_rmsnorm_kernel(TpPeerPtrs partial, TpPeerPtrs flags, uint32_t* __restr
     const uint32_t* mine = static_cast<const uint32_t*>(flags.p[rank]) + b * 8 + tid;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t it = 0;
-    while (static_cast<int32_t>(tp_ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+    while (!failed && static_cast<int32_t>(tp_ld_acquire_sys(mine) - epoch) < 0) {
+      if ((++it & 0xff) == 0 && globaltimer_ns() - t0 > limit_ns) {
         if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (tid << 8));
         s_ok = 0;
         break;
@@ -162,9 +166,11 @@ extern "C" int sb_tp_ar_add_rmsnorm(const void* const* partial, const void* cons
   const int blocks = T < sb::TP_MAX_BLOCKS ? T : sb::TP_MAX_BLOCKS;
   if (multicast)
     sb::tp_ar_add_rmsnorm_kernel<true><<<blocks, sb::TP_THREADS, 0, s>>>(pp, ff, epochs, (const bf16*)residual, (const bf16*)w,
-                                                                         (bf16*)y, (bf16*)res_out, T, H, eps, rank, world, status);
+                                                                         (bf16*)y, (bf16*)res_out, T, H, eps, rank, world, status,
+                                                                         sb::peer_wait_limit_ns());
   else
     sb::tp_ar_add_rmsnorm_kernel<false><<<blocks, sb::TP_THREADS, 0, s>>>(pp, ff, epochs, (const bf16*)residual, (const bf16*)w,
-                                                                          (bf16*)y, (bf16*)res_out, T, H, eps, rank, world, status);
+                                                                          (bf16*)y, (bf16*)res_out, T, H, eps, rank, world, status,
+                                                                          sb::peer_wait_limit_ns());
   return (int)cudaGetLastError();
 }

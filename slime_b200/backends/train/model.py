@@ -338,6 +338,12 @@ def train_one_step(args, rollout_id, step_id, data_iterator, model: TrainModel, 
     lr = model.scheduler.get_lr()
     grad_norm = opt.step(grad_scale=1.0, lr=lr, skip_on_nonfinite=getattr(args, "check_for_nan_in_loss_and_grad", True))
     model.scheduler.step(increment=step_gbs)
+    if any(getattr(b, "fused", None) is not None for b in model.buffers):
+        # the peer-memory optimizer step has bounded waits: an expired one made every rank skip the update (the skip
+        # flag is all-reduced with the norm) and left a status word, which is surfaced here instead of training on
+        from slime_b200.ops import _lib
+
+        _lib.check_status(model.device)
     return reduce_train_step_metrics(args, logs, step_gbs), grad_norm
 
 

@@ -102,7 +102,7 @@ class DistributedOptimizer:
         Parameters replicated over TP are counted once per TP rank by this simple sum; the
         replicated tensors are norms/biases and contribute negligibly, and every rank applies
         the same coefficient, so training stays consistent."""
-        self.ctl[0] = 0.0
+        self.ctl.zero_()  # [squared norm, skip flag]; a fused reduce raises the flag itself when one of its waits gave up
         for b in self.buffers:
             g = b.grad_shard()
             if getattr(b, "fused", None) is not None:
@@ -117,7 +117,7 @@ class DistributedOptimizer:
         if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
             # shards are disjoint across DP ranks and model-parallel ranks hold different parameters,
             # so one sum over the whole trainer world gives the global norm
-            dist.all_reduce(self.ctl[0:1])
+            dist.all_reduce(self.ctl)  # the skip flag travels with the norm: every rank takes the same decision
         return self.ctl[0:1]
 
     # ---- update -----------------------------------------------------------------------------------
@@ -133,7 +133,8 @@ class DistributedOptimizer:
             bc1, bc2 = 1.0 - b1, 1.0 - b2
         self.compute_grad_sqnorm(grad_scale)
         # non-finite guard stays on the device: the flag turns the Adam kernel into a no-op
-        self.ctl[1] = (~torch.isfinite(self.ctl[0])).float() if skip_on_nonfinite else 0.0
+        if skip_on_nonfinite:
+            self.ctl[1] += (~torch.isfinite(self.ctl[0])).float()
         self.last_grad_norm = self.ctl[0:1].sqrt() * grad_scale  # device tensor; .item() only when logged
         for b, st in zip(self.buffers, self.state):
             g = b.grad_shard()

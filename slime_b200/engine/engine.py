@@ -98,6 +98,9 @@ class Engine:
         self.lp_hist = torch.zeros(self.ring, B, dtype=torch.float32, pin_memory=pin)
         self.tok_np, self.lp_np = self.tok_hist.numpy(), self.lp_hist.numpy()
         self.hist_events: list = [None] * self.ring
+        # tensor-parallel decode over peer memory has bounded waits; their status word rides along with the tokens
+        self.status_hist = torch.zeros(self.ring, dtype=torch.int32, pin_memory=pin) if self.runner._fused_tp is not None else None
+        self.status_np = self.status_hist.numpy() if self.status_hist is not None else None
         self.step_no = 0  # decode steps launched so far
         self.processed = 0  # decode steps whose results the host has consumed
         self.kept_hist: dict[int, tuple] = {}
@@ -109,7 +112,11 @@ class Engine:
     def add_request(self, input_ids, sampling: SamplingParams | dict | None = None, rid: str | None = None, **kw) -> Request:
         sp = sampling if isinstance(sampling, SamplingParams) else SamplingParams.from_dict(sampling)
         req = Request(rid=rid or uuid.uuid4().hex, input_ids=list(input_ids), sampling=sp, **kw)
-        req.seed = sp.sampling_seed if sp.sampling_seed is not None else (self.args.random_seed * 1000003 + hash(req.rid)) & 0x7FFFFFFFFFFF
+        # Without an explicit seed the stream is numbered by arrival order: the ranks of a tensor-parallel engine see the
+        # same requests in the same order, so they draw the same tokens (a hash of the random request id would differ
+        # from process to process).
+        self._req_counter = getattr(self, "_req_counter", 0) + 1
+        req.seed = sp.sampling_seed if sp.sampling_seed is not None else (self.args.random_seed * 1000003 + self._req_counter) & 0x7FFFFFFFFFFF
         room = self.max_context - len(req.input_ids)
         if room <= 0:
             self._finish(req, {"type": "length", "length": 0})
@@ -359,6 +366,10 @@ class Engine:
         slot = self.step_no % self.ring
         self.tok_hist[slot, :n].copy_(tok[:n], non_blocking=True)
         self.lp_hist[slot, :n].copy_(lp[:n], non_blocking=True)
+        if self.status_hist is not None:
+            from slime_b200.ops import _lib
+
+            self.status_hist[slot : slot + 1].copy_(_lib.status_word(self.device), non_blocking=True)
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -403,6 +414,12 @@ class Engine:
             ev = self.hist_events[slot]
             if ev is not None:
                 ev.synchronize()
+            if self.status_np is not None and self.status_np[slot] != 0:
+                from slime_b200.ops import _lib
+
+                code = int(self.status_np[slot])
+                _lib.status_word(self.device).zero_()
+                raise _lib.KernelWaitExpired(code & 0xFF, code >> 8)  # this step's hidden states were not all written
             if self.h_inspect.any():
                 for b in np.nonzero(self.h_inspect)[0]:
                     r = self.slot_req[b]

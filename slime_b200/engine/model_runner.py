@@ -354,10 +354,12 @@ class ModelRunner:
                 P(ds["seq_lens"]), P(ds["slots"]), n, ps, W, _lib.stream()), "sb_decode_prepare")  # fmt: skip
         else:
             self._prepare_reference(n)
-        if self._fused_tp is not None:
-            self._fused_tp.begin_forward()
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
+        if self._fused_tp is not None:
+            # after the NCCL all-reduce of the vocab-parallel embedding: that collective has already lined the ranks
+            # up, so the bounded barrier only ever waits for launch jitter
+            self._fused_tp.begin_forward()
         normed, res = ops.rmsnorm(x, w.layers[0]["ln1"], cfg.norm_epsilon, None)
         for li, L in enumerate(w.layers):
             qkv = self._qkv(L, normed, pos, slots, li)

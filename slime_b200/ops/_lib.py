@@ -31,7 +31,7 @@ _SIGS = {
     "sb_symm_barrier": [P, I, I, ctypes.c_uint, I, P, P],
     "sb_symm_barrier_dev": [P, I, I, P, I, P, P],
     "sb_tp_ar_add_rmsnorm": [P, P, P, P, P, P, P, I, I, F, I, I, I, P, P],
-    "sb_dp_reduce_shard": [P, I, I, I, L, L, P, P, P, P],
+    "sb_dp_reduce_shard": [P, I, I, I, L, L, P, P, P, P, P],
     "sb_dp_adam_bcast": [P, P, P, P, P, I, I, I, L, L, F, F, F, F, F, F, F, F, F, P, I, P],
     "sb_group_fp8_quant_1x128": [P, P, P, P, I, I, L, L, I, P],
     "sb_moe_topk": [P, P, P, P, L, I, I, I, I, F, P],
@@ -151,13 +151,37 @@ def status_word(device) -> torch.Tensor:
     return t
 
 
+STATUS_NAMES = {1: "ERR_WAIT_FULL", 2: "ERR_WAIT_EMPTY", 3: "ERR_WAIT_TMEM_FULL", 4: "ERR_WAIT_TMEM_EMPTY",
+                5: "ERR_WAIT_PEER", 6: "ERR_BOUNDS"}  # fmt: skip
+
+
+class KernelWaitExpired(RuntimeError):
+    """A bounded wait inside a kernel gave up. ``code`` is the low byte of the status word, ``where`` the rest
+    (CTA or peer index). The results of the launches since the last check are not to be used."""
+
+    def __init__(self, code: int, where: int):
+        super().__init__(f"kernel wait limit expired: {STATUS_NAMES.get(code, code)} (code={code}, where={where})")
+        self.code, self.where = code, where
+
+
 def check_status(device) -> None:
-    """Host-side check of the bounded-wait status word (synchronises)."""
+    """Host-side check of the bounded-wait status word (synchronises). Clears the word before raising, so the
+    kernels run normally again afterwards."""
     t = status_word(device)
     code = int(t.item())
     if code != 0:
         t.zero_()
-        raise RuntimeError(f"kernel wait limit expired: code={code & 0xff} cta={code >> 8}")
+        raise KernelWaitExpired(code & 0xFF, code >> 8)
+
+
+def set_peer_wait_limit(seconds: float | None) -> float:
+    """Limit of every wait on another GPU (signal-pad barriers, per-CTA peer flags); ``None`` restores the default.
+    Returns the previous limit in seconds."""
+    get = bind("sb_get_peer_wait_limit_ns", [], ctypes.c_ulonglong)
+    st = bind("sb_set_peer_wait_limit_ns", [ctypes.c_ulonglong], None)
+    old = get() / 1e9
+    st(0 if seconds is None else max(1, int(seconds * 1e9)))
+    return old
 
 
 _sm_count = {}

@@ -73,6 +73,7 @@ class FusedDataParallel:
         # barrier words sit at the top of the signal pad, away from the slots torch's own primitives use
         self.base_word = self.g.pad_words - 16
         self._pads = (ctypes.c_void_p * self.world)(*self.g.pad_ptrs)
+        self._align = torch.zeros(1, dtype=torch.float32, device=buffer.grad_data.device)
         logger.info("fused data-parallel step: %d ranks, %s", self.world, "NVSwitch multimem" if self.use_mc else "P2P loads/stores")
 
     def barrier(self):
@@ -86,9 +87,15 @@ class FusedDataParallel:
         """grad shard <- sum over ranks (in place in this rank's buffer); ctl[0] += squared norm of the shard."""
         lib, P = self._lib.lib(), self._lib.ptr
         s, e = self.b.shard_range()
+        # Ranks reach the optimizer step with whatever skew their rollouts and micro-batch counts left (seconds, with
+        # long-tail generations). A one-element NCCL all-reduce absorbs that skew on the device with NCCL's own,
+        # unbounded-by-us wait, so the bounded barrier below only ever waits for launch jitter and its limit stays a
+        # fault detector instead of a limit on skew.
+        dist.all_reduce(self._align, group=self.b.group)
         self.barrier()  # every rank's backward has finished writing its gradient buffer
         rc = lib.sb_dp_reduce_shard(self.g.c_ptrs(self.use_mc), self.world, self.rank, int(self.use_mc), s, e - s,
-                                    P(self.b.grad_shard()), P(self.partials), P(ctl), self._lib.stream())  # fmt: skip
+                                    P(self.b.grad_shard()), P(self.partials), P(ctl),
+                                    P(self._lib.status_word(self.b.grad_data.device)), self._lib.stream())  # fmt: skip
         self._lib.check(rc, "sb_dp_reduce_shard")
 
     def adam_bcast(self, st: dict, *, lr, b1, b2, eps, wd, bc1, bc2, grad_scale, clip, ctl, stateless):

@@ -102,3 +102,42 @@ def test_sum_of_sample_mean_matches_per_sample_loop(kernels):
     assert torch.allclose(got2, expect2, atol=1e-5)
     per_tok = get_sum_of_sample_mean(total, resp, masks, calculate_per_token_loss=True)(x.detach())
     assert torch.allclose(per_tok, sum((p * m).sum() for p, m in zip(x.detach().split(resp), masks)), atol=1e-5)
+
+
+def test_peer_wait_expiry_sets_status_and_context_survives(kernels):
+    """A barrier whose second participant never arrives: the wait runs out (5 ms limit), the kernel returns with
+    ERR_WAIT_PEER in the status word, the host check raises, later barriers return at once while the word is set, and
+    an ordinary launch afterwards still works."""
+    import ctypes
+    import time
+
+    from slime_b200 import ops
+    from slime_b200.ops import _lib
+
+    lib = _lib.lib()
+    pad = torch.zeros(64, dtype=torch.int32, device="cuda")  # stands in for both ranks' signal pads; nobody signals word 1
+    pads = (ctypes.c_void_p * 2)(pad.data_ptr(), pad.data_ptr() + 128)
+    status = _lib.status_word("cuda")
+    status.zero_()
+    old = _lib.set_peer_wait_limit(0.005)
+    try:
+        t0 = time.perf_counter()
+        _lib.check(lib.sb_symm_barrier(pads, 0, 2, 1, 0, _lib.ptr(status), _lib.stream()), "sb_symm_barrier")
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0
+        assert int(status.item()) & 0xFF == 5
+        # sticky word: a second barrier announces itself and returns without waiting
+        _lib.check(lib.sb_symm_barrier(pads, 0, 2, 2, 0, _lib.ptr(status), _lib.stream()), "sb_symm_barrier")
+        torch.cuda.synchronize()
+        with pytest.raises(_lib.KernelWaitExpired) as ei:
+            _lib.check_status("cuda")
+        assert ei.value.code == 5
+    finally:
+        _lib.set_peer_wait_limit(old)
+    assert int(status.item()) == 0
+    a = torch.randn(256, 128, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(128, 128, device="cuda", dtype=torch.bfloat16)
+    out = ops.gemm(a, b)
+    torch.cuda.synchronize()
+    _lib.check_status("cuda")
+    assert _rel(out, a.float() @ b.float().t()) < 2e-2

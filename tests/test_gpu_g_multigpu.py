@@ -11,11 +11,21 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
 def _torchrun(script, nproc, extra_env=None, timeout=420):
+    """One torchrun job with a rendezvous port of its own (jobs run back to back; a port shared between them can
+    still be held by the previous job's store when the next one starts)."""
     env = dict(os.environ, **(extra_env or {}))
     env.setdefault("MASTER_ADDR", "127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
-           "--master-port", str(29600 + nproc), os.path.join(ROOT, script)]  # fmt: skip
+           "--master-port", str(_free_port()), os.path.join(ROOT, script)]  # fmt: skip
     return subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
 
 
@@ -40,11 +50,9 @@ def test_fused_tp_allreduce_norm_matches_nccl(kernels, multimem):
     assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
-@pytest.mark.skipif(os.environ.get("SLIME_B200_TEST_TP_ENGINE") != "1",
-                    reason="opt-in: run directly with torchrun (tests/multigpu/engine_tp_check.py); the gloo variant runs in the CPU suite")
 def test_tensor_parallel_engine_matches_single_gpu(kernels):
     _need(2)
-    r = _torchrun("tests/multigpu/engine_tp_check.py", 2, timeout=180)
+    r = _torchrun("tests/multigpu/engine_tp_check.py", 2, timeout=300)
     assert r.returncode == 0 and "RESULT ok" in r.stdout and "fused_tp=True" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 

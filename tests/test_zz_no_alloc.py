@@ -110,3 +110,18 @@ def test_static_rejects_sizes_beyond_the_scratch(clib, H):
     msg = clib.sb_last_error().decode()
     assert "sb_rmsnorm_bwd_static" in msg and str(MAX_H) in msg
     torch.cuda.synchronize()
+
+
+def test_static_rejects_misaligned_pointers(clib):
+    """A base pointer off the 16-byte boundary the kernels load from is refused on the host; nothing is launched."""
+    T, H = 16, 64
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    dy, h, w, rstd, _ = _inputs(T, H, 3, False)
+    dh, dw = torch.empty_like(dy), torch.empty(H, device="cuda")
+    odd = torch.empty(T * H + 8, device="cuda", dtype=torch.bfloat16)[1:]  # starts 2 bytes past an aligned address
+    for args in [(odd, h, w, rstd, None, dh, dw), (dy, h, w, rstd, None, odd, dw), (dy, h, w, rstd, odd, dh, dw)]:
+        rc = clib.sb_rmsnorm_bwd_static(*[_ptr(a) for a in args], T, H, 0, stream)
+        assert rc == 1
+        assert "misaligned" in clib.sb_last_error().decode()
+    assert clib.sb_rmsnorm_bwd_static(_ptr(dy), _ptr(h), _ptr(w), _ptr(rstd), None, _ptr(dh), _ptr(dw), T, H, 0, stream) == 0
+    torch.cuda.synchronize()
