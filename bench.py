@@ -3,12 +3,21 @@
     python bench.py --gpus N --steps K --warmup W            # this framework
     python bench.py --impl reference --gpus N ...            # the unmodified reference (if runnable)
 
-Workload (Qwen2.5-0.5B architecture, random init, bf16, synthetic data): per GPU and per step
-32 prompts of 256 random token ids, 8 samples each at temperature 1.0 with ``ignore_eos`` and a
-response length drawn uniformly from [128, 1024]; reward = fraction of response tokens whose id is
-divisible by 7; GRPO group-normalised advantages, clipped policy loss (eps 0.2 / 0.28), one optimizer
-step per rollout, then the trainer's weights are synced into the rollout engine. Data parallel only;
-weak scaling (per-GPU work is fixed as N grows).
+Workloads (random init, bf16, synthetic data; weak scaling: per-GPU work is fixed as N grows):
+
+``--config qwen2.5-0.5b`` (default): Qwen2.5-0.5B architecture, data parallel only. Per GPU and per step 32 prompts of
+256 random token ids, 8 samples each at temperature 1.0 with ``ignore_eos`` and a response length drawn uniformly
+from [128, 1024].
+
+``--config qwen3-4b``: Qwen3-4B architecture (36 layers, hidden 2560, 32 Q / 8 KV heads of 128, QK-norm, FFN 9728),
+trainer TP2 + sequence parallel x DP N/2, one TP2 rollout engine per GPU pair (TP1 on a single GPU), 8 prompts of
+512 ids per GPU x 8 samples, response length uniform in [1024, 8192]: 64 prompts x 8 samples on 8 GPUs. A step of
+this config takes about a minute per GPU (the decode phase alone streams ~140 TB of KV cache per GPU), so it is
+not the default: give it a small ``--steps``.
+
+Both: reward = fraction of response tokens whose id is divisible by 7; GRPO group-normalised advantages, clipped
+policy loss (eps 0.2 / 0.28), one optimizer step per rollout, then the trainer's weights are synced into the
+rollout engine (``perf/update_weights_time`` in the output).
 
 ``value`` = tokens (prompt + response of every sample) per second over the whole job, from CUDA-event
 time around exactly K steps (max over ranks). ``e2e`` = the same metric from a separate wall-clock
@@ -40,16 +49,32 @@ def parse():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    p.add_argument("--model", type=str, default="qwen2.5-0.5b")
-    p.add_argument("--prompts-per-gpu", type=int, default=32)
+    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference", "library"])
+    p.add_argument("--config", type=str, default="qwen2.5-0.5b", choices=sorted(CONFIGS))
+    p.add_argument("--model", type=str, default=None)
+    p.add_argument("--prompts-per-gpu", type=int, default=None)
     p.add_argument("--n-samples", type=int, default=8)
-    p.add_argument("--prompt-len", type=int, default=256)
-    p.add_argument("--min-response", type=int, default=128)
-    p.add_argument("--max-response", type=int, default=1024)
-    p.add_argument("--max-tokens-per-gpu", type=int, default=16384)
+    p.add_argument("--prompt-len", type=int, default=None)
+    p.add_argument("--min-response", type=int, default=None)
+    p.add_argument("--max-response", type=int, default=None)
+    p.add_argument("--max-tokens-per-gpu", type=int, default=None)
+    p.add_argument("--tp", type=int, default=None, help="tensor-parallel size of trainer and engines (config default)")
+    p.add_argument("--recompute", type=str, default=None, choices=["full", "none"])
+    p.add_argument("--e2e-steps", type=int, default=None, help="steps of the end-to-end arm (default: --steps)")
     p.add_argument("--no-e2e", action="store_true")
-    return p.parse_args()
+    a = p.parse_args()
+    for k, v in CONFIGS[a.config].items():
+        if getattr(a, k, None) is None:
+            setattr(a, k, v)
+    return a
+
+
+CONFIGS = {
+    "qwen2.5-0.5b": dict(model="qwen2.5-0.5b", prompts_per_gpu=32, prompt_len=256, min_response=128, max_response=1024,
+                         max_tokens_per_gpu=16384, tp=1, recompute="none", mem_fraction=0.45),
+    "qwen3-4b": dict(model="qwen3-4b", prompts_per_gpu=8, prompt_len=512, min_response=1024, max_response=8192,
+                     max_tokens_per_gpu=9216, tp=2, recompute="full", mem_fraction=0.8),
+}  # fmt: skip
 
 
 def reference_arm(a):
@@ -73,12 +98,13 @@ def reference_arm(a):
 
 class ClockSampler:
     def __init__(self, gpu_index: int):
-        self.proc, self.path = None, os.path.join(ROOT, "gpurun_out", f"bench_clocks_{os.getpid()}.csv")
+        import tempfile
+
+        self.proc, self.path = None, os.path.join(tempfile.gettempdir(), f"slime_b200_bench_clocks_{os.getpid()}.csv")
         self.gpu = gpu_index
 
     def start(self):
         try:
-            os.makedirs(os.path.dirname(self.path), exist_ok=True)
             self.f = open(self.path, "w")
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={_SMI_FIELDS}", "--format=csv,noheader,nounits",
                                           "-lms", "200", "-i", str(self.gpu)], stdout=self.f, stderr=subprocess.DEVNULL)  # fmt: skip
@@ -112,7 +138,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}  # fmt: skip
 
 
-def build_args(a, world):
+def build_args(a, world, tp):
     from slime_b200.models.config import apply_to_args, get_preset
     from slime_b200.utils.arguments import namespace_from_dict
 
@@ -122,11 +148,16 @@ def build_args(a, world):
         use_dynamic_batch_size=True, max_tokens_per_gpu=a.max_tokens_per_gpu, lr=1e-6, weight_decay=0.1, adam_beta2=0.98,
         eps_clip=0.2, eps_clip_high=0.28, advantage_estimator="grpo", rollout_temperature=1.0, rollout_ignore_eos=True,
         rollout_max_context_len=a.prompt_len + a.max_response + 16, custom_rm_path="slime_b200.rollout.synthetic.mod7_reward",
-        actor_num_nodes=1, actor_num_gpus_per_node=world, rollout_num_gpus=world, sglang_mem_fraction_static=0.45,
-        sglang_max_running_requests=a.prompts_per_gpu * a.n_samples, rollout_seed=42, seed=1234,
+        actor_num_nodes=1, actor_num_gpus_per_node=world, rollout_num_gpus=world, rollout_num_gpus_per_engine=tp,
+        sglang_mem_fraction_static=a.mem_fraction, sglang_max_running_requests=a.prompts_per_gpu * a.n_samples * tp,
+        rollout_seed=42, seed=1234, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
+        recompute_granularity="full" if a.recompute == "full" else None,
     ))  # fmt: skip
     apply_to_args(get_preset(a.model), ns)
     ns.kv_channels = ns.kv_channels or ns.hidden_size // ns.num_attention_heads
+    if tp > 1:  # vocab-parallel embedding / LM head
+        mult = 128 * tp
+        ns.padded_vocab_size = -(-ns.vocab_size // mult) * mult
     return ns
 
 
@@ -134,6 +165,8 @@ def main():
     a = parse()
     if a.impl == "reference":
         return reference_arm(a)
+    if a.impl == "library":
+        os.environ["SLIME_B200_LIBRARY_OPS"] = "1"  # read by slime_b200.ops at import: see ops.library_mode()
 
     import torch
     import torch.distributed as dist
@@ -150,13 +183,17 @@ def main():
     from slime_b200.ops import _lib
     from slime_b200.parallel import state as mpu
 
-    mpu.initialize_model_parallel()
-    args = build_args(a, world)
+    tp = min(a.tp, world)
+    assert world % tp == 0, f"{world} GPUs do not split into tensor-parallel groups of {tp}"
+    mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
+    args = build_args(a, world, tp)
     runner = ColocatedGRPO(args)
-    gen = torch.Generator().manual_seed(1000 + rank)
-    G, n = a.prompts_per_gpu, a.n_samples
+    # one data stream per data-parallel rank: the ranks of a tensor-parallel group see the same prompts
+    gen = torch.Generator().manual_seed(1000 + mpu.get_data_parallel_rank())
+    G, n = a.prompts_per_gpu * tp, a.n_samples
     # inputs staged in pinned host memory, one fresh batch per step (> L2: the step touches ~GBs of weights/KV)
-    total_steps = a.warmup + a.steps * (1 if a.no_e2e else 2)
+    e2e_steps = 0 if a.no_e2e else (a.e2e_steps or a.steps)
+    total_steps = a.warmup + a.steps + e2e_steps
     prompts_host = torch.randint(0, args.vocab_size, (total_steps, G, a.prompt_len), generator=gen, dtype=torch.int32).pin_memory()
     resp_lens = torch.randint(a.min_response, a.max_response + 1, (total_steps, G * n), generator=gen)
     dev_prompts = torch.empty(G, a.prompt_len, dtype=torch.int32, device="cuda")
@@ -187,7 +224,7 @@ def main():
     tokens, parts = 0, {"rollout_s": 0.0, "train_s": 0.0, "sync_s": 0.0}
     for i in range(a.warmup, a.warmup + a.steps):
         out, _ = one_step(i)
-        tokens += out["tokens"]
+        tokens += out["tokens"] / tp  # every rank of a tensor-parallel group reports the group's tokens
         for k in parts:
             parts[k] += out[k]
     end.record()
@@ -201,9 +238,9 @@ def main():
         sync()
         t0 = time.perf_counter()
         e2e_tokens = 0
-        for i in range(a.warmup + a.steps, a.warmup + 2 * a.steps):
+        for i in range(a.warmup + a.steps, a.warmup + a.steps + e2e_steps):
             out, loss = one_step(i)
-            e2e_tokens += out["tokens"]
+            e2e_tokens += out["tokens"] / tp
         sync()
         e2e_s = time.perf_counter() - t0
         stats = runner.engine.stats
@@ -212,13 +249,15 @@ def main():
                "d2h": stats.get("d2h_bytes", 0) / max(stats["steps"], 1)}  # fmt: skip
 
     t = torch.tensor([ms, float(tokens), e2e["seconds"] if e2e else 0.0, float(e2e["tokens"]) if e2e else 0.0,
-                      float(launches)], dtype=torch.float64, device="cuda")  # fmt: skip
+                      float(launches), parts["rollout_s"], parts["train_s"], parts["sync_s"]], dtype=torch.float64, device="cuda")  # fmt: skip
+    phase_max = {k: v / a.steps for k, v in parts.items()}
     if world > 1:
         mx = t.clone()
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = t.clone()
         dist.all_reduce(sm, op=dist.ReduceOp.SUM)
         ms, tokens, launches = float(mx[0]), float(sm[1]), float(sm[4])
+        phase_max = {"rollout_s": float(mx[5]) / a.steps, "train_s": float(mx[6]) / a.steps, "sync_s": float(mx[7]) / a.steps}
         if e2e:
             e2e["seconds"], e2e["tokens"] = float(mx[2]), float(sm[3])
     if rank == 0:
@@ -227,15 +266,20 @@ def main():
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-            "data": "synthetic (random prompt ids, random-init weights)", "impl": "ours",
-            "config": {"model": a.model, "global_batch": G * n * world, "seq_len": f"{a.prompt_len}+U[{a.min_response},{a.max_response}]",
-                       "parallelism": f"dp{world}", "prompts_per_gpu": G, "n_samples_per_prompt": n, "colocated": True,
+            "data": "synthetic (random prompt ids, random-init weights)", "impl": a.impl,
+            "config": {"model": a.model, "layers": args.num_layers, "hidden": args.hidden_size,
+                       "global_batch": a.prompts_per_gpu * n * world, "seq_len": f"{a.prompt_len}+U[{a.min_response},{a.max_response}]",
+                       "parallelism": (f"tp{tp}xdp{world // tp}" if tp > 1 else f"dp{world}"),
+                       "rollout": f"{world // tp} engine(s) x tp{tp}", "prompts_per_gpu": a.prompts_per_gpu,
+                       "n_samples_per_prompt": n, "colocated": True, "recompute": a.recompute,
                        "l2": "inputs larger than L2 (fresh prompts each step; weights+KV+activations >> 126 MB)",
-                       "phase_seconds_rank0": {k: v / a.steps for k, v in parts.items()}},
+                       "phase_seconds_rank0": {k: v / a.steps for k, v in parts.items()},
+                       "phase_seconds_max_over_ranks": phase_max,
+                       "perf/update_weights_time": phase_max["sync_s"]},
             "clocks": clocks, "gpu_launches": int(launches),
         }  # fmt: skip
         if e2e:
-            line["e2e"] = {"value": e2e["tokens"] / e2e["seconds"], "unit": "tokens/s",
+            line["e2e"] = {"value": e2e["tokens"] / e2e["seconds"], "unit": "tokens/s", "steps": e2e_steps,
                            "h2d_bytes_per_step": int(runner_h2d_bytes(runner, a, G, n)),
                            "d2h_bytes_per_step": int(runner_d2h_bytes(runner, a, G, n))}  # fmt: skip
         print(json.dumps(line), flush=True)

@@ -45,7 +45,13 @@ class ColocatedGRPO:
             random_seed=args.rollout_seed + mpu.get_data_parallel_rank(),
             disable_cuda_graph=bool(getattr(args, "sglang_disable_cuda_graph", False)),
         )
-        self.engine = Engine(cfg, sa, device=self.device, num_pages=engine_pages)
+        # One engine per tensor-parallel group of the trainer, sharded the same way: rank r of the group holds shard r
+        # of both the trainer's and the engine's weights, so weight sync is a device-local copy and the ranks of a
+        # group step the engine in lockstep (same requests, same seeds, same tokens).
+        tps = mpu.get_tensor_model_parallel_world_size()
+        self.engine = Engine(cfg, sa, device=self.device, num_pages=engine_pages,
+                             tp_group=mpu.get_tensor_model_parallel_group() if tps > 1 else None, tp_size=tps,
+                             tp_rank=mpu.get_tensor_model_parallel_rank())  # fmt: skip
         self.actor.connect_rollout_engines([self.engine])
         self.actor.update_weights()
         self.rollout_id = 0

@@ -98,7 +98,7 @@ class TrainModel:
         dp = mpu.get_data_parallel_world_size(with_context_parallel=True)
         # Peer-memory optimizer step: needs buffers that stay mapped, so not with a trainer that releases its memory
         # between phases, and not with optimizer state on the host.
-        symmetric = (symmetric_memory_usable(dp, self.device) and dp == dist.get_world_size()
+        symmetric = (symmetric_memory_usable(dp, self.device) and mpu.get_pipeline_model_parallel_world_size() == 1
                      and not getattr(self.args, "offload_train", False) and not getattr(self.args, "optimizer_cpu_offload", False)
                      and getattr(self.args, "fused_dp_step", True))  # fmt: skip
         self.dense_buffer = FlatBuffer(dense, dense_names, mpu.get_data_parallel_group(with_context_parallel=True), dp,

@@ -112,6 +112,7 @@ class GroupedExperts(nn.Module):
             w1 = tp.set_tp_attrs(_param((2 * f, cfg.hidden_size), dtype, device, cfg.init_method_std, gen), etp > 1, 0, 2, "column")
             w2 = tp.set_tp_attrs(_param((cfg.hidden_size, f), dtype, device, out_std, gen), etp > 1, 1, 1, "row")
             w1.is_expert = w2.is_expert = True
+            w1.num_local_experts = w2.num_local_experts = num_local  # global expert id = ep_rank * num_local + e
             self.linear_fc1.register_parameter(f"weight{e}", w1)
             self.linear_fc2.register_parameter(f"weight{e}", w2)
         self.int4_qat_group = 0  # >0: fake-INT4 the expert weights in forward (straight-through backward)

@@ -3,8 +3,15 @@
 Activations travel as one ``[2, T, H]`` tensor (branch output + residual stream). Every stage
 builds the micro-batch locally from the same rollout payload, so tensor shapes are known
 without a shape exchange even though sequence lengths vary per micro-batch. Send/recv pairs
-are issued with ``batch_isend_irecv`` on the pipeline group; interleaved (virtual) stages run
-their chunks back to back on the same rank.
+are issued with ``batch_isend_irecv`` on the pipeline group.
+
+Two schedules:
+  * one chunk per rank: non-interleaved 1F1B (warm-up forwards, steady 1F1B pairs, cool-down backwards);
+  * ``vpp`` chunks per rank (virtual pipeline): chunk ``v`` of rank ``r`` is virtual stage ``v * pp + r``, so an
+    activation visits every rank once per chunk and wraps from the last rank back to the first. Micro-batches are
+    processed in groups of ``pp``: all forwards of a group in (chunk, micro-batch) order, then all backwards with the
+    chunks reversed. Every rank walks the same order, sends never block and receives are posted in the order the
+    peer sends, so the dependencies form a DAG ordered by (chunk, micro-batch, rank).
 Replaces Megatron's ``get_forward_backward_func`` (slime/backends/megatron_utils/model.py:460,647).
 """
 
@@ -51,8 +58,57 @@ def _get_batch(model, data_iterator, args):
     return get_batch(data_iterator, keys, getattr(args, "data_pad_size_multiplier", 128), device=model.device)
 
 
+def _run_interleaved(model, data_iterator, num_microbatches: int, forward_step, args, forward_only: bool) -> list[dict]:
+    """Virtual-pipeline schedule (see the module docstring). Returns the last virtual stage's per-micro-batch results."""
+    pp, rank = mpu.get_pipeline_model_parallel_world_size(), mpu.get_pipeline_model_parallel_rank()
+    vpp = len(model.chunks)
+    group = mpu.get_pipeline_model_parallel_group()
+    prev_r, next_r = mpu.get_pipeline_model_parallel_prev_rank(), mpu.get_pipeline_model_parallel_next_rank()
+    dtype = model.chunks[0].dtype
+    results: list[dict] = []
+    sends = []
+    for g0 in range(0, num_microbatches, pp):
+        ms = list(range(g0, min(g0 + pp, num_microbatches)))
+        batches = {m: _get_batch(model, data_iterator, args) for m in ms}
+        saved = {}
+        for v in range(vpp):
+            for m in ms:
+                first_v, last_v = rank == 0 and v == 0, rank == pp - 1 and v == vpp - 1
+                inp = None
+                if not first_v:
+                    inp = torch.empty(_shape_for(batches[m], model, args), dtype=dtype, device=model.device)
+                    dist.recv(inp, src=prev_r, group=group)
+                    inp.requires_grad_(not forward_only)
+                out, res = forward_step(batches[m], model.chunks[v], inp)
+                if last_v:
+                    results.append(res)
+                else:
+                    sends.append(dist.isend(out.detach().contiguous(), next_r, group=group))
+                if not forward_only:
+                    saved[(m, v)] = (inp, out)
+        if not forward_only:
+            for v in reversed(range(vpp)):
+                for m in ms:
+                    first_v, last_v = rank == 0 and v == 0, rank == pp - 1 and v == vpp - 1
+                    inp, out = saved.pop((m, v))
+                    if last_v:
+                        out.backward()
+                    else:
+                        g = torch.empty_like(out)
+                        dist.recv(g, src=next_r, group=group)
+                        torch.autograd.backward(out, grad_tensors=g)
+                    if not first_v:
+                        sends.append(dist.isend(inp.grad.contiguous(), prev_r, group=group))
+        for w in sends:
+            w.wait()
+        sends = []
+    return results
+
+
 def run_forward_only(model, data_iterator, num_microbatches: int, forward_step, args) -> list[dict]:
     pp = mpu.get_pipeline_model_parallel_world_size()
+    if pp > 1 and len(model.chunks) > 1:
+        return _run_interleaved(model, data_iterator, num_microbatches, forward_step, args, forward_only=True)
     first, last = mpu.is_pipeline_first_stage(), mpu.is_pipeline_last_stage()
     results = []
     dtype = model.chunks[0].dtype
@@ -61,7 +117,7 @@ def run_forward_only(model, data_iterator, num_microbatches: int, forward_step, 
         x = None
         if pp > 1 and not first:
             x, _ = _p2p(recv_prev_shape=_shape_for(batch, model, args), dtype=dtype, device=model.device)
-        for chunk in model.chunks:  # virtual chunks hosted on this rank run back to back
+        for chunk in model.chunks:  # pp == 1: the chunks of the one rank are consecutive layers
             x, res = forward_step(batch, chunk, x)
         if pp > 1 and not last:
             _p2p(send_next=x)
@@ -99,6 +155,8 @@ def run_forward_backward(model, data_iterator, num_microbatches: int, forward_st
             batch = _get_batch(model, data_iterator, args)
             bwd(fwd(batch, None), None, None)
         return logs
+    if len(model.chunks) > 1:
+        return _run_interleaved(model, data_iterator, num_microbatches, forward_step, args, forward_only=False)
 
     warmup = min(pp - rank - 1, num_microbatches)
     steady = num_microbatches - warmup
@@ -118,10 +176,12 @@ def run_forward_backward(model, data_iterator, num_microbatches: int, forward_st
         if not first:
             inp, _ = _p2p(recv_prev_shape=shape, dtype=dtype, device=model.device)
         out = fwd(batch, inp)
+        pending.append((inp, out, shape))
         grad_out = None
         if not last:
-            _, grad_out = _p2p(send_next=out.detach(), recv_next_shape=shape, dtype=dtype, device=model.device)
-        pending.append((inp, out, shape))
+            # the gradient that comes back now is that of the oldest forward still pending, whose token count (dynamic
+            # batching) generally differs from the micro-batch just sent
+            _, grad_out = _p2p(send_next=out.detach(), recv_next_shape=pending[0][2], dtype=dtype, device=model.device)
         b_inp, b_out, _ = pending.pop(0)
         g = bwd(b_out, b_inp, grad_out)
         if not first:

@@ -45,7 +45,9 @@ def post_process_rewards(args, samples: list[Sample]):
     if args.advantage_estimator in GROUP_NORM_ESTIMATORS and args.rewards_normalization:
         r = torch.tensor(raw, dtype=torch.float)
         n = args.n_samples_per_prompt
-        r = r.reshape(-1, n) if r.numel() == n * args.rollout_batch_size else r.view(-1, r.shape[-1])
+        # groups are consecutive blocks of n samples; a rank that generated only its own slice of the rollout batch
+        # still has whole groups (a ragged tail, e.g. after dynamic filtering, is normalised as one group)
+        r = r.reshape(-1, n) if r.numel() % n == 0 else r.view(1, -1)
         r = r - r.mean(dim=-1, keepdim=True)
         if args.advantage_estimator in STD_NORM_ESTIMATORS and args.grpo_std_normalization:
             r = r / (r.std(dim=-1, keepdim=True) + 1e-6)

@@ -147,35 +147,51 @@ class UpdateWeightFromTensor(WeightUpdaterBase):
         e = self.engines[0]
         return (
             getattr(e, "weights", None) is not None and e.weights.tp == mpu.get_tensor_model_parallel_world_size()
+            and e.weights.rank == mpu.get_tensor_model_parallel_rank()
             and mpu.get_pipeline_model_parallel_world_size() == 1 and self.model.cfg.num_experts is None
+            and self._fused_pairs(e) is not None
         )  # fmt: skip
+
+    # trainer parameter (name inside a layer) -> engine buffer of the same shard shape
+    _LAYER_MAP = {
+        "self_attention.linear_qkv.weight": "qkv", "self_attention.linear_qkv.bias": "qkv_bias",
+        "self_attention.linear_qkv.layer_norm_weight": "ln1", "self_attention.q_layernorm.weight": "q_norm",
+        "self_attention.k_layernorm.weight": "k_norm", "self_attention.linear_proj.weight": "o",
+        "mlp.linear_fc1.weight": "gate_up", "mlp.linear_fc1.layer_norm_weight": "ln2", "mlp.linear_fc2.weight": "down",
+    }  # fmt: skip
+
+    def _fused_pairs(self, e):
+        """(trainer shard, engine buffer) for every parameter, or None when a name has no same-shape counterpart."""
+        w, pairs = e.weights, []
+        for name, p in self.model.named_parameters():
+            if name == "embedding.word_embeddings.weight":
+                dst = w.embed
+            elif name == "output_layer.weight":
+                if self.model.cfg.tie_word_embeddings:
+                    continue
+                dst = w.lm_head
+            elif name == "decoder.final_layernorm.weight":
+                dst = w.final_norm
+            else:
+                _, _, i, sub = name.split(".", 3)
+                key = self._LAYER_MAP.get(sub)
+                dst = w.layers[int(i)].get(key) if key else None
+            if dst is None or dst.shape != p.shape:
+                return None
+            pairs.append((p.data, dst))
+        return pairs
 
     @torch.no_grad()
     def _copy_fused(self):
-        """Same sharding on both sides: one device copy per fused tensor, no gather / split / rename."""
-        fused = {
-            "self_attention.linear_qkv.weight": "self_attn.qkv_proj.weight",
-            "self_attention.linear_qkv.bias": "self_attn.qkv_proj.bias",
-            "mlp.linear_fc1.weight": "mlp.gate_up_proj.weight",
-        }
+        """Same sharding on both sides (rank r of the tensor-parallel group holds shard r of the trainer's and of the
+        engine's weights, in the same fused layouts): the sync is a device-local copy of every shard, with no gather,
+        split or rename. On CUDA all tensors go in one launch of the multi-tensor copy kernel."""
+        from slime_b200.weight_sync import device_sync
+
         for e in self.engines:
-            w = e.weights
-            for name, p in self.model.named_parameters():
-                if name == "embedding.word_embeddings.weight":
-                    w.embed.copy_(p)
-                elif name == "output_layer.weight":
-                    if not self.model.cfg.tie_word_embeddings:
-                        w.lm_head.copy_(p)
-                elif name == "decoder.final_layernorm.weight":
-                    w.final_norm.copy_(p)
-                else:
-                    _, _, i, sub = name.split(".", 3)
-                    if sub in fused:
-                        ok = w.load_weight(f"model.layers.{i}.{fused[sub]}", p.data)
-                    else:
-                        pairs = convert.convert_to_hf(self.model.cfg, name, p.data)
-                        ok = all(w.load_weight(n, t) for n, t in pairs)
-                    assert ok, f"engine rejected {name}"
+            pairs = self._fused_pairs(e)
+            assert pairs is not None, "engine and trainer shards differ in shape"
+            device_sync.copy_tensors(pairs)
 
 
 class UpdateWeightFromDistributed(WeightUpdaterBase):

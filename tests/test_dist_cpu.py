@@ -16,3 +16,15 @@ def test_invariants(mode, world, port):
                         "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests/multigpu/dist_cpu_check.py")],
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)  # fmt: skip
     assert r.returncode == 0 and f"RESULT ok mode={mode} world={world}" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("mode,world,port", [("tp", 2, 29691), ("tp_sp", 2, 29692), ("pp", 2, 29693), ("pp_vpp", 2, 29694),
+                                             ("ep", 2, 29695), ("dp", 2, 29696), ("tp_dp", 4, 29697)])
+def test_model_under_parallel_layout_matches_single_rank_oracle(mode, world, port):
+    """4-layer trainer model (qk-norm, GQA, dense or MoE) under each layout: loss, gradient shards and gradient norm
+    equal a plain-PyTorch single-rank transformer."""
+    env = dict(os.environ, MODE=mode, DEVICE="cpu", MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests/multigpu/model_parallel_check.py")],
+                       env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)  # fmt: skip
+    assert r.returncode == 0 and f"RESULT ok mode={mode} world={world}" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
