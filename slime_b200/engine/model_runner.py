@@ -450,10 +450,9 @@ class ModelRunner:
 def _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, scale):
     """Attention of new tokens over (cached + new) context, causal aligned to the sequence end."""
     if q.is_cuda:
-        from flash_attn import flash_attn_varlen_func
+        from slime_b200.ops import attention
 
-        return flash_attn_varlen_func(q, k_all, v_all, cu_q.to(torch.int32), cu_k.to(torch.int32), max_q, max_k,
-                                      softmax_scale=scale, causal=True)  # fmt: skip
+        return attention.extend_attention(q, k_all, v_all, cu_q, cu_k, scale)
     out = torch.empty_like(q)
     cq, ck = cu_q.tolist(), cu_k.tolist()
     Hq, Hkv = q.shape[1], k_all.shape[1]

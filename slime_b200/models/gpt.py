@@ -91,10 +91,13 @@ class SelfAttention(nn.Module):
         normed, residual = ops.rmsnorm(x, self.linear_qkv.layer_norm_weight, cfg.norm_epsilon, residual)
         inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
         qkv = ops.linear(inp, self.linear_qkv.weight, self.linear_qkv.bias)
+        cp = mpu.get_context_parallel_world_size()
         ctx = ops.rope_attention(
             qkv, packed.position_ids, rope_table, packed.cu_seqlens, packed.max_seqlen, self.hq, self.hkv, self.d,
             self.q_layernorm.weight if self.q_layernorm is not None else None,
             self.k_layernorm.weight if self.k_layernorm is not None else None, cfg.norm_epsilon,
+            cp_local_cu_seqlens=getattr(packed, "local_cu_seqlens", None) if cp > 1 else None,
+            cp_group=mpu.get_context_parallel_group() if cp > 1 else None,
         )  # fmt: skip
         out = ops.linear(ctx, self.linear_proj.weight)
         out = tp.reduce_scatter_to_sequence_parallel_region(out) if self.sp else tp.reduce_from_tensor_model_parallel_region(out)

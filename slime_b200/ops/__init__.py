@@ -400,11 +400,12 @@ def embedding(ids, table, vocab_lo: int = 0):
 
 # ------------------------------------------------------------------- attention
 def rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, eps=1e-6,
-                   scale=None):
+                   scale=None, cp_local_cu_seqlens=None, cp_group=None):
     """RoPE (+ per-head q/k RMSNorm) and packed causal attention on a fused qkv row, as one autograd node."""
     from slime_b200.ops import attention
 
-    return attention.rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w, k_norm_w, eps, scale)
+    return attention.rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w, k_norm_w, eps, scale,
+                                    cp_local_cu_seqlens, cp_group)
 
 
 def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True):

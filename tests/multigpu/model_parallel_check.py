@@ -1,6 +1,6 @@
 """Run under torchrun: the trainer model under a parallel layout equals a single-rank plain-PyTorch model.
 
-    MODE=tp | tp_sp | pp | pp_vpp | ep | dp | tp_dp        DEVICE=cpu (gloo, fp32) | cuda (nccl, bf16)
+    MODE=tp | tp_sp | pp | pp_vpp | ep | dp | tp_dp | cp   DEVICE=cpu (gloo, fp32) | cuda (nccl, bf16)
 
 Every rank builds the same full set of weights from one seed (Megatron names, full shapes), keeps the shard its
 coordinates own, and runs forward + backward of a weighted next-token log-likelihood over a few packed micro-batches
@@ -19,10 +19,10 @@ import torch.distributed as dist
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 
-LAYOUTS = {  # mode -> (tp, pp, vpp, ep, sequence_parallel)
+LAYOUTS = {  # mode -> (tp, pp, vpp, ep, sequence_parallel); "cp" is context parallel over the whole world
     "tp": (2, 1, None, 1, False), "tp_sp": (2, 1, None, 1, True), "pp": (1, 2, None, 1, False),
     "pp_vpp": (1, 2, 2, 1, False), "ep": (1, 1, None, 2, False), "dp": (1, 1, None, 1, False),
-    "tp_dp": (2, 1, None, 1, True),
+    "tp_dp": (2, 1, None, 1, True), "cp": (1, 1, None, 1, False),
 }  # fmt: skip
 
 
@@ -133,7 +133,8 @@ def main():
     from slime_b200.weight_sync import convert
 
     tp, pp, vpp, ep, sp = LAYOUTS[mode]
-    mpu.initialize_model_parallel(tp, pp, vpp, 1, ep, 1, **({} if cuda else {"backend": "gloo"}))
+    cp = world if mode == "cp" else 1
+    mpu.initialize_model_parallel(tp, pp, vpp, cp, ep, 1, **({} if cuda else {"backend": "gloo"}))
     moe = mode == "ep"
     cfg = ModelConfig(num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=64,
                       ffn_hidden_size=256, vocab_size=512, rotary_base=1e4, tie_word_embeddings=False, qk_layernorm=True,
@@ -171,6 +172,7 @@ def main():
 
     # ---- data: this DP rank's samples (every model-parallel rank of a DP group builds the same micro-batches)
     dp, dpr = mpu.get_data_parallel_world_size(), mpu.get_data_parallel_rank()
+    dpcp = mpu.get_data_parallel_world_size(with_context_parallel=True)  # the group gradients are reduced over
     g = torch.Generator().manual_seed(100 + dpr)
     lens = [37, 64, 19, 50, 23, 41]
     samples = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in lens]
@@ -189,12 +191,16 @@ def main():
         logits = out[0]
         idx = batch["_sample_ids"]
         loss, off = 0.0, 0
-        for i in idx:
+        cu_local = batch["packed_seq_params"].local_cu_seqlens.tolist()
+        pos_all = batch["position_ids"][0].long()
+        for j, i in enumerate(idx):
             n = lens[i]
-            lp, _ = calculate_log_probs_and_entropy(logits[off : off + n - 1], samples[i][1:].to(dev),
-                                                    mpu.get_tensor_model_parallel_group(), with_entropy=False)  # fmt: skip
-            loss = loss + (lp * wts[i][1:].to(dev)).sum()
-            off += n
+            a, b = cu_local[j], cu_local[j + 1]  # this rank's rows of the sample (all of them without context parallelism)
+            pos = pos_all[a:b]  # their positions in the sample (zig-zag chunks under context parallelism)
+            keep = pos + 1 < n  # the last token, and context-parallel padding, predict nothing
+            tgt = samples[i].to(dev)[(pos + 1).clamp_max(n - 1)]
+            lp, _ = calculate_log_probs_and_entropy(logits[a:b], tgt, mpu.get_tensor_model_parallel_group(), with_entropy=False)
+            loss = loss + (lp * wts[i].to(dev)[(pos + 1).clamp_max(n - 1)] * keep).sum()
         return loss, {"loss": loss.detach()}
 
     # the batch builder does not say which samples it packed: wrap the iterator to remember them
@@ -227,7 +233,7 @@ def main():
     mine = torch.zeros(1, dtype=torch.float64, device=dev)
     if mpu.is_pipeline_last_stage() and logs:
         mine += sum(float(l["loss"]) for l in logs)
-    dist.all_reduce(mine, group=mpu.get_data_parallel_group())
+    dist.all_reduce(mine, group=mpu.get_data_parallel_group(with_context_parallel=True))
     if mpu.is_pipeline_last_stage():
         torch.testing.assert_close(float(mine), float(ref_loss.detach()), rtol=rtol, atol=atol * 10)
 
@@ -244,14 +250,14 @@ def main():
         else:
             want = gfull
         got = p.main_grad.float().cpu()
-        if dp == 1:  # with data parallelism the reduced gradient only exists per flat-buffer shard: checked below
+        if dpcp == 1:  # with data parallelism the reduced gradient only exists per flat-buffer shard: checked below
             err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-6)
             worst = max(worst, err)
             assert err < (5e-2 if cuda else 2e-3), (name, err)
         own_tp = (not getattr(p, "tensor_model_parallel", False)) and tpr != 0 and not getattr(p, "is_expert", False)
         if not own_tp:  # replicated parameters count once
             sq += got.double().pow(2).sum().to(dev)
-    if dp == 1:
+    if dpcp == 1:
         dist.all_reduce(sq)  # tp / pp / ep ranks hold disjoint parameters (replicated ones were counted once)
         ref_sq = sum(float(v.grad.double().pow(2).sum()) for v in Wg.values() if v.grad is not None)
         torch.testing.assert_close(float(sq) ** 0.5, ref_sq**0.5, rtol=rtol, atol=atol)
