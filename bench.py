@@ -278,14 +278,35 @@ def main():
                        "perf/update_weights_time": phase_max["sync_s"]},
             "clocks": clocks, "gpu_launches": int(launches),
         }  # fmt: skip
+        if a.impl == "library":
+            line["library_replaces"] = ("explanatory arm, not the reference framework: GEMMs -> cuBLAS (torch.mm), training / prefill "
+                                        "attention -> flash-attn, RMSNorm / RoPE / SwiGLU / embedding -> eager PyTorch, fused loss -> "
+                                        "logits + PyTorch ops, peer-memory collectives -> NCCL; the engine's decode attention, KV write "
+                                        "and sampling kernels stay")
         if e2e:
             line["e2e"] = {"value": e2e["tokens"] / e2e["seconds"], "unit": "tokens/s", "steps": e2e_steps,
                            "h2d_bytes_per_step": int(runner_h2d_bytes(runner, a, G, n)),
                            "d2h_bytes_per_step": int(runner_d2h_bytes(runner, a, G, n))}  # fmt: skip
         print(json.dumps(line), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        _finish(runner.engine)
     return 0
+
+
+def _finish(engine, grace_s: float = 60.0):
+    """The result line is out. Tear the process groups down in order (graphs that captured NCCL collectives first);
+    should the teardown itself stall, leave after ``grace_s`` instead of holding the GPUs."""
+    import threading
+
+    from slime_b200.utils.distributed_utils import shutdown_distributed
+
+    t = threading.Thread(target=shutdown_distributed, args=([engine],), daemon=True)
+    t.start()
+    t.join(grace_s)
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if t.is_alive():
+        os._exit(0)
 
 
 def runner_h2d_bytes(runner, a, G, n):

@@ -217,6 +217,7 @@ def _can_use_fused_logprob(args, f, model) -> bool:
         and mpu.get_context_parallel_world_size() == 1
         and getattr(args, "rollout_top_p", 1.0) == 1.0
         and getattr(args, "fused_loss", True)
+        and os.environ.get("SLIME_B200_LIBRARY_OPS") != "1"
     )
 
 
@@ -255,7 +256,7 @@ def _fused_policy_eligible(args, model) -> bool:
         and not args.use_opsm and not args.use_kl_loss and not args.get_mismatch_metrics
         and args.custom_tis_function_path is None and getattr(args, "custom_pg_loss_reducer_function_path", None) is None
         and getattr(args, "rollout_top_p", 1.0) == 1.0 and getattr(args, "fused_loss", True)
-        and not getattr(args, "recompute_loss_function", False)
+        and not getattr(args, "recompute_loss_function", False) and os.environ.get("SLIME_B200_LIBRARY_OPS") != "1"
     )  # fmt: skip
 
 

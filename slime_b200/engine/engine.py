@@ -606,6 +606,22 @@ class Engine:
                     self.runner.drop_graphs()
                 self.released.discard(tag)
 
+    def shutdown(self):
+        """Release what must be gone before the process group is destroyed. A tensor-parallel engine captures NCCL
+        collectives (embedding all-reduce, logits all-gather) in its decode graphs; NCCL does not finish destroying a
+        communicator while graphs that recorded its collectives are alive, so ``destroy_process_group`` blocks forever
+        unless the graphs are dropped first."""
+        import gc
+
+        with self.lock:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            self.runner.drop_graphs()
+            self.runner._fused_tp = None
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+
     def update_weights(self, named_tensors, version: str | None = None, flush_cache: bool = True):
         with self.lock:
             missing = self.weights.load_weights(named_tensors, version)

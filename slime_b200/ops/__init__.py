@@ -16,9 +16,44 @@ from slime_b200.ops import _lib, reference
 
 P = _lib.ptr
 
+# Comparison arm (``bench.py --impl library``): GEMMs go to cuBLAS through torch.matmul, training / prefill attention to
+# the flash-attn library, RMSNorm / RoPE / SwiGLU / embedding to eager PyTorch, the fused loss and the peer-memory
+# collectives are switched off by their own modules (NCCL runs instead). Explanatory only: it shows what the kernels of
+# this package buy on the same box; it is not the reference framework.
+LIBRARY_MODE = os.environ.get("SLIME_B200_LIBRARY_OPS") == "1"
+
+
+def _is_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+def library_mode() -> bool:
+    return LIBRARY_MODE
+
 
 def _cuda(t: torch.Tensor) -> bool:
-    return t.is_cuda
+    return t.is_cuda and not LIBRARY_MODE
+
+
+def _library_gemm(a, b, a_mn, b_mn, bias, out, out_dtype, accumulate):
+    A = a.t() if a_mn else a
+    B = b if b_mn else b.t()
+    if out_dtype == torch.float32:
+        try:
+            res = torch.mm(A, B, out_dtype=torch.float32)
+        except TypeError:
+            res = torch.mm(A, B).float()
+    else:
+        res = torch.mm(A, B)
+    if bias is not None:
+        res = res + bias.to(res.dtype)
+    if out is None:
+        return res
+    if accumulate:
+        out.add_(res)
+    else:
+        out.copy_(res)
+    return out
 
 
 # ------------------------------------------------------------------------ GEMM
@@ -53,6 +88,8 @@ def gemm(a, b, *, a_mn=False, b_mn=False, bias=None, out=None, out_dtype=None, a
     N, Kb = (b.shape[1], b.shape[0]) if b_mn else b.shape
     assert K == Kb, f"inner dims differ: {K} vs {Kb}"
     out_dtype = out.dtype if out is not None else (out_dtype or a.dtype)
+    if LIBRARY_MODE and a.is_cuda:
+        return _library_gemm(a, b, a_mn, b_mn, bias, out, out_dtype, accumulate)
     if not _cuda(a):
         res = reference.gemm(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, out_dtype=torch.float32)
         if out is None:
@@ -306,7 +343,7 @@ def rope_kv_write(qkv, positions, cos_sin, slots, k_cache, v_cache, Hq, Hkv, D, 
     """Inference path: (per-head RMSNorm +) RoPE on the q and k heads of a packed qkv row IN PLACE, and the new k / v
     rows scattered into cache slot ``slots[t]`` (negative: skipped), as one launch. Returns ``qkv``."""
     T = qkv.shape[0]
-    if not _cuda(qkv):
+    if not _is_cuda(qkv):
         x = qkv.view(T, Hq + 2 * Hkv, D)
         x[:, :Hq] = reference.rope(x[:, :Hq], positions, cos_sin, q_norm_w, eps)
         x[:, Hq : Hq + Hkv] = reference.rope(x[:, Hq : Hq + Hkv], positions, cos_sin, k_norm_w, eps)
@@ -324,7 +361,7 @@ class _SwiGLU(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gu):
         ctx.save_for_backward(gu)
-        if not _cuda(gu):
+        if not _is_cuda(gu):
             return reference.swiglu(gu)
         shape = gu.shape
         F_ = shape[-1] // 2
@@ -337,7 +374,7 @@ class _SwiGLU(torch.autograd.Function):
     def backward(ctx, dact):
         (gu,) = ctx.saved_tensors
         F_ = gu.shape[-1] // 2
-        if not _cuda(gu):
+        if not _is_cuda(gu):
             g, u, d = gu[..., :F_].float(), gu[..., F_:].float(), dact.float()
             sg = torch.sigmoid(g)
             silu = g * sg
@@ -421,13 +458,17 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if not _cuda(q):
+    if not _is_cuda(q):
         return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale)
     caller_splits = splits
     if splits is None:
         ctas = B * Hkv
         splits = 1 if ctas >= _lib.sm_count(q.device) else min(16, max(1, (2 * _lib.sm_count(q.device)) // max(ctas, 1)))
-        splits = max(1, min(splits, -(-block_table.shape[1] * page_size // 128)))  # never more splits than 128-token tiles
+        tiles = -(-block_table.shape[1] * page_size // 128)  # 128-token tiles of the longest context the table can hold
+        # Long contexts: one CTA per (request, kv head) would walk up to `tiles` tiles in sequence, and once most requests
+        # of a batch have finished the few long ones left keep only a few SMs busy. At most ~16 tiles per CTA.
+        splits = max(splits, min(16, -(-tiles // 16)))
+        splits = max(1, min(splits, tiles))  # never more splits than tiles
     if out is None:
         out = torch.empty_like(q)
     same_layout = k_cache.stride() == v_cache.stride() and k_cache.stride(2) == 1
@@ -481,7 +522,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
 def kv_write(k, v, slots, k_cache, v_cache):
     """Scatter rows ``k[t], v[t]`` ([T, Hkv*D] views, possibly strided) into cache slot ``slots[t]``."""
     row = k_cache.shape[1] * k_cache.shape[2]
-    if not _cuda(k):
+    if not _is_cuda(k):
         ok = slots >= 0
         k_cache.view(-1, row)[slots[ok].long()] = k[ok].reshape(-1, row)
         v_cache.view(-1, row)[slots[ok].long()] = v[ok].reshape(-1, row)
@@ -504,7 +545,7 @@ def sample(logits, temperature, top_k=None, top_p=None, min_p=None, seeds=None, 
     logprob = torch.empty(B, dtype=torch.float32, device=dev)
     kept_ids = torch.empty(B, kept_cap, dtype=torch.int32, device=dev) if kept_cap > 0 else None
     kept_count = torch.zeros(B, dtype=torch.int32, device=dev) if kept_cap > 0 else None
-    if not _cuda(logits):
+    if not _is_cuda(logits):
         from slime_b200.ops.sampling_ref import sample_reference
 
         return sample_reference(logits, temperature, top_k, top_p, min_p, seeds, positions, kept_cap)

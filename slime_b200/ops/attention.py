@@ -119,11 +119,28 @@ class _FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+def _library_segments(q, k, v, seg, scale):
+    """Comparison arm only (``ops.library_mode()``): the flash-attn library on the same segments."""
+    from flash_attn import flash_attn_varlen_func
+
+    s = seg.to(torch.int32)
+    zero = torch.zeros(1, dtype=torch.int32, device=seg.device)
+    # the library wants cumulative offsets: segments are laid out back to back on both sides in every caller
+    cu_q = torch.cat([s[:1, 0], s[:, 0] + s[:, 1]]).contiguous()
+    cu_k = torch.cat([s[:1, 2], s[:, 2] + s[:, 3]]).contiguous()
+    mq, mk = int(s[:, 1].max()), int(s[:, 3].max())
+    return flash_attn_varlen_func(q, k, v, cu_q, cu_k, mq, mk, softmax_scale=scale, causal=True)
+
+
 def segment_attention(q, k, v, seg, scale=None):
     """Causal GQA attention over a segment table. q: [Tq, Hq, D], k / v: [Tk, Hkv, D] -> [Tq, Hq, D]."""
+    from slime_b200 import ops
+
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
     if not q.is_cuda:
         return _reference_segments(q, k, v, seg, scale)
+    if ops.library_mode():
+        return _library_segments(q, k, v, seg, scale)
     return _FlashAttention.apply(q, k, v, seg, scale)
 
 
@@ -269,7 +286,9 @@ def rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, 
         ctx = context_parallel_attention(q3[:, :Hq], q3[:, Hq : Hq + Hkv], q3[:, Hq + Hkv :], cp_local_cu_seqlens, cp_group, scale)
         return ctx.reshape(T, Hq * D)
     seg = segments_from_cu_seqlens(cu_seqlens)
-    if qkv.is_cuda:
+    from slime_b200 import ops as _ops
+
+    if qkv.is_cuda and not _ops.library_mode():
         return _RopeAttentionCUDA.apply(qkv, positions, cos_sin, q_norm_w, k_norm_w, seg, Hq, Hkv, D, eps, scale)
     from slime_b200.ops import rope_qk
 

@@ -6,6 +6,7 @@ repetitions with an L2 flush (a 256 MiB memset) between them. One JSON object pe
     gemm    tcgen05 GEMM vs cuBLAS (torch.matmul) for forward / dgrad / wgrad layouts
     decode  each kernel of one rollout decode step at a given batch and context length
     norm    RMSNorm forward/backward bandwidth
+    attn    flash attention forward / backward (own kernels; the flash-attn library on the same tensors for comparison)
 
 ``--small`` shrinks the working set to a case suitable for a profiler capture (a few launches, < 1 GB).
 """
@@ -297,9 +298,52 @@ def bench_moe(a):
     _lib.check_status("cuda")
 
 
+def bench_attn(a):
+    """Flash attention forward / backward (own tcgen05 kernels) on packed equal-length sequences, and the flash-attn
+    library (an mma.sync-class kernel) on the same tensors when it is importable. FLOPs: causal, 4 * S^2 * H * D / 2 per
+    sequence forward, 2.5 x that backward."""
+    from slime_b200.ops import attention
+
+    try:
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward, _flash_attn_varlen_forward
+    except Exception:  # noqa: BLE001
+        _flash_attn_varlen_forward = None
+    cases = [(14, 2, 64, 1024, 16), (14, 2, 64, 4096, 4), (32, 8, 128, 2048, 4), (32, 8, 128, 8192, 1), (16, 4, 128, 8192, 1)]
+    if a.small:
+        cases = [(32, 8, 128, 2048, 2)]
+    for Hq, Hkv, D, S_, nseq in cases:
+        T = S_ * nseq
+        qkv = (torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda") * 0.5).to(torch.bfloat16)
+        x3 = qkv.view(T, Hq + 2 * Hkv, D)
+        q, k, v = x3[:, :Hq], x3[:, Hq : Hq + Hkv], x3[:, Hq + Hkv :]
+        cu = torch.arange(0, T + 1, S_, dtype=torch.int32, device="cuda")
+        seg = attention.segments_from_cu_seqlens(cu)
+        scale = 1.0 / math.sqrt(D)
+        fwd_flops = 4.0 * S_ * S_ * Hq * D / 2 * nseq
+        out, lse = attention.flash_fwd(q, k, v, seg, scale)
+        d_o = torch.randn_like(out)
+        dqkv = torch.zeros_like(qkv)
+        d3 = dqkv.view(T, Hq + 2 * Hkv, D)
+        tf = time_ms(lambda: attention.flash_fwd(q, k, v, seg, scale, out=out), a.iters)
+        tb = time_ms(lambda: attention.flash_bwd(q, k, v, out, d_o, lse, seg, scale, dq=d3[:, :Hq], dk=d3[:, Hq : Hq + Hkv],
+                                                 dv=d3[:, Hq + Hkv :]), a.iters)  # fmt: skip
+        rec = dict(kind="flash_attn", Hq=Hq, Hkv=Hkv, D=D, seqlen=S_, nseq=nseq, fwd_ms=tf, fwd_tflops=fwd_flops / tf / 1e9,
+                   bwd_ms=tb, bwd_tflops=2.5 * fwd_flops / tb / 1e9)  # fmt: skip
+        if _flash_attn_varlen_forward is not None and not a.no_cublas:
+            res = _flash_attn_varlen_forward(q, k, v, cu, cu, S_, S_, 0.0, scale, causal=True)
+            lo, llse, rng = res[0], res[1], res[3]
+            lf = time_ms(lambda: _flash_attn_varlen_forward(q, k, v, cu, cu, S_, S_, 0.0, scale, causal=True), a.iters)
+            lb = time_ms(lambda: _flash_attn_varlen_backward(d_o, q, k, v, lo, llse, d3[:, :Hq], d3[:, Hq : Hq + Hkv],
+                                                             d3[:, Hq + Hkv :], cu, cu, S_, S_, 0.0, scale, True, -1, -1, 0.0,
+                                                             None, False, rng), a.iters)  # fmt: skip
+            rec.update(lib_fwd_ms=lf, lib_bwd_ms=lb, lib_fwd_tflops=fwd_flops / lf / 1e9, lib_bwd_tflops=2.5 * fwd_flops / lb / 1e9)
+        _emit(**rec)
+    _lib.check_status("cuda")
+
+
 def main(argv=None):
     p = argparse.ArgumentParser(prog="python -m slime_b200.ops.microbench")
-    p.add_argument("what", choices=["gemm", "decode", "norm", "fp8", "moe"])
+    p.add_argument("what", choices=["gemm", "decode", "norm", "fp8", "moe", "attn"])
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--reps", type=int, default=20, help="back-to-back launches per timed repetition (decode)")
     p.add_argument("--small", action="store_true")
@@ -313,7 +357,7 @@ def main(argv=None):
     from slime_b200.ops import build
 
     build.build()
-    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm, "fp8": bench_fp8, "moe": bench_moe}[a.what](a)
+    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm, "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn}[a.what](a)
 
 
 if __name__ == "__main__":

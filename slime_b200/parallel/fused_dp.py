@@ -26,7 +26,7 @@ logger = logging.getLogger(__name__)
 
 
 def symmetric_memory_usable(group_size: int, device) -> bool:
-    if os.environ.get("SLIME_B200_DISABLE_FUSED_DP") == "1":
+    if os.environ.get("SLIME_B200_DISABLE_FUSED_DP") == "1" or os.environ.get("SLIME_B200_LIBRARY_OPS") == "1":
         return False
     if group_size < 2 or group_size > 8 or torch.device(device).type != "cuda":
         return False

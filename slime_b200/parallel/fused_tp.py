@@ -33,7 +33,7 @@ MAX_BLOCKS = 148
 
 
 def usable(group_size: int, device, hidden: int) -> bool:
-    if os.environ.get("SLIME_B200_DISABLE_FUSED_TP") == "1":
+    if os.environ.get("SLIME_B200_DISABLE_FUSED_TP") == "1" or os.environ.get("SLIME_B200_LIBRARY_OPS") == "1":
         return False
     return symmetric_memory_usable(group_size, device) and hidden % 8 == 0 and hidden <= 8192
 

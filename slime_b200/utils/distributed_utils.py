@@ -85,3 +85,19 @@ def distributed_masked_whiten(values: torch.Tensor, mask: torch.Tensor, process_
         var *= count / (count - 1)  # unbiased, like torch.var
     out = (v - mean) * (var + epsilon) ** -0.5
     return out if shift_mean else out + mean
+
+
+def shutdown_distributed(engines=()) -> None:
+    """Orderly end of a distributed process: engines drop their CUDA graphs (see ``Engine.shutdown``), every rank
+    arrives, then the process groups are destroyed."""
+    import torch
+    import torch.distributed as dist
+
+    for e in engines:
+        if e is not None and hasattr(e, "shutdown"):
+            e.shutdown()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()

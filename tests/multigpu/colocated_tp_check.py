@@ -16,6 +16,9 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 
 
 def main():
+    import faulthandler
+
+    faulthandler.dump_traceback_later(240, exit=True)  # a stuck job prints where every thread is and ends itself
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     cuda = os.environ.get("DEVICE", "cpu") == "cuda"
     if cuda:

@@ -37,6 +37,9 @@ def hf_weights(cfg, device, seed=0):
 
 
 def main():
+    import faulthandler
+
+    faulthandler.dump_traceback_later(240, exit=True)  # a stuck job prints where every thread is and ends itself
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     cpu = os.environ.get("ENGINE_TP_CHECK_DEVICE") == "cpu"  # host-side logic only: gloo ranks, reference ops
     if cpu:
@@ -84,8 +87,9 @@ def main():
             worst = max(worst, float((ref - torch.tensor(lp)).abs().max()))
         assert worst < (1e-4 if cpu else 0.08), worst
         print(f"RESULT ok world={world} fused_tp={fused} max_logprob_diff={worst:.4f}", flush=True)
-    dist.barrier()
-    dist.destroy_process_group()
+    from slime_b200.utils.distributed_utils import shutdown_distributed
+
+    shutdown_distributed([tp])
 
 
 if __name__ == "__main__":

@@ -26,7 +26,11 @@ def _torchrun(script, nproc, extra_env=None, timeout=420):
     env.setdefault("MASTER_ADDR", "127.0.0.1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}", "--master-addr", "127.0.0.1",
            "--master-port", str(_free_port()), os.path.join(ROOT, script)]  # fmt: skip
-    return subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+    try:
+        return subprocess.run(cmd, env=env, cwd=ROOT, capture_output=True, text=True, timeout=timeout)
+    except subprocess.TimeoutExpired as e:
+        out = (e.stdout or b"")[-3000:], (e.stderr or b"")[-3000:]
+        raise AssertionError(f"{script} still running after {timeout} s; its output so far:\n{out[0]!r}\n{out[1]!r}") from None
 
 
 def _need(n):
