@@ -52,21 +52,78 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, 
   n0 = (r / pm) * BN;
 }
 
-// Optional extra kernel parameter. NoExtra: nothing. AllGatherA: the rows of A are spread over up to 8 GPUs (rank r holds
-// rows [r * rows_per_rank, (r + 1) * rows_per_rank) in its own buffer, reachable through peer memory): the producer
-// picks the tensor map of the GPU that owns a tile's rows, so the all-gather of a sequence-parallel activation happens
-// inside the GEMM's operand loads (plain TMA loads from peer memory, no multicast) and is never materialised.
+// Optional extra kernel parameter: a collective fused into the GEMM over NVLink peer memory (no multicast loads).
+//
+// GatherA (all-gather -> GEMM, sequence-parallel column linear): the rows of A are spread over up to 8 GPUs, rank r
+// holding rows [r * rows_per_rank, (r + 1) * rows_per_rank) in a buffer every rank can read. A seventh warp in every CTA
+// pulls the peers' shards ONCE into this GPU's `gathered` buffer (plain 16-byte loads from peer memory, 4-row pieces
+// striped over the CTAs, nearest peer first) and counts the pieces of each 128-row block; the tile order starts with the
+// rank's own rows, and the TMA producer waits (bounded) for a remote block's counter before it loads tiles of that
+// block from LOCAL memory. Every remote byte crosses NVLink once, under the GEMM of the rows that are already there,
+// and the gathered activation is left behind for the weight-gradient GEMM of the backward pass.
+//
+// ScatterC (GEMM -> reduce-scatter, sequence-parallel row linear): every rank computes the full [M, N] partial product;
+// rows [o * rows_per_rank, ...) belong to rank o. The epilogue TMA-stores each bf16 tile into slot `rank` of the
+// owner's receive buffer (its own or a peer's) and then raises one flag word per (tile, source rank, epilogue warp) on
+// the owner; tiles owned by peers are computed first. When a CTA has finished its share of the GEMM its epilogue warps
+// turn to the tiles this rank owns: wait (bounded) for every source's flag, sum the `world` slots in rank order in fp32
+// and write the reduced bf16 tile. No NCCL call, no second launch, fixed summation order.
 struct NoExtra {
-  static constexpr bool kAllGather = false;
+  static constexpr int kMode = 0;
 };
-struct AllGatherA {
-  static constexpr bool kAllGather = true;
-  CUtensorMap maps[8];
-  int rows_per_rank;
+struct GatherA {
+  static constexpr int kMode = 1;
+  const void* peer[8];  // shard of rank r: [rows_per_rank, K] bf16, contiguous rows
+  void* gathered;       // this GPU's [world * rows_per_rank, K] bf16, contiguous: the A operand (own rows filled by the caller)
+  uint32_t* counters;   // one per 128-row block of `gathered`: pieces copied so far, monotonic over calls
+  uint32_t target;      // value a block's counter has when this call's copy of the block is complete
+  int rows_per_rank, world, rank, row_bytes;
+  unsigned long long limit_ns;
 };
+struct ScatterC {
+  static constexpr int kMode = 2;
+  CUtensorMap slot[8];        // owner o's receive buffer viewed as [world * rows_per_rank, N] bf16 (slot-major)
+  const __nv_bfloat16* recv;  // this rank's own receive buffer, same view
+  uint32_t* flags[8];         // owner o's flag words: [owned tiles][world][4 epilogue warps]
+  __nv_bfloat16* out;         // [rows_per_rank, N] bf16, pitch ld_out
+  int ld_out;
+  uint32_t epoch;
+  int rows_per_rank, world, rank;
+  unsigned long long limit_ns;
+};
+constexpr int GATHER_PIECE_ROWS = 4;
+
+__device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+// All of this thread's bulk groups have completed (their writes performed), not merely read their source.
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Rotation of the row-tile index: the walk starts at tile `rot` and wraps (own rows first when gathering, last when
+// scattering).
+template <int BN>
+__device__ __forceinline__ void tile_origin_rot(int tile, int tiles_m, int tiles_n, int rot, int& m0, int& n0) {
+  tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
+  if (rot != 0) {
+    int mt = m0 / GEMM_BM + rot;
+    if (mt >= tiles_m) mt -= tiles_m;
+    m0 = mt * GEMM_BM;
+  }
+}
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI, typename Extra = NoExtra>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + 32, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv, const __nv_bfloat16* __restrict__ bias,
                  int M, int N, int K, int ldc, int accumulate, int* status, const int* __restrict__ tile_boff,
@@ -96,6 +153,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const bool add_out = (accumulate & 1) != 0 || splitk > 1;
   const int kb_per = (num_kb + splitk - 1) / splitk;
   const int num_items = num_tiles * splitk;
+  int rot = 0;  // first row tile of the walk
+  if constexpr (Extra::kMode == 1) rot = extra.rank * (extra.rows_per_rank / GEMM_BM);
+  if constexpr (Extra::kMode == 2) rot = ((extra.rank + 1) % extra.world) * (extra.rows_per_rank / GEMM_BM);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -133,7 +193,31 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const int tile = item / splitk, ks = item - tile * splitk;
         int m0, n0;
-        tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
+        tile_origin_rot<BN>(tile, tiles_m, tiles_n, rot, m0, n0);
+        if constexpr (Extra::kMode == 1) {
+          // rows of another rank: wait until the gather warps have brought the whole 128-row block into local memory
+          if (m0 / extra.rows_per_rank != extra.rank) {
+            const uint32_t* ctr = extra.counters + m0 / GEMM_BM;
+            const unsigned long long t0 = globaltimer_ns();
+            uint32_t it = 0;
+            while (static_cast<int32_t>(ld_acquire_gpu_u32(ctr) - extra.target) < 0) {
+              if ((++it & 0x3f) == 0) {
+                if (*cta_abort) {
+                  ok = false;
+                  break;
+                }
+                if (globaltimer_ns() - t0 > extra.limit_ns) {
+                  *cta_abort = 1;
+                  if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (blockIdx.x << 8));
+                  ok = false;
+                  break;
+                }
+              }
+            }
+            if (!ok) break;
+            fence_proxy_async_all();  // rows written with plain stores by other CTAs -> visible to this TMA load
+          }
+        }
         // Grouped GEMM: B is the experts' matrices stacked along its row dimension and every 128-row tile of A belongs
         // to one expert; tile_boff[m-tile] is the row at which that expert's matrix starts in the stack.
         const int boff = tile_boff != nullptr ? __ldg(tile_boff + m0 / GEMM_BM) : 0;
@@ -146,11 +230,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_arrive_expect_tx(&full[stage], S::STAGE_BYTES);
           uint8_t* a_dst = sA + stage * S::A_BYTES;
           uint8_t* b_dst = sB + stage * S::B_BYTES;
-          if constexpr (Extra::kAllGather) {
-            static_assert(!Extra::kAllGather || !A_MN, "the gathered operand is row-major [rows, K]");
-            const int owner = m0 / extra.rows_per_rank;  // rows_per_rank is a multiple of the row tile
-            tma_load_2d(a_dst, &extra.maps[owner], &full[stage], kb * GEMM_BK, m0 - owner * extra.rows_per_rank);
-          } else if constexpr (!A_MN) {
+          if constexpr (!A_MN) {
             tma_load_2d(a_dst, &tmA, &full[stage], kb * GEMM_BK, m0);
           } else {
 #pragma unroll
@@ -216,7 +296,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     int acc = 0;
@@ -228,7 +308,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int tile = item / splitk;
       const __nv_bfloat16* bias = (item - tile * splitk) == 0 ? bias_all : nullptr;  // one slice adds the bias
       int m0, n0;
-      tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
+      tile_origin_rot<BN>(tile, tiles_m, tiles_n, rot, m0, n0);
       bool ok = mbar_wait(&tfull[acc], acc_phase, cta_abort, status, ERR_WAIT_TMEM_FULL);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -296,13 +376,29 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           fence_proxy_async();  // generic-proxy writes -> visible to the TMA engine
           __syncwarp();
           if (lane == 0) {
-            if (add_out)
+            if constexpr (Extra::kMode == 2) {
+              const int owner = m0 / extra.rows_per_rank;
+              tma_store_2d(&extra.slot[owner], dst, col0, row0 - owner * extra.rows_per_rank + extra.rank * extra.rows_per_rank);
+            } else if (add_out) {
               tma_reduce_add_2d(&tmC, dst, col0, row0);
-            else
+            } else {
               tma_store_2d(&tmC, dst, col0, row0);
+            }
             bulk_commit_group();
           }
           buf ^= 1;
+        }
+        if constexpr (Extra::kMode == 2) {
+          // this warp's 32 rows of the tile are on their way: once the stores have completed, tell the owner
+          if (lane == 0) {
+            bulk_wait_group_all();
+            fence_proxy_async_all();
+            __threadfence_system();
+            const int owner = m0 / extra.rows_per_rank;
+            const int lt = ((m0 - owner * extra.rows_per_rank) / GEMM_BM) * tiles_n + n0 / BN;
+            st_release_sys_u32(extra.flags[owner] + (static_cast<size_t>(lt) * extra.world + extra.rank) * 4 + q, extra.epoch);
+          }
+          __syncwarp();
         }
       } else {
         const int row = m0 + q * 32 + lane;
@@ -342,6 +438,80 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if constexpr (TMA_EPI) {
       if (lane == 0) bulk_wait_group_read<0>();  // staging memory must outlive the stores that read it
       __syncwarp();
+    }
+    if constexpr (Extra::kMode == 2) {
+      // ---------------------------------------------------- reduce the tiles this rank owns (see ScatterC)
+      const int tpr = extra.rows_per_rank / GEMM_BM;
+      const int owned = tpr * tiles_n;
+      const uint32_t* my_flags = extra.flags[extra.rank];
+      constexpr int VEC = BN / 8;        // 16-byte vectors per tile row
+      constexpr int RPI = 32 / VEC;      // rows handled per warp iteration (1 for BN = 256, 2 for BN = 128)
+      bool ok2 = (*cta_abort == 0);
+      for (int t = blockIdx.x; t < owned && ok2; t += gridDim.x) {
+        if (lane < extra.world) {
+          const uint32_t* f = my_flags + (static_cast<size_t>(t) * extra.world + lane) * 4 + q;
+          const unsigned long long t0 = globaltimer_ns();
+          uint32_t it = 0;
+          while (static_cast<int32_t>(ld_acquire_sys_u32(f) - extra.epoch) < 0) {
+            if ((++it & 0x3f) == 0 && (*cta_abort || globaltimer_ns() - t0 > extra.limit_ns)) {
+              if (status) atomicCAS(status, 0, ERR_WAIT_PEER | (lane << 8));
+              *cta_abort = 1;
+              ok2 = false;
+              break;
+            }
+          }
+        }
+        ok2 = __all_sync(0xffffffffu, ok2);
+        if (!ok2) break;
+        const int row_base = (t / tiles_n) * GEMM_BM + q * 32;
+        const int col = (t % tiles_n) * BN + (lane % VEC) * 8;
+        if (col < N) {
+          for (int rr = lane / VEC; rr < 32; rr += RPI) {
+            const int row = row_base + rr;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int r = 0; r < extra.world; ++r) {
+              const uint4 u = *reinterpret_cast<const uint4*>(extra.recv + (static_cast<size_t>(r) * extra.rows_per_rank + row) * N + col);
+              const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
+              acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y;
+              acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+            }
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]);
+            o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]);
+            o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4*>(extra.out + static_cast<size_t>(row) * extra.ld_out + col) = o;
+          }
+        }
+      }
+    }
+  }
+  if constexpr (Extra::kMode == 1) {
+    if (warp == 6) {
+      // ---------------------------------------------------- gather warp: pull the peers' shards into `gathered`
+      const int per_shard = extra.rows_per_rank / GATHER_PIECE_ROWS;
+      const int total = (extra.world - 1) * per_shard;
+      const int n16 = GATHER_PIECE_ROWS * extra.row_bytes / 16;  // 16-byte vectors per piece (rows are contiguous)
+      for (int p = blockIdx.x; p < total; p += gridDim.x) {
+        const int s = p / per_shard, piece = p - s * per_shard;
+        const int src = (extra.rank + 1 + s) % extra.world;  // nearest peer first: the order the tiles are walked in
+        const size_t row0 = static_cast<size_t>(piece) * GATHER_PIECE_ROWS;
+        const uint4* from = reinterpret_cast<const uint4*>(static_cast<const char*>(extra.peer[src]) + row0 * extra.row_bytes);
+        uint4* to = reinterpret_cast<uint4*>(static_cast<char*>(extra.gathered) +
+                                             (static_cast<size_t>(src) * extra.rows_per_rank + row0) * extra.row_bytes);
+        for (int i = lane; i < n16; i += 32 * 8) {
+          uint4 v[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + u * 32 < n16) v[u] = from[i + u * 32];
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            if (i + u * 32 < n16) to[i + u * 32] = v[u];
+        }
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(extra.counters + (src * extra.rows_per_rank + static_cast<int>(row0)) / GEMM_BM, 1u);
+      }
     }
   }
 
@@ -388,8 +558,10 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   }
   const int splitk = (accumulate >> 8) > 1 ? (accumulate >> 8) : 1;
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
-  const int grid = tiles < num_sms ? tiles : num_sms;
-  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(GEMM_THREADS), S::TOTAL, stream, tmA, tmB, tmC, C,
+  int grid = tiles < num_sms ? tiles : num_sms;
+  if (Extra::kMode != 0) grid = num_sms;  // the collective's own work (gather pieces, owned tiles) is striped over every CTA
+  constexpr int threads = Extra::kMode == 1 ? GEMM_THREADS + 32 : GEMM_THREADS;  // + the gather warp
+  cudaError_t le = launch_pdl(kern, dim3(grid), dim3(threads), S::TOTAL, stream, tmA, tmB, tmC, C,
                               reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status, tile_boff, extra);
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));
   return le;
@@ -497,44 +669,87 @@ extern "C" int sb_gemm_bf16_grouped(const void* A, const void* B, void* C, const
   }
 }
 
-// All-gather fused into the GEMM: C[M, N] = gather(A_0 .. A_{world-1}) * B^T (+ bias), where A_r [rows_per_rank, K]
-// (row-major, pitch lda) lives on GPU r and a_ptrs[r] is its address as seen from this GPU (own buffer or peer
-// mapping). M = world * rows_per_rank; rows_per_rank must be a multiple of 128. B [N, K] row-major, C bf16 or fp32.
-// The caller makes sure (barrier) that every A_r is complete before the launch and not rewritten before it ends.
-extern "C" int sb_gemm_bf16_allgather_a(const void* const* a_ptrs, int world, int rows_per_rank, const void* B, void* C,
-                                        const void* bias, int N, int K, int lda, int ldb, int ldc, int out_f32, int bn,
-                                        int* status, int num_sms, cudaStream_t stream) {
-  if (world < 1 || world > 8 || rows_per_rank <= 0 || rows_per_rank % sb::GEMM_BM != 0) {
-    sb::set_last_error("sb_gemm_bf16_allgather_a: 1..8 ranks, rows_per_rank a positive multiple of 128");
+// All-gather fused into the GEMM (see GatherA): C[M, N] = gathered * op(B) (+ bias), M = world * rows_per_rank.
+// peers[r]: rank r's shard [rows_per_rank, K] bf16 with contiguous rows, as mapped into this GPU (own included; the own
+// shard is not read). gathered: this GPU's [M, K] bf16 buffer whose rows of THIS rank the caller has already filled;
+// counters: M / 128 words, zero before the first call; target = 32 * (number of calls made with these counters,
+// this one included). rows_per_rank a multiple of 128, K a multiple of 8. B: [N, K] (b_mn = 0) or [K, N] (b_mn = 1).
+// The caller makes sure (barrier) that every rank's shard is complete before the launch and stays until it ends.
+extern "C" int sb_gemm_bf16_gather_a(const void* const* peers, int world, int rank, int rows_per_rank, void* gathered,
+                                     unsigned* counters, unsigned target, const void* B, void* C, const void* bias, int N,
+                                     int K, int ldb, int ldc, int b_mn, int bn, int* status, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || rows_per_rank <= 0 || rows_per_rank % sb::GEMM_BM != 0 || (K & 7)) {
+    sb::set_last_error("sb_gemm_bf16_gather_a: 1..8 ranks, rows_per_rank a positive multiple of 128, K a multiple of 8");
     return (int)cudaErrorInvalidValue;
   }
   const int M = world * rows_per_rank;
-  const size_t c_elem = out_f32 ? 4 : 2;
-  const bool tma_epi = (reinterpret_cast<uintptr_t>(C) & 15) == 0 && (size_t(ldc) * c_elem) % 16 == 0;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || (size_t(ldc) * 2) % 16) {
+    sb::set_last_error("sb_gemm_bf16_gather_a: C must be 16-byte aligned with a 16-byte-multiple pitch");
+    return (int)cudaErrorInvalidValue;
+  }
   try {
-    sb::AllGatherA ex{};
+    sb::GatherA ex{};
+    for (int r = 0; r < 8; ++r) ex.peer[r] = peers[r < world ? r : 0];
+    ex.gathered = gathered;
+    ex.counters = counters;
+    ex.target = target;
     ex.rows_per_rank = rows_per_rank;
-    for (int r = 0; r < world; ++r)
-      ex.maps[r] = sb::make_tmap_2d(a_ptrs[r], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows_per_rank, K, size_t(lda) * 2,
-                                    sb::GEMM_BM, sb::GEMM_BK, CU_TENSOR_MAP_SWIZZLE_128B);
-    for (int r = world; r < 8; ++r) ex.maps[r] = ex.maps[0];
-    const void* A0 = a_ptrs[0];
-#define SB_AG(BNV, ST, OF, TE)                                                                                            \
-  return (int)sb::launch_gemm<BNV, ST, false, false, OF, TE, sb::AllGatherA>(A0, B, C, bias, M, N, K, lda, ldb, ldc, 0, status, \
+    ex.world = world;
+    ex.rank = rank;
+    ex.row_bytes = K * 2;
+    ex.limit_ns = sb::peer_wait_limit_ns();
+#define SB_GA(BNV, ST, BM_)                                                                                                  \
+  return (int)sb::launch_gemm<BNV, ST, false, BM_, false, true, sb::GatherA>(gathered, B, C, bias, M, N, K, K, ldb, ldc, 0, status, \
                                                                              num_sms, stream, nullptr, 0, ex);
     if (bn == 256) {
-      if (out_f32) {
-        if (tma_epi) { SB_AG(256, 4, true, true) } else { SB_AG(256, 4, true, false) }
-      } else {
-        if (tma_epi) { SB_AG(256, 4, false, true) } else { SB_AG(256, 4, false, false) }
-      }
+      if (b_mn) { SB_GA(256, 4, true) } else { SB_GA(256, 4, false) }
     }
-    if (out_f32) {
-      if (tma_epi) { SB_AG(128, 6, true, true) } else { SB_AG(128, 6, true, false) }
-    } else {
-      if (tma_epi) { SB_AG(128, 6, false, true) } else { SB_AG(128, 6, false, false) }
+    if (b_mn) { SB_GA(128, 6, true) } else { SB_GA(128, 6, false) }
+#undef SB_GA
+  } catch (const std::exception& e) {
+    sb::set_last_error(e.what());
+    return (int)cudaErrorInvalidValue;
+  }
+}
+
+// Reduce-scatter fused into the GEMM (see ScatterC): out[rows_per_rank, N] = rows of THIS rank of sum_r (A_r * op(B_r)),
+// every rank calling with its own A [M, K] and B, M = world * rows_per_rank. recv[o] / flags[o]: owner o's receive buffer
+// ([world][rows_per_rank][N] bf16) and flag words ((rows_per_rank / 128) * ceil(N / bn) * world * 4, zero before the first
+// call) as mapped into this GPU; epoch: 1, 2, 3, ... per call on a given pair of buffers. N a multiple of 8. The caller
+// alternates between two receive buffers (a rank may run one call ahead of its peers).
+extern "C" int sb_gemm_bf16_scatter_c(const void* A, const void* B, int M, int N, int K, int lda, int ldb, int b_mn,
+                                      const void* const* recv, const void* const* flags, int world, int rank, void* out,
+                                      int ld_out, unsigned epoch, int bn, int* status, int num_sms, cudaStream_t stream) {
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || M <= 0 || M % (world * sb::GEMM_BM) != 0 || (N & 7)) {
+    sb::set_last_error("sb_gemm_bf16_scatter_c: 1..8 ranks, M a multiple of world * 128, N a multiple of 8");
+    return (int)cudaErrorInvalidValue;
+  }
+  const int rows_per_rank = M / world;
+  try {
+    sb::ScatterC ex{};
+    for (int o = 0; o < 8; ++o) {
+      const int src = o < world ? o : 0;
+      ex.slot[o] = sb::make_tmap_2d(recv[src], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, size_t(world) * rows_per_rank, N, size_t(N) * 2,
+                                    32, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+      ex.flags[o] = static_cast<uint32_t*>(const_cast<void*>(flags[src]));
     }
-#undef SB_AG
+    ex.recv = static_cast<const __nv_bfloat16*>(recv[rank]);
+    ex.out = static_cast<__nv_bfloat16*>(out);
+    ex.ld_out = ld_out;
+    ex.epoch = epoch;
+    ex.rows_per_rank = rows_per_rank;
+    ex.world = world;
+    ex.rank = rank;
+    ex.limit_ns = sb::peer_wait_limit_ns();
+    void* c_unused = const_cast<void*>(recv[rank]);  // tmC is built but never stored through in this mode
+#define SB_SC(BNV, ST, BM_)                                                                                                   \
+  return (int)sb::launch_gemm<BNV, ST, false, BM_, false, true, sb::ScatterC>(A, B, c_unused, nullptr, M, N, K, lda, ldb, N, 0, status, \
+                                                                              num_sms, stream, nullptr, 0, ex);
+    if (bn == 256) {
+      if (b_mn) { SB_SC(256, 4, true) } else { SB_SC(256, 4, false) }
+    }
+    if (b_mn) { SB_SC(128, 6, true) } else { SB_SC(128, 6, false) }
+#undef SB_SC
   } catch (const std::exception& e) {
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;

@@ -42,6 +42,10 @@ class TrainModel:
         self.args, self.role = args, role
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self.cfg = ModelConfig.from_args(args)
+        if getattr(args, "max_tokens_per_gpu", None):
+            from slime_b200.parallel import fused_tp
+
+            fused_tp.set_max_tokens(args.max_tokens_per_gpu)
         pp, ppr = mpu.get_pipeline_model_parallel_world_size(), mpu.get_pipeline_model_parallel_rank()
         vpp = mpu.get_virtual_pipeline_model_parallel_world_size() or 1
         dtype = torch.bfloat16 if getattr(args, "bf16", True) else torch.float32

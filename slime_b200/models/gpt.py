@@ -54,6 +54,17 @@ class PackedSeqParams:
         self.qkv_format = "thd"
 
 
+def _fused_sp_linears(cfg: ModelConfig, x, rows_local: int):
+    """The fused all-gather->GEMM / GEMM->reduce-scatter pair of the tensor-parallel group when it exists and this
+    micro-batch fits its buffers (the same answer on every rank of the group: it depends on shapes only)."""
+    if not x.is_cuda:
+        return None
+    from slime_b200.parallel import fused_tp
+
+    fl = fused_tp.sequence_parallel_linears(mpu.get_tensor_model_parallel_group(), cfg.hidden_size, x.device)
+    return fl if fl is not None and fl.fits(rows_local, cfg.hidden_size) else None
+
+
 class SelfAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
         super().__init__()
@@ -89,8 +100,12 @@ class SelfAttention(nn.Module):
     def forward(self, x, residual, rope_table, packed: PackedSeqParams):
         cfg = self.cfg
         normed, residual = ops.rmsnorm(x, self.linear_qkv.layer_norm_weight, cfg.norm_epsilon, residual)
-        inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
-        qkv = ops.linear(inp, self.linear_qkv.weight, self.linear_qkv.bias)
+        fused = _fused_sp_linears(cfg, normed, normed.shape[0]) if self.sp else None
+        if fused is not None:
+            qkv = fused.column(normed, self.linear_qkv.weight, self.linear_qkv.bias)
+        else:
+            inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
+            qkv = ops.linear(inp, self.linear_qkv.weight, self.linear_qkv.bias)
         cp = mpu.get_context_parallel_world_size()
         ctx = ops.rope_attention(
             qkv, packed.position_ids, rope_table, packed.cu_seqlens, packed.max_seqlen, self.hq, self.hkv, self.d,
@@ -99,6 +114,8 @@ class SelfAttention(nn.Module):
             cp_local_cu_seqlens=getattr(packed, "local_cu_seqlens", None) if cp > 1 else None,
             cp_group=mpu.get_context_parallel_group() if cp > 1 else None,
         )  # fmt: skip
+        if fused is not None:
+            return fused.row(ctx, self.linear_proj.weight), residual
         out = ops.linear(ctx, self.linear_proj.weight)
         out = tp.reduce_scatter_to_sequence_parallel_region(out) if self.sp else tp.reduce_from_tensor_model_parallel_region(out)
         return out, residual
@@ -129,6 +146,9 @@ class MLP(nn.Module):
         return self.ffn(normed), residual
 
     def ffn(self, normed):
+        fused = _fused_sp_linears(self.cfg, normed, normed.shape[0]) if self.sp else None
+        if fused is not None:
+            return fused.row(ops.swiglu(fused.column(normed, self.linear_fc1.weight)), self.linear_fc2.weight)
         inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
         act = ops.swiglu(ops.linear(inp, self.linear_fc1.weight))
         out = ops.linear(act, self.linear_fc2.weight)

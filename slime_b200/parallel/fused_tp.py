@@ -87,21 +87,39 @@ class FusedAllReduceNorm:
         return y, r
 
 
-class AllGatherGemm:
-    """``gather_rows(x_0 .. x_{n-1}) @ W^T`` with the gather done by the GEMM's own operand loads.
+class _SymmBarrier:
+    """Bounded device-side barrier over a symmetric allocation's signal pad (epoch kept on the device: graph safe)."""
 
-    Sequence-parallel column-parallel linears (QKV, gate/up) take an activation that is sharded by rows over the
-    tensor-parallel ranks. Each rank writes its shard into a symmetric buffer; after one bounded barrier either the
-    tcgen05 GEMM on every rank reads the row tiles it needs straight from the owning GPU (plain TMA loads over NVLink:
-    the gathered activation never exists in memory), or the peers' shards are pulled by the copy engines while the GEMM
-    already runs on the rows that are local (see ``__call__``). No NCCL all-gather runs in either mode.
+    def __init__(self, storage: SymmetricStorage, word_offset_from_top: int, device):
+        from slime_b200.ops import _lib
 
-        ag = AllGatherGemm(tp_group, max_rows_per_rank, K, device)
-        ag.shard(rows).copy_(x_local)             # or let the producing kernel write there
-        y = ag(rows, weight)                      # [world * rows, N]
+        self._lib = _lib
+        self.world, self.rank = storage.world, storage.rank
+        self._pads = (ctypes.c_void_p * self.world)(*storage.pad_ptrs)
+        self._base = storage.pad_words - word_offset_from_top
+        self._counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.device = device
 
-    ``rows`` (per rank) must be a multiple of 128. Two buffers alternate, so a rank may refill its shard for the next
-    call while slower ranks still read the previous one; the barrier at the start of every call keeps two calls apart.
+    def __call__(self):
+        lib, P = self._lib.lib(), self._lib.ptr
+        rc = lib.sb_symm_barrier_dev(self._pads, self.rank, self.world, P(self._counter), self._base,
+                                     P(self._lib.status_word(self.device)), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_symm_barrier_dev")
+
+
+class GatherGemm:
+    """All-gather fused into the GEMM: ``gather_rows(x_0 .. x_{n-1}) @ op(W)`` in one kernel (``GatherA`` in
+    ``csrc/gemm_sm100.cu``).
+
+    Sequence-parallel column-parallel linears (QKV, gate/up) and the input-gradient GEMM of row-parallel ones take an
+    operand that is sharded by rows over the tensor-parallel ranks. Each rank puts its shard into a symmetric buffer;
+    after one bounded barrier the GEMM kernel on every rank starts on its own rows while a dedicated warp in each CTA
+    pulls the peers' rows once into local memory (plain loads over NVLink) and releases them to the tile loop block by
+    block. Returns the product and the gathered operand (the backward's weight-gradient GEMM reads it again).
+
+    ``rows`` (per rank) must be a multiple of 128. Two shard buffers alternate, so a rank may refill its shard for the
+    next call while slower ranks still read the previous one; the barrier at the start of every call keeps two calls
+    apart.
     """
 
     def __init__(self, group, max_rows_per_rank: int, k: int, device):
@@ -111,69 +129,202 @@ class AllGatherGemm:
         self.k, self.max_rows, self.device = k, max_rows_per_rank, torch.device(device)
         self.bufs = [SymmetricStorage(max_rows_per_rank * k, torch.bfloat16, device, group) for _ in range(2)]
         self.world, self.rank = self.bufs[0].world, self.bufs[0].rank
-        self._pads = (ctypes.c_void_p * self.world)(*self.bufs[0].pad_ptrs)
-        self._pad_base = self.bufs[0].pad_words - 48
-        self._counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self._barrier = _SymmBarrier(self.bufs[0], 48, self.device)
         self._which = 0
-        self._stage = self._side = None
         torch.cuda.synchronize(self.device)
         import torch.distributed as dist
 
         dist.barrier(group=group)
 
-    def shard(self, rows: int) -> torch.Tensor:
-        assert rows <= self.max_rows and rows % 128 == 0, f"{rows} rows per rank: need a multiple of 128 up to {self.max_rows}"
-        return self.bufs[self._which].tensor[: rows * self.k].view(rows, self.k)
+    def fits(self, rows: int, k: int) -> bool:
+        return k == self.k and rows <= self.max_rows and rows % 128 == 0
 
-    def _barrier(self):
-        lib, P = self._lib.lib(), self._lib.ptr
-        rc = lib.sb_symm_barrier_dev(self._pads, self.rank, self.world, P(self._counter), self._pad_base,
-                                     P(self._lib.status_word(self.device)), self._lib.stream())  # fmt: skip
-        self._lib.check(rc, "sb_symm_barrier_dev")
-
-    def __call__(self, rows: int, weight: torch.Tensor, bias=None, out_dtype=torch.bfloat16, mode: str | None = None):
-        """``mode="direct"``: one GEMM whose TMA loads read remote row tiles from the owning GPU every time they are
-        needed (each remote tile crosses NVLink once per column tile of the output: right for narrow outputs).
-        ``mode="staged"``: the own shard is multiplied first while the copy engines pull the peers' shards into local
-        memory on a side stream; each peer's rows are multiplied as soon as its copy has landed (every remote byte crosses
-        NVLink once). Default: staged. Measured on 2 GPUs, M 8192, K 2560: N 3072: NCCL all-gather + GEMM 167 us, staged
-        130 us, direct 447 us (the GEMM alone: 100 us); N 256: NCCL path 88 us, direct 89 us."""
-        from slime_b200 import ops
+    def __call__(self, x_local: torch.Tensor, weight: torch.Tensor, bias=None, b_mn: bool = False):
+        """``x_local`` [rows, K] bf16 -> (``[world * rows, N]`` bf16, gathered ``[world * rows, K]``). ``weight`` is
+        [N, K] (``b_mn`` False) or [K, N] (``b_mn`` True: the product is with the transpose-free stored matrix)."""
         from slime_b200.ops import _pick_bn
 
         lib, P = self._lib.lib(), self._lib.ptr
+        rows, k = x_local.shape
+        assert self.fits(rows, k), f"shard [{rows}, {k}] does not fit (max rows {self.max_rows}, K {self.k}, rows % 128)"
         buf = self.bufs[self._which]
-        self._barrier()  # every rank's shard is complete
-        n = weight.shape[0]
+        buf.tensor[: rows * k].view(rows, k).copy_(x_local)
         m = rows * self.world
-        out = torch.empty(m, n, dtype=out_dtype, device=self.device)
-        mode = mode or "staged"
-        if mode == "direct":
-            ptrs = (ctypes.c_void_p * self.world)(*buf.ptrs)
-            rc = lib.sb_gemm_bf16_allgather_a(ptrs, self.world, rows, P(weight), P(out), P(bias), n, self.k, self.k,
-                                              weight.stride(0), out.stride(0), int(out_dtype == torch.float32), _pick_bn(m, n),
-                                              P(self._lib.status_word(self.device)), self._lib.sm_count(self.device),
-                                              self._lib.stream())  # fmt: skip
-            self._lib.check(rc, "sb_gemm_bf16_allgather_a")
-        else:
-            if self._stage is None or self._stage.shape[0] < m:
-                self._stage = torch.empty(self.max_rows * self.world, self.k, dtype=torch.bfloat16, device=self.device)
-                self._side = torch.cuda.Stream(device=self.device)
-            main = torch.cuda.current_stream(self.device)
-            self._side.wait_stream(main)  # after the barrier
-            events = {}
-            with torch.cuda.stream(self._side):
-                for step in range(1, self.world):  # nearest peers first, a different peer per rank at every step
-                    p = (self.rank + step) % self.world
-                    src = buf.handle.get_buffer(p, (rows, self.k), torch.bfloat16)
-                    self._stage[p * rows : (p + 1) * rows].copy_(src, non_blocking=True)
-                    events[p] = torch.cuda.Event()
-                    events[p].record(self._side)
-            own = buf.tensor[: rows * self.k].view(rows, self.k)
-            ops.gemm(own, weight, bias=bias, out=out[self.rank * rows : (self.rank + 1) * rows])
-            for step in range(1, self.world):
-                p = (self.rank + step) % self.world
-                main.wait_event(events[p])
-                ops.gemm(self._stage[p * rows : (p + 1) * rows], weight, bias=bias, out=out[p * rows : (p + 1) * rows])
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        gathered = torch.empty(m, k, dtype=torch.bfloat16, device=self.device)
+        gathered[self.rank * rows : (self.rank + 1) * rows].copy_(x_local)
+        counters = torch.zeros(m // 128, dtype=torch.int32, device=self.device)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=self.device)
+        self._barrier()  # every rank's shard is complete
+        peers = (ctypes.c_void_p * self.world)(*buf.ptrs)
+        fn = self._lib.bind("sb_gemm_bf16_gather_a", [self._lib.P, self._lib.I, self._lib.I, self._lib.I, self._lib.P, self._lib.P,
+                                                      ctypes.c_uint, self._lib.P, self._lib.P, self._lib.P] + [self._lib.I] * 6
+                            + [self._lib.P, self._lib.I, self._lib.P])  # fmt: skip
+        rc = fn(peers, self.world, self.rank, rows, P(gathered), P(counters), 128 // 4, P(weight), P(out), P(bias), n, k,
+                weight.stride(0), out.stride(0), int(b_mn), _pick_bn(m, n), P(self._lib.status_word(self.device)),
+                self._lib.sm_count(self.device), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_gemm_bf16_gather_a")
+        self._which ^= 1
+        return out, gathered
+
+
+class GemmReduceScatter:
+    """GEMM fused with the reduce-scatter of its output rows (``ScatterC`` in ``csrc/gemm_sm100.cu``).
+
+    Sequence-parallel row-parallel linears (attention output, MLP down) and the input-gradient GEMM of column-parallel
+    ones produce a full ``[M, N]`` partial product on every rank, of which rank ``o`` needs the sum of rows
+    ``[o * M / n, (o + 1) * M / n)``. The kernel's epilogue stores every tile straight into the owning rank's receive
+    buffer (TMA stores over NVLink for the peers' tiles, which are computed first) and, once its share of the GEMM is
+    done, sums the slots of the tiles it owns as their flags arrive. One launch, no NCCL, rank-order summation.
+    Two receive buffers alternate: a rank may be one call ahead of its peers, never two (it needs their tiles to finish).
+    """
+
+    def __init__(self, group, max_rows_per_rank: int, n: int, device):
+        from slime_b200.ops import _lib
+
+        self._lib = _lib
+        self.n, self.max_rows, self.device = n, max_rows_per_rank, torch.device(device)
+        probe = SymmetricStorage(8, torch.int32, device, group)
+        self.world, self.rank = probe.world, probe.rank
+        self.recv = [SymmetricStorage(self.world * max_rows_per_rank * n, torch.bfloat16, device, group) for _ in range(2)]
+        nflags = (max_rows_per_rank // 128) * (-(-n // 128)) * self.world * 4
+        self.flags = [SymmetricStorage(nflags, torch.int32, device, group) for _ in range(2)]
+        self.epochs = [0, 0]
+        self._which = 0
+        torch.cuda.synchronize(self.device)
+        import torch.distributed as dist
+
+        dist.barrier(group=group)  # every rank's flags are zero before anyone raises one
+
+    def fits(self, m: int, n: int) -> bool:
+        return n == self.n and m % (self.world * 128) == 0 and m // self.world <= self.max_rows
+
+    def __call__(self, a: torch.Tensor, weight: torch.Tensor, b_mn: bool = False):
+        """``a`` [M, K] bf16, ``weight`` [N, K] (or [K, N] with ``b_mn``) -> this rank's ``[M / world, N]`` bf16 rows of the
+        sum over ranks of ``a @ op(weight)``."""
+        from slime_b200.ops import _pick_bn
+
+        lib, P = self._lib.lib(), self._lib.ptr
+        m, k = a.shape
+        n = weight.shape[1] if b_mn else weight.shape[0]
+        assert self.fits(m, n), f"product [{m}, {n}] does not fit (max rows per rank {self.max_rows}, N {self.n})"
+        if a.stride(-1) != 1 or a.stride(0) % 8:
+            a = a.contiguous()
+        w = self._which
+        self.epochs[w] += 1
+        out = torch.empty(m // self.world, n, dtype=torch.bfloat16, device=self.device)
+        recv = (ctypes.c_void_p * self.world)(*self.recv[w].ptrs)
+        flags = (ctypes.c_void_p * self.world)(*self.flags[w].ptrs)
+        fn = self._lib.bind("sb_gemm_bf16_scatter_c", [self._lib.P, self._lib.P] + [self._lib.I] * 6 + [self._lib.P, self._lib.P,
+                                                       self._lib.I, self._lib.I, self._lib.P, self._lib.I, ctypes.c_uint, self._lib.I,
+                                                       self._lib.P, self._lib.I, self._lib.P])  # fmt: skip
+        rc = fn(P(a), P(weight), m, n, k, a.stride(0), weight.stride(0), int(b_mn), recv, flags, self.world, self.rank, P(out),
+                out.stride(0), self.epochs[w], _pick_bn(m, n), P(self._lib.status_word(self.device)),
+                self._lib.sm_count(self.device), self._lib.stream())  # fmt: skip
+        self._lib.check(rc, "sb_gemm_bf16_scatter_c")
         self._which ^= 1
         return out
+
+
+class FusedSequenceParallelLinears:
+    """The two fused collectives a sequence-parallel transformer layer needs, shared by every layer of a model (all
+    gathered operands and scattered products have ``hidden`` columns), with their autograd rules:
+
+        column(x_local, W, b)   = gather(x) @ W^T + b        backward: dx = reduce_scatter(dy @ W), dW += dy^T gather(x)
+        row(x, W)               = reduce_scatter(x @ W^T)     backward: dx = gather(dy) @ W,        dW += gather(dy)^T x
+    """
+
+    def __init__(self, group, max_tokens: int, hidden: int, device):
+        import torch.distributed as dist
+
+        world = dist.get_world_size(group)
+        rows = -(-(max_tokens + world * 128) // (world * 128)) * 128
+        self.ag = GatherGemm(group, rows, hidden, device)
+        self.rs = GemmReduceScatter(group, rows, hidden, device)
+        self.world = world
+
+    def fits(self, rows_local: int, hidden: int) -> bool:
+        return self.ag.fits(rows_local, hidden) and self.rs.fits(rows_local * self.world, hidden)
+
+    def column(self, x_local, weight, bias=None):
+        return _FusedColumn.apply(x_local, weight, bias, self)
+
+    def row(self, x, weight):
+        return _FusedRow.apply(x, weight, self)
+
+
+def _wgrad(dy, x, weight):
+    """dW += dy^T x, straight into the fp32 main-grad buffer when the parameter has one."""
+    from slime_b200 import ops
+
+    main_grad = getattr(weight, "main_grad", None)
+    if main_grad is not None:
+        ops.gemm(dy, x, a_mn=True, b_mn=True, out=main_grad, accumulate=True)
+        weight.grad_added_to_main_grad = True
+        return None
+    return ops.gemm(dy, x, a_mn=True, b_mn=True, out_dtype=weight.dtype)
+
+
+class _FusedColumn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x_local, weight, bias, fused):
+        y, gathered = fused.ag(x_local, weight, bias)
+        ctx.save_for_backward(gathered, weight)
+        ctx.fused, ctx.has_bias = fused, bias is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        gathered, weight = ctx.saved_tensors
+        dy = dy if dy.stride(-1) == 1 and dy.stride(0) % 8 == 0 else dy.contiguous()
+        dx = ctx.fused.rs(dy, weight, b_mn=True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(dy, gathered, weight) if ctx.needs_input_grad[1] else None
+        db = dy.float().sum(0).to(dy.dtype) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        return dx, dw, db, None
+
+
+class _FusedRow(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, fused):
+        ctx.save_for_backward(x, weight)
+        ctx.fused = fused
+        return fused.rs(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        x, weight = ctx.saved_tensors
+        dx, dy = ctx.fused.ag(dy_local.contiguous(), weight, None, b_mn=True)
+        dw = _wgrad(dy, x, weight) if ctx.needs_input_grad[1] else None
+        return (dx if ctx.needs_input_grad[0] else None), dw, None
+
+
+_LINEARS: dict = {}
+_MAX_TOKENS = 16384  # capacity (packed tokens of a micro-batch) the shared buffers are sized for
+
+
+def set_max_tokens(n: int) -> None:
+    """Called by the trainer with ``--max-tokens-per-gpu`` before the first forward pass."""
+    global _MAX_TOKENS
+    _MAX_TOKENS = max(int(n), 256)
+
+
+def sequence_parallel_linears(group, hidden: int, device, max_tokens: int | None = None):
+    """The shared ``FusedSequenceParallelLinears`` of a tensor-parallel group (created on first use), or None where the
+    fused path does not exist (CPU, one rank, no symmetric memory, SLIME_B200_DISABLE_FUSED_TP=1)."""
+    import torch.distributed as dist
+
+    if group is None or torch.device(device).type != "cuda" or not usable(dist.get_world_size(group), device, hidden):
+        return None
+    if os.environ.get("SLIME_B200_DISABLE_FUSED_TP_LINEAR") == "1":
+        return None
+    max_tokens = max_tokens or _MAX_TOKENS
+    key = (id(group), hidden, torch.device(device).index)
+    cur = _LINEARS.get(key)
+    if cur is None or cur.ag.max_rows * cur.world < max_tokens:
+        try:
+            cur = FusedSequenceParallelLinears(group, max_tokens, hidden, device)
+        except Exception as e:  # noqa: BLE001
+            logger.warning("fused sequence-parallel linears unavailable (%r): using NCCL", e)
+            return None
+        _LINEARS[key] = cur
+    return cur

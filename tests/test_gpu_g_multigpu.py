@@ -60,8 +60,25 @@ def test_tensor_parallel_engine_matches_single_gpu(kernels):
     assert r.returncode == 0 and "RESULT ok" in r.stdout and "fused_tp=True" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
 
 
-def test_allgather_fused_gemm_matches_nccl_path(kernels):
+def test_fused_sequence_parallel_linears_match_nccl_path(kernels):
+    """All-gather -> GEMM and GEMM -> reduce-scatter as single kernels, forward and backward, against NCCL + GEMM."""
     _need(2)
-    n = min(torch.cuda.device_count(), 8)
-    r = _torchrun("tests/multigpu/ag_gemm_check.py", n, timeout=240)
+    n = 2 if torch.cuda.device_count() < 4 else 4
+    r = _torchrun("tests/multigpu/fused_linear_check.py", n, timeout=300)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("mode", ["tp_sp", "cp"])
+def test_trainer_model_parallel_parity_on_gpus(kernels, mode):
+    """The trainer model under TP2 + SP (fused linears, own attention kernels) and under CP2 against the fp32 oracle."""
+    _need(2)
+    r = _torchrun("tests/multigpu/model_parallel_check.py", 2, {"MODE": mode, "DEVICE": "cuda"}, timeout=300)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_colocated_grpo_with_tensor_parallel_engine(kernels):
+    """Two GRPO steps with trainer and rollout engine both TP2 over the same ranks (fused decode all-reduce, fused
+    linears, shard-to-shard weight sync)."""
+    _need(2)
+    r = _torchrun("tests/multigpu/colocated_tp_check.py", 2, {"DEVICE": "cuda"}, timeout=300)
     assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
