@@ -145,6 +145,8 @@ class TrainActor:
         from slime_b200.runtime import memory
 
         memory.offload_train_state(self.model)
+        if getattr(self.args, "release_communicators_on_sleep", False):
+            mpu.release_communicators()  # NCCL buffers go too; rebuilt in wake_up
         self.asleep = True
 
     def wake_up(self):
@@ -152,6 +154,7 @@ class TrainActor:
             return
         from slime_b200.runtime import memory
 
+        mpu.reload_communicators()  # no-op unless they were released
         memory.onload_train_state(self.model)
         self.asleep = False
 

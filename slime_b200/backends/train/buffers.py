@@ -23,7 +23,10 @@ class FlatBuffer:
     def __init__(self, params: list[torch.nn.Parameter], names: list[str], group, group_size: int, group_rank: int,
                  device, grad_dtype=torch.float32, allocator=None, symmetric=False):  # fmt: skip
         self.params, self.names = params, names
-        self.group, self.group_size, self.group_rank = group, group_size, group_rank
+        # `group` may be a getter: communicators can be released and rebuilt between phases (parallel/state.py), so the
+        # handle is looked up at every use instead of being cached
+        self._group = group
+        self.group_size, self.group_rank = group_size, group_rank
         self.offsets: list[tuple[int, int]] = []
         off = 0
         for p in params:
@@ -40,8 +43,8 @@ class FlatBuffer:
         if symmetric and grad_dtype == torch.float32:
             from slime_b200.parallel.fused_dp import FusedDataParallel, SymmetricStorage
 
-            self.param_store = SymmetricStorage(self.numel, dtype, device, group)
-            self.grad_store = SymmetricStorage(self.numel, grad_dtype, device, group)
+            self.param_store = SymmetricStorage(self.numel, dtype, device, self.group)
+            self.grad_store = SymmetricStorage(self.numel, grad_dtype, device, self.group)
             self.param_data, self.grad_data = self.param_store.tensor, self.grad_store.tensor
             self.fused = FusedDataParallel.__new__(FusedDataParallel)  # finished below, once the views exist
         else:
@@ -55,6 +58,11 @@ class FlatBuffer:
             p.grad_added_to_main_grad = False
         if self.fused is not None:
             self.fused.__init__(self)
+
+    @property
+    def group(self):
+        g = self._group
+        return g() if callable(g) else g
 
     # ---- shard views ----------------------------------------------------------------
     def shard_range(self, rank: int | None = None) -> tuple[int, int]:

@@ -105,13 +105,13 @@ class TrainModel:
         symmetric = (symmetric_memory_usable(dp, self.device) and mpu.get_pipeline_model_parallel_world_size() == 1
                      and not getattr(self.args, "offload_train", False) and not getattr(self.args, "optimizer_cpu_offload", False)
                      and getattr(self.args, "fused_dp_step", True))  # fmt: skip
-        self.dense_buffer = FlatBuffer(dense, dense_names, mpu.get_data_parallel_group(with_context_parallel=True), dp,
+        self.dense_buffer = FlatBuffer(dense, dense_names, lambda: mpu.get_data_parallel_group(with_context_parallel=True), dp,
                                        mpu.get_data_parallel_rank(with_context_parallel=True), self.device, allocator=alloc,
                                        symmetric=symmetric)  # fmt: skip
         self.buffers.append(self.dense_buffer)
         self.expert_buffer = None
         if expert:
-            self.expert_buffer = FlatBuffer(expert, expert_names, mpu.get_expert_data_parallel_group(),
+            self.expert_buffer = FlatBuffer(expert, expert_names, mpu.get_expert_data_parallel_group,
                                             mpu.get_expert_data_parallel_world_size(), mpu.get_expert_data_parallel_rank(),
                                             self.device, allocator=alloc)  # fmt: skip
             self.buffers.append(self.expert_buffer)

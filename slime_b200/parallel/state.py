@@ -112,6 +112,12 @@ def initialize_model_parallel(
     """Create every process group. Must be called by all ranks in the same order."""
     st = _STATE
     st.reset()
+    st.layout_args = dict(
+        tensor_model_parallel_size=tensor_model_parallel_size, pipeline_model_parallel_size=pipeline_model_parallel_size,
+        virtual_pipeline_model_parallel_size=virtual_pipeline_model_parallel_size, context_parallel_size=context_parallel_size,
+        expert_model_parallel_size=expert_model_parallel_size, expert_tensor_parallel_size=expert_tensor_parallel_size,
+        backend=backend, timeout=timeout,
+    )  # fmt: skip
     if not dist.is_available() or not dist.is_initialized():
         assert (
             tensor_model_parallel_size * pipeline_model_parallel_size * context_parallel_size == 1
@@ -165,6 +171,64 @@ def initialize_model_parallel(
     st.virtual_pp_rank = 0 if virtual_pipeline_model_parallel_size else None
     st.initialized = True
     return st
+
+
+# ---- reloadable communicators ------------------------------------------------------------------------------
+# In colocated mode the trainer sleeps while the rollout engine owns the GPU. NCCL communicators of a large layout hold
+# gigabytes of buffers (the reference measures > 10 GB, docs/en/blogs/release_v0.1.0.md:92), so they are torn down for
+# the rollout phase and rebuilt at wake-up. Because every group in this package is fetched through the getters below
+# (nothing caches a handle: buffers take a getter, not a group), this needs no patching of torch.distributed as in the
+# reference (slime/utils/reloadable_process_group.py:145-270): release destroys WORLD (which shuts down every subgroup in
+# one global order, the only order that cannot deadlock pipeline ranks with overlapping subgroups), keeps the rendezvous
+# store alive, and leaves a gloo WORLD on a fresh PrefixStore namespace for host-side coordination; reload replaces
+# it by a device WORLD on the next namespace and recreates every subgroup from the remembered layout.
+def communicators_released() -> bool:
+    return getattr(_STATE, "released", False)
+
+
+def release_communicators() -> bool:
+    """Destroy every device communicator of this process. Topology queries (sizes, ranks, rank lists) keep working;
+    group getters return None until ``reload_communicators``. Returns False when there was nothing to release."""
+    from torch.distributed.distributed_c10d import PrefixStore, _get_default_store
+
+    st = _STATE
+    if not (dist.is_available() and dist.is_initialized()) or communicators_released():
+        return False
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    info = getattr(st, "world_info", None)
+    if info is None:
+        info = st.world_info = dict(backend=str(dist.get_backend()), store=_get_default_store(), rank=dist.get_rank(),
+                                    world=dist.get_world_size(), generation=0)  # fmt: skip
+    dist.barrier()
+    dist.destroy_process_group()  # WORLD and, with it, every subgroup
+    for a in ParallelState.AXES:
+        ax = getattr(st, a)
+        ax.group = ax.gloo_group = None
+    info["generation"] += 1
+    dist.init_process_group("gloo", store=PrefixStore(f"slime-b200-world-{info['generation']}-gloo", info["store"]),
+                            rank=info["rank"], world_size=info["world"])  # fmt: skip
+    st.released = True
+    return True
+
+
+def reload_communicators() -> bool:
+    """Inverse of ``release_communicators``: device WORLD and every subgroup are recreated with the same ranks."""
+    from torch.distributed.distributed_c10d import PrefixStore
+
+    st = _STATE
+    if not communicators_released():
+        return False
+    info, layout, vpp_rank = st.world_info, dict(st.layout_args), st.virtual_pp_rank
+    dist.barrier()  # still the temporary gloo WORLD: no device communicator is created before every rank is here
+    dist.destroy_process_group()
+    info["generation"] += 1
+    kw = {"timeout": layout["timeout"]} if layout.get("timeout") is not None else {}
+    dist.init_process_group(info["backend"], store=PrefixStore(f"slime-b200-world-{info['generation']}", info["store"]),
+                            rank=info["rank"], world_size=info["world"], **kw)  # fmt: skip
+    initialize_model_parallel(**layout)
+    _STATE.world_info, _STATE.virtual_pp_rank, _STATE.released = info, vpp_rank, False
+    return True
 
 
 def destroy_model_parallel():

@@ -41,6 +41,7 @@ _CLUSTER = [
     _f("--rollout-num-gpus", type=int, default=None), _f("--rollout-num-gpus-per-engine", type=int, default=1),
     _f("--num-gpus-per-node", type=int, default=8), _f("--colocate", action=_T), _f("--offload", action=_T),
     _f("--offload-train", action=B, default=None), _f("--offload-rollout", action=B, default=None),
+    _f("--release-communicators-on-sleep", action=B, default=False),
 ]
 _TRAIN = [
     _f("--train-backend", type=str, choices=["megatron", "b200"], default="megatron"),

@@ -118,11 +118,47 @@ def check_tp(rank, world):
         torch.testing.assert_close(local.grad, ref_logits.grad[:, rank * vl : (rank + 1) * vl], rtol=1e-4, atol=1e-5)
 
 
+def check_reload(rank, world):
+    """Communicators are destroyed and rebuilt: topology queries survive, collectives work again on the new groups,
+    a buffer that was handed a group getter follows, and repeated cycles do not collide in the rendezvous store."""
+    from slime_b200.backends.train.buffers import FlatBuffer
+    from slime_b200.parallel import state as mpu
+
+    tp = 2
+    mpu.initialize_model_parallel(tensor_model_parallel_size=tp, backend="gloo")
+    dp = world // tp
+    p = torch.nn.Parameter(torch.zeros(256, dtype=torch.bfloat16))
+    buf = FlatBuffer([p], ["p"], mpu.get_data_parallel_group, dp, mpu.get_data_parallel_rank(), torch.device("cpu"))
+
+    def exercise(tag):
+        t = torch.tensor([float(rank + 1)])
+        dist.all_reduce(t, group=mpu.get_tensor_model_parallel_group())
+        base = (rank // tp) * tp
+        assert float(t) == sum(base + i + 1 for i in range(tp)), (tag, float(t))
+        buf.grad_data.fill_(1.0)
+        buf.all_reduce_grads()
+        assert float(buf.grad_data[0]) == dp, (tag, float(buf.grad_data[0]))
+
+    exercise("before")
+    for cycle in range(2):
+        assert mpu.release_communicators()
+        assert mpu.communicators_released() and mpu.get_tensor_model_parallel_group() is None
+        assert mpu.get_tensor_model_parallel_world_size() == tp and mpu.get_data_parallel_world_size() == dp
+        assert mpu.get_tensor_model_parallel_rank() == rank % tp
+        t = torch.ones(1)
+        dist.all_reduce(t)  # the temporary host-side WORLD
+        assert float(t) == world
+        assert not mpu.release_communicators()  # idempotent
+        assert mpu.reload_communicators()
+        exercise(f"cycle {cycle}")
+    assert not mpu.reload_communicators()
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
     mode = os.environ.get("MODE", "cp")
-    {"cp": check_cp, "dp": check_dp, "tp": check_tp}[mode](rank, world)
+    {"cp": check_cp, "dp": check_dp, "tp": check_tp, "reload": check_reload}[mode](rank, world)
     dist.barrier()
     if rank == 0:
         print(f"RESULT ok mode={mode} world={world}", flush=True)

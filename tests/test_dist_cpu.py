@@ -9,7 +9,7 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("mode,world,port", [("cp", 2, 29681), ("cp", 4, 29682), ("dp", 2, 29683), ("dp", 3, 29684), ("tp", 2, 29685)])
+@pytest.mark.parametrize("mode,world,port", [("cp", 2, 29681), ("cp", 4, 29682), ("dp", 2, 29683), ("dp", 3, 29684), ("tp", 2, 29685), ("reload", 4, 29686)])
 def test_invariants(mode, world, port):
     env = dict(os.environ, MODE=mode, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
