@@ -154,11 +154,48 @@ def check_reload(rank, world):
     assert not mpu.reload_communicators()
 
 
+def check_expert_route(rank, world):
+    """An expert-parallel trainer model (EP = world) ships each routed expert to the rank whose engine shard hosts it
+    (here the shards are rotated by one rank, so every tensor crosses)."""
+    from slime_b200.backends.train.model import TrainModel
+    from slime_b200.models.config import ModelConfig, apply_to_args
+    from slime_b200.parallel import state as mpu
+    from slime_b200.utils.arguments import namespace_from_dict
+    from slime_b200.weight_sync import expert_routing as er
+
+    mpu.initialize_model_parallel(expert_model_parallel_size=world, expert_tensor_parallel_size=1, backend="gloo")
+    cfg = ModelConfig(num_layers=2, hidden_size=32, num_attention_heads=2, num_query_groups=2, kv_channels=16, ffn_hidden_size=64,
+                      vocab_size=64, num_experts=4, moe_ffn_hidden_size=16, moe_router_topk=2, tie_word_embeddings=False)
+    args = namespace_from_dict(dict(expert_model_parallel_size=world, bf16=False, seed=rank + 5, untie_embeddings_and_output_weights=True))
+    apply_to_args(cfg, args)
+    model = TrainModel(args, device=torch.device("cpu"), with_optimizer=False)
+    tensors = er.collect_expert_tensors(model)
+    assert len(tensors) == 2 * 4 * 2  # layers x experts x (fc1, fc2), each listed once with its global expert id
+    targets = [((s + 1) % world,) for s in range(world)]  # engine shard s lives on rank s + 1
+    rounds = er.plan_expert_transfers(tensors, cfg.num_experts, targets, buffer_size=1 << 20)
+    from slime_b200.backends.train.checkpoint import global_param_name
+
+    local = {global_param_name(n, p): p.detach() for n, p in model.named_parameters() if getattr(p, "is_expert", False)}
+    received = {}
+    for rnd in rounds:
+        er.run_round(rnd, rank, local.__getitem__, received.__setitem__)
+    per = cfg.num_experts // world
+    mine = [t for t in tensors if targets[t.layer_expert[1] // per][0] == rank]
+    assert sorted(received) == sorted(t.name for t in mine)
+    # values: the sender's tensors were drawn from a rank-dependent seed; compare checksums through an all-gather
+    sums = {n: float(v.double().sum()) for n, v in local.items()}
+    everyone = [None] * world
+    dist.all_gather_object(everyone, sums)
+    truth = {k: v for part in everyone for k, v in part.items()}
+    for n, v in received.items():
+        assert abs(float(v.double().sum()) - truth[n]) < 1e-9, n
+
+
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     dist.init_process_group("gloo")
     mode = os.environ.get("MODE", "cp")
-    {"cp": check_cp, "dp": check_dp, "tp": check_tp, "reload": check_reload}[mode](rank, world)
+    {"cp": check_cp, "dp": check_dp, "tp": check_tp, "reload": check_reload, "expert_route": check_expert_route}[mode](rank, world)
     dist.barrier()
     if rank == 0:
         print(f"RESULT ok mode={mode} world={world}", flush=True)
