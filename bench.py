@@ -59,7 +59,7 @@ def parse():
     p.add_argument("--max-response", type=int, default=None)
     p.add_argument("--max-tokens-per-gpu", type=int, default=None)
     p.add_argument("--tp", type=int, default=None, help="tensor-parallel size of trainer and engines (config default)")
-    p.add_argument("--recompute", type=str, default=None, choices=["full", "none"])
+    p.add_argument("--recompute", type=str, default=None, choices=["full", "none", "auto"])
     p.add_argument("--e2e-steps", type=int, default=None, help="steps of the end-to-end arm (default: --steps)")
     p.add_argument("--no-e2e", action="store_true")
     a = p.parse_args()
@@ -72,8 +72,10 @@ def parse():
 CONFIGS = {
     "qwen2.5-0.5b": dict(model="qwen2.5-0.5b", prompts_per_gpu=32, prompt_len=256, min_response=128, max_response=1024,
                          max_tokens_per_gpu=16384, tp=1, recompute="none", mem_fraction=0.45),
+    # recompute: "auto" = none under TP2 (a 9216-token micro-batch keeps ~22 GB of activations per rank, which 180 GB
+    # holds next to the trainer state and the KV pool), full on a single GPU where the whole optimizer state is local
     "qwen3-4b": dict(model="qwen3-4b", prompts_per_gpu=8, prompt_len=512, min_response=1024, max_response=8192,
-                     max_tokens_per_gpu=9216, tp=2, recompute="full", mem_fraction=0.8),
+                     max_tokens_per_gpu=9216, tp=2, recompute="auto", mem_fraction=0.72),
 }  # fmt: skip
 
 
@@ -184,6 +186,8 @@ def main():
     from slime_b200.parallel import state as mpu
 
     tp = min(a.tp, world)
+    if a.recompute == "auto":
+        a.recompute = "none" if tp > 1 else "full"
     assert world % tp == 0, f"{world} GPUs do not split into tensor-parallel groups of {tp}"
     mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
     args = build_args(a, world, tp)

@@ -55,8 +55,8 @@ __device__ __forceinline__ void tile_origin(int tile, int tiles_m, int tiles_n, 
 // Optional extra kernel parameter: a collective fused into the GEMM over NVLink peer memory (no multicast loads).
 //
 // GatherA (all-gather -> GEMM, sequence-parallel column linear): the rows of A are spread over up to 8 GPUs, rank r
-// holding rows [r * rows_per_rank, (r + 1) * rows_per_rank) in a buffer every rank can read. A seventh warp in every CTA
-// pulls the peers' shards ONCE into this GPU's `gathered` buffer (plain 16-byte loads from peer memory, 4-row pieces
+// holding rows [r * rows_per_rank, (r + 1) * rows_per_rank) in a buffer every rank can read. Four extra warps in every CTA
+// pull the peers' shards ONCE into this GPU's `gathered` buffer (plain 16-byte loads from peer memory, 4-row pieces
 // striped over the CTAs, nearest peer first) and counts the pieces of each 128-row block; the tile order starts with the
 // rank's own rows, and the TMA producer waits (bounded) for a remote block's counter before it loads tiles of that
 // block from LOCAL memory. Every remote byte crosses NVLink once, under the GEMM of the rows that are already there,
@@ -92,6 +92,7 @@ struct ScatterC {
   unsigned long long limit_ns;
 };
 constexpr int GATHER_PIECE_ROWS = 4;
+constexpr int GATHER_WARPS = 4;  // per CTA: enough 16-byte loads in flight over NVLink to run at link rate
 
 __device__ __forceinline__ void st_release_sys_u32(uint32_t* addr, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
@@ -123,7 +124,7 @@ __device__ __forceinline__ void tile_origin_rot(int tile, int tiles_m, int tiles
 }
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, bool OUT_F32, bool TMA_EPI, typename Extra = NoExtra>
-__global__ void __launch_bounds__(GEMM_THREADS + 32, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + 32 * GATHER_WARPS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, void* __restrict__ Cv, const __nv_bfloat16* __restrict__ bias,
                  int M, int N, int K, int ldc, int accumulate, int* status, const int* __restrict__ tile_boff,
@@ -389,6 +390,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           buf ^= 1;
         }
         if constexpr (Extra::kMode == 2) {
+          // the accumulator has been drained into the staging buffers: hand it back before waiting for the stores
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tempty[acc]);
           // this warp's 32 rows of the tile are on their way: once the stores have completed, tell the owner
           if (lane == 0) {
             bulk_wait_group_all();
@@ -427,9 +432,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
+      if constexpr (Extra::kMode != 2) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+      }
       if (++acc == 2) {
         acc = 0;
         acc_phase ^= 1;
@@ -466,33 +473,50 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int row_base = (t / tiles_n) * GEMM_BM + q * 32;
         const int col = (t % tiles_n) * BN + (lane % VEC) * 8;
         if (col < N) {
-          for (int rr = lane / VEC; rr < 32; rr += RPI) {
-            const int row = row_base + rr;
-            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          constexpr int UNR = 4;  // rows in flight per lane
+          for (int rr0 = lane / VEC; rr0 < 32; rr0 += RPI * UNR) {
+            float acc[UNR][8];
+#pragma unroll
+            for (int j = 0; j < UNR; ++j)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
             for (int r = 0; r < extra.world; ++r) {
-              const uint4 u = *reinterpret_cast<const uint4*>(extra.recv + (static_cast<size_t>(r) * extra.rows_per_rank + row) * N + col);
-              const float2 a0 = unpack_bf16x2(u.x), a1 = unpack_bf16x2(u.y), a2 = unpack_bf16x2(u.z), a3 = unpack_bf16x2(u.w);
-              acc[0] += a0.x; acc[1] += a0.y; acc[2] += a1.x; acc[3] += a1.y;
-              acc[4] += a2.x; acc[5] += a2.y; acc[6] += a3.x; acc[7] += a3.y;
+              uint4 u[UNR];
+#pragma unroll
+              for (int j = 0; j < UNR; ++j) {
+                const int row = row_base + rr0 + j * RPI;
+                u[j] = (rr0 + j * RPI < 32) ? *reinterpret_cast<const uint4*>(extra.recv + (static_cast<size_t>(r) * extra.rows_per_rank + row) * N + col)
+                                            : make_uint4(0, 0, 0, 0);
+              }
+#pragma unroll
+              for (int j = 0; j < UNR; ++j) {
+                const float2 a0 = unpack_bf16x2(u[j].x), a1 = unpack_bf16x2(u[j].y), a2 = unpack_bf16x2(u[j].z), a3 = unpack_bf16x2(u[j].w);
+                acc[j][0] += a0.x; acc[j][1] += a0.y; acc[j][2] += a1.x; acc[j][3] += a1.y;
+                acc[j][4] += a2.x; acc[j][5] += a2.y; acc[j][6] += a3.x; acc[j][7] += a3.y;
+              }
             }
-            uint4 o;
-            o.x = pack_bf16x2(acc[0], acc[1]);
-            o.y = pack_bf16x2(acc[2], acc[3]);
-            o.z = pack_bf16x2(acc[4], acc[5]);
-            o.w = pack_bf16x2(acc[6], acc[7]);
-            *reinterpret_cast<uint4*>(extra.out + static_cast<size_t>(row) * extra.ld_out + col) = o;
+#pragma unroll
+            for (int j = 0; j < UNR; ++j) {
+              if (rr0 + j * RPI >= 32) break;
+              uint4 o;
+              o.x = pack_bf16x2(acc[j][0], acc[j][1]);
+              o.y = pack_bf16x2(acc[j][2], acc[j][3]);
+              o.z = pack_bf16x2(acc[j][4], acc[j][5]);
+              o.w = pack_bf16x2(acc[j][6], acc[j][7]);
+              *reinterpret_cast<uint4*>(extra.out + static_cast<size_t>(row_base + rr0 + j * RPI) * extra.ld_out + col) = o;
+            }
           }
         }
       }
     }
   }
   if constexpr (Extra::kMode == 1) {
-    if (warp == 6) {
-      // ---------------------------------------------------- gather warp: pull the peers' shards into `gathered`
+    if (warp >= 6) {
+      // ---------------------------------------------------- gather warps: pull the peers' shards into `gathered`
       const int per_shard = extra.rows_per_rank / GATHER_PIECE_ROWS;
       const int total = (extra.world - 1) * per_shard;
       const int n16 = GATHER_PIECE_ROWS * extra.row_bytes / 16;  // 16-byte vectors per piece (rows are contiguous)
-      for (int p = blockIdx.x; p < total; p += gridDim.x) {
+      for (int p = blockIdx.x * GATHER_WARPS + (warp - 6); p < total; p += gridDim.x * GATHER_WARPS) {
         const int s = p / per_shard, piece = p - s * per_shard;
         const int src = (extra.rank + 1 + s) % extra.world;  // nearest peer first: the order the tiles are walked in
         const size_t row0 = static_cast<size_t>(piece) * GATHER_PIECE_ROWS;
@@ -560,7 +584,7 @@ static cudaError_t launch_gemm(const void* A, const void* B, void* C, const void
   const int tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN) * splitk;
   int grid = tiles < num_sms ? tiles : num_sms;
   if (Extra::kMode != 0) grid = num_sms;  // the collective's own work (gather pieces, owned tiles) is striped over every CTA
-  constexpr int threads = Extra::kMode == 1 ? GEMM_THREADS + 32 : GEMM_THREADS;  // + the gather warp
+  constexpr int threads = Extra::kMode == 1 ? GEMM_THREADS + 32 * GATHER_WARPS : GEMM_THREADS;  // + the gather warps
   cudaError_t le = launch_pdl(kern, dim3(grid), dim3(threads), S::TOTAL, stream, tmA, tmB, tmC, C,
                               reinterpret_cast<const __nv_bfloat16*>(bias), M, N, K, ldc, accumulate, status, tile_boff, extra);
   if (le != cudaSuccess) set_last_error(std::string("gemm launch: ") + cudaGetErrorString(le));

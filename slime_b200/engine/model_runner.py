@@ -198,14 +198,16 @@ class ModelRunner:
 
     def _gather_logits(self, logits):
         """Vocab-parallel LM head: [T, V/tp] per rank -> [T, V] on every rank (rank r owns columns r*V/tp ...)."""
+        V = self.cfg.vocab_size  # columns past it are padding of the vocabulary sharding: never sampled, never scored
         if self.tp_group is None or self.w.tp == 1:
-            return logits
+            return logits if logits.shape[1] == V else logits[:, :V]
         import torch.distributed as dist
 
         T, vl = logits.shape
         parts = torch.empty(self.w.tp * T, vl, dtype=logits.dtype, device=logits.device)  # rank-major concatenation
         dist.all_gather_into_tensor(parts, logits.contiguous(), group=self.tp_group)
-        return parts.view(self.w.tp, T, vl).permute(1, 0, 2).reshape(T, -1)
+        full = parts.view(self.w.tp, T, vl).permute(1, 0, 2).reshape(T, -1)
+        return full if full.shape[1] == V else full[:, :V]
 
     def _row_parallel_norm(self, inp, weight, ln, res, T: int):
         """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual)."""

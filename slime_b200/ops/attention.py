@@ -8,7 +8,8 @@ Work is described by SEGMENTS ``[nseg, 4] = (q_off, q_len, k_off, k_len)``: rows
 attend rows ``[k_off, k_off + k_len)`` of K / V, causally aligned at the end (query ``i`` sees keys
 ``j <= (k_len - q_len) + i``). A packed training batch is one segment per sequence with ``q_off == k_off``; a prefill
 over a cached prefix has ``k_len > q_len``; a context-parallel rank passes each local query chunk against a prefix of
-the gathered keys. Replaces the flash-attn / TE attention calls of the reference
+the gathered keys. In the backward every key tile of a segment has one owner, so the key ranges of the segments of
+one call must not overlap (query ranges never do). Replaces the flash-attn / TE attention calls of the reference
 (slime_plugins/models/flash_dot_product_attention.py:25-80).
 """
 
@@ -268,7 +269,10 @@ def context_parallel_attention(q, k, v, local_cu_seqlens, cp_group, scale=None):
     perm, seg = context_parallel_plan(local_cu_seqlens, cp, rank, k.shape[0])
     kg = _AllGatherRows.apply(k, cp_group).index_select(0, perm)
     vg = _AllGatherRows.apply(v, cp_group).index_select(0, perm)
-    return segment_attention(q, kg, vg, seg, scale)
+    # The two chunks of a sequence read overlapping key ranges, and the backward kernels give every key tile of a
+    # segment one owner: segments of one call must not share keys. One call per chunk; autograd adds the two dK / dV.
+    n = seg.shape[0] // 2
+    return segment_attention(q, kg, vg, seg[:n].contiguous(), scale) + segment_attention(q, kg, vg, seg[n:].contiguous(), scale)
 
 
 def rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, q_norm_w=None, k_norm_w=None, eps=1e-6,

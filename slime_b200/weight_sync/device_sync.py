@@ -119,8 +119,10 @@ class GatherToEngine:
                 if name == "output_layer.weight" and cfg.tie_word_embeddings:
                     continue
                 rows, cols = p.shape
-                for r in range(n):
-                    block(r, off, dst, r * rows, rows, cols)
+                for r in range(n):  # rows past the real vocabulary are padding of the trainer's sharding: not synced
+                    valid = max(0, min(rows, cfg.vocab_size - r * rows))
+                    if valid:
+                        block(r, off, dst, r * rows, valid, cols)
                 continue
             if name == "decoder.final_layernorm.weight":
                 block(self.rank, off, w.final_norm, 0, 1, p.numel())

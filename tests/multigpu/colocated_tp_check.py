@@ -84,7 +84,9 @@ def main():
     if rank == 0:
         print(f"RESULT ok world={world} tp={tp} dp={dp} device={'cuda' if cuda else 'cpu'} fused_tp={runner.engine.runner._fused_tp is not None}"
               f" logprob_diff={diff:.2e}", flush=True)
-    dist.destroy_process_group()
+    from slime_b200.utils.distributed_utils import shutdown_distributed
+
+    shutdown_distributed([runner.engine])
 
 
 if __name__ == "__main__":
