@@ -135,7 +135,8 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
     import subprocess
 
     ckpt, data = tmp_path / "ckpt", tmp_path / "data"
-    for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist"):
+    for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist",
+              "Qwen3-8B", "Qwen3-8B_torch_dist", "Qwen3-32B_torch_dist", "Qwen2.5-0.5B-Instruct_torch_dist"):
         (ckpt / d).mkdir(parents=True)
     for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl"):
         (data / f).parent.mkdir(parents=True, exist_ok=True)
@@ -146,6 +147,21 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     scripts = sorted(glob.glob(os.path.join(root, "recipes", "run-*.sh")))
     assert len(scripts) >= 4
+    # launch lines of the script-based examples go through the same parser
+    examples = [os.path.join(root, "examples", p) for p in (
+        "delta_weight_sync/run-qwen3-30B-A3B-delta.sh", "on_policy_distillation/run-qwen3-8B-opd.sh",
+        "fully_async/run-qwen2.5-0.5B-fully_async.sh", "eval_multi_task/multi_task.sh")]  # fmt: skip
+    for script in examples:
+        r = subprocess.run(["bash", script], env=dict(os.environ, DRY_RUN="1", NUM_GPUS="8", CKPT_DIR=str(ckpt), DATA_DIR=str(data)), capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-2000:]
+        argv = r.stdout.strip().split("\n")
+        args = parse_args(argv[1:])
+        if "delta" in script:
+            assert args.update_weight_mode == "delta" and args.update_weight_delta_encoding == "xor"
+        if "opd" in script:
+            assert args.use_opd and args.opd_type == "megatron" and args.opd_kl_coef == 1.0
+        if "multi_task" in script:
+            assert args.eval_config.endswith("multi_task.yaml")
     for script in scripts:
         r = subprocess.run(["bash", script], env=dict(os.environ, DRY_RUN="1", NUM_GPUS="8", CKPT_DIR=str(ckpt), DATA_DIR=str(data)), capture_output=True, text=True, timeout=120)
         assert r.returncode == 0, r.stderr[-2000:]
