@@ -111,15 +111,23 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* addr) {
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
-// Rotation of the row-tile index: the walk starts at tile `rot` and wraps (own rows first when gathering, last when
-// scattering).
+// Order of the row tiles. rot > 0: the walk starts at tile `rot` and wraps (gathering: own rows first, while the
+// peers' rows arrive). rot < 0, -rot = world << 8 | rank (scattering): consecutive positions of the walk belong to
+// different owners (rank + 1, rank + 2, ..., rank), so the stores to the peers are spread over the whole GEMM instead of
+// saturating NVLink during its first part, and every owner starts receiving at once.
 template <int BN>
 __device__ __forceinline__ void tile_origin_rot(int tile, int tiles_m, int tiles_n, int rot, int& m0, int& n0) {
   tile_origin<BN>(tile, tiles_m, tiles_n, m0, n0);
-  if (rot != 0) {
+  if (rot > 0) {
     int mt = m0 / GEMM_BM + rot;
     if (mt >= tiles_m) mt -= tiles_m;
     m0 = mt * GEMM_BM;
+  } else if (rot < 0) {
+    const int world = (-rot) >> 8, rank = (-rot) & 0xff;
+    const int mt = m0 / GEMM_BM, tpr = tiles_m / world;
+    int owner = rank + 1 + mt % world;
+    if (owner >= world) owner -= world;
+    m0 = (owner * tpr + mt / world) * GEMM_BM;
   }
 }
 
@@ -156,7 +164,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_items = num_tiles * splitk;
   int rot = 0;  // first row tile of the walk
   if constexpr (Extra::kMode == 1) rot = extra.rank * (extra.rows_per_rank / GEMM_BM);
-  if constexpr (Extra::kMode == 2) rot = ((extra.rank + 1) % extra.world) * (extra.rows_per_rank / GEMM_BM);
+  if constexpr (Extra::kMode == 2) rot = -((extra.world << 8) | extra.rank);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {

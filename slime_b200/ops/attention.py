@@ -61,9 +61,11 @@ def _strides_ok(t: torch.Tensor) -> bool:
     return t.stride(-1) == 1 and t.stride(1) == t.shape[-1] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
-def flash_fwd(q, k, v, seg, scale, max_q_len_hint: int | None = None, out=None):
+def flash_fwd(q, k, v, seg, scale, max_q_len_hint: int | None = None, out=None, zero_uncovered: bool = False):
     """Forward kernel launch. q [Tq, Hq, D] (heads contiguous inside a token row, any 16-byte-multiple row pitch),
-    k / v [Tk, Hkv, D]. Returns ``(out [Tq, Hq, D], lse [Hq, Tq] fp32)``."""
+    k / v [Tk, Hkv, D]. Returns ``(out [Tq, Hq, D], lse [Hq, Tq] fp32)``. The kernel writes the rows of ``out`` that
+    lie inside a segment and no others; ``zero_uncovered`` starts from zeros for callers whose segments do not cover
+    every row."""
     from slime_b200.ops import _lib
 
     Tq, Hq, D = q.shape
@@ -71,8 +73,8 @@ def flash_fwd(q, k, v, seg, scale, max_q_len_hint: int | None = None, out=None):
     assert D in (64, 128), f"flash attention kernels cover head dims 64 and 128, not {D}"
     q, k, v = (t if _strides_ok(t) else t.contiguous() for t in (q, k, v))
     if out is None:
-        out = torch.empty(Tq, Hq, D, dtype=q.dtype, device=q.device)
-    lse = torch.empty(Hq, Tq, dtype=torch.float32, device=q.device)
+        out = (torch.zeros if zero_uncovered else torch.empty)(Tq, Hq, D, dtype=q.dtype, device=q.device)
+    lse = (torch.zeros if zero_uncovered else torch.empty)(Hq, Tq, dtype=torch.float32, device=q.device)
     nseg = seg.shape[0]
     max_q_tiles = -(-Tq // 128) + nseg
     fn = _lib.bind("sb_flash_fwd", [_lib.P] * 6 + [_lib.I] * 12 + [_lib.F, _lib.P, _lib.P])
@@ -108,7 +110,7 @@ def flash_bwd(q, k, v, o, d_o, lse, seg, scale, dq=None, dk=None, dv=None):
 class _FlashAttention(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, seg, scale):
-        out, lse = flash_fwd(q, k, v, seg, scale)
+        out, lse = flash_fwd(q, k, v, seg, scale, zero_uncovered=True)
         ctx.save_for_backward(q, k, v, out, lse, seg)
         ctx.scale = scale
         return out
