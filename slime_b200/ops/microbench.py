@@ -7,6 +7,7 @@ repetitions with an L2 flush (a 256 MiB memset) between them. One JSON object pe
     decode  each kernel of one rollout decode step at a given batch and context length
     norm    RMSNorm forward/backward bandwidth
     attn    flash attention forward / backward (own kernels; the flash-attn library on the same tensors for comparison)
+    fused_emul  the peer-memory kernels (DP reduce / Adam, TP all-reduce + norm) with all ranks emulated on one GPU
 
 ``--small`` shrinks the working set to a case suitable for a profiler capture (a few launches, < 1 GB).
 """
@@ -341,9 +342,63 @@ def bench_attn(a):
     _lib.check_status("cuda")
 
 
+def bench_fused_emul(a):
+    """The peer-memory kernels with every "rank" a buffer of THIS GPU (profilers attach to one process on one GPU, and
+    kernels that wait on one another must not run as separate launches on one device): the data path, instruction mix
+    and DRAM behaviour are those of the multi-GPU run, the NVLink hop is not. Flags are preset so no wait occurs."""
+    import ctypes
+
+    lib, P = _lib.lib(), _lib.ptr
+    dev = torch.device("cuda")
+    status = _lib.status_word(dev)
+    # ---- data-parallel reduce-scatter shard + squared norm, then Adam + all-gather stores (world = 4)
+    world, n = 4, (8 if a.small else 64) * 1024 * 1024
+    grads = [torch.randn(n, device=dev) for _ in range(world)]
+    params = [torch.zeros(n, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    gp = (ctypes.c_void_p * world)(*[g.data_ptr() for g in grads])
+    pp = (ctypes.c_void_p * world)(*[p.data_ptr() for p in params])
+    shard = n // world
+    partials, ctl = torch.zeros(148 * 8, device=dev), torch.zeros(2, device=dev)
+    master, m, v = (torch.zeros(shard, device=dev) for _ in range(3))
+
+    def reduce():
+        _lib.check(lib.sb_dp_reduce_shard(gp, world, 0, 0, 0, shard, P(grads[0][:shard]), P(partials), P(ctl), P(status),
+                                          _lib.stream()), "sb_dp_reduce_shard")  # fmt: skip
+
+    def adam():
+        _lib.check(lib.sb_dp_adam_bcast(P(master), P(m), P(v), P(grads[0][:shard]), pp, world, 0, 0, 0, shard, 1e-6, 0.9, 0.98,
+                                        1e-8, 0.1, 0.1, 0.02, 1.0, 1.0, P(ctl), 0, _lib.stream()), "sb_dp_adam_bcast")  # fmt: skip
+
+    t = time_ms(reduce, a.iters)
+    _emit(kind="dp_reduce_shard_emulated", world=world, shard_elems=shard, ms=t, read_gbs=world * shard * 4 / t / 1e6)
+    t = time_ms(adam, a.iters)
+    _emit(kind="dp_adam_bcast_emulated", world=world, shard_elems=shard, ms=t,
+          bytes_gbs=(shard * (4 * 4 + 3 * 4) + world * shard * 2) / t / 1e6)  # fmt: skip
+    # ---- tensor-parallel all-reduce + residual + RMSNorm (world = 2)
+    T, H, world = 256, 2560, 2
+    parts = [torch.randn(T, H, device=dev).to(torch.bfloat16) for _ in range(world)]
+    flags = torch.full((148 * 8,), 1 << 30, dtype=torch.int32, device=dev)  # every peer "has arrived" already
+    epochs = torch.zeros(148, dtype=torch.int32, device=dev)
+    res, w = torch.randn(T, H, device=dev).to(torch.bfloat16), torch.ones(H, device=dev, dtype=torch.bfloat16)
+    y, r = torch.empty_like(res), torch.empty_like(res)
+    ptrs = (ctypes.c_void_p * world)(*[x.data_ptr() for x in parts])
+    fl = (ctypes.c_void_p * world)(*[flags.data_ptr()] * world)
+
+    def ar():
+        _lib.check(lib.sb_tp_ar_add_rmsnorm(ptrs, fl, P(epochs), P(res), P(w), P(y), P(r), T, H, 1e-6, 0, world, 0, P(status),
+                                            _lib.stream()), "sb_tp_ar_add_rmsnorm")  # fmt: skip
+
+    t = time_ms(ar, a.iters)
+    _emit(kind="tp_ar_add_rmsnorm_emulated", T=T, H=H, world=world, us=t * 1e3, gbs=(world + 3) * T * H * 2 / t / 1e6)
+    want = (parts[0].float() + parts[1].float() + res.float())
+    want = want * torch.rsqrt(want.pow(2).mean(-1, keepdim=True) + 1e-6)
+    assert (y.float() - want).abs().max() < 0.05
+    _lib.check_status(dev)
+
+
 def main(argv=None):
     p = argparse.ArgumentParser(prog="python -m slime_b200.ops.microbench")
-    p.add_argument("what", choices=["gemm", "decode", "norm", "fp8", "moe", "attn"])
+    p.add_argument("what", choices=["gemm", "decode", "norm", "fp8", "moe", "attn", "fused_emul"])
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--reps", type=int, default=20, help="back-to-back launches per timed repetition (decode)")
     p.add_argument("--small", action="store_true")
@@ -357,7 +412,7 @@ def main(argv=None):
     from slime_b200.ops import build
 
     build.build()
-    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm, "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn}[a.what](a)
+    {"gemm": bench_gemm, "decode": bench_decode, "norm": bench_norm, "fp8": bench_fp8, "moe": bench_moe, "attn": bench_attn, "fused_emul": bench_fused_emul}[a.what](a)
 
 
 if __name__ == "__main__":

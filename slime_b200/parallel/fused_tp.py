@@ -183,6 +183,7 @@ class GemmReduceScatter:
         from slime_b200.ops import _lib
 
         self._lib = _lib
+        self.group = group
         self.n, self.max_rows, self.device = n, max_rows_per_rank, torch.device(device)
         probe = SymmetricStorage(8, torch.int32, device, group)
         self.world, self.rank = probe.world, probe.rank
@@ -199,6 +200,12 @@ class GemmReduceScatter:
     def fits(self, m: int, n: int) -> bool:
         return n == self.n and m % (self.world * 128) == 0 and m // self.world <= self.max_rows
 
+    def profitable(self, k: int) -> bool:
+        """Whether the single-kernel path beats GEMM + NCCL reduce-scatter for an inner dimension ``k`` (see __call__)."""
+        if os.environ.get("SLIME_B200_FORCE_FUSED_RS") == "1":
+            return True
+        return self.world == 2 and k >= 4096
+
     def __call__(self, a: torch.Tensor, weight: torch.Tensor, b_mn: bool = False):
         """``a`` [M, K] bf16, ``weight`` [N, K] (or [K, N] with ``b_mn``) -> this rank's ``[M / world, N]`` bf16 rows of the
         sum over ranks of ``a @ op(weight)``."""
@@ -210,6 +217,18 @@ class GemmReduceScatter:
         assert self.fits(m, n), f"product [{m}, {n}] does not fit (max rows per rank {self.max_rows}, N {self.n})"
         if a.stride(-1) != 1 or a.stride(0) % 8:
             a = a.contiguous()
+        if not self.profitable(k):
+            # Measured at M 9216, N 2560 (device time, max over ranks): 2 GPUs, K 4864: fused 213 us, GEMM + NCCL
+            # reduce-scatter 238 us; K 2048: 177 vs 150 us. 4 GPUs, K 2432: 202 vs 171 us; K 1024: 285 vs 130 us. A short K
+            # leaves too little GEMM to hide the tile stores and the owner's reduction behind, so those shapes keep NCCL.
+            import torch.distributed as dist
+
+            from slime_b200 import ops
+
+            part = ops.gemm(a, weight, b_mn=b_mn)
+            out = torch.empty(m // self.world, n, dtype=torch.bfloat16, device=self.device)
+            dist.reduce_scatter_tensor(out, part, group=self.group)
+            return out
         w = self._which
         self.epochs[w] += 1
         out = torch.empty(m // self.world, n, dtype=torch.bfloat16, device=self.device)

@@ -23,6 +23,7 @@ def main():
     from slime_b200.parallel import fused_tp, state as mpu, tensor_parallel as tp
 
     build.build()
+    os.environ["SLIME_B200_FORCE_FUSED_RS"] = "1"  # this check measures the single-kernel path at every shape
     mpu.initialize_model_parallel(tensor_model_parallel_size=world)
     dev = torch.device("cuda", local)
     H = 2560
