@@ -208,6 +208,10 @@ def main():
         h2d["bytes"] = prompts_host[i].numel() * 4
         out = runner.step(prompts_host[i].tolist(), resp_lens[i].tolist())
         loss = out["metrics"].get("train/loss", 0.0)  # python float: already read back D2H
+        if rank == 0:  # progress on stderr: a long step of the large config is otherwise silent for minutes
+            kind = "warmup" if i < a.warmup else "step"
+            print(f"[bench] {kind} {i}: rollout {out['rollout_s']:.2f} s, train {out['train_s']:.2f} s, sync {out['sync_s']:.3f} s, "
+                  f"{out['tokens'] // tp} tokens on this data-parallel rank", file=sys.stderr, flush=True)
         return out, loss
 
     def sync():

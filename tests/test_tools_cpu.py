@@ -136,9 +136,11 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
 
     ckpt, data = tmp_path / "ckpt", tmp_path / "data"
     for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist",
-              "Qwen3-8B", "Qwen3-8B_torch_dist", "Qwen3-32B_torch_dist", "Qwen2.5-0.5B-Instruct_torch_dist"):
+              "Qwen3-8B", "Qwen3-8B_torch_dist", "Qwen3-32B_torch_dist", "Qwen2.5-0.5B-Instruct_torch_dist", "Qwen3-32B",
+              "Qwen3-235B-A22B", "Qwen3-235B-A22B_torch_dist", "Qwen3-4B-Base", "Qwen3-4B-Base_torch_dist"):
         (ckpt / d).mkdir(parents=True)
-    for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl"):
+    for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl",
+              "openhermes2_5/openhermes2_5.parquet"):
         (data / f).parent.mkdir(parents=True, exist_ok=True)
         (data / f).write_text("")
 
@@ -168,7 +170,17 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
         argv = r.stdout.strip().split("\n")
         assert argv[0] in ("train.py", "train_async.py")
         args = parse_args(argv[1:])
-        assert args.num_layers > 0 and args.rollout_batch_size == 32 and args.n_samples_per_prompt == 8
+        assert args.num_layers > 0
+        if "sft" in script:
+            assert args.loss_type == "sft_loss" and args.debug_train_only and args.rollout_batch_size == 128
+        else:
+            assert args.rollout_batch_size == 32 and args.n_samples_per_prompt == 8
+        if "qwen3-8B" in script:
+            assert args.use_critic and args.advantage_estimator == "ppo"
+        if "32B" in script:
+            assert args.tensor_model_parallel_size == 4 and args.rollout_num_gpus == 4 and not args.colocate
+        if "reproducibility" in script:
+            assert args.deterministic_mode
         if "30B" in script:
             assert args.num_experts == 128 and args.expert_model_parallel_size == 8 and args.sglang_ep_size == 8
         if "async" in script:
