@@ -38,6 +38,7 @@ def test_trainer_forward_backward_matches_fp32_reference(kernels):
     lp = torch.log_softmax(out.float(), -1).cpu()
     lp_ref = torch.log_softmax(out_ref.float(), -1)
     assert (lp - lp_ref).abs().max().item() < 0.15
+    assert (lp - lp_ref).abs().mean().item() < 0.03  # the bound above is for the worst of 300 x V entries
     tgt = torch.randint(0, cfg.vocab_size, (300,))
     loss = -torch.log_softmax(out.float(), -1)[0].gather(-1, tgt.cuda()[:, None]).mean()
     loss_ref = -lp_ref[0].gather(-1, tgt[:, None]).mean()
@@ -48,6 +49,7 @@ def test_trainer_forward_backward_matches_fp32_reference(kernels):
         g, gr = p.grad.float().cpu(), q.grad
         denom = gr.abs().max().item() + 1e-6
         assert (g - gr).abs().max().item() / denom < 0.12, n
+        assert (g - gr).abs().mean().item() / denom < 0.02, n  # the typical entry is much closer than the worst one
 
 
 def test_engine_matches_trainer_logprobs(kernels):
