@@ -120,3 +120,34 @@ def test_multi_agent_example_fans_out_one_rollout(engine):
     assert sel.metadata["selected_candidate"] == 1 and sel.reward == pytest.approx(w if correct else 0.0)
     assert sorted(round(s.reward, 3) for s in outs if s.metadata["agent_role"] == "solver") == [0.0, 0.0, w]
     assert all(s.response_length == len(s.rollout_log_probs) > 0 and s.status == Sample.Status.COMPLETED for s in outs)
+
+
+def test_retool_example_runs_the_interpreter_between_turns(engine):
+    from examples.retool import generate_with_retool as ex
+
+    args, state, tok = engine
+    call = '<tool_call> {"name": "code_interpreter", "arguments": {"code": "print(6*7)"}} </tool_call>'
+
+    def script(prompt):
+        if "<tool_response>" in prompt:
+            assert "<tool_response> 42 </tool_response>" in prompt
+            return "so Answer: 42"
+        return "compute " + call
+
+    state["script"] = script
+    s = Sample(index=0, prompt="what is 6 times 7 ?", label="42")
+    out = asyncio.run(ex.generate(args, s, {"max_new_tokens": 200, "temperature": 1.0}))
+    assert out.status == Sample.Status.COMPLETED and len(state["calls"]) == 2
+    assert state["calls"][0][1]["stop"] == ["</tool_call>"] and state["calls"][0][1]["no_stop_trim"] is True
+    assert out.metadata["tool_calls"] == 1 and out.metadata["tool_calls_ok"] == 1
+    first, obs = len(tok.encode("compute " + call)), len(tok.encode(ex.format_observation("42")))
+    assert out.loss_mask == [1] * first + [0] * obs + [1] * 3
+    assert out.response_length == len(out.loss_mask) == len(out.rollout_log_probs)
+    assert asyncio.run(ex.reward_func(args, out)) == 1.0
+    # a wrong final answer still earns the tool bonus; a broken snippet does not
+    out.label = "43"
+    assert asyncio.run(ex.reward_func(args, out)) == pytest.approx(-1.0 + ex.TOOL_BONUS)
+    assert ex.extract_code('<tool_call>{"name": "other", "arguments": {}}</tool_call>') is None
+    assert ex.extract_code("<tool_call>{broken</tool_call>") is None
+    ok, text = asyncio.run(ex.run_python("import time\nprint(1/0)"))
+    assert not ok and "ZeroDivisionError" in text

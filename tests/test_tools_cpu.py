@@ -137,7 +137,7 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
     ckpt, data = tmp_path / "ckpt", tmp_path / "data"
     for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist",
               "Qwen3-8B", "Qwen3-8B_torch_dist", "Qwen3-32B_torch_dist", "Qwen2.5-0.5B-Instruct_torch_dist", "Qwen3-32B",
-              "Qwen3-235B-A22B", "Qwen3-235B-A22B_torch_dist", "Qwen3-4B-Base", "Qwen3-4B-Base_torch_dist"):
+              "Qwen3-235B-A22B", "Qwen3-235B-A22B_torch_dist", "Qwen3-4B-Base", "Qwen3-4B-Base_torch_dist", "Qwen3-4B-retool-sft", "Qwen3-4B-retool-sft_torch_dist"):
         (ckpt / d).mkdir(parents=True)
     for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl",
               "openhermes2_5/openhermes2_5.parquet"):
@@ -152,7 +152,7 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
     # launch lines of the script-based examples go through the same parser
     examples = [os.path.join(root, "examples", p) for p in (
         "delta_weight_sync/run-qwen3-30B-A3B-delta.sh", "on_policy_distillation/run-qwen3-8B-opd.sh",
-        "fully_async/run-qwen2.5-0.5B-fully_async.sh", "eval_multi_task/multi_task.sh")]  # fmt: skip
+        "fully_async/run-qwen2.5-0.5B-fully_async.sh", "eval_multi_task/multi_task.sh", "retool/retool_qwen3_4b_rl.sh")]  # fmt: skip
     for script in examples:
         r = subprocess.run(["bash", script], env=dict(os.environ, DRY_RUN="1", NUM_GPUS="8", CKPT_DIR=str(ckpt), DATA_DIR=str(data)), capture_output=True, text=True, timeout=120)
         assert r.returncode == 0, r.stderr[-2000:]
