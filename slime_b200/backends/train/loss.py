@@ -195,7 +195,9 @@ def apply_opd_kl_to_advantages(args, rollout_data, advantages, student_log_probs
     rev = []
     for i, (adv, s, t) in enumerate(zip(advantages, student_log_probs, teacher)):
         t = torch.as_tensor(t, dtype=torch.float32, device=adv.device)
-        d = s.detach().float() - t[-s.numel():] if t.numel() >= s.numel() else s.detach().float() * 0
+        if t.numel() < s.numel():  # a silent zero here would train without the distillation signal
+            raise ValueError(f"sample {i}: teacher log-probs cover {t.numel()} tokens, the response has {s.numel()}")
+        d = s.detach().float() - t[-s.numel():]
         advantages[i] = adv - args.opd_kl_coef * d
         rev.append(d)
     rollout_data["opd_reverse_kl"] = rev

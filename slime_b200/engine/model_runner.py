@@ -166,7 +166,7 @@ class ModelRunner:
         # Row-parallel projections (attention output, MLP down) leave their result in fp32 when no cross-rank sum
         # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
         # into K slices that the epilogue sums with TMA reduce-add.
-        self._proj_dtype = torch.float32 if (self.device.type == "cuda" and weights.tp == 1) else None
+        self._proj_dtype = torch.float32 if (self.device.type == "cuda" and weights.tp == 1 and not ops.library_mode()) else None
         # Tensor-parallel decode: all-reduce + residual add + RMSNorm as one peer-memory kernel when the ranks share an
         # NVLink domain; otherwise NCCL all-reduce followed by the fused add+norm.
         self._fused_tp = None

@@ -38,6 +38,8 @@ def _cuda(t: torch.Tensor) -> bool:
 def _library_gemm(a, b, a_mn, b_mn, bias, out, out_dtype, accumulate):
     A = a.t() if a_mn else a
     B = b if b_mn else b.t()
+    if A.dtype != B.dtype:
+        A = A.to(B.dtype)
     if out_dtype == torch.float32:
         try:
             res = torch.mm(A, B, out_dtype=torch.float32)

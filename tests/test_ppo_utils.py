@@ -113,3 +113,19 @@ def test_logprob_keep_mask_forces_target_and_keeps_entropy_unmasked():
         assert lp[i].item() == pytest.approx(ref.item(), abs=1e-6)
     lsm = torch.log_softmax(z, -1)
     assert torch.allclose(ent, -(lsm.exp() * lsm).sum(-1), atol=1e-6)
+
+
+def test_opd_subtracts_reverse_kl_and_rejects_short_teacher():
+    from argparse import Namespace
+
+    from slime_b200.backends.train.loss import apply_opd_kl_to_advantages
+
+    args = Namespace(opd_kl_coef=0.5)
+    adv = [torch.zeros(3), torch.ones(2)]
+    student = [torch.tensor([-1.0, -2.0, -3.0]), torch.tensor([-0.5, -0.5])]
+    data = {"teacher_log_probs": [[-9.0, -1.0, -1.0, -1.0], [-1.5, -0.5]]}  # a longer teacher vector is right-aligned
+    apply_opd_kl_to_advantages(args, data, adv, student)
+    assert torch.allclose(adv[0], torch.tensor([0.0, 0.5, 1.0])) and torch.allclose(adv[1], torch.tensor([0.5, 1.0]))
+    assert torch.allclose(data["opd_reverse_kl"][1], torch.tensor([1.0, 0.0]))
+    with pytest.raises(ValueError, match="teacher log-probs cover 1 tokens"):
+        apply_opd_kl_to_advantages(args, {"teacher_log_probs": [[-1.0]]}, [torch.zeros(2)], [torch.zeros(2)])
