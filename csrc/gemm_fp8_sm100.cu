@@ -10,7 +10,9 @@
 // block in the other TMEM accumulator. Warp roles: 0 = TMA producer (4-stage ring of 16 KB A + 32 KB B tiles,
 // 128-byte swizzle: one smem row = one K block), 1 = MMA issuer, 2..9 = promotion + store (two warps per TMEM lane
 // quarter, one per 128-column half of the 128 x 256 tile, i.e. per B scale block; thread = output row, 128 fp32
-// accumulators in registers). Persistent over output tiles. Every wait is bounded: on expiry the CTA records a status word,
+// accumulators in registers). Persistent over output tiles. Grouped form (expert MLPs): B is a stack of E matrices
+// [E * N, K] with scales [E, ceil(N/128), K/128]; every 128-row tile of A belongs to one expert and `tile_boff[m-tile]`
+// is that expert's first row in the stack. Every wait is bounded: on expiry the CTA records a status word,
 // stops issuing, frees its TMEM and returns.
 #include <string>
 
@@ -41,7 +43,7 @@ template <bool OUT_F32>
 __global__ void __launch_bounds__(F8_THREADS, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const float* __restrict__ sa_t, const float* __restrict__ sb, void* __restrict__ Cv, int M, int N,
-                      int K, int ldc, int* status) {
+                      int K, int ldc, const int* __restrict__ tile_boff, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
@@ -91,6 +93,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         int m0, n0;
         f8_tile_origin(tile, tiles_m, tiles_n, m0, n0);
+        const int boff = tile_boff != nullptr ? __ldg(tile_boff + m0 / F8_BM) : 0;
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, cta_abort, status, ERR_WAIT_EMPTY)) {
             ok = false;
@@ -98,7 +101,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
           mbar_arrive_expect_tx(&full[stage], F8_STAGE_BYTES);
           tma_load_2d(sA + stage * F8_A_BYTES, &tmA, &full[stage], kb * F8_BK, m0);
-          tma_load_2d(sB + stage * F8_B_BYTES, &tmB, &full[stage], kb * F8_BK, n0);
+          tma_load_2d(sB + stage * F8_B_BYTES, &tmB, &full[stage], kb * F8_BK, n0 + boff);
           if (++stage == F8_STAGES) {
             stage = 0;
             phase ^= 1;
@@ -151,7 +154,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       f8_tile_origin(tile, tiles_m, tiles_n, m0, n0);
       const int row = m0 + row_in_tile;
       const int nblk = min(n0 / 128 + h, (N + 127) / 128 - 1);  // a tile's second half may lie past N: its scales are unused
-      const float* sb_row = sb + static_cast<size_t>(nblk) * num_kb;
+      // grouped: the expert's own scale table ([ceil(N/128), K/128] per expert)
+      const int expert = tile_boff != nullptr ? __ldg(tile_boff + m0 / F8_BM) / N : 0;
+      const float* sb_row = sb + (static_cast<size_t>(expert) * ((N + 127) / 128) + nblk) * num_kb;
       float c[HALF];
 #pragma unroll
       for (int i = 0; i < HALF; ++i) c[i] = 0.f;
@@ -232,18 +237,25 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
 // A, B: e4m3 bytes, row-major with pitches lda / ldb (bytes = elements; multiples of 16). sa_t: [K/128, M] fp32.
 // sb: [ceil(N/128), K/128] fp32. C: [M, N] bf16 (out_f32 = 0) or fp32, pitch ldc elements. K must be a multiple of 128.
-extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t, const float* sb, void* C, int M, int N,
-                                 int K, int lda, int ldb, int ldc, int out_f32, int* status, int num_sms,
-                                 cudaStream_t stream) {
+// Grouped (tile_boff != nullptr): B is [num_experts * N, K], sb is [num_experts, ceil(N/128), K/128], M a multiple of 128
+// and tile_boff[M / 128] the first stack row of each row tile's expert.
+static int fp8_launch(const void* A, const void* B, const float* sa_t, const float* sb, void* C, int M, int N, int K, int lda,
+                      int ldb, int ldc, int out_f32, const int* tile_boff, int num_experts, int* status, int num_sms,
+                      cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if (K % sb::F8_BK != 0 || lda % 16 != 0 || ldb % 16 != 0) {
     sb::set_last_error("sb_gemm_fp8_block: K must be a multiple of 128 and the row pitches multiples of 16 bytes");
     return (int)cudaErrorInvalidValue;
   }
+  if (tile_boff != nullptr && (M % sb::F8_BM != 0 || num_experts <= 0)) {
+    sb::set_last_error("sb_gemm_fp8_grouped: M must be a multiple of 128 (expert-padded rows) and num_experts positive");
+    return (int)cudaErrorInvalidValue;
+  }
   try {
     CUtensorMap tmA = sb::make_tmap_2d(A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, size_t(lda), sb::F8_BM, sb::F8_BK,
                                        CU_TENSOR_MAP_SWIZZLE_128B);
-    CUtensorMap tmB = sb::make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, size_t(ldb), sb::F8_BN, sb::F8_BK,
+    const size_t b_rows = tile_boff != nullptr ? size_t(num_experts) * N : size_t(N);
+    CUtensorMap tmB = sb::make_tmap_2d(B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, b_rows, K, size_t(ldb), sb::F8_BN, sb::F8_BK,
                                        CU_TENSOR_MAP_SWIZZLE_128B);
     const int tiles = ((M + sb::F8_BM - 1) / sb::F8_BM) * ((N + sb::F8_BN - 1) / sb::F8_BN);
     const int grid = tiles < num_sms ? tiles : num_sms;
@@ -252,12 +264,12 @@ extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t
       e = sb::ensure_dynamic_smem(reinterpret_cast<const void*>(sb::gemm_fp8_block_kernel<true>), sb::F8_SMEM);
       if (e != cudaSuccess) return (int)e;
       e = sb::launch_pdl(sb::gemm_fp8_block_kernel<true>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB, sa_t,
-                         sb, C, M, N, K, ldc, status);
+                         sb, C, M, N, K, ldc, tile_boff, status);
     } else {
       e = sb::ensure_dynamic_smem(reinterpret_cast<const void*>(sb::gemm_fp8_block_kernel<false>), sb::F8_SMEM);
       if (e != cudaSuccess) return (int)e;
       e = sb::launch_pdl(sb::gemm_fp8_block_kernel<false>, dim3(grid), dim3(sb::F8_THREADS), sb::F8_SMEM, stream, tmA, tmB,
-                         sa_t, sb, C, M, N, K, ldc, status);
+                         sa_t, sb, C, M, N, K, ldc, tile_boff, status);
     }
     if (e != cudaSuccess) sb::set_last_error(std::string("fp8 gemm launch: ") + cudaGetErrorString(e));
     return (int)e;
@@ -265,4 +277,20 @@ extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t
     sb::set_last_error(e.what());
     return (int)cudaErrorInvalidValue;
   }
+}
+
+extern "C" int sb_gemm_fp8_block(const void* A, const void* B, const float* sa_t, const float* sb, void* C, int M, int N,
+                                 int K, int lda, int ldb, int ldc, int out_f32, int* status, int num_sms,
+                                 cudaStream_t stream) {
+  return fp8_launch(A, B, sa_t, sb, C, M, N, K, lda, ldb, ldc, out_f32, nullptr, 0, status, num_sms, stream);
+}
+
+extern "C" int sb_gemm_fp8_grouped(const void* A, const void* B, const float* sa_t, const float* sb, void* C,
+                                   const int* tile_boff, int M, int N, int K, int num_experts, int lda, int ldb, int ldc,
+                                   int out_f32, int* status, int num_sms, cudaStream_t stream) {
+  if (tile_boff == nullptr) {
+    sb::set_last_error("sb_gemm_fp8_grouped: needs tile_boff");
+    return (int)cudaErrorInvalidValue;
+  }
+  return fp8_launch(A, B, sa_t, sb, C, M, N, K, lda, ldb, ldc, out_f32, tile_boff, num_experts, status, num_sms, stream);
 }

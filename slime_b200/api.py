@@ -44,6 +44,9 @@ class ColocatedGRPO:
             page_size=getattr(args, "sglang_page_size", None) or 16,
             random_seed=args.rollout_seed + mpu.get_data_parallel_rank(),
             disable_cuda_graph=bool(getattr(args, "sglang_disable_cuda_graph", False)),
+            quantization=getattr(args, "sglang_quantization", None),
+            ep_size=getattr(args, "sglang_ep_size", None) or 1,
+            enable_return_routed_experts=bool(getattr(args, "use_rollout_routing_replay", False)),
         )
         # One engine per tensor-parallel group of the trainer, sharded the same way: rank r of the group holds shard r
         # of both the trainer's and the engine's weights, so weight sync is a device-local copy and the ranks of a
@@ -73,7 +76,7 @@ class ColocatedGRPO:
                                     sampling_seed=a.rollout_seed * 1_000_003 + self.sample_index)  # fmt: skip
                 if a.rollout_top_p != 1.0:
                     sp.custom_params = {"return_top_p_token_ids": True}
-                reqs.append(self.engine.add_request(p, sp))
+                reqs.append(self.engine.add_request(p, sp, return_routed_experts=self.engine.runner.record_routed))
                 s = Sample(group_index=self.rollout_id * len(prompts) + g, index=self.sample_index, prompt="", tokens=list(p))
                 self.sample_index += 1
                 samples.append(s)

@@ -82,6 +82,8 @@ class TrainActor:
             load_function(hook)(args)
         if getattr(args, "deterministic_mode", False):
             torch.use_deterministic_algorithms(True, warn_only=True)
+        if getattr(args, "use_routing_replay", False):
+            os.environ["ENABLE_ROUTING_REPLAY"] = "1"  # read by every router (slime/utils/routing_replay.py:81 in the reference)
         self.model = TrainModel(args, role=self.role, device=device)
         start = 0
         if getattr(args, "load", None):
@@ -204,6 +206,34 @@ class TrainActor:
             self.prof.step(rollout_id)
         return out
 
+    def fill_routing_replay(self, iterator, data: dict):
+        """R3: hand every MoE layer the experts the rollout engine picked, micro-batch by micro-batch in the order the
+        passes will walk them. Rows follow the packed token stream of ``get_batch`` (CP slice per sample, padding rows
+        at the end, this rank's sequence-parallel slice). Same role as slime/backends/megatron_utils/actor.py:308-355
+        in the reference."""
+        from slime_b200.backends.train.cp_utils import prepare_routed_experts_for_routing_replay
+
+        a = self.args
+        if "rollout_routed_experts" not in data:
+            raise ValueError("rollout_routed_experts is required in the rollout data when --use-rollout-routing-replay is set")
+        tp_size, tp_rank = mpu.get_tensor_model_parallel_world_size(), mpu.get_tensor_model_parallel_rank()
+        layers = [i for i in range(a.num_layers) if self.model.cfg.is_moe_layer(i)]
+        routing_replay.RoutingReplay.clear_all()
+        iterator.reset()
+        for _ in range(len(iterator)):
+            batch = iterator.get_next(["rollout_routed_experts", "total_lengths"])
+            rows = torch.cat([prepare_routed_experts_for_routing_replay(torch.as_tensor(r), tl)
+                              for r, tl in zip(batch["rollout_routed_experts"], batch["total_lengths"])])  # fmt: skip
+            pad = (-rows.shape[0]) % (tp_size * a.data_pad_size_multiplier)
+            if pad:
+                rows = torch.nn.functional.pad(rows, (0, 0, 0, 0, 0, pad))
+            if a.sequence_parallel and tp_size > 1:
+                n = rows.shape[0] // tp_size
+                rows = rows[tp_rank * n : (tp_rank + 1) * n]
+            routing_replay.fill_from_rollout([rows], layers)
+        iterator.reset()
+        del data["rollout_routed_experts"]
+
     def compute_log_prob(self, data_iterator, num_microbatches, store_prefix=""):
         with timer(f"{store_prefix}log_probs"):
             return forward_only(get_log_probs_and_entropy, self.args, self.model, data_iterator, num_microbatches, store_prefix)
@@ -235,6 +265,8 @@ class TrainActor:
                     data.update(self.compute_log_prob(it, num_mb, "teacher_"))
                 if self._active_model_tag != ("old_actor" if a.keep_old_actor else "actor"):
                     self._switch_model("old_actor" if a.keep_old_actor else "actor")
+                if a.use_rollout_routing_replay:
+                    self.fill_routing_replay(it[0], data)
                 if (not a.use_rollout_logprobs or a.get_mismatch_metrics) and not self.can_reuse_log_probs_in_loss(num_mb):
                     if a.use_routing_replay:
                         routing_replay.set_stage("replay_forward" if a.use_rollout_routing_replay else "record")
@@ -252,7 +284,7 @@ class TrainActor:
                 self.rollout_data_postprocess(a, rollout_id, data)
             train_metric_utils.log_rollout_data(rollout_id, a, data)
             if a.use_routing_replay:
-                routing_replay.set_stage("replay_backward")
+                routing_replay.set_stage("replay_forward")  # recomputed layers switch to the backward cursor themselves
             capture = getattr(a, "save_debug_train_data", None) is not None and "log_probs" not in data
             if capture:
                 enable_log_prob_capture()

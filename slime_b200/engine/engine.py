@@ -50,7 +50,8 @@ class Engine:
         self.eos_ids: set[int] = set()
         if tokenizer is not None and getattr(tokenizer, "eos_token_id", None) is not None:
             self.eos_ids.add(tokenizer.eos_token_id)
-        self.weights = EngineWeights(cfg, self.dtype, self.device, tp_size, tp_rank)
+        self.weights = EngineWeights(cfg, self.dtype, self.device, tp_size, tp_rank, ep_size=min(self.args.ep_size, tp_size),
+                                     quantization=self.args.quantization)
         self.max_context = self.args.context_length or min(cfg.max_position_embeddings, 32768)
         self.page_size = self.args.page_size
         self.max_running = self.args.max_running_requests
@@ -62,6 +63,8 @@ class Engine:
         self.runner = ModelRunner(cfg, self.weights, self.kv, self.max_running, self.max_context,
                                   use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
         self.runner._alloc_static()
+        self.runner.record_routed = bool(self.args.enable_return_routed_experts) and cfg.num_experts is not None
+        self.routed_hist: dict[int, torch.Tensor] = {}  # decode step -> [slots, moe layers * k] int32 on the host
         self.waiting: list[Request] = []
         self.running: list[Request] = []  # decoding (own a slot) until their results are finalised
         self.prefilling: list[Request] = []
@@ -176,7 +179,8 @@ class Engine:
             if first is not None and first in pending_first_hash:
                 still_waiting.append(req)
                 continue
-            want_cache = req.logprob_start_len < 0  # input log-probs need every position computed
+            # input log-probs and routed experts need every position computed
+            want_cache = req.logprob_start_len < 0 and not (req.return_routed_experts and self.runner.record_routed)
             pages, chain = self.kv.allocator.match_prefix(ctx) if want_cache else ([], b"")
             cached = len(pages) * ps
             total_pages = -(-(len(ctx) + 1) // ps)
@@ -237,6 +241,12 @@ class Engine:
         logits = self.runner.prefill(t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long),
                                      t(cu_k), max_q, max_k, rows, fresh)  # fmt: skip
         self.stats["prefill_tokens"] += len(ids)
+        routed = self.runner.take_routed()
+        if routed is not None:
+            routed = routed.cpu()
+            for (req, n), a in zip(batch, cu_q[:-1]):
+                if req.return_routed_experts:
+                    req.routed_experts.append(routed[a : a + n])
         if want_all_rows:
             self._record_input_logprobs(batch, logits, cu_q)
             logits = logits.index_select(0, t(last_rows, torch.long))
@@ -370,6 +380,11 @@ class Engine:
             from slime_b200.ops import _lib
 
             self.status_hist[slot : slot + 1].copy_(_lib.status_word(self.device), non_blocking=True)
+        if self.runner.last_routed is not None and any(r.return_routed_experts for r in self.running):
+            host = torch.empty(self.runner.last_routed[:n].shape, dtype=torch.int32, pin_memory=self.device.type == "cuda")
+            host.copy_(self.runner.last_routed[:n], non_blocking=True)  # ordered before the step's event
+            self.routed_hist[self.step_no] = host
+            self.stats["d2h_bytes"] += host.numel() * 4
         if self.device.type == "cuda":
             ev = torch.cuda.Event()
             ev.record()
@@ -391,6 +406,11 @@ class Engine:
             self._deactivate(b)
         # consume the previous step's results while this one runs
         finished += self._process_until(self.step_no - 1)
+        if (self.routed_hist or self.kept_hist) and self.step_no % 64 == 0:  # drop per-step records every reader is past
+            low = min((r.harvested for r in self.running), default=self.step_no)
+            for hist in (self.routed_hist, self.kept_hist):
+                for s_ in [s_ for s_ in hist if s_ < low]:
+                    del hist[s_]
         if self.step_no - min((r.harvested for r in self.running), default=self.step_no) > self.ring // 2:
             self._sync_results()
             for r in self.running:
@@ -478,6 +498,11 @@ class Engine:
                 c = max(int(kept[1][b]), 0)
                 r.kept_ids += kept[0][b, :c].tolist()
                 r.kept_offsets.append(len(r.kept_ids))
+        if r.return_routed_experts:
+            for s in range(r.harvested, upto):
+                hist = self.routed_hist.get(s)
+                if hist is not None and b < hist.shape[0]:
+                    r.routed_experts.append(hist[b : b + 1].clone())
         r.harvested = upto
         r.num_computed = len(r.input_ids) + len(r.output_ids) - 1
         self._commit_pages(r, None)
@@ -486,6 +511,7 @@ class Engine:
         """Return a decoding request to the queue: tokens generated so far are kept and re-prefilled later."""
         self._harvest(req, self.processed)
         self._release_slot(req)
+        req.routed_experts = []  # the re-prefill computes every position again
         self.kv.allocator.release(req.pages)
         req.pages, req.num_computed, req.committed_pages, req.chain_hash = [], 0, 0, b""
         req.state = ReqState.WAITING

@@ -28,29 +28,55 @@ _LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
 class EngineWeights:
     """Fused, TP-sharded weight buffers addressed by Hugging Face names."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp_size=1, tp_rank=0):
+    def __init__(self, cfg: ModelConfig, dtype, device, tp_size=1, tp_rank=0, ep_size=1, quantization: str | None = None):
+        """``quantization="fp8"`` keeps the projection matrices whose shapes allow it as block-scaled e4m3
+        (``engine/quant.py``); embeddings, the LM head, routers, norms and biases stay in ``dtype``.
+        ``ep_size`` is 1 (every rank holds all experts and computes all routes) or ``tp_size`` (rank r holds experts
+        ``r*E/ep ... (r+1)*E/ep - 1`` at full width; the ranks' expert outputs are summed like any row-parallel
+        projection). Same split as ``--sglang-ep-size`` with the all-reduce MoE path (scripts/models/qwen3-30B-A3B.sh and
+        tests/test_qwen3_30B_A3B.py:98-120 in the reference run rollout engines with ep 8)."""
         self.cfg, self.dtype, self.device, self.tp, self.rank = cfg, dtype, device, tp_size, tp_rank
+        if ep_size not in (1, tp_size):
+            raise ValueError(f"engine expert parallelism must be 1 or the engine's size ({tp_size}), got {ep_size}")
+        self.ep = ep_size
+        if cfg.num_experts is not None and cfg.num_experts % ep_size:
+            raise ValueError(f"{cfg.num_experts} experts do not divide over {ep_size} ranks")
+        self.experts_local = None if cfg.num_experts is None else cfg.num_experts // ep_size
+        self.first_expert = 0 if cfg.num_experts is None or ep_size == 1 else tp_rank * self.experts_local
         h, d = cfg.hidden_size, cfg.head_dim
         self.hq, self.hkv = cfg.num_attention_heads // tp_size, max(cfg.num_query_groups // tp_size, 1)
         self.f = cfg.ffn_hidden_size // tp_size
         self.vocab_local = cfg.padded_vocab_size // tp_size
         e = lambda *s: torch.zeros(*s, dtype=dtype, device=device)  # noqa: E731
+        if quantization not in (None, "fp8"):
+            raise ValueError(f"unknown engine quantization {quantization!r} (None or 'fp8')")
+        self.quantization = quantization
+
+        def mat(*shape, parts=()):
+            """A projection matrix: fp8 when asked for and every separately loaded row range starts on a scale block."""
+            from slime_b200.engine import quant
+
+            if quantization == "fp8" and quant.supported(shape[-2], shape[-1], parts):
+                return quant.Fp8Weight(*shape, device=device)
+            return e(*shape)
+
         self.embed = e(self.vocab_local, h)
         self.lm_head = self.embed if cfg.tie_word_embeddings else e(self.vocab_local, h)
         self.final_norm = e(h)
         self.layers = []
         for i in range(cfg.num_layers):
             L = {
-                "ln1": e(h), "qkv": e((self.hq + 2 * self.hkv) * d, h), "o": e(h, self.hq * d), "ln2": e(h),
+                "ln1": e(h), "qkv": mat((self.hq + 2 * self.hkv) * d, h, parts=(self.hq * d, (self.hq + self.hkv) * d)),
+                "o": mat(h, self.hq * d), "ln2": e(h),
                 "qkv_bias": e((self.hq + 2 * self.hkv) * d) if cfg.add_qkv_bias else None,
                 "q_norm": e(d) if cfg.qk_layernorm else None, "k_norm": e(d) if cfg.qk_layernorm else None,
             }  # fmt: skip
             if cfg.is_moe_layer(i):
-                el = cfg.num_experts  # TODO(ep): shard experts over the engine's EP group
+                el = self.experts_local
                 fe = cfg.moe_ffn_hidden_size
-                L.update(router=e(cfg.num_experts, h), w13=e(el, 2 * fe, h), w2=e(el, h, fe))
+                L.update(router=e(cfg.num_experts, h), w13=mat(el, 2 * fe, h, parts=(fe,)), w2=mat(el, h, fe))
             else:
-                L.update(gate_up=e(2 * self.f, h), down=e(h, self.f))
+                L.update(gate_up=mat(2 * self.f, h, parts=(self.f,)), down=mat(h, self.f))
             self.layers.append(L)
         self.version = "default"
 
@@ -68,7 +94,11 @@ class EngineWeights:
         yield self.final_norm
         for L in self.layers:
             for v in L.values():
-                if v is not None:
+                if v is None:
+                    continue
+                if hasattr(v, "tensors"):  # a quantised matrix: its bytes and its scales
+                    yield from v.tensors()
+                else:
                     yield v
 
     # -- loading -----------------------------------------------------------------------
@@ -78,6 +108,7 @@ class EngineWeights:
 
     def load_weight(self, name: str, t: torch.Tensor):
         cfg, d = self.cfg, self.cfg.head_dim
+        raw = t
         t = t.to(self.device, self.dtype, non_blocking=True)
         if name == "model.embed_tokens.weight":
             self.embed[: min(self.vocab_local, t.shape[0] - self.rank * self.vocab_local)].copy_(
@@ -100,41 +131,73 @@ class EngineWeights:
         sub = m.group(2)
         hq, hkv = self.hq, self.hkv
         q_rows, kv_rows = hq * d, hkv * d
-        table = {
+        vectors = {
             "input_layernorm.weight": lambda: L["ln1"].copy_(t),
             "post_attention_layernorm.weight": lambda: L["ln2"].copy_(t),
-            "self_attn.q_proj.weight": lambda: L["qkv"][:q_rows].copy_(self._rows(t, q_rows)),
-            "self_attn.k_proj.weight": lambda: L["qkv"][q_rows : q_rows + kv_rows].copy_(self._rows(t, kv_rows)),
-            "self_attn.v_proj.weight": lambda: L["qkv"][q_rows + kv_rows :].copy_(self._rows(t, kv_rows)),
-            "self_attn.qkv_proj.weight": lambda: L["qkv"].copy_(t),  # already fused + sharded for this rank
             "self_attn.q_proj.bias": lambda: L["qkv_bias"][:q_rows].copy_(self._rows(t, q_rows)),
             "self_attn.k_proj.bias": lambda: L["qkv_bias"][q_rows : q_rows + kv_rows].copy_(self._rows(t, kv_rows)),
             "self_attn.v_proj.bias": lambda: L["qkv_bias"][q_rows + kv_rows :].copy_(self._rows(t, kv_rows)),
             "self_attn.qkv_proj.bias": lambda: L["qkv_bias"].copy_(t),
-            "self_attn.o_proj.weight": lambda: L["o"].copy_(t[:, self.rank * q_rows : (self.rank + 1) * q_rows]),
             "self_attn.q_norm.weight": lambda: L["q_norm"].copy_(t),
             "self_attn.k_norm.weight": lambda: L["k_norm"].copy_(t),
-            "mlp.gate_proj.weight": lambda: L["gate_up"][: self.f].copy_(self._rows(t, self.f)),
-            "mlp.up_proj.weight": lambda: L["gate_up"][self.f :].copy_(self._rows(t, self.f)),
-            "mlp.gate_up_proj.weight": lambda: L["gate_up"].copy_(t),
-            "mlp.down_proj.weight": lambda: L["down"].copy_(t[:, self.rank * self.f : (self.rank + 1) * self.f]),
             "mlp.gate.weight": lambda: L["router"].copy_(t),
         }
-        if sub in table:
-            table[sub]()
+        if sub in vectors:
+            vectors[sub]()
             return True
-        em = re.match(r"^mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$", sub)
-        if em:
-            e, kind = int(em.group(1)), em.group(2)
+        # matrices: (buffer, first row in the buffer, rows there, how the incoming tensor is cut for this rank:
+        # 0 = by rows, 1 = by columns, None = already this rank's)
+        f = self.f
+        matrices = {
+            "self_attn.q_proj": ("qkv", 0, q_rows, 0), "self_attn.k_proj": ("qkv", q_rows, kv_rows, 0),
+            "self_attn.v_proj": ("qkv", q_rows + kv_rows, kv_rows, 0), "self_attn.qkv_proj": ("qkv", 0, q_rows + 2 * kv_rows, None),
+            "self_attn.o_proj": ("o", 0, cfg.hidden_size, 1), "mlp.gate_proj": ("gate_up", 0, f, 0),
+            "mlp.up_proj": ("gate_up", f, f, 0), "mlp.gate_up_proj": ("gate_up", 0, 2 * f, None),
+            "mlp.down_proj": ("down", 0, cfg.hidden_size, 1),
+        }  # fmt: skip
+        stem, _, kind = sub.rpartition(".")
+        buf = None
+        if stem in matrices and kind in ("weight", "weight_scale_inv"):
+            key, r0, rows, cut = matrices[stem]
+            if key not in L:
+                return False
+            buf = L[key]
+        else:
+            em = re.match(r"^mlp\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)$", stem)
+            if em is None or kind not in ("weight", "weight_scale_inv") or "w13" not in L:
+                return False
+            e, which = int(em.group(1)) - self.first_expert, em.group(2)
+            if not 0 <= e < self.experts_local:
+                return True  # another rank's expert
             fe = cfg.moe_ffn_hidden_size
-            if kind == "gate_proj":
-                L["w13"][e, :fe].copy_(t)
-            elif kind == "up_proj":
-                L["w13"][e, fe:].copy_(t)
+            buf = L["w13"][e] if which != "down_proj" else L["w2"][e]
+            r0, rows, cut = (fe if which == "up_proj" else 0), (cfg.hidden_size if which == "down_proj" else fe), None
+        self._put(buf, r0, rows, cut, t, raw, scale=kind == "weight_scale_inv")
+        return True
+
+    def _put(self, buf, r0: int, rows: int, cut, t, raw, scale: bool):
+        """Write this rank's part of an incoming matrix (or of its block scales) into rows ``[r0, r0 + rows)`` of ``buf``."""
+        from slime_b200.engine.quant import BLOCK, Fp8Weight
+
+        fp8_in = raw.dtype == torch.float8_e4m3fn
+        src = raw.to(self.device, non_blocking=True) if (scale or fp8_in) else t
+        unit = BLOCK if scale else 1  # scale tensors count in blocks of 128 rows / columns
+        if cut == 0:
+            n = -(-rows // unit)
+            src = src[self.rank * n : (self.rank + 1) * n]
+        elif cut == 1:
+            cols = buf.shape[-1] // unit
+            src = src[:, self.rank * cols : (self.rank + 1) * cols]
+        if isinstance(buf, Fp8Weight):
+            if scale:
+                buf.load_scale_rows(r0, src)
             else:
-                L["w2"][e].copy_(t)
-            return True
-        return False
+                buf.load_rows(r0, src)
+            return
+        if scale or fp8_in:
+            raise ValueError("block-fp8 weights were sent to an engine that keeps this matrix in bf16; start it with "
+                             "quantization='fp8' (and shapes that are multiples of 128) or send bf16 weights")
+        buf[r0 : r0 + src.shape[0]].copy_(src)
 
     def load_weights(self, named_tensors, version: str | None = None):
         missing = [n for n, t in named_tensors if not self.load_weight(n, t)]
@@ -143,15 +206,40 @@ class EngineWeights:
         return missing
 
     def init_random(self, seed: int = 0, std: float = 0.02):
+        from slime_b200.engine.quant import Fp8Weight
+
         g = torch.Generator(device=self.device).manual_seed(seed)
+        quantised = [v for L in self.layers for v in L.values() if isinstance(v, Fp8Weight)]
+        skip = {t.data_ptr() for v in quantised for t in v.tensors()}
         for t in self.tensors():
+            if t.data_ptr() in skip:
+                continue
             if t.dim() == 1:
                 t.fill_(1.0)
             else:
                 t.copy_(torch.empty(t.shape, dtype=torch.float32, device=self.device).normal_(0, std, generator=g))
+        for v in quantised:
+            v.fill_random_(std, g)
         for L in self.layers:
             if L.get("qkv_bias") is not None:
                 L["qkv_bias"].zero_()
+
+
+def _linear(x, w, bias=None, out_dtype=None, out=None):
+    """``x @ w^T`` for a bf16 matrix (tcgen05 bf16 GEMM) or a block-fp8 one (activation quantised here, fp8 GEMM)."""
+    if isinstance(w, torch.Tensor):
+        return ops.gemm(x, w, bias=bias, out_dtype=out_dtype, out=out)
+    from slime_b200.engine import quant
+
+    return quant.linear(x, w, bias=bias, out_dtype=out_dtype, out=out)
+
+
+def _grouped_linear(x, w, lay):
+    from slime_b200.ops import grouped
+
+    if isinstance(w, torch.Tensor):
+        return grouped.grouped_gemm(x, w, lay)
+    return grouped.grouped_gemm_fp8(x, w.q, w.scale, lay, out_dtype=x.dtype)
 
 
 class ModelRunner:
@@ -187,6 +275,24 @@ class ModelRunner:
         if max_batch not in self.graph_buckets:
             self.graph_buckets.append(max_batch)
         self._static = None
+        # expert choices of the tokens of the current forward pass, one [T, k] tensor per MoE layer (routing replay)
+        self.record_routed = False
+        self._moe_layer_idx = torch.tensor([i for i in range(cfg.num_layers) if cfg.is_moe_layer(i)], dtype=torch.long,
+                                           device=self.device)  # fmt: skip
+        self._routed: list[torch.Tensor] = []
+        self.last_routed = None
+
+    def take_routed(self):
+        """``[T, layers, k]`` int32 expert ids of the pass just run, one column per layer of the model (zeros for dense
+        layers: the consumer indexes by layer number); None when not recording."""
+        if not self._routed:
+            return None
+        picked = torch.stack(self._routed, 1)
+        self._routed = []
+        if self._moe_layer_idx.numel() == self.cfg.num_layers:
+            return picked
+        out = picked.new_zeros(picked.shape[0], self.cfg.num_layers, picked.shape[2])
+        return out.index_copy_(1, self._moe_layer_idx, picked)  # the index lives on the device: capturable
 
     # ------------------------------------------------------------------ layer math
     def _tp_reduce(self, x):
@@ -212,15 +318,15 @@ class ModelRunner:
     def _row_parallel_norm(self, inp, weight, ln, res, T: int):
         """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual)."""
         if self._fused_tp is not None and T <= self._fused_tp.max_tokens:
-            ops.gemm(inp, weight, out=self._fused_tp.partial(T))
+            _linear(inp, weight, out=self._fused_tp.partial(T))
             return self._fused_tp(T, res, ln, self.cfg.norm_epsilon)
-        x = self._tp_reduce(ops.gemm(inp, weight, out_dtype=self._proj_dtype))
+        x = self._tp_reduce(_linear(inp, weight, out_dtype=self._proj_dtype))
         return ops.rmsnorm(x, ln, self.cfg.norm_epsilon, res)
 
     def _mlp(self, L, x):
         if "gate_up" in L:
-            act = ops.swiglu(ops.gemm(x, L["gate_up"]))
-            return self._tp_reduce(ops.gemm(act, L["down"], out_dtype=self._proj_dtype))
+            act = ops.swiglu(_linear(x, L["gate_up"]))
+            return self._tp_reduce(_linear(act, L["down"], out_dtype=self._proj_dtype))
         return self._moe(L, x)
 
     def _moe(self, L, x):
@@ -231,19 +337,20 @@ class ModelRunner:
         probs, idx = grouped.route_topk(logits, cfg.moe_router_topk, score=cfg.moe_router_score_function,
                                         pre_softmax=cfg.moe_router_pre_softmax, renorm=cfg.norm_topk_prob,
                                         bias=L.get("router_bias"), scale=cfg.moe_router_topk_scaling_factor)  # fmt: skip
-        self._last_routed = idx
+        if self.record_routed:
+            self._routed.append(idx.to(torch.int32))
         # expert-sorted, tile-padded layout built on the device (no host sync: the step stays graph-capturable), then
         # one grouped GEMM per projection over all experts
 
-        lay = grouped.DeviceLayout(idx, L["w13"].shape[0])
-        act = ops.swiglu(grouped.grouped_gemm(lay.pad(x), L["w13"], lay))
-        return lay.combine(grouped.grouped_gemm(act, L["w2"], lay), probs, x.shape[0])
+        lay = grouped.DeviceLayout(idx, L["w13"].shape[0], self.w.first_expert)
+        y = lay.combine(_grouped_linear(ops.swiglu(_grouped_linear(lay.pad(x), L["w13"], lay)), L["w2"], lay), probs, x.shape[0])
+        return self._tp_reduce(y) if self.w.ep > 1 else y
 
     def _qkv(self, L, normed, positions, slots, li):
         """Packed q / k / v of the new tokens, rotated (and per-head normalised) in place, k and v also written to
         their cache slots of layer ``li``: one GEMM and one fused launch."""
         cfg = self.cfg
-        qkv = ops.gemm(normed, L["qkv"], bias=L["qkv_bias"])
+        qkv = _linear(normed, L["qkv"], bias=L["qkv_bias"])
         return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[li], self.kv.v[li], self.w.hq, self.w.hkv,
                                  cfg.head_dim, L["q_norm"], L["k_norm"], cfg.norm_epsilon)  # fmt: skip
 
@@ -273,7 +380,7 @@ class ModelRunner:
                 k_all = self.kv.k[li].index_select(0, kv_gather_slots)
                 v_all = self.kv.v[li].index_select(0, kv_gather_slots)
                 ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale)
-            x = self._tp_reduce(ops.gemm(ctx.reshape(T, -1), L["o"], out_dtype=self._proj_dtype))
+            x = self._tp_reduce(_linear(ctx.reshape(T, -1), L["o"], out_dtype=self._proj_dtype))
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._mlp(L, normed)
         h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
@@ -371,7 +478,7 @@ class ModelRunner:
             # the norm that follows the MLP is the next layer's input norm (or the final norm)
             next_ln = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.final_norm
             if "gate_up" in L:
-                act = ops.swiglu(ops.gemm(normed, L["gate_up"]))
+                act = ops.swiglu(_linear(normed, L["gate_up"]))
                 normed, res = self._row_parallel_norm(act, L["down"], next_ln, res, n)
             else:
                 normed, res = ops.rmsnorm(self._moe(L, normed), next_ln, cfg.norm_epsilon, res)
@@ -381,6 +488,7 @@ class ModelRunner:
             logits, st["temperature"][:n], st["top_k"][:n] if filtered else None, st["top_p"][:n] if filtered else None,
             st["min_p"][:n] if filtered else None, st["seeds"][:n], ds["out_pos"][:n], kept_cap,
         )  # fmt: skip
+        routed = self.take_routed()
         if self.device.type == "cuda":
             _lib.check(_lib.lib().sb_decode_advance(P(ds["ids"]), P(ds["pos"]), P(ds["out_pos"]), P(st["active"]), P(tok), n,
                                                     _lib.stream()), "sb_decode_advance")  # fmt: skip
@@ -389,7 +497,7 @@ class ModelRunner:
             ds["ids"][:n] = torch.where(act, tok, ds["ids"][:n])
             ds["pos"][:n] += act.int()
             ds["out_pos"][:n] += act.int()
-        return tok, lp, kept_ids, kept_cnt
+        return tok, lp, kept_ids, kept_cnt, routed
 
     def _prepare_reference(self, n):
         st, ds = self._static, self._dev_state
@@ -409,9 +517,12 @@ class ModelRunner:
     @torch.no_grad()
     def decode(self, n: int, filtered: bool, kept_cap: int = 0):
         """One decode step over slots [0, n) (host state must have been uploaded). Under CUDA graphs the
-        step is one replay of the bucket that covers ``n``; extra slots are inactive by construction."""
-        if not self.use_cuda_graph or self.cfg.num_experts is not None:
-            return self._decode_step(n, filtered, kept_cap)
+        step is one replay of the bucket that covers ``n``; extra slots are inactive by construction. MoE layers are
+        captured too: their expert-sorted layout is built on the device with static shapes. ``last_routed`` holds the
+        step's expert choices when ``record_routed`` is set (a buffer of the graph: copy it before the next replay)."""
+        if not self.use_cuda_graph:
+            *outs, self.last_routed = self._decode_step(n, filtered, kept_cap)
+            return tuple(outs)
         bucket = next(b for b in self.graph_buckets if b >= n)
         key = (bucket, filtered, kept_cap)
         if key not in self.graphs:
@@ -419,7 +530,8 @@ class ModelRunner:
         graph, outs, n_kernels = self.graphs[key]
         self.replayed_launches += n_kernels
         graph.replay()
-        return outs
+        self.last_routed = outs[4]
+        return outs[:4]
 
     def _capture(self, bucket, filtered, kept_cap):
         """Capture one decode step. Warm-up and capture run with every slot inactive, so they only touch the

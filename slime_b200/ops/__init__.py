@@ -560,13 +560,25 @@ def sample(logits, temperature, top_k=None, top_p=None, min_p=None, seeds=None, 
 
 
 # ----------------------------------------------------------------- quantisers
-def block_fp8_quant(x, block=(128, 128), pow2_scale=False):
+def block_fp8_quant(x, block=(128, 128), pow2_scale=False, out=None):
+    """Block-scaled e4m3 of ``x`` [M, N]: ``(q, scale_inv [ceil(M/bm), ceil(N/bn)])``. ``out=(q, scale_inv)`` writes into
+    existing contiguous tensors (the engine's resident fp8 buffers during a weight sync) instead of allocating."""
     if not _cuda(x):
-        return reference.block_fp8_quant(x, block, pow2_scale)
+        q, s = reference.block_fp8_quant(x, block, pow2_scale)
+        if out is not None:
+            out[0].copy_(q)
+            out[1].copy_(s)
+            return out
+        return q, s
     x = x.contiguous()
     M, N = x.shape
-    q = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
-    s = torch.empty(-(-M // block[0]), -(-N // block[1]), dtype=torch.float32, device=x.device)
+    if out is not None:
+        q, s = out
+        assert q.is_contiguous() and s.is_contiguous() and q.shape == x.shape and s.dtype == torch.float32
+        assert tuple(s.shape) == (-(-M // block[0]), -(-N // block[1]))
+    else:
+        q = torch.empty(M, N, dtype=torch.float8_e4m3fn, device=x.device)
+        s = torch.empty(-(-M // block[0]), -(-N // block[1]), dtype=torch.float32, device=x.device)
     rc = _lib.lib().sb_block_fp8_quant(P(x), P(q), P(s), M, N, x.stride(0), q.stride(0), block[0], block[1],
                                        int(pow2_scale), _lib.stream())
     _lib.check(rc, "sb_block_fp8_quant")

@@ -39,6 +39,7 @@ _SIGS = {
     "sb_moe_gather_sum": [P, P, P, P, L, I, I, I, P],
     "sb_moe_route_weight_grad": [P, P, P, P, L, I, I, P],
     "sb_gemm_fp8_block": [P, P, P, P, P, I, I, I, I, I, I, I, P, I, P],
+    "sb_gemm_fp8_grouped": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, I, P],
     
     "sb_gemm_bf16_grouped": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, I, P],
     "sb_gemm_bf16_splitk": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, I, P, I, P],

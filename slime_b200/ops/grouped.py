@@ -179,18 +179,25 @@ class DeviceLayout:
     tiles past the last used row are zero rows attached to the last expert (they cost a little compute, nothing else).
     """
 
-    def __init__(self, idx: torch.Tensor, num_experts: int):
+    def __init__(self, idx: torch.Tensor, num_experts: int, first_expert: int = 0):
+        """``num_experts`` experts live here, global ids ``first_expert ...``; routes to other experts get no row
+        (``slot_dest = -1``: the permutation kernels skip them), which is all expert parallelism needs when the
+        activations are replicated over the group and the outputs are summed over it afterwards."""
         T, k = idx.shape
         dev = idx.device
-        flat = idx.reshape(-1).long()
+        flat = idx.reshape(-1).long() - first_expert
+        here = (flat >= 0) & (flat < num_experts)
+        key = torch.where(here, flat, torch.full_like(flat, num_experts))  # routes served elsewhere sort to the end
         self.k, self.num_experts = k, num_experts
-        self.order = torch.argsort(flat, stable=True)  # assignments grouped by expert, token order kept inside a group
-        sorted_e = flat.index_select(0, self.order)
-        counts = torch.bincount(flat, minlength=num_experts)
+        self.order = torch.argsort(key, stable=True)  # assignments grouped by expert, token order kept inside a group
+        sorted_e = key.index_select(0, self.order)
+        # counts by scatter-add: fixed output size, no host synchronisation (bincount reads its maximum on the host)
+        counts = torch.zeros(num_experts + 1, dtype=torch.long, device=dev).scatter_add_(0, key, torch.ones_like(key))[:num_experts]
         padded = (counts + (TILE - 1)) // TILE * TILE
         pend = torch.cumsum(padded, 0)
-        shift = (pend - padded) - (torch.cumsum(counts, 0) - counts)
-        self.dest = torch.arange(flat.numel(), device=dev) + shift.index_select(0, sorted_e)
+        shift = torch.cat([(pend - padded) - (torch.cumsum(counts, 0) - counts), torch.zeros(1, dtype=torch.long, device=dev)])
+        dest = torch.arange(flat.numel(), device=dev) + shift.index_select(0, sorted_e)
+        self.dest = torch.where(sorted_e < num_experts, dest, torch.full_like(dest, -1))
         # the same destinations in slot order (slot s = token s // k, route s % k): what the permutation kernels index by
         self.slot_dest = torch.empty(flat.numel(), dtype=torch.int32, device=dev)
         self.slot_dest[self.order] = self.dest.to(torch.int32)
@@ -256,6 +263,39 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay, *, b_mn: bool = False, o
         int(out_dtype == torch.float32), _pick_bn(M, N), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
     )  # fmt: skip
     _lib.check(rc, "sb_gemm_bf16_grouped")
+    return out
+
+
+def grouped_gemm_fp8(a: torch.Tensor, w_q: torch.Tensor, w_scale: torch.Tensor, lay, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """``out[rows of e] = a[rows of e] @ dequant(w_q[e], w_scale[e])^T`` for block-quantised expert weights.
+
+    ``a`` [rows_padded, K] bf16 is quantised here to e4m3 with one scale per row and 128-wide K group; ``w_q`` [E, N, K]
+    e4m3 with ``w_scale`` [E, ceil(N/128), K/128] (128 x 128 blocks, as block-fp8 checkpoints store them). One launch
+    of the tcgen05 fp8 kernel over all experts; on CPU the dequantised fp32 product per tile. Same role as the grouped
+    fp8 GEMM of the reference's rollout engines (slime/backends/megatron_utils/alignment/deepgemm_moe_forward.py:371-468).
+    """
+    from slime_b200 import ops
+
+    E, N, K = w_q.shape
+    M = a.shape[0]
+    assert M == lay.rows_padded and E == lay.num_experts and a.shape[1] == K and K % 128 == 0
+    a_q, a_s, a_st = ops.fp8_act_quant(a)
+    if not a.is_cuda:
+        out = torch.zeros(M, N, dtype=torch.float32)
+        a_f = a_q.float() * a_s.repeat_interleave(128, 1)
+        for t, e in enumerate(lay.tile_expert.tolist()):
+            we = ops.reference.block_fp8_dequant(w_q[e], w_scale[e], (128, 128), torch.float32)
+            out[t * TILE : (t + 1) * TILE] = a_f[t * TILE : (t + 1) * TILE] @ we.t()
+        return out.to(out_dtype)
+    out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    if M == 0:
+        return out
+    boff = lay.tile_expert * N
+    rc = _lib.lib().sb_gemm_fp8_grouped(
+        P(a_q), P(w_q), P(a_st), P(w_scale), P(out), P(boff), M, N, K, E, a_q.stride(0), w_q.stride(1), out.stride(0),
+        int(out_dtype == torch.float32), P(_lib.status_word(a.device)), _lib.sm_count(a.device), _lib.stream(),
+    )  # fmt: skip
+    _lib.check(rc, "sb_gemm_fp8_grouped")
     return out
 
 

@@ -5,7 +5,8 @@ are replayed in the training forward and in the backward recompute, so all three
 passes route identically. R3 (``--use-rollout-routing-replay``): the indices come
 from the rollout engine (``Sample.rollout_routed_experts``) instead.
 The stage is selected with ``ROUTING_REPLAY_STAGE`` in {fallthrough, record,
-replay_forward, replay_backward}. Parity: slime/utils/routing_replay.py:81-226.
+replay_forward, replay_backward}; under ``replay_forward`` a call made from inside the backward pass (a recomputed
+layer) reads the backward cursor by itself. Parity: slime/utils/routing_replay.py:81-226.
 """
 
 from __future__ import annotations
@@ -77,7 +78,10 @@ class RoutingReplay:
             self.record(idx)
             return idx
         if stage in ("replay_forward", "replay_backward"):
-            idx = (self.pop_forward() if stage == "replay_forward" else self.pop_backward()).to(scores.device, non_blocking=True)
+            # A layer re-run by activation recomputation executes inside the backward pass: it takes the backward
+            # cursor, so the forward cursor stays in step with the micro-batches whatever the recompute setting.
+            recomputing = stage == "replay_backward" or torch._C._current_graph_task_id() != -1
+            idx = (self.pop_backward() if recomputing else self.pop_forward()).to(scores.device, non_blocking=True)
             assert idx.shape[0] == scores.shape[0] and idx.shape[1] == k, (
                 f"replayed routing {tuple(idx.shape)} does not match scores {tuple(scores.shape)} (k={k})"
             )
@@ -91,9 +95,9 @@ def set_stage(stage: str):
 
 def fill_from_rollout(routed_experts: list[torch.Tensor], layer_ids: list[int]):
     """R3: load per-micro-batch routed experts ``[T, layers, k]`` into each layer's replay list."""
-    for li, layer in enumerate(layer_ids):
+    for layer in layer_ids:  # the rollout reports one column per layer of the model, dense ones included
         inst = RoutingReplay._by_layer.get(layer)
         if inst is None:
             continue
         for mb in routed_experts:
-            inst.top_indices_list.append(mb[:, li].contiguous())
+            inst.top_indices_list.append(mb[:, layer].contiguous())

@@ -191,7 +191,10 @@ class UpdateWeightFromTensor(WeightUpdaterBase):
         for e in self.engines:
             pairs = self._fused_pairs(e)
             assert pairs is not None, "engine and trainer shards differ in shape"
-            device_sync.copy_tensors(pairs)
+            device_sync.copy_tensors([(s, d) for s, d in pairs if isinstance(d, torch.Tensor)])
+            for s, d in pairs:  # block-fp8 engine buffers: quantised on the device straight into the resident bytes and scales
+                if not isinstance(d, torch.Tensor):
+                    d.load_rows(0, s)
 
 
 class UpdateWeightFromDistributed(WeightUpdaterBase):

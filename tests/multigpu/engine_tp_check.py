@@ -28,8 +28,16 @@ def hf_weights(cfg, device, seed=0):
         out += [(p + "input_layernorm.weight", 1 + mat(h)), (p + "post_attention_layernorm.weight", 1 + mat(h)),
                 (p + "self_attn.q_proj.weight", mat(nq * d, h)), (p + "self_attn.k_proj.weight", mat(nkv * d, h)),
                 (p + "self_attn.v_proj.weight", mat(nkv * d, h)), (p + "self_attn.o_proj.weight", mat(h, nq * d)),
-                (p + "mlp.gate_proj.weight", mat(f, h)), (p + "mlp.up_proj.weight", mat(f, h)),
-                (p + "mlp.down_proj.weight", mat(h, f))]  # fmt: skip
+                ]  # fmt: skip
+        if cfg.is_moe_layer(i):
+            fe = cfg.moe_ffn_hidden_size
+            out.append((p + "mlp.gate.weight", mat(cfg.num_experts, h, std=0.5)))
+            for e in range(cfg.num_experts):
+                out += [(p + f"mlp.experts.{e}.gate_proj.weight", mat(fe, h)), (p + f"mlp.experts.{e}.up_proj.weight", mat(fe, h)),
+                        (p + f"mlp.experts.{e}.down_proj.weight", mat(h, fe))]  # fmt: skip
+        else:
+            out += [(p + "mlp.gate_proj.weight", mat(f, h)), (p + "mlp.up_proj.weight", mat(f, h)),
+                    (p + "mlp.down_proj.weight", mat(h, f))]  # fmt: skip
         if cfg.add_qkv_bias:
             out += [(p + "self_attn.q_proj.bias", mat(nq * d)), (p + "self_attn.k_proj.bias", mat(nkv * d)),
                     (p + "self_attn.v_proj.bias", mat(nkv * d))]  # fmt: skip
@@ -57,8 +65,13 @@ def main():
     dev = torch.device("cpu") if cpu else torch.device("cuda", local)
     cfg = ModelConfig(num_layers=4, hidden_size=512, num_attention_heads=8, num_query_groups=4, kv_channels=64,
                       ffn_hidden_size=1024, vocab_size=2048, rotary_base=1e4, tie_word_embeddings=False, add_qkv_bias=True)
+    moe = os.environ.get("ENGINE_TP_CHECK_MOE") == "1"  # experts sharded over the engine's ranks, attention tensor-parallel
+    if moe:
+        cfg = ModelConfig(num_layers=3, hidden_size=512, num_attention_heads=8, num_query_groups=4, kv_channels=64,
+                          ffn_hidden_size=1024, vocab_size=2048, rotary_base=1e4, tie_word_embeddings=False, qk_layernorm=True,
+                          num_experts=8, moe_ffn_hidden_size=256, moe_router_topk=2, moe_layer_freq=[0, 1, 1])
     weights = hf_weights(cfg, dev)
-    sargs = dict(page_size=16, max_running_requests=16, context_length=256, disable_cuda_graph=cpu)
+    sargs = dict(page_size=16, max_running_requests=16, context_length=256, disable_cuda_graph=cpu, ep_size=world if moe else 1)
     prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + i)] for i in range(6)]
     sp = dict(max_new_tokens=24, temperature=0)
 
@@ -66,6 +79,8 @@ def main():
     missing = tp.weights.load_weights(weights)
     assert not missing, missing
     fused = tp.runner._fused_tp is not None
+    if moe:
+        assert tp.weights.ep == world and tp.weights.layers[1]["w13"].shape[0] == cfg.num_experts // world
     reqs = tp.generate(prompts, dict(sp, ignore_eos=True))
     out_tp = [r.output_ids for r in reqs]
     lp_tp = [r.output_logprobs for r in reqs]
@@ -73,7 +88,7 @@ def main():
         torch.cuda.synchronize()
         _lib.check_status(dev)
     if rank == 0:
-        one = Engine(cfg, ServerArgs(**sargs), device=dev, num_pages=128)
+        one = Engine(cfg, ServerArgs(**dict(sargs, ep_size=1)), device=dev, num_pages=128)
         assert not one.weights.load_weights(weights)
         if cpu:  # fp32 reference ops on both sides: greedy decoding must agree token for token
             out_one = [r.output_ids for r in one.generate(prompts, dict(sp, ignore_eos=True))]
@@ -85,8 +100,8 @@ def main():
             rq = one.generate([p + o], [dict(max_new_tokens=0)], logprob_start_len=0)[0]
             ref = torch.tensor(rq.input_logprobs[len(p):])
             worst = max(worst, float((ref - torch.tensor(lp)).abs().max()))
-        assert worst < (1e-4 if cpu else 0.08), worst
-        print(f"RESULT ok world={world} fused_tp={fused} max_logprob_diff={worst:.4f}", flush=True)
+        assert worst < (1e-4 if cpu else (0.25 if moe else 0.08)), worst  # bf16 router near-ties move a route now and then
+        print(f"RESULT ok world={world} fused_tp={fused} moe_ep={world if moe else 0} max_logprob_diff={worst:.4f}", flush=True)
     from slime_b200.utils.distributed_utils import shutdown_distributed
 
     shutdown_distributed([tp])

@@ -28,3 +28,13 @@ def test_model_under_parallel_layout_matches_single_rank_oracle(mode, world, por
                         "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests/multigpu/model_parallel_check.py")],
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)  # fmt: skip
     assert r.returncode == 0 and f"RESULT ok mode={mode} world={world}" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
+def test_colocated_moe_with_fp8_engine_and_rollout_routing_replay():
+    """Two gloo ranks: expert-parallel trainer, one block-fp8 rollout engine per rank, routers replaying the engine's
+    expert choices through forward, log-prob pass and recomputed backward."""
+    env = dict(os.environ, DEVICE="cpu", MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", "29699", os.path.join(ROOT, "tests/multigpu/colocated_moe_check.py")],
+                       env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)  # fmt: skip
+    assert r.returncode == 0 and "RESULT ok world=2 ep=2" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]

@@ -190,15 +190,65 @@ def test_openai_compatible_endpoints():
         srv.shutdown()
 
 
-def test_tensor_parallel_engine_on_gloo_matches_single_rank():
-    """Two gloo ranks: TP weight slicing, row-parallel reductions and the vocab-parallel logits gather (host logic)."""
+@pytest.mark.parametrize("moe", [False, True], ids=["dense", "moe_ep2"])
+def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe):
+    """Two gloo ranks: TP weight slicing, row-parallel reductions and the vocab-parallel logits gather (host logic);
+    with ``moe`` also experts sharded over the two ranks (each rank serves its own experts' routes, outputs summed)."""
     import os
     import subprocess
     import sys
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, ENGINE_TP_CHECK_DEVICE="cpu", MASTER_ADDR="127.0.0.1")
+    env = dict(os.environ, ENGINE_TP_CHECK_DEVICE="cpu", MASTER_ADDR="127.0.0.1", ENGINE_TP_CHECK_MOE=str(int(moe)))
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-                        "127.0.0.1", "--master-port", "29671", os.path.join(root, "tests/multigpu/engine_tp_check.py")],
+                        "127.0.0.1", "--master-port", str(29671 + int(moe)), os.path.join(root, "tests/multigpu/engine_tp_check.py")],
                        env=env, cwd=root, capture_output=True, text=True, timeout=280)  # fmt: skip
     assert r.returncode == 0 and "RESULT ok world=2" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def make_moe_engine(**kw):
+    cfg = get_preset("tiny-moe")
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=8, context_length=128, disable_cuda_graph=True, **kw),
+               device="cpu", num_pages=96)  # fmt: skip
+    e.weights.init_random(0, std=0.2)
+    return e
+
+
+def test_moe_engine_returns_routed_experts_for_every_fed_token():
+    e = make_moe_engine(enable_return_routed_experts=True)
+    cfg = e.cfg
+    p = [1, 2, 3, 4, 5, 6, 7, 8, 9]
+    a, b = e.generate([p, p[:5]], [dict(max_new_tokens=6, ignore_eos=True, sampling_seed=3)] * 2, return_routed_experts=True)
+    for r in (a, b):
+        routed = torch.cat(r.routed_experts)
+        n = len(r.input_ids) + len(r.output_ids) - 1  # the last sampled token is never fed to the model
+        assert routed.shape == (n, cfg.num_layers, cfg.moe_router_topk) and routed.dtype == torch.int32
+        assert int(routed.min()) >= 0 and int(routed.max()) < cfg.num_experts
+        # teacher forcing over the same tokens takes the same routes
+        again = e.generate([r.input_ids + r.output_ids], [dict(max_new_tokens=0)], logprob_start_len=0, return_routed_experts=True)[0]
+        assert torch.equal(torch.cat(again.routed_experts)[:n], routed)
+        meta = e.meta_info(r)
+        from slime_b200.utils.misc import decode_int32_meta_array
+
+        assert decode_int32_meta_array(meta, "routed_experts").reshape(n, cfg.num_layers, -1).tolist() == routed.tolist()
+    # a request that does not ask for them gets none, and an engine that does not record keeps the prefix cache
+    c = e.generate([p], [dict(max_new_tokens=2, ignore_eos=True)])[0]
+    assert c.routed_experts == [] and "routed_experts" not in e.meta_info(c)
+
+
+def test_device_layout_skips_routes_of_other_ranks():
+    from slime_b200.ops import grouped
+
+    torch.manual_seed(0)
+    T, k, E, H = 37, 2, 8, 16
+    idx = torch.stack([torch.randperm(E)[:k] for _ in range(T)])
+    x, probs = torch.randn(T, H), torch.rand(T, k)
+    w = torch.randn(E, H, H)
+    full = grouped.DeviceLayout(idx, E)
+    ref = full.combine(grouped.grouped_gemm(full.pad(x), w, full), probs, T)
+    parts = []
+    for r in range(4):  # four expert-parallel ranks, two experts each: their partial outputs add up to the full result
+        lay = grouped.DeviceLayout(idx, E // 4, first_expert=r * 2)
+        assert int((lay.slot_dest >= 0).sum()) == int(((idx >= r * 2) & (idx < r * 2 + 2)).sum())
+        parts.append(lay.combine(grouped.grouped_gemm(lay.pad(x), w[r * 2 : r * 2 + 2], lay), probs, T))
+    assert torch.allclose(sum(parts), ref, atol=1e-5)

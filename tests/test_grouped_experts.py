@@ -202,3 +202,30 @@ def test_route_topk_kernel_matches_torch(kernels, E, k):
         w_ref, idx_ref = grouped.route_topk(logits.cpu(), k, **kw_cpu)
         assert torch.equal(idx.cpu(), idx_ref), kw  # random logits: no ties, the order of the picks is the same
         torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-4, atol=1e-6)
+
+
+@pytest.mark.gpu
+def test_moe_engine_decode_in_cuda_graphs_matches_eager_launches(kernels):
+    """The MoE decode step is captured like the dense one (its layout is built on the device with static shapes): the
+    replayed step draws the same tokens, log-probs and expert choices as eager launches of the same kernels."""
+    from slime_b200.engine.engine import Engine
+    from slime_b200.engine.server_args import ServerArgs
+    from slime_b200.models.config import get_preset
+
+    prompts = [[(5 * i + 3 * j) % 500 for j in range(6 + i)] for i in range(4)]
+    got = []
+    for graphs in (False, True):
+        e = Engine(get_preset("tiny-moe"), ServerArgs(page_size=16, max_running_requests=4, context_length=128,
+                                                      disable_cuda_graph=not graphs, enable_return_routed_experts=True),
+                   device="cuda", num_pages=64)  # fmt: skip
+        e.weights.init_random(0, std=0.2)
+        reqs = e.generate(prompts, dict(max_new_tokens=10, temperature=0, ignore_eos=True), return_routed_experts=True)
+        assert bool(e.runner.graphs) == graphs
+        for r in reqs:
+            routed = torch.cat(r.routed_experts)
+            assert routed.shape == (len(r.input_ids) + len(r.output_ids) - 1, 2, 2)
+        got.append(([r.output_ids for r in reqs], [r.output_logprobs for r in reqs], [torch.cat(r.routed_experts) for r in reqs]))
+        e.shutdown()
+    assert got[0][0] == got[1][0]
+    assert max(abs(a - b) for x, y in zip(got[0][1], got[1][1]) for a, b in zip(x, y)) < 1e-3
+    assert all(torch.equal(a, b) for a, b in zip(got[0][2], got[1][2]))
