@@ -39,9 +39,38 @@ class ModelConfig:
     moe_router_enable_expert_bias: bool = False
     moe_router_topk_scaling_factor: float | None = None
     moe_shared_expert_intermediate_size: int | None = None
+    moe_shared_expert_gate: bool = False  # Qwen3-Next: the shared expert's output is scaled by sigmoid(w_g . x)
+    moe_router_num_groups: int | None = None  # DeepSeek-V3: experts in groups, only the best groups are eligible
+    moe_router_group_topk: int | None = None
     moe_layer_freq: int | list | None = None
     moe_aux_loss_coeff: float = 0.0
     norm_topk_prob: bool = True
+    # attention variants (models/mixers.py)
+    rotary_percent: float = 1.0  # fraction of the head dim that is rotated (GLM-4 family: 0.5)
+    rotary_interleaved: bool = False  # rotate (2i, 2i+1) pairs instead of (i, i + d/2)
+    attention_output_gate: bool = False  # Qwen3-Next: q projection carries a sigmoid gate for the attention output
+    qk_layernorm_full: bool = False  # MiniMax-M2: RMSNorm over all heads of q (and of k) at once instead of per head
+    softmax_sinks: bool = False  # learnable per-head sink logit in the softmax denominator
+    # gated delta-net linear attention (Qwen3-Next / Qwen3.5): layers with (i + 1) % full_attention_interval != 0
+    full_attention_interval: int | None = None
+    linear_num_key_heads: int | None = None
+    linear_num_value_heads: int | None = None
+    linear_key_head_dim: int | None = None
+    linear_value_head_dim: int | None = None
+    linear_conv_kernel_dim: int = 4
+    # multi-head latent attention (DeepSeek-V3 / Kimi-K2 / Moonlight / GLM-5)
+    multi_latent_attention: bool = False
+    q_lora_rank: int | None = None
+    kv_lora_rank: int | None = None
+    qk_head_dim: int | None = None  # the part of a query / key head without position information
+    qk_pos_emb_head_dim: int | None = None  # the rotated part, one key shared by all heads
+    v_head_dim: int | None = None
+    # sparse attention with a lightning indexer over MLA (GLM-5, DeepSeek-V3.2)
+    index_topk: int | None = None
+    index_n_heads: int | None = None
+    index_head_dim: int | None = None
+    index_topk_freq: int = 1  # a layer computes its own top-k when max(layer - offset, 0) % freq == 0, else reuses
+    index_skip_topk_offset: int = 0
     # multi-token prediction (draft head)
     mtp_num_layers: int | None = None
     model_arch: str = "qwen2"
@@ -68,14 +97,43 @@ class ModelConfig:
             return bool(f[layer])
         return layer % f == 0
 
-    def num_params(self) -> int:
+    def mixer(self, layer: int) -> str:
+        """Token mixer of a layer: ``attention`` (the fused kernel path), ``general_attention`` (attention variants
+        composed from separate ops), ``gated_delta_net``, ``mla`` or ``dsa``."""
+        if self.full_attention_interval and (layer + 1) % self.full_attention_interval != 0:
+            return "gated_delta_net"
+        if self.multi_latent_attention:
+            return "dsa" if self.index_topk else "mla"
+        if (self.rotary_percent < 1.0 or self.rotary_interleaved or self.attention_output_gate or self.qk_layernorm_full
+                or self.softmax_sinks):  # fmt: skip
+            return "general_attention"
+        return "attention"
+
+    def mixer_params(self, layer: int) -> int:
         h, d = self.hidden_size, self.head_dim
-        attn = h * d * (self.num_attention_heads + 2 * self.num_query_groups) + self.num_attention_heads * d * h
+        kind = self.mixer(layer)
+        if kind == "gated_delta_net":
+            kd, vd = self.linear_num_key_heads * self.linear_key_head_dim, self.linear_num_value_heads * self.linear_value_head_dim
+            return (h * (2 * kd + 2 * vd) + h * 2 * self.linear_num_value_heads + (2 * kd + vd) * self.linear_conv_kernel_dim
+                    + 2 * self.linear_num_value_heads + self.linear_value_head_dim + vd * h)  # fmt: skip
+        if kind in ("mla", "dsa"):
+            hq, dn, dr, dv = self.num_attention_heads, self.qk_head_dim, self.qk_pos_emb_head_dim, self.v_head_dim
+            q = (h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * hq * (dn + dr)) if self.q_lora_rank else h * hq * (dn + dr)
+            n = q + h * (self.kv_lora_rank + dr) + self.kv_lora_rank + self.kv_lora_rank * hq * (dn + dv) + hq * dv * h
+            if kind == "dsa":
+                n += self.index_n_heads * self.index_head_dim * self.q_lora_rank + self.index_head_dim * (h + 2) + self.index_n_heads * h
+            return n
+        n = h * d * ((2 if self.attention_output_gate else 1) * self.num_attention_heads + 2 * self.num_query_groups)
+        n += self.num_attention_heads * d * h
         if self.add_qkv_bias:
-            attn += d * (self.num_attention_heads + 2 * self.num_query_groups)
+            n += d * (self.num_attention_heads + 2 * self.num_query_groups)
+        return n
+
+    def num_params(self) -> int:
+        h = self.hidden_size
         total = 0
         for i in range(self.num_layers):
-            total += attn + 2 * h
+            total += self.mixer_params(i) + 2 * h
             if self.is_moe_layer(i):
                 total += self.num_experts * 3 * h * self.moe_ffn_hidden_size + self.num_experts * h
                 if self.moe_shared_expert_intermediate_size:
@@ -136,6 +194,39 @@ class ModelConfig:
             )
             if c.get("shared_expert_intermediate_size"):
                 kw["moe_shared_expert_intermediate_size"] = c["shared_expert_intermediate_size"]
+            if c.get("n_shared_experts"):  # DeepSeek-style: shared experts of the routed experts' width
+                kw["moe_shared_expert_intermediate_size"] = c["n_shared_experts"] * c["moe_intermediate_size"]
+            if c.get("first_k_dense_replace"):
+                k0 = c["first_k_dense_replace"]
+                kw["moe_layer_freq"] = [0] * k0 + [1] * (c["num_hidden_layers"] - k0)
+            if c.get("scoring_func") == "sigmoid":
+                kw.update(moe_router_score_function="sigmoid", moe_router_enable_expert_bias=c.get("topk_method") == "noaux_tc"
+                          or bool(c.get("use_routing_bias")))  # fmt: skip
+            if c.get("routed_scaling_factor"):
+                kw["moe_router_topk_scaling_factor"] = c["routed_scaling_factor"]
+            if c.get("n_group") and c.get("topk_group") and c["n_group"] > 1:
+                kw.update(moe_router_num_groups=c["n_group"], moe_router_group_topk=c["topk_group"])
+            if "qwen3next" in a or "qwen3_5" in a or "qwen3_next" in a:
+                kw["moe_shared_expert_gate"] = True
+        if c.get("partial_rotary_factor") and c["partial_rotary_factor"] < 1.0:
+            kw["rotary_percent"] = c["partial_rotary_factor"]
+        if a.startswith("glm4") or a.startswith("glm"):
+            kw["rotary_interleaved"] = not a.startswith("glm4moe") and "moe" not in a
+            kw["post_self_attn_layernorm"] = kw["post_mlp_layernorm"] = a.startswith("glm4for")
+            kw["qk_layernorm"] = bool(c.get("use_qk_norm", False))
+        if c.get("full_attention_interval"):  # Qwen3-Next / Qwen3.5 hybrids
+            kw.update(full_attention_interval=c["full_attention_interval"], linear_num_key_heads=c["linear_num_key_heads"],
+                      linear_num_value_heads=c["linear_num_value_heads"], linear_key_head_dim=c["linear_key_head_dim"],
+                      linear_value_head_dim=c["linear_value_head_dim"], linear_conv_kernel_dim=c.get("linear_conv_kernel_dim", 4),
+                      attention_output_gate=True, qk_layernorm=True)  # fmt: skip
+        if c.get("kv_lora_rank"):
+            kw.update(multi_latent_attention=True, q_lora_rank=c.get("q_lora_rank"), kv_lora_rank=c["kv_lora_rank"],
+                      qk_head_dim=c["qk_nope_head_dim"], qk_pos_emb_head_dim=c["qk_rope_head_dim"], v_head_dim=c["v_head_dim"],
+                      qk_layernorm=False)  # fmt: skip
+            if c.get("index_topk"):
+                kw.update(index_topk=c["index_topk"], index_n_heads=c["index_n_heads"], index_head_dim=c["index_head_dim"])
+        if "minimax" in a:
+            kw.update(qk_layernorm=False, qk_layernorm_full=bool(c.get("use_qk_norm", True)))
         return cls(**kw)
 
     def to_hf_dict(self) -> dict:

@@ -159,7 +159,12 @@ class TransformerLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
         super().__init__()
         self.layer_number = layer_number  # global, 0-based
-        self.self_attention = SelfAttention(cfg, layer_number, dtype, device, sequence_parallel)
+        if cfg.mixer(layer_number) == "attention":
+            self.self_attention = SelfAttention(cfg, layer_number, dtype, device, sequence_parallel)
+        else:  # attention variants, linear attention, latent attention: models/mixers.py
+            from slime_b200.models.mixers import build_mixer
+
+            self.self_attention = build_mixer(cfg, layer_number, dtype, device, sequence_parallel)
         if cfg.is_moe_layer(layer_number):
             from slime_b200.models.moe import MoELayer
 

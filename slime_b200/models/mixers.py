@@ -1,0 +1,496 @@
+"""Token mixers beyond the fused GQA attention path: attention variants, gated delta-net, latent attention, sparse
+latent attention with a lightning indexer.
+
+``ModelConfig.mixer(layer)`` names the mixer of a layer and ``build_mixer`` constructs it; every mixer has the calling
+convention of ``gpt.SelfAttention``: ``forward(x, residual, rope_table, packed) -> (out, residual)`` on packed
+(``thd``) rows, doing its own pre-norm with the fused add + RMSNorm.
+
+* ``GeneralSelfAttention``: tensor-parallel GQA attention composed from separate ops, for the variants the fused
+  RoPE + attention kernel does not cover: partial rotary embeddings (GLM-4 family, Qwen3-Next), interleaved rotary
+  pairs, a sigmoid output gate carried by the query projection (Qwen3-Next), RMSNorm over all heads at once
+  (MiniMax-M2; slime_plugins/models/minimax_m2.py:12 in the reference) and learnable softmax sinks
+  (slime_plugins/models/learnable_softmax_attention.py:23). The attention core is the flash kernel pair.
+* ``GatedDeltaNet``: the linear-attention layer of Qwen3-Next / Qwen3.5 (slime_plugins/models/qwen3_next.py:27,
+  qwen3_5.py:31): short causal depthwise convolution, gated delta rule evaluated chunk by chunk (a triangular solve and
+  matmuls per chunk, so autograd provides the backward), gated RMSNorm. ``gated_delta_rule_recurrent`` is the
+  token-by-token definition the chunked form is tested against.
+* ``MLASelfAttention``: multi-head latent attention (DeepSeek-V3, Kimi-K2, Moonlight): low-rank query and key/value
+  projections with a shared rotary key.
+* ``DSASelfAttention``: the same with a lightning indexer that picks ``index_topk`` keys per query; layers can reuse the
+  choice of an earlier layer (slime_plugins/models/glm5/glm5.py:264-281,302-550 in the reference).
+
+The last three keep their parameters replicated over the tensor-parallel group and compute on the full sequence on
+every rank (sequence-parallel rows are gathered before and split after), the way the reference wraps Hugging Face
+modules (slime_plugins/models/hf_attention.py:63-173); their math is plain PyTorch ops.
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from slime_b200 import ops
+from slime_b200.models.config import ModelConfig
+from slime_b200.parallel import state as mpu
+from slime_b200.parallel import tensor_parallel as tp
+
+
+def _param(shape, dtype, device, std=None, ones=False, generator=None):
+    t = torch.empty(*shape, dtype=torch.float32, device=device)
+    if ones:
+        t.fill_(1.0)
+    elif std == 0.0:
+        t.zero_()
+    else:
+        t.normal_(0.0, std, generator=generator)
+    return nn.Parameter(t.to(dtype))
+
+
+def _replicated(shape, dtype, device, std=None, ones=False):
+    gen = tp.get_rng_tracker().states.get("default")
+    return tp.set_tp_attrs(_param(shape, dtype, device, std, ones, gen), False)
+
+
+# ------------------------------------------------------------------------------------------------- rotary helpers
+def rotary_cos_sin(table: torch.Tensor, positions: torch.Tensor):
+    """``table`` [max_pos, rot] = [cos(rot/2) | sin(rot/2)] -> (cos, sin) [T, 1, rot/2] for ``positions``."""
+    cs = table[positions.long()]
+    half = cs.shape[-1] // 2
+    return cs[:, None, :half], cs[:, None, half:]
+
+
+def apply_rotary(x: torch.Tensor, cos, sin, interleaved: bool = False) -> torch.Tensor:
+    """Rotate the first ``2 * cos.shape[-1]`` channels of ``x`` [T, H, D]; the rest passes through (partial rotary)."""
+    rot = 2 * cos.shape[-1]
+    xr, rest = x[..., :rot].float(), x[..., rot:]
+    if interleaved:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([a * cos - b * sin, b * cos + a * sin], dim=-1).flatten(-2)
+    else:
+        a, b = xr[..., : rot // 2], xr[..., rot // 2 :]
+        out = torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+    return torch.cat([out.to(x.dtype), rest], dim=-1)
+
+
+def _rms(x, w, eps):
+    y = x.float()
+    y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+    return (y * w.float()).to(x.dtype)
+
+
+def dense_causal_attention(q, k, v, cu_seqlens, scale, allowed=None):
+    """Per-sequence causal attention with explicit matrices: q / k [T, H, Dqk], v [T, H, Dv] (query / key and value
+    widths may differ), ``allowed`` [T, Lmax] bool optional extra mask per query row over the keys of ITS sequence
+    (column j = j-th token of the sequence). fp32 math; meant for correctness, not for long sequences."""
+    out = torch.zeros(q.shape[0], q.shape[1], v.shape[-1], dtype=torch.float32, device=q.device)
+    pieces = []
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        if n <= 0:
+            continue
+        qs, ks, vs = (t[a:b].float().transpose(0, 1) for t in (q, k, v))
+        att = (qs @ ks.transpose(-1, -2)) * scale
+        mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
+        if allowed is not None:
+            mask = mask & allowed[a:b, :n]
+        att = att.masked_fill(~mask, float("-inf"))
+        pieces.append((a, b, (att.softmax(-1) @ vs).transpose(0, 1)))
+    for a, b, o in pieces:
+        out = out + F.pad(o, (0, 0, 0, 0, a, q.shape[0] - b))
+    return out.to(q.dtype)
+
+
+# -------------------------------------------------------------------------------------------- attention variants
+class GeneralSelfAttention(nn.Module):
+    """Tensor-parallel GQA attention for the variants listed in the module docstring. Parameter names and shard layouts
+    are those of ``gpt.SelfAttention`` (rows of the fused projection: [q heads | gate heads if gated | k heads | v heads]
+    of the local shard), plus ``softmax_offset`` [local heads] when the model has sinks."""
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+        super().__init__()
+        self.cfg, self.sp = cfg, sequence_parallel
+        tps = mpu.get_tensor_model_parallel_world_size()
+        assert cfg.num_attention_heads % tps == 0 and cfg.num_query_groups % tps == 0, "heads must divide by tp"
+        assert mpu.get_context_parallel_world_size() == 1, "the composed attention path has no context-parallel form"
+        self.hq, self.hkv, self.d = cfg.num_attention_heads // tps, cfg.num_query_groups // tps, cfg.head_dim
+        self.gated = cfg.attention_output_gate
+        self.rot = int(self.d * cfg.rotary_percent) // 2 * 2
+        h = cfg.hidden_size
+        gen = tp.get_rng_tracker().states.get("tp")
+        out_std = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
+        rows = ((2 if self.gated else 1) * self.hq + 2 * self.hkv) * self.d
+        self.linear_qkv = nn.Module()
+        self.linear_qkv.weight = tp.set_tp_attrs(_param((rows, h), dtype, device, cfg.init_method_std, generator=gen), True, 0, 1, "column")
+        self.linear_qkv.layer_norm_weight = tp.set_tp_attrs(_param((h,), dtype, device, ones=True), False)
+        self.linear_qkv.layer_norm_weight.sequence_parallel = sequence_parallel
+        self.linear_qkv.bias = tp.set_tp_attrs(_param((rows,), dtype, device, 0.0), True, 0, 1, "column") if cfg.add_qkv_bias else None
+        self.q_layernorm = self.k_layernorm = None
+        if cfg.qk_layernorm or cfg.qk_layernorm_full:
+            # per head: one [d] vector shared by the heads; over all heads: one vector per projection, sharded like it
+            self.q_layernorm, self.k_layernorm = nn.Module(), nn.Module()
+            full = cfg.qk_layernorm_full
+            qn, kn = (self.hq * self.d, self.hkv * self.d) if full else (self.d, self.d)
+            self.q_layernorm.weight = tp.set_tp_attrs(_param((qn,), dtype, device, ones=True), full, 0, 1)
+            self.k_layernorm.weight = tp.set_tp_attrs(_param((kn,), dtype, device, ones=True), full, 0, 1)
+            if not full:
+                self.q_layernorm.weight.needs_tp_grad_reduce = True
+                self.k_layernorm.weight.needs_tp_grad_reduce = True
+        if cfg.softmax_sinks:
+            self.softmax_offset = tp.set_tp_attrs(_param((self.hq,), torch.float32, device, 0.0), True, 0, 1)
+        else:
+            self.softmax_offset = None
+        self.linear_proj = nn.Module()
+        self.linear_proj.weight = tp.set_tp_attrs(_param((h, self.hq * self.d), dtype, device, out_std, generator=gen), True, 1, 1, "row")
+        self._rope = None
+
+    def _table(self, device, need: int):
+        if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
+            self._rope = ops.rope_cos_sin(max(need, 4096), self.rot, self.cfg.rotary_base, device=device,
+                                          scaling_factor=self.cfg.rotary_scaling_factor)  # fmt: skip
+        return self._rope
+
+    def _full_norm(self, t, w, eps):
+        """RMSNorm over all heads of the model: the sum of squares crosses tensor-parallel ranks."""
+        T = t.shape[0]
+        flat = t.reshape(T, -1).float()
+        ss = flat.pow(2).sum(-1, keepdim=True)
+        n = flat.shape[-1]
+        if mpu.get_tensor_model_parallel_world_size() > 1:
+            # summed over ranks in the forward pass AND in the backward pass: every rank's output depends on the total
+            ss = tp.reduce_from_tensor_model_parallel_region(tp.copy_to_tensor_model_parallel_region(ss))
+            n = n * mpu.get_tensor_model_parallel_world_size()
+        return (flat * torch.rsqrt(ss / n + eps) * w.float()).to(t.dtype).view_as(t)
+
+    def forward(self, x, residual, rope_table, packed):
+        cfg, d, hq, hkv = self.cfg, self.d, self.hq, self.hkv
+        normed, residual = ops.rmsnorm(x, self.linear_qkv.layer_norm_weight, cfg.norm_epsilon, residual)
+        inp = tp.gather_from_sequence_parallel_region(normed) if self.sp else tp.copy_to_tensor_model_parallel_region(normed)
+        qkv = ops.linear(inp, self.linear_qkv.weight, self.linear_qkv.bias)
+        T = qkv.shape[0]
+        sizes = [hq * d] + ([hq * d] if self.gated else []) + [hkv * d, hkv * d]
+        parts = qkv.split(sizes, dim=-1)
+        q, gate = parts[0].view(T, hq, d), (parts[1] if self.gated else None)
+        k, v = parts[-2].view(T, hkv, d), parts[-1].view(T, hkv, d)
+        if self.q_layernorm is not None:
+            if cfg.qk_layernorm_full:
+                q = self._full_norm(q, self.q_layernorm.weight, cfg.norm_epsilon)
+                k = self._full_norm(k, self.k_layernorm.weight, cfg.norm_epsilon)
+            else:
+                q, k = _rms(q, self.q_layernorm.weight, cfg.norm_epsilon), _rms(k, self.k_layernorm.weight, cfg.norm_epsilon)
+        if self.rot > 0:
+            cos, sin = rotary_cos_sin(self._table(q.device, int(packed.max_seqlen) + 1), packed.position_ids.reshape(-1))
+            q, k = apply_rotary(q, cos, sin, cfg.rotary_interleaved), apply_rotary(k, cos, sin, cfg.rotary_interleaved)
+        ctx = ops.varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), packed.cu_seqlens, packed.max_seqlen,
+                                   sinks=self.softmax_offset).reshape(T, hq * d)  # fmt: skip
+        if gate is not None:
+            ctx = ctx * torch.sigmoid(gate.float()).to(ctx.dtype)
+        out = ops.linear(ctx, self.linear_proj.weight)
+        out = tp.reduce_scatter_to_sequence_parallel_region(out) if self.sp else tp.reduce_from_tensor_model_parallel_region(out)
+        return out, residual
+
+
+# ------------------------------------------------------------------------------------------------ gated delta net
+def _l2norm(x, eps=1e-6):
+    return x * torch.rsqrt(x.pow(2).sum(-1, keepdim=True) + eps)
+
+
+def gated_delta_rule_recurrent(q, k, v, g, beta, cu_seqlens):
+    """Definition, one token at a time. q / k [T, H, Dk], v [T, H, Dv], g [T, H] (log decay, <= 0), beta [T, H];
+    the state ``S`` [H, Dk, Dv] starts at zero for every sequence:
+
+        S <- exp(g_t) S;  delta = beta_t (v_t - S^T k_t);  S <- S + k_t delta^T;  o_t = S^T q_t
+
+    with q and k L2-normalised and q scaled by ``Dk ** -0.5``."""
+    q, k = _l2norm(q.float()) * q.shape[-1] ** -0.5, _l2norm(k.float())
+    v, g, beta = v.float(), g.float(), beta.float()
+    out = torch.zeros_like(v)
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        S = torch.zeros(q.shape[1], q.shape[2], v.shape[2], dtype=torch.float32, device=q.device)
+        for t in range(a, b):
+            S = S * g[t].exp()[:, None, None]
+            delta = (v[t] - torch.einsum("hkv,hk->hv", S, k[t])) * beta[t][:, None]
+            S = S + k[t][:, :, None] * delta[:, None, :]
+            out[t] = torch.einsum("hkv,hk->hv", S, q[t])
+    return out
+
+
+def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = 64):
+    """The same function, ``chunk`` tokens at a time. Inside a chunk with cumulative log decay ``G`` and incoming state
+    ``S0`` the updates ``delta`` solve the unit lower-triangular system
+
+        (I + A) delta = beta * (V - exp(G) K S0),   A[i, j] = beta_i exp(G_i - G_j) <k_i, k_j>  (j < i),
+
+    then ``O = exp(G) Q S0 + (tril(exp(G_i - G_j)) * Q K^T) delta`` and ``S <- exp(G_C) S0 + (exp(G_C - G) K)^T delta``.
+    Everything is matmuls and one triangular solve per chunk, all differentiable."""
+    Dk = q.shape[-1]
+    qf, kf = _l2norm(q.float()) * Dk**-0.5, _l2norm(k.float())
+    vf, gf, bf = v.float(), g.float(), beta.float()
+    outs = []
+    cu = cu_seqlens.tolist()
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        if n <= 0:
+            continue
+        pad = (-n) % chunk
+        # [H, n_chunks, C, *]
+        shape = lambda t: F.pad(t[a:b], (0, 0) * (t.dim() - 1) + (0, pad)).transpose(0, 1).reshape(t.shape[1], -1, chunk, *t.shape[2:])  # noqa: E731
+        Q, K, V, Gc, B = shape(qf), shape(kf), shape(vf), shape(gf), shape(bf)
+        G = Gc.cumsum(-1)  # padded tokens have g = 0, beta = 0: they change nothing
+        diff = G[..., :, None] - G[..., None, :]
+        tri = torch.ones(chunk, chunk, dtype=torch.bool, device=q.device).tril()
+        decay = torch.where(tri, diff, torch.full_like(diff, float("-inf"))).exp()  # [H, N, C, C], zero above the diagonal
+        KK = K @ K.transpose(-1, -2)
+        A = (B[..., :, None] * decay * KK).tril(-1)
+        eye = torch.eye(chunk, device=q.device)
+        QK = (Q @ K.transpose(-1, -2)) * decay
+        eG = G.exp()[..., None]
+        S = torch.zeros(q.shape[1], Dk, v.shape[-1], dtype=torch.float32, device=q.device)
+        seq_out = []
+        for c in range(Q.shape[1]):
+            rhs = B[:, c, :, None] * (V[:, c] - eG[:, c] * (K[:, c] @ S))
+            delta = torch.linalg.solve_triangular(eye + A[:, c], rhs, upper=False, unitriangular=True)
+            seq_out.append(eG[:, c] * (Q[:, c] @ S) + QK[:, c] @ delta)
+            last = G[:, c, -1]
+            S = last.exp()[:, None, None] * S + ((last[:, None] - G[:, c]).exp()[..., None] * K[:, c]).transpose(-1, -2) @ delta
+        o = torch.stack(seq_out, 1).reshape(q.shape[1], -1, v.shape[-1])[:, :n].transpose(0, 1)
+        outs.append(o)
+    return torch.cat(outs) if outs else vf[:0]
+
+
+def causal_short_conv(x, weight, positions, activation=True):
+    """Depthwise causal convolution over time with zero history at every sequence start. x [T, C], weight [C, K]
+    (tap K-1 multiplies the current token), ``positions`` [T] the index of each token inside its sequence."""
+    K = weight.shape[1]
+    acc = x.float() * weight[:, K - 1].float()
+    pos = positions.reshape(-1)
+    for s in range(1, K):
+        shifted = F.pad(x.float(), (0, 0, s, 0))[: x.shape[0]]
+        acc = acc + torch.where((pos >= s)[:, None], shifted, torch.zeros_like(shifted)) * weight[:, K - 1 - s].float()
+    return (F.silu(acc) if activation else acc).to(x.dtype)
+
+
+class GatedDeltaNet(nn.Module):
+    """Qwen3-Next / Qwen3.5 linear-attention layer. Parameters (replicated over tensor-parallel ranks):
+    ``in_proj_qkvz`` [2 Kdim + 2 Vdim, H] (rows grouped per key head: q, k, then that head's value and gate heads),
+    ``in_proj_ba`` [2 Hv, H], ``conv1d.weight`` [2 Kdim + Vdim, K], ``A_log`` / ``dt_bias`` [Hv], ``norm.weight`` [Dv],
+    ``out_proj`` [H, Vdim], ``input_layernorm.weight`` [H]."""
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+        super().__init__()
+        self.cfg, self.sp = cfg, sequence_parallel
+        self.hk, self.hv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        self.dk, self.dv = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        assert self.hv % self.hk == 0
+        self.key_dim, self.value_dim = self.hk * self.dk, self.hv * self.dv
+        h, std = cfg.hidden_size, cfg.init_method_std
+        self.input_layernorm = nn.Module()
+        self.input_layernorm.weight = _replicated((h,), dtype, device, ones=True)
+        self.input_layernorm.weight.sequence_parallel = sequence_parallel
+        self.in_proj_qkvz, self.in_proj_ba, self.conv1d, self.norm, self.out_proj = (nn.Module() for _ in range(5))
+        self.in_proj_qkvz.weight = _replicated((2 * self.key_dim + 2 * self.value_dim, h), dtype, device, std)
+        self.in_proj_ba.weight = _replicated((2 * self.hv, h), dtype, device, std)
+        self.conv1d.weight = _replicated((2 * self.key_dim + self.value_dim, cfg.linear_conv_kernel_dim), dtype, device, 0.2)
+        self.dt_bias = _replicated((self.hv,), torch.float32, device, ones=True)
+        gen = tp.get_rng_tracker().states.get("default")
+        a = torch.empty(self.hv, dtype=torch.float32, device=device).uniform_(1e-3, 16.0, generator=gen)
+        self.A_log = tp.set_tp_attrs(nn.Parameter(a.log()), False)
+        self.norm.weight = _replicated((self.dv,), dtype, device, ones=True)
+        self.out_proj.weight = _replicated((h, self.value_dim), dtype, device, std / math.sqrt(2.0 * cfg.num_layers))
+
+    def _split(self, qkvz, ba):
+        """Undo the per-key-head grouping of the fused projections."""
+        T, r = qkvz.shape[0], self.hv // self.hk
+        qkvz = qkvz.view(T, self.hk, 2 * self.dk + 2 * r * self.dv)
+        q, k, v, z = qkvz.split([self.dk, self.dk, r * self.dv, r * self.dv], dim=-1)
+        b, a = ba.view(T, self.hk, 2 * r).split([r, r], dim=-1)
+        return (q, k, v.reshape(T, self.hv, self.dv), z.reshape(T, self.hv, self.dv), b.reshape(T, self.hv), a.reshape(T, self.hv))
+
+    def forward(self, x, residual, rope_table, packed):
+        cfg = self.cfg
+        normed, residual = ops.rmsnorm(x, self.input_layernorm.weight, cfg.norm_epsilon, residual)
+        inp = tp.gather_from_sequence_parallel_region_no_reduce(normed) if self.sp else normed
+        T = inp.shape[0]
+        q, k, v, z, b, a = self._split(F.linear(inp, self.in_proj_qkvz.weight), F.linear(inp, self.in_proj_ba.weight))
+        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+        mixed = causal_short_conv(mixed, self.conv1d.weight, packed.position_ids)
+        q, k, v = mixed.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
+        q, k, v = q.view(T, self.hk, self.dk), k.view(T, self.hk, self.dk), v.view(T, self.hv, self.dv)
+        beta = torch.sigmoid(b.float())
+        g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias.float())
+        r = self.hv // self.hk
+        if r > 1:
+            q, k = q.repeat_interleave(r, dim=1), k.repeat_interleave(r, dim=1)
+        o = gated_delta_rule_chunked(q, k, v, g, beta, packed.cu_seqlens)  # the alignment padding is a sequence of its own
+        if o.shape[0] < T:  # rows past the last sequence (alignment padding of the packed stream)
+            o = F.pad(o, (0, 0, 0, 0, 0, T - o.shape[0]))
+        o = _rms(o, self.norm.weight, cfg.norm_epsilon).float() * F.silu(z.float())
+        out = F.linear(o.to(inp.dtype).reshape(T, self.value_dim), self.out_proj.weight)
+        return (tp.scatter_to_sequence_parallel_region(out) if self.sp else out), residual
+
+
+# ---------------------------------------------------------------------------------------------- latent attention
+class MLASelfAttention(nn.Module):
+    """Multi-head latent attention. Parameters (replicated over tensor-parallel ranks), Megatron names:
+    ``linear_q_down_proj`` [q_lora, H] + ``q_layernorm`` + ``linear_q_up_proj`` [Hq (Dn + Dr), q_lora] (or ``linear_q_proj``
+    when the model has no query compression), ``linear_kv_down_proj`` [kv_lora + Dr, H], ``kv_layernorm``,
+    ``linear_kv_up_proj`` [Hq (Dn + Dv), kv_lora], ``linear_proj`` [H, Hq Dv], ``input_layernorm``."""
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+        super().__init__()
+        self.cfg, self.sp, self.layer_number = cfg, sequence_parallel, layer_number
+        self.hq, self.dn, self.dr, self.dv = cfg.num_attention_heads, cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
+        h, std = cfg.hidden_size, cfg.init_method_std
+        mk = lambda *shape, **kw: _replicated(shape, dtype, device, **kw)  # noqa: E731
+        self.input_layernorm = nn.Module()
+        self.input_layernorm.weight = mk(h, ones=True)
+        self.input_layernorm.weight.sequence_parallel = sequence_parallel
+        names = ["linear_q_down_proj", "q_layernorm", "linear_q_up_proj", "linear_q_proj", "linear_kv_down_proj", "kv_layernorm",
+                 "linear_kv_up_proj", "linear_proj"]  # fmt: skip
+        for n in names:
+            setattr(self, n, nn.Module())
+        if cfg.q_lora_rank:
+            self.linear_q_down_proj.weight = mk(cfg.q_lora_rank, h, std=std)
+            self.q_layernorm.weight = mk(cfg.q_lora_rank, ones=True)
+            self.linear_q_up_proj.weight = mk(self.hq * (self.dn + self.dr), cfg.q_lora_rank, std=std)
+            del self.linear_q_proj
+        else:
+            self.linear_q_proj.weight = mk(self.hq * (self.dn + self.dr), h, std=std)
+            del self.linear_q_down_proj, self.q_layernorm, self.linear_q_up_proj
+        self.linear_kv_down_proj.weight = mk(cfg.kv_lora_rank + self.dr, h, std=std)
+        self.kv_layernorm.weight = mk(cfg.kv_lora_rank, ones=True)
+        self.linear_kv_up_proj.weight = mk(self.hq * (self.dn + self.dv), cfg.kv_lora_rank, std=std)
+        self.linear_proj.weight = mk(h, self.hq * self.dv, std=std / math.sqrt(2.0 * cfg.num_layers))
+        self.scale = (self.dn + self.dr) ** -0.5
+        self._rope = None
+
+    def _table(self, device, need):
+        if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
+            self._rope = ops.rope_cos_sin(max(need, 4096), self.dr, self.cfg.rotary_base, device=device,
+                                          scaling_factor=self.cfg.rotary_scaling_factor)  # fmt: skip
+        return self._rope
+
+    def _qkv(self, inp, packed):
+        cfg, T = self.cfg, inp.shape[0]
+        if cfg.q_lora_rank:
+            q_latent = _rms(F.linear(inp, self.linear_q_down_proj.weight), self.q_layernorm.weight, cfg.norm_epsilon)
+            q = F.linear(q_latent, self.linear_q_up_proj.weight)
+        else:
+            q_latent, q = inp, F.linear(inp, self.linear_q_proj.weight)
+        q = q.view(T, self.hq, self.dn + self.dr)
+        kv_down = F.linear(inp, self.linear_kv_down_proj.weight)
+        c_kv, k_pe = kv_down.split([cfg.kv_lora_rank, self.dr], dim=-1)
+        kv = F.linear(_rms(c_kv, self.kv_layernorm.weight, cfg.norm_epsilon), self.linear_kv_up_proj.weight)
+        k_nope, v = kv.view(T, self.hq, self.dn + self.dv).split([self.dn, self.dv], dim=-1)
+        cos, sin = rotary_cos_sin(self._table(inp.device, int(packed.max_seqlen) + 1), packed.position_ids.reshape(-1))
+        q_pe = apply_rotary(q[..., self.dn :], cos, sin, cfg.rotary_interleaved)
+        k_pe = apply_rotary(k_pe.view(T, 1, self.dr), cos, sin, cfg.rotary_interleaved)
+        q = torch.cat([q[..., : self.dn], q_pe], dim=-1)
+        k = torch.cat([k_nope, k_pe.expand(T, self.hq, self.dr)], dim=-1)
+        return q, k, v, q_latent, (cos, sin)
+
+    def _allowed(self, inp, q_latent, rope, packed):
+        return None
+
+    def forward(self, x, residual, rope_table, packed):
+        cfg = self.cfg
+        normed, residual = ops.rmsnorm(x, self.input_layernorm.weight, cfg.norm_epsilon, residual)
+        inp = tp.gather_from_sequence_parallel_region_no_reduce(normed) if self.sp else normed
+        q, k, v, q_latent, rope = self._qkv(inp, packed)
+        ctx = dense_causal_attention(q, k, v, packed.cu_seqlens, self.scale, self._allowed(inp, q_latent, rope, packed))
+        out = F.linear(ctx.reshape(inp.shape[0], -1), self.linear_proj.weight)
+        return (tp.scatter_to_sequence_parallel_region(out) if self.sp else out), residual
+
+
+def indexer_logits(q_idx, k_idx, weights):
+    """Lightning indexer: ``logits[t, s] = sum_h weights[t, h] * relu(<q_idx[t, h], k_idx[s]>)``; q_idx [T, Hi, Di],
+    k_idx [S, Di], weights [T, Hi] -> [T, S] fp32."""
+    return torch.einsum("thd,sd->ths", q_idx.float(), k_idx.float()).relu_().mul_(weights.float()[:, :, None]).sum(1)
+
+
+def select_topk_keys(logits_fn, cu_seqlens, T: int, topk: int, device) -> torch.Tensor:
+    """Per query row the ``topk`` best-scoring keys among the causally visible ones of its own sequence, as a boolean
+    matrix [T, Lmax] over in-sequence key positions (rows with fewer visible keys keep all of them).
+    ``logits_fn(a, b)`` returns the [b - a, b - a] score block of one sequence."""
+    cu = cu_seqlens.tolist()
+    lmax = max((b - a for a, b in zip(cu[:-1], cu[1:])), default=0)
+    allowed = torch.zeros(T, lmax, dtype=torch.bool, device=device)
+    for a, b in zip(cu[:-1], cu[1:]):
+        n = b - a
+        if n <= 0:
+            continue
+        causal = torch.ones(n, n, dtype=torch.bool, device=device).tril()
+        if n <= topk:
+            allowed[a:b, :n] = causal
+            continue
+        scores = logits_fn(a, b).masked_fill(~causal, float("-inf"))
+        idx = scores.topk(topk, dim=-1).indices
+        pick = torch.zeros(n, n, dtype=torch.bool, device=device).scatter_(1, idx, True)
+        allowed[a:b, :n] = pick & causal
+    return allowed
+
+
+class DSASelfAttention(MLASelfAttention):
+    """Latent attention restricted to the keys a lightning indexer picks. Extra parameters: ``wq_b`` [Hi Di, q_lora],
+    ``wk`` [Di, H], ``k_norm`` (LayerNorm weight and bias [Di]), ``weights_proj`` [Hi, H]. The first ``Dr`` channels of
+    the indexer's queries and key are rotated like the attention's rotary part. A layer for which
+    ``max(layer - index_skip_topk_offset, 0) % index_topk_freq != 0`` (1-based layer numbers) reuses the choice of the
+    nearest earlier layer that computed one; the choice travels on the micro-batch's ``packed`` object, so it is
+    per micro-batch and survives activation recomputation."""
+
+    _HOLDER = "_dsa_topk"
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+        super().__init__(cfg, layer_number, dtype, device, sequence_parallel)
+        assert cfg.q_lora_rank, "the indexer reads the compressed query"
+        self.hi, self.di = cfg.index_n_heads, cfg.index_head_dim
+        mk = lambda *shape, **kw: _replicated(shape, dtype, device, **kw)  # noqa: E731
+        one_based = layer_number + 1
+        self.skip = (max(one_based - cfg.index_skip_topk_offset, 0) % cfg.index_topk_freq) != 0
+        src = one_based
+        while (max(src - cfg.index_skip_topk_offset, 0) % cfg.index_topk_freq) != 0:
+            src -= 1
+        self.source_layer = src - 1
+        if not self.skip:
+            self.wq_b, self.wk, self.k_norm, self.weights_proj = (nn.Module() for _ in range(4))
+            self.wq_b.weight = mk(self.hi * self.di, cfg.q_lora_rank, std=cfg.init_method_std)
+            self.wk.weight = mk(self.di, cfg.hidden_size, std=cfg.init_method_std)
+            self.k_norm.weight, self.k_norm.bias = mk(self.di, ones=True), mk(self.di, std=0.0)
+            self.weights_proj.weight = mk(self.hi, cfg.hidden_size, std=cfg.init_method_std)
+
+    def _allowed(self, inp, q_latent, rope, packed):
+        holder = getattr(packed, self._HOLDER, None)
+        if holder is None:
+            holder = {}
+            setattr(packed, self._HOLDER, holder)
+        if self.skip:
+            if self.source_layer not in holder:
+                raise AssertionError(f"layer {self.layer_number} reuses the key choice of layer {self.source_layer}, which did not "
+                                     "run before it in this pipeline stage: every stage must start on a computing layer")  # fmt: skip
+            return holder[self.source_layer]
+        cfg, T = self.cfg, inp.shape[0]
+        cos, sin = rope
+        with torch.no_grad():  # the choice is discrete: no gradient reaches the indexer through it
+            q_idx = apply_rotary(F.linear(q_latent, self.wq_b.weight).view(T, self.hi, self.di), cos, sin, cfg.rotary_interleaved)
+            k_idx = F.layer_norm(F.linear(inp, self.wk.weight).float(), (self.di,), self.k_norm.weight.float(), self.k_norm.bias.float())
+            k_idx = apply_rotary(k_idx.view(T, 1, self.di), cos, sin, cfg.rotary_interleaved).view(T, self.di)
+            w = F.linear(inp, self.weights_proj.weight).float() * (self.hi**-0.5) * (self.di**-0.5)
+            allowed = select_topk_keys(lambda a, b: indexer_logits(q_idx[a:b], k_idx[a:b], w[a:b]), packed.cu_seqlens, T,
+                                       cfg.index_topk, inp.device)  # fmt: skip
+        holder[self.layer_number] = allowed
+        return allowed
+
+
+def build_mixer(cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+    kind = cfg.mixer(layer_number)
+    if kind == "attention":
+        from slime_b200.models.gpt import SelfAttention
+
+        return SelfAttention(cfg, layer_number, dtype, device, sequence_parallel)
+    cls = {"general_attention": GeneralSelfAttention, "gated_delta_net": GatedDeltaNet, "mla": MLASelfAttention,
+           "dsa": DSASelfAttention}[kind]  # fmt: skip
+    return cls(cfg, layer_number, dtype, device, sequence_parallel)

@@ -32,6 +32,16 @@ def _param(shape, dtype, device, std, generator=None):
     return nn.Parameter(t.to(dtype))
 
 
+def group_limited(scores: torch.Tensor, num_groups: int, group_topk: int) -> torch.Tensor:
+    """Group-limited routing: experts are split into ``num_groups`` equal groups, a group's score is the sum of its two
+    best experts, and only experts of the ``group_topk`` best groups stay eligible (the others get -inf)."""
+    T, E = scores.shape
+    per = scores.view(T, num_groups, E // num_groups)
+    group_score = per.topk(min(2, per.shape[-1]), dim=-1).values.sum(-1)
+    keep = torch.zeros_like(group_score, dtype=torch.bool).scatter_(1, group_score.topk(group_topk, dim=-1).indices, True)
+    return per.masked_fill(~keep[:, :, None], float("-inf")).view(T, E)
+
+
 class TopKRouter(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device):
         super().__init__()
@@ -54,6 +64,8 @@ class TopKRouter(nn.Module):
         if cfg.moe_router_score_function == "sigmoid":
             scores = torch.sigmoid(logits)
             sel = scores + self.expert_bias if self.expert_bias is not None else scores
+            if cfg.moe_router_num_groups and cfg.moe_router_group_topk and cfg.moe_router_num_groups > 1:
+                sel = group_limited(sel, cfg.moe_router_num_groups, cfg.moe_router_group_topk)
             idx = self.replay.compute_topk(sel, k)
             probs = scores.gather(-1, idx)
             if cfg.norm_topk_prob:
@@ -159,12 +171,19 @@ class MoELayer(nn.Module):
             nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device)), False
         )
         self.router = TopKRouter(cfg, layer_number, dtype, device)
+        # replicated parameters that only see this rank's rows under sequence parallelism: their gradients are partial
+        # sums and must be added up over the tensor-parallel group
+        self.pre_mlp_layernorm.weight.sequence_parallel = sequence_parallel
+        self.router.weight.sequence_parallel = sequence_parallel
         self.experts = GroupedExperts(cfg, dtype, device, self.num_local)
         if cfg.moe_shared_expert_intermediate_size:
             from slime_b200.models.gpt import MLP
 
             self.shared_experts = MLP(cfg, dtype, device, sequence_parallel, ffn=cfg.moe_shared_expert_intermediate_size,
                                       with_norm=False)  # fmt: skip
+            if cfg.moe_shared_expert_gate:
+                self.shared_experts.gate_weight = tp.set_tp_attrs(_param((1, cfg.hidden_size), dtype, device, cfg.init_method_std), False)
+                self.shared_experts.gate_weight.sequence_parallel = sequence_parallel
         else:
             self.shared_experts = None
         self.aux_loss = None
@@ -213,5 +232,8 @@ class MoELayer(nn.Module):
         inv[order] = torch.arange(order.numel(), device=order.device)
         out = weighted.index_select(0, inv).view(T, k, H).float().sum(1).to(x.dtype)
         if self.shared_experts is not None:
-            out = out + self.shared_experts.ffn(normed)
+            shared = self.shared_experts.ffn(normed)
+            if cfg.moe_shared_expert_gate:
+                shared = shared * torch.sigmoid(normed.float() @ self.shared_experts.gate_weight.float().t()).to(shared.dtype)
+            out = out + shared
         return out, residual

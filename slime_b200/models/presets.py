@@ -5,9 +5,9 @@
     MODEL_ARGS=($(python -m slime_b200.models.presets qwen3-30B-A3B))   # in a launch script
 
 Every entry is the constructor arguments of ``ModelConfig``; ``--hf-checkpoint preset:<name>`` builds a random-weight
-model from it, and a real checkpoint's ``config.json`` overrides nothing here (it is read instead). Families whose layers
-this framework does not implement yet (multi-head latent attention, gated delta-net hybrids, sparse-attention
-indexers) are listed in ``UNSUPPORTED`` with the missing piece, so asking for one fails with a reason instead of a
+model from it, and a real checkpoint's ``config.json`` overrides nothing here (it is read instead). Families with attention variants, latent
+attention, sparse latent attention or gated delta-net layers build their layers from ``models/mixers.py``; what is not
+implemented is listed in ``UNSUPPORTED`` with the missing piece, so asking for it fails with a reason instead of a
 silently wrong model. Parity: scripts/models/*.sh (39 flag sets).
 """
 
@@ -51,29 +51,87 @@ MORE_PRESETS: dict[str, dict] = {
                                             num_experts=128, moe_ffn_hidden_size=1536, moe_router_topk=8)),
 }  # fmt: skip
 
+def _mla(q_lora, kv_lora=512, nope=128, rope=64, v=128) -> dict:
+    return dict(multi_latent_attention=True, q_lora_rank=q_lora, kv_lora_rank=kv_lora, qk_head_dim=nope,
+                qk_pos_emb_head_dim=rope, v_head_dim=v)  # fmt: skip
+
+
+def _sigmoid_router(scale, groups=None, group_topk=None) -> dict:
+    return dict(moe_router_score_function="sigmoid", moe_router_pre_softmax=True, moe_router_enable_expert_bias=True,
+                moe_router_topk_scaling_factor=scale, moe_router_num_groups=groups, moe_router_group_topk=group_topk)  # fmt: skip
+
+
+def _gdn(key_heads, value_heads, key_dim=128, value_dim=128) -> dict:
+    # Head counts of the linear-attention layers come from the checkpoint's config.json (linear_num_key_heads, ...);
+    # a preset only needs them for random-weight runs.
+    return dict(full_attention_interval=4, linear_num_key_heads=key_heads, linear_num_value_heads=value_heads,
+                linear_key_head_dim=key_dim, linear_value_head_dim=value_dim, linear_conv_kernel_dim=4,
+                attention_output_gate=True, rotary_percent=0.25)  # fmt: skip
+
+
+def _deepseek_v3(layers: int) -> dict:
+    return _moe(min(3, layers), max(layers - 3, 0), **_dense(
+        layers, 7168, 18432, 128, 128, 129280, kv=128, rope=1e4, arch="DeepseekV3ForCausalLM", rotary_scaling_factor=40.0,
+        num_experts=256, moe_ffn_hidden_size=2048, moe_router_topk=8, moe_shared_expert_intermediate_size=2048,
+        **_mla(1536), **_sigmoid_router(2.5, 8, 4)))  # fmt: skip
+
+
+def _kimi_k2(eps: float, scaling: float) -> dict:
+    return _moe(1, 60, **_dense(61, 7168, 18432, 64, 64, 163840, kv=64, rope=5e4, eps=eps, arch="DeepseekV3ForCausalLM",
+                                rotary_scaling_factor=scaling, num_experts=384, moe_ffn_hidden_size=2048, moe_router_topk=8,
+                                moe_shared_expert_intermediate_size=2048, **_mla(1536), **_sigmoid_router(2.827)))  # fmt: skip
+
+
+def _glm5(rope: float) -> dict:
+    # indexer sizes follow the DeepSeek-V3.2 layout this family adopted; a checkpoint's config.json overrides them
+    return _moe(3, 75, **_dense(78, 6144, 12288, 64, 64, 154880, kv=192, rope=rope, arch="GlmMoeDsaForCausalLM",
+                                num_experts=256, moe_ffn_hidden_size=2048, moe_router_topk=8,
+                                moe_shared_expert_intermediate_size=2048, index_topk=2048, index_n_heads=32, index_head_dim=128,
+                                **_mla(2048, nope=192, v=256), **_sigmoid_router(2.5)))  # fmt: skip
+
+
+def _glm45(dense, moe, hidden, ffn, experts, moe_ffn, scale=None) -> dict:
+    return _moe(dense, moe, **_dense(dense + moe, hidden, ffn, 96, 8, 151552, kv=128, bias=True, arch="Glm4MoeForCausalLM",
+                                     rotary_percent=0.5, num_experts=experts, moe_ffn_hidden_size=moe_ffn, moe_router_topk=8,
+                                     moe_shared_expert_intermediate_size=moe_ffn, **_sigmoid_router(scale)))  # fmt: skip
+
+
+MORE_PRESETS.update({
+    "glm4-9b": _dense(40, 4096, 13696, 32, 2, 151552, rope=1e4, eps=1e-5, bias=True, arch="Glm4ForCausalLM",
+                      post_self_attn_layernorm=True, post_mlp_layernorm=True, rotary_interleaved=True, rotary_percent=0.5),
+    "glm4-32b": _dense(64, 6144, 23040, 48, 8, 151552, rope=1e4, eps=1e-5, arch="Glm4ForCausalLM",
+                       post_self_attn_layernorm=True, post_mlp_layernorm=True, rotary_interleaved=True, rotary_percent=0.5),
+    "glm4.5-106b-a12b": _glm45(1, 45, 4096, 10944, 128, 1408),
+    "glm4.5-355b-a32b": _glm45(3, 89, 5120, 12288, 160, 1536, 2.5),
+    "glm4.7-30b-a3b": _moe(1, 46, **_dense(47, 2048, 10240, 20, 20, 154880, kv=192, bias=True, arch="Glm4MoeLiteForCausalLM",
+                                           num_experts=64, moe_ffn_hidden_size=1536, moe_router_topk=4,
+                                           moe_shared_expert_intermediate_size=1536, **_mla(768, nope=192, v=256),
+                                           **_sigmoid_router(1.8))),
+    "deepseek-v3": _deepseek_v3(61), "deepseek-v3-5layer": _deepseek_v3(5), "deepseek-v3-20layer": _deepseek_v3(20),
+    "kimi-k2": _kimi_k2(1e-6, 32.0), "kimi-k2-thinking": _kimi_k2(1e-5, 64.0),
+    "moonlight": _moe(1, 26, **_dense(27, 2048, 11264, 16, 16, 163840, kv=128, rope=5e4, eps=1e-5, arch="DeepseekV3ForCausalLM",
+                                      num_experts=64, moe_ffn_hidden_size=1408, moe_router_topk=6,
+                                      moe_shared_expert_intermediate_size=2816, **_mla(None), **_sigmoid_router(2.446))),
+    "glm5-744b-a40b": _glm5(1e6), "glm5.2-744b-a40b": _glm5(8e6),
+    "minimax-m2": _dense(62, 3072, 1536, 48, 8, 200064, kv=128, rope=5e6, arch="MiniMaxM2ForCausalLM", rotary_percent=0.5,
+                         qk_layernorm_full=True, num_experts=256, moe_ffn_hidden_size=1536, moe_router_topk=8,
+                         moe_router_score_function="sigmoid", moe_router_pre_softmax=True, moe_router_enable_expert_bias=True),
+    "qwen3-next-80b-a3b": _dense(48, 2048, 5120, 16, 2, 151936, kv=256, rope=1e7, qk=True, arch="Qwen3NextForCausalLM",
+                                 num_experts=512, moe_ffn_hidden_size=512, moe_router_topk=10,
+                                 moe_shared_expert_intermediate_size=512, moe_shared_expert_gate=True, **_gdn(16, 32)),
+    "qwen3.5-0.8b": _dense(24, 1024, 3584, 8, 2, 248320, kv=256, rope=1e7, tied=True, qk=True, arch="Qwen3_5ForCausalLM", **_gdn(16, 16)),
+    "qwen3.5-4b": _dense(32, 2560, 9216, 16, 4, 248320, kv=256, rope=1e7, tied=True, qk=True, arch="Qwen3_5ForCausalLM", **_gdn(16, 32)),
+    "qwen3.5-9b": _dense(32, 4096, 12288, 16, 4, 248320, kv=256, rope=1e7, qk=True, arch="Qwen3_5ForCausalLM", **_gdn(16, 32)),
+    "qwen3.5-27b": _dense(64, 5120, 17408, 24, 4, 248320, kv=256, rope=1e7, qk=True, arch="Qwen3_5ForCausalLM", **_gdn(16, 48)),
+    "qwen3.5-35b-a3b": _dense(40, 2048, 512, 16, 2, 248320, kv=256, rope=1e7, qk=True, arch="Qwen3_5MoeForCausalLM",
+                              num_experts=256, moe_ffn_hidden_size=512, moe_router_topk=8,
+                              moe_shared_expert_intermediate_size=512, moe_shared_expert_gate=True, **_gdn(16, 32)),
+})  # fmt: skip
+
 # name -> what is missing. The numbers of these families are in the recipes they come from; they are not repeated here
 # because a preset that cannot be instantiated correctly is worse than none.
 UNSUPPORTED: dict[str, str] = {
-    "glm4-32b": "partial rotary (rotary_percent 0.5, interleaved) is not implemented in the rope kernel",
-    "glm4.5-106b-a12b": "partial rotary (rotary_percent 0.5) and sequence-level aux loss are not implemented",
-    "glm4.5-355b-a32b": "partial rotary (rotary_percent 0.5) and sequence-level aux loss are not implemented",
-    "glm4.7-30b-a3b": "partial rotary (rotary_percent 0.5) and sequence-level aux loss are not implemented",
-    "deepseek-v3": "multi-head latent attention (MLA) is not implemented",
-    "deepseek-v3-5layer": "multi-head latent attention (MLA) is not implemented",
-    "deepseek-v3-20layer": "multi-head latent attention (MLA) is not implemented",
-    "kimi-k2": "multi-head latent attention (MLA) is not implemented",
-    "kimi-k2-thinking": "multi-head latent attention (MLA) is not implemented",
-    "moonlight": "multi-head latent attention (MLA) is not implemented",
-    "glm5-744b-a40b": "sparse attention with a lightning indexer (DSA) over MLA is not implemented",
-    "glm5.2-744b-a40b": "sparse attention with a lightning indexer (DSA) over MLA is not implemented",
-    "minimax-m2": "per-layer qk-norm over the full projection and its router variant are not implemented",
-    "qwen3-next-80b-a3b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-0.8b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-4b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-9b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-27b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-35b-a3b": "gated delta-net linear-attention layers are not implemented",
-    "qwen3.5-35b-a3b-vl": "gated delta-net layers and the vision tower are not implemented",
+    "qwen3.5-35b-a3b-vl": "the vision tower (image / video patches into the token stream) is not implemented",
 }
 
 ALIASES = {"qwen2.5-0.5b": "qwen2.5-0.5b", "llama3.2-3b-instruct-amd": "llama3.2-3b-instruct"}
@@ -91,7 +149,8 @@ def to_flags(cfg) -> list[str]:
             continue
         if cfg.num_experts is None and (f.name.startswith("moe_") or f.name == "norm_topk_prob"):
             continue
-        if f.name in ("rotary_scaling_factor", "mtp_num_layers", "norm_topk_prob") and v == base[f.name]:
+        if f.name in ("rotary_scaling_factor", "mtp_num_layers", "norm_topk_prob", "rotary_percent", "linear_conv_kernel_dim",
+                      "index_topk_freq", "index_skip_topk_offset") and v == base[f.name]:  # fmt: skip
             continue
         flag = "--" + f.name.replace("_", "-")
         if isinstance(v, bool):

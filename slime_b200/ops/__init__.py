@@ -447,11 +447,11 @@ def rope_attention(qkv, positions, cos_sin, cu_seqlens, max_seqlen, Hq, Hkv, D, 
                                     cp_local_cu_seqlens, cp_group)
 
 
-def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True):
-    """Packed causal GQA attention. q: [T, Hq, D], k/v: [T, Hkv, D]."""
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True, sinks=None):
+    """Packed causal GQA attention. q: [T, Hq, D], k/v: [T, Hkv, D]; ``sinks`` [Hq]: learnable per-head sink logits."""
     from slime_b200.ops import attention
 
-    return attention.varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale, causal)
+    return attention.varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale, causal, sinks)
 
 
 def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None, out=None, splits=None,

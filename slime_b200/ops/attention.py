@@ -35,8 +35,9 @@ def segments_extend(cu_q: torch.Tensor, cu_k: torch.Tensor) -> torch.Tensor:
     return torch.stack([cq[:-1], cq[1:] - cq[:-1], ck[:-1], ck[1:] - ck[:-1]], dim=1).contiguous()
 
 
-def _reference_segments(q, k, v, seg, scale):
-    """fp32 oracle / CPU path: q [Tq, Hq, D], k / v [Tk, Hkv, D]; rows outside every segment come out as zeros."""
+def _reference_segments(q, k, v, seg, scale, sinks=None):
+    """fp32 oracle / CPU path: q [Tq, Hq, D], k / v [Tk, Hkv, D]; rows outside every segment come out as zeros.
+    ``sinks`` [Hq]: one extra logit per head that takes part in the softmax and contributes no value."""
     Hq, Hkv = q.shape[1], k.shape[1]
     out = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
     pieces = []
@@ -48,7 +49,12 @@ def _reference_segments(q, k, v, seg, scale):
         vs = v[k_off : k_off + k_len].float().transpose(0, 1).repeat_interleave(Hq // Hkv, 0)
         att = (qs @ ks.transpose(-1, -2)) * scale
         mask = torch.ones(q_len, k_len, dtype=torch.bool, device=q.device).tril(diagonal=k_len - q_len)
-        o = att.masked_fill(~mask, float("-inf")).softmax(-1) @ vs
+        att = att.masked_fill(~mask, float("-inf"))
+        if sinks is not None:
+            col = sinks.float().view(Hq, 1, 1).expand(Hq, q_len, 1)
+            o = torch.cat([att, col], -1).softmax(-1)[..., :-1] @ vs
+        else:
+            o = att.softmax(-1) @ vs
         pieces.append((q_off, q_len, o.transpose(0, 1)))
     for q_off, q_len, o in pieces:  # out-of-place assembly keeps autograd happy
         pad = torch.zeros_like(out)
@@ -122,6 +128,36 @@ class _FlashAttention(torch.autograd.Function):
         return dq, dk, dv, None, None
 
 
+class _SinkFlashAttention(torch.autograd.Function):
+    """Attention with a learnable per-head sink logit ``b_h`` in the softmax denominator, on the plain flash kernels.
+
+    With ``lse`` the log-sum-exp of the real scores, the sink turns the probabilities into ``sigmoid(lse - b) * P``,
+    so the output is the plain output times ``g = sigmoid(lse - b)`` per (head, row). Backward: the score gradient
+    is ``g P (dP - g (dO . O))``, which is what the plain backward computes when it is handed ``g dO`` for ``dO`` and
+    ``g O`` for ``O`` (its row term is the dot product of the two); ``d b_h = -sum_rows (1 - g) (dO . g O)``.
+    Same role as slime_plugins/models/learnable_softmax_attention.py:23 in the reference.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, seg, scale, sinks):
+        out, lse = flash_fwd(q, k, v, seg, scale, zero_uncovered=True)
+        gate = torch.sigmoid(lse - sinks.float()[:, None])  # [Hq, Tq]
+        out = (out.float() * gate.t()[:, :, None]).to(q.dtype)
+        ctx.save_for_backward(q, k, v, out, lse, seg, gate)
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, d_o):
+        q, k, v, out, lse, seg, gate = ctx.saved_tensors
+        gt = gate.t()[:, :, None]
+        d_scaled = (d_o.float() * gt).to(d_o.dtype)
+        dq, dk, dv = flash_bwd(q, k, v, out, d_scaled, lse, seg, ctx.scale)
+        row = (d_o.float() * out.float()).sum(-1)  # [Tq, Hq] = dO . (g O)
+        d_sinks = -((1.0 - gate.t()) * row).sum(0)
+        return dq, dk, dv, None, None, d_sinks
+
+
 def _library_segments(q, k, v, seg, scale):
     """Comparison arm only (``ops.library_mode()``): the flash-attn library on the same segments."""
     from flash_attn import flash_attn_varlen_func
@@ -135,22 +171,26 @@ def _library_segments(q, k, v, seg, scale):
     return flash_attn_varlen_func(q, k, v, cu_q, cu_k, mq, mk, softmax_scale=scale, causal=True)
 
 
-def segment_attention(q, k, v, seg, scale=None):
-    """Causal GQA attention over a segment table. q: [Tq, Hq, D], k / v: [Tk, Hkv, D] -> [Tq, Hq, D]."""
+def segment_attention(q, k, v, seg, scale=None, sinks=None):
+    """Causal GQA attention over a segment table. q: [Tq, Hq, D], k / v: [Tk, Hkv, D] -> [Tq, Hq, D]. ``sinks`` [Hq]
+    (optional, learnable): a per-head logit added to every row's softmax denominator."""
     from slime_b200 import ops
 
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
-    if not q.is_cuda:
-        return _reference_segments(q, k, v, seg, scale)
+    if not q.is_cuda or q.shape[-1] not in (64, 128):
+        # the flash kernels cover head dims 64 and 128; other widths (256 in Qwen3-Next / Qwen3.5) take the explicit form
+        return _reference_segments(q, k, v, seg, scale, sinks)
+    if sinks is not None:
+        return _SinkFlashAttention.apply(q, k, v, seg, scale, sinks)
     if ops.library_mode():
         return _library_segments(q, k, v, seg, scale)
     return _FlashAttention.apply(q, k, v, seg, scale)
 
 
-def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=True):
+def varlen_attention(q, k, v, cu_seqlens, max_seqlen=None, scale=None, causal=True, sinks=None):
     """Packed causal self-attention (one segment per sequence)."""
     assert causal, "the attention kernels are causal"
-    return segment_attention(q, k, v, segments_from_cu_seqlens(cu_seqlens), scale)
+    return segment_attention(q, k, v, segments_from_cu_seqlens(cu_seqlens), scale, sinks)
 
 
 def extend_attention(q, k_all, v_all, cu_q, cu_k, scale=None):

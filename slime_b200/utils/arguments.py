@@ -230,6 +230,13 @@ _MODEL = [
     _f("--kv-lora-rank", type=int, default=None), _f("--qk-head-dim", type=int, default=None),
     _f("--qk-pos-emb-head-dim", type=int, default=None), _f("--v-head-dim", type=int, default=None),
     _f("--mscale", type=float, default=1.0), _f("--mscale-all-dim", type=float, default=1.0),
+    _f("--qk-layernorm-full", action=_T), _f("--softmax-sinks", action=_T),
+    _f("--full-attention-interval", type=int, default=None), _f("--linear-num-key-heads", type=int, default=None),
+    _f("--linear-num-value-heads", type=int, default=None), _f("--linear-key-head-dim", type=int, default=None),
+    _f("--linear-value-head-dim", type=int, default=None), _f("--linear-conv-kernel-dim", type=int, default=4),
+    _f("--index-topk", type=int, default=None), _f("--index-n-heads", type=int, default=None),
+    _f("--index-head-dim", type=int, default=None), _f("--index-topk-freq", type=int, default=1),
+    _f("--index-skip-topk-offset", type=int, default=0),
     _f("--spec", type=str, nargs="*", default=None), _f("--enable-experimental", action=_T),
     _f("--no-masked-softmax-fusion", action=_T), _f("--no-gradient-accumulation-fusion", action=_T),
     _f("--init-method-std", type=float, default=0.02),

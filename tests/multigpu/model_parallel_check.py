@@ -1,6 +1,6 @@
 """Run under torchrun: the trainer model under a parallel layout equals a single-rank plain-PyTorch model.
 
-    MODE=tp | tp_sp | pp | pp_vpp | ep | dp | tp_dp | cp   DEVICE=cpu (gloo, fp32) | cuda (nccl, bf16)
+    MODE=tp | tp_sp | pp | pp_vpp | ep | dp | tp_dp | cp | tp_sp_moe | tp_ep_moe   DEVICE=cpu (gloo, fp32) | cuda (nccl, bf16)
 
 Every rank builds the same full set of weights from one seed (Megatron names, full shapes), keeps the shard its
 coordinates own, and runs forward + backward of a weighted next-token log-likelihood over a few packed micro-batches
@@ -22,7 +22,8 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspa
 LAYOUTS = {  # mode -> (tp, pp, vpp, ep, sequence_parallel); "cp" is context parallel over the whole world
     "tp": (2, 1, None, 1, False), "tp_sp": (2, 1, None, 1, True), "pp": (1, 2, None, 1, False),
     "pp_vpp": (1, 2, 2, 1, False), "ep": (1, 1, None, 2, False), "dp": (1, 1, None, 1, False),
-    "tp_dp": (2, 1, None, 1, True), "cp": (1, 1, None, 1, False),
+    "tp_dp": (2, 1, None, 1, True), "cp": (1, 1, None, 1, False), "tp_sp_moe": (2, 1, None, 1, True),
+    "tp_ep_moe": (2, 1, None, 2, True),
 }  # fmt: skip
 
 
@@ -135,7 +136,7 @@ def main():
     tp, pp, vpp, ep, sp = LAYOUTS[mode]
     cp = world if mode == "cp" else 1
     mpu.initialize_model_parallel(tp, pp, vpp, cp, ep, 1, **({} if cuda else {"backend": "gloo"}))
-    moe = mode == "ep"
+    moe = mode in ("ep", "tp_sp_moe", "tp_ep_moe")
     cfg = ModelConfig(num_layers=4, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=64,
                       ffn_hidden_size=256, vocab_size=512, rotary_base=1e4, tie_word_embeddings=False, qk_layernorm=True,
                       num_experts=4 if moe else None, moe_ffn_hidden_size=128 if moe else None, moe_router_topk=2)  # fmt: skip
@@ -237,50 +238,45 @@ def main():
     if mpu.is_pipeline_last_stage():
         torch.testing.assert_close(float(mine), float(ref_loss.detach()), rtol=rtol, atol=atol * 10)
 
-    # gradients: every local shard against the oracle's slice; DP-reduced buffers hold the sum over DP ranks
-    worst = 0.0
-    sq = torch.zeros(1, dtype=torch.float64, device=dev)
-    for name, (gname, p) in local_slices.items():
+    # gradients: every local shard against the oracle's slice. A flat buffer reduced over a group of one rank holds whole
+    # gradients; one reduced over several ranks (data parallel, or expert-data parallel = the tensor-parallel ranks
+    # when experts are not tensor-parallel) holds the sum over those ranks in each rank's shard of the buffer only.
+    def oracle_slice(gname, p):
         gfull = Wg[gname].grad
         if getattr(p, "tensor_model_parallel", False) and not getattr(p, "is_expert", False):
             if gname in ("embedding.word_embeddings.weight", "output_layer.weight"):
-                want = gfull.chunk(tp, 0)[tpr]
-            else:
-                want = convert.shard_for_tp(cfg, gname, gfull, p.partition_dim, getattr(p, "partition_stride", 1), tp, tpr)
+                return gfull.chunk(tp, 0)[tpr]
+            return convert.shard_for_tp(cfg, gname, gfull, p.partition_dim, getattr(p, "partition_stride", 1), tp, tpr)
+        return gfull
+
+    worst = 0.0
+    sq = torch.zeros(1, dtype=torch.float64, device=dev)
+    whole = all(b.group_size == 1 for b in model.buffers)
+    for b in model.buffers:
+        if b.group_size == 1:
+            for name, p in zip(b.names, b.params):
+                gname = global_param_name(name, p)
+                want, got = oracle_slice(gname, p), p.main_grad.float().cpu()
+                err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-6)
+                worst = max(worst, err)
+                assert err < (5e-2 if cuda else 2e-3), (name, err)
+                own_tp = (not getattr(p, "tensor_model_parallel", False)) and tpr != 0 and not getattr(p, "is_expert", False)
+                if not own_tp:  # replicated parameters count once
+                    sq += got.double().pow(2).sum().to(dev)
         else:
-            want = gfull
-        got = p.main_grad.float().cpu()
-        if dpcp == 1:  # with data parallelism the reduced gradient only exists per flat-buffer shard: checked below
-            err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-6)
-            worst = max(worst, err)
-            assert err < (5e-2 if cuda else 2e-3), (name, err)
-        own_tp = (not getattr(p, "tensor_model_parallel", False)) and tpr != 0 and not getattr(p, "is_expert", False)
-        if not own_tp:  # replicated parameters count once
-            sq += got.double().pow(2).sum().to(dev)
-    if dpcp == 1:
-        dist.all_reduce(sq)  # tp / pp / ep ranks hold disjoint parameters (replicated ones were counted once)
-        ref_sq = sum(float(v.grad.double().pow(2).sum()) for v in Wg.values() if v.grad is not None)
-        torch.testing.assert_close(float(sq) ** 0.5, ref_sq**0.5, rtol=rtol, atol=atol)
-    else:
-        # data parallel: the reduced gradient lives in each rank's shard of the flat buffer
-        for b in model.buffers:
-            s, e = b.shard_range()
+            s0, e0 = b.shard_range()
             flat_ref = torch.zeros(b.numel)
             for (name, p), (ps, pe) in zip(zip(b.names, b.params), b.offsets):
-                gname = global_param_name(name, p)
-                gfull = Wg[gname].grad
-                if getattr(p, "tensor_model_parallel", False) and not getattr(p, "is_expert", False):
-                    if gname in ("embedding.word_embeddings.weight", "output_layer.weight"):
-                        gfull = gfull.chunk(tp, 0)[tpr]
-                    else:
-                        gfull = convert.shard_for_tp(cfg, gname, gfull, p.partition_dim, getattr(p, "partition_stride", 1), tp, tpr)
-                flat_ref[ps:pe] = gfull.reshape(-1)
-            got = b.grad_data[s:e].float().cpu()
-            want = flat_ref[s:e]
+                flat_ref[ps:pe] = oracle_slice(global_param_name(name, p), p).reshape(-1)
+            got, want = b.grad_data[s0:e0].float().cpu(), flat_ref[s0:e0]
             err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-6)
             worst = max(worst, err)
             # bf16 router logits flip near-tie top-k choices of the random MoE: expert gradients then differ visibly
-            assert err < ((0.3 if moe else 5e-2) if cuda else 2e-3), ("dp shard", err)
+            assert err < ((0.3 if moe else 5e-2) if cuda else 2e-3), ("reduced shard", b.names[0], err)
+    if whole:
+        dist.all_reduce(sq)  # tp / pp / ep ranks hold disjoint parameters (replicated ones were counted once)
+        ref_sq = sum(float(v.grad.double().pow(2).sum()) for v in Wg.values() if v.grad is not None)
+        torch.testing.assert_close(float(sq) ** 0.5, ref_sq**0.5, rtol=rtol, atol=atol)
     dist.barrier()
     if rank == 0:
         print(f"RESULT ok mode={mode} world={world} device={dev.type} worst_grad_rel_err={worst:.2e}", flush=True)

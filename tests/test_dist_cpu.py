@@ -19,7 +19,8 @@ def test_invariants(mode, world, port):
 
 
 @pytest.mark.parametrize("mode,world,port", [("tp", 2, 29691), ("tp_sp", 2, 29692), ("pp", 2, 29693), ("pp_vpp", 2, 29694),
-                                             ("ep", 2, 29695), ("dp", 2, 29696), ("tp_dp", 4, 29697), ("cp", 2, 29698)])
+                                             ("ep", 2, 29695), ("dp", 2, 29696), ("tp_dp", 4, 29697), ("cp", 2, 29698),
+                                             ("tp_sp_moe", 2, 29701), ("tp_ep_moe", 2, 29702)])
 def test_model_under_parallel_layout_matches_single_rank_oracle(mode, world, port):
     """4-layer trainer model (qk-norm, GQA, dense or MoE) under each layout: loss, gradient shards and gradient norm
     equal a plain-PyTorch single-rank transformer."""

@@ -1,0 +1,188 @@
+"""Token mixers (models/mixers.py) on CPU: each against an independent, slower statement of its definition."""
+
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from slime_b200.models import mixers
+from slime_b200.models.config import ModelConfig
+from slime_b200.models.gpt import GPTModel, PackedSeqParams
+
+
+def packed_for(lens, pad_to=None):
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    T = cu[-1]
+    pos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lens])
+    if pad_to and T % pad_to:
+        pad = pad_to - T % pad_to
+        cu.append(T + pad)
+        pos = torch.cat([pos, torch.arange(pad, dtype=torch.int32)])
+    p = PackedSeqParams(torch.tensor(cu, dtype=torch.int32), max(lens), pos)
+    return p, pos.numel()
+
+
+def test_chunked_gated_delta_rule_matches_the_recurrence_with_gradients():
+    torch.manual_seed(0)
+    lens, H, Dk, Dv = [70, 5, 129], 3, 8, 12
+    T = sum(lens)
+    cu = torch.tensor([0, 70, 75, 204], dtype=torch.int32)
+    mk = lambda *s: torch.randn(*s, dtype=torch.float64).float().requires_grad_()  # noqa: E731
+    q, k, v = mk(T, H, Dk), mk(T, H, Dk), mk(T, H, Dv)
+    g = (-torch.rand(T, H) * 0.5).requires_grad_()
+    beta = torch.rand(T, H).requires_grad_()
+    ref = mixers.gated_delta_rule_recurrent(q, k, v, g, beta, cu)
+    for chunk in (16, 64):
+        out = mixers.gated_delta_rule_chunked(q, k, v, g, beta, cu, chunk=chunk)
+        assert torch.allclose(out, ref, atol=2e-5, rtol=1e-4), float((out - ref).abs().max())
+    w = torch.randn_like(ref)
+    grads_ref = torch.autograd.grad((ref * w).sum(), [q, k, v, g, beta])
+    grads = torch.autograd.grad((mixers.gated_delta_rule_chunked(q, k, v, g, beta, cu, chunk=32) * w).sum(), [q, k, v, g, beta])
+    for a, b in zip(grads, grads_ref):
+        assert torch.allclose(a, b, atol=5e-4, rtol=1e-3), float((a - b).abs().max())
+
+
+def test_short_conv_restarts_at_every_sequence():
+    torch.manual_seed(1)
+    lens, C, K = [5, 1, 7], 6, 4
+    p, T = packed_for(lens)
+    x, w = torch.randn(T, C), torch.randn(C, K)
+    got = mixers.causal_short_conv(x, w, p.position_ids)
+    off = 0
+    for n in lens:
+        seq = x[off : off + n].t()[None]  # [1, C, n]
+        ref = F.silu(F.conv1d(F.pad(seq, (K - 1, 0)), w[:, None, :], groups=C))[0].t()
+        assert torch.allclose(got[off : off + n], ref, atol=1e-6)
+        off += n
+
+
+def test_partial_and_interleaved_rotary():
+    from slime_b200 import ops
+
+    T, H, D, rot = 9, 2, 16, 8
+    x = torch.randn(T, H, D)
+    pos = torch.arange(T)
+    table = ops.rope_cos_sin(32, rot, 1e4)
+    cos, sin = mixers.rotary_cos_sin(table, pos)
+    y = mixers.apply_rotary(x, cos, sin)
+    assert torch.equal(y[..., rot:], x[..., rot:])  # pass-through part
+    inv = 1.0 / (1e4 ** (torch.arange(0, rot, 2).float() / rot))
+    ang = pos[:, None].float() * inv[None]
+    x1, x2 = x[..., : rot // 2], x[..., rot // 2 : rot]
+    assert torch.allclose(y[..., : rot // 2], x1 * ang.cos()[:, None] - x2 * ang.sin()[:, None], atol=1e-5)
+    yi = mixers.apply_rotary(x, cos, sin, interleaved=True)
+    a, b = x[..., 0:rot:2], x[..., 1:rot:2]
+    assert torch.allclose(yi[..., 0:rot:2], a * ang.cos()[:, None] - b * ang.sin()[:, None], atol=1e-5)
+    assert torch.allclose(yi[..., 1:rot:2], b * ang.cos()[:, None] + a * ang.sin()[:, None], atol=1e-5)
+    # norms are preserved by a rotation
+    assert torch.allclose(yi.norm(dim=-1), x.norm(dim=-1), atol=1e-5)
+
+
+def test_softmax_sinks_match_an_explicit_extra_column_and_train():
+    from slime_b200.ops import attention
+
+    torch.manual_seed(2)
+    T, Hq, Hkv, D = 11, 4, 2, 8
+    q, k, v = torch.randn(T, Hq, D), torch.randn(T, Hkv, D), torch.randn(T, Hkv, D)
+    sinks = torch.randn(Hq, requires_grad=True)
+    seg = attention.segments_from_cu_seqlens(torch.tensor([0, 4, 11], dtype=torch.int32))
+    out = attention.segment_attention(q, k, v, seg, 0.3, sinks=sinks)
+    # explicit: a zero-valued key whose logit is the sink
+    ref = torch.zeros_like(out)
+    for a, b in ((0, 4), (4, 11)):
+        for h in range(Hq):
+            s = (q[a:b, h] @ k[a:b, h // 2].t()) * 0.3
+            s = s.masked_fill(~torch.ones(b - a, b - a, dtype=torch.bool).tril(), float("-inf"))
+            p = torch.cat([s, sinks[h].expand(b - a, 1)], -1).softmax(-1)
+            ref[a:b, h] = p[:, :-1] @ v[a:b, h // 2]
+    assert torch.allclose(out, ref, atol=1e-5)
+    # the gate form used on the GPU path: plain attention times sigmoid(lse - sink)
+    plain = attention.segment_attention(q, k, v, seg, 0.3)
+    lse = torch.stack([torch.cat([torch.logsumexp(((q[a:b, h] @ k[a:b, h // 2].t()) * 0.3).masked_fill(
+        ~torch.ones(b - a, b - a, dtype=torch.bool).tril(), float("-inf")), -1) for a, b in ((0, 4), (4, 11))]) for h in range(Hq)])
+    assert torch.allclose(out, plain * torch.sigmoid(lse - sinks[:, None]).t()[:, :, None], atol=1e-5)
+    out.sum().backward()
+    assert sinks.grad is not None and float(sinks.grad.abs().sum()) > 0
+
+
+def _tiny(**kw):
+    base = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2, kv_channels=16, ffn_hidden_size=128,
+                vocab_size=256, rotary_base=1e4, tie_word_embeddings=False)  # fmt: skip
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+@pytest.mark.parametrize("kw,kinds", [
+    (dict(rotary_percent=0.5, rotary_interleaved=True, post_self_attn_layernorm=True, post_mlp_layernorm=True), ["general_attention"] * 2),
+    (dict(qk_layernorm_full=True, softmax_sinks=True), ["general_attention"] * 2),
+    (dict(num_layers=4, full_attention_interval=4, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+          linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25),
+     ["gated_delta_net"] * 3 + ["general_attention"]),
+    (dict(multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4, v_head_dim=8), ["mla"] * 2),
+    (dict(num_layers=3, multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4,
+          v_head_dim=8, index_topk=4, index_n_heads=2, index_head_dim=8, index_topk_freq=2, index_skip_topk_offset=1), ["dsa"] * 3),
+], ids=["glm4_partial_rotary", "minimax_full_norm_sinks", "qwen3_next_hybrid", "mla", "dsa_shared_topk"])  # fmt: skip
+def test_models_with_each_mixer_are_causal_packed_and_trainable(kw, kinds):
+    """Whole model per family: the layer kinds are as configured; logits of a token do not depend on later tokens or on
+    the other sequences of the pack; every parameter receives a gradient (indexer weights excepted: the choice they
+    make is discrete)."""
+    torch.manual_seed(0)
+    cfg = _tiny(**kw)
+    assert [cfg.mixer(i) for i in range(cfg.num_layers)] == kinds
+    model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=1)
+    lens = [9, 6]
+    ids = torch.randint(0, cfg.vocab_size, (sum(lens),))
+    p, T = packed_for(lens)
+    logits = model(ids, position_ids=p.position_ids, packed_seq_params=p)[0]
+    assert logits.shape == (T, cfg.vocab_size) and torch.isfinite(logits).all()
+    # sequence 1 alone gives the same logits; changing its last token leaves earlier rows alone
+    p1, _ = packed_for([9])
+    alone = model(ids[:9], position_ids=p1.position_ids, packed_seq_params=p1)[0]
+    assert torch.allclose(alone, logits[:9], atol=1e-4), float((alone - logits[:9]).abs().max())
+    ids2 = ids.clone()
+    ids2[8] = (ids2[8] + 1) % cfg.vocab_size
+    p, _ = packed_for(lens)
+    moved = model(ids2, position_ids=p.position_ids, packed_seq_params=p)[0]
+    assert torch.allclose(moved[:8], logits[:8], atol=1e-5) and torch.allclose(moved[9:], logits[9:], atol=1e-5)
+    assert not torch.allclose(moved[8], logits[8], atol=1e-5)
+    p, _ = packed_for(lens)
+    model(ids, position_ids=p.position_ids, packed_seq_params=p)[0].logsumexp(-1).sum().backward()
+    missing = [n for n, q in model.named_parameters() if q.grad is None or float(q.grad.abs().sum()) == 0]
+    assert all(any(t in n for t in ("wq_b", "wk.", "k_norm", "weights_proj")) for n in missing), missing
+
+
+def test_dsa_restricts_attention_to_the_indexers_choice():
+    torch.manual_seed(3)
+    cfg = _tiny(num_layers=1, multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4,
+                v_head_dim=8, index_topk=3, index_n_heads=2, index_head_dim=8)  # fmt: skip
+    layer = mixers.DSASelfAttention(cfg, 0, torch.float32, "cpu", False)
+    p, T = packed_for([10, 4])
+    x = torch.randn(T, cfg.hidden_size)
+    out, _ = layer(x, None, None, p)
+    allowed = getattr(p, layer._HOLDER)[0]
+    assert allowed.shape == (T, 10)
+    counts = allowed.sum(-1)
+    # rows with at most top-k visible keys keep all of them, the others exactly top-k, never a future key
+    assert counts[:3].tolist() == [1, 2, 3] and (counts[3:10] == 3).all() and counts[10:].tolist() == [1, 2, 3, 3]
+    assert not allowed[:10].triu(1).any()
+    # with top-k >= sequence length the layer is plain latent attention
+    cfg_all = ModelConfig(**{**cfg.__dict__, "index_topk": 64})
+    dense = mixers.MLASelfAttention(cfg_all, 0, torch.float32, "cpu", False)
+    sparse = mixers.DSASelfAttention(cfg_all, 0, torch.float32, "cpu", False)
+    sparse.load_state_dict(dense.state_dict(), strict=False)
+    p1, _ = packed_for([10, 4])
+    p2, _ = packed_for([10, 4])
+    assert torch.allclose(dense(x, None, None, p1)[0], sparse(x, None, None, p2)[0], atol=1e-6)
+
+
+def test_indexer_logits_definition():
+    q, k, w = torch.randn(5, 3, 4), torch.randn(7, 4), torch.randn(5, 3)
+    ref = torch.zeros(5, 7)
+    for t in range(5):
+        for s in range(7):
+            ref[t, s] = sum(float(w[t, h]) * max(float(q[t, h] @ k[s]), 0.0) for h in range(3))
+    assert torch.allclose(mixers.indexer_logits(q, k, w), ref, atol=1e-5)
+    assert math.isfinite(float(ref.sum()))

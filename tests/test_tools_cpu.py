@@ -123,9 +123,16 @@ def test_model_presets_round_trip_through_flags():
             assert a == b, (name, f.name, a, b)
     import pytest
 
-    with pytest.raises(KeyError, match="MLA"):
-        get_preset("kimi-k2")
+    with pytest.raises(KeyError, match="vision tower"):
+        get_preset("qwen3.5-35b-a3b-vl")
     assert get_preset("qwen3-235b-a22b").num_params() > 2.3e11
+    # the parameter counts of the latent-attention and hybrid families agree with the published sizes
+    for name, billions in (("deepseek-v3", 671), ("kimi-k2", 1026), ("glm5-744b-a40b", 744), ("qwen3-next-80b-a3b", 80),
+                           ("minimax-m2", 229), ("moonlight", 16)):  # fmt: skip
+        assert abs(get_preset(name).num_params() / 1e9 - billions) < 1.0, name
+    kinds = [get_preset("qwen3-next-80b-a3b").mixer(i) for i in range(8)]
+    assert kinds == ["gated_delta_net"] * 3 + ["general_attention"] + ["gated_delta_net"] * 3 + ["general_attention"]
+    assert get_preset("glm5-744b-a40b").mixer(0) == "dsa" and get_preset("kimi-k2").mixer(5) == "mla"
 
 
 def test_run_recipes_produce_parseable_command_lines(tmp_path):
