@@ -51,6 +51,13 @@ class TrainModel:
         dtype = torch.bfloat16 if getattr(args, "bf16", True) else torch.float32
         provider = load_function(args.custom_model_provider_path) if getattr(args, "custom_model_provider_path", None) else None
         self.chunks: list[GPTModel] = []
+        spec = getattr(args, "spec", None)
+        if spec and len(spec) == 2 and not spec[0].startswith("slime_plugins."):
+            # --spec <module> <function>: a per-layer mixer factory (the reference passes Megatron layer specs this way,
+            # e.g. scripts/models/qwen3-next-80B-A3B.sh; its own plug-in names select the built-in mixers instead)
+            from slime_b200.models import mixers
+
+            mixers.set_custom_builder(load_function(f"{spec[0]}.{spec[1]}"))
         for v in range(vpp):
             rng = pipeline_layer_range(self.cfg, pp, ppr, getattr(args, "decoder_first_pipeline_num_layers", None),
                                        getattr(args, "decoder_last_pipeline_num_layers", None), vpp, v)  # fmt: skip

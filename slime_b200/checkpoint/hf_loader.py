@@ -65,7 +65,7 @@ def supports_hf_weight_loading(path: str) -> bool:
             arch = (json.load(f).get("architectures") or [""])[0].lower()
     except OSError:
         return False
-    return any(k in arch for k in ("qwen2", "qwen3", "llama", "glm4", "mimo", "minimax", "deepseek"))
+    return any(k in arch for k in ("qwen2", "qwen3", "llama", "glm", "mimo", "minimax", "deepseek", "kimi"))
 
 
 @torch.no_grad()
@@ -87,7 +87,7 @@ def load_hf_weights(path: str, model) -> list[str]:
         if not all(s in reader for s in sources):
             missing.append(name)
             continue
-        full = convert.merge_hf_sources(rule, [reader.get(s) for s in sources])
+        full = convert.merge_hf_sources(rule, [reader.get(s) for s in sources], cfg)
         if name in ("embedding.word_embeddings.weight", "output_layer.weight"):
             full = convert.pad_vocab(full, cfg.padded_vocab_size)
         if getattr(p, "tensor_model_parallel", False) and tp > 1 and not getattr(p, "is_expert", False):

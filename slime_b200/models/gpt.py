@@ -159,7 +159,9 @@ class TransformerLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
         super().__init__()
         self.layer_number = layer_number  # global, 0-based
-        if cfg.mixer(layer_number) == "attention":
+        from slime_b200.models import mixers as _mixers
+
+        if cfg.mixer(layer_number) == "attention" and _mixers._CUSTOM_BUILDER is None:
             self.self_attention = SelfAttention(cfg, layer_number, dtype, device, sequence_parallel)
         else:  # attention variants, linear attention, latent attention: models/mixers.py
             from slime_b200.models.mixers import build_mixer

@@ -276,8 +276,9 @@ def causal_short_conv(x, weight, positions, activation=True):
 
 class GatedDeltaNet(nn.Module):
     """Qwen3-Next / Qwen3.5 linear-attention layer. Parameters (replicated over tensor-parallel ranks):
-    ``in_proj_qkvz`` [2 Kdim + 2 Vdim, H] (rows grouped per key head: q, k, then that head's value and gate heads),
-    ``in_proj_ba`` [2 Hv, H], ``conv1d.weight`` [2 Kdim + Vdim, K], ``A_log`` / ``dt_bias`` [Hv], ``norm.weight`` [Dv],
+    ``in_proj_qkvz`` [2 Kdim + 2 Vdim, H] (rows grouped per key head: q, k, then that head's value and gate heads) and
+    ``in_proj_ba`` [2 Hv, H] for Qwen3-Next, or ``in_proj_qkv`` [2 Kdim + Vdim, H], ``in_proj_z`` [Vdim, H],
+    ``in_proj_b`` / ``in_proj_a`` [Hv, H] for Qwen3.5; ``conv1d.weight`` [2 Kdim + Vdim, K], ``A_log`` / ``dt_bias`` [Hv], ``norm.weight`` [Dv],
     ``out_proj`` [H, Vdim], ``input_layernorm.weight`` [H]."""
 
     def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
@@ -291,9 +292,19 @@ class GatedDeltaNet(nn.Module):
         self.input_layernorm = nn.Module()
         self.input_layernorm.weight = _replicated((h,), dtype, device, ones=True)
         self.input_layernorm.weight.sequence_parallel = sequence_parallel
-        self.in_proj_qkvz, self.in_proj_ba, self.conv1d, self.norm, self.out_proj = (nn.Module() for _ in range(5))
-        self.in_proj_qkvz.weight = _replicated((2 * self.key_dim + 2 * self.value_dim, h), dtype, device, std)
-        self.in_proj_ba.weight = _replicated((2 * self.hv, h), dtype, device, std)
+        self.conv1d, self.norm, self.out_proj = (nn.Module() for _ in range(3))
+        # Qwen3-Next fuses the input projections (rows grouped per key head); Qwen3.5 keeps four plain ones
+        self.fused_in_proj = "qwen3next" in (cfg.model_arch or "").lower().replace("_", "")
+        if self.fused_in_proj:
+            self.in_proj_qkvz, self.in_proj_ba = nn.Module(), nn.Module()
+            self.in_proj_qkvz.weight = _replicated((2 * self.key_dim + 2 * self.value_dim, h), dtype, device, std)
+            self.in_proj_ba.weight = _replicated((2 * self.hv, h), dtype, device, std)
+        else:
+            self.in_proj_qkv, self.in_proj_z, self.in_proj_b, self.in_proj_a = (nn.Module() for _ in range(4))
+            self.in_proj_qkv.weight = _replicated((2 * self.key_dim + self.value_dim, h), dtype, device, std)
+            self.in_proj_z.weight = _replicated((self.value_dim, h), dtype, device, std)
+            self.in_proj_b.weight = _replicated((self.hv, h), dtype, device, std)
+            self.in_proj_a.weight = _replicated((self.hv, h), dtype, device, std)
         self.conv1d.weight = _replicated((2 * self.key_dim + self.value_dim, cfg.linear_conv_kernel_dim), dtype, device, 0.2)
         self.dt_bias = _replicated((self.hv,), torch.float32, device, ones=True)
         gen = tp.get_rng_tracker().states.get("default")
@@ -315,8 +326,13 @@ class GatedDeltaNet(nn.Module):
         normed, residual = ops.rmsnorm(x, self.input_layernorm.weight, cfg.norm_epsilon, residual)
         inp = tp.gather_from_sequence_parallel_region_no_reduce(normed) if self.sp else normed
         T = inp.shape[0]
-        q, k, v, z, b, a = self._split(F.linear(inp, self.in_proj_qkvz.weight), F.linear(inp, self.in_proj_ba.weight))
-        mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+        if self.fused_in_proj:
+            q, k, v, z, b, a = self._split(F.linear(inp, self.in_proj_qkvz.weight), F.linear(inp, self.in_proj_ba.weight))
+            mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+        else:
+            mixed = F.linear(inp, self.in_proj_qkv.weight)
+            z = F.linear(inp, self.in_proj_z.weight).view(T, self.hv, self.dv)
+            b, a = F.linear(inp, self.in_proj_b.weight), F.linear(inp, self.in_proj_a.weight)
         mixed = causal_short_conv(mixed, self.conv1d.weight, packed.position_ids)
         q, k, v = mixed.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k, v = q.view(T, self.hk, self.dk), k.view(T, self.hk, self.dk), v.view(T, self.hv, self.dv)
@@ -485,7 +501,52 @@ class DSASelfAttention(MLASelfAttention):
         return allowed
 
 
+class HuggingfaceAttention(nn.Module):
+    """Run a Hugging Face style token-mixing module as a layer of this model: the pre-norm, the sequence-parallel gather
+    before and the split after are done here, ``hf_forward`` sees ``[1, T, H]`` hidden states of the whole packed stream
+    plus the packing metadata. Its parameters are replicated over tensor-parallel ranks. Subclass and override
+    ``hf_forward``, or pass ``module`` whose ``forward(hidden_states, position_ids=..., cu_seqlens=...)`` returns the
+    mixed hidden states (a tuple's first element is taken). Same role as slime_plugins/models/hf_attention.py:63-173 in
+    the reference."""
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool, module: nn.Module | None = None):
+        super().__init__()
+        self.cfg, self.sp, self.layer_number = cfg, sequence_parallel, layer_number
+        self.input_layernorm = nn.Module()
+        self.input_layernorm.weight = _replicated((cfg.hidden_size,), dtype, device, ones=True)
+        self.input_layernorm.weight.sequence_parallel = sequence_parallel
+        self.hf_module = module
+        if module is not None:
+            module.to(device=device, dtype=dtype)
+            for p in module.parameters():
+                tp.set_tp_attrs(p, False)
+
+    def hf_forward(self, hidden_states, packed):
+        out = self.hf_module(hidden_states, position_ids=packed.position_ids.reshape(1, -1).long(), cu_seqlens=packed.cu_seqlens)
+        return out[0] if isinstance(out, tuple) else out
+
+    def forward(self, x, residual, rope_table, packed):
+        normed, residual = ops.rmsnorm(x, self.input_layernorm.weight, self.cfg.norm_epsilon, residual)
+        inp = tp.gather_from_sequence_parallel_region_no_reduce(normed) if self.sp else normed
+        out = self.hf_forward(inp.unsqueeze(0), packed).squeeze(0)
+        return (tp.scatter_to_sequence_parallel_region(out) if self.sp else out), residual
+
+
+_CUSTOM_BUILDER = None
+
+
+def set_custom_builder(fn) -> None:
+    """``fn(cfg, layer_number, dtype, device, sequence_parallel) -> module | None`` is asked first for every layer's
+    mixer (``--spec <module> <function>`` installs it); None falls through to the built-in choice."""
+    global _CUSTOM_BUILDER
+    _CUSTOM_BUILDER = fn
+
+
 def build_mixer(cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+    if _CUSTOM_BUILDER is not None:
+        custom = _CUSTOM_BUILDER(cfg, layer_number, dtype, device, sequence_parallel)
+        if custom is not None:
+            return custom
     kind = cfg.mixer(layer_number)
     if kind == "attention":
         from slime_b200.models.gpt import SelfAttention

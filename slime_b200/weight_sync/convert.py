@@ -55,6 +55,69 @@ def qkv_from_megatron_layout(cfg: ModelConfig, t: torch.Tensor) -> torch.Tensor:
     return torch.cat([q, k, v], dim=0)
 
 
+def _qkv_pieces(cfg: ModelConfig, tp: int = 1) -> list[int]:
+    """Row counts of the pieces of a fused projection shard: q, (gate,) k, v."""
+    d = cfg.head_dim
+    q, k = cfg.num_attention_heads // tp * d, cfg.num_query_groups // tp * d
+    return [q] * (2 if cfg.attention_output_gate else 1) + [k, k]
+
+
+def _zero_centred(cfg: ModelConfig) -> bool:
+    """Qwen3-Next / Qwen3.5 checkpoints store ``w - 1`` for their RMSNorm weights (the layer computes ``1 + w``); the
+    trainer keeps the effective weight."""
+    return _family(cfg) in ("qwen3next", "qwen3_5")
+
+
+# trainer name inside ``self_attention.`` -> checkpoint name inside the layer, for the mixers of models/mixers.py
+_MIXER_NAMES = {
+    # gated delta-net
+    "input_layernorm.weight": "input_layernorm.weight", "in_proj_qkvz.weight": "linear_attn.in_proj_qkvz.weight",
+    "in_proj_ba.weight": "linear_attn.in_proj_ba.weight", "in_proj_qkv.weight": "linear_attn.in_proj_qkv.weight",
+    "in_proj_z.weight": "linear_attn.in_proj_z.weight", "in_proj_b.weight": "linear_attn.in_proj_b.weight",
+    "in_proj_a.weight": "linear_attn.in_proj_a.weight", "conv1d.weight": "linear_attn.conv1d.weight",
+    "dt_bias": "linear_attn.dt_bias", "A_log": "linear_attn.A_log", "norm.weight": "linear_attn.norm.weight",
+    "out_proj.weight": "linear_attn.out_proj.weight",
+    # latent attention (DeepSeek-V3 naming)
+    "linear_q_down_proj.weight": "self_attn.q_a_proj.weight", "linear_q_up_proj.weight": "self_attn.q_b_proj.weight",
+    "linear_q_proj.weight": "self_attn.q_proj.weight", "linear_kv_down_proj.weight": "self_attn.kv_a_proj_with_mqa.weight",
+    "kv_layernorm.weight": "self_attn.kv_a_layernorm.weight", "linear_kv_up_proj.weight": "self_attn.kv_b_proj.weight",
+    # lightning indexer
+    "wq_b.weight": "self_attn.indexer.wq_b.weight", "wk.weight": "self_attn.indexer.wk.weight",
+    "k_norm.weight": "self_attn.indexer.k_norm.weight", "k_norm.bias": "self_attn.indexer.k_norm.bias",
+    "weights_proj.weight": "self_attn.indexer.weights_proj.weight",
+    # learnable sinks
+    "softmax_offset": "self_attn.sinks",
+}  # fmt: skip
+_ZERO_CENTRED = ("input_layernorm.weight", "post_attention_layernorm.weight", "model.norm.weight", "q_norm.weight", "k_norm.weight")
+
+
+def _mixer_to_hf(cfg: ModelConfig, layer: str, sub: str, t: torch.Tensor):
+    """``self_attention.<sub>`` of a non-standard mixer -> checkpoint pairs, or None when ``sub`` is not one of theirs."""
+    p = f"model.layers.{layer}"
+    latent = cfg.multi_latent_attention
+    if sub == "q_layernorm.weight" and latent:
+        return [(f"{p}.self_attn.q_a_layernorm.weight", t)]
+    if sub not in _MIXER_NAMES:
+        return None
+    if sub == "conv1d.weight":
+        t = t.unsqueeze(1)  # depthwise Conv1d weight [C, 1, K]
+    return [(f"{p}.{_MIXER_NAMES[sub]}", t)]
+
+
+def _gated_q_to_hf(cfg: ModelConfig, q: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """[q heads] + [gate heads] -> the checkpoint's q_proj rows, per head (query, gate)."""
+    d, h = cfg.head_dim, cfg.num_attention_heads
+    rest = q.shape[1:]
+    return torch.cat([q.reshape(h, d, *rest), gate.reshape(h, d, *rest)], dim=1).reshape(2 * h * d, *rest)
+
+
+def _gated_q_from_hf(cfg: ModelConfig, qg: torch.Tensor):
+    d, h = cfg.head_dim, cfg.num_attention_heads
+    rest = qg.shape[1:]
+    x = qg.reshape(h, 2 * d, *rest)
+    return x[:, :d].reshape(h * d, *rest), x[:, d:].reshape(h * d, *rest)
+
+
 def _family(cfg: ModelConfig) -> str:
     a = (cfg.model_arch or "").lower()
     for key in ("qwen3_5", "qwen3next", "qwen3moe", "qwen2moe", "qwen3", "qwen2", "glm4moe", "glm4", "llama", "mimo",
@@ -72,13 +135,29 @@ def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[st
     if name == "output_layer.weight":
         return [("lm_head.weight", t[: cfg.vocab_size])]
     if name == "decoder.final_layernorm.weight":
-        return [("model.norm.weight", t)]
+        return [("model.norm.weight", t - 1 if _zero_centred(cfg) else t)]
     m = _LAYER.match(name)
     if m is None:
         raise ValueError(f"unknown trainer parameter name: {name}")
     i, sub = m.group(1), m.group(2)
+    out = _layer_to_hf(cfg, i, sub, t)
+    if _zero_centred(cfg):
+        out = [(n, x - 1 if n.endswith(_ZERO_CENTRED) and ".linear_attn." not in n else x) for n, x in out]
+    return out
+
+
+def _layer_to_hf(cfg: ModelConfig, i: str, sub: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
+    name = f"decoder.layers.{i}.{sub}"
     p = f"model.layers.{i}"
     fam = _family(cfg)
+    if sub.startswith("self_attention."):
+        got = _mixer_to_hf(cfg, i, sub[len("self_attention.") :], t)
+        if got is not None:
+            return got
+    if sub == "self_attention.linear_qkv.weight" and cfg.attention_output_gate:
+        q, gate, k, v = t.split(_qkv_pieces(cfg), dim=0)
+        return [(f"{p}.self_attn.q_proj.weight", _gated_q_to_hf(cfg, q, gate)), (f"{p}.self_attn.k_proj.weight", k),
+                (f"{p}.self_attn.v_proj.weight", v)]  # fmt: skip
     if sub == "self_attention.linear_qkv.weight":
         q, k, v = split_qkv(cfg, t)
         return [(f"{p}.self_attn.q_proj.weight", q), (f"{p}.self_attn.k_proj.weight", k), (f"{p}.self_attn.v_proj.weight", v)]
@@ -124,6 +203,8 @@ def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[st
     if sub == "mlp.shared_experts.linear_fc2.weight":
         sp = "shared_expert" if fam in ("qwen2moe", "qwen3next", "qwen3_5") else "shared_experts"
         return [(f"{p}.mlp.{sp}.down_proj.weight", t)]
+    if sub == "mlp.shared_experts.gate_weight":
+        return [(f"{p}.mlp.shared_expert_gate.weight", t)]
     raise ValueError(f"unknown trainer parameter name: {name}")
 
 
@@ -144,13 +225,8 @@ def merge_tp_shards(cfg: ModelConfig, name: str, shards: list[torch.Tensor], par
     if len(shards) == 1:
         return shards[0]
     if "linear_qkv" in name and partition_dim == 0:
-        tp = len(shards)
-        d = cfg.head_dim
-        hq, hkv = cfg.num_attention_heads // tp * d, cfg.num_query_groups // tp * d
-        q = torch.cat([s[:hq] for s in shards], dim=0)
-        k = torch.cat([s[hq : hq + hkv] for s in shards], dim=0)
-        v = torch.cat([s[hq + hkv :] for s in shards], dim=0)
-        return torch.cat([q, k, v], dim=0)
+        pieces = [s.split(_qkv_pieces(cfg, len(shards)), dim=0) for s in shards]  # q, (gate,) k, v of every rank
+        return torch.cat([torch.cat([pc[j] for pc in pieces], dim=0) for j in range(len(pieces[0]))], dim=0)
     if stride == 2 and partition_dim == 0:
         halves = [s.chunk(2, dim=0) for s in shards]
         return torch.cat([h[0] for h in halves] + [h[1] for h in halves], dim=0)
@@ -162,8 +238,7 @@ def shard_for_tp(cfg: ModelConfig, name: str, full: torch.Tensor, partition_dim:
     if tp == 1:
         return full
     if "linear_qkv" in name and partition_dim == 0:
-        q, k, v = split_qkv(cfg, full)
-        return torch.cat([q.chunk(tp, 0)[rank], k.chunk(tp, 0)[rank], v.chunk(tp, 0)[rank]], dim=0)
+        return torch.cat([piece.chunk(tp, 0)[rank] for piece in full.split(_qkv_pieces(cfg), dim=0)], dim=0)
     if stride == 2 and partition_dim == 0:
         g, u = full.chunk(2, dim=0)
         return torch.cat([g.chunk(tp, 0)[rank], u.chunk(tp, 0)[rank]], dim=0)
@@ -179,7 +254,7 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
     if name == "output_layer.weight":
         return ["model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"], "copy"
     if name == "decoder.final_layernorm.weight":
-        return ["model.norm.weight"], "copy"
+        return ["model.norm.weight"], "copy+1" if _zero_centred(cfg) else "copy"
     m = _LAYER.match(name)
     if m is None:
         raise ValueError(f"unknown trainer parameter name: {name}")
@@ -198,18 +273,35 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
         "mlp.router.expert_bias": "mlp.gate.e_score_correction_bias",
         "post_self_attn_layernorm.weight": "post_self_attn_layernorm.weight",
         "post_mlp_layernorm.weight": "post_mlp_layernorm.weight",
-        "mlp.shared_experts.linear_fc2.weight": "mlp.shared_experts.down_proj.weight",
     }
+    plus1 = "+1" if _zero_centred(cfg) else ""
+    if sub.startswith("self_attention."):
+        inner = sub[len("self_attention.") :]
+        if inner == "q_layernorm.weight" and cfg.multi_latent_attention:
+            return [f"{p}.self_attn.q_a_layernorm.weight"], "copy"
+        if inner in _MIXER_NAMES and not (inner == "input_layernorm.weight" and cfg.mixer(int(i)) == "attention"):
+            rule = "conv" if inner == "conv1d.weight" else ("copy" + plus1 if inner == "input_layernorm.weight" else "copy")
+            return [f"{p}.{_MIXER_NAMES[inner]}"], rule
     if sub in simple:
-        return [f"{p}.{simple[sub]}"], "copy"
+        norm = simple[sub].endswith(_ZERO_CENTRED)
+        return [f"{p}.{simple[sub]}"], "copy" + (plus1 if norm else "")
+    if sub == "self_attention.linear_qkv.weight" and cfg.attention_output_gate:
+        return [f"{p}.self_attn.{x}_proj.weight" for x in "qkv"], "gated_qkv"
     if sub == "self_attention.linear_qkv.weight":
         return [f"{p}.self_attn.{x}_proj.weight" for x in "qkv"], "qkv"
     if sub == "self_attention.linear_qkv.bias":
         return [f"{p}.self_attn.{x}_proj.bias" for x in "qkv"], "qkv"
     if sub == "mlp.linear_fc1.weight":
+        if _family(cfg) == "glm4":  # GLM-4 dense checkpoints store the fused [gate; up] matrix
+            return [f"{p}.mlp.gate_up_proj.weight"], "copy"
         return [f"{p}.mlp.gate_proj.weight", f"{p}.mlp.up_proj.weight"], "gate_up"
+    sp = "shared_expert" if _family(cfg) in ("qwen2moe", "qwen3next", "qwen3_5") else "shared_experts"
     if sub == "mlp.shared_experts.linear_fc1.weight":
-        return [f"{p}.mlp.shared_experts.gate_proj.weight", f"{p}.mlp.shared_experts.up_proj.weight"], "gate_up"
+        return [f"{p}.mlp.{sp}.gate_proj.weight", f"{p}.mlp.{sp}.up_proj.weight"], "gate_up"
+    if sub == "mlp.shared_experts.linear_fc2.weight":
+        return [f"{p}.mlp.{sp}.down_proj.weight"], "copy"
+    if sub == "mlp.shared_experts.gate_weight":
+        return [f"{p}.mlp.shared_expert_gate.weight"], "copy"
     em = _EXPERT.match(sub)
     if em:
         which, e = em.group(1), em.group(2)
@@ -219,9 +311,16 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
     raise ValueError(f"unknown trainer parameter name: {name}")
 
 
-def merge_hf_sources(rule: str, tensors: list[torch.Tensor]) -> torch.Tensor:
+def merge_hf_sources(rule: str, tensors: list[torch.Tensor], cfg: ModelConfig | None = None) -> torch.Tensor:
     if rule == "copy":
         return tensors[0]
+    if rule == "copy+1":  # zero-centred norm weight -> effective weight
+        return tensors[0] + 1
+    if rule == "conv":  # depthwise Conv1d weight [C, 1, K] -> [C, K]
+        return tensors[0].squeeze(1)
+    if rule == "gated_qkv":  # q_proj rows are per head (query, gate)
+        q, gate = _gated_q_from_hf(cfg, tensors[0])
+        return torch.cat([q, gate, tensors[1], tensors[2]], dim=0)
     return torch.cat(tensors, dim=0)  # qkv -> [q|k|v], gate_up -> [gate;up]
 
 

@@ -186,3 +186,96 @@ def test_indexer_logits_definition():
             ref[t, s] = sum(float(w[t, h]) * max(float(q[t, h] @ k[s]), 0.0) for h in range(3))
     assert torch.allclose(mixers.indexer_logits(q, k, w), ref, atol=1e-5)
     assert math.isfinite(float(ref.sum()))
+
+
+@pytest.mark.parametrize("kw,arch", [
+    (dict(rotary_percent=0.5, rotary_interleaved=True, post_self_attn_layernorm=True, post_mlp_layernorm=True), "Glm4ForCausalLM"),
+    (dict(qk_layernorm_full=True, softmax_sinks=True), "MiniMaxM2ForCausalLM"),
+    (dict(num_layers=4, full_attention_interval=4, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+          linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25, num_experts=4,
+          moe_ffn_hidden_size=32, moe_router_topk=2, moe_shared_expert_intermediate_size=32, moe_shared_expert_gate=True),
+     "Qwen3NextForCausalLM"),
+    (dict(num_layers=4, full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=8,
+          linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25), "Qwen3_5ForCausalLM"),
+    (dict(multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4, v_head_dim=8,
+          num_experts=4, moe_ffn_hidden_size=32, moe_router_topk=2, moe_layer_freq=[0, 1], moe_shared_expert_intermediate_size=32,
+          moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True), "DeepseekV3ForCausalLM"),
+    (dict(multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4, v_head_dim=8,
+          index_topk=4, index_n_heads=2, index_head_dim=8), "GlmMoeDsaForCausalLM"),
+], ids=["glm4", "minimax_m2", "qwen3_next", "qwen3_5", "deepseek_v3", "glm5_dsa"])  # fmt: skip
+def test_checkpoint_names_round_trip_for_each_family(kw, arch):
+    """Every trainer parameter maps to checkpoint names and back to the same tensor (names follow the public
+    checkpoints of each family; zero-centred norms and the per-head (query, gate) rows are translated)."""
+    from slime_b200.weight_sync import convert
+
+    torch.manual_seed(0)
+    cfg = _tiny(model_arch=arch, **kw)
+    model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=3)
+    hf = {}
+    for name, p in model.named_parameters():
+        for hf_name, t in convert.convert_to_hf(cfg, name, p.detach().clone()):
+            assert hf_name not in hf, hf_name
+            hf[hf_name] = t
+    # spot checks of the public naming
+    names = set(hf)
+    if arch == "Qwen3NextForCausalLM":
+        assert "model.layers.0.linear_attn.in_proj_qkvz.weight" in names and hf["model.layers.0.linear_attn.conv1d.weight"].dim() == 3
+        assert hf["model.layers.3.self_attn.q_proj.weight"].shape[0] == 2 * cfg.num_attention_heads * cfg.head_dim
+        ln = dict(model.named_parameters())["decoder.layers.0.self_attention.input_layernorm.weight"]
+        assert torch.allclose(hf["model.layers.0.input_layernorm.weight"], ln - 1)  # stored zero-centred
+        assert torch.allclose(hf["model.layers.0.linear_attn.norm.weight"], torch.ones(8))  # the gated norm is not
+    if arch == "Qwen3_5ForCausalLM":
+        assert {"model.layers.0.linear_attn.in_proj_qkv.weight", "model.layers.0.linear_attn.in_proj_z.weight",
+                "model.layers.0.linear_attn.in_proj_a.weight"} <= names  # fmt: skip
+    if arch == "DeepseekV3ForCausalLM":
+        assert {"model.layers.0.self_attn.q_a_proj.weight", "model.layers.0.self_attn.q_a_layernorm.weight",
+                "model.layers.0.self_attn.kv_a_proj_with_mqa.weight", "model.layers.1.mlp.shared_experts.down_proj.weight",
+                "model.layers.1.mlp.experts.3.up_proj.weight"} <= names  # fmt: skip
+    if arch == "GlmMoeDsaForCausalLM":
+        assert "model.layers.0.self_attn.indexer.wq_b.weight" in names and "model.layers.1.self_attn.indexer.k_norm.bias" in names
+    if arch == "MiniMaxM2ForCausalLM":
+        assert hf["model.layers.0.self_attn.q_norm.weight"].numel() == cfg.num_attention_heads * cfg.head_dim
+        assert "model.layers.0.self_attn.sinks" in names
+    for name, p in model.named_parameters():
+        sources, rule = convert.hf_sources_for(cfg, name)
+        back = convert.merge_hf_sources(rule, [hf[s] for s in sources], cfg)
+        assert back.shape == p.shape and torch.allclose(back, p.detach(), atol=1e-6), name
+
+
+def test_gated_qkv_shards_merge_and_split():
+    from slime_b200.weight_sync import convert
+
+    cfg = _tiny(attention_output_gate=True, rotary_percent=0.25, qk_layernorm=True)
+    rows = (2 * cfg.num_attention_heads + 2 * cfg.num_query_groups) * cfg.head_dim
+    full = torch.arange(rows * 3, dtype=torch.float32).view(rows, 3)
+    shards = [convert.shard_for_tp(cfg, "decoder.layers.0.self_attention.linear_qkv.weight", full, 0, 1, 2, r) for r in range(2)]
+    assert shards[0].shape[0] == rows // 2
+    assert torch.equal(convert.merge_tp_shards(cfg, "decoder.layers.0.self_attention.linear_qkv.weight", shards, 0, 1), full)
+
+
+def test_hugging_face_style_module_runs_as_a_layer():
+    """A custom builder swaps the mixer of chosen layers for a wrapped external module; the rest keep the built-in one."""
+    import torch.nn as nn
+
+    class Toy(nn.Module):  # "attention" that mixes nothing: enough to see the plumbing
+        def __init__(self, h):
+            super().__init__()
+            self.proj = nn.Linear(h, h, bias=False)
+
+        def forward(self, hidden_states, position_ids=None, cu_seqlens=None):
+            assert hidden_states.dim() == 3 and position_ids.shape[1] == hidden_states.shape[1] and cu_seqlens is not None
+            return (self.proj(hidden_states),)
+
+    cfg = _tiny()
+    mixers.set_custom_builder(lambda c, i, dt, dev, sp: mixers.HuggingfaceAttention(c, i, dt, dev, sp, Toy(c.hidden_size)) if i == 1 else None)
+    try:
+        model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=1)
+    finally:
+        mixers.set_custom_builder(None)
+    kinds = [type(layer.self_attention).__name__ for layer in model.decoder.layers]
+    assert kinds == ["SelfAttention", "HuggingfaceAttention"]
+    p, T = packed_for([7, 5])
+    ids = torch.randint(0, cfg.vocab_size, (T,))
+    model(ids, position_ids=p.position_ids, packed_seq_params=p)[0].sum().backward()
+    w = model.decoder.layers[1].self_attention.hf_module.proj.weight
+    assert w.grad is not None and float(w.grad.abs().sum()) > 0 and w.tensor_model_parallel is False
