@@ -69,6 +69,8 @@ class TrainModel:
                 m = GPTModel(self.cfg, dtype=dtype, device=self.device, sequence_parallel=getattr(args, "sequence_parallel", False),
                              pre_process=pre, post_process=post, layer_range=rng, value_head=(role == "critic"),
                              recompute_granularity=getattr(args, "recompute_granularity", None), seed=args.seed)  # fmt: skip
+            if getattr(args, "enable_mtp_training", False) and hasattr(m, "mtp_training"):
+                m.mtp_training = True
             self.chunks.append(m)
         self._freeze_params()
         self._build_buffers()
@@ -340,6 +342,11 @@ def train_one_step(args, rollout_id, step_id, data_iterator, model: TrainModel, 
         aux = [l.mlp.aux_loss for l in chunk.decoder.layers if getattr(l.mlp, "aux_loss", None) is not None]
         if aux:
             loss = loss + sum(aux) / max(num_microbatches, 1)
+        if getattr(args, "enable_mtp_training", False) and getattr(chunk, "mtp", None) is not None:
+            # the draft head learns the tokens actually sampled (cross entropy), scaled like Megatron's MTP loss
+            mtp = chunk.mtp_loss(batch["full_loss_masks"])
+            loss = loss + args.mtp_loss_scaling_factor * mtp / max(num_microbatches, 1)
+            log = dict(log, mtp_loss=mtp.detach()) if isinstance(log, dict) and "keys" not in log else log
         return loss, log
 
     logs = pipeline.run_forward_backward(model, data_iterator[0], num_microbatches, forward_step, args)

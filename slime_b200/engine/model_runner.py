@@ -127,6 +127,8 @@ class EngineWeights:
         m = _LAYER_RE.match(name)
         if m is None:
             return False
+        if int(m.group(1)) >= len(self.layers):
+            return True  # a draft (multi-token-prediction) depth stored as an extra layer: this engine does not run it
         L = self.layers[int(m.group(1))]
         sub = m.group(2)
         hq, hkv = self.hq, self.hkv

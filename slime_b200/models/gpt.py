@@ -192,6 +192,40 @@ class TransformerLayer(nn.Module):
         return m, residual
 
 
+class MTPLayer(nn.Module):
+    """One multi-token-prediction depth (DeepSeek-V3 style draft head): the trunk's hidden state of position i and the
+    embedding of token i+1 are normalised, concatenated, projected back to the model width and passed through one
+    transformer layer; the shared output head then predicts token i+2. Parameters: ``enorm``, ``hnorm``, ``eh_proj``
+    [H, 2H] (columns: embedding half, hidden half), ``transformer_layer.*``, ``final_layernorm``. Same role as the MTP
+    block the reference enables with ``--mtp-num-layers`` / ``--enable-mtp-training``
+    (slime/backends/megatron_utils/model_provider.py:200-232, docker/patch/latest/megatron.patch:556-640)."""
+
+    def __init__(self, cfg: ModelConfig, layer_number: int, dtype, device, sequence_parallel: bool):
+        super().__init__()
+        h = cfg.hidden_size
+        self.cfg, self.sp = cfg, sequence_parallel
+        for n in ("enorm", "hnorm", "final_layernorm"):
+            m = nn.Module()
+            m.weight = tp.set_tp_attrs(_param((h,), dtype, device, ones=True), False)
+            m.weight.sequence_parallel = sequence_parallel
+            setattr(self, n, m)
+        self.eh_proj = nn.Module()
+        gen = tp.get_rng_tracker().states.get("default")
+        self.eh_proj.weight = tp.set_tp_attrs(_param((h, 2 * h), dtype, device, cfg.init_method_std, generator=gen), False)
+        self.eh_proj.weight.sequence_parallel = sequence_parallel  # fed this rank's rows only
+        self.transformer_layer = TransformerLayer(cfg, layer_number, dtype, device, sequence_parallel)
+
+    def forward(self, hidden, next_embedding, rope_table, packed):
+        eps = self.cfg.norm_epsilon
+        e, _ = ops.rmsnorm(next_embedding, self.enorm.weight, eps)
+        hn, _ = ops.rmsnorm(hidden, self.hnorm.weight, eps)
+        x = ops.linear(torch.cat([e, hn], dim=-1), self.eh_proj.weight)
+        x, residual = self.transformer_layer(x, None, rope_table, packed)
+        pre = x if residual is None else x + residual
+        out, _ = ops.rmsnorm(pre, self.final_layernorm.weight, eps)
+        return out, pre
+
+
 class LinearForLastLayer(nn.Module):
     """Critic value head ``hidden -> 1`` (replicated across TP)."""
 
@@ -279,6 +313,14 @@ class GPTModel(nn.Module):
             else:
                 self.output_layer = None
         self.value_head = value_head
+        self.mtp = None
+        if cfg.mtp_num_layers and post_process and not value_head:
+            assert pre_process, "multi-token prediction shares the embedding table: it needs the first stage's weights (pp = 1)"
+            self.mtp = nn.Module()
+            self.mtp.layers = nn.ModuleList([MTPLayer(cfg, cfg.num_layers + k, dtype, device, self.sequence_parallel)
+                                             for k in range(cfg.mtp_num_layers)])  # fmt: skip
+        self.mtp_training = False  # set by the trainer (--enable-mtp-training): keep what the draft loss needs
+        self._mtp_inputs = None
         self._rope = None
         self.input_tensor = None  # set by the pipeline schedule on non-first stages
 
@@ -325,10 +367,47 @@ class GPTModel(nn.Module):
             if residual is None:
                 residual = torch.zeros_like(x)
             return torch.stack([x, residual])
-        h, _ = ops.rmsnorm(x, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual)
+        h, pre = ops.rmsnorm(x, self.decoder.final_layernorm.weight, cfg.norm_epsilon, residual)
+        if self.mtp is not None and self.mtp_training and torch.is_grad_enabled():
+            self._mtp_inputs = (pre if residual is not None else x, input_ids, packed, table)
         if self.sequence_parallel:
             h = tp.gather_from_sequence_parallel_region_no_reduce(h)
         return h
+
+    def mtp_loss(self, full_loss_mask: torch.Tensor) -> torch.Tensor:
+        """Draft-head loss of the micro-batch whose trunk forward just ran: mean over valid positions of the cross
+        entropy of depth k predicting token i + k + 2 from position i, averaged over depths. ``full_loss_mask`` [T] is 1
+        where position i predicts a trained token i + 1; a depth-k target is trained when it lies in the same sequence
+        and its own predicting position is trained. Depth k + 1 consumes depth k's hidden state."""
+        from slime_b200.utils.ppo_utils import calculate_log_probs_and_entropy
+
+        assert self._mtp_inputs is not None, "run the trunk forward with mtp_training set first"
+        hidden, ids, packed, table = self._mtp_inputs
+        self._mtp_inputs = None
+        ids = ids.reshape(-1)
+        T = ids.numel()
+        seq = torch.searchsorted(packed.cu_seqlens.long(), torch.arange(T, device=ids.device), right=True)
+        mask = full_loss_mask.reshape(-1).float()
+        w = self.output_weight()
+        total = hidden.new_zeros((), dtype=torch.float32)
+        for k, layer in enumerate(self.mtp.layers):
+            shift = k + 1
+            nxt = torch.cat([ids[shift:], ids.new_zeros(shift)])  # token i + k + 1, the draft head's extra input
+            emb = ops.embedding(nxt, self.embedding.word_embeddings.weight, self.vocab_start)
+            if mpu.get_tensor_model_parallel_world_size() > 1:
+                emb = tp.reduce_from_tensor_model_parallel_region(emb)
+            if self.sequence_parallel:
+                emb = tp.scatter_to_sequence_parallel_region(emb)
+            out, hidden = layer(hidden, emb, table, packed)
+            if self.sequence_parallel:
+                out = tp.gather_from_sequence_parallel_region_no_reduce(out)
+            logits = _lm_head(tp.copy_to_tensor_model_parallel_region(out), w)
+            tgt = torch.cat([ids[shift + 1 :], ids.new_zeros(shift + 1)])  # token i + k + 2
+            same = torch.cat([seq[shift + 1 :] == seq[: T - shift - 1], seq.new_zeros(shift + 1, dtype=torch.bool)])
+            valid = torch.cat([mask[shift:], mask.new_zeros(shift)]) * same.float()
+            lp, _ = calculate_log_probs_and_entropy(logits, tgt, mpu.get_tensor_model_parallel_group(), with_entropy=False)
+            total = total - (lp.reshape(-1) * valid).sum() / valid.sum().clamp_min(1.0)
+        return total / len(self.mtp.layers)
 
     def forward(self, input_ids, position_ids=None, attention_mask=None, labels=None, packed_seq_params=None,
                 loss_mask=None, return_hidden=False, **kw):  # fmt: skip

@@ -136,6 +136,18 @@ def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[st
         return [("lm_head.weight", t[: cfg.vocab_size])]
     if name == "decoder.final_layernorm.weight":
         return [("model.norm.weight", t - 1 if _zero_centred(cfg) else t)]
+    mm = _MTP.match(name)
+    if mm is not None:
+        # DeepSeek-V3 layout: draft depth k is checkpoint layer num_layers + k, with its own norms and projection
+        k, sub = int(mm.group(1)), mm.group(2)
+        i = str(cfg.num_layers + k)
+        p = f"model.layers.{i}"
+        own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
+               "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip
+        if sub in own:
+            return [(f"{p}.{own[sub]}", t)]
+        assert sub.startswith("transformer_layer."), name
+        return _layer_to_hf(cfg, i, sub[len("transformer_layer.") :], t)
     m = _LAYER.match(name)
     if m is None:
         raise ValueError(f"unknown trainer parameter name: {name}")
@@ -255,6 +267,15 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
         return ["model.embed_tokens.weight" if cfg.tie_word_embeddings else "lm_head.weight"], "copy"
     if name == "decoder.final_layernorm.weight":
         return ["model.norm.weight"], "copy+1" if _zero_centred(cfg) else "copy"
+    mm = _MTP.match(name)
+    if mm is not None:
+        k, sub = int(mm.group(1)), mm.group(2)
+        p = f"model.layers.{cfg.num_layers + k}"
+        own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
+               "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip
+        if sub in own:
+            return [f"{p}.{own[sub]}"], "copy"
+        return hf_sources_for(cfg, f"decoder.layers.{cfg.num_layers + k}.{sub[len('transformer_layer.'):]}")
     m = _LAYER.match(name)
     if m is None:
         raise ValueError(f"unknown trainer parameter name: {name}")

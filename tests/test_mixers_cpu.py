@@ -279,3 +279,81 @@ def test_hugging_face_style_module_runs_as_a_layer():
     model(ids, position_ids=p.position_ids, packed_seq_params=p)[0].sum().backward()
     w = model.decoder.layers[1].self_attention.hf_module.proj.weight
     assert w.grad is not None and float(w.grad.abs().sum()) > 0 and w.tensor_model_parallel is False
+
+
+def test_mtp_loss_shifts_inputs_targets_and_masks_per_sequence():
+    """Depth-1 draft head: position i sees the trunk's hidden state of i and the embedding of token i + 1 and is
+    scored on token i + 2; nothing crosses a sequence boundary; the loss trains the head and the trunk."""
+    from slime_b200 import ops
+    from slime_b200.weight_sync import convert
+
+    torch.manual_seed(0)
+    cfg = _tiny(mtp_num_layers=1)
+    model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=1)
+    model.mtp_training = True
+    lens = [7, 5]
+    ids = torch.randint(0, cfg.vocab_size, (sum(lens),))
+    full_mask = torch.tensor([0, 0, 1, 1, 1, 1, 0] + [0, 1, 1, 1, 0], dtype=torch.float32)
+
+    def run(tokens, ls, mask):
+        p, _ = packed_for(ls)
+        model(tokens, position_ids=p.position_ids, packed_seq_params=p)
+        return model.mtp_loss(mask)
+
+    both = run(ids, lens, full_mask)
+    # per sequence: sums of per-token terms add up (the packed loss is a mean over all valid positions)
+    def terms(tokens, n, mask):
+        p, _ = packed_for([n])
+        model(tokens, position_ids=p.position_ids, packed_seq_params=p)
+        hidden, _, packed, table = model._mtp_inputs
+        model._mtp_inputs = None
+        nxt = torch.cat([tokens[1:], tokens.new_zeros(1)])
+        emb = ops.embedding(nxt, model.embedding.word_embeddings.weight, 0)
+        out, _ = model.mtp.layers[0](hidden, emb, table, packed)
+        logp = (out.float() @ model.output_weight().float().t()).log_softmax(-1)
+        tot, cnt = 0.0, 0
+        for i in range(n - 2):
+            if mask[i + 1] > 0:
+                tot, cnt = tot - logp[i, tokens[i + 2]], cnt + 1
+        return tot, cnt
+
+    t1, c1 = terms(ids[:7], 7, full_mask[:7])
+    t2, c2 = terms(ids[7:], 5, full_mask[7:])
+    assert c1 == 4 and c2 == 3  # targets whose own predicting position is trained, inside the sequence
+    assert torch.allclose(both, (t1 + t2) / (c1 + c2), atol=1e-5)
+    run(ids, lens, full_mask).backward()
+    named = dict(model.named_parameters())
+    assert float(named["mtp.layers.0.eh_proj.weight"].grad.abs().sum()) > 0
+    assert float(named["decoder.layers.0.mlp.linear_fc1.weight"].grad.abs().sum()) > 0
+    # checkpoint names: the draft depth is stored as one more layer with its own norms and projection
+    hf = dict(x for n, p in model.named_parameters() if n.startswith("mtp.") for x in convert.convert_to_hf(cfg, n, p.detach()))
+    assert {"model.layers.2.enorm.weight", "model.layers.2.eh_proj.weight", "model.layers.2.shared_head.norm.weight",
+            "model.layers.2.self_attn.q_proj.weight", "model.layers.2.mlp.down_proj.weight"} <= set(hf)
+    for n, p in model.named_parameters():
+        if n.startswith("mtp."):
+            src, rule = convert.hf_sources_for(cfg, n)
+            assert torch.equal(convert.merge_hf_sources(rule, [hf[s] for s in src], cfg), p.detach()), n
+
+
+def test_grpo_step_trains_the_draft_head_end_to_end():
+    """Colocated GRPO on CPU with --enable-mtp-training: the draft layer's matrices move with the step, and the rollout
+    engine (which does not run the draft depth) accepts the synced weights."""
+    from slime_b200.api import ColocatedGRPO
+    from slime_b200.models.config import apply_to_args
+    from slime_b200.utils.arguments import namespace_from_dict
+
+    cfg = _tiny(mtp_num_layers=1)
+    args = namespace_from_dict(dict(
+        rollout_batch_size=2, n_samples_per_prompt=4, num_rollout=1, global_batch_size=8, colocate=True, use_dynamic_batch_size=True,
+        max_tokens_per_gpu=256, lr=1e-3, eps_clip=0.2, eps_clip_high=0.28, rollout_ignore_eos=True, rollout_max_context_len=64,
+        custom_rm_path="slime_b200.rollout.synthetic.mod7_reward", actor_num_nodes=1, actor_num_gpus_per_node=1, rollout_num_gpus=1,
+        sglang_max_running_requests=8, sglang_disable_cuda_graph=True, untie_embeddings_and_output_weights=True,
+        data_pad_size_multiplier=8, enable_mtp_training=True, mtp_num_layers=1))  # fmt: skip
+    apply_to_args(cfg, args)
+    r = ColocatedGRPO(args, device="cpu", engine_pages=64)
+    before = {n: p.detach().clone() for n, p in r.actor.model.named_parameters() if n.startswith("mtp.") and p.dim() == 2}
+    assert "mtp.layers.0.eh_proj.weight" in before
+    out = r.step(torch.randint(0, cfg.vocab_size, (2, 8), generator=torch.Generator().manual_seed(0)).tolist(), 12)
+    assert math.isfinite(float(out["metrics"]["train/loss"]))
+    after = dict(r.actor.model.named_parameters())
+    assert all(not torch.equal(after[n].detach(), w) for n, w in before.items())
