@@ -266,9 +266,55 @@ class Engine:
                 self._record_kept(req, kept_ids, kept_cnt, i)
                 if self._append_token(req, toks[i], lps[i]):
                     finished.append(req)
+                elif req.prefill_only:
+                    req.kv_export = self.export_kv(req)
+                    self._finish(req, {"type": "prefill_done"})
+                    finished.append(req)
                 else:
                     self._start_decoding(req)
         return finished
+
+    # ------------------------------------------------------ prefill / decode disaggregation
+    def export_kv(self, req: Request):
+        """``(k, v)``, each ``[layers, tokens, kv heads, head dim]``: the cached keys and values of the request's computed
+        tokens, copied out of the paged cache (the pages can be released afterwards)."""
+        slots = torch.tensor(self._slots(req, 0, req.num_computed), dtype=torch.long, device=self.device)
+        k = torch.stack([kl.index_select(0, slots) for kl in self.kv.k])
+        v = torch.stack([vl.index_select(0, slots) for vl in self.kv.v])
+        return k, v
+
+    def import_request(self, input_ids, first_token: int, first_logprob: float, kv, sampling: SamplingParams | dict | None = None,
+                       rid: str | None = None, **kw) -> Request:  # fmt: skip
+        """Decode side of a disaggregated pair: adopt a prompt whose prefill ran on another engine. ``kv`` is what
+        ``export_kv`` returned there (any device); it is written into freshly allocated pages and the request starts
+        decoding from ``first_token`` without a prefill pass here. Same role as the prefill -> decode KV hand-over of
+        the reference's PD-disaggregated rollout servers (slime/ray/rollout.py:46-219, worker types prefill / decode)."""
+        sp = sampling if isinstance(sampling, SamplingParams) else SamplingParams.from_dict(sampling)
+        req = Request(rid=rid or uuid.uuid4().hex, input_ids=list(input_ids), sampling=sp, **kw)
+        self._req_counter = getattr(self, "_req_counter", 0) + 1
+        req.seed = sp.sampling_seed if sp.sampling_seed is not None else (self.args.random_seed * 1000003 + self._req_counter) & 0x7FFFFFFFFFFF
+        n = len(req.input_ids)
+        k, v = kv
+        if k.shape[1] != n or k.shape[0] != len(self.kv.k) or tuple(k.shape[2:]) != tuple(self.kv.k[0].shape[1:]):
+            raise ValueError(f"KV of shape {tuple(k.shape)} does not fit {n} tokens of this engine's cache "
+                             f"[{len(self.kv.k)}, *, {tuple(self.kv.k[0].shape[1:])}]")  # fmt: skip
+        sp.max_new_tokens = max(0, min(sp.max_new_tokens, self.max_context - n))
+        req.weight_version = self.weights.version
+        with self.lock:
+            req.pages = self.kv.allocator.alloc(-(-(n + 1) // self.page_size))
+            slots = torch.tensor(self._slots(req, 0, n), dtype=torch.long, device=self.device)
+            for li in range(len(self.kv.k)):
+                self.kv.k[li].index_copy_(0, slots, k[li].to(self.device, self.kv.k[li].dtype))
+                self.kv.v[li].index_copy_(0, slots, v[li].to(self.device, self.kv.v[li].dtype))
+            req.num_computed = n
+            req.ctx_ids = list(req.input_ids)
+            req.state = ReqState.RUNNING
+            req.first_scheduled = req.first_token_time = time.time()
+            self._commit_pages(req, req.ctx_ids)
+            self.stats["imported_tokens"] = self.stats.get("imported_tokens", 0) + n
+            if not self._append_token(req, int(first_token), float(first_logprob)):
+                self._start_decoding(req)
+        return req
 
     def _record_input_logprobs(self, batch, logits, cu_q):
         lsm = torch.log_softmax(logits.float(), -1)

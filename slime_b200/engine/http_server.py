@@ -44,6 +44,9 @@ class EngineServer:
         self._weights_snapshot = None
         self._update_groups: dict[str, object] = {}
         self.num_generated = 0
+        # prefill / decode disaggregation: KV of finished prefill-only requests, waiting for their decode worker
+        self.kv_store: dict[str, tuple] = {}
+        self.kv_store_ttl = 600.0
 
     # ------------------------------------------------------------------ scheduler thread
     def _scheduler_loop(self):
@@ -77,6 +80,10 @@ class EngineServer:
         sps = sp if isinstance(sp, list) else [sp] * len(prompts)
         loop = asyncio.get_running_loop()
         stream = bool(body.get("stream"))
+        prefill_only = body.get("disaggregation") == "prefill"
+        room = body.get("bootstrap_room")
+        if room is not None and not batched:
+            return await self._generate_imported(body, ids, sps[0], room)
         reqs, events, queues = [], [], []
         for p, s in zip(prompts, sps):
             ev = asyncio.Event()
@@ -97,7 +104,7 @@ class EngineServer:
                 p, SamplingParams.from_dict(s), rid=body.get("rid"), return_logprob=bool(body.get("return_logprob", False)),
                 logprob_start_len=int(body.get("logprob_start_len", -1) if body.get("return_logprob") else -1),
                 return_routed_experts=bool(body.get("return_routed_experts", False)), stream=stream,
-                on_token=on_token if stream else None, done_event=_Done(ev),
+                on_token=on_token if stream else None, done_event=_Done(ev), prefill_only=prefill_only,
             )  # fmt: skip
             if req.finished():
                 ev.set()
@@ -121,7 +128,70 @@ class EngineServer:
         await asyncio.gather(*[e.wait() for e in events])
         self.num_generated += sum(len(r.output_ids) for r in reqs)
         out = [self._render(r) for r in reqs]
+        if prefill_only:
+            now = time.time()
+            for rid in [k for k, (_, t0) in self.kv_store.items() if now - t0 > self.kv_store_ttl]:
+                del self.kv_store[rid]  # a decode worker that never came
+            for r, o in zip(reqs, out):
+                if r.kv_export is not None:
+                    self.kv_store[r.rid] = (r.kv_export, now)
+                    r.kv_export = None
+                    o["meta_info"]["kv_handle"] = r.rid
         return web.json_response(out if batched else out[0])
+
+    async def _kv_fetch(self, request):
+        """Decode worker's pull of a prefilled prompt's KV: 4-byte little-endian header length, a JSON header (shape,
+        dtype), then the raw bytes of k and of v. The entry is dropped once served."""
+        from aiohttp import web
+
+        entry = self.kv_store.pop(request.match_info["rid"], None)
+        if entry is None:
+            return web.json_response({"error": "unknown or expired KV handle"}, status=404)
+        (k, v), _ = entry
+        k, v = k.contiguous().cpu(), v.contiguous().cpu()
+        header = json.dumps({"shape": list(k.shape), "dtype": str(k.dtype).replace("torch.", "")}).encode()
+        raw = lambda t: t.view(torch.uint8).numpy().tobytes()  # noqa: E731
+        return web.Response(body=len(header).to_bytes(4, "little") + header + raw(k) + raw(v), content_type="application/octet-stream")
+
+    async def _generate_imported(self, body, ids, sampling, room):
+        """Decode side: pull the KV from the prefill worker named in the request and continue from its first token."""
+        import aiohttp
+        from aiohttp import web
+
+        host = body["bootstrap_host"]
+        async with aiohttp.ClientSession() as s, s.get(f"{host}/disagg/kv/{room}") as resp:
+            if resp.status != 200:
+                return web.json_response({"error": f"KV {room} not available at {host}"}, status=502)
+            blob = await resp.read()
+        n = int.from_bytes(blob[:4], "little")
+        header = json.loads(blob[4 : 4 + n])
+        dt = getattr(torch, header["dtype"])
+        count = 1
+        for d in header["shape"]:
+            count *= d
+        nbytes = count * torch.empty(0, dtype=dt).element_size()
+        body_bytes = memoryview(blob)[4 + n :]
+        k = torch.frombuffer(bytearray(body_bytes[:nbytes]), dtype=dt).view(header["shape"])
+        v = torch.frombuffer(bytearray(body_bytes[nbytes : 2 * nbytes]), dtype=dt).view(header["shape"])
+        loop = asyncio.get_running_loop()
+        ev = asyncio.Event()
+
+        class _Done:
+            def set(self_inner):
+                loop.call_soon_threadsafe(ev.set)
+
+        try:
+            req = self.engine.import_request(ids, int(body["first_token"]), float(body.get("first_logprob", 0.0)), (k, v),
+                                             SamplingParams.from_dict(sampling), rid=body.get("rid"),
+                                             return_logprob=bool(body.get("return_logprob", False)), done_event=_Done())  # fmt: skip
+        except Exception as e:  # noqa: BLE001 - out of pages, shape mismatch
+            return web.json_response({"error": repr(e)}, status=503)
+        if req.finished():
+            ev.set()
+        self._wake.set()
+        await ev.wait()
+        self.num_generated += len(req.output_ids)
+        return web.json_response(self._render(req))
 
     # ---------------------------------------------------------------- OpenAI-compatible front end
     async def _run_one(self, ids: list[int], sampling: dict, rid=None):
@@ -431,6 +501,7 @@ class EngineServer:
         app = web.Application(client_max_size=1 << 34)
         r = app.router
         r.add_post("/generate", self._generate)
+        r.add_get("/disagg/kv/{rid}", self._kv_fetch)
         r.add_post("/v1/chat/completions", self._chat_completions)
         r.add_post("/v1/completions", self._completions)
         r.add_get("/v1/models", self._models)

@@ -60,6 +60,8 @@ class Request:
     logprob_start_len: int = -1  # >=0: also return input-token log-probs from this position
     return_routed_experts: bool = False
     stream: bool = False
+    prefill_only: bool = False  # prefill / decode disaggregation: stop after the first token and export the prompt's KV
+    kv_export: Any = None  # (k, v) [layers, tokens, kv heads, head dim] of a finished prefill-only request
     # ---- engine state ----
     state: ReqState = ReqState.WAITING
     output_ids: list[int] = field(default_factory=list)

@@ -172,11 +172,20 @@ class Router:
         key = request.headers.get("X-SMG-Routing-Key")
         has_pd = any(w.worker_type == "prefill" for w in self.workers.values())
         try:
-            if has_pd:
-                pre = self.pick(ids if isinstance(ids, list) and ids and isinstance(ids[0], int) else None, key, "prefill")
-                body = dict(body, bootstrap_host=pre.url, bootstrap_port=pre.bootstrap_port)
-                await self._forward(pre, "/generate", dict(body, sampling_params=dict(body.get("sampling_params") or {}, max_new_tokens=0)))
+            if has_pd and isinstance(ids, list) and ids and isinstance(ids[0], int):
+                # prefill on one worker (it keeps the prompt's KV and samples the first token), decode on another,
+                # which pulls the KV from the first and continues without a prefill pass of its own
+                pre = self.pick(ids, key, "prefill")
+                status, first = await self._forward(pre, "/generate", dict(body, disaggregation="prefill", stream=False, return_logprob=True))
+                meta = first.get("meta_info", {}) if isinstance(first, dict) else {}
+                if status != 200 or (meta.get("finish_reason") or {}).get("type") != "prefill_done":
+                    return web.json_response(first, status=status)  # failed, or already finished with its first token
+                lp = (meta.get("output_token_logprobs") or [[0.0]])[0][0]
+                body = dict(body, bootstrap_host=pre.url, bootstrap_room=meta["kv_handle"], first_token=first["output_ids"][0],
+                            first_logprob=lp)  # fmt: skip
                 w = self.pick(None, key, "decode")
+            elif has_pd:
+                w = self.pick(None, key, "decode")  # batched prompts: the decode worker runs both phases
             else:
                 w = self.pick(ids if isinstance(ids, list) and ids and isinstance(ids[0], int) else None, key)
         except RuntimeError as e:

@@ -252,3 +252,64 @@ def test_device_layout_skips_routes_of_other_ranks():
         assert int((lay.slot_dest >= 0).sum()) == int(((idx >= r * 2) & (idx < r * 2 + 2)).sum())
         parts.append(lay.combine(grouped.grouped_gemm(lay.pad(x), w[r * 2 : r * 2 + 2], lay), probs, T))
     assert torch.allclose(sum(parts), ref, atol=1e-5)
+
+
+def test_prefill_decode_disaggregation_hands_the_kv_over():
+    """A prefill-only engine exports the prompt's KV and the first token; a second engine adopts both and decodes the
+    same continuation, with the same log-probs, as one engine doing everything."""
+    whole, pre, dec = make_engine(), make_engine(), make_engine()
+    prompts = [[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11], [5, 4, 3]]
+    sp = dict(max_new_tokens=9, ignore_eos=True, sampling_seed=5)
+    ref = whole.generate(prompts, [dict(sp)] * 2)
+    staged = pre.generate(prompts, [dict(sp)] * 2, prefill_only=True)
+    assert [r.finish_reason["type"] for r in staged] == ["prefill_done"] * 2 and all(len(r.output_ids) == 1 for r in staged)
+    assert staged[0].kv_export[0].shape == (pre.cfg.num_layers, 11, pre.weights.hkv, pre.cfg.head_dim)
+    assert not pre.has_work() and pre.kv.allocator.available() == whole.kv.allocator.available()  # pages went back
+    adopted = [dec.import_request(r.input_ids, r.output_ids[0], r.output_logprobs[0], r.kv_export, dict(sp)) for r in staged]
+    while dec.has_work():
+        dec.step()
+    for a, b in zip(adopted, ref):
+        assert a.output_ids == b.output_ids and a.finish_reason == b.finish_reason
+        assert np.abs(np.array(a.output_logprobs) - np.array(b.output_logprobs)).max() < 1e-5
+    assert dec.stats["prefill_tokens"] == 0 and dec.stats["imported_tokens"] == 14
+    with pytest.raises(ValueError, match="does not fit"):
+        dec.import_request([1, 2], 3, 0.0, staged[0].kv_export, dict(sp))
+
+
+def test_router_runs_prefill_and_decode_on_different_servers():
+    """Router + one prefill server + one decode server over HTTP: the decode server pulls the prompt's KV from the
+    prefill server and returns what a single server returns; its own prefill counter stays at zero."""
+    import requests
+
+    from slime_b200.engine.http_server import EngineServer
+    from slime_b200.engine.router import Router
+    from slime_b200.utils.misc import get_free_port
+
+    engines = [make_engine() for _ in range(3)]
+    servers = [EngineServer(e, "127.0.0.1", get_free_port(start_port=31200 + 17 * i)).start(block=False) for i, e in enumerate(engines)]
+    router = Router("127.0.0.1", get_free_port(start_port=31300), policy="round_robin").start(block=False)
+    try:
+        urls = [f"http://127.0.0.1:{s.port}" for s in servers]
+        router.add_worker(urls[0], "prefill")
+        router.add_worker(urls[1], "decode")
+        body = {"input_ids": [1, 2, 3, 4, 5, 6, 7, 8, 9], "return_logprob": True,
+                "sampling_params": {"max_new_tokens": 7, "ignore_eos": True, "sampling_seed": 3}}  # fmt: skip
+        via = requests.post(f"http://127.0.0.1:{router.port}/generate", json=body, timeout=120)
+        assert via.status_code == 200, via.text
+        via = via.json()
+        ref = requests.post(urls[2] + "/generate", json=body, timeout=120).json()
+        assert via["output_ids"] == ref["output_ids"] and via["meta_info"]["finish_reason"] == ref["meta_info"]["finish_reason"]
+        a = [x[0] for x in via["meta_info"]["output_token_logprobs"]]
+        b = [x[0] for x in ref["meta_info"]["output_token_logprobs"]]
+        assert np.abs(np.array(a) - np.array(b)).max() < 1e-5
+        assert engines[1].stats["prefill_tokens"] == 0 and engines[1].stats["imported_tokens"] == 9
+        assert engines[0].stats["prefill_tokens"] == 9 and engines[0].stats["decode_tokens"] == 0
+        assert not servers[0].kv_store  # served once, then dropped
+        # a request that ends with its first token never reaches the decode server
+        one = requests.post(f"http://127.0.0.1:{router.port}/generate", timeout=120,
+                            json=dict(body, sampling_params=dict(body["sampling_params"], max_new_tokens=1))).json()
+        assert one["output_ids"] == ref["output_ids"][:1] and engines[1].stats["imported_tokens"] == 9
+    finally:
+        router.shutdown()
+        for s in servers:
+            s.shutdown()
