@@ -151,3 +151,112 @@ def test_retool_example_runs_the_interpreter_between_turns(engine):
     assert ex.extract_code("<tool_call>{broken</tool_call>") is None
     ok, text = asyncio.run(ex.run_python("import time\nprint(1/0)"))
     assert not ok and "ZeroDivisionError" in text
+
+
+def test_coding_agent_example_fixes_a_bug_and_is_graded_in_a_clean_sandbox(monkeypatch):
+    """Whole session on this host: the in-sandbox agent calls the adapter twice (a file rewrite, then a plain reply), the
+    patch is extracted with git, applied to a fresh workspace with a hidden test, and the rows carry reward 1."""
+    import json
+
+    from examples.coding_agent_rl import generate as ex
+    from examples.coding_agent_rl import tasks
+    from slime_b200.agent import adapters
+    from slime_b200.agent.trajectory import TurnRecord
+    from slime_b200.utils import processing_utils
+    from slime_b200.utils.misc import SingletonMeta
+
+    class Tok:
+        def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=True, tools=None):
+            text = "".join(f"[{m['role']}]{m.get('content') or ''}" + "".join(json.dumps(c["function"]) for c in m.get("tool_calls", []))
+                           for m in messages)  # fmt: skip
+            return [ord(c) for c in text + ("[assistant]" if add_generation_prompt else "")]
+
+        def decode(self, ids, skip_special_tokens=False):
+            return "".join(chr(i) for i in ids)
+
+    fixed = "def add(a, b):\\n    return a + b\\n"
+    outputs = ['I will fix it.<tool_call>{"name": "write_file", "arguments": {"path": "calc.py", "content": "' + fixed + '"}}</tool_call>',
+               "The subtraction was a typo; fixed."]  # fmt: skip
+
+    async def fake(prompt_ids, session, body, *, adapter, session_id=None):
+        text = outputs.pop(0)
+        return TurnRecord(prompt_ids=list(prompt_ids), output_ids=[ord(c) for c in text], finish_reason="stop",
+                          output_log_probs=[-0.25] * len(text))  # fmt: skip
+
+    monkeypatch.setattr(adapters, "call_engine_generate", fake)
+    monkeypatch.setattr(processing_utils, "load_tokenizer", lambda *a, **k: Tok())
+    monkeypatch.setenv("CODING_AGENT", "mini")
+    monkeypatch.setenv("CODING_SANDBOX", "local")
+    SingletonMeta._instances.pop(ex.AdapterService, None)
+    args = Namespace(hf_checkpoint="tok", sglang_router_ip="127.0.0.1", sglang_router_port=1, rollout_max_context_len=4096)
+    task = {"instance_id": "calc-1", "problem": "add() in calc.py returns the wrong result. Fix it.",
+            "files": {"calc.py": "def add(a, b):\n    return a - b\n", "README.md": "calc\n"},
+            "test_files": {"test_calc.py": "from calc import add\nassert add(2, 3) == 5\n"}, "test_cmd": "python test_calc.py"}  # fmt: skip
+    try:
+        s = Sample(index=0, prompt="fix the bug", label=json.dumps(task))
+        rows = asyncio.run(ex.generate(args, s, {"max_new_tokens": 256, "temperature": 1.0}))
+        assert not outputs and len(rows) >= 1, [r.metadata for r in rows]
+        assert all(r.reward == 1.0 for r in rows) and rows[-1].metadata["verdict"] == "solved"
+        assert rows[-1].metadata["agent_exit_code"] == 0 and rows[-1].metadata["patch_chars"] > 0
+        assert sum(rows[-1].loss_mask) > 0 and len(rows[-1].loss_mask) == rows[-1].response_length
+        # an agent that changes nothing scores 0 without running the tests
+        outputs.append("Looks fine to me.")
+        rows = asyncio.run(ex.generate(args, Sample(index=1, prompt="fix", label=json.dumps(task)), {"max_new_tokens": 64}))
+        assert rows[-1].reward == 0.0 and rows[-1].metadata["verdict"] == "empty_patch"
+        # rows without a usable task abort instead of raising
+        bad = asyncio.run(ex.generate(args, Sample(index=2, prompt="x", label="{}"), {}))
+        assert bad[0].status == Sample.Status.ABORTED and "bad_task" in bad[0].metadata["abort_reason"]
+    finally:
+        service = SingletonMeta._instances.pop(ex.AdapterService, None)
+        if service is not None:
+            service.handle.stop()
+
+    async def wrong_patch():
+        t = tasks.Task("t", "p", "python test_calc.py", files=task["files"], test_files=task["test_files"])
+        return await tasks.grade(t, "diff --git a/nope.py b/nope.py\n--- a/nope.py\n+++ b/nope.py\n@@ -1 +1 @@\n-x\n+y\n", ex.sandbox_factory())
+
+    assert asyncio.run(wrong_patch())[1]["verdict"] == "patch_does_not_apply"
+
+
+def test_tau_style_tool_agent_masks_environment_turns_and_takes_the_env_reward(engine):
+    from examples.tau_bench import generate_with_tau as ex
+    from examples.tau_bench.envs import MockRetailEnv
+
+    args, state, tok = engine
+
+    def template(messages, tokenize=True, add_generation_prompt=True, tools=None):
+        parts = []
+        for m in messages:
+            body = m.get("content") or ""
+            for c in m.get("tool_calls", []):
+                body += " <tool_call> " + '{"name": "' + c["function"]["name"] + '", "arguments": ' + c["function"]["arguments"].replace(" ", "") + "} </tool_call>"
+            parts.append(f"<|{m['role']}|> {body}")
+        return tok.encode(" ".join(parts) + (" <|assistant|>" if add_generation_prompt else ""))
+
+    tok.apply_chat_template = template
+
+    def script(prompt):
+        if "Order cancelled" in prompt:
+            return "It is cancelled . Anything else ?" if "That is all" not in prompt.split("Order cancelled")[-1] else "Goodbye !"
+        if "go ahead" in prompt:
+            return '<tool_call> {"name": "cancel_order", "arguments": {"order_id":"W100"}} </tool_call>'
+        if '"status":' in prompt or "pending" in prompt.split("<|tool|>")[-1]:
+            return "Do you confirm the cancellation ?"
+        return '<tool_call> {"name": "get_order", "arguments": {"order_id":"W100"}} </tool_call>'
+
+    state["script"] = script
+    s = Sample(index=0, prompt="", label='{"env": "mock_retail", "task_index": 0}')
+    out = asyncio.run(ex.generate(args, s, {"max_new_tokens": 400, "temperature": 1.0}))
+    assert out.status == Sample.Status.COMPLETED and out.reward == 1.0, (out.metadata, out.response)
+    assert out.metadata["tool_calls"] == 2 and out.metadata["env_done"]
+    assert len(out.loss_mask) == out.response_length == len(out.rollout_log_probs)
+    assert 0 < sum(out.loss_mask) < out.response_length  # the model's turns are trained on, the environment's are not
+    trained = tok.decode([t for t, m in zip(out.tokens[-out.response_length:], out.loss_mask) if m])
+    assert "cancel_order" in trained and "Order cancelled" not in trained and "go ahead" not in trained
+    # the environment itself: a delivered order cannot be cancelled, and touching the wrong order loses the reward
+    env = MockRetailEnv(0)
+    env.reset()
+    assert env.step({"name": "cancel_order", "arguments": {"order_id": "W300"}})[0].startswith("Error")
+    env.step({"name": "cancel_order", "arguments": {"order_id": "W200"}})
+    env.step({"name": "respond", "arguments": {"content": "done"}})
+    assert env.step({"name": "respond", "arguments": {"content": "bye"}}) == ("###STOP###", 0.0, True)
