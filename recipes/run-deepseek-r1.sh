@@ -1,0 +1,11 @@
+#!/bin/bash
+# DeepSeek-R1 (671B) on 16 nodes x 8 GPUs: TP8 + SP, PP4 (last stage 13 layers), CP4, EP32, CPU Adam, dynamic sampling;
+# 64-GPU rollout engines started from the block-fp8 checkpoint.
+source "$(dirname -- "${BASH_SOURCE[0]}")/common.sh"
+MODEL_ARGS=($(model_args deepseek-v3))
+launch train.py "${MODEL_ARGS[@]}" $(ckpt_args DeepSeek-R1) "${DAPO_ROLLOUT_ARGS[@]}" \
+  --rollout-batch-size 128 --n-samples-per-prompt 8 --rollout-max-response-len 32768 --num-steps-per-rollout 4 "${DYNAMIC_SAMPLING_ARGS[@]}" \
+  "${AIME_EVAL_ARGS[@]}" --n-samples-per-eval-prompt 8 --eval-max-response-len 32768 \
+  --tensor-model-parallel-size 8 --sequence-parallel --pipeline-model-parallel-size 4 --decoder-last-pipeline-num-layers 13 --context-parallel-size 4 --expert-model-parallel-size 32 --expert-tensor-parallel-size 1 --use-dynamic-batch-size --max-tokens-per-gpu 16384 \
+  "${RECOMPUTE_ARGS[@]}" "${GRPO_ARGS[@]}" "${CPU_ADAM_ARGS[@]}" "${MISC_ARGS[@]}" \
+  --actor-num-nodes "${NUM_NODES:-16}" --actor-num-gpus-per-node 8 --colocate --rollout-num-gpus-per-engine 64 --sglang-mem-fraction-static 0.7 --sglang-ep-size 64 --sglang-quantization fp8 --sglang-server-concurrency 1024

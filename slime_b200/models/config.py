@@ -286,8 +286,8 @@ PRESETS: dict[str, dict] = {
                          model_arch="LlamaForCausalLM"),
     "glm4-9b": dict(num_layers=40, hidden_size=4096, num_attention_heads=32, num_query_groups=2, kv_channels=128,
                     ffn_hidden_size=13696, vocab_size=151552, rotary_base=1e4, tie_word_embeddings=False,
-                    add_qkv_bias=True, post_self_attn_layernorm=True, post_mlp_layernorm=True,
-                    model_arch="Glm4ForCausalLM"),
+                    add_qkv_bias=True, post_self_attn_layernorm=True, post_mlp_layernorm=True, norm_epsilon=1e-5,
+                    rotary_percent=0.5, rotary_interleaved=True, model_arch="Glm4ForCausalLM"),
     "tiny": dict(num_layers=2, hidden_size=128, num_attention_heads=4, num_query_groups=2, kv_channels=64,
                  ffn_hidden_size=256, vocab_size=512, rotary_base=1e4, tie_word_embeddings=True, add_qkv_bias=True,
                  model_arch="Qwen2ForCausalLM"),

@@ -459,7 +459,8 @@ def backend_validate_args(args) -> None:
     if args.vocab_size is not None and args.padded_vocab_size is None:
         mult = args.make_vocab_size_divisible_by * args.tensor_model_parallel_size
         args.padded_vocab_size = -(-args.vocab_size // mult) * mult
-    if args.allgather_cp and not str(getattr(args, "model_arch", "")).lower().startswith(("deepseekv32", "glmmoedsa")):
+    if args.allgather_cp and not (getattr(args, "index_topk", None)
+                                  or str(getattr(args, "model_arch", "")).lower().startswith(("deepseekv32", "glmmoedsa"))):
         raise ValueError("--allgather-cp is only supported for DSA (DeepSeek-V3.2 / GLM-5) models")
     if args.virtual_pipeline_model_parallel_size is None and args.num_layers_per_virtual_pipeline_stage:
         per_stage = args.num_layers // args.pipeline_model_parallel_size

@@ -142,9 +142,11 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
     import subprocess
 
     ckpt, data = tmp_path / "ckpt", tmp_path / "data"
-    for d in ("Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-4B_torch_dist", "Qwen3-30B-A3B", "Qwen3-30B-A3B_torch_dist",
-              "Qwen3-8B", "Qwen3-8B_torch_dist", "Qwen3-32B_torch_dist", "Qwen2.5-0.5B-Instruct_torch_dist", "Qwen3-32B",
-              "Qwen3-235B-A22B", "Qwen3-235B-A22B_torch_dist", "Qwen3-4B-Base", "Qwen3-4B-Base_torch_dist", "Qwen3-4B-retool-sft", "Qwen3-4B-retool-sft_torch_dist"):
+    models = ["Qwen2.5-0.5B-Instruct", "Qwen3-4B", "Qwen3-30B-A3B", "Qwen3-8B", "Qwen3-32B", "Qwen3-235B-A22B", "Qwen3-4B-Base",
+              "Qwen3-4B-retool-sft", "GLM-Z1-9B-0414", "GLM-4.7-30B-A3B", "GLM-4.5-355B-A32B", "GLM-5", "GLM-5.2", "Kimi-K2-Instruct",
+              "Kimi-K2-Thinking", "DeepSeek-R1", "MiMo-7B-RL", "MiniMax-M2", "Moonlight-16B-A3B", "Qwen3-Next-80B-A3B-Thinking",
+              "Qwen3.5-27B", "Qwen3.5-35B-A3B"]  # fmt: skip
+    for d in [m + suffix for m in models for suffix in ("", "_torch_dist")]:
         (ckpt / d).mkdir(parents=True)
     for f in ("gsm8k/train.jsonl", "gsm8k/test.jsonl", "dapo-math-17k/dapo-math-17k.jsonl", "aime-2024/aime-2024.jsonl",
               "openhermes2_5/openhermes2_5.parquet"):
@@ -155,7 +157,7 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     scripts = sorted(glob.glob(os.path.join(root, "recipes", "run-*.sh")))
-    assert len(scripts) >= 4
+    assert len(scripts) >= 23  # one per launch recipe of the reference's scripts/ folder
     # launch lines of the script-based examples go through the same parser
     examples = [os.path.join(root, "examples", p) for p in (
         "delta_weight_sync/run-qwen3-30B-A3B-delta.sh", "on_policy_distillation/run-qwen3-8B-opd.sh",
@@ -181,14 +183,28 @@ def test_run_recipes_produce_parseable_command_lines(tmp_path):
         if "sft" in script:
             assert args.loss_type == "sft_loss" and args.debug_train_only and args.rollout_batch_size == 128
         else:
-            assert args.rollout_batch_size == 32 and args.n_samples_per_prompt == 8
+            assert args.rollout_batch_size in (8, 32, 64, 128) and args.n_samples_per_prompt in (4, 8)
+        base = os.path.basename(script)
+        if base == "run-deepseek-r1.sh":
+            assert args.multi_latent_attention and args.q_lora_rank == 1536 and args.sglang_quantization == "fp8"
+            assert args.moe_router_num_groups == 8 and args.expert_model_parallel_size == 32 and args.actor_num_nodes == 16
+        if base == "run-glm5-744B-A40B.sh":
+            assert args.index_topk == 2048 and args.v_head_dim == 256 and args.context_parallel_size == 2
+        if base == "run-qwen3-next-80B-A3B.sh":
+            assert args.full_attention_interval == 4 and args.attention_output_gate and args.advantage_estimator == "gspo"
+        if base == "run-mimo-7B-rl-mtp.sh":
+            assert args.enable_mtp_training and args.mtp_num_layers == 1
+        if base == "run-glm4-9B.sh":
+            assert args.rotary_percent == 0.5 and args.rotary_interleaved and args.post_mlp_layernorm
+        if base == "run-minimax-m2.sh":
+            assert args.qk_layernorm_full and args.moe_router_score_function == "sigmoid"
         if "qwen3-8B" in script:
             assert args.use_critic and args.advantage_estimator == "ppo"
-        if "32B" in script:
+        if base == "run-qwen3-32B.sh":
             assert args.tensor_model_parallel_size == 4 and args.rollout_num_gpus == 4 and not args.colocate
         if "reproducibility" in script:
             assert args.deterministic_mode
-        if "30B" in script:
+        if base == "run-qwen3-30B-A3B.sh":
             assert args.num_experts == 128 and args.expert_model_parallel_size == 8 and args.sglang_ep_size == 8
         if "async" in script:
             assert args.rollout_function_path.endswith("generate_rollout_fully_async") and not args.colocate
