@@ -76,6 +76,10 @@ CONFIGS = {
     # holds next to the trainer state and the KV pool), full on a single GPU where the whole optimizer state is local
     "qwen3-4b": dict(model="qwen3-4b", prompts_per_gpu=8, prompt_len=512, min_response=1024, max_response=8192,
                      max_tokens_per_gpu=9216, tp=2, recompute="auto", mem_fraction=0.72),
+    # MoE config: trainer TP4 (+ sequence parallel) with the experts spread over all ranks (EP = world, at most 8), one
+    # rollout engine per tensor-parallel group with its experts sharded over the group and block-fp8 resident weights
+    "qwen3-30b-a3b": dict(model="qwen3-30b-a3b", prompts_per_gpu=4, prompt_len=512, min_response=1024, max_response=8192,
+                          max_tokens_per_gpu=20480, tp=4, ep=8, recompute="full", mem_fraction=0.6, quantization="fp8"),
 }  # fmt: skip
 
 
@@ -154,6 +158,8 @@ def build_args(a, world, tp):
         sglang_mem_fraction_static=a.mem_fraction, sglang_max_running_requests=a.prompts_per_gpu * a.n_samples * tp,
         rollout_seed=42, seed=1234, tensor_model_parallel_size=tp, sequence_parallel=tp > 1,
         recompute_granularity="full" if a.recompute == "full" else None,
+        expert_model_parallel_size=getattr(a, "ep_used", 1), expert_tensor_parallel_size=1,
+        sglang_quantization=getattr(a, "quantization", None), sglang_ep_size=tp if getattr(a, "ep_used", 1) > 1 else 1,
     ))  # fmt: skip
     apply_to_args(get_preset(a.model), ns)
     ns.kv_channels = ns.kv_channels or ns.hidden_size // ns.num_attention_heads
@@ -189,7 +195,9 @@ def main():
     if a.recompute == "auto":
         a.recompute = "none" if tp > 1 else "full"
     assert world % tp == 0, f"{world} GPUs do not split into tensor-parallel groups of {tp}"
-    mpu.initialize_model_parallel(tensor_model_parallel_size=tp)
+    a.ep_used = min(getattr(a, "ep", None) or 1, world)
+    mpu.initialize_model_parallel(tensor_model_parallel_size=tp, expert_model_parallel_size=a.ep_used,
+                                  expert_tensor_parallel_size=1 if a.ep_used > 1 else None)
     args = build_args(a, world, tp)
     runner = ColocatedGRPO(args)
     # one data stream per data-parallel rank: the ranks of a tensor-parallel group see the same prompts
@@ -277,7 +285,7 @@ def main():
             "data": "synthetic (random prompt ids, random-init weights)", "impl": a.impl,
             "config": {"model": a.model, "layers": args.num_layers, "hidden": args.hidden_size,
                        "global_batch": a.prompts_per_gpu * n * world, "seq_len": f"{a.prompt_len}+U[{a.min_response},{a.max_response}]",
-                       "parallelism": (f"tp{tp}xdp{world // tp}" if tp > 1 else f"dp{world}"),
+                       "parallelism": (f"tp{tp}xdp{world // tp}" if tp > 1 else f"dp{world}") + (f"+ep{a.ep_used}" if a.ep_used > 1 else ""),
                        "rollout": f"{world // tp} engine(s) x tp{tp}", "prompts_per_gpu": a.prompts_per_gpu,
                        "n_samples_per_prompt": n, "colocated": True, "recompute": a.recompute,
                        "l2": "inputs larger than L2 (fresh prompts each step; weights+KV+activations >> 126 MB)",
