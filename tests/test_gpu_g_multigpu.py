@@ -82,3 +82,18 @@ def test_colocated_grpo_with_tensor_parallel_engine(kernels):
     _need(2)
     r = _torchrun("tests/multigpu/colocated_tp_check.py", 2, {"DEVICE": "cuda"}, timeout=300)
     assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_colocated_moe_with_fp8_engines_and_routing_replay(kernels):
+    """Two GRPO steps on a small MoE: experts of the trainer spread over the two GPUs, one block-fp8 rollout engine per GPU
+    (fp8 dense and grouped GEMMs, MoE decode in CUDA graphs), routers replaying the engines' expert choices."""
+    _need(2)
+    r = _torchrun("tests/multigpu/colocated_moe_check.py", 2, {"DEVICE": "cuda"}, timeout=300)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
+
+
+def test_expert_parallel_engine_matches_single_rank(kernels):
+    """TP2 + EP2 rollout engine on a small MoE against the single-GPU engine."""
+    _need(2)
+    r = _torchrun("tests/multigpu/engine_tp_check.py", 2, {"ENGINE_TP_CHECK_MOE": "1"}, timeout=300)
+    assert r.returncode == 0 and "RESULT ok" in r.stdout, r.stdout[-3000:] + r.stderr[-3000:]
