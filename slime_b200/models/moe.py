@@ -200,24 +200,24 @@ class MoELayer(nn.Module):
         order = torch.argsort(flat_e, stable=True)
         tok_of_row = order // k
         rows = normed.index_select(0, tok_of_row)
-        counts = torch.bincount(flat_e, minlength=cfg.num_experts)
+        counts = torch.zeros(cfg.num_experts, dtype=torch.long, device=x.device).scatter_add_(0, flat_e, torch.ones_like(flat_e))
 
         if self.ep > 1:
             group = mpu.get_expert_model_parallel_group()
             send_counts = counts.view(self.ep, self.num_local)
             recv_counts = torch.empty_like(send_counts)
             dist.all_to_all_single(recv_counts.view(-1), send_counts.reshape(-1).contiguous(), group=group)
-            in_splits = send_counts.sum(1).tolist()
-            out_splits = recv_counts.sum(1).tolist()
+            # the one host synchronisation of the layer: NCCL's all-to-all wants its split sizes on the host
+            send_h, recv_h = torch.stack([send_counts, recv_counts]).tolist()
+            in_splits, out_splits = [sum(r) for r in send_h], [sum(r) for r in recv_h]
             recv = _AllToAll.apply(rows, out_splits, in_splits, group)
             # received rows are ordered (source rank, local expert); regroup by local expert
-            rc = recv_counts.tolist()
-            src_e = torch.cat(
-                [torch.full((rc[r][e],), e, dtype=torch.long, device=x.device) for r in range(self.ep) for e in range(self.num_local)]
-            ) if recv.shape[0] else torch.zeros(0, dtype=torch.long, device=x.device)
+            total = sum(out_splits)
+            src_e = torch.repeat_interleave(torch.arange(self.num_local, device=x.device).repeat(self.ep), recv_counts.reshape(-1),
+                                            output_size=total)  # fmt: skip
             local_order = torch.argsort(src_e, stable=True)
             grouped = recv.index_select(0, local_order)
-            local_counts = recv_counts.sum(0).tolist()
+            local_counts = [sum(recv_h[r][e] for r in range(self.ep)) for e in range(self.num_local)]
             y = self.experts(grouped, local_counts)
             back = torch.empty_like(y)
             back = back.index_copy(0, local_order, y)
