@@ -115,7 +115,7 @@ def save_checkpoint(args, iteration: int | str, model, save_optimizer: bool = Tr
         os.makedirs(path, exist_ok=True)
     if _world():
         dist.barrier()
-    state = {"model." + k if False else k: v for k, v in model_state_for_save(model).items()}
+    state = dict(model_state_for_save(model))
     if save_optimizer and model.optimizer is not None:
         osd = model.optimizer.state_dict()
         for bi, shard in enumerate(osd["shards"]):
@@ -134,9 +134,13 @@ def save_checkpoint(args, iteration: int | str, model, save_optimizer: bool = Tr
             "format": "torch_dist",
         }
 
+    rng = None if getattr(args, "no_save_rng", False) else collect_rng_state()
+
     def _write():
         writer = dcp.FileSystemWriter(path, single_file_per_rank=True, thread_count=2)
         dcp.save(state, storage_writer=writer, no_dist=not _world())
+        if rng is not None:  # every rank keeps its own streams (host, device, model-parallel generators)
+            torch.save(rng, os.path.join(path, f"rng_rank{rank:05d}.pt"))
         if rank == 0:
             torch.save(common, os.path.join(path, "common.pt"))
             tmp = os.path.join(base, TRACKER + ".tmp")
@@ -144,6 +148,8 @@ def save_checkpoint(args, iteration: int | str, model, save_optimizer: bool = Tr
                 f.write(str(iteration))
             os.replace(tmp, os.path.join(base, TRACKER))
 
+    if async_save and _world():
+        logger.warning("async_save: a multi-rank save is collective and runs synchronously")
     if async_save and not _world():
         t = threading.Thread(target=_write, daemon=True)
         t.start()
@@ -250,6 +256,45 @@ def _load_native(args, model, base, load_optimizer):
             opt.step_count = common.get("optimizer_step", 0)
             if model.scheduler is not None and common.get("opt_param_scheduler"):
                 model.scheduler.load_state_dict(common["opt_param_scheduler"])
-    if not getattr(args, "no_load_rng", False) and common.get("rng_state"):
-        torch.set_rng_state(common["rng_state"]["torch"])
+    if not getattr(args, "no_load_rng", False) and not getattr(args, "finetune", False):
+        rank = dist.get_rank() if _world() else 0
+        own = os.path.join(path, f"rng_rank{rank:05d}.pt")
+        if os.path.exists(own):
+            restore_rng_state(torch.load(own, weights_only=False))
+        elif common.get("rng_state"):  # a checkpoint written by another layout (or an older one): rank 0's host stream only
+            torch.set_rng_state(common["rng_state"]["torch"])
     return iteration if isinstance(iteration, int) else None
+
+
+def collect_rng_state() -> dict:
+    """This rank's random streams: torch host and device generators, ``random``, numpy, and the model-parallel
+    generators parameters and dropout draw from (Megatron checkpoints carry the same per rank)."""
+    import random
+
+    import numpy as np
+
+    from slime_b200.parallel import tensor_parallel as tp
+
+    out = {"torch": torch.get_rng_state(), "python": random.getstate(), "numpy": np.random.get_state(),
+           "tracker": {k: g.get_state() for k, g in tp.get_rng_tracker().states.items()}}  # fmt: skip
+    if torch.cuda.is_available():
+        out["cuda"] = torch.cuda.get_rng_state()
+    return out
+
+
+def restore_rng_state(state: dict) -> None:
+    import random
+
+    import numpy as np
+
+    from slime_b200.parallel import tensor_parallel as tp
+
+    torch.set_rng_state(state["torch"])
+    random.setstate(state["python"])
+    np.random.set_state(state["numpy"])
+    if "cuda" in state and torch.cuda.is_available():
+        torch.cuda.set_rng_state(state["cuda"])
+    gens = tp.get_rng_tracker().states
+    for k, st in state.get("tracker", {}).items():
+        if k in gens:
+            gens[k].set_state(st.to(gens[k].get_state().device) if hasattr(st, "to") else st)

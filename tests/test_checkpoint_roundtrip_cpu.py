@@ -54,6 +54,21 @@ def test_save_load_continue_identically(tmp_path):
     _fake_step(m2, 3)
     for (n, p1), (_, p2) in zip(m1.named_parameters(), m2.named_parameters()):
         assert torch.equal(p1, p2), n
+    # every random stream of the rank came back: host generator, python, numpy and the model-parallel generators
+    import random
+
+    import numpy as np
+
+    from slime_b200.parallel import tensor_parallel as tp
+
+    assert os.path.exists(os.path.join(path, "rng_rank00000.pt"))
+    saved = torch.load(os.path.join(path, "rng_rank00000.pt"), weights_only=False)
+    ckpt.restore_rng_state(saved)
+    draws = (torch.rand(3), random.random(), np.random.rand(), {k: torch.rand(2, generator=g) for k, g in tp.get_rng_tracker().states.items()})
+    torch.rand(5), random.random(), np.random.rand()
+    ckpt.restore_rng_state(saved)
+    again = (torch.rand(3), random.random(), np.random.rand(), {k: torch.rand(2, generator=g) for k, g in tp.get_rng_tracker().states.items()})
+    assert torch.equal(draws[0], again[0]) and draws[1:3] == again[1:3] and all(torch.equal(draws[3][k], again[3][k]) for k in draws[3])
 
     # --ckpt-step picks an older iteration; --finetune / no optimizer keeps fresh optimizer state
     ckpt.save_checkpoint(a, 3, m1)
