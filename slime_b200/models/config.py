@@ -24,6 +24,12 @@ class ModelConfig:
     norm_epsilon: float = 1e-6
     rotary_base: float = 10000.0
     rotary_scaling_factor: float = 1.0
+    rotary_scaling_type: str = "linear"  # linear (positions divided by the factor) | yarn
+    rotary_original_max_position: int = 4096  # yarn: the context length the frequencies were trained at
+    yarn_beta_fast: float = 32.0
+    yarn_beta_slow: float = 1.0
+    mscale: float = 1.0
+    mscale_all_dim: float = 0.0
     max_position_embeddings: int = 32768
     tie_word_embeddings: bool = True
     add_qkv_bias: bool = False
@@ -225,6 +231,15 @@ class ModelConfig:
                       qk_layernorm=False)  # fmt: skip
             if c.get("index_topk"):
                 kw.update(index_topk=c["index_topk"], index_n_heads=c["index_n_heads"], index_head_dim=c["index_head_dim"])
+            kw["rotary_interleaved"] = True  # DeepSeek-style checkpoints rotate (2i, 2i + 1) pairs of the rotary part
+        rs = c.get("rope_scaling") or {}
+        if rs.get("type", rs.get("rope_type")) == "yarn":
+            kw.update(rotary_scaling_type="yarn", rotary_scaling_factor=float(rs["factor"]),
+                      rotary_original_max_position=int(rs.get("original_max_position_embeddings", 4096)),
+                      yarn_beta_fast=float(rs.get("beta_fast", 32)), yarn_beta_slow=float(rs.get("beta_slow", 1)),
+                      mscale=float(rs.get("mscale", 1.0)), mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)))  # fmt: skip
+        elif rs.get("type", rs.get("rope_type")) == "linear":
+            kw["rotary_scaling_factor"] = float(rs["factor"])
         if "minimax" in a:
             kw.update(qk_layernorm=False, qk_layernorm_full=bool(c.get("use_qk_norm", True)))
         return cls(**kw)

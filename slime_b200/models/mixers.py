@@ -382,12 +382,24 @@ class MLASelfAttention(nn.Module):
         self.linear_kv_up_proj.weight = mk(self.hq * (self.dn + self.dv), cfg.kv_lora_rank, std=std)
         self.linear_proj.weight = mk(h, self.hq * self.dv, std=std / math.sqrt(2.0 * cfg.num_layers))
         self.scale = (self.dn + self.dr) ** -0.5
+        if cfg.rotary_scaling_type == "yarn" and cfg.rotary_scaling_factor > 1 and cfg.mscale_all_dim:
+            from slime_b200.ops.reference import yarn_mscale
+
+            self.scale *= yarn_mscale(cfg.rotary_scaling_factor, cfg.mscale_all_dim) ** 2  # YaRN's attention temperature
         self._rope = None
 
     def _table(self, device, need):
         if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
-            self._rope = ops.rope_cos_sin(max(need, 4096), self.dr, self.cfg.rotary_base, device=device,
-                                          scaling_factor=self.cfg.rotary_scaling_factor)  # fmt: skip
+            c = self.cfg
+            if c.rotary_scaling_type == "yarn" and c.rotary_scaling_factor > 1:
+                from slime_b200.ops import reference
+
+                self._rope = reference.rope_cos_sin_yarn(max(need, 4096), self.dr, c.rotary_base, c.rotary_scaling_factor,
+                                                         c.rotary_original_max_position, c.yarn_beta_fast, c.yarn_beta_slow,
+                                                         c.mscale, c.mscale_all_dim, device=device)  # fmt: skip
+            else:
+                self._rope = ops.rope_cos_sin(max(need, 4096), self.dr, c.rotary_base, device=device,
+                                              scaling_factor=c.rotary_scaling_factor)  # fmt: skip
         return self._rope
 
     def _qkv(self, inp, packed):

@@ -53,7 +53,7 @@ MORE_PRESETS: dict[str, dict] = {
 
 def _mla(q_lora, kv_lora=512, nope=128, rope=64, v=128) -> dict:
     return dict(multi_latent_attention=True, q_lora_rank=q_lora, kv_lora_rank=kv_lora, qk_head_dim=nope,
-                qk_pos_emb_head_dim=rope, v_head_dim=v)  # fmt: skip
+                qk_pos_emb_head_dim=rope, v_head_dim=v, rotary_interleaved=True)  # fmt: skip
 
 
 def _sigmoid_router(scale, groups=None, group_topk=None) -> dict:
@@ -72,13 +72,15 @@ def _gdn(key_heads, value_heads, key_dim=128, value_dim=128) -> dict:
 def _deepseek_v3(layers: int) -> dict:
     return _moe(min(3, layers), max(layers - 3, 0), **_dense(
         layers, 7168, 18432, 128, 128, 129280, kv=128, rope=1e4, arch="DeepseekV3ForCausalLM", rotary_scaling_factor=40.0,
+        rotary_scaling_type="yarn", mscale=1.0, mscale_all_dim=1.0,
         num_experts=256, moe_ffn_hidden_size=2048, moe_router_topk=8, moe_shared_expert_intermediate_size=2048,
         **_mla(1536), **_sigmoid_router(2.5, 8, 4)))  # fmt: skip
 
 
 def _kimi_k2(eps: float, scaling: float) -> dict:
     return _moe(1, 60, **_dense(61, 7168, 18432, 64, 64, 163840, kv=64, rope=5e4, eps=eps, arch="DeepseekV3ForCausalLM",
-                                rotary_scaling_factor=scaling, num_experts=384, moe_ffn_hidden_size=2048, moe_router_topk=8,
+                                rotary_scaling_factor=scaling, rotary_scaling_type="yarn", mscale=1.0, mscale_all_dim=1.0,
+                                num_experts=384, moe_ffn_hidden_size=2048, moe_router_topk=8,
                                 moe_shared_expert_intermediate_size=2048, **_mla(1536), **_sigmoid_router(2.827)))  # fmt: skip
 
 
@@ -150,7 +152,8 @@ def to_flags(cfg) -> list[str]:
         if cfg.num_experts is None and (f.name.startswith("moe_") or f.name == "norm_topk_prob"):
             continue
         if f.name in ("rotary_scaling_factor", "mtp_num_layers", "norm_topk_prob", "rotary_percent", "linear_conv_kernel_dim",
-                      "index_topk_freq", "index_skip_topk_offset") and v == base[f.name]:  # fmt: skip
+                      "index_topk_freq", "index_skip_topk_offset", "rotary_scaling_type", "rotary_original_max_position",
+                      "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim") and v == base[f.name]:  # fmt: skip
             continue
         flag = "--" + f.name.replace("_", "-")
         if isinstance(v, bool):

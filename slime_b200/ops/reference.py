@@ -37,6 +37,44 @@ def rope_cos_sin(max_pos: int, dim: int, base: float, device=None, scaling_facto
     return torch.cat([ang.cos(), ang.sin()], dim=-1).float()
 
 
+def yarn_inv_freq(dim: int, base: float, factor: float, original_max_position: int, beta_fast: float = 32.0,
+                  beta_slow: float = 1.0) -> torch.Tensor:
+    """YaRN frequencies: dimensions that turn more than ``beta_fast`` times over the original context keep their
+    frequency, those that turn less than ``beta_slow`` times are slowed by ``factor`` (position interpolation), the
+    ones in between blend linearly."""
+    import math
+
+    idx = torch.arange(0, dim, 2, dtype=torch.float64)
+    extra = 1.0 / (base ** (idx / dim))
+    inter = extra / factor
+
+    def correction_dim(rotations: float) -> float:
+        return dim * math.log(original_max_position / (rotations * 2 * math.pi)) / (2 * math.log(base))
+
+    low = max(math.floor(correction_dim(beta_fast)), 0)
+    high = min(math.ceil(correction_dim(beta_slow)), dim - 1)
+    ramp = ((torch.arange(dim // 2, dtype=torch.float64) - low) / max(high - low, 1e-3)).clamp(0, 1)
+    keep = 1.0 - ramp
+    return inter * (1 - keep) + extra * keep
+
+
+def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    import math
+
+    return 1.0 if factor <= 1 else 0.1 * mscale * math.log(factor) + 1.0
+
+
+def rope_cos_sin_yarn(max_pos: int, dim: int, base: float, factor: float, original_max_position: int, beta_fast: float = 32.0,
+                      beta_slow: float = 1.0, mscale: float = 1.0, mscale_all_dim: float = 0.0, device=None) -> torch.Tensor:
+    """Table ``[max_pos, dim]`` = ``[cos | sin]`` with YaRN frequencies; the table carries the magnitude correction
+    ``yarn_mscale(factor, mscale) / yarn_mscale(factor, mscale_all_dim)`` (1 when both are equal)."""
+    inv = yarn_inv_freq(dim, base, factor, original_max_position, beta_fast, beta_slow)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    m = yarn_mscale(factor, mscale) / yarn_mscale(factor, mscale_all_dim)
+    return (torch.cat([ang.cos(), ang.sin()], dim=-1) * m).float().to(device) if device is not None else (
+        torch.cat([ang.cos(), ang.sin()], dim=-1) * m).float()
+
+
 def rope(x, positions, cos_sin, norm_weight=None, eps=1e-6, sign=1.0):
     """x: [T, H, D]; rotate-half RoPE, optionally preceded by per-head RMSNorm over D."""
     T, H, D = x.shape

@@ -229,8 +229,11 @@ _MODEL = [
     _f("--multi-latent-attention", action=_T), _f("--q-lora-rank", type=int, default=None),
     _f("--kv-lora-rank", type=int, default=None), _f("--qk-head-dim", type=int, default=None),
     _f("--qk-pos-emb-head-dim", type=int, default=None), _f("--v-head-dim", type=int, default=None),
-    _f("--mscale", type=float, default=1.0), _f("--mscale-all-dim", type=float, default=1.0),
+    _f("--mscale", type=float, default=1.0), _f("--mscale-all-dim", type=float, default=0.0),
     _f("--qk-layernorm-full", action=_T), _f("--softmax-sinks", action=_T),
+    _f("--rotary-scaling-type", type=str, default="linear", choices=["linear", "yarn"]),
+    _f("--rotary-original-max-position", type=int, default=4096), _f("--yarn-beta-fast", type=float, default=32.0),
+    _f("--yarn-beta-slow", type=float, default=1.0),
     _f("--full-attention-interval", type=int, default=None), _f("--linear-num-key-heads", type=int, default=None),
     _f("--linear-num-value-heads", type=int, default=None), _f("--linear-key-head-dim", type=int, default=None),
     _f("--linear-value-head-dim", type=int, default=None), _f("--linear-conv-kernel-dim", type=int, default=4),

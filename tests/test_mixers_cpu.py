@@ -357,3 +357,25 @@ def test_grpo_step_trains_the_draft_head_end_to_end():
     assert math.isfinite(float(out["metrics"]["train/loss"]))
     after = dict(r.actor.model.named_parameters())
     assert all(not torch.equal(after[n].detach(), w) for n, w in before.items())
+
+
+def test_yarn_frequencies_keep_fast_dimensions_and_interpolate_slow_ones():
+    from slime_b200.ops import reference
+
+    dim, base, factor, orig = 64, 1e4, 40.0, 4096
+    plain = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+    inv = reference.yarn_inv_freq(dim, base, factor, orig)
+    assert torch.allclose(inv[:4], plain[:4])  # many turns inside the original context: untouched
+    assert torch.allclose(inv[-4:], plain[-4:] / factor)  # less than one turn: positions interpolated by the factor
+    mid = (inv / plain)[4:-4]
+    assert ((mid <= 1 + 1e-12) & (mid >= 1 / factor - 1e-12)).all() and (mid[1:] <= mid[:-1] + 1e-12).all()  # monotone blend
+    assert torch.allclose(reference.yarn_inv_freq(dim, base, 1.0, orig), plain)
+    assert reference.yarn_mscale(1.0) == 1.0 and abs(reference.yarn_mscale(40.0, 1.0) - (0.1 * math.log(40.0) + 1)) < 1e-12
+    table = reference.rope_cos_sin_yarn(16, dim, base, factor, orig, mscale=1.0, mscale_all_dim=1.0)
+    assert table.shape == (16, dim) and torch.allclose(table[0, : dim // 2], torch.ones(dim // 2))
+    # the latent-attention layer picks the table and the attention temperature up from the config
+    cfg = _tiny(multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=8, v_head_dim=8,
+                rotary_scaling_type="yarn", rotary_scaling_factor=40.0, mscale=1.0, mscale_all_dim=1.0)  # fmt: skip
+    layer = mixers.MLASelfAttention(cfg, 0, torch.float32, "cpu", False)
+    assert abs(layer.scale - 16**-0.5 * reference.yarn_mscale(40.0, 1.0) ** 2) < 1e-9
+    assert torch.allclose(layer._table("cpu", 8)[:8], reference.rope_cos_sin_yarn(4096, 8, 1e4, 40.0, 4096, mscale=1.0, mscale_all_dim=1.0)[:8])
