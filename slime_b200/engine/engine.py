@@ -747,4 +747,5 @@ class Engine:
             m["top_p_token_offsets"] = encode_int32_meta_array(req.kept_offsets)
         if req.return_routed_experts and req.routed_experts:
             m["routed_experts"] = encode_int32_meta_array(torch.cat(req.routed_experts).reshape(-1))
+        m.update(req.extra_meta)
         return m

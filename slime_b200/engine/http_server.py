@@ -22,6 +22,7 @@ import asyncio
 import base64
 import io
 import json
+import os
 import threading
 import time
 
@@ -159,10 +160,16 @@ class EngineServer:
         from aiohttp import web
 
         host = body["bootstrap_host"]
-        async with aiohttp.ClientSession() as s, s.get(f"{host}/disagg/kv/{room}") as resp:
-            if resp.status != 200:
-                return web.json_response({"error": f"KV {room} not available at {host}"}, status=502)
-            blob = await resp.read()
+        limit = float(os.environ.get("SLIME_B200_DISAGG_TRANSFER_TIMEOUT", "600"))  # a stuck transfer ends with 504
+        t0 = time.time()
+        try:
+            async with aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=limit)) as s, s.get(f"{host}/disagg/kv/{room}") as resp:
+                if resp.status != 200:
+                    return web.json_response({"error": f"KV {room} not available at {host}"}, status=502)
+                blob = await resp.read()
+        except asyncio.TimeoutError:
+            return web.json_response({"error": f"KV transfer from {host} exceeded {limit:.0f} s"}, status=504)
+        transfer_s = max(time.time() - t0, 1e-9)
         n = int.from_bytes(blob[:4], "little")
         header = json.loads(blob[4 : 4 + n])
         dt = getattr(torch, header["dtype"])
@@ -186,6 +193,9 @@ class EngineServer:
                                              return_logprob=bool(body.get("return_logprob", False)), done_event=_Done())  # fmt: skip
         except Exception as e:  # noqa: BLE001 - out of pages, shape mismatch
             return web.json_response({"error": repr(e)}, status=503)
+        mb = len(blob) / 1e6
+        req.extra_meta.update(pd_transfer_total_mb=mb, pd_transfer_duration=transfer_s, pd_transfer_speed_gb_s=mb / 1e3 / transfer_s,
+                              pd_prefill_host=host, pd_prefill_retry_count=0)  # fmt: skip
         if req.finished():
             ev.set()
         self._wake.set()
@@ -345,6 +355,7 @@ class EngineServer:
     async def _release(self, request):
         body = await self._json(request)
         self.engine.flush_cache()
+        self.kv_store.clear()  # exported KV nobody has fetched yet goes with the cache it was copied from
         self.engine.release_memory_occupation(body.get("tags"))
         return self._ok()
 

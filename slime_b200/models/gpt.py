@@ -378,22 +378,26 @@ class GPTModel(nn.Module):
         """Draft-head loss of the micro-batch whose trunk forward just ran: mean over valid positions of the cross
         entropy of depth k predicting token i + k + 2 from position i, averaged over depths. ``full_loss_mask`` [T] is 1
         where position i predicts a trained token i + 1; a depth-k target is trained when it lies in the same sequence
-        and its own predicting position is trained. Depth k + 1 consumes depth k's hidden state."""
+        and its own predicting position is trained. Depth k + 1 consumes depth k's hidden state. (The reference's Megatron
+        patch detaches the same three inputs: docker/patch/latest/megatron.patch:556-640.)"""
         from slime_b200.utils.ppo_utils import calculate_log_probs_and_entropy
 
         assert self._mtp_inputs is not None, "run the trunk forward with mtp_training set first"
         hidden, ids, packed, table = self._mtp_inputs
         self._mtp_inputs = None
+        # the draft head is trained without touching the policy: it sees the trunk's hidden states, the embedding table
+        # and the output head as constants, so only its own parameters receive gradients
+        hidden = hidden.detach()
         ids = ids.reshape(-1)
         T = ids.numel()
         seq = torch.searchsorted(packed.cu_seqlens.long(), torch.arange(T, device=ids.device), right=True)
         mask = full_loss_mask.reshape(-1).float()
-        w = self.output_weight()
+        w = self.output_weight().detach()
         total = hidden.new_zeros((), dtype=torch.float32)
         for k, layer in enumerate(self.mtp.layers):
             shift = k + 1
             nxt = torch.cat([ids[shift:], ids.new_zeros(shift)])  # token i + k + 1, the draft head's extra input
-            emb = ops.embedding(nxt, self.embedding.word_embeddings.weight, self.vocab_start)
+            emb = ops.embedding(nxt, self.embedding.word_embeddings.weight.detach(), self.vocab_start)
             if mpu.get_tensor_model_parallel_world_size() > 1:
                 emb = tp.reduce_from_tensor_model_parallel_region(emb)
             if self.sequence_parallel:

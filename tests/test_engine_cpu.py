@@ -305,6 +305,8 @@ def test_router_runs_prefill_and_decode_on_different_servers():
         assert engines[1].stats["prefill_tokens"] == 0 and engines[1].stats["imported_tokens"] == 9
         assert engines[0].stats["prefill_tokens"] == 9 and engines[0].stats["decode_tokens"] == 0
         assert not servers[0].kv_store  # served once, then dropped
+        assert via["meta_info"]["pd_transfer_total_mb"] > 0 and via["meta_info"]["pd_transfer_speed_gb_s"] > 0
+        assert "pd_transfer_total_mb" not in ref["meta_info"]
         # a request that ends with its first token never reaches the decode server
         one = requests.post(f"http://127.0.0.1:{router.port}/generate", timeout=120,
                             json=dict(body, sampling_params=dict(body["sampling_params"], max_new_tokens=1))).json()
