@@ -72,6 +72,9 @@ class TrainModel:
             if getattr(args, "enable_mtp_training", False) and hasattr(m, "mtp_training"):
                 m.mtp_training = True
             self.chunks.append(m)
+        from slime_b200.observability import layerwise_dump
+
+        self.layer_dump = layerwise_dump.enable_from_env(self, prefix=f"{role}_")
         self._freeze_params()
         self._build_buffers()
         self.optimizer = self.scheduler = None
@@ -351,6 +354,10 @@ def train_one_step(args, rollout_id, step_id, data_iterator, model: TrainModel, 
 
     logs = pipeline.run_forward_backward(model, data_iterator[0], num_microbatches, forward_step, args)
     model.finalize_grads()
+    if getattr(args, "ci_test", False) and getattr(args, "enable_mtp_training", False) and getattr(args, "ci_check_mtp_only_grad", False):
+        from slime_b200.backends.train.ci_utils import check_mtp_only_grad
+
+        check_mtp_only_grad(model, step_id)
 
     # non-finite guard on the device: the flag makes the Adam kernel a no-op (no host sync)
     opt = model.optimizer

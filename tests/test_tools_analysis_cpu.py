@@ -87,3 +87,72 @@ def test_timeline_viewer(tmp_path):
     page = html_path.read_text()
     assert "rollout_3.pt" in page and '"span_summary"' in page and "__DATA__" not in page
     assert tv.main([str(tmp_path / "missing.pt")]) == 1
+
+
+def test_layerwise_dump_and_compare(tmp_path, monkeypatch):
+    import torch
+
+    from slime_b200.models.config import get_preset
+    from slime_b200.models.gpt import GPTModel
+    from slime_b200.observability import layerwise_dump as ld
+
+    cfg = get_preset("tiny")
+    ids = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(0))
+    for tag, seed in (("a", 1), ("b", 1), ("c", 2)):
+        model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=seed)
+        dump = ld.LayerDump(str(tmp_path), None, prefix=f"{tag}_")
+        assert dump.register(model) == cfg.num_layers
+        model(ids)
+        model(ids + 1 - 1)  # a second pass does not overwrite the first
+        dump.remove()
+    same = ld.compare(str(tmp_path / "a_rank0"), str(tmp_path / "b_rank0"))
+    assert [r["layer"] for r in same] == [0, 1] and all(r["max_abs"] == 0 and not r["over"] for r in same)
+    diff = ld.compare(str(tmp_path / "a_rank0"), str(tmp_path / "c_rank0"))
+    assert all(r["over"] for r in diff)
+    assert ld.main([str(tmp_path / "a_rank0"), str(tmp_path / "c_rank0"), "1e-3"]) == 0
+
+
+def test_command_utils_build_commands(monkeypatch, capsys):
+    from slime_b200.utils.external_utils import command_utils as U
+
+    monkeypatch.setenv("DRY_RUN", "1")
+    monkeypatch.setenv("SLIME_SCRIPT_EXTRA_ENV_VARS", "A=1 B=two")
+    assert U._parse_extra_env_vars("A=1 B=two junk") == {"A": "1", "B": "two"}
+    assert U.execute_train("--num-rollout 1", 2, model_preset="qwen2.5-0.5B") == 0
+    out = capsys.readouterr().out
+    assert "train.py --swiglu" in out and "--num-layers 24" in out and "--actor-num-gpus-per-node 2" in out
+    assert U.get_bool_env_var("DRY_RUN") and not U.get_bool_env_var("NOT_SET_ANYWHERE")
+    import pytest
+
+    monkeypatch.setenv("X_BAD", "maybe")
+    with pytest.raises(ValueError):
+        U.get_bool_env_var("X_BAD")
+    assert len(U.create_run_id().split("-")) == 3
+
+
+def test_ci_check_that_the_draft_loss_does_not_leak(monkeypatch):
+    import torch
+
+    from slime_b200.backends.train.ci_utils import check_mtp_loss, check_mtp_only_grad
+
+    class P:
+        def __init__(self, g):
+            self.main_grad = torch.tensor(g)
+
+    class M:
+        def __init__(self, d):
+            self.d = d
+
+        def named_parameters(self):
+            return list(self.d.items())
+
+    check_mtp_only_grad(M({"mtp.layers.0.eh_proj.weight": P([1.0]), "decoder.layers.0.mlp.linear_fc1.weight": P([0.0])}))
+    import pytest
+
+    with pytest.raises(AssertionError, match="policy parameters received"):
+        check_mtp_only_grad(M({"mtp.layers.0.eh_proj.weight": P([1.0]), "decoder.layers.0.x": P([0.5])}))
+    with pytest.raises(AssertionError, match="no draft-head"):
+        check_mtp_only_grad(M({"mtp.layers.0.eh_proj.weight": P([0.0])}))
+    check_mtp_loss(0.3)
+    with pytest.raises(AssertionError):
+        check_mtp_loss(2.0)
