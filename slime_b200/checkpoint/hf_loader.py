@@ -77,7 +77,9 @@ def load_hf_weights(path: str, model) -> list[str]:
     missing = []
     from slime_b200.backends.train.checkpoint import global_param_name
 
-    for name, p in model.named_parameters():
+    # parameters, and the buffers a checkpoint carries (the router's score-correction bias)
+    tensors = list(model.named_parameters()) + [(n, b) for n, b in model.named_buffers() if n.endswith("expert_bias")]
+    for name, p in tensors:
         gname = global_param_name(name, p)
         try:
             sources, rule = convert.hf_sources_for(cfg, gname)

@@ -65,16 +65,32 @@ class EngineWeights:
         self.final_norm = e(h)
         self.layers = []
         for i in range(cfg.num_layers):
+            kind = cfg.mixer(i)
+            if kind not in ("attention", "general_attention") or cfg.attention_output_gate or cfg.softmax_sinks:
+                raise NotImplementedError(f"the rollout engine runs GQA attention layers; layer {i} of this model is {kind!r}"
+                                          + (" with an output gate" if cfg.attention_output_gate else "")
+                                          + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
+            full_norm = cfg.qk_layernorm_full  # one weight per projection (sharded like it) instead of one per head
             L = {
                 "ln1": e(h), "qkv": mat((self.hq + 2 * self.hkv) * d, h, parts=(self.hq * d, (self.hq + self.hkv) * d)),
                 "o": mat(h, self.hq * d), "ln2": e(h),
                 "qkv_bias": e((self.hq + 2 * self.hkv) * d) if cfg.add_qkv_bias else None,
-                "q_norm": e(d) if cfg.qk_layernorm else None, "k_norm": e(d) if cfg.qk_layernorm else None,
+                "q_norm": e(self.hq * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
+                "k_norm": e(self.hkv * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
+                "post_attn_ln": e(h) if cfg.post_self_attn_layernorm else None,
+                "post_mlp_ln": e(h) if cfg.post_mlp_layernorm else None,
             }  # fmt: skip
             if cfg.is_moe_layer(i):
                 el = self.experts_local
                 fe = cfg.moe_ffn_hidden_size
                 L.update(router=e(cfg.num_experts, h), w13=mat(el, 2 * fe, h, parts=(fe,)), w2=mat(el, h, fe))
+                if cfg.moe_router_enable_expert_bias:
+                    L["router_bias"] = torch.zeros(cfg.num_experts, dtype=torch.float32, device=device)
+                if cfg.moe_shared_expert_intermediate_size:
+                    fs = cfg.moe_shared_expert_intermediate_size // tp_size
+                    L.update(shared_gate_up=mat(2 * fs, h, parts=(fs,)), shared_down=mat(h, fs))
+                    if cfg.moe_shared_expert_gate:
+                        L["shared_gate"] = e(1, h)
             else:
                 L.update(gate_up=mat(2 * self.f, h, parts=(self.f,)), down=mat(h, self.f))
             self.layers.append(L)
@@ -140,10 +156,17 @@ class EngineWeights:
             "self_attn.k_proj.bias": lambda: L["qkv_bias"][q_rows : q_rows + kv_rows].copy_(self._rows(t, kv_rows)),
             "self_attn.v_proj.bias": lambda: L["qkv_bias"][q_rows + kv_rows :].copy_(self._rows(t, kv_rows)),
             "self_attn.qkv_proj.bias": lambda: L["qkv_bias"].copy_(t),
-            "self_attn.q_norm.weight": lambda: L["q_norm"].copy_(t),
-            "self_attn.k_norm.weight": lambda: L["k_norm"].copy_(t),
+            "self_attn.q_norm.weight": lambda: L["q_norm"].copy_(self._rows(t, q_rows) if cfg.qk_layernorm_full else t),
+            "self_attn.k_norm.weight": lambda: L["k_norm"].copy_(self._rows(t, kv_rows) if cfg.qk_layernorm_full else t),
             "mlp.gate.weight": lambda: L["router"].copy_(t),
+            "post_self_attn_layernorm.weight": lambda: L["post_attn_ln"].copy_(t),
+            "post_mlp_layernorm.weight": lambda: L["post_mlp_ln"].copy_(t),
+            "mlp.gate.e_score_correction_bias": lambda: L["router_bias"].copy_(raw.to(self.device, torch.float32)),
+            "mlp.shared_expert_gate.weight": lambda: L["shared_gate"].copy_(t),
         }
+        if sub in vectors and sub.split(".")[0] in ("post_self_attn_layernorm", "post_mlp_layernorm") and L.get(
+                "post_attn_ln" if sub.startswith("post_self") else "post_mlp_ln") is None:
+            return False
         if sub in vectors:
             vectors[sub]()
             return True
@@ -157,6 +180,11 @@ class EngineWeights:
             "mlp.up_proj": ("gate_up", f, f, 0), "mlp.gate_up_proj": ("gate_up", 0, 2 * f, None),
             "mlp.down_proj": ("down", 0, cfg.hidden_size, 1),
         }  # fmt: skip
+        if cfg.moe_shared_expert_intermediate_size:
+            fs = cfg.moe_shared_expert_intermediate_size // self.tp
+            for prefix in ("mlp.shared_experts", "mlp.shared_expert"):
+                matrices.update({f"{prefix}.gate_proj": ("shared_gate_up", 0, fs, 0), f"{prefix}.up_proj": ("shared_gate_up", fs, fs, 0),
+                                 f"{prefix}.down_proj": ("shared_down", 0, cfg.hidden_size, 1)})  # fmt: skip
         stem, _, kind = sub.rpartition(".")
         buf = None
         if stem in matrices and kind in ("weight", "weight_scale_inv"):
@@ -268,7 +296,9 @@ class ModelRunner:
                     self._fused_tp = fused_tp.FusedAllReduceNorm(tp_group, max_batch, cfg.hidden_size, self.device)
                 except Exception as e:  # noqa: BLE001
                     logger.warning("fused tensor-parallel all-reduce unavailable (%r): using NCCL", e)
-        self.rope = ops.rope_cos_sin(max_context + 1, cfg.head_dim, cfg.rotary_base, device=self.device,
+        self._composed_attention = cfg.rotary_percent < 1.0 or cfg.rotary_interleaved or cfg.qk_layernorm_full
+        rot = int(cfg.head_dim * cfg.rotary_percent) // 2 * 2
+        self.rope = ops.rope_cos_sin(max_context + 1, rot, cfg.rotary_base, device=self.device,
                                      scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         self.graphs: dict[int, tuple] = {}
@@ -317,8 +347,12 @@ class ModelRunner:
         full = parts.view(self.w.tp, T, vl).permute(1, 0, 2).reshape(T, -1)
         return full if full.shape[1] == V else full[:, :V]
 
-    def _row_parallel_norm(self, inp, weight, ln, res, T: int):
-        """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual)."""
+    def _row_parallel_norm(self, inp, weight, ln, res, T: int, post=None):
+        """``rmsnorm(sum over TP ranks of inp @ weight^T + res)`` -> (normed, new residual); ``post``: a sandwich norm
+        applied to the projected sum before it joins the residual stream."""
+        if post is not None:
+            x = self._post_norm(self._tp_reduce(_linear(inp, weight)), post)
+            return ops.rmsnorm(x, ln, self.cfg.norm_epsilon, res)
         if self._fused_tp is not None and T <= self._fused_tp.max_tokens:
             _linear(inp, weight, out=self._fused_tp.partial(T))
             return self._fused_tp(T, res, ln, self.cfg.norm_epsilon)
@@ -331,14 +365,30 @@ class ModelRunner:
             return self._tp_reduce(_linear(act, L["down"], out_dtype=self._proj_dtype))
         return self._moe(L, x)
 
-    def _moe(self, L, x):
+    def _route(self, L, logits):
+        """Expert choice and weights of every token, as the trainer's router computes them."""
         cfg = self.cfg
-        logits = ops.router_gemm(x, L["router"])
         from slime_b200.ops import grouped
 
-        probs, idx = grouped.route_topk(logits, cfg.moe_router_topk, score=cfg.moe_router_score_function,
-                                        pre_softmax=cfg.moe_router_pre_softmax, renorm=cfg.norm_topk_prob,
-                                        bias=L.get("router_bias"), scale=cfg.moe_router_topk_scaling_factor)  # fmt: skip
+        if cfg.moe_router_num_groups and cfg.moe_router_group_topk and cfg.moe_router_num_groups > 1:
+            # group-limited routing (sigmoid scores): no kernel for it; a handful of small device ops, capturable
+            from slime_b200.models.moe import group_limited
+
+            scores = torch.sigmoid(logits.float())
+            sel = scores + L["router_bias"] if L.get("router_bias") is not None else scores
+            idx = torch.topk(group_limited(sel, cfg.moe_router_num_groups, cfg.moe_router_group_topk), cfg.moe_router_topk, dim=-1).indices
+            probs = scores.gather(-1, idx)
+            if cfg.norm_topk_prob:
+                probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
+            return probs * (cfg.moe_router_topk_scaling_factor or 1.0), idx
+        return grouped.route_topk(logits, cfg.moe_router_topk, score=cfg.moe_router_score_function,
+                                  pre_softmax=cfg.moe_router_pre_softmax, renorm=cfg.norm_topk_prob,
+                                  bias=L.get("router_bias"), scale=cfg.moe_router_topk_scaling_factor)  # fmt: skip
+
+    def _moe(self, L, x):
+        from slime_b200.ops import grouped
+
+        probs, idx = self._route(L, ops.router_gemm(x, L["router"]))
         if self.record_routed:
             self._routed.append(idx.to(torch.int32))
         # expert-sorted, tile-padded layout built on the device (no host sync: the step stays graph-capturable), then
@@ -346,15 +396,57 @@ class ModelRunner:
 
         lay = grouped.DeviceLayout(idx, L["w13"].shape[0], self.w.first_expert)
         y = lay.combine(_grouped_linear(ops.swiglu(_grouped_linear(lay.pad(x), L["w13"], lay)), L["w2"], lay), probs, x.shape[0])
-        return self._tp_reduce(y) if self.w.ep > 1 else y
+        shared = None
+        if "shared_gate_up" in L:  # always-on expert, tensor-parallel like a dense MLP
+            shared = _linear(ops.swiglu(_linear(x, L["shared_gate_up"])), L["shared_down"])
+            if L.get("shared_gate") is not None:
+                shared = shared * torch.sigmoid(x.float() @ L["shared_gate"].float().t()).to(shared.dtype)
+        if self.w.ep > 1:  # expert outputs and the shared expert's partial sums travel in one reduction
+            return self._tp_reduce(y if shared is None else y + shared)
+        if shared is not None:
+            y = y + (self._tp_reduce(shared) if self.w.tp > 1 else shared)
+        return y
 
     def _qkv(self, L, normed, positions, slots, li):
         """Packed q / k / v of the new tokens, rotated (and per-head normalised) in place, k and v also written to
         their cache slots of layer ``li``: one GEMM and one fused launch."""
         cfg = self.cfg
         qkv = _linear(normed, L["qkv"], bias=L["qkv_bias"])
-        return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[li], self.kv.v[li], self.w.hq, self.w.hkv,
-                                 cfg.head_dim, L["q_norm"], L["k_norm"], cfg.norm_epsilon)  # fmt: skip
+        if not self._composed_attention:
+            return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[li], self.kv.v[li], self.w.hq, self.w.hkv,
+                                     cfg.head_dim, L["q_norm"], L["k_norm"], cfg.norm_epsilon)  # fmt: skip
+        # attention variants the fused kernel does not cover (partial / interleaved rotary, RMSNorm over all heads):
+        # the same steps as separate ops, then the ordinary cache write
+        from slime_b200.models import mixers
+
+        T, d, hq, hkv = qkv.shape[0], cfg.head_dim, self.w.hq, self.w.hkv
+        q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+        if L["q_norm"] is not None:
+            if cfg.qk_layernorm_full:
+                q, k = self._full_norm(q, L["q_norm"]), self._full_norm(k, L["k_norm"])
+            else:
+                q = mixers._rms(q.view(T, hq, d), L["q_norm"], cfg.norm_epsilon).view(T, -1)
+                k = mixers._rms(k.view(T, hkv, d), L["k_norm"], cfg.norm_epsilon).view(T, -1)
+        if self.rope.shape[1] > 0:
+            cos, sin = mixers.rotary_cos_sin(self.rope, positions)
+            q = mixers.apply_rotary(q.view(T, hq, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
+            k = mixers.apply_rotary(k.view(T, hkv, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
+        k, v = k.contiguous(), v.contiguous()
+        ops.kv_write(k, v, slots, self.kv.k[li], self.kv.v[li])
+        return torch.cat([q, k, v], dim=-1)
+
+    def _full_norm(self, t, w):
+        """RMSNorm over all heads of the model: the sum of squares crosses the tensor-parallel ranks."""
+        f = t.float()
+        ss = f.pow(2).sum(-1, keepdim=True)
+        n = f.shape[-1] * self.w.tp
+        if self.w.tp > 1:
+            ss = self._tp_reduce(ss)
+        return (f * torch.rsqrt(ss / n + self.cfg.norm_epsilon) * w.float()).to(t.dtype)
+
+    def _post_norm(self, x, w):
+        """GLM-4 sandwich norm: the sub-layer's output is normalised before it joins the residual stream."""
+        return x if w is None else ops.rmsnorm(x, w, self.cfg.norm_epsilon)[0]
 
     # --------------------------------------------------------------------- prefill
     @torch.no_grad()
@@ -383,8 +475,9 @@ class ModelRunner:
                 v_all = self.kv.v[li].index_select(0, kv_gather_slots)
                 ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale)
             x = self._tp_reduce(_linear(ctx.reshape(T, -1), L["o"], out_dtype=self._proj_dtype))
+            x = self._post_norm(x, L["post_attn_ln"])
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
-            x = self._mlp(L, normed)
+            x = self._post_norm(self._mlp(L, normed), L["post_mlp_ln"])
         h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
         if last_rows is not None:
             h = h.index_select(0, last_rows)
@@ -476,14 +569,14 @@ class ModelRunner:
             qkv = self._qkv(L, normed, pos, slots, li)
             q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
             ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
-            normed, res = self._row_parallel_norm(ctx.reshape(n, -1), L["o"], L["ln2"], res, n)
+            normed, res = self._row_parallel_norm(ctx.reshape(n, -1), L["o"], L["ln2"], res, n, post=L["post_attn_ln"])
             # the norm that follows the MLP is the next layer's input norm (or the final norm)
             next_ln = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.final_norm
             if "gate_up" in L:
                 act = ops.swiglu(_linear(normed, L["gate_up"]))
-                normed, res = self._row_parallel_norm(act, L["down"], next_ln, res, n)
+                normed, res = self._row_parallel_norm(act, L["down"], next_ln, res, n, post=L["post_mlp_ln"])
             else:
-                normed, res = ops.rmsnorm(self._moe(L, normed), next_ln, cfg.norm_epsilon, res)
+                normed, res = ops.rmsnorm(self._post_norm(self._moe(L, normed), L["post_mlp_ln"]), next_ln, cfg.norm_epsilon, res)
         h = normed
         logits = self._gather_logits(ops.gemm(h, w.lm_head, out_dtype=torch.float32))
         tok, lp, kept_ids, kept_cnt = ops.sample(

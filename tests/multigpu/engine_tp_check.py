@@ -70,7 +70,31 @@ def main():
         cfg = ModelConfig(num_layers=3, hidden_size=512, num_attention_heads=8, num_query_groups=4, kv_channels=64,
                           ffn_hidden_size=1024, vocab_size=2048, rotary_base=1e4, tie_word_embeddings=False, qk_layernorm=True,
                           num_experts=8, moe_ffn_hidden_size=256, moe_router_topk=2, moe_layer_freq=[0, 1, 1])
-    weights = hf_weights(cfg, dev)
+    family = os.environ.get("ENGINE_TP_CHECK_FAMILY")  # attention / routing variants served through the composed path
+    if family:
+        from slime_b200.models.gpt import GPTModel
+        from slime_b200.weight_sync import convert
+
+        extra = {"glm4": dict(add_qkv_bias=True, post_self_attn_layernorm=True, post_mlp_layernorm=True, rotary_percent=0.5,
+                              rotary_interleaved=True),
+                 "minimax_m2": dict(qk_layernorm_full=True, rotary_percent=0.5, num_experts=8, moe_ffn_hidden_size=256,
+                                    moe_router_topk=2, moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
+                                    moe_shared_expert_intermediate_size=512)}[family]  # fmt: skip
+        cfg = ModelConfig(num_layers=3, hidden_size=512, num_attention_heads=8, num_query_groups=4, kv_channels=64,
+                          ffn_hidden_size=1024, vocab_size=2048, rotary_base=1e4, tie_word_embeddings=False, **extra)
+        moe = cfg.num_experts is not None
+        trainer = GPTModel(cfg, dtype=torch.float32 if cpu else torch.bfloat16, device=dev, seed=5)  # same weights on every rank
+        with torch.no_grad():
+            for _n, p in trainer.named_parameters():
+                if p.dim() == 1:
+                    p.add_(torch.randn(p.shape, generator=torch.Generator().manual_seed(p.numel())).to(p) * 0.1)
+            for n, b in trainer.named_buffers():
+                if n.endswith("expert_bias"):
+                    b.copy_(torch.linspace(-0.3, 0.3, b.numel()))
+        weights = [x for n, p in list(trainer.named_parameters()) + list(trainer.named_buffers())
+                   for x in convert.convert_to_hf(cfg, n, p.detach())]  # fmt: skip
+    else:
+        weights = hf_weights(cfg, dev)
     sargs = dict(page_size=16, max_running_requests=16, context_length=256, disable_cuda_graph=cpu, ep_size=world if moe else 1)
     prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + i)] for i in range(6)]
     sp = dict(max_new_tokens=24, temperature=0)
@@ -108,7 +132,7 @@ def main():
             assert mean < 0.05 and worst < 1.5, (mean, worst)
         else:
             assert worst < (1e-4 if cpu else 0.08), worst
-        print(f"RESULT ok world={world} fused_tp={fused} moe_ep={world if moe else 0} max_logprob_diff={worst:.4f}", flush=True)
+        print(f"RESULT ok world={world} fused_tp={fused} moe_ep={world if moe else 0} family={family} max_logprob_diff={worst:.4f}", flush=True)
     from slime_b200.utils.distributed_utils import shutdown_distributed
 
     shutdown_distributed([tp])

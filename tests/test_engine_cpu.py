@@ -190,8 +190,9 @@ def test_openai_compatible_endpoints():
         srv.shutdown()
 
 
-@pytest.mark.parametrize("moe", [False, True], ids=["dense", "moe_ep2"])
-def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe):
+@pytest.mark.parametrize("moe,family", [(False, None), (True, None), (False, "glm4"), (False, "minimax_m2")],
+                         ids=["dense", "moe_ep2", "glm4", "minimax_m2_ep2"])
+def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe, family):
     """Two gloo ranks: TP weight slicing, row-parallel reductions and the vocab-parallel logits gather (host logic);
     with ``moe`` also experts sharded over the two ranks (each rank serves its own experts' routes, outputs summed)."""
     import os
@@ -200,8 +201,10 @@ def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe):
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     env = dict(os.environ, ENGINE_TP_CHECK_DEVICE="cpu", MASTER_ADDR="127.0.0.1", ENGINE_TP_CHECK_MOE=str(int(moe)))
+    if family:
+        env["ENGINE_TP_CHECK_FAMILY"] = family
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-                        "127.0.0.1", "--master-port", str(29671 + int(moe)), os.path.join(root, "tests/multigpu/engine_tp_check.py")],
+                        "127.0.0.1", "--master-port", str(29671 + int(moe) + {None: 0, "glm4": 2, "minimax_m2": 3}[family]), os.path.join(root, "tests/multigpu/engine_tp_check.py")],
                        env=env, cwd=root, capture_output=True, text=True, timeout=280)  # fmt: skip
     assert r.returncode == 0 and "RESULT ok world=2" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
