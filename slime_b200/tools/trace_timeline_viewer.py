@@ -27,7 +27,7 @@ import types
 from pathlib import Path
 from typing import Any
 
-CACHE_VERSION = 1
+CACHE_VERSION = 2
 
 
 class _Bag:
@@ -152,11 +152,57 @@ def build_cache(pt_path: Path) -> dict:
     for ln in lanes:
         for s in ln["spans"]:
             per_name.setdefault(s["name"], []).append(s["t1"] - s["t0"])
-    summary = {n: {"count": len(d), "total_s": round(sum(d), 6), "mean_s": round(sum(d) / len(d), 6), "max_s": round(max(d), 6)}
+    def pct(d, q):
+        d = sorted(d)
+        return d[min(len(d) - 1, int(q * len(d)))]
+
+    summary = {n: {"count": len(d), "total_s": round(sum(d), 6), "mean_s": round(sum(d) / len(d), 6), "p50_s": round(pct(d, 0.5), 6),
+                   "p95_s": round(pct(d, 0.95), 6), "max_s": round(max(d), 6)}
                for n, d in sorted(per_name.items(), key=lambda kv: -sum(kv[1]))}  # fmt: skip
-    return {"version": CACHE_VERSION, "source": pt_path.name, "rollout_id": dump.get("rollout_id") if isinstance(dump, dict) else None,
+    return {"version": CACHE_VERSION, "analysis": analyse_lanes(lanes), "source": pt_path.name, "rollout_id": dump.get("rollout_id") if isinstance(dump, dict) else None,
             "num_samples": len(samples), "num_lanes": len(lanes), "origin_ts": t0,
             "duration_s": round(max((ln["t1"] for ln in lanes), default=0.0), 6), "span_summary": summary, "lanes": lanes}  # fmt: skip
+
+
+def analyse_lanes(lanes: list[dict]) -> dict:
+    """What a rollout's wall time went to. ``concurrency``: time-weighted mean number of samples in flight and the share
+    of the wall time during which fewer than a tenth of the lanes were active (the long tail a partial-rollout or
+    over-sampling setting would cut). ``stragglers``: the five lanes that finished last with their longest top-level
+    span. ``idle``: per lane, the time inside its extent that no top-level span covers (waiting between turns)."""
+    if not lanes:
+        return {"concurrency": {}, "stragglers": [], "idle": {}}
+    edges = sorted([(ln["t0"], 1) for ln in lanes] + [(ln["t1"], -1) for ln in lanes])
+    end = max(ln["t1"] for ln in lanes)
+    active, last, area, tail = 0, edges[0][0], 0.0, 0.0
+    thin = max(1, len(lanes) // 10)
+    for t, d in edges:
+        area += active * (t - last)
+        if 0 < active <= thin:
+            tail += t - last
+        active, last = active + d, t
+    wall = max(end - edges[0][0], 1e-9)
+    stragglers = []
+    for ln in sorted(lanes, key=lambda x: -x["t1"])[:5]:
+        top = max((s for s in ln["spans"] if s["depth"] == 0), key=lambda s: s["t1"] - s["t0"], default=None)
+        stragglers.append({"label": ln["label"], "end_s": round(ln["t1"], 4), "duration_s": round(ln["t1"] - ln["t0"], 4),
+                           "response_length": ln.get("response_length"),
+                           "longest_span": None if top is None else {"name": top["name"], "s": round(top["t1"] - top["t0"], 4)}})  # fmt: skip
+    idle = {}
+    for ln in lanes:
+        tops = sorted((s["t0"], s["t1"]) for s in ln["spans"] if s["depth"] == 0)
+        covered, cur = 0.0, None
+        for a, b in tops:
+            if cur is None or a > cur[1]:
+                covered += 0.0 if cur is None else cur[1] - cur[0]
+                cur = [a, b]
+            else:
+                cur[1] = max(cur[1], b)
+        covered += 0.0 if cur is None else cur[1] - cur[0]
+        idle[ln["label"]] = round(max(ln["t1"] - ln["t0"] - covered, 0.0), 6)
+    worst_idle = dict(sorted(idle.items(), key=lambda kv: -kv[1])[:5])
+    return {"concurrency": {"mean_in_flight": round(area / wall, 3), "wall_s": round(wall, 4), "thin_tail_s": round(tail, 4),
+                            "thin_tail_share": round(tail / wall, 4), "thin_means_at_most": thin},
+            "stragglers": stragglers, "idle": {"total_s": round(sum(idle.values()), 4), "worst": worst_idle}}  # fmt: skip
 
 
 def timeline_paths(pt_path: Path) -> tuple[Path, Path]:
@@ -182,12 +228,13 @@ body{margin:0;font:12px system-ui,sans-serif;background:#111;color:#ddd}#bar{pad
 #wrap{display:flex;height:calc(100vh - 34px)}#labels{width:150px;overflow:hidden;background:#161616}#labels div{height:__LANE__px;line-height:__LANE__px;padding-left:8px;border-bottom:1px solid #222;cursor:pointer;white-space:nowrap}
 canvas{flex:1;display:block}#tip{position:fixed;pointer-events:none;background:#000d;border:1px solid #555;padding:6px 8px;max-width:460px;white-space:pre-wrap;display:none;z-index:9}
 input{background:#222;color:#ddd;border:1px solid #444;padding:2px 6px}</style></head><body>
-<div id="bar"><b>__TITLE__</b><span id="info"></span><input id="flt" placeholder="filter span names"><span id="sum"></span></div>
+<div id="bar"><b>__TITLE__</b><span id="info"></span><input id="flt" placeholder="filter span names"><select id="srt"><option value="lane">order: dump</option><option value="t0">start</option><option value="dur">duration</option><option value="t1">end</option><option value="reward">reward</option></select><span id="sum"></span></div>
 <div id="wrap"><div id="labels"></div><canvas id="cv"></canvas></div><div id="tip"></div><script>
 const D=__DATA__,LH=__LANE__,cv=document.getElementById('cv'),cx=cv.getContext('2d'),tip=document.getElementById('tip');
 let x0=0,x1=Math.max(D.duration_s,1e-3),scroll=0,flt='',hidden=new Set(),hit=[];
 const colors={};function col(n){if(!colors[n]){let h=0;for(const c of n)h=(h*31+c.charCodeAt(0))%360;colors[n]=`hsl(${h},55%,45%)`}return colors[n]}
-function lanes(){return D.lanes.filter(l=>!hidden.has(l.lane))}
+let srt='lane';const key={lane:l=>l.lane,t0:l=>l.t0,dur:l=>-(l.t1-l.t0),t1:l=>-l.t1,reward:l=>-(+l.reward||0)};
+function lanes(){return D.lanes.filter(l=>!hidden.has(l.lane)).sort((a,b)=>key[srt](a)-key[srt](b))}
 function draw(){const W=cv.width=cv.clientWidth,H=cv.height=cv.clientHeight;cx.clearRect(0,0,W,H);hit=[];const L=lanes(),sx=t=>(t-x0)/(x1-x0)*W;
  const lab=document.getElementById('labels');lab.innerHTML='';L.forEach((l,i)=>{const y=i*LH-scroll;if(y<-LH||y>H)return;const d=document.createElement('div');d.textContent=`${l.label} r=${l.reward} ${l.status||''}`;d.style.position='absolute';d.style.top=(y+34)+'px';d.style.width='142px';d.onclick=()=>{hidden.add(l.lane);draw()};lab.appendChild(d);
   cx.fillStyle=i%2?'#151515':'#191919';cx.fillRect(0,y,W,LH);
@@ -200,7 +247,7 @@ let drag=null;cv.onmousedown=e=>drag=[e.clientX,e.clientY,x0,x1,scroll];window.o
 window.onmousemove=e=>{if(drag){const dt=(e.clientX-drag[0])/cv.clientWidth*(drag[3]-drag[2]);x0=drag[2]-dt;x1=drag[3]-dt;scroll=Math.max(0,drag[4]-(e.clientY-drag[1]));draw();return}
  const r=cv.getBoundingClientRect(),x=e.clientX-r.left,y=e.clientY-r.top;let f=null;for(const h of hit)if(x>=h[0]&&x<=h[2]&&y>=h[1]&&y<=h[3])f=h;
  if(f){const o=f[4];tip.style.display='block';tip.style.left=(e.clientX+12)+'px';tip.style.top=(e.clientY+12)+'px';tip.textContent=`${o.name}  [${f[5].label}]\n`+(o.t0!==undefined?`${o.t0.toFixed(4)} -> ${o.t1.toFixed(4)} s  (${((o.t1-o.t0)*1e3).toFixed(2)} ms)${o.open?'  (never closed)':''}\n`:`at ${o.t.toFixed(4)} s\n`)+(o.error?`error: ${o.error}\n`:'')+JSON.stringify(o.attrs,null,1)}else tip.style.display='none'};
-document.getElementById('flt').oninput=e=>{flt=e.target.value;draw()};window.onresize=draw;
+document.getElementById('flt').oninput=e=>{flt=e.target.value;draw()};document.getElementById('srt').onchange=e=>{srt=e.target.value;draw()};window.onresize=draw;
 document.getElementById('sum').textContent=Object.entries(D.span_summary).slice(0,4).map(([n,s])=>`${n}: ${s.count}x mean ${(s.mean_s*1e3).toFixed(1)} ms`).join(' | ');draw();
 </script></body></html>"""
 
@@ -238,7 +285,18 @@ def main(argv=None) -> int:
     html = ensure_html(pt, data)
     print(f"{data['num_lanes']} lanes, {data['duration_s']:.2f} s -> {html}")
     for name, s in list(data["span_summary"].items())[:10]:
-        print(f"  {name:<32} {s['count']:6d}x  mean {s['mean_s'] * 1e3:9.2f} ms  max {s['max_s'] * 1e3:9.2f} ms")
+        print(f"  {name:<32} {s['count']:6d}x  mean {s['mean_s'] * 1e3:9.2f} ms  p50 {s['p50_s'] * 1e3:9.2f}  p95 {s['p95_s'] * 1e3:9.2f}"
+              f"  max {s['max_s'] * 1e3:9.2f} ms")
+    an = data.get("analysis") or {}
+    c = an.get("concurrency") or {}
+    if c:
+        print(f"  in flight: {c['mean_in_flight']:.1f} samples on average over {c['wall_s']:.2f} s; at most {c['thin_means_at_most']} "
+              f"active for {c['thin_tail_s']:.2f} s ({100 * c['thin_tail_share']:.1f} % of the wall time)")
+        for st in an.get("stragglers", [])[:3]:
+            ls = st["longest_span"]
+            print(f"  straggler {st['label']}: ended at {st['end_s']:.2f} s after {st['duration_s']:.2f} s, {st['response_length']} response "
+                  f"tokens" + (f", longest span {ls['name']} {ls['s']:.2f} s" if ls else ""))
+        print(f"  idle inside lanes (no top-level span): {an['idle']['total_s']:.2f} s in total")
     if a.serve:
         print(f"http://0.0.0.0:{a.port}/{html.name}")
         serve_directory(pt.parent, a.port)

@@ -3,6 +3,7 @@
 import gzip
 import json
 
+import pytest
 import torch
 
 from slime_b200.observability import trace_utils
@@ -87,6 +88,23 @@ def test_timeline_viewer(tmp_path):
     page = html_path.read_text()
     assert "rollout_3.pt" in page and '"span_summary"' in page and "__DATA__" not in page
     assert tv.main([str(tmp_path / "missing.pt")]) == 1
+    assert {"p50_s", "p95_s"} <= set(data["span_summary"]["generate"]) and 'id="srt"' in page
+
+
+def test_timeline_analysis_of_concurrency_stragglers_and_idle_time():
+    def lane(i, t0, t1, spans):
+        return {"lane": i, "label": f"s{i}", "t0": t0, "t1": t1, "response_length": 10 * (i + 1),
+                "spans": [{"name": n, "t0": a, "t1": b, "depth": d} for n, a, b, d in spans]}  # fmt: skip
+
+    lanes = [lane(i, 0.0, 1.0, [("generate", 0.0, 1.0, 0)]) for i in range(19)]
+    lanes.append(lane(19, 0.0, 5.0, [("generate", 0.0, 2.0, 0), ("tool", 0.5, 0.7, 1), ("generate", 3.0, 5.0, 0)]))
+    a = tv.analyse_lanes(lanes)
+    c = a["concurrency"]
+    assert c["wall_s"] == 5.0 and c["thin_means_at_most"] == 2
+    assert c["mean_in_flight"] == pytest.approx((20 * 1.0 + 1 * 4.0) / 5.0) and c["thin_tail_s"] == pytest.approx(4.0)
+    assert a["stragglers"][0]["label"] == "s19" and a["stragglers"][0]["longest_span"] == {"name": "generate", "s": 2.0}
+    assert a["idle"]["total_s"] == pytest.approx(1.0) and list(a["idle"]["worst"])[0] == "s19"  # the gap between its two turns
+    assert tv.analyse_lanes([]) == {"concurrency": {}, "stragglers": [], "idle": {}}
 
 
 def test_layerwise_dump_and_compare(tmp_path, monkeypatch):
