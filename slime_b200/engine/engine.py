@@ -58,7 +58,7 @@ class Engine:
         if num_pages is None:
             num_pages = self._pages_from_memory()
         self.num_pages = num_pages
-        self.kv = PagedKVCache(cfg.num_layers, self.weights.hkv, cfg.head_dim, num_pages, self.page_size, self.dtype,
+        self.kv = PagedKVCache(self._num_kv_layers(), self.weights.hkv, cfg.head_dim, num_pages, self.page_size, self.dtype,
                                self.device, enable_prefix_cache=not self.args.disable_radix_cache)  # fmt: skip
         self.runner = ModelRunner(cfg, self.weights, self.kv, self.max_running, self.max_context,
                                   use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
@@ -75,9 +75,13 @@ class Engine:
                       "h2d_bytes": 0, "d2h_bytes": 0, "decode_steps": 0}  # fmt: skip
         self._init_decode_state()
 
+    def _num_kv_layers(self) -> int:
+        """Layers that keep keys and values (delta-net layers keep a recurrent state per decode slot instead)."""
+        return sum(1 for L in self.weights.layers if L["kind"] == "attention")
+
     # ----------------------------------------------------------------- sizing
     def _pages_from_memory(self) -> int:
-        per_page = PagedKVCache.bytes_per_page(self.cfg.num_layers, self.weights.hkv, self.cfg.head_dim, self.page_size, self.dtype)
+        per_page = PagedKVCache.bytes_per_page(self._num_kv_layers(), self.weights.hkv, self.cfg.head_dim, self.page_size, self.dtype)
         if self.args.max_total_tokens:
             return max(8, self.args.max_total_tokens // self.page_size)
         if self.device.type != "cuda":
@@ -180,7 +184,9 @@ class Engine:
                 still_waiting.append(req)
                 continue
             # input log-probs and routed experts need every position computed
-            want_cache = req.logprob_start_len < 0 and not (req.return_routed_experts and self.runner.record_routed)
+            # (a recurrent layer's state at a page boundary is not kept, so hybrid models do not reuse prefixes either)
+            want_cache = (req.logprob_start_len < 0 and not (req.return_routed_experts and self.runner.record_routed)
+                          and not self.runner.has_gdn)  # fmt: skip
             pages, chain = self.kv.allocator.match_prefix(ctx) if want_cache else ([], b"")
             cached = len(pages) * ps
             total_pages = -(-(len(ctx) + 1) // ps)
@@ -238,8 +244,12 @@ class Engine:
                 req.state = ReqState.RUNNING
                 self.prefilling.append(req)
         rows = None if want_all_rows else t(last_rows, torch.long)
+        states = [getattr(req, "gdn_state", None) for req, _ in batch] if self.runner.has_gdn else None
         logits = self.runner.prefill(t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long),
-                                     t(cu_k), max_q, max_k, rows, fresh)  # fmt: skip
+                                     t(cu_k), max_q, max_k, rows, fresh, gdn_states=states)  # fmt: skip
+        if self.runner.has_gdn:
+            for (req, _), st in zip(batch, self.runner.last_gdn_states):
+                req.gdn_state = st
         self.stats["prefill_tokens"] += len(ids)
         routed = self.runner.take_routed()
         if routed is not None:
@@ -278,6 +288,8 @@ class Engine:
     def export_kv(self, req: Request):
         """``(k, v)``, each ``[layers, tokens, kv heads, head dim]``: the cached keys and values of the request's computed
         tokens, copied out of the paged cache (the pages can be released afterwards)."""
+        if self.runner.has_gdn:
+            raise NotImplementedError("prefill / decode disaggregation does not carry the recurrent state of delta-net layers")
         slots = torch.tensor(self._slots(req, 0, req.num_computed), dtype=torch.long, device=self.device)
         k = torch.stack([kl.index_select(0, slots) for kl in self.kv.k])
         v = torch.stack([vl.index_select(0, slots) for vl in self.kv.v])
@@ -358,6 +370,9 @@ class Engine:
         L = r.seq_len
         r.slot, r.decode_from_step, r.harvested = b, self.step_no, self.step_no
         self.slot_req[b] = r
+        if self.runner.has_gdn:
+            self.runner.load_gdn_state(b, r.gdn_state)
+            r.gdn_state = None
         h["active"][b], h["init_mask"][b] = 1, 1
         h["init_ids"][b], h["init_pos"][b], h["init_out_pos"][b] = r.output_ids[-1], L - 1, len(r.output_ids)
         h["top_k"][b], h["temperature"][b] = max(r.sampling.top_k, 0), r.sampling.temperature
@@ -558,6 +573,7 @@ class Engine:
         self._harvest(req, self.processed)
         self._release_slot(req)
         req.routed_experts = []  # the re-prefill computes every position again
+        req.gdn_state = None
         self.kv.allocator.release(req.pages)
         req.pages, req.num_computed, req.committed_pages, req.chain_hash = [], 0, 0, b""
         req.state = ReqState.WAITING

@@ -66,20 +66,25 @@ class EngineWeights:
         self.layers = []
         for i in range(cfg.num_layers):
             kind = cfg.mixer(i)
-            if kind not in ("attention", "general_attention") or cfg.attention_output_gate or cfg.softmax_sinks:
-                raise NotImplementedError(f"the rollout engine runs GQA attention layers; layer {i} of this model is {kind!r}"
-                                          + (" with an output gate" if cfg.attention_output_gate else "")
-                                          + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
+            if kind not in ("attention", "general_attention", "gated_delta_net") or cfg.softmax_sinks:
+                raise NotImplementedError(f"the rollout engine runs GQA attention and gated delta-net layers; layer {i} of this "
+                                          f"model is {kind!r}" + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
             full_norm = cfg.qk_layernorm_full  # one weight per projection (sharded like it) instead of one per head
-            L = {
-                "ln1": e(h), "qkv": mat((self.hq + 2 * self.hkv) * d, h, parts=(self.hq * d, (self.hq + self.hkv) * d)),
-                "o": mat(h, self.hq * d), "ln2": e(h),
-                "qkv_bias": e((self.hq + 2 * self.hkv) * d) if cfg.add_qkv_bias else None,
-                "q_norm": e(self.hq * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
-                "k_norm": e(self.hkv * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
-                "post_attn_ln": e(h) if cfg.post_self_attn_layernorm else None,
-                "post_mlp_ln": e(h) if cfg.post_mlp_layernorm else None,
-            }  # fmt: skip
+            if kind == "gated_delta_net":
+                # linear-attention layer: replicated over tensor-parallel ranks (every rank computes all of it)
+                kd, vd = cfg.linear_num_key_heads * cfg.linear_key_head_dim, cfg.linear_num_value_heads * cfg.linear_value_head_dim
+                hv = cfg.linear_num_value_heads
+                f32 = lambda *sh: torch.zeros(*sh, dtype=torch.float32, device=device)  # noqa: E731
+                L = {"kind": "gdn", "ln1": e(h), "ln2": e(h), "post_attn_ln": None, "post_mlp_ln": None,
+                     "gdn_conv": e(2 * kd + vd, cfg.linear_conv_kernel_dim), "gdn_dt_bias": f32(hv), "gdn_A_log": f32(hv),
+                     "gdn_norm": e(cfg.linear_value_head_dim), "gdn_out": e(h, vd)}  # fmt: skip
+                if "qwen3next" in (cfg.model_arch or "").lower().replace("_", ""):
+                    L.update(gdn_qkvz=e(2 * kd + 2 * vd, h), gdn_ba=e(2 * hv, h))
+                else:
+                    L.update(gdn_qkv=e(2 * kd + vd, h), gdn_z=e(vd, h), gdn_b=e(hv, h), gdn_a=e(hv, h))
+            else:
+                L = self._attention_buffers(e, mat, h, d, full_norm)
+            L.setdefault("kind", "attention")
             if cfg.is_moe_layer(i):
                 el = self.experts_local
                 fe = cfg.moe_ffn_hidden_size
@@ -95,6 +100,21 @@ class EngineWeights:
                 L.update(gate_up=mat(2 * self.f, h, parts=(self.f,)), down=mat(h, self.f))
             self.layers.append(L)
         self.version = "default"
+
+    def _attention_buffers(self, e, mat, h, d, full_norm):
+        cfg = self.cfg
+        L = {
+            "ln1": e(h), "qkv": mat((self.hq + 2 * self.hkv) * d, h, parts=(self.hq * d, (self.hq + self.hkv) * d)),
+            "o": mat(h, self.hq * d), "ln2": e(h),
+            "qkv_bias": e((self.hq + 2 * self.hkv) * d) if cfg.add_qkv_bias else None,
+            "q_norm": e(self.hq * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
+            "k_norm": e(self.hkv * d if full_norm else d) if (cfg.qk_layernorm or full_norm) else None,
+            "post_attn_ln": e(h) if cfg.post_self_attn_layernorm else None,
+            "post_mlp_ln": e(h) if cfg.post_mlp_layernorm else None,
+        }  # fmt: skip
+        if cfg.attention_output_gate:
+            L["gate"] = e(self.hq * d, h)  # sigmoid gate of the attention output, one row per query channel
+        return L
 
     def num_bytes(self) -> int:
         seen, total = set(), 0
@@ -137,8 +157,11 @@ class EngineWeights:
                     t[self.rank * self.vocab_local : (self.rank + 1) * self.vocab_local]
                 )
             return True
+        from slime_b200.weight_sync import convert
+
+        plus1 = 1.0 if convert._zero_centred(cfg) else 0.0  # Qwen3-Next / Qwen3.5 store their RMSNorm weights minus one
         if name == "model.norm.weight":
-            self.final_norm.copy_(t)
+            self.final_norm.copy_(t + plus1)
             return True
         m = _LAYER_RE.match(name)
         if m is None:
@@ -149,15 +172,35 @@ class EngineWeights:
         sub = m.group(2)
         hq, hkv = self.hq, self.hkv
         q_rows, kv_rows = hq * d, hkv * d
+        if sub.startswith("linear_attn."):
+            if L["kind"] != "gdn":
+                return False
+            inner = sub[len("linear_attn.") :]
+            table = {"in_proj_qkvz.weight": "gdn_qkvz", "in_proj_ba.weight": "gdn_ba", "in_proj_qkv.weight": "gdn_qkv",
+                     "in_proj_z.weight": "gdn_z", "in_proj_b.weight": "gdn_b", "in_proj_a.weight": "gdn_a", "conv1d.weight": "gdn_conv",
+                     "dt_bias": "gdn_dt_bias", "A_log": "gdn_A_log", "norm.weight": "gdn_norm", "out_proj.weight": "gdn_out"}  # fmt: skip
+            key = table.get(inner)
+            if key is None or key not in L:
+                return False
+            src = raw.to(self.device, L[key].dtype)
+            L[key].copy_(src.squeeze(1) if inner == "conv1d.weight" and src.dim() == 3 else src)
+            return True
+        if sub == "self_attn.q_proj.weight" and cfg.attention_output_gate and L["kind"] == "attention":
+            # checkpoint rows are per head (query, gate): split them into the fused projection's q rows and the gate matrix
+            x = t.view(cfg.num_attention_heads, 2 * d, -1)
+            q_full, g_full = x[:, :d].reshape(-1, x.shape[-1]), x[:, d:].reshape(-1, x.shape[-1])
+            L["qkv"][: hq * d].copy_(self._rows(q_full, hq * d))
+            L["gate"].copy_(self._rows(g_full, hq * d))
+            return True
         vectors = {
-            "input_layernorm.weight": lambda: L["ln1"].copy_(t),
-            "post_attention_layernorm.weight": lambda: L["ln2"].copy_(t),
+            "input_layernorm.weight": lambda: L["ln1"].copy_(t + plus1),
+            "post_attention_layernorm.weight": lambda: L["ln2"].copy_(t + plus1),
             "self_attn.q_proj.bias": lambda: L["qkv_bias"][:q_rows].copy_(self._rows(t, q_rows)),
             "self_attn.k_proj.bias": lambda: L["qkv_bias"][q_rows : q_rows + kv_rows].copy_(self._rows(t, kv_rows)),
             "self_attn.v_proj.bias": lambda: L["qkv_bias"][q_rows + kv_rows :].copy_(self._rows(t, kv_rows)),
             "self_attn.qkv_proj.bias": lambda: L["qkv_bias"].copy_(t),
-            "self_attn.q_norm.weight": lambda: L["q_norm"].copy_(self._rows(t, q_rows) if cfg.qk_layernorm_full else t),
-            "self_attn.k_norm.weight": lambda: L["k_norm"].copy_(self._rows(t, kv_rows) if cfg.qk_layernorm_full else t),
+            "self_attn.q_norm.weight": lambda: L["q_norm"].copy_((self._rows(t, q_rows) if cfg.qk_layernorm_full else t) + plus1),
+            "self_attn.k_norm.weight": lambda: L["k_norm"].copy_((self._rows(t, kv_rows) if cfg.qk_layernorm_full else t) + plus1),
             "mlp.gate.weight": lambda: L["router"].copy_(t),
             "post_self_attn_layernorm.weight": lambda: L["post_attn_ln"].copy_(t),
             "post_mlp_layernorm.weight": lambda: L["post_mlp_ln"].copy_(t),
@@ -279,7 +322,8 @@ class ModelRunner:
         self.device = weights.device
         self.max_batch, self.max_context = max_batch, max_context
         self.max_pages_per_req = -(-max_context // kv.page_size)
-        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        # head dims other than 64 / 128 fall back to attention written with plain ops, which reads lengths on the host
+        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda" and cfg.head_dim in (64, 128)
         self.tp_group = tp_group
         # Row-parallel projections (attention output, MLP down) leave their result in fp32 when no cross-rank sum
         # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
@@ -296,6 +340,20 @@ class ModelRunner:
                     self._fused_tp = fused_tp.FusedAllReduceNorm(tp_group, max_batch, cfg.hidden_size, self.device)
                 except Exception as e:  # noqa: BLE001
                     logger.warning("fused tensor-parallel all-reduce unavailable (%r): using NCCL", e)
+        # KV slabs exist for the attention layers only; gated delta-net layers keep a recurrent state per decode slot
+        self.kv_of, n_attn = [], 0
+        for L in weights.layers:
+            self.kv_of.append(n_attn if L["kind"] == "attention" else None)
+            n_attn += L["kind"] == "attention"
+        self.has_gdn = any(L["kind"] == "gdn" for L in weights.layers)
+        self.gdn_S, self.gdn_conv, self.last_gdn_states = {}, {}, None
+        if self.has_gdn:
+            hv, dk, dv = cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+            C, K = 2 * cfg.linear_num_key_heads * dk + hv * dv, cfg.linear_conv_kernel_dim
+            for li, L in enumerate(weights.layers):
+                if L["kind"] == "gdn":
+                    self.gdn_S[li] = torch.zeros(max_batch, hv, dk, dv, dtype=torch.float32, device=self.device)
+                    self.gdn_conv[li] = torch.zeros(max_batch, K - 1, C, dtype=weights.dtype, device=self.device)
         self._composed_attention = cfg.rotary_percent < 1.0 or cfg.rotary_interleaved or cfg.qk_layernorm_full
         rot = int(cfg.head_dim * cfg.rotary_percent) // 2 * 2
         self.rope = ops.rope_cos_sin(max_context + 1, rot, cfg.rotary_base, device=self.device,
@@ -413,7 +471,7 @@ class ModelRunner:
         cfg = self.cfg
         qkv = _linear(normed, L["qkv"], bias=L["qkv_bias"])
         if not self._composed_attention:
-            return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[li], self.kv.v[li], self.w.hq, self.w.hkv,
+            return ops.rope_kv_write(qkv, positions, self.rope, slots, self.kv.k[self.kv_of[li]], self.kv.v[self.kv_of[li]], self.w.hq, self.w.hkv,
                                      cfg.head_dim, L["q_norm"], L["k_norm"], cfg.norm_epsilon)  # fmt: skip
         # attention variants the fused kernel does not cover (partial / interleaved rotary, RMSNorm over all heads):
         # the same steps as separate ops, then the ordinary cache write
@@ -432,7 +490,7 @@ class ModelRunner:
             q = mixers.apply_rotary(q.view(T, hq, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
             k = mixers.apply_rotary(k.view(T, hkv, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
         k, v = k.contiguous(), v.contiguous()
-        ops.kv_write(k, v, slots, self.kv.k[li], self.kv.v[li])
+        ops.kv_write(k, v, slots, self.kv.k[self.kv_of[li]], self.kv.v[self.kv_of[li]])
         return torch.cat([q, k, v], dim=-1)
 
     def _full_norm(self, t, w):
@@ -444,37 +502,127 @@ class ModelRunner:
             ss = self._tp_reduce(ss)
         return (f * torch.rsqrt(ss / n + self.cfg.norm_epsilon) * w.float()).to(t.dtype)
 
+    # ------------------------------------------------------------ gated delta-net layers
+    def _gdn_project(self, L, x):
+        """Input projections of a delta-net layer -> (pre-convolution q|k|v channels [T, C], z [T, Hv, Dv], b, a [T, Hv])."""
+        cfg, T = self.cfg, x.shape[0]
+        hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        if "gdn_qkvz" in L:  # rows grouped per key head: q, k, then that head's value and gate heads
+            r = hv // hk
+            qkvz = ops.gemm(x, L["gdn_qkvz"]).view(T, hk, 2 * dk + 2 * r * dv)
+            q, k, v, z = qkvz.split([dk, dk, r * dv, r * dv], dim=-1)
+            b, a = ops.gemm(x, L["gdn_ba"]).view(T, hk, 2 * r).split([r, r], dim=-1)
+            mixed = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], dim=-1)
+            return mixed, z.reshape(T, hv, dv), b.reshape(T, hv), a.reshape(T, hv)
+        return ops.gemm(x, L["gdn_qkv"]), ops.gemm(x, L["gdn_z"]).view(T, hv, dv), ops.gemm(x, L["gdn_b"]), ops.gemm(x, L["gdn_a"])
+
+    def _gdn_finish(self, L, o, z):
+        """Gated RMSNorm of the delta-rule output and the output projection."""
+        from slime_b200.models import mixers
+
+        T = o.shape[0]
+        y = mixers._rms(o, L["gdn_norm"], self.cfg.norm_epsilon).float() * torch.nn.functional.silu(z.float())
+        return ops.gemm(y.to(self.w.dtype).reshape(T, -1), L["gdn_out"])
+
+    def _gdn_gates(self, L, b, a):
+        beta = torch.sigmoid(b.float())
+        g = -L["gdn_A_log"].float().exp() * torch.nn.functional.softplus(a.float() + L["gdn_dt_bias"].float())
+        return g, beta
+
+    def _gdn_heads(self, mixed):
+        cfg, T = self.cfg, mixed.shape[0]
+        hk, hv, dk, dv = cfg.linear_num_key_heads, cfg.linear_num_value_heads, cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        q, k, v = mixed.split([hk * dk, hk * dk, hv * dv], dim=-1)
+        q, k, v = q.view(T, hk, dk), k.view(T, hk, dk), v.view(T, hv, dv)
+        if hv // hk > 1:
+            q, k = q.repeat_interleave(hv // hk, dim=1), k.repeat_interleave(hv // hk, dim=1)
+        return q, k, v
+
+    def _gdn_prefill(self, L, li, x, positions_in_call, cu_q, states_in, states_out):
+        """Delta-net layer over the new tokens of every request; ``states_in[i][li]`` = (state, convolution history) the
+        request arrived with (None at its first chunk); the states after the chunk go to ``states_out[i][li]``."""
+        from slime_b200.models import mixers
+
+        K = self.cfg.linear_conv_kernel_dim
+        mixed_in, z, b, a = self._gdn_project(L, x)
+        n_req = cu_q.numel() - 1
+        S_in = [None if states_in is None or states_in[i] is None else states_in[i][li][0] for i in range(n_req)]
+        h_in = [None if states_in is None or states_in[i] is None else states_in[i][li][1] for i in range(n_req)]
+        mixed = mixers.causal_short_conv(mixed_in, L["gdn_conv"], positions_in_call, history=h_in if any(h is not None for h in h_in) else None,
+                                         cu_seqlens=cu_q)  # fmt: skip
+        q, k, v = self._gdn_heads(mixed)
+        g, beta = self._gdn_gates(L, b, a)
+        o, finals = mixers.gated_delta_rule_chunked(q, k, v, g, beta, cu_q, initial_states=S_in, return_final_states=True)
+        bounds = cu_q.tolist()
+        for i, (lo, hi) in enumerate(zip(bounds[:-1], bounds[1:])):
+            prev = h_in[i] if h_in[i] is not None else mixed_in.new_zeros(K - 1, mixed_in.shape[1])
+            hist = torch.cat([prev.to(mixed_in.dtype), mixed_in[lo:hi]])[-(K - 1):]
+            states_out[i][li] = (finals[i], hist)
+        return self._gdn_finish(L, o.to(self.w.dtype), z)
+
+    def _gdn_decode(self, L, li, x, n):
+        from slime_b200.models import mixers
+
+        mixed_in, z, b, a = self._gdn_project(L, x)
+        mixed = mixers.short_conv_step(mixed_in, L["gdn_conv"], self.gdn_conv[li][:n])
+        q, k, v = self._gdn_heads(mixed)
+        g, beta = self._gdn_gates(L, b, a)
+        o = mixers.gated_delta_rule_step(q, k, v, g, beta, self.gdn_S[li][:n])
+        return self._gdn_finish(L, o.to(self.w.dtype), z)
+
+    def load_gdn_state(self, slot: int, states: dict | None):
+        """Put a request's recurrent states (from its prefill) into decode slot ``slot``."""
+        for li in self.gdn_S:
+            S, hist = states[li]
+            self.gdn_S[li][slot].copy_(S)
+            self.gdn_conv[li][slot].copy_(hist)
+
     def _post_norm(self, x, w):
         """GLM-4 sandwich norm: the sub-layer's output is normalised before it joins the residual stream."""
         return x if w is None else ops.rmsnorm(x, w, self.cfg.norm_epsilon)[0]
 
     # --------------------------------------------------------------------- prefill
     @torch.no_grad()
-    def prefill(self, ids, positions, slots, cu_q, kv_gather_slots, cu_k, max_q, max_k, last_rows, fresh: bool):
+    def prefill(self, ids, positions, slots, cu_q, kv_gather_slots, cu_k, max_q, max_k, last_rows, fresh: bool, gdn_states=None):
         """Extend pass over packed new tokens.
 
         ids/positions/slots: [T] for the new tokens; ``cu_q`` their per-request boundaries.
         ``kv_gather_slots``/``cu_k``: cache slots of every context token (cached prefix + new) per
         request, used when some context is already cached (``fresh`` False). Returns logits
         ``[len(last_rows), V/tp]`` fp32 for the requested rows and, when ``last_rows`` is None, all rows.
+        Models with delta-net layers: ``gdn_states[i]`` is request i's recurrent state from its earlier chunks (or
+        None); the states after this pass are left in ``last_gdn_states``.
         """
         cfg, w, d = self.cfg, self.w, self.cfg.head_dim
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
         res = None
         T = ids.numel()
+        if self.has_gdn:
+            from slime_b200.models.gpt import positions_from_cu_seqlens
+
+            in_call = positions_from_cu_seqlens(cu_q, T)  # position inside this pass (a later chunk starts at 0 again)
+            self.last_gdn_states = [dict() for _ in range(cu_q.numel() - 1)]
         for li, L in enumerate(w.layers):
             normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
+            if L["kind"] == "gdn":
+                x = self._gdn_prefill(L, li, normed, in_call, cu_q, gdn_states, self.last_gdn_states)
+                normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
+                x = self._mlp(L, normed)
+                continue
             qkv = self._qkv(L, normed, positions, slots, li)
             q3 = qkv.view(T, w.hq + 2 * w.hkv, d)
             q, k, v = q3[:, : w.hq], q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
             if fresh:
                 ctx = ops.varlen_attention(q, k, v, cu_q, max_q, self.scale)
             else:
-                k_all = self.kv.k[li].index_select(0, kv_gather_slots)
-                v_all = self.kv.v[li].index_select(0, kv_gather_slots)
+                k_all = self.kv.k[self.kv_of[li]].index_select(0, kv_gather_slots)
+                v_all = self.kv.v[self.kv_of[li]].index_select(0, kv_gather_slots)
                 ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale)
-            x = self._tp_reduce(_linear(ctx.reshape(T, -1), L["o"], out_dtype=self._proj_dtype))
+            ctx = ctx.reshape(T, -1)
+            if "gate" in L:
+                ctx = ctx * torch.sigmoid(ops.gemm(normed, L["gate"]).float()).to(ctx.dtype)
+            x = self._tp_reduce(_linear(ctx, L["o"], out_dtype=self._proj_dtype))
             x = self._post_norm(x, L["post_attn_ln"])
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._post_norm(self._mlp(L, normed), L["post_mlp_ln"])
@@ -566,10 +714,16 @@ class ModelRunner:
             self._fused_tp.begin_forward()
         normed, res = ops.rmsnorm(x, w.layers[0]["ln1"], cfg.norm_epsilon, None)
         for li, L in enumerate(w.layers):
-            qkv = self._qkv(L, normed, pos, slots, li)
-            q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
-            ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[li], self.kv.v[li], bt, seq_lens, ps, self.scale)
-            normed, res = self._row_parallel_norm(ctx.reshape(n, -1), L["o"], L["ln2"], res, n, post=L["post_attn_ln"])
+            if L["kind"] == "gdn":
+                normed, res = ops.rmsnorm(self._gdn_decode(L, li, normed, n), L["ln2"], cfg.norm_epsilon, res)
+            else:
+                qkv = self._qkv(L, normed, pos, slots, li)
+                q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
+                ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[self.kv_of[li]], self.kv.v[self.kv_of[li]], bt, seq_lens, ps,
+                                                 self.scale).reshape(n, -1)  # fmt: skip
+                if "gate" in L:
+                    ctx = ctx * torch.sigmoid(ops.gemm(normed, L["gate"]).float()).to(ctx.dtype)
+                normed, res = self._row_parallel_norm(ctx, L["o"], L["ln2"], res, n, post=L["post_attn_ln"])
             # the norm that follows the MLP is the next layer's input norm (or the final norm)
             next_ln = w.layers[li + 1]["ln1"] if li + 1 < len(w.layers) else w.final_norm
             if "gate_up" in L:

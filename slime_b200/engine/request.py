@@ -62,6 +62,7 @@ class Request:
     stream: bool = False
     prefill_only: bool = False  # prefill / decode disaggregation: stop after the first token and export the prompt's KV
     kv_export: Any = None  # (k, v) [layers, tokens, kv heads, head dim] of a finished prefill-only request
+    gdn_state: Any = None  # {layer: (recurrent state, convolution history)} between prefill chunks, until a decode slot takes it
     extra_meta: dict = field(default_factory=dict)  # added verbatim to meta_info (e.g. the pd_* transfer figures)
     # ---- engine state ----
     state: ReqState = ReqState.WAITING

@@ -219,22 +219,25 @@ def gated_delta_rule_recurrent(q, k, v, g, beta, cu_seqlens):
     return out
 
 
-def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = 64):
+def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = 64, initial_states=None, return_final_states: bool = False):
     """The same function, ``chunk`` tokens at a time. Inside a chunk with cumulative log decay ``G`` and incoming state
     ``S0`` the updates ``delta`` solve the unit lower-triangular system
 
         (I + A) delta = beta * (V - exp(G) K S0),   A[i, j] = beta_i exp(G_i - G_j) <k_i, k_j>  (j < i),
 
     then ``O = exp(G) Q S0 + (tril(exp(G_i - G_j)) * Q K^T) delta`` and ``S <- exp(G_C) S0 + (exp(G_C - G) K)^T delta``.
-    Everything is matmuls and one triangular solve per chunk, all differentiable."""
+    Everything is matmuls and one triangular solve per chunk, all differentiable. ``initial_states``: one ``[H, Dk, Dv]``
+    tensor (or None) per sequence to start from; ``return_final_states`` also returns the state after each sequence's last
+    token (what a decode step continues from)."""
     Dk = q.shape[-1]
     qf, kf = _l2norm(q.float()) * Dk**-0.5, _l2norm(k.float())
     vf, gf, bf = v.float(), g.float(), beta.float()
-    outs = []
+    outs, finals = [], []
     cu = cu_seqlens.tolist()
-    for a, b in zip(cu[:-1], cu[1:]):
+    for si, (a, b) in enumerate(zip(cu[:-1], cu[1:])):
         n = b - a
         if n <= 0:
+            finals.append(None if initial_states is None else initial_states[si])
             continue
         pad = (-n) % chunk
         # [H, n_chunks, C, *]
@@ -250,6 +253,8 @@ def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = 64):
         QK = (Q @ K.transpose(-1, -2)) * decay
         eG = G.exp()[..., None]
         S = torch.zeros(q.shape[1], Dk, v.shape[-1], dtype=torch.float32, device=q.device)
+        if initial_states is not None and initial_states[si] is not None:
+            S = initial_states[si].float()
         seq_out = []
         for c in range(Q.shape[1]):
             rhs = B[:, c, :, None] * (V[:, c] - eG[:, c] * (K[:, c] @ S))
@@ -259,19 +264,52 @@ def gated_delta_rule_chunked(q, k, v, g, beta, cu_seqlens, chunk: int = 64):
             S = last.exp()[:, None, None] * S + ((last[:, None] - G[:, c]).exp()[..., None] * K[:, c]).transpose(-1, -2) @ delta
         o = torch.stack(seq_out, 1).reshape(q.shape[1], -1, v.shape[-1])[:, :n].transpose(0, 1)
         outs.append(o)
-    return torch.cat(outs) if outs else vf[:0]
+        finals.append(S)  # padded tokens (g = 0, beta = 0) left it untouched
+    out = torch.cat(outs) if outs else vf[:0]
+    return (out, finals) if return_final_states else out
 
 
-def causal_short_conv(x, weight, positions, activation=True):
+def gated_delta_rule_step(q, k, v, g, beta, S):
+    """One token per row: q / k [B, H, Dk], v [B, H, Dv], g / beta [B, H], state ``S`` [B, H, Dk, Dv] (updated in place).
+    Returns the outputs [B, H, Dv]."""
+    q, k = _l2norm(q.float()) * q.shape[-1] ** -0.5, _l2norm(k.float())
+    S.mul_(g.float().exp()[:, :, None, None])
+    delta = (v.float() - torch.einsum("bhkv,bhk->bhv", S, k)) * beta.float()[:, :, None]
+    S.add_(k[:, :, :, None] * delta[:, :, None, :])
+    return torch.einsum("bhkv,bhk->bhv", S, q)
+
+
+def causal_short_conv(x, weight, positions, activation=True, history=None, cu_seqlens=None):
     """Depthwise causal convolution over time with zero history at every sequence start. x [T, C], weight [C, K]
-    (tap K-1 multiplies the current token), ``positions`` [T] the index of each token inside its sequence."""
+    (tap K-1 multiplies the current token), ``positions`` [T] the index of each token inside its sequence (of THIS call:
+    a continued sequence starts at 0 again and brings ``history``). ``history``: per sequence of ``cu_seqlens`` a
+    ``[K-1, C]`` tensor of the inputs that preceded this call (or None), oldest first."""
     K = weight.shape[1]
     acc = x.float() * weight[:, K - 1].float()
     pos = positions.reshape(-1)
     for s in range(1, K):
         shifted = F.pad(x.float(), (0, 0, s, 0))[: x.shape[0]]
         acc = acc + torch.where((pos >= s)[:, None], shifted, torch.zeros_like(shifted)) * weight[:, K - 1 - s].float()
+    if history is not None:
+        add = torch.zeros_like(acc)
+        for si, (a, b) in enumerate(zip(cu_seqlens.tolist()[:-1], cu_seqlens.tolist()[1:])):
+            h = history[si]
+            if h is None or b <= a:
+                continue
+            hf = h.float()
+            for t in range(min(K - 1, b - a)):  # token t of the call still sees K-1-t history rows
+                for s in range(t + 1, K):
+                    add[a + t] += hf[K - 1 - (s - t)] * weight[:, K - 1 - s].float()
+        acc = acc + add
     return (F.silu(acc) if activation else acc).to(x.dtype)
+
+
+def short_conv_step(x, weight, state):
+    """One token per row: x [B, C], ``state`` [B, K-1, C] the previous inputs (oldest first, updated in place)."""
+    window = torch.cat([state.float(), x.float()[:, None, :]], dim=1)  # [B, K, C]
+    y = (window * weight.float().t()[None]).sum(1)
+    state.copy_(window[:, 1:].to(state.dtype))
+    return F.silu(y).to(x.dtype)
 
 
 class GatedDeltaNet(nn.Module):

@@ -460,7 +460,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if not _is_cuda(q):
+    if not _is_cuda(q) or D not in (64, 128):
+        # the decode kernels cover head dims 64 and 128; other widths (256: Qwen3-Next / Qwen3.5) take the plain form
         return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale)
     caller_splits = splits
     if splits is None:

@@ -26,6 +26,13 @@ FAMILIES = {
     "minimax_m2": dict(qk_layernorm_full=True, rotary_percent=0.5, num_experts=4, moe_ffn_hidden_size=32, moe_router_topk=2,
                        moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True, moe_router_pre_softmax=True,
                        model_arch="MiniMaxM2ForCausalLM"),
+    "qwen3_next": dict(num_layers=4, full_attention_interval=4, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=8,
+                       linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25, num_experts=4,
+                       moe_ffn_hidden_size=32, moe_router_topk=2, moe_shared_expert_intermediate_size=32, moe_shared_expert_gate=True,
+                       model_arch="Qwen3NextForCausalLM"),
+    "qwen3_5": dict(num_layers=4, full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=8,
+                    linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25,
+                    model_arch="Qwen3_5ForCausalLM"),
     "deepseek_routing": dict(qk_layernorm=True, num_experts=8, moe_ffn_hidden_size=32, moe_router_topk=2, moe_router_num_groups=4,
                              moe_router_group_topk=2, moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
                              moe_shared_expert_intermediate_size=64, model_arch="Qwen3MoeForCausalLM"),
@@ -93,3 +100,30 @@ def test_hf_checkpoint_round_trip_keeps_the_router_bias(tmp_path):
     assert not missing, missing
     for (n, x), (_, y) in zip(list(a.named_parameters()) + list(a.named_buffers()), list(b.named_parameters()) + list(b.named_buffers())):
         assert torch.equal(x, y), n
+
+
+def test_hybrid_engine_carries_recurrent_state_through_chunked_prefill_and_batched_decode():
+    """Qwen3.5-style hybrid: prompts prefilled in small chunks (the delta-net state and the convolution history travel from
+    chunk to chunk), then decoded together in one batch; every request's log-probs equal the trainer's."""
+    torch.manual_seed(0)
+    cfg = ModelConfig(**{**BASE, **FAMILIES["qwen3_5"]})
+    model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=3)
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=4, context_length=64, disable_cuda_graph=True, chunked_prefill_size=5,
+                               max_prefill_tokens=7), device="cpu", num_pages=64)  # fmt: skip
+    hf = [x for n, p in model.named_parameters() for x in convert.convert_to_hf(cfg, n, p.detach())]
+    assert not e.weights.load_weights(hf)
+    assert e.kv.num_layers == 2 and e.runner.has_gdn  # two of the four layers keep keys and values
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (13, 3, 9)]
+    reqs = e.generate(prompts, [dict(max_new_tokens=5 + i, temperature=0, ignore_eos=True) for i in range(3)])
+    assert e.stats["steps"] > 6  # the prompts really went through several prefill passes
+    for p, r in zip(prompts, reqs):
+        full = p + r.output_ids
+        with torch.no_grad():
+            lp = model(torch.tensor(full))[0].log_softmax(-1)
+        want = [float(lp[len(p) - 1 + i, t]) for i, t in enumerate(r.output_ids)]
+        assert np.abs(np.array(r.output_logprobs) - np.array(want)).max() < 2e-4
+        assert r.num_cached_tokens == 0  # hybrids do not reuse prefixes
+    # the same prompt again: still no prefix reuse, same answer
+    again = e.generate([prompts[0]], [dict(max_new_tokens=5, temperature=0, ignore_eos=True)])[0]
+    assert again.output_ids == reqs[0].output_ids and again.num_cached_tokens == 0

@@ -381,3 +381,35 @@ def test_yarn_frequencies_keep_fast_dimensions_and_interpolate_slow_ones():
     layer = mixers.MLASelfAttention(cfg, 0, torch.float32, "cpu", False)
     assert abs(layer.scale - 16**-0.5 * reference.yarn_mscale(40.0, 1.0) ** 2) < 1e-9
     assert torch.allclose(layer._table("cpu", 8)[:8], reference.rope_cos_sin_yarn(4096, 8, 1e4, 40.0, 4096, mscale=1.0, mscale_all_dim=1.0)[:8])
+
+
+def test_delta_rule_and_conv_continue_from_saved_state():
+    """Prefill in two pieces, and decode one token at a time, equal one pass over the whole sequence."""
+    torch.manual_seed(0)
+    T, H, Dk, Dv, C, K = 23, 2, 4, 6, 5, 4
+    q, k, v = torch.randn(T, H, Dk), torch.randn(T, H, Dk), torch.randn(T, H, Dv)
+    g, beta = -torch.rand(T, H) * 0.4, torch.rand(T, H)
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    whole, final = mixers.gated_delta_rule_chunked(q, k, v, g, beta, cu, chunk=8, return_final_states=True)
+    cut = 13
+    first, st = mixers.gated_delta_rule_chunked(q[:cut], k[:cut], v[:cut], g[:cut], beta[:cut], torch.tensor([0, cut], dtype=torch.int32),
+                                                chunk=8, return_final_states=True)  # fmt: skip
+    second, st2 = mixers.gated_delta_rule_chunked(q[cut:], k[cut:], v[cut:], g[cut:], beta[cut:], torch.tensor([0, T - cut], dtype=torch.int32),
+                                                  chunk=8, initial_states=st, return_final_states=True)  # fmt: skip
+    assert torch.allclose(torch.cat([first, second]), whole, atol=1e-5) and torch.allclose(st2[0], final[0], atol=1e-5)
+    S = st[0].clone()[None]
+    for t in range(cut, T):
+        o = mixers.gated_delta_rule_step(q[t][None], k[t][None], v[t][None], g[t][None], beta[t][None], S)
+        assert torch.allclose(o[0], whole[t], atol=1e-5), t
+    assert torch.allclose(S[0], final[0], atol=1e-5)
+    # convolution: history of the last K-1 inputs
+    x, w = torch.randn(T, C), torch.randn(C, K)
+    pos = torch.arange(T, dtype=torch.int32)
+    ref = mixers.causal_short_conv(x, w, pos)
+    hist = x[cut - (K - 1) : cut]
+    tail = mixers.causal_short_conv(x[cut:], w, torch.arange(T - cut, dtype=torch.int32), history=[hist],
+                                    cu_seqlens=torch.tensor([0, T - cut], dtype=torch.int32))  # fmt: skip
+    assert torch.allclose(tail, ref[cut:], atol=1e-6)
+    state = hist.clone()[None]
+    for t in range(cut, T):
+        assert torch.allclose(mixers.short_conv_step(x[t][None], w, state)[0], ref[t], atol=1e-6), t
