@@ -130,7 +130,7 @@ class EngineWeights:
         yield self.final_norm
         for L in self.layers:
             for v in L.values():
-                if v is None:
+                if v is None or isinstance(v, str):  # absent buffers, and the layer's kind tag
                     continue
                 if hasattr(v, "tensors"):  # a quantised matrix: its bytes and its scales
                     yield from v.tensors()
@@ -283,6 +283,9 @@ class EngineWeights:
 
         g = torch.Generator(device=self.device).manual_seed(seed)
         quantised = [v for L in self.layers for v in L.values() if isinstance(v, Fp8Weight)]
+        for L in self.layers:  # the decay parameter of delta-net layers must start in its valid range
+            if "gdn_A_log" in L:
+                L["gdn_A_log"].copy_(torch.empty_like(L["gdn_A_log"]).uniform_(1e-3, 16.0, generator=g).log())
         skip = {t.data_ptr() for v in quantised for t in v.tensors()}
         for t in self.tensors():
             if t.data_ptr() in skip:
