@@ -58,8 +58,9 @@ class Engine:
         if num_pages is None:
             num_pages = self._pages_from_memory()
         self.num_pages = num_pages
-        self.kv = PagedKVCache(self._num_kv_layers(), self.weights.hkv, cfg.head_dim, num_pages, self.page_size, self.dtype,
-                               self.device, enable_prefix_cache=not self.args.disable_radix_cache)  # fmt: skip
+        kv_heads, kv_dim, v_dim = self._kv_geometry()
+        self.kv = PagedKVCache(self._num_kv_layers(), kv_heads, kv_dim, num_pages, self.page_size, self.dtype,
+                               self.device, enable_prefix_cache=not self.args.disable_radix_cache, v_head_dim=v_dim)  # fmt: skip
         self.runner = ModelRunner(cfg, self.weights, self.kv, self.max_running, self.max_context,
                                   use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
         self.runner._alloc_static()
@@ -75,13 +76,22 @@ class Engine:
                       "h2d_bytes": 0, "d2h_bytes": 0, "decode_steps": 0}  # fmt: skip
         self._init_decode_state()
 
+    def _kv_geometry(self):
+        """(heads, key width, value width) of one cached token: latent attention caches a single vector per token (the
+        compressed key/value plus the shared rotary key) and no separate values."""
+        c = self.cfg
+        if c.multi_latent_attention:
+            return 1, c.kv_lora_rank + c.qk_pos_emb_head_dim, 0
+        return self.weights.hkv, c.head_dim, None
+
     def _num_kv_layers(self) -> int:
         """Layers that keep keys and values (delta-net layers keep a recurrent state per decode slot instead)."""
-        return sum(1 for L in self.weights.layers if L["kind"] == "attention")
+        return sum(1 for L in self.weights.layers if L["kind"] in ("attention", "mla"))
 
     # ----------------------------------------------------------------- sizing
     def _pages_from_memory(self) -> int:
-        per_page = PagedKVCache.bytes_per_page(self._num_kv_layers(), self.weights.hkv, self.cfg.head_dim, self.page_size, self.dtype)
+        kv_heads, kv_dim, v_dim = self._kv_geometry()
+        per_page = PagedKVCache.bytes_per_page(self._num_kv_layers(), kv_heads, kv_dim, self.page_size, self.dtype, v_head_dim=v_dim)
         if self.args.max_total_tokens:
             return max(8, self.args.max_total_tokens // self.page_size)
         if self.device.type != "cuda":

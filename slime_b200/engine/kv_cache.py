@@ -131,8 +131,12 @@ class PageAllocator:
 class PagedKVCache:
     """Device tensors + allocator. Memory tag ``kv_cache``: released / re-created as a whole."""
 
-    def __init__(self, num_layers, num_kv_heads, head_dim, num_pages, page_size, dtype, device, enable_prefix_cache=True):
+    def __init__(self, num_layers, num_kv_heads, head_dim, num_pages, page_size, dtype, device, enable_prefix_cache=True,
+                 v_head_dim: int | None = None):  # fmt: skip
+        """``v_head_dim``: width of the value slab when it differs from the key slab's (0 for latent attention, whose
+        single cached vector per token serves as key and value)."""
         self.num_layers, self.hkv, self.d = num_layers, num_kv_heads, head_dim
+        self.dv = head_dim if v_head_dim is None else v_head_dim
         self.page_size, self.num_pages, self.dtype, self.device = page_size, num_pages, dtype, device
         self.allocator = PageAllocator(num_pages, page_size, enable_prefix_cache)
         self.k: list[torch.Tensor] = []
@@ -145,7 +149,7 @@ class PagedKVCache:
         slots = self.num_pages * self.page_size
         # one slab per kind so a layer's cache is a contiguous view
         self._k_slab = torch.zeros(self.num_layers, slots, self.hkv, self.d, dtype=self.dtype, device=self.device)
-        self._v_slab = torch.zeros(self.num_layers, slots, self.hkv, self.d, dtype=self.dtype, device=self.device)
+        self._v_slab = torch.zeros(self.num_layers, slots, self.hkv, self.dv, dtype=self.dtype, device=self.device)
         self.k = [self._k_slab[i] for i in range(self.num_layers)]
         self.v = [self._v_slab[i] for i in range(self.num_layers)]
 
@@ -157,5 +161,6 @@ class PagedKVCache:
             torch.cuda.empty_cache()
 
     @staticmethod
-    def bytes_per_page(num_layers, num_kv_heads, head_dim, page_size, dtype=torch.bfloat16) -> int:
-        return 2 * num_layers * page_size * num_kv_heads * head_dim * torch.empty(0, dtype=dtype).element_size()
+    def bytes_per_page(num_layers, num_kv_heads, head_dim, page_size, dtype=torch.bfloat16, v_head_dim: int | None = None) -> int:
+        width = head_dim + (head_dim if v_head_dim is None else v_head_dim)
+        return num_layers * page_size * num_kv_heads * width * torch.empty(0, dtype=dtype).element_size()

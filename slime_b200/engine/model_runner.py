@@ -66,9 +66,9 @@ class EngineWeights:
         self.layers = []
         for i in range(cfg.num_layers):
             kind = cfg.mixer(i)
-            if kind not in ("attention", "general_attention", "gated_delta_net") or cfg.softmax_sinks:
-                raise NotImplementedError(f"the rollout engine runs GQA attention and gated delta-net layers; layer {i} of this "
-                                          f"model is {kind!r}" + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
+            if kind not in ("attention", "general_attention", "gated_delta_net", "mla") or cfg.softmax_sinks:
+                raise NotImplementedError(f"the rollout engine runs GQA attention, latent attention and gated delta-net layers; "
+                                          f"layer {i} of this model is {kind!r}" + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
             full_norm = cfg.qk_layernorm_full  # one weight per projection (sharded like it) instead of one per head
             if kind == "gated_delta_net":
                 # linear-attention layer: replicated over tensor-parallel ranks (every rank computes all of it)
@@ -82,6 +82,16 @@ class EngineWeights:
                     L.update(gdn_qkvz=e(2 * kd + 2 * vd, h), gdn_ba=e(2 * hv, h))
                 else:
                     L.update(gdn_qkv=e(2 * kd + vd, h), gdn_z=e(vd, h), gdn_b=e(hv, h), gdn_a=e(hv, h))
+            elif kind == "mla":
+                # latent attention: the compressions are replicated, the per-head expansions are sharded by head
+                hq_l, dn, dr, dv = cfg.num_attention_heads // tp_size, cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
+                L = {"kind": "mla", "ln1": e(h), "ln2": e(h), "post_attn_ln": None, "post_mlp_ln": None,
+                     "kv_a": e(cfg.kv_lora_rank + dr, h), "kv_a_ln": e(cfg.kv_lora_rank), "kv_b": e(hq_l * (dn + dv), cfg.kv_lora_rank),
+                     "o": e(h, hq_l * dv)}  # fmt: skip
+                if cfg.q_lora_rank:
+                    L.update(q_a=e(cfg.q_lora_rank, h), q_a_ln=e(cfg.q_lora_rank), q_b=e(hq_l * (dn + dr), cfg.q_lora_rank))
+                else:
+                    L["q_proj"] = e(hq_l * (dn + dr), h)
             else:
                 L = self._attention_buffers(e, mat, h, d, full_norm)
             L.setdefault("kind", "attention")
@@ -185,6 +195,23 @@ class EngineWeights:
             src = raw.to(self.device, L[key].dtype)
             L[key].copy_(src.squeeze(1) if inner == "conv1d.weight" and src.dim() == 3 else src)
             return True
+        if L["kind"] == "mla" and sub.startswith("self_attn."):
+            inner = sub[len("self_attn.") :]
+            hq_l, dn, dr, dv = cfg.num_attention_heads // self.tp, cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
+            whole = {"q_a_proj.weight": "q_a", "q_a_layernorm.weight": "q_a_ln", "kv_a_proj_with_mqa.weight": "kv_a",
+                     "kv_a_layernorm.weight": "kv_a_ln"}  # fmt: skip
+            by_head = {"q_b_proj.weight": ("q_b", dn + dr), "q_proj.weight": ("q_proj", dn + dr), "kv_b_proj.weight": ("kv_b", dn + dv)}
+            if inner in whole and whole[inner] in L:
+                L[whole[inner]].copy_(t)
+                return True
+            if inner in by_head and by_head[inner][0] in L:
+                key, per = by_head[inner]
+                L[key].copy_(self._rows(t, hq_l * per))
+                return True
+            if inner == "o_proj.weight":
+                L["o"].copy_(t[:, self.rank * hq_l * dv : (self.rank + 1) * hq_l * dv])
+                return True
+            return False
         if sub == "self_attn.q_proj.weight" and cfg.attention_output_gate and L["kind"] == "attention":
             # checkpoint rows are per head (query, gate): split them into the fused projection's q rows and the gate matrix
             x = t.view(cfg.num_attention_heads, 2 * d, -1)
@@ -326,7 +353,8 @@ class ModelRunner:
         self.max_batch, self.max_context = max_batch, max_context
         self.max_pages_per_req = -(-max_context // kv.page_size)
         # head dims other than 64 / 128 fall back to attention written with plain ops, which reads lengths on the host
-        self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda" and cfg.head_dim in (64, 128)
+        self.use_cuda_graph = (use_cuda_graph and self.device.type == "cuda" and cfg.head_dim in (64, 128)
+                               and not cfg.multi_latent_attention)  # fmt: skip
         self.tp_group = tp_group
         # Row-parallel projections (attention output, MLP down) leave their result in fp32 when no cross-rank sum
         # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
@@ -346,8 +374,9 @@ class ModelRunner:
         # KV slabs exist for the attention layers only; gated delta-net layers keep a recurrent state per decode slot
         self.kv_of, n_attn = [], 0
         for L in weights.layers:
-            self.kv_of.append(n_attn if L["kind"] == "attention" else None)
-            n_attn += L["kind"] == "attention"
+            self.kv_of.append(n_attn if L["kind"] in ("attention", "mla") else None)
+            n_attn += L["kind"] in ("attention", "mla")
+        self.has_mla = any(L["kind"] == "mla" for L in weights.layers)
         self.has_gdn = any(L["kind"] == "gdn" for L in weights.layers)
         self.gdn_S, self.gdn_conv, self.last_gdn_states = {}, {}, None
         if self.has_gdn:
@@ -362,6 +391,11 @@ class ModelRunner:
         self.rope = ops.rope_cos_sin(max_context + 1, rot, cfg.rotary_base, device=self.device,
                                      scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        if cfg.multi_latent_attention:
+            from slime_b200.models import mixers
+
+            self.rope = mixers.mla_rope_table(cfg, max_context + 1, self.device)
+            self.scale = mixers.mla_softmax_scale(cfg)
         self.graphs: dict[int, tuple] = {}
         self.replayed_launches = 0  # kernel-library launches executed through graph replays
         self.graph_buckets = [b for b in (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256, 384, 512) if b <= max_batch]
@@ -505,6 +539,72 @@ class ModelRunner:
             ss = self._tp_reduce(ss)
         return (f * torch.rsqrt(ss / n + self.cfg.norm_epsilon) * w.float()).to(t.dtype)
 
+    # ------------------------------------------------------------ latent attention layers
+    def _mla_project(self, L, x, positions, slots, li):
+        """Queries [T, hq, dn + dr] (rotary part rotated) of the new tokens; their latent vectors (normalised compressed
+        key/value + rotated shared key) are written to the cache slab of layer ``li`` and returned [T, kv_lora + dr]."""
+        from slime_b200.models import mixers
+
+        cfg, T = self.cfg, x.shape[0]
+        dn, dr = cfg.qk_head_dim, cfg.qk_pos_emb_head_dim
+        hq = cfg.num_attention_heads // self.w.tp
+        if "q_a" in L:
+            q = ops.gemm(mixers._rms(ops.gemm(x, L["q_a"]), L["q_a_ln"], cfg.norm_epsilon), L["q_b"])
+        else:
+            q = ops.gemm(x, L["q_proj"])
+        q = q.view(T, hq, dn + dr)
+        c_kv, k_pe = ops.gemm(x, L["kv_a"]).split([cfg.kv_lora_rank, dr], dim=-1)
+        cos, sin = mixers.rotary_cos_sin(self.rope, positions)
+        q = torch.cat([q[..., :dn], mixers.apply_rotary(q[..., dn:], cos, sin, cfg.rotary_interleaved)], dim=-1)
+        k_pe = mixers.apply_rotary(k_pe.reshape(T, 1, dr), cos, sin, cfg.rotary_interleaved).reshape(T, dr)
+        latent = torch.cat([mixers._rms(c_kv, L["kv_a_ln"], cfg.norm_epsilon), k_pe], dim=-1).contiguous()
+        cache = self.kv.k[self.kv_of[li]]
+        ok = slots >= 0
+        cache.view(cache.shape[0], -1)[slots[ok].long()] = latent[ok].to(cache.dtype)
+        return q, latent
+
+    def _mla_absorbed(self, L, q, latent, allowed):
+        """Attention of queries ``q`` [B, hq, dn + dr] over per-row latent contexts ``latent`` [B, Lmax, kv_lora + dr] with
+        ``allowed`` [B, Lmax]: the key expansion is folded into the query and the value expansion applied after the
+        weighted sum, so the cached vector is never expanded per head. Returns [B, hq * dv]."""
+        cfg = self.cfg
+        dn, dv, r = cfg.qk_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        hq = q.shape[1]
+        w = L["kv_b"].float().view(hq, dn + dv, r)
+        q_lat = torch.einsum("bhd,hdr->bhr", q[..., :dn].float(), w[:, :dn])  # queries in latent coordinates
+        lat = latent.float()
+        scores = (torch.einsum("bhr,blr->bhl", q_lat, lat[..., :r]) + torch.einsum("bhd,bld->bhl", q[..., dn:].float(), lat[..., r:]))
+        scores = (scores * self.scale).masked_fill(~allowed[:, None, :], float("-inf"))
+        out_lat = torch.einsum("bhl,blr->bhr", scores.softmax(-1), lat[..., :r])
+        return torch.einsum("bhr,hdr->bhd", out_lat, w[:, dn:]).reshape(q.shape[0], hq * dv).to(self.w.dtype)
+
+    def _mla_prefill(self, L, li, x, positions, slots, cu_q, kv_gather_slots, cu_k, fresh):
+        q, latent = self._mla_project(L, x, positions, slots, li)
+        cache = self.kv.k[self.kv_of[li]]
+        ctx_lat = latent if fresh else cache.view(cache.shape[0], -1).index_select(0, kv_gather_slots)
+        cq, ck = cu_q.tolist(), (cu_q if fresh else cu_k).tolist()
+        lmax = max(b - a for a, b in zip(ck[:-1], ck[1:]))
+        T = x.shape[0]
+        lat = ctx_lat.new_zeros(T, lmax, ctx_lat.shape[-1])
+        allowed = torch.zeros(T, lmax, dtype=torch.bool, device=x.device)
+        for (qa, qb), (ka, kb) in zip(zip(cq[:-1], cq[1:]), zip(ck[:-1], ck[1:])):
+            n_q, n_k = qb - qa, kb - ka
+            if n_q <= 0:
+                continue
+            lat[qa:qb, :n_k] = ctx_lat[ka:kb]
+            allowed[qa:qb, :n_k] = torch.ones(n_q, n_k, dtype=torch.bool, device=x.device).tril(diagonal=n_k - n_q)
+        return self._mla_absorbed(L, q, lat, allowed)
+
+    def _mla_decode(self, L, li, x, positions, slots, block_table, seq_lens, n):
+        q, _ = self._mla_project(L, x, positions, slots, li)
+        cache = self.kv.k[self.kv_of[li]]
+        ps = self.kv.page_size
+        lmax = int(seq_lens.max())
+        pos = torch.arange(lmax, device=x.device)
+        idx = block_table[:, (pos // ps).clamp_max(block_table.shape[1] - 1)].long() * ps + pos % ps  # [n, lmax]
+        lat = cache.view(cache.shape[0], -1)[idx.clamp_(0, cache.shape[0] - 1)]
+        return self._mla_absorbed(L, q, lat, pos[None, :] < seq_lens[:, None])
+
     # ------------------------------------------------------------ gated delta-net layers
     def _gdn_project(self, L, x):
         """Input projections of a delta-net layer -> (pre-convolution q|k|v channels [T, C], z [T, Hv, Dv], b, a [T, Hv])."""
@@ -610,6 +710,12 @@ class ModelRunner:
             normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
             if L["kind"] == "gdn":
                 x = self._gdn_prefill(L, li, normed, in_call, cu_q, gdn_states, self.last_gdn_states)
+                normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
+                x = self._mlp(L, normed)
+                continue
+            if L["kind"] == "mla":
+                ctx = self._mla_prefill(L, li, normed, positions, slots, cu_q, kv_gather_slots, cu_k, fresh)
+                x = self._tp_reduce(_linear(ctx, L["o"], out_dtype=self._proj_dtype))
                 normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
                 x = self._mlp(L, normed)
                 continue
@@ -719,6 +825,9 @@ class ModelRunner:
         for li, L in enumerate(w.layers):
             if L["kind"] == "gdn":
                 normed, res = ops.rmsnorm(self._gdn_decode(L, li, normed, n), L["ln2"], cfg.norm_epsilon, res)
+            elif L["kind"] == "mla":
+                ctx = self._mla_decode(L, li, normed, pos, slots, bt, seq_lens, n)
+                normed, res = self._row_parallel_norm(ctx, L["o"], L["ln2"], res, n)
             else:
                 qkv = self._qkv(L, normed, pos, slots, li)
                 q3 = qkv.view(n, w.hq + 2 * w.hkv, d)

@@ -388,6 +388,26 @@ class GatedDeltaNet(nn.Module):
 
 
 # ---------------------------------------------------------------------------------------------- latent attention
+def mla_rope_table(cfg: ModelConfig, need: int, device) -> torch.Tensor:
+    """Rotary table of the latent-attention rotary part (YaRN frequencies when the model asks for them)."""
+    if cfg.rotary_scaling_type == "yarn" and cfg.rotary_scaling_factor > 1:
+        from slime_b200.ops import reference
+
+        return reference.rope_cos_sin_yarn(need, cfg.qk_pos_emb_head_dim, cfg.rotary_base, cfg.rotary_scaling_factor,
+                                           cfg.rotary_original_max_position, cfg.yarn_beta_fast, cfg.yarn_beta_slow, cfg.mscale,
+                                           cfg.mscale_all_dim, device=device)  # fmt: skip
+    return ops.rope_cos_sin(need, cfg.qk_pos_emb_head_dim, cfg.rotary_base, device=device, scaling_factor=cfg.rotary_scaling_factor)
+
+
+def mla_softmax_scale(cfg: ModelConfig) -> float:
+    scale = (cfg.qk_head_dim + cfg.qk_pos_emb_head_dim) ** -0.5
+    if cfg.rotary_scaling_type == "yarn" and cfg.rotary_scaling_factor > 1 and cfg.mscale_all_dim:
+        from slime_b200.ops.reference import yarn_mscale
+
+        scale *= yarn_mscale(cfg.rotary_scaling_factor, cfg.mscale_all_dim) ** 2  # YaRN's attention temperature
+    return scale
+
+
 class MLASelfAttention(nn.Module):
     """Multi-head latent attention. Parameters (replicated over tensor-parallel ranks), Megatron names:
     ``linear_q_down_proj`` [q_lora, H] + ``q_layernorm`` + ``linear_q_up_proj`` [Hq (Dn + Dr), q_lora] (or ``linear_q_proj``
@@ -419,25 +439,12 @@ class MLASelfAttention(nn.Module):
         self.kv_layernorm.weight = mk(cfg.kv_lora_rank, ones=True)
         self.linear_kv_up_proj.weight = mk(self.hq * (self.dn + self.dv), cfg.kv_lora_rank, std=std)
         self.linear_proj.weight = mk(h, self.hq * self.dv, std=std / math.sqrt(2.0 * cfg.num_layers))
-        self.scale = (self.dn + self.dr) ** -0.5
-        if cfg.rotary_scaling_type == "yarn" and cfg.rotary_scaling_factor > 1 and cfg.mscale_all_dim:
-            from slime_b200.ops.reference import yarn_mscale
-
-            self.scale *= yarn_mscale(cfg.rotary_scaling_factor, cfg.mscale_all_dim) ** 2  # YaRN's attention temperature
+        self.scale = mla_softmax_scale(cfg)
         self._rope = None
 
     def _table(self, device, need):
         if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
-            c = self.cfg
-            if c.rotary_scaling_type == "yarn" and c.rotary_scaling_factor > 1:
-                from slime_b200.ops import reference
-
-                self._rope = reference.rope_cos_sin_yarn(max(need, 4096), self.dr, c.rotary_base, c.rotary_scaling_factor,
-                                                         c.rotary_original_max_position, c.yarn_beta_fast, c.yarn_beta_slow,
-                                                         c.mscale, c.mscale_all_dim, device=device)  # fmt: skip
-            else:
-                self._rope = ops.rope_cos_sin(max(need, 4096), self.dr, c.rotary_base, device=device,
-                                              scaling_factor=c.rotary_scaling_factor)  # fmt: skip
+            self._rope = mla_rope_table(self.cfg, max(need, 4096), device)
         return self._rope
 
     def _qkv(self, inp, packed):

@@ -79,7 +79,15 @@ def main():
                               rotary_interleaved=True),
                  "minimax_m2": dict(qk_layernorm_full=True, rotary_percent=0.5, num_experts=8, moe_ffn_hidden_size=256,
                                     moe_router_topk=2, moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
-                                    moe_shared_expert_intermediate_size=512)}[family]  # fmt: skip
+                                    moe_shared_expert_intermediate_size=512),
+                 "deepseek_v3": dict(multi_latent_attention=True, q_lora_rank=96, kv_lora_rank=64, qk_head_dim=32,
+                                     qk_pos_emb_head_dim=16, v_head_dim=32, rotary_interleaved=True, num_experts=8,
+                                     moe_ffn_hidden_size=256, moe_router_topk=2, moe_layer_freq=[0, 1, 1],
+                                     moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
+                                     moe_shared_expert_intermediate_size=256, moe_router_num_groups=4, moe_router_group_topk=2),
+                 "qwen3_next": dict(full_attention_interval=3, linear_num_key_heads=4, linear_num_value_heads=8,
+                                    linear_key_head_dim=32, linear_value_head_dim=32, attention_output_gate=True, qk_layernorm=True,
+                                    rotary_percent=0.25, model_arch="Qwen3NextForCausalLM")}[family]  # fmt: skip
         cfg = ModelConfig(num_layers=3, hidden_size=512, num_attention_heads=8, num_query_groups=4, kv_channels=64,
                           ffn_hidden_size=1024, vocab_size=2048, rotary_base=1e4, tie_word_embeddings=False, **extra)
         moe = cfg.num_experts is not None

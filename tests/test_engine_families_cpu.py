@@ -33,6 +33,13 @@ FAMILIES = {
     "qwen3_5": dict(num_layers=4, full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=2, linear_key_head_dim=8,
                     linear_value_head_dim=8, attention_output_gate=True, qk_layernorm=True, rotary_percent=0.25,
                     model_arch="Qwen3_5ForCausalLM"),
+    "deepseek_v3": dict(multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4, v_head_dim=8,
+                        rotary_interleaved=True, num_experts=4, moe_ffn_hidden_size=32, moe_router_topk=2, moe_layer_freq=[0, 1],
+                        moe_shared_expert_intermediate_size=32, moe_router_score_function="sigmoid",
+                        moe_router_enable_expert_bias=True, moe_router_topk_scaling_factor=2.5, rotary_scaling_type="yarn",
+                        rotary_scaling_factor=40.0, mscale=1.0, mscale_all_dim=1.0, model_arch="DeepseekV3ForCausalLM"),
+    "moonlight": dict(multi_latent_attention=True, q_lora_rank=None, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4,
+                      v_head_dim=8, rotary_interleaved=True, model_arch="DeepseekV3ForCausalLM"),
     "deepseek_routing": dict(qk_layernorm=True, num_experts=8, moe_ffn_hidden_size=32, moe_router_topk=2, moe_router_num_groups=4,
                              moe_router_group_topk=2, moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
                              moe_shared_expert_intermediate_size=64, model_arch="Qwen3MoeForCausalLM"),
@@ -127,3 +134,27 @@ def test_hybrid_engine_carries_recurrent_state_through_chunked_prefill_and_batch
     # the same prompt again: still no prefix reuse, same answer
     again = e.generate([prompts[0]], [dict(max_new_tokens=5, temperature=0, ignore_eos=True)])[0]
     assert again.output_ids == reqs[0].output_ids and again.num_cached_tokens == 0
+
+
+def test_latent_attention_engine_reuses_prefixes_and_prefills_in_chunks():
+    """DeepSeek-style model: the latent cache serves a cached prefix and chunked prefill (queries of a later chunk attend
+    the latent vectors of earlier ones), and sibling requests share pages; log-probs equal the trainer's."""
+    torch.manual_seed(0)
+    cfg = ModelConfig(**{**BASE, **FAMILIES["deepseek_v3"]})
+    model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=3)
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=4, context_length=64, disable_cuda_graph=True, chunked_prefill_size=6,
+                               max_prefill_tokens=10), device="cpu", num_pages=64)  # fmt: skip
+    hf = [x for n, p in list(model.named_parameters()) + list(model.named_buffers()) for x in convert.convert_to_hf(cfg, n, p.detach())]
+    assert not e.weights.load_weights(hf)
+    assert e.kv.k[0].shape[1:] == (1, cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim) and e.kv.v[0].shape[-1] == 0
+    g = torch.Generator().manual_seed(5)
+    p = torch.randint(0, cfg.vocab_size, (14,), generator=g).tolist()
+    reqs = e.generate([p, p, p[:9] + [1, 2]], [dict(max_new_tokens=5, temperature=0, ignore_eos=True)] * 3)
+    assert reqs[1].num_cached_tokens >= 4 and reqs[2].num_cached_tokens >= 4  # pages of the first request's prompt were reused
+    for r in reqs:
+        full = r.input_ids + r.output_ids
+        with torch.no_grad():
+            lp = model(torch.tensor(full))[0].log_softmax(-1)
+        want = [float(lp[len(r.input_ids) - 1 + i, t]) for i, t in enumerate(r.output_ids)]
+        assert np.abs(np.array(r.output_logprobs) - np.array(want)).max() < 2e-4
+    assert reqs[0].output_ids == reqs[1].output_ids
