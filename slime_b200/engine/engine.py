@@ -81,7 +81,7 @@ class Engine:
         compressed key/value plus the shared rotary key) and no separate values."""
         c = self.cfg
         if c.multi_latent_attention:
-            return 1, c.kv_lora_rank + c.qk_pos_emb_head_dim, 0
+            return 1, c.kv_lora_rank + c.qk_pos_emb_head_dim + (c.index_head_dim if c.index_topk else 0), 0
         return self.weights.hkv, c.head_dim, None
 
     def _num_kv_layers(self) -> int:

@@ -66,7 +66,7 @@ class EngineWeights:
         self.layers = []
         for i in range(cfg.num_layers):
             kind = cfg.mixer(i)
-            if kind not in ("attention", "general_attention", "gated_delta_net", "mla") or cfg.softmax_sinks:
+            if kind not in ("attention", "general_attention", "gated_delta_net", "mla", "dsa") or cfg.softmax_sinks:
                 raise NotImplementedError(f"the rollout engine runs GQA attention, latent attention and gated delta-net layers; "
                                           f"layer {i} of this model is {kind!r}" + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
             full_norm = cfg.qk_layernorm_full  # one weight per projection (sharded like it) instead of one per head
@@ -82,7 +82,7 @@ class EngineWeights:
                     L.update(gdn_qkvz=e(2 * kd + 2 * vd, h), gdn_ba=e(2 * hv, h))
                 else:
                     L.update(gdn_qkv=e(2 * kd + vd, h), gdn_z=e(vd, h), gdn_b=e(hv, h), gdn_a=e(hv, h))
-            elif kind == "mla":
+            elif kind in ("mla", "dsa"):
                 # latent attention: the compressions are replicated, the per-head expansions are sharded by head
                 hq_l, dn, dr, dv = cfg.num_attention_heads // tp_size, cfg.qk_head_dim, cfg.qk_pos_emb_head_dim, cfg.v_head_dim
                 L = {"kind": "mla", "ln1": e(h), "ln2": e(h), "post_attn_ln": None, "post_mlp_ln": None,
@@ -92,6 +92,18 @@ class EngineWeights:
                     L.update(q_a=e(cfg.q_lora_rank, h), q_a_ln=e(cfg.q_lora_rank), q_b=e(hq_l * (dn + dr), cfg.q_lora_rank))
                 else:
                     L["q_proj"] = e(hq_l * (dn + dr), h)
+                if kind == "dsa":
+                    # lightning indexer (replicated): which cached tokens a query may attend; a layer for which
+                    # max(layer - offset, 0) % freq != 0 (1-based) reuses the choice of the nearest earlier computing layer
+                    one_based = i + 1
+                    src = one_based
+                    while (max(src - cfg.index_skip_topk_offset, 0) % cfg.index_topk_freq) != 0:
+                        src -= 1
+                    L["index_source"] = src - 1
+                    if src == one_based:
+                        hi, di = cfg.index_n_heads, cfg.index_head_dim
+                        L.update(idx_wq_b=e(hi * di, cfg.q_lora_rank), idx_wk=e(di, h), idx_k_norm_w=e(di), idx_k_norm_b=e(di),
+                                 idx_weights=e(hi, h))  # fmt: skip
             else:
                 L = self._attention_buffers(e, mat, h, d, full_norm)
             L.setdefault("kind", "attention")
@@ -140,7 +152,7 @@ class EngineWeights:
         yield self.final_norm
         for L in self.layers:
             for v in L.values():
-                if v is None or isinstance(v, str):  # absent buffers, and the layer's kind tag
+                if v is None or isinstance(v, (str, int)):  # absent buffers, the layer's kind tag, the indexer's source layer
                     continue
                 if hasattr(v, "tensors"):  # a quantised matrix: its bytes and its scales
                     yield from v.tensors()
@@ -210,6 +222,11 @@ class EngineWeights:
                 return True
             if inner == "o_proj.weight":
                 L["o"].copy_(t[:, self.rank * hq_l * dv : (self.rank + 1) * hq_l * dv])
+                return True
+            indexer = {"indexer.wq_b.weight": "idx_wq_b", "indexer.wk.weight": "idx_wk", "indexer.k_norm.weight": "idx_k_norm_w",
+                       "indexer.k_norm.bias": "idx_k_norm_b", "indexer.weights_proj.weight": "idx_weights"}  # fmt: skip
+            if inner in indexer and indexer[inner] in L:
+                L[indexer[inner]].copy_(t)
                 return True
             return False
         if sub == "self_attn.q_proj.weight" and cfg.attention_output_gate and L["kind"] == "attention":
@@ -377,6 +394,7 @@ class ModelRunner:
             self.kv_of.append(n_attn if L["kind"] in ("attention", "mla") else None)
             n_attn += L["kind"] in ("attention", "mla")
         self.has_mla = any(L["kind"] == "mla" for L in weights.layers)
+        self._dsa_masks: dict[int, torch.Tensor] = {}  # key choices of the indexer layers of the pass in flight
         self.has_gdn = any(L["kind"] == "gdn" for L in weights.layers)
         self.gdn_S, self.gdn_conv, self.last_gdn_states = {}, {}, None
         if self.has_gdn:
@@ -557,11 +575,42 @@ class ModelRunner:
         cos, sin = mixers.rotary_cos_sin(self.rope, positions)
         q = torch.cat([q[..., :dn], mixers.apply_rotary(q[..., dn:], cos, sin, cfg.rotary_interleaved)], dim=-1)
         k_pe = mixers.apply_rotary(k_pe.reshape(T, 1, dr), cos, sin, cfg.rotary_interleaved).reshape(T, dr)
-        latent = torch.cat([mixers._rms(c_kv, L["kv_a_ln"], cfg.norm_epsilon), k_pe], dim=-1).contiguous()
+        parts = [mixers._rms(c_kv, L["kv_a_ln"], cfg.norm_epsilon), k_pe]
+        index_q = None
+        if cfg.index_topk:  # every layer caches an indexer key slot (unused on layers that reuse another layer's choice)
+            hi, di = cfg.index_n_heads, cfg.index_head_dim
+            if "idx_wk" in L:
+                q_latent = mixers._rms(ops.gemm(x, L["q_a"]), L["q_a_ln"], cfg.norm_epsilon)
+                qi = mixers.apply_rotary(ops.gemm(q_latent, L["idx_wq_b"]).view(T, hi, di), cos, sin, cfg.rotary_interleaved)
+                ki = torch.nn.functional.layer_norm(ops.gemm(x, L["idx_wk"]).float(), (di,), L["idx_k_norm_w"].float(), L["idx_k_norm_b"].float())
+                ki = mixers.apply_rotary(ki.view(T, 1, di), cos, sin, cfg.rotary_interleaved).view(T, di)
+                wi = ops.gemm(x, L["idx_weights"]).float() * (hi**-0.5) * (di**-0.5)
+                index_q = (qi.float(), wi)
+                parts.append(ki.to(x.dtype))
+            else:
+                parts.append(x.new_zeros(T, di))
+        latent = torch.cat(parts, dim=-1).contiguous()
         cache = self.kv.k[self.kv_of[li]]
         ok = slots >= 0
         cache.view(cache.shape[0], -1)[slots[ok].long()] = latent[ok].to(cache.dtype)
-        return q, latent
+        return q, latent, index_q
+
+    def _dsa_restrict(self, L, li, index_q, lat, allowed):
+        """Keep, per query row, the ``index_topk`` cached tokens the indexer scores highest (rows that see fewer keep all).
+        The choice is remembered for the layers of this pass that reuse it."""
+        cfg = self.cfg
+        if not cfg.index_topk:
+            return allowed
+        if index_q is None:
+            return self._dsa_masks[L["index_source"]]
+        if allowed.shape[1] > cfg.index_topk:
+            qi, wi = index_q
+            ki = lat[..., cfg.kv_lora_rank + cfg.qk_pos_emb_head_dim :].float()
+            logits = (torch.einsum("bhd,bld->bhl", qi, ki).relu_() * wi[:, :, None]).sum(1).masked_fill(~allowed, float("-inf"))
+            pick = torch.zeros_like(allowed).scatter_(1, logits.topk(cfg.index_topk, dim=-1).indices, True)
+            allowed = pick & allowed
+        self._dsa_masks[li] = allowed
+        return allowed
 
     def _mla_absorbed(self, L, q, latent, allowed):
         """Attention of queries ``q`` [B, hq, dn + dr] over per-row latent contexts ``latent`` [B, Lmax, kv_lora + dr] with
@@ -570,16 +619,17 @@ class ModelRunner:
         cfg = self.cfg
         dn, dv, r = cfg.qk_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         hq = q.shape[1]
+        dr = cfg.qk_pos_emb_head_dim
         w = L["kv_b"].float().view(hq, dn + dv, r)
         q_lat = torch.einsum("bhd,hdr->bhr", q[..., :dn].float(), w[:, :dn])  # queries in latent coordinates
         lat = latent.float()
-        scores = (torch.einsum("bhr,blr->bhl", q_lat, lat[..., :r]) + torch.einsum("bhd,bld->bhl", q[..., dn:].float(), lat[..., r:]))
+        scores = (torch.einsum("bhr,blr->bhl", q_lat, lat[..., :r]) + torch.einsum("bhd,bld->bhl", q[..., dn:].float(), lat[..., r : r + dr]))
         scores = (scores * self.scale).masked_fill(~allowed[:, None, :], float("-inf"))
         out_lat = torch.einsum("bhl,blr->bhr", scores.softmax(-1), lat[..., :r])
         return torch.einsum("bhr,hdr->bhd", out_lat, w[:, dn:]).reshape(q.shape[0], hq * dv).to(self.w.dtype)
 
     def _mla_prefill(self, L, li, x, positions, slots, cu_q, kv_gather_slots, cu_k, fresh):
-        q, latent = self._mla_project(L, x, positions, slots, li)
+        q, latent, index_q = self._mla_project(L, x, positions, slots, li)
         cache = self.kv.k[self.kv_of[li]]
         ctx_lat = latent if fresh else cache.view(cache.shape[0], -1).index_select(0, kv_gather_slots)
         cq, ck = cu_q.tolist(), (cu_q if fresh else cu_k).tolist()
@@ -593,17 +643,17 @@ class ModelRunner:
                 continue
             lat[qa:qb, :n_k] = ctx_lat[ka:kb]
             allowed[qa:qb, :n_k] = torch.ones(n_q, n_k, dtype=torch.bool, device=x.device).tril(diagonal=n_k - n_q)
-        return self._mla_absorbed(L, q, lat, allowed)
+        return self._mla_absorbed(L, q, lat, self._dsa_restrict(L, li, index_q, lat, allowed))
 
     def _mla_decode(self, L, li, x, positions, slots, block_table, seq_lens, n):
-        q, _ = self._mla_project(L, x, positions, slots, li)
+        q, _, index_q = self._mla_project(L, x, positions, slots, li)
         cache = self.kv.k[self.kv_of[li]]
         ps = self.kv.page_size
         lmax = int(seq_lens.max())
         pos = torch.arange(lmax, device=x.device)
         idx = block_table[:, (pos // ps).clamp_max(block_table.shape[1] - 1)].long() * ps + pos % ps  # [n, lmax]
         lat = cache.view(cache.shape[0], -1)[idx.clamp_(0, cache.shape[0] - 1)]
-        return self._mla_absorbed(L, q, lat, pos[None, :] < seq_lens[:, None])
+        return self._mla_absorbed(L, q, lat, self._dsa_restrict(L, li, index_q, lat, pos[None, :] < seq_lens[:, None]))
 
     # ------------------------------------------------------------ gated delta-net layers
     def _gdn_project(self, L, x):

@@ -38,6 +38,9 @@ FAMILIES = {
                         moe_shared_expert_intermediate_size=32, moe_router_score_function="sigmoid",
                         moe_router_enable_expert_bias=True, moe_router_topk_scaling_factor=2.5, rotary_scaling_type="yarn",
                         rotary_scaling_factor=40.0, mscale=1.0, mscale_all_dim=1.0, model_arch="DeepseekV3ForCausalLM"),
+    "glm5_dsa": dict(num_layers=3, multi_latent_attention=True, q_lora_rank=24, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4,
+                     v_head_dim=12, rotary_interleaved=True, index_topk=5, index_n_heads=8, index_head_dim=8, index_topk_freq=2,
+                     index_skip_topk_offset=1, model_arch="GlmMoeDsaForCausalLM"),
     "moonlight": dict(multi_latent_attention=True, q_lora_rank=None, kv_lora_rank=16, qk_head_dim=8, qk_pos_emb_head_dim=4,
                       v_head_dim=8, rotary_interleaved=True, model_arch="DeepseekV3ForCausalLM"),
     "deepseek_routing": dict(qk_layernorm=True, num_experts=8, moe_ffn_hidden_size=32, moe_router_topk=2, moe_router_num_groups=4,
