@@ -66,9 +66,8 @@ class EngineWeights:
         self.layers = []
         for i in range(cfg.num_layers):
             kind = cfg.mixer(i)
-            if kind not in ("attention", "general_attention", "gated_delta_net", "mla", "dsa") or cfg.softmax_sinks:
-                raise NotImplementedError(f"the rollout engine runs GQA attention, latent attention and gated delta-net layers; "
-                                          f"layer {i} of this model is {kind!r}" + (" with softmax sinks" if cfg.softmax_sinks else ""))  # fmt: skip
+            if kind not in ("attention", "general_attention", "gated_delta_net", "mla", "dsa"):
+                raise NotImplementedError(f"the rollout engine has no layer of kind {kind!r} (layer {i})")
             full_norm = cfg.qk_layernorm_full  # one weight per projection (sharded like it) instead of one per head
             if kind == "gated_delta_net":
                 # linear-attention layer: replicated over tensor-parallel ranks (every rank computes all of it)
@@ -136,6 +135,8 @@ class EngineWeights:
         }  # fmt: skip
         if cfg.attention_output_gate:
             L["gate"] = e(self.hq * d, h)  # sigmoid gate of the attention output, one row per query channel
+        if cfg.softmax_sinks:
+            L["sinks"] = torch.zeros(self.hq, dtype=torch.float32, device=self.device)  # per-head logit in the denominator
         return L
 
     def num_bytes(self) -> int:
@@ -250,6 +251,7 @@ class EngineWeights:
             "post_mlp_layernorm.weight": lambda: L["post_mlp_ln"].copy_(t),
             "mlp.gate.e_score_correction_bias": lambda: L["router_bias"].copy_(raw.to(self.device, torch.float32)),
             "mlp.shared_expert_gate.weight": lambda: L["shared_gate"].copy_(t),
+            "self_attn.sinks": lambda: L["sinks"].copy_(self._rows(raw.to(self.device, torch.float32), hq)),
         }
         if sub in vectors and sub.split(".")[0] in ("post_self_attn_layernorm", "post_mlp_layernorm") and L.get(
                 "post_attn_ln" if sub.startswith("post_self") else "post_mlp_ln") is None:
@@ -371,7 +373,7 @@ class ModelRunner:
         self.max_pages_per_req = -(-max_context // kv.page_size)
         # head dims other than 64 / 128 fall back to attention written with plain ops, which reads lengths on the host
         self.use_cuda_graph = (use_cuda_graph and self.device.type == "cuda" and cfg.head_dim in (64, 128)
-                               and not cfg.multi_latent_attention)  # fmt: skip
+                               and not cfg.multi_latent_attention and not cfg.softmax_sinks)  # fmt: skip
         self.tp_group = tp_group
         # Row-parallel projections (attention output, MLP down) leave their result in fp32 when no cross-rank sum
         # follows: the fused add+RMSNorm reads it unrounded, and a skinny decode GEMM with a long K can then be cut
@@ -773,11 +775,11 @@ class ModelRunner:
             q3 = qkv.view(T, w.hq + 2 * w.hkv, d)
             q, k, v = q3[:, : w.hq], q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
             if fresh:
-                ctx = ops.varlen_attention(q, k, v, cu_q, max_q, self.scale)
+                ctx = ops.varlen_attention(q, k, v, cu_q, max_q, self.scale, sinks=L.get("sinks"))
             else:
                 k_all = self.kv.k[self.kv_of[li]].index_select(0, kv_gather_slots)
                 v_all = self.kv.v[self.kv_of[li]].index_select(0, kv_gather_slots)
-                ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale)
+                ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale, sinks=L.get("sinks"))
             ctx = ctx.reshape(T, -1)
             if "gate" in L:
                 ctx = ctx * torch.sigmoid(ops.gemm(normed, L["gate"]).float()).to(ctx.dtype)
@@ -882,7 +884,7 @@ class ModelRunner:
                 qkv = self._qkv(L, normed, pos, slots, li)
                 q3 = qkv.view(n, w.hq + 2 * w.hkv, d)
                 ctx = ops.paged_decode_attention(q3[:, : w.hq], self.kv.k[self.kv_of[li]], self.kv.v[self.kv_of[li]], bt, seq_lens, ps,
-                                                 self.scale).reshape(n, -1)  # fmt: skip
+                                                 self.scale, sinks=L.get("sinks")).reshape(n, -1)  # fmt: skip
                 if "gate" in L:
                     ctx = ctx * torch.sigmoid(ops.gemm(normed, L["gate"]).float()).to(ctx.dtype)
                 normed, res = self._row_parallel_norm(ctx, L["o"], L["ln2"], res, n, post=L["post_attn_ln"])
@@ -972,12 +974,12 @@ class ModelRunner:
         self.graphs.clear()
 
 
-def _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, scale):
+def _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, scale, sinks=None):
     """Attention of new tokens over (cached + new) context, causal aligned to the sequence end."""
-    if q.is_cuda:
+    if q.is_cuda or sinks is not None:
         from slime_b200.ops import attention
 
-        return attention.extend_attention(q, k_all, v_all, cu_q, cu_k, scale)
+        return attention.segment_attention(q, k_all, v_all, attention.segments_extend(cu_q, cu_k), scale, sinks)
     out = torch.empty_like(q)
     cq, ck = cu_q.tolist(), cu_k.tolist()
     Hq, Hkv = q.shape[1], k_all.shape[1]

@@ -455,14 +455,15 @@ def varlen_attention(q, k, v, cu_seqlens, max_seqlen, scale=None, causal=True, s
 
 
 def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None, out=None, splits=None,
-                           workspace=None, use_tensor_cores=True):
+                           workspace=None, use_tensor_cores=True, sinks=None):
     """One query token per request over a paged KV cache. q: [B, Hq, D]; caches [slots, Hkv, D]."""
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
-    if not _is_cuda(q) or D not in (64, 128):
-        # the decode kernels cover head dims 64 and 128; other widths (256: Qwen3-Next / Qwen3.5) take the plain form
-        return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale)
+    if not _is_cuda(q) or D not in (64, 128) or sinks is not None:
+        # the decode kernels cover head dims 64 and 128 without sinks; other widths (256: Qwen3-Next / Qwen3.5) and
+        # softmax sinks take the plain form
+        return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale, sinks)
     caller_splits = splits
     if splits is None:
         ctas = B * Hkv

@@ -115,8 +115,9 @@ def varlen_attention(q, k, v, cu_seqlens, scale=None, causal=True):
     return out
 
 
-def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None):
-    """q: [B, Hq, D]; caches [slots, Hkv, D]; attends over the first seq_lens[b] cached tokens."""
+def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale=None, sinks=None):
+    """q: [B, Hq, D]; caches [slots, Hkv, D]; attends over the first seq_lens[b] cached tokens. ``sinks`` [Hq]: one extra
+    logit per head in the softmax denominator (it carries no value)."""
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -127,7 +128,11 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
         slots = block_table[b, pos // page_size].long() * page_size + pos % page_size
         ks = k_cache[slots].float().repeat_interleave(Hq // Hkv, dim=1)  # [n, Hq, D]
         vs = v_cache[slots].float().repeat_interleave(Hq // Hkv, dim=1)
-        att = torch.einsum("hd,nhd->hn", q[b].float() * scale, ks).softmax(-1)
+        logits = torch.einsum("hd,nhd->hn", q[b].float() * scale, ks)
+        if sinks is not None:
+            att = torch.cat([logits, sinks.float()[:, None]], dim=-1).softmax(-1)[:, :-1]
+        else:
+            att = logits.softmax(-1)
         out[b] = torch.einsum("hn,nhd->hd", att, vs).to(q.dtype)
     return out
 

@@ -23,6 +23,7 @@ FAMILIES = {
                      moe_layer_freq=[0, 1], moe_shared_expert_intermediate_size=32, moe_router_score_function="sigmoid",
                      moe_router_enable_expert_bias=True, moe_router_pre_softmax=True, moe_router_topk_scaling_factor=1.5,
                      model_arch="Glm4MoeForCausalLM"),
+    "sinks": dict(softmax_sinks=True, qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
     "minimax_m2": dict(qk_layernorm_full=True, rotary_percent=0.5, num_experts=4, moe_ffn_hidden_size=32, moe_router_topk=2,
                        moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True, moe_router_pre_softmax=True,
                        model_arch="MiniMaxM2ForCausalLM"),
@@ -57,7 +58,7 @@ def test_engine_reproduces_the_trainers_log_probs(family):
     with torch.no_grad():  # make biases and norm weights non-trivial so that a dropped one shows
         for n, p in model.named_parameters():
             if p.dim() == 1:
-                p.add_(torch.randn_like(p) * 0.1)
+                p.add_(torch.randn_like(p) * (1.0 if "softmax_offset" in n else 0.1))
         for n, b in model.named_buffers():
             if "expert_bias" in n:
                 b.copy_(torch.randn_like(b) * 0.5)
