@@ -1,13 +1,13 @@
 #!/bin/bash
 # Shared by the run recipes: resolves paths, turns a model preset into architecture flags, launches train.py.
-#   DATA_DIR      where prompt / eval sets live           (default /root/data)
-#   CKPT_DIR      where checkpoints are read and written  (default /root/ckpt)
+#   DATA_DIR      where prompt / eval sets live           (default ~/data)
+#   CKPT_DIR      where checkpoints are read and written  (default ~/ckpt)
 #   NUM_GPUS      GPUs of this node used by the job       (default: all visible)
 #   DRY_RUN=1     print the command line instead of running it (one argument per line)
 set -euo pipefail
 REPO_ROOT="$(cd -- "$(dirname -- "${BASH_SOURCE[0]}")/.." && pwd)"
-DATA_DIR="${DATA_DIR:-/root/data}"
-CKPT_DIR="${CKPT_DIR:-/root/ckpt}"
+DATA_DIR="${DATA_DIR:-${HOME}/data}"
+CKPT_DIR="${CKPT_DIR:-${HOME}/ckpt}"
 if [ -z "${NUM_GPUS:-}" ]; then
   NUM_GPUS=$(python -c 'import torch; print(max(torch.cuda.device_count(), 1))')
 fi

@@ -33,9 +33,10 @@ def model_flags(preset: str) -> str:
     return subprocess.check_output([sys.executable, "-m", "slime_b200.models.presets", preset], cwd=REPO_ROOT, text=True).strip()
 
 
-def convert_checkpoint(model_name: str, preset: str, num_gpus_per_node: int = 1, dir_src: str = "/root/models", dir_dst: str = "/root/models",
+def convert_checkpoint(model_name: str, preset: str, num_gpus_per_node: int = 1, dir_src: str = "~/models", dir_dst: str = "~/models",
                        extra_args: str = "") -> str:  # fmt: skip
     """Hugging Face directory -> ``<name>_torch_dist`` (skipped when it already exists). Returns the destination."""
+    dir_src, dir_dst = os.path.expanduser(dir_src), os.path.expanduser(dir_dst)
     dst = os.path.join(dir_dst, f"{model_name}_torch_dist")
     if os.path.exists(os.path.join(dst, "latest_checkpointed_iteration.txt")):
         print(f"convert_checkpoint: {dst} exists, skipping")
@@ -58,8 +59,9 @@ def rsync_simple(path_src: str, path_dst: str) -> None:
     run(f"mkdir -p {shlex.quote(path_dst)} && rsync -a --info=progress2 {shlex.quote(path_src.rstrip('/'))}/ {shlex.quote(path_dst)}")
 
 
-def hf_download_dataset(full_name: str, dst_root: str = "/root/datasets") -> None:
+def hf_download_dataset(full_name: str, dst_root: str = "~/datasets") -> None:
     _, name = full_name.split("/")
+    dst_root = os.path.expanduser(dst_root)
     run(f"hf download --repo-type dataset {full_name} --local-dir {os.path.join(dst_root, name)}")
 
 
