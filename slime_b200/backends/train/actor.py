@@ -82,6 +82,11 @@ class TrainActor:
             load_function(hook)(args)
         if getattr(args, "deterministic_mode", False):
             torch.use_deterministic_algorithms(True, warn_only=True)
+        if getattr(args, "numa_affinity", False) or os.environ.get("SLIME_B200_NUMA_AFFINITY") == "1":
+            from slime_b200.utils.distributed_utils import set_numa_affinity
+
+            cpus = set_numa_affinity(int(os.environ.get("LOCAL_RANK", "0")))
+            logger.info("NUMA affinity: %s", f"{len(cpus)} CPUs" if cpus else "unchanged")
         if getattr(args, "use_routing_replay", False):
             os.environ["ENABLE_ROUTING_REPLAY"] = "1"  # read by every router (slime/utils/routing_replay.py:81 in the reference)
         self.model = TrainModel(args, role=self.role, device=device)

@@ -165,13 +165,20 @@ class TrainModel:
         if tps > 1:
             flat = [p.main_grad for _n, p in self.named_parameters()
                     if getattr(p, "sequence_parallel", False) or getattr(p, "needs_tp_grad_reduce", False)]  # fmt: skip
-            if flat:
-                coalesced = torch.cat([g.reshape(-1) for g in flat])
-                dist.all_reduce(coalesced, group=mpu.get_tensor_model_parallel_group())
-                off = 0
-                for g in flat:
-                    g.copy_(coalesced[off : off + g.numel()].view_as(g))
-                    off += g.numel()
+            # coalesced, at most ~1 GiB per collective (the staging copy of a very large model's norm grads stays bounded)
+            limit, batch, size = 1 << 30, [], 0
+            for g in flat + [None]:
+                if g is not None:
+                    batch.append(g)
+                    size += g.numel() * g.element_size()
+                if batch and (g is None or size >= limit):
+                    coalesced = torch.cat([x.reshape(-1) for x in batch])
+                    dist.all_reduce(coalesced, group=mpu.get_tensor_model_parallel_group())
+                    off = 0
+                    for x in batch:
+                        x.copy_(coalesced[off : off + x.numel()].view_as(x))
+                        off += x.numel()
+                    batch, size = [], 0
         if mpu.get_pipeline_model_parallel_world_size() > 1 and self.cfg.tie_word_embeddings:
             w = None
             if self.chunks[0].pre_process:

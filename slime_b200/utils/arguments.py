@@ -202,7 +202,7 @@ _PLUGIN = [
     _f("--padded-vocab-size", type=int, default=None), _f("--runtime-env-json", type=str, default=None),
 ]
 _CI = [
-    _f("--ci-test", action=_T), _f("--ci-disable-kl-checker", action=_T), _f("--ci-check-mtp-only-grad", action=_T),
+    _f("--ci-test", action=_T), _f("--ci-disable-kl-checker", action=_T), _f("--ci-check-mtp-only-grad", action=_T), _f("--numa-affinity", action=_T),
     _f("--ci-train-rollout-logprob-abs-diff-threshold", type=float, default=0.1),
     _f("--ci-save-grad-norm", type=str, default=None), _f("--ci-load-grad-norm", type=str, default=None),
 ]

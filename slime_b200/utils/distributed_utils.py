@@ -101,3 +101,27 @@ def shutdown_distributed(engines=()) -> None:
     if dist.is_available() and dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()
+
+
+def set_numa_affinity(local_rank: int) -> list[int] | None:
+    """Pin this process to the CPUs NVML reports as closest to GPU ``local_rank`` (its NUMA node). Returns the CPU list,
+    or None when NVML, the GPU or an allowed CPU among them is not available (nothing is changed then). Same role as
+    the affinity step of slime/ray/train_actor.py:47-94 in the reference; here it is opt-in
+    (``SLIME_B200_NUMA_AFFINITY=1`` or ``--numa-affinity``), since containers often expose a CPU set of their own."""
+    import os
+
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = -(-os.cpu_count() // 64)
+        mask = pynvml.nvmlDeviceGetCpuAffinity(handle, words)
+        cpus = [64 * w + b for w, m in enumerate(mask) for b in range(64) if (int(m) >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return allowed
+    except Exception:  # noqa: BLE001 - no NVML, no such GPU, no permission: affinity is an optimisation only
+        return None
