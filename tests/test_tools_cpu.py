@@ -98,6 +98,17 @@ def test_int4_direct_conversion(tmp_path):
     assert (deq - w).abs().max() <= w.abs().max() / 7 * 0.51 + 1e-3  # half a quantisation step of the largest group
     cfg = json.load(open(os.path.join(out, "config.json")))["quantization_config"]
     assert cfg["format"] == "pack-quantized" and cfg["config_groups"]["group_0"]["weights"]["group_size"] == 32
+    # and back: the packed triples become bf16 weights again, within half a quantisation step of the originals
+    from slime_b200.tools import convert_int4_to_bf16 as back
+
+    restored_dir = str(tmp_path / "bf16")
+    stats2 = back.convert(out, restored_dir, device="cpu")
+    assert stats2["restored"] == stats["quantised"] and "quantization_config" not in json.load(open(os.path.join(restored_dir, "config.json")))
+    with safe_open(os.path.join(restored_dir, "model.safetensors"), framework="pt") as f:
+        names = set(f.keys())
+        assert not any(n.endswith(("weight_packed", "weight_scale", "weight_shape")) for n in names) and names == set(original)
+        got = f.get_tensor(name + ".weight")
+    assert got.dtype == torch.bfloat16 and (got.float() - deq).abs().max() <= deq.abs().max() * 2**-8
 
 
 def test_model_presets_round_trip_through_flags():
