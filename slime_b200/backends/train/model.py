@@ -166,7 +166,7 @@ class TrainModel:
             flat = [p.main_grad for _n, p in self.named_parameters()
                     if getattr(p, "sequence_parallel", False) or getattr(p, "needs_tp_grad_reduce", False)]  # fmt: skip
             # coalesced, at most ~1 GiB per collective (the staging copy of a very large model's norm grads stays bounded)
-            limit, batch, size = 1 << 30, [], 0
+            limit, batch, size = int(os.environ.get("SLIME_GRAD_COALESCE_CHUNK_BYTES", 1 << 30)), [], 0
             for g in flat + [None]:
                 if g is not None:
                     batch.append(g)
