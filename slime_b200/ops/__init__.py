@@ -12,7 +12,7 @@ import os
 
 import torch
 
-from slime_b200.ops import _lib, reference
+from slime_b200.ops import _checks, _lib, reference
 
 P = _lib.ptr
 
@@ -345,6 +345,9 @@ def rope_kv_write(qkv, positions, cos_sin, slots, k_cache, v_cache, Hq, Hkv, D, 
     """Inference path: (per-head RMSNorm +) RoPE on the q and k heads of a packed qkv row IN PLACE, and the new k / v
     rows scattered into cache slot ``slots[t]`` (negative: skipped), as one launch. Returns ``qkv``."""
     T = qkv.shape[0]
+    if _checks.enabled():
+        _checks.index_range("rope_kv_write", "slots", slots, upper=k_cache.shape[0], lower=-(1 << 31))
+        _checks.index_range("rope_kv_write", "positions", positions, upper=cos_sin.shape[0])
     if not _is_cuda(qkv):
         x = qkv.view(T, Hq + 2 * Hkv, D)
         x[:, :Hq] = reference.rope(x[:, :Hq], positions, cos_sin, q_norm_w, eps)
@@ -434,6 +437,8 @@ class _Embedding(torch.autograd.Function):
 
 
 def embedding(ids, table, vocab_lo: int = 0):
+    if _checks.enabled():  # ids of other vocabulary shards are legal (their rows come out as zeros); negatives are not
+        _checks.index_range("embedding", "ids", ids, upper=1 << 31, lower=0)
     return _Embedding.apply(ids.reshape(-1), table, vocab_lo)
 
 
@@ -460,6 +465,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     B, Hq, D = q.shape
     Hkv = k_cache.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if _checks.enabled():
+        _checks.paged("paged_decode_attention", block_table, seq_lens, page_size, k_cache.shape[0])
     if not _is_cuda(q) or D not in (64, 128) or sinks is not None:
         # the decode kernels cover head dims 64 and 128 without sinks; other widths (256: Qwen3-Next / Qwen3.5) and
         # softmax sinks take the plain form
@@ -525,6 +532,8 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
 
 def kv_write(k, v, slots, k_cache, v_cache):
     """Scatter rows ``k[t], v[t]`` ([T, Hkv*D] views, possibly strided) into cache slot ``slots[t]``."""
+    if _checks.enabled():
+        _checks.index_range("kv_write", "slots", slots, upper=k_cache.shape[0], lower=-(1 << 31))
     row = k_cache.shape[1] * k_cache.shape[2]
     if not _is_cuda(k):
         ok = slots >= 0

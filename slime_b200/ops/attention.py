@@ -177,6 +177,9 @@ def segment_attention(q, k, v, seg, scale=None, sinks=None):
     from slime_b200 import ops
 
     scale = scale if scale is not None else 1.0 / math.sqrt(q.shape[-1])
+    from slime_b200.ops import _checks
+
+    _checks.segments("segment_attention", seg, q.shape[0], k.shape[0])
     if not q.is_cuda or q.shape[-1] not in (64, 128):
         # the flash kernels cover head dims 64 and 128; other widths (256 in Qwen3-Next / Qwen3.5) take the explicit form
         return _reference_segments(q, k, v, seg, scale, sinks)

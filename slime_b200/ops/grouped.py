@@ -20,7 +20,7 @@ from __future__ import annotations
 
 import torch
 
-from slime_b200.ops import _lib
+from slime_b200.ops import _checks, _lib
 
 TILE = 128
 P = _lib.ptr
@@ -61,6 +61,7 @@ def route_topk(logits: torch.Tensor, k: int, *, score: str = "softmax", pre_soft
 
 def scatter_rows(x: torch.Tensor, dest: torch.Tensor, k: int, num_rows: int) -> torch.Tensor:
     """``out[dest[s]] = x[s // k]`` for every route slot ``s`` with ``dest[s] >= 0``; other rows of ``out`` are zero."""
+    _checks.index_range("scatter_rows", "dest", dest, upper=num_rows, lower=-(1 << 31))
     out = x.new_zeros(num_rows, x.shape[-1])
     if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
         rc = _lib.lib().sb_moe_scatter_rows(P(x.contiguous()), P(dest), P(out), dest.numel(), k, x.shape[-1], _lib.stream())
@@ -75,6 +76,7 @@ def scatter_rows(x: torch.Tensor, dest: torch.Tensor, k: int, num_rows: int) -> 
 def gather_sum(rows: torch.Tensor, dest: torch.Tensor, weights: torch.Tensor | None, k: int, round_each: bool = False):
     """``y[t] = sum_j weights[t*k+j] * rows[dest[t*k+j]]`` in route order ``j = 0..k-1`` (fp32 accumulation, one writer
     per element: deterministic). Routes with ``dest < 0`` are skipped."""
+    _checks.index_range("gather_sum", "dest", dest, upper=rows.shape[0], lower=-(1 << 31))
     T, H = dest.numel() // k, rows.shape[-1]
     if rows.is_cuda and rows.dtype == torch.bfloat16 and H % 8 == 0:
         y = torch.empty(T, H, dtype=rows.dtype, device=rows.device)
@@ -243,6 +245,7 @@ def grouped_gemm(a: torch.Tensor, w: torch.Tensor, lay, *, b_mn: bool = False, o
     M, K = a.shape
     N = C if b_mn else R
     assert M == lay.rows_padded and E == lay.num_experts and K == (R if b_mn else C)
+    _checks.index_range("grouped_gemm", "tile_expert", lay.tile_expert, upper=E)
     out_dtype = out_dtype or a.dtype
     if not a.is_cuda:
         out = torch.zeros(M, N, dtype=torch.float32)

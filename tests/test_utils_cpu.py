@@ -178,3 +178,36 @@ def test_sample_round_trip_and_response_bookkeeping():
     back = Sample.from_dict(d)
     assert back.tokens == s.tokens and back.loss_mask == s.loss_mask and back.metadata == {"k": 1} and back.status == s.status
     assert math.isclose(sum(back.rollout_log_probs), -0.3)
+
+
+# ------------------------------------------------------------------------------------------------ debug index checks
+def test_debug_mode_catches_bad_indices_before_any_launch(monkeypatch):
+    """SLIME_B200_CHECKS=1: every op with a data-dependent index validates it on the host and names the offender."""
+    from slime_b200 import ops
+    from slime_b200.ops import _checks, attention, grouped
+
+    k_cache, v_cache = torch.zeros(32, 2, 4), torch.zeros(32, 2, 4)
+    good_slots = torch.tensor([0, 5, -1], dtype=torch.int32)
+    k, v = torch.randn(3, 8), torch.randn(3, 8)
+    bt = torch.tensor([[0, 1, 7, 0]], dtype=torch.int32)
+    q = torch.randn(1, 2, 4)
+    # off: the same calls run (or fail later, in the op itself); on: they are refused up front
+    monkeypatch.setenv("SLIME_B200_CHECKS", "1")
+    ops.kv_write(k, v, good_slots, k_cache, v_cache)  # -1 = "skip this row" stays legal
+    with pytest.raises(_checks.IndexCheckError, match=r"kv_write: slots\[1\] = 99 is outside"):
+        ops.kv_write(k, v, torch.tensor([0, 99, 1], dtype=torch.int32), k_cache, v_cache)
+    ops.paged_decode_attention(q, k_cache, v_cache, bt, torch.tensor([9], dtype=torch.int32), 4)
+    with pytest.raises(_checks.IndexCheckError, match=r"block_table\[0, 2\] = 9 is not one of the cache's 8 pages"):
+        ops.paged_decode_attention(q, k_cache, v_cache, torch.tensor([[0, 1, 9, 0]], dtype=torch.int32), torch.tensor([9], dtype=torch.int32), 4)
+    with pytest.raises(_checks.IndexCheckError, match="does not fit a block table of 16 tokens"):
+        ops.paged_decode_attention(q, k_cache, v_cache, bt, torch.tensor([17], dtype=torch.int32), 4)
+    # an entry past the used length is never read, so it may hold anything
+    ops.paged_decode_attention(q, k_cache, v_cache, torch.tensor([[0, 1, 99, 99]], dtype=torch.int32), torch.tensor([8], dtype=torch.int32), 4)
+    with pytest.raises(_checks.IndexCheckError, match="embedding: ids"):
+        ops.embedding(torch.tensor([3, -2]), torch.randn(8, 4))
+    with pytest.raises(_checks.IndexCheckError, match="scatter_rows: dest"):
+        grouped.scatter_rows(torch.randn(2, 8), torch.tensor([0, 7], dtype=torch.int32), 1, 4)
+    with pytest.raises(_checks.IndexCheckError, match=r"segment 0 covers key rows \[2, 9\) of 6"):
+        attention.segment_attention(torch.randn(6, 2, 4), torch.randn(6, 1, 4), torch.randn(6, 1, 4), torch.tensor([[0, 3, 2, 7]], dtype=torch.int32))
+    monkeypatch.setenv("SLIME_B200_CHECKS", "0")
+    _checks.index_range("x", "y", torch.tensor([5]), upper=2)  # switched off: no check, no cost
