@@ -260,3 +260,69 @@ def test_tau_style_tool_agent_masks_environment_turns_and_takes_the_env_reward(e
     env.step({"name": "cancel_order", "arguments": {"order_id": "W200"}})
     env.step({"name": "respond", "arguments": {"content": "done"}})
     assert env.step({"name": "respond", "arguments": {"content": "bye"}}) == ("###STOP###", 0.0, True)
+
+
+def test_message_level_agent_keeps_the_exact_token_trajectory(engine):
+    from examples.strands_sglang import generate_with_strands as ex
+    from examples.strands_sglang import token_agent as ta
+
+    args, state, tok = engine
+
+    def template(messages, tokenize=True, add_generation_prompt=True, tools=None):
+        parts = []
+        for m in messages:
+            body = m.get("content") or ""
+            for c in m.get("tool_calls", []):
+                body += " <tool_call> " + '{"name": "' + c["function"]["name"] + '", "arguments": ' + c["function"]["arguments"].replace(" ", "") + "} </tool_call>"
+            parts.append(f"<|{m['role']}|> {body}")
+        return tok.encode(" ".join(parts) + (" <|assistant|>" if add_generation_prompt else ""))
+
+    tok.apply_chat_template = template
+    spec = ex.execute_python_code.tool_spec["function"]
+    assert spec["name"] == "execute_python_code" and spec["parameters"]["required"] == ["code"]
+    assert spec["parameters"]["properties"]["code"] == {"type": "string"}
+
+    def script(prompt):
+        if "<|tool|> 42" in prompt:
+            return "So the answer is \\boxed{42}"
+        return '<tool_call> {"name": "execute_python_code", "arguments": {"code":"print(6*7)"}} </tool_call>'
+
+    state["script"] = script
+    out = asyncio.run(ex.generate(args, Sample(index=0, prompt="What is 6 times 7 ?", label="42"), {"max_new_tokens": 200}))
+    assert out.status == Sample.Status.COMPLETED and out.metadata == {"tool_iters": 1, "tool_calls": 1}
+    assert len(out.loss_mask) == out.response_length == len(out.rollout_log_probs) == len(out.tokens) - 0 - (len(out.tokens) - out.response_length)
+    trained = tok.decode([t for t, m in zip(out.tokens[-out.response_length:], out.loss_mask) if m])
+    assert "print(6*7)" in trained and "\\boxed{42}" in trained and "<|tool|>" not in trained
+    context = tok.decode([t for t, m in zip(out.tokens[-out.response_length:], out.loss_mask) if not m])
+    assert "<|tool|> 42" in context
+    assert all(lp == -0.5 for lp, m in zip(out.rollout_log_probs, out.loss_mask) if m) and all(lp == 0.0 for lp, m in zip(out.rollout_log_probs, out.loss_mask) if not m)
+    assert tok.decode(out.tokens[: len(out.tokens) - out.response_length]).startswith("<|system|> You are a helpful")
+    # the second request carried the first turn's ids unchanged (no re-tokenisation): its prompt extends the first one
+    p1, p2 = state["calls"][0][0], state["calls"][1][0]
+    assert p2.startswith(p1) and p2[len(p1):].lstrip().startswith("<tool_call>")
+    assert asyncio.run(ex.reward_func(args, out)) == 1.0
+
+    # a model that keeps calling the tool is stopped by the limiter and kept as truncated, with a softened penalty
+    state["script"] = lambda prompt: '<tool_call> {"name": "execute_python_code", "arguments": {"code":"print(1)"}} </tool_call>'
+    args.strands_max_tool_iters = 3
+    out = asyncio.run(ex.generate(args, Sample(index=1, prompt="loop", label="7"), {"max_new_tokens": 400}))
+    assert out.status == Sample.Status.TRUNCATED and out.metadata["tool_iters"] == 3
+    assert sum(out.loss_mask) > 0 and len(out.loss_mask) == out.response_length
+    assert asyncio.run(ex.reward_func(args, out)) == pytest.approx(-0.95)
+    out.metadata["tool_iters"] = 20
+    assert asyncio.run(ex.reward_func(args, out)) == -0.6  # never better than -0.6
+
+    # the token budget is what is left of max_new_tokens after everything appended so far
+    state["script"] = script
+    state["calls"].clear()
+    out = asyncio.run(ex.generate(args, Sample(index=2, prompt="What is 6 times 7 ?", label="42"), {"max_new_tokens": 50}))
+    budgets = [c[1]["max_new_tokens"] for c in state["calls"]]
+    assert budgets[0] == 50 and budgets[-1] < 50 - 5  # (a retried request may repeat an entry)
+
+    # unknown tools and failing tools come back as observations
+    async def bad_tools():
+        agent = ta.ToolAgent(ta.TokenTrackingModel(tok, "http://unused", {}), tools=[ex.execute_python_code])
+        return await agent._run_tool({"name": "nope", "arguments": {}}), await agent._run_tool({"name": "execute_python_code", "arguments": {"bad": 1}})
+
+    a, b = asyncio.run(bad_tools())
+    assert a.startswith("Error: unknown tool") and b.startswith("Error: TypeError")
