@@ -51,7 +51,8 @@ class Engine:
         if tokenizer is not None and getattr(tokenizer, "eos_token_id", None) is not None:
             self.eos_ids.add(tokenizer.eos_token_id)
         self.weights = EngineWeights(cfg, self.dtype, self.device, tp_size, tp_rank, ep_size=min(self.args.ep_size, tp_size),
-                                     quantization=self.args.quantization)
+                                     quantization=self.args.quantization,
+                                     draft_layers=min(cfg.mtp_num_layers or 0, 1) if self.args.speculative_algorithm else 0)
         self.max_context = self.args.context_length or min(cfg.max_position_embeddings, 32768)
         self.page_size = self.args.page_size
         self.max_running = self.args.max_running_requests
@@ -75,6 +76,11 @@ class Engine:
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0, "aborted": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "decode_steps": 0}  # fmt: skip
         self._init_decode_state()
+        self.spec = None  # host-driven speculative rounds instead of the slot-based decode loop
+        if self.args.speculative_algorithm:
+            from slime_b200.engine.speculative import SpeculativeDecoder
+
+            self.spec = SpeculativeDecoder(self)
 
     def _kv_geometry(self):
         """(heads, key width, value width) of one cached token: latent attention caches a single vector per token (the
@@ -86,7 +92,7 @@ class Engine:
 
     def _num_kv_layers(self) -> int:
         """Layers that keep keys and values (delta-net layers keep a recurrent state per decode slot instead)."""
-        return sum(1 for L in self.weights.layers if L["kind"] in ("attention", "mla"))
+        return sum(1 for L in self.weights.layers + self.weights.draft if L["kind"] in ("attention", "mla"))
 
     # ----------------------------------------------------------------- sizing
     def _pages_from_memory(self) -> int:
@@ -161,7 +167,7 @@ class Engine:
             if batch:
                 return self._run_prefill(batch)
             if self.running:
-                return self._run_decode()
+                return self.spec.decode_round() if self.spec is not None else self._run_decode()
             return []
 
     def _admit(self) -> list[tuple[Request, int]]:
@@ -255,8 +261,8 @@ class Engine:
                 self.prefilling.append(req)
         rows = None if want_all_rows else t(last_rows, torch.long)
         states = [getattr(req, "gdn_state", None) for req, _ in batch] if self.runner.has_gdn else None
-        logits = self.runner.prefill(t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long),
-                                     t(cu_k), max_q, max_k, rows, fresh, gdn_states=states)  # fmt: skip
+        dev_in = (t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long), t(cu_k))
+        logits = self.runner.prefill(*dev_in, max_q, max_k, rows, fresh, gdn_states=states)
         if self.runner.has_gdn:
             for (req, _), st in zip(batch, self.runner.last_gdn_states):
                 req.gdn_state = st
@@ -292,6 +298,8 @@ class Engine:
                     finished.append(req)
                 else:
                     self._start_decoding(req)
+        if self.spec is not None:
+            self.spec.after_prefill(batch, dev_in, cu_q, max_q, max_k, fresh)
         return finished
 
     # ------------------------------------------------------ prefill / decode disaggregation
@@ -311,6 +319,8 @@ class Engine:
         ``export_kv`` returned there (any device); it is written into freshly allocated pages and the request starts
         decoding from ``first_token`` without a prefill pass here. Same role as the prefill -> decode KV hand-over of
         the reference's PD-disaggregated rollout servers (slime/ray/rollout.py:46-219, worker types prefill / decode)."""
+        if self.spec is not None:
+            raise NotImplementedError("a speculating engine cannot adopt a prompt: the draft head's keys are not part of the hand-over")
         sp = sampling if isinstance(sampling, SamplingParams) else SamplingParams.from_dict(sampling)
         req = Request(rid=rid or uuid.uuid4().hex, input_ids=list(input_ids), sampling=sp, **kw)
         self._req_counter = getattr(self, "_req_counter", 0) + 1
@@ -375,6 +385,10 @@ class Engine:
 
     def _start_decoding(self, r: Request):
         """Give the request a decode slot; its first input token and position reach the device with the next upload."""
+        if self.spec is not None:  # speculative rounds are driven from the request's own lists: no slot, no device state
+            r.slot, r.end_step = None, None
+            self.running.append(r)
+            return
         b = heapq.heappop(self.free_slots)
         h = self.runner.host
         L = r.seq_len
@@ -401,6 +415,10 @@ class Engine:
         self.runner.host["block_table"][b, :] = 0
 
     def _release_slot(self, r: Request):
+        if r.slot is None:  # a request of the speculative loop
+            if r in self.running:
+                self.running.remove(r)
+            return
         b = r.slot
         self._deactivate(b)
         self.slot_req[b] = None
@@ -584,6 +602,7 @@ class Engine:
         self._release_slot(req)
         req.routed_experts = []  # the re-prefill computes every position again
         req.gdn_state = None
+        req.spec_draft, req.spec_hidden = [], None
         self.kv.allocator.release(req.pages)
         req.pages, req.num_computed, req.committed_pages, req.chain_hash = [], 0, 0, b""
         req.state = ReqState.WAITING
@@ -697,7 +716,8 @@ class Engine:
                         self.kv.allocator.free.remove(0)
                         self.kv.allocator.refcnt[0] = 1
                 elif tag == "weights":
-                    fresh = EngineWeights(self.cfg, self.dtype, self.device, self.weights.tp, self.weights.rank)
+                    fresh = EngineWeights(self.cfg, self.dtype, self.device, self.weights.tp, self.weights.rank, ep_size=self.weights.ep,
+                                          quantization=self.weights.quantization, draft_layers=self.weights.num_draft_layers)
                     fresh.version = self.weights.version
                     self.weights = fresh
                     self.runner.w = fresh

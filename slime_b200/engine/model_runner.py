@@ -23,13 +23,17 @@ from slime_b200.models.config import ModelConfig
 logger = logging.getLogger(__name__)
 
 _LAYER_RE = re.compile(r"^model\.layers\.(\d+)\.(.+)$")
+_MIMO_DRAFT_RE = re.compile(r"^model\.mtp_layers\.(\d+)\.(.+)$")
 
 
 class EngineWeights:
     """Fused, TP-sharded weight buffers addressed by Hugging Face names."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device, tp_size=1, tp_rank=0, ep_size=1, quantization: str | None = None):
-        """``quantization="fp8"`` keeps the projection matrices whose shapes allow it as block-scaled e4m3
+    def __init__(self, cfg: ModelConfig, dtype, device, tp_size=1, tp_rank=0, ep_size=1, quantization: str | None = None,
+                 draft_layers: int = 0):
+        """``draft_layers``: how many multi-token-prediction depths (checkpoint layers ``num_layers + k``) to keep for
+        speculative decoding; 0 ignores them.
+        ``quantization="fp8"`` keeps the projection matrices whose shapes allow it as block-scaled e4m3
         (``engine/quant.py``); embeddings, the LM head, routers, norms and biases stay in ``dtype``.
         ``ep_size`` is 1 (every rank holds all experts and computes all routes) or ``tp_size`` (rank r holds experts
         ``r*E/ep ... (r+1)*E/ep - 1`` at full width; the ranks' expert outputs are summed like any row-parallel
@@ -64,7 +68,9 @@ class EngineWeights:
         self.lm_head = self.embed if cfg.tie_word_embeddings else e(self.vocab_local, h)
         self.final_norm = e(h)
         self.layers = []
-        for i in range(cfg.num_layers):
+        self.draft = []  # draft heads: an ordinary layer plus the two input norms, the joining projection and a final norm
+        self.num_draft_layers = draft_layers
+        for i in range(cfg.num_layers + draft_layers):
             kind = cfg.mixer(i)
             if kind not in ("attention", "general_attention", "gated_delta_net", "mla", "dsa"):
                 raise NotImplementedError(f"the rollout engine has no layer of kind {kind!r} (layer {i})")
@@ -119,7 +125,13 @@ class EngineWeights:
                         L["shared_gate"] = e(1, h)
             else:
                 L.update(gate_up=mat(2 * self.f, h, parts=(self.f,)), down=mat(h, self.f))
-            self.layers.append(L)
+            if i >= cfg.num_layers:
+                if L["kind"] == "gdn" or kind == "dsa":
+                    raise NotImplementedError(f"a draft head with a {kind} mixer is not supported by the rollout engine")
+                L.update(enorm=e(h), hnorm=e(h), eh_proj=e(h, 2 * h), final_ln=e(h))
+                self.draft.append(L)
+            else:
+                self.layers.append(L)
         self.version = "default"
 
     def _attention_buffers(self, e, mat, h, d, full_norm):
@@ -151,7 +163,7 @@ class EngineWeights:
         yield self.embed
         yield self.lm_head
         yield self.final_norm
-        for L in self.layers:
+        for L in self.layers + self.draft:
             for v in L.values():
                 if v is None or isinstance(v, (str, int)):  # absent buffers, the layer's kind tag, the indexer's source layer
                     continue
@@ -186,13 +198,36 @@ class EngineWeights:
         if name == "model.norm.weight":
             self.final_norm.copy_(t + plus1)
             return True
+        mimo = _MIMO_DRAFT_RE.match(name)
+        if mimo is not None:
+            # MiMo stores its draft head outside the layer list, the joining projection's halves as (hidden, embedding)
+            depth, sub = int(mimo.group(1)), mimo.group(2)
+            if depth >= len(self.draft):
+                return True
+            if sub == "input_proj.weight":
+                h_half, e_half = t.chunk(2, dim=1)
+                self.draft[depth]["eh_proj"].copy_(torch.cat([e_half, h_half], dim=1))
+                return True
+            own = {"token_layernorm.weight": "enorm.weight", "hidden_layernorm.weight": "hnorm.weight",
+                   "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip
+            return self.load_weight(f"model.layers.{len(self.layers) + depth}.{own.get(sub, sub)}", raw)
         m = _LAYER_RE.match(name)
         if m is None:
             return False
-        if int(m.group(1)) >= len(self.layers):
-            return True  # a draft (multi-token-prediction) depth stored as an extra layer: this engine does not run it
-        L = self.layers[int(m.group(1))]
         sub = m.group(2)
+        if int(m.group(1)) >= len(self.layers):
+            # a draft (multi-token-prediction) depth stored as an extra layer (DeepSeek-V3 layout): kept only when the
+            # engine speculates; its copies of the embedding and the output head are the trunk's
+            depth = int(m.group(1)) - len(self.layers)
+            if depth >= len(self.draft) or sub in ("embed_tokens.weight", "shared_head.head.weight"):
+                return True
+            L = self.draft[depth]
+            own = {"enorm.weight": "enorm", "hnorm.weight": "hnorm", "eh_proj.weight": "eh_proj", "shared_head.norm.weight": "final_ln"}
+            if sub in own:
+                L[own[sub]].copy_(t)
+                return True
+        else:
+            L = self.layers[int(m.group(1))]
         hq, hkv = self.hq, self.hkv
         q_rows, kv_rows = hq * d, hkv * d
         if sub.startswith("linear_attn."):
@@ -328,7 +363,7 @@ class EngineWeights:
         from slime_b200.engine.quant import Fp8Weight
 
         g = torch.Generator(device=self.device).manual_seed(seed)
-        quantised = [v for L in self.layers for v in L.values() if isinstance(v, Fp8Weight)]
+        quantised = [v for L in self.layers + self.draft for v in L.values() if isinstance(v, Fp8Weight)]
         for L in self.layers:  # the decay parameter of delta-net layers must start in its valid range
             if "gdn_A_log" in L:
                 L["gdn_A_log"].copy_(torch.empty_like(L["gdn_A_log"]).uniform_(1e-3, 16.0, generator=g).log())
@@ -342,7 +377,7 @@ class EngineWeights:
                 t.copy_(torch.empty(t.shape, dtype=torch.float32, device=self.device).normal_(0, std, generator=g))
         for v in quantised:
             v.fill_random_(std, g)
-        for L in self.layers:
+        for L in self.layers + self.draft:
             if L.get("qkv_bias") is not None:
                 L["qkv_bias"].zero_()
 
@@ -392,7 +427,7 @@ class ModelRunner:
                     logger.warning("fused tensor-parallel all-reduce unavailable (%r): using NCCL", e)
         # KV slabs exist for the attention layers only; gated delta-net layers keep a recurrent state per decode slot
         self.kv_of, n_attn = [], 0
-        for L in weights.layers:
+        for L in weights.layers + weights.draft:  # a draft head's layer number is num_layers + depth
             self.kv_of.append(n_attn if L["kind"] in ("attention", "mla") else None)
             n_attn += L["kind"] in ("attention", "mla")
         self.has_mla = any(L["kind"] == "mla" for L in weights.layers)
@@ -428,6 +463,7 @@ class ModelRunner:
                                            device=self.device)  # fmt: skip
         self._routed: list[torch.Tensor] = []
         self.last_routed = None
+        self.last_hidden = None  # residual stream before the final norm of the last prefill pass, all rows (draft heads read it)
 
     def take_routed(self):
         """``[T, layers, k]`` int32 expert ids of the pass just run, one column per layer of the model (zeros for dense
@@ -787,10 +823,55 @@ class ModelRunner:
             x = self._post_norm(x, L["post_attn_ln"])
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._post_norm(self._mlp(L, normed), L["post_mlp_ln"])
-        h, _ = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
+        h, self.last_hidden = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
         if last_rows is not None:
             h = h.index_select(0, last_rows)
         return self._gather_logits(ops.gemm(h, w.lm_head, out_dtype=torch.float32))
+
+    @torch.no_grad()
+    def draft_extend(self, depth: int, hidden, next_ids, positions, slots, cu_q, kv_gather_slots, cu_k, max_q, max_k, fresh: bool):
+        """Draft head ``depth`` over packed rows: row p joins the residual stream ``hidden[p]`` the trunk (or the previous
+        draft step) left at position p with the embedding of the token at position p + 1, runs one transformer layer with
+        its own cache slab (written at ``slots``) and returns ``(normed [T, H], stream [T, H])``: the first feeds the shared
+        output head (a guess for the token at position p + 2), the second is the next draft step's ``hidden``. Same
+        computation as ``models/gpt.py::MTPLayer``; arguments as in ``prefill``."""
+        cfg, w, d, eps = self.cfg, self.w, self.cfg.head_dim, self.cfg.norm_epsilon
+        L, li = w.draft[depth], cfg.num_layers + depth
+        recording, self.record_routed = self.record_routed, False  # a draft head's routing is nobody's training signal
+        try:
+            emb = ops.embedding(next_ids, w.embed, w.rank * w.vocab_local)
+            emb = self._tp_reduce(emb) if w.tp > 1 else emb
+            e_n = ops.rmsnorm(emb, L["enorm"], eps)[0]
+            h_n = ops.rmsnorm(hidden.to(emb.dtype), L["hnorm"], eps)[0]
+            x = ops.gemm(torch.cat([e_n, h_n], dim=-1), L["eh_proj"])
+            T = x.shape[0]
+            normed, res = ops.rmsnorm(x, L["ln1"], eps, None)
+            if L["kind"] == "mla":
+                ctx = self._mla_prefill(L, li, normed, positions, slots, cu_q, kv_gather_slots, cu_k, fresh)
+                x = self._tp_reduce(_linear(ctx, L["o"], out_dtype=self._proj_dtype))
+            else:
+                qkv = self._qkv(L, normed, positions, slots, li)
+                q3 = qkv.view(T, w.hq + 2 * w.hkv, d)
+                q, k, v = q3[:, : w.hq], q3[:, w.hq : w.hq + w.hkv], q3[:, w.hq + w.hkv :]
+                if fresh:
+                    ctx = ops.varlen_attention(q, k, v, cu_q, max_q, self.scale, sinks=L.get("sinks"))
+                else:
+                    k_all = self.kv.k[self.kv_of[li]].index_select(0, kv_gather_slots)
+                    v_all = self.kv.v[self.kv_of[li]].index_select(0, kv_gather_slots)
+                    ctx = _extend_attention(q, k_all, v_all, cu_q, cu_k, max_q, max_k, self.scale, sinks=L.get("sinks"))
+                ctx = ctx.reshape(T, -1)
+                if "gate" in L:
+                    ctx = ctx * torch.sigmoid(ops.gemm(normed, L["gate"]).float()).to(ctx.dtype)
+                x = self._post_norm(self._tp_reduce(_linear(ctx, L["o"], out_dtype=self._proj_dtype)), L["post_attn_ln"])
+            normed, res = ops.rmsnorm(x, L["ln2"], eps, res)
+            x = self._post_norm(self._mlp(L, normed), L["post_mlp_ln"])
+            return ops.rmsnorm(x, L["final_ln"], eps, res)
+        finally:
+            self.record_routed = recording
+
+    def logits_of(self, normed):
+        """Output head over already normalised rows -> fp32 logits over the whole vocabulary."""
+        return self._gather_logits(ops.gemm(normed, self.w.lm_head, out_dtype=torch.float32))
 
     # ---------------------------------------------------------------------- decode
     # Per-slot decode state is device-owned (ids / pos / out_pos): the token sampled in step t is the

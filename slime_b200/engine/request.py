@@ -94,6 +94,9 @@ class Request:
     harvested: int = 0
     end_step: int | None = None
     end_reason: dict | None = None
+    # speculative decoding (engine/speculative.py): guesses for the tokens after the last one, the draft head's stream
+    spec_draft: list[int] = field(default_factory=list)
+    spec_hidden: Any = None
 
     @property
     def seq_len(self) -> int:

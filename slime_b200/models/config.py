@@ -100,7 +100,7 @@ class ModelConfig:
         if f is None:
             return True
         if isinstance(f, (list, tuple)):
-            return bool(f[layer])
+            return bool(f[min(layer, len(f) - 1)])  # draft depths (layer >= num_layers) follow the last layer
         return layer % f == 0
 
     def mixer(self, layer: int) -> str:

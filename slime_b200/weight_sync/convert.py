@@ -23,6 +23,8 @@ from slime_b200.models.config import ModelConfig
 _LAYER = re.compile(r"^decoder\.layers\.(\d+)\.(.+)$")
 _EXPERT = re.compile(r"^mlp\.experts\.linear_fc([12])\.weight(\d+)$")
 _MTP = re.compile(r"^mtp\.layers\.(\d+)\.(.+)$")
+_MIMO_MTP = {"enorm.weight": "token_layernorm.weight", "hnorm.weight": "hidden_layernorm.weight",
+             "final_layernorm.weight": "final_layernorm.weight"}  # fmt: skip
 
 
 def split_qkv(cfg: ModelConfig, t: torch.Tensor):
@@ -138,8 +140,19 @@ def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[st
         return [("model.norm.weight", t - 1 if _zero_centred(cfg) else t)]
     mm = _MTP.match(name)
     if mm is not None:
-        # DeepSeek-V3 layout: draft depth k is checkpoint layer num_layers + k, with its own norms and projection
         k, sub = int(mm.group(1)), mm.group(2)
+        if _family(cfg) == "mimo":
+            # MiMo layout: model.mtp_layers.k.*, the joining projection's column halves in (hidden, embedding) order
+            # (slime/backends/megatron_utils/megatron_to_hf/mimo.py:18-75 in the reference)
+            p = f"model.mtp_layers.{k}"
+            if sub == "eh_proj.weight":
+                e_half, h_half = t.chunk(2, dim=1)
+                return [(f"{p}.input_proj.weight", torch.cat([h_half, e_half], dim=1))]
+            if sub in _MIMO_MTP:
+                return [(f"{p}.{_MIMO_MTP[sub]}", t)]
+            assert sub.startswith("transformer_layer."), name
+            return [(n.replace(f"model.layers.{k}.", f"{p}.", 1), x) for n, x in _layer_to_hf(cfg, str(k), sub[len("transformer_layer.") :], t)]
+        # DeepSeek-V3 layout: draft depth k is checkpoint layer num_layers + k, with its own norms and projection
         i = str(cfg.num_layers + k)
         p = f"model.layers.{i}"
         own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
@@ -270,6 +283,14 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
     mm = _MTP.match(name)
     if mm is not None:
         k, sub = int(mm.group(1)), mm.group(2)
+        if _family(cfg) == "mimo":
+            p = f"model.mtp_layers.{k}"
+            if sub == "eh_proj.weight":
+                return [f"{p}.input_proj.weight"], "swap_halves"
+            if sub in _MIMO_MTP:
+                return [f"{p}.{_MIMO_MTP[sub]}"], "copy"
+            names, rule = hf_sources_for(cfg, f"decoder.layers.{k}.{sub[len('transformer_layer.'):]}")
+            return [n.replace(f"model.layers.{k}.", f"{p}.", 1) for n in names], rule
         p = f"model.layers.{cfg.num_layers + k}"
         own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
                "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip
@@ -337,6 +358,9 @@ def merge_hf_sources(rule: str, tensors: list[torch.Tensor], cfg: ModelConfig | 
         return tensors[0]
     if rule == "copy+1":  # zero-centred norm weight -> effective weight
         return tensors[0] + 1
+    if rule == "swap_halves":  # MiMo's joining projection: (hidden, embedding) columns -> (embedding, hidden)
+        a, b = tensors[0].chunk(2, dim=1)
+        return torch.cat([b, a], dim=1)
     if rule == "conv":  # depthwise Conv1d weight [C, 1, K] -> [C, K]
         return tensors[0].squeeze(1)
     if rule == "gated_qkv":  # q_proj rows are per head (query, gate)

@@ -85,6 +85,7 @@ def main():
                                      moe_ffn_hidden_size=256, moe_router_topk=2, moe_layer_freq=[0, 1, 1],
                                      moe_router_score_function="sigmoid", moe_router_enable_expert_bias=True,
                                      moe_shared_expert_intermediate_size=256, moe_router_num_groups=4, moe_router_group_topk=2),
+                 "mtp_moe": dict(qk_layernorm=True, num_experts=8, moe_ffn_hidden_size=256, moe_router_topk=2, mtp_num_layers=1),
                  "qwen3_next": dict(full_attention_interval=3, linear_num_key_heads=4, linear_num_value_heads=8,
                                     linear_key_head_dim=32, linear_value_head_dim=32, attention_output_gate=True, qk_layernorm=True,
                                     rotary_percent=0.25, model_arch="Qwen3NextForCausalLM")}[family]  # fmt: skip
@@ -107,7 +108,9 @@ def main():
     prompts = [[(7 * i + 3 * j) % cfg.vocab_size for j in range(5 + i)] for i in range(6)]
     sp = dict(max_new_tokens=24, temperature=0)
 
-    tp = Engine(cfg, ServerArgs(**sargs), device=dev, num_pages=128, tp_group=dist.group.WORLD, tp_size=world, tp_rank=rank)
+    # with a draft head: the tensor-parallel engine speculates, the single-rank reference decodes token by token
+    spec = dict(speculative_algorithm="EAGLE", speculative_num_steps=2, speculative_num_draft_tokens=3) if cfg.mtp_num_layers else {}
+    tp = Engine(cfg, ServerArgs(**sargs, **spec), device=dev, num_pages=128, tp_group=dist.group.WORLD, tp_size=world, tp_rank=rank)
     missing = tp.weights.load_weights(weights)
     assert not missing, missing
     fused = tp.runner._fused_tp is not None

@@ -191,8 +191,8 @@ def test_openai_compatible_endpoints():
 
 
 @pytest.mark.parametrize("moe,family", [(False, None), (True, None), (False, "glm4"), (False, "minimax_m2"), (False, "deepseek_v3"),
-                                        (False, "qwen3_next")],
-                         ids=["dense", "moe_ep2", "glm4", "minimax_m2_ep2", "deepseek_v3_ep2", "qwen3_next"])  # fmt: skip
+                                        (False, "qwen3_next"), (False, "mtp_moe")],
+                         ids=["dense", "moe_ep2", "glm4", "minimax_m2_ep2", "deepseek_v3_ep2", "qwen3_next", "speculative_moe_ep2"])  # fmt: skip
 def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe, family):
     """Two gloo ranks: TP weight slicing, row-parallel reductions and the vocab-parallel logits gather (host logic);
     with ``moe`` also experts sharded over the two ranks (each rank serves its own experts' routes, outputs summed)."""
@@ -205,7 +205,7 @@ def test_tensor_parallel_engine_on_gloo_matches_single_rank(moe, family):
     if family:
         env["ENGINE_TP_CHECK_FAMILY"] = family
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-                        "127.0.0.1", "--master-port", str(29671 + int(moe) + {None: 0, "glm4": 2, "minimax_m2": 3, "deepseek_v3": 4, "qwen3_next": 5}[family]), os.path.join(root, "tests/multigpu/engine_tp_check.py")],
+                        "127.0.0.1", "--master-port", str(29671 + int(moe) + {None: 0, "glm4": 2, "minimax_m2": 3, "deepseek_v3": 4, "qwen3_next": 5, "mtp_moe": 6}[family]), os.path.join(root, "tests/multigpu/engine_tp_check.py")],
                        env=env, cwd=root, capture_output=True, text=True, timeout=280)  # fmt: skip
     assert r.returncode == 0 and "RESULT ok world=2" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
