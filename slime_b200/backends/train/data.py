@@ -94,6 +94,10 @@ def get_batch(data_iterator: DataIterator, keys, pad_multiplier: int = 128, pad_
     batch["tokens"] = tokens.unsqueeze(0)
     batch["position_ids"] = positions.unsqueeze(0)
 
+    mm = [d for d in (batch.get("multimodal_train_inputs") or []) if d]
+    if mm:  # processor outputs of the samples that carry images, concatenated in stream order (model kwargs)
+        batch["multimodal"] = {k: torch.cat([torch.as_tensor(d[k]) for d in mm if d.get(k) is not None]).to(device)
+                               for k in sorted({k for d in mm for k in d}) if any(d.get(k) is not None for d in mm)}  # fmt: skip
     if batch.get("loss_masks") is not None:
         full = []
         for m, tl, rl in zip(batch["loss_masks"], batch["total_lengths"], batch["response_lengths"]):

@@ -208,7 +208,7 @@ def forward_only(f, args, model: TrainModel, data_iterator: list[DataIterator], 
 
     def forward_step(batch, chunk, input_tensor):
         chunk.set_input_tensor(input_tensor)
-        out = chunk(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"],
+        out = chunk(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"], **batch.get("multimodal", {}),
                     return_hidden=use_fused)  # fmt: skip
         if not chunk.post_process:
             return out, None
@@ -342,7 +342,7 @@ def train_one_step(args, rollout_id, step_id, data_iterator, model: TrainModel, 
 
     def forward_step(batch, chunk, input_tensor):
         chunk.set_input_tensor(input_tensor)
-        out = chunk(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"], return_hidden=fused)
+        out = chunk(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"], **batch.get("multimodal", {}), return_hidden=fused)
         if not chunk.post_process:
             return out, None
         if fused:

@@ -57,6 +57,12 @@ class ModelConfig:
     attention_output_gate: bool = False  # Qwen3-Next: q projection carries a sigmoid gate for the attention output
     qk_layernorm_full: bool = False  # MiniMax-M2: RMSNorm over all heads of q (and of k) at once instead of per head
     softmax_sinks: bool = False  # learnable per-head sink logit in the softmax denominator
+    # vision inputs (models/vision.py): the encoder's own config, the placeholder token ids, and multi-axis rotary positions
+    vision: dict | None = None
+    image_token_id: int | None = None
+    video_token_id: int | None = None
+    mrope_section: list | None = None  # rotary frequency bands per position stream (temporal, height, width)
+    mrope_interleaved: bool = True  # bands of the three streams interleaved (Qwen3-VL / Qwen3.5) or one after another (Qwen2-VL)
     # gated delta-net linear attention (Qwen3-Next / Qwen3.5): layers with (i + 1) % full_attention_interval != 0
     full_attention_interval: int | None = None
     linear_num_key_heads: int | None = None
@@ -111,7 +117,7 @@ class ModelConfig:
         if self.multi_latent_attention:
             return "dsa" if self.index_topk else "mla"
         if (self.rotary_percent < 1.0 or self.rotary_interleaved or self.attention_output_gate or self.qk_layernorm_full
-                or self.softmax_sinks):  # fmt: skip
+                or self.softmax_sinks or self.mrope_section):  # fmt: skip
             return "general_attention"
         return "attention"
 
@@ -172,8 +178,12 @@ class ModelConfig:
         else:
             with open(os.path.join(path_or_dict, "config.json")) as f:
                 c = json.load(f)
+        top = c
         c = c.get("text_config", c)
-        arch = (c.get("architectures") or [c.get("model_type", "qwen2")])[0]
+        arch = (c.get("architectures") or top.get("architectures") or [c.get("model_type", "qwen2")])[0]
+        rp = c.get("rope_parameters") or {}
+        if rp:  # newer configs keep every rotary setting in one dict
+            c = {**c, **{k: v for k, v in rp.items() if k in ("rope_theta", "partial_rotary_factor")}}
         a = arch.lower()
         kw = dict(
             num_layers=c["num_hidden_layers"],
@@ -242,6 +252,11 @@ class ModelConfig:
             kw["rotary_scaling_factor"] = float(rs["factor"])
         if "minimax" in a:
             kw.update(qk_layernorm=False, qk_layernorm_full=bool(c.get("use_qk_norm", True)))
+        section = rp.get("mrope_section") or rs.get("mrope_section")
+        if top.get("vision_config") is not None:
+            kw.update(vision=dict(top["vision_config"]), image_token_id=top.get("image_token_id"), video_token_id=top.get("video_token_id"))
+            if section:
+                kw.update(mrope_section=list(section), mrope_interleaved=bool(rp.get("mrope_interleaved", rs.get("mrope_interleaved", "qwen2" not in a))))
         return cls(**kw)
 
     def to_hf_dict(self) -> dict:

@@ -51,6 +51,7 @@ class PackedSeqParams:
         self.cu_seqlens_q = self.cu_seqlens_kv = self.cu_seqlens = cu_seqlens
         self.max_seqlen_q = self.max_seqlen_kv = self.max_seqlen = int(max_seqlen)
         self.position_ids = position_ids
+        self.mrope_positions = None  # [3, T] temporal / height / width streams when the batch carries images
         self.qkv_format = "thd"
 
 
@@ -319,6 +320,11 @@ class GPTModel(nn.Module):
             self.mtp = nn.Module()
             self.mtp.layers = nn.ModuleList([MTPLayer(cfg, cfg.num_layers + k, dtype, device, self.sequence_parallel)
                                              for k in range(cfg.mtp_num_layers)])  # fmt: skip
+        self.vision = None
+        if cfg.vision is not None and pre_process:
+            from slime_b200.models.vision import VisionConfig, VisionTower
+
+            self.vision = VisionTower(VisionConfig.from_dict(cfg.vision), dtype, device)
         self.mtp_training = False  # set by the trainer (--enable-mtp-training): keep what the draft loss needs
         self._mtp_inputs = None
         self._rope = None
@@ -343,14 +349,17 @@ class GPTModel(nn.Module):
         self.input_tensor = t
 
     # ------------------------------------------------------------------ forward
-    def forward_hidden(self, input_ids, position_ids, packed: PackedSeqParams):
+    def forward_hidden(self, input_ids, position_ids, packed: PackedSeqParams, vision_rows=None):
         """Runs this stage's layers; returns the final-normed hidden states on the last stage,
-        else the ``(x, residual)`` pair stacked as ``[2, T, H]`` for the next stage."""
+        else the ``(x, residual)`` pair stacked as ``[2, T, H]`` for the next stage. ``vision_rows``: (row indices,
+        vectors) that replace the embeddings of the image / video placeholder tokens."""
         cfg = self.cfg
         if self.pre_process:
             x = ops.embedding(input_ids, self.embedding.word_embeddings.weight, self.vocab_start)
             if mpu.get_tensor_model_parallel_world_size() > 1:
                 x = tp.reduce_from_tensor_model_parallel_region(x)
+            if vision_rows is not None:
+                x = x.index_put((vision_rows[0],), vision_rows[1].to(x.dtype))
             if self.sequence_parallel:
                 x = tp.scatter_to_sequence_parallel_region(x)
             residual = None
@@ -413,10 +422,37 @@ class GPTModel(nn.Module):
             total = total - (lp.reshape(-1) * valid).sum() / valid.sum().clamp_min(1.0)
         return total / len(self.mtp.layers)
 
+    def _vision_inputs(self, ids, packed, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw):
+        """Encoder outputs for the placeholder rows and the three position streams of the packed stream (the reference
+        does the same around a Transformers vision class: slime_plugins/models/qwen3_5_vl.py:150-200, :230-262)."""
+        from slime_b200.models.vision import mrope_position_ids
+
+        cfg = self.cfg
+        if mpu.get_context_parallel_world_size() > 1:
+            raise NotImplementedError("vision inputs with context parallelism: the placeholder rows of a rank's slices are not mapped yet")
+        rows, vecs = [], []
+        for values, grids, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
+            if values is None:
+                continue
+            assert grids is not None and tok is not None and self.vision is not None, "pixel values need their grids, a placeholder id and an encoder"
+            where = (ids == tok).nonzero(as_tuple=False).flatten()
+            out = self.vision(values.to(ids.device), grids)
+            if where.numel() != out.shape[0]:
+                raise ValueError(f"{where.numel()} placeholder tokens for {out.shape[0]} encoder vectors")
+            rows.append(where)
+            vecs.append(out)
+        if cfg.mrope_section:
+            merge = (cfg.vision or {}).get("spatial_merge_size", 2)
+            packed.mrope_positions, _ = mrope_position_ids(ids, packed.cu_seqlens, image_grid_thw, video_grid_thw, image_token_id=cfg.image_token_id,
+                                                           video_token_id=cfg.video_token_id, spatial_merge_size=merge)  # fmt: skip
+        return (torch.cat(rows), torch.cat(vecs)) if rows else None
+
     def forward(self, input_ids, position_ids=None, attention_mask=None, labels=None, packed_seq_params=None,
-                loss_mask=None, return_hidden=False, **kw):  # fmt: skip
+                loss_mask=None, return_hidden=False, pixel_values=None, image_grid_thw=None, pixel_values_videos=None,
+                video_grid_thw=None, **kw):  # fmt: skip
         """``input_ids``: [1, T] or [T]. Returns logits ``[1, T, V/tp]`` (fp32) on the last stage,
-        values ``[1, T, 1]`` for a critic, or hidden states when ``return_hidden``."""
+        values ``[1, T, 1]`` for a critic, or hidden states when ``return_hidden``. ``pixel_values`` / ``image_grid_thw``
+        (and the video pair): image processor outputs for the placeholder tokens of the stream, in order."""
         ids = input_ids.reshape(-1)
         packed = packed_seq_params
         if packed is None:
@@ -424,7 +460,13 @@ class GPTModel(nn.Module):
             packed = PackedSeqParams(cu, ids.numel())
         if position_ids is None:
             position_ids = positions_from_cu_seqlens(packed.cu_seqlens, ids.numel())
-        h = self.forward_hidden(ids, position_ids.reshape(-1).to(torch.int32), packed)
+        vision_rows = None
+        packed.mrope_positions = None
+        if pixel_values is not None or pixel_values_videos is not None:
+            vision_rows = self._vision_inputs(ids, packed, pixel_values, image_grid_thw, pixel_values_videos, video_grid_thw)
+            if not self.pre_process:
+                vision_rows = None
+        h = self.forward_hidden(ids, position_ids.reshape(-1).to(torch.int32), packed, vision_rows)
         if not self.post_process or return_hidden:
             return h
         if self.value_head:

@@ -55,8 +55,13 @@ def _replicated(shape, dtype, device, std=None, ones=False):
 
 
 # ------------------------------------------------------------------------------------------------- rotary helpers
-def rotary_cos_sin(table: torch.Tensor, positions: torch.Tensor):
-    """``table`` [max_pos, rot] = [cos(rot/2) | sin(rot/2)] -> (cos, sin) [T, 1, rot/2] for ``positions``."""
+def rotary_cos_sin(table: torch.Tensor, positions: torch.Tensor, band_axes: torch.Tensor | None = None):
+    """``table`` [max_pos, rot] = [cos(rot/2) | sin(rot/2)] -> (cos, sin) [T, 1, rot/2] for ``positions`` [T], or for the
+    three position streams ``positions`` [3, T] of vision inputs with ``band_axes`` [rot/2] naming each band's stream."""
+    if positions.dim() == 2:
+        from slime_b200.models.vision import mrope_cos_sin
+
+        return mrope_cos_sin(table, positions, band_axes)
     cs = table[positions.long()]
     half = cs.shape[-1] // 2
     return cs[:, None, :half], cs[:, None, half:]
@@ -182,7 +187,14 @@ class GeneralSelfAttention(nn.Module):
             else:
                 q, k = _rms(q, self.q_layernorm.weight, cfg.norm_epsilon), _rms(k, self.k_layernorm.weight, cfg.norm_epsilon)
         if self.rot > 0:
-            cos, sin = rotary_cos_sin(self._table(q.device, int(packed.max_seqlen) + 1), packed.position_ids.reshape(-1))
+            streams = getattr(packed, "mrope_positions", None) if cfg.mrope_section else None
+            if streams is not None:  # vision inputs: three position streams, one per group of frequency bands
+                from slime_b200.models.vision import mrope_band_axes
+
+                axes = mrope_band_axes(cfg.mrope_section, self.rot // 2, cfg.mrope_interleaved, q.device)
+                cos, sin = rotary_cos_sin(self._table(q.device, int(packed.max_seqlen) + 1), streams, axes)
+            else:
+                cos, sin = rotary_cos_sin(self._table(q.device, int(packed.max_seqlen) + 1), packed.position_ids.reshape(-1))
             q, k = apply_rotary(q, cos, sin, cfg.rotary_interleaved), apply_rotary(k, cos, sin, cfg.rotary_interleaved)
         ctx = ops.varlen_attention(q.contiguous(), k.contiguous(), v.contiguous(), packed.cu_seqlens, packed.max_seqlen,
                                    sinks=self.softmax_offset).reshape(T, hq * d)  # fmt: skip

@@ -129,9 +129,23 @@ def _family(cfg: ModelConfig) -> str:
     return "qwen2"
 
 
+def _vl_name(cfg: ModelConfig, hf_name: str) -> str:
+    """Checkpoints of models with vision inputs keep the language model under ``model.language_model`` (next to
+    ``model.visual``)."""
+    if cfg.vision is not None and hf_name.startswith("model.") and not hf_name.startswith(("model.visual.", "model.language_model.")):
+        return "model.language_model." + hf_name[len("model.") :]
+    return hf_name
+
+
 def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
     """One gathered trainer tensor -> HF (name, tensor) pairs. Names not handled raise."""
     name = name.removeprefix("module.").removeprefix("module.")
+    if name.startswith("vision."):  # the image encoder keeps the checkpoint's own parameter names
+        return [("model.visual." + name[len("vision.") :], t)]
+    return [(_vl_name(cfg, n), x) for n, x in _text_to_hf(cfg, name, t)]
+
+
+def _text_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
     if name == "embedding.word_embeddings.weight":
         return [("model.embed_tokens.weight", t[: cfg.vocab_size])]
     if name == "output_layer.weight":
@@ -272,6 +286,14 @@ def shard_for_tp(cfg: ModelConfig, name: str, full: torch.Tensor, partition_dim:
 
 # ---------------------------------------------------------------------- HF -> trainer names
 def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
+    """HF tensor names a trainer parameter is assembled from, and the rule that joins them (``merge_hf_sources``)."""
+    if name.startswith("vision."):
+        return ["model.visual." + name[len("vision.") :]], "copy"
+    names, rule = _text_sources_for(cfg, name)
+    return [_vl_name(cfg, n) for n in names], rule
+
+
+def _text_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
     """HF tensor names needed to build trainer tensor ``name`` and the merge rule
     ('copy' | 'qkv' | 'gate_up')."""
     if name == "embedding.word_embeddings.weight":
@@ -289,14 +311,14 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
                 return [f"{p}.input_proj.weight"], "swap_halves"
             if sub in _MIMO_MTP:
                 return [f"{p}.{_MIMO_MTP[sub]}"], "copy"
-            names, rule = hf_sources_for(cfg, f"decoder.layers.{k}.{sub[len('transformer_layer.'):]}")
+            names, rule = _text_sources_for(cfg, f"decoder.layers.{k}.{sub[len('transformer_layer.'):]}")
             return [n.replace(f"model.layers.{k}.", f"{p}.", 1) for n in names], rule
         p = f"model.layers.{cfg.num_layers + k}"
         own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
                "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip
         if sub in own:
             return [f"{p}.{own[sub]}"], "copy"
-        return hf_sources_for(cfg, f"decoder.layers.{cfg.num_layers + k}.{sub[len('transformer_layer.'):]}")
+        return _text_sources_for(cfg, f"decoder.layers.{cfg.num_layers + k}.{sub[len('transformer_layer.'):]}")
     m = _LAYER.match(name)
     if m is None:
         raise ValueError(f"unknown trainer parameter name: {name}")

@@ -1,0 +1,124 @@
+"""Vision inputs: the image encoder, the multi-axis rotary positions and the whole model against the Transformers
+implementation of Qwen3.5 with random weights (the library serves as the oracle here, nothing else uses it)."""
+
+import pytest
+import torch
+
+from slime_b200.models import vision
+from slime_b200.models.config import ModelConfig
+from slime_b200.models.gpt import GPTModel, PackedSeqParams
+from slime_b200.weight_sync import convert
+
+IMG, VID, VSTART, VEND = 190, 191, 192, 193
+
+
+def _hf_model():
+    from transformers.models.qwen3_5.configuration_qwen3_5 import Qwen3_5Config
+    from transformers.models.qwen3_5.modeling_qwen3_5 import Qwen3_5ForConditionalGeneration
+
+    text = dict(vocab_size=200, hidden_size=64, intermediate_size=128, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=32, linear_conv_kernel_dim=4, linear_key_head_dim=8, linear_value_head_dim=8, linear_num_key_heads=2,
+                linear_num_value_heads=4, full_attention_interval=2, rms_norm_eps=1e-6, max_position_embeddings=512,
+                layer_types=["linear_attention", "full_attention"] * 2,
+                rope_parameters=dict(rope_type="default", rope_theta=10000.0, partial_rotary_factor=0.5, mrope_section=[4, 2, 2],
+                                     mrope_interleaved=True))  # fmt: skip
+    vis = dict(depth=2, hidden_size=32, num_heads=2, intermediate_size=64, patch_size=4, temporal_patch_size=2, spatial_merge_size=2,
+               out_hidden_size=64, num_position_embeddings=64, in_channels=3)  # fmt: skip
+    cfg = Qwen3_5Config(text_config=text, vision_config=vis, image_token_id=IMG, video_token_id=VID, vision_start_token_id=VSTART,
+                        vision_end_token_id=VEND)  # fmt: skip
+    torch.manual_seed(0)
+    model = Qwen3_5ForConditionalGeneration(cfg).eval()
+    with torch.no_grad():
+        for p in model.parameters():  # the library's init leaves norms at 1 / biases at 0: make every tensor matter
+            p.add_(torch.randn_like(p) * 0.05)
+    return cfg, model
+
+
+@pytest.fixture(scope="module")
+def pair():
+    hf_cfg, hf = _hf_model()
+    d = hf_cfg.to_dict()
+    d["architectures"] = ["Qwen3_5ForConditionalGeneration"]
+    cfg = ModelConfig.from_hf(d)
+    assert cfg.vision["depth"] == 2 and cfg.image_token_id == IMG and cfg.mrope_section == [4, 2, 2] and cfg.mrope_interleaved
+    assert cfg.rotary_percent == 0.5 and cfg.full_attention_interval == 2
+    ours = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=1)
+    sd = hf.state_dict()
+    with torch.no_grad():
+        for name, p in list(ours.named_parameters()) + list(ours.named_buffers()):
+            names, rule = convert.hf_sources_for(cfg, name)
+            p.copy_(convert.merge_hf_sources(rule, [sd[n] for n in names], cfg))
+    return hf_cfg, hf, cfg, ours
+
+
+def _image_inputs(grids, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n = sum(t * h * w for t, h, w in grids)
+    return torch.randn(n, 3 * 2 * 4 * 4, generator=g), torch.tensor(grids)
+
+
+def test_vision_tower_matches_the_library_encoder(pair):
+    _, hf, _, ours = pair
+    px, grid = _image_inputs([[1, 4, 6], [1, 8, 4], [2, 4, 4]])
+    with torch.no_grad():
+        want = hf.model.visual(px, grid_thw=grid).pooler_output
+        got = ours.vision(px, grid)
+    assert got.shape == want.shape == (6 + 8 + 8, 64)
+    assert (got - want).abs().max() < 2e-5, float((got - want).abs().max())
+
+
+def test_position_streams_match_the_library(pair):
+    _, hf, cfg, _ = pair
+    ids = torch.tensor([[5, 6, VSTART] + [IMG] * 6 + [VEND, 7, 8, VSTART] + [IMG] * 8 + [VEND, 9, 10, 11]])
+    grid = torch.tensor([[1, 4, 6], [1, 8, 4]])
+    import inspect
+
+    kw = dict(mm_token_type_ids=(ids == IMG).int()) if "mm_token_type_ids" in inspect.signature(hf.model.get_rope_index).parameters else {}
+    want, want_delta = hf.model.get_rope_index(ids, image_grid_thw=grid, **kw)
+    got, delta = vision.mrope_position_ids(ids, [0, ids.numel()], grid, None, image_token_id=IMG, video_token_id=VID, spatial_merge_size=2)
+    assert torch.equal(got, want[:, 0]) and delta[0] == int(want_delta.reshape(-1)[0])
+    # packed: every sequence restarts at zero and consumes its own grids
+    two, d2 = vision.mrope_position_ids(torch.cat([ids[0], ids[0]]), [0, ids.numel(), 2 * ids.numel()], torch.cat([grid, grid]), None,
+                                        image_token_id=IMG, video_token_id=VID)  # fmt: skip
+    assert torch.equal(two[:, : ids.numel()], got) and torch.equal(two[:, ids.numel() :], got) and d2 == [delta[0]] * 2
+    with pytest.raises(ValueError, match="more grids"):
+        vision.mrope_position_ids(ids, [0, ids.numel()], torch.cat([grid, grid]), None, image_token_id=IMG)
+    with pytest.raises(ValueError, match="shorter than its grid"):
+        vision.mrope_position_ids(ids[:, :8], [0, 8], grid[:1], None, image_token_id=IMG)
+    axes = vision.mrope_band_axes([4, 2, 2], 8, True)
+    assert axes.tolist() == [0, 1, 2, 0, 1, 2, 0, 0]
+    assert vision.mrope_band_axes([4, 2, 2], 8, False).tolist() == [0, 0, 0, 0, 1, 1, 2, 2]
+
+
+def test_whole_model_with_an_image_matches_the_library(pair):
+    _, hf, cfg, ours = pair
+    ids = torch.tensor([[5, 6, VSTART] + [IMG] * 6 + [VEND, 7, 8, VSTART] + [IMG] * 8 + [VEND, 9, 10, 11]])
+    px, grid = _image_inputs([[1, 4, 6], [1, 8, 4]], seed=3)
+    with torch.no_grad():
+        import inspect
+
+        kw = dict(mm_token_type_ids=(ids == IMG).int()) if "mm_token_type_ids" in inspect.signature(hf.forward).parameters else {}
+        want = hf(input_ids=ids, pixel_values=px, image_grid_thw=grid, **kw).logits[0]
+        got = ours(ids, pixel_values=px, image_grid_thw=grid)[0]
+        text_only = ours(ids)[0]
+    assert (got - want).abs().max() < 2e-4, float((got - want).abs().max())
+    assert (text_only - want).abs().max() > 1e-2  # the image matters
+    # two samples packed into one stream give each sample's own logits
+    packed = PackedSeqParams(torch.tensor([0, ids.numel(), 2 * ids.numel()], dtype=torch.int32), ids.numel())
+    with torch.no_grad():
+        both = ours(torch.cat([ids[0], ids[0]]), packed_seq_params=packed, pixel_values=torch.cat([px, px]), image_grid_thw=torch.cat([grid, grid]))[0]
+    assert (both[: ids.numel()] - got).abs().max() < 1e-4 and (both[ids.numel() :] - got).abs().max() < 1e-4
+
+
+def test_image_encoder_receives_gradients_and_names_round_trip(pair):
+    _, hf, cfg, ours = pair
+    ids = torch.tensor([[5, VSTART] + [IMG] * 4 + [VEND, 7, 8]])
+    px, grid = _image_inputs([[1, 4, 4]], seed=5)
+    ours.zero_grad()
+    ours(ids, pixel_values=px, image_grid_thw=grid).float().logsumexp(-1).sum().backward()
+    assert float(ours.vision.merger.linear_fc2.weight.grad.abs().sum()) > 0 and float(ours.vision.patch_embed.proj.weight.grad.abs().sum()) > 0
+    sd = hf.state_dict()
+    out = dict(x for n, p in list(ours.named_parameters()) + list(ours.named_buffers()) for x in convert.convert_to_hf(cfg, n, p.detach()))
+    assert set(out) == set(sd), (sorted(set(out) - set(sd))[:5], sorted(set(sd) - set(out))[:5])
+    for k in sd:
+        assert torch.allclose(out[k], sd[k], atol=1e-6), k
