@@ -1,12 +1,11 @@
 #!/bin/bash
 # Vision-language RL on Geometry-3K: prompts carry images (`--multimodal-keys`), the processor turns them into pixel
 # tensors that travel with the sample (`multimodal_inputs` for the engine, `multimodal_train_inputs` for the trainer).
-# The trainer side needs a model provider with a vision tower (--custom-model-provider-path); the dense text stack,
-# rollout plumbing, reward (math verification) and loss are the regular ones.
+# Checkpoints whose config has a `vision_config` of the Qwen3-VL / Qwen3.5 kind get the built-in vision tower on both
+# sides (trainer: inside the model; engine: `image_data`); other towers come in through --custom-model-provider-path.
 source "$(dirname -- "${BASH_SOURCE[0]}")/../../recipes/common.sh"
 launch train.py \
-  --hf-checkpoint "${CKPT_DIR}/Qwen2.5-VL-3B-Instruct" \
-  --custom-model-provider-path "${VLM_PROVIDER:-my_vlm.provider.build_model}" \
+  --hf-checkpoint "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-4B}" ${VLM_PROVIDER:+--custom-model-provider-path "${VLM_PROVIDER}"} \
   --prompt-data "${DATA_DIR}/geo3k/train.parquet" --input-key problem --label-key answer \
   --multimodal-keys '{"image": "images"}' --apply-chat-template --rollout-shuffle --rm-type math \
   --num-rollout 300 --rollout-batch-size 32 --n-samples-per-prompt 8 --rollout-max-response-len 4096 \

@@ -62,6 +62,12 @@ class Engine:
         kv_heads, kv_dim, v_dim = self._kv_geometry()
         self.kv = PagedKVCache(self._num_kv_layers(), kv_heads, kv_dim, num_pages, self.page_size, self.dtype,
                                self.device, enable_prefix_cache=not self.args.disable_radix_cache, v_head_dim=v_dim)  # fmt: skip
+        if self.args.enable_hierarchical_cache and not self.args.disable_radix_cache:
+            from slime_b200.engine.kv_cache import HostKVTier
+
+            per_page = PagedKVCache.bytes_per_page(self._num_kv_layers(), kv_heads, kv_dim, self.page_size, self.dtype, v_head_dim=v_dim)
+            host_pages = (self.args.hicache_size << 30) // per_page if self.args.hicache_size > 0 else int(num_pages * self.args.hicache_ratio)
+            self.kv.allocator.host_tier = HostKVTier(self.kv, host_pages)
         self.runner = ModelRunner(cfg, self.weights, self.kv, self.max_running, self.max_context,
                                   use_cuda_graph=not self.args.disable_cuda_graph, tp_group=tp_group)  # fmt: skip
         self.runner._alloc_static()
@@ -201,8 +207,9 @@ class Engine:
                 continue
             # input log-probs and routed experts need every position computed
             # (a recurrent layer's state at a page boundary is not kept, so hybrid models do not reuse prefixes either)
+            # (image placeholder tokens look the same for every image: such prompts neither reuse nor offer prefixes)
             want_cache = (req.logprob_start_len < 0 and not (req.return_routed_experts and self.runner.record_routed)
-                          and not self.runner.has_gdn)  # fmt: skip
+                          and not self.runner.has_gdn and req.mm is None)  # fmt: skip
             pages, chain = self.kv.allocator.match_prefix(ctx) if want_cache else ([], b"")
             cached = len(pages) * ps
             total_pages = -(-(len(ctx) + 1) // ps)
@@ -243,10 +250,20 @@ class Engine:
         ids, pos, slots, cu_q, cu_k, gather, last_rows, samplers = [], [], [], [0], [0], [], [], []
         fresh, max_q, max_k = True, 0, 0
         want_all_rows = any(r.logprob_start_len >= 0 for r, _ in batch)
+        mrope = self.cfg.mrope_section is not None and any(r.mm is not None for r, _ in batch)
+        streams, emb_rows, emb_vecs = [], [], []
         for req, n in batch:
             s, e = req.num_computed, req.num_computed + n
             ids += req.ctx_ids[s:e]
             pos += list(range(s, e))
+            if req.mm is not None:
+                self._prepare_vision(req)
+                inside = (req.mm_rows >= s) & (req.mm_rows < e)
+                if bool(inside.any()):
+                    emb_rows.append(req.mm_rows[inside] - s + cu_q[-1])
+                    emb_vecs.append(req.mm_embeds[inside])
+            if mrope:
+                streams.append(self._position_streams(req, s, e))
             slots += self._slots(req, s, e)
             cu_q.append(cu_q[-1] + n)
             cu_k.append(cu_k[-1] + e)
@@ -261,8 +278,10 @@ class Engine:
                 self.prefilling.append(req)
         rows = None if want_all_rows else t(last_rows, torch.long)
         states = [getattr(req, "gdn_state", None) for req, _ in batch] if self.runner.has_gdn else None
-        dev_in = (t(ids), t(pos), t(slots), t(cu_q), None if fresh else t(gather, torch.long), t(cu_k))
-        logits = self.runner.prefill(*dev_in, max_q, max_k, rows, fresh, gdn_states=states)
+        dev_pos = torch.cat(streams, dim=1).to(self.device, torch.int32) if mrope else t(pos)
+        dev_in = (t(ids), dev_pos, t(slots), t(cu_q), None if fresh else t(gather, torch.long), t(cu_k))
+        embed_rows = (torch.cat(emb_rows).to(self.device), torch.cat(emb_vecs)) if emb_rows else None
+        logits = self.runner.prefill(*dev_in, max_q, max_k, rows, fresh, gdn_states=states, embed_rows=embed_rows)
         if self.runner.has_gdn:
             for (req, _), st in zip(batch, self.runner.last_gdn_states):
                 req.gdn_state = st
@@ -301,6 +320,51 @@ class Engine:
         if self.spec is not None:
             self.spec.after_prefill(batch, dev_in, cu_q, max_q, max_k, fresh)
         return finished
+
+    # ------------------------------------------------------------------------- vision inputs
+    def _prepare_vision(self, req: Request):
+        """First pass of a request with images: run the encoder once, locate the placeholder tokens, lay out the three
+        position streams of the prompt. (``image_data`` of ``/generate``: slime/rollout/sglang_rollout.py:158-203 and
+        examples/geo3k_vlm_multi_turn/rollout.py:192-209 in the reference send processor-expanded ``input_ids`` plus the
+        images.)"""
+        if req.mm_embeds is not None:
+            return
+        from slime_b200.models.vision import mrope_position_ids
+
+        cfg, mm = self.cfg, req.mm
+        if self.weights.vision is None:
+            raise ValueError("this model has no image encoder")
+        ids = torch.tensor(req.input_ids)
+        rows, vecs = [], []
+        for values, grids, tok in ((mm.get("pixel_values"), mm.get("image_grid_thw"), cfg.image_token_id),
+                                   (mm.get("pixel_values_videos"), mm.get("video_grid_thw"), cfg.video_token_id)):  # fmt: skip
+            if values is None:
+                continue
+            where = (ids == tok).nonzero(as_tuple=False).flatten()
+            out = self.runner.encode_images(torch.as_tensor(values), torch.as_tensor(grids))
+            if where.numel() != out.shape[0]:
+                raise ValueError(f"{where.numel()} placeholder tokens for {out.shape[0]} encoder vectors")
+            rows.append(where)
+            vecs.append(out)
+        order = torch.cat(rows).argsort()
+        req.mm_rows, req.mm_embeds = torch.cat(rows)[order], torch.cat(vecs)[order.to(vecs[0].device)]
+        if cfg.mrope_section:
+            merge = (cfg.vision or {}).get("spatial_merge_size", 2)
+            g = lambda k: None if mm.get(k) is None else torch.as_tensor(mm[k])  # noqa: E731
+            streams, delta = mrope_position_ids(ids, [0, ids.numel()], g("image_grid_thw"), g("video_grid_thw"),
+                                                image_token_id=cfg.image_token_id, video_token_id=cfg.video_token_id,
+                                                spatial_merge_size=merge)  # fmt: skip
+            req.mm_positions, req.rope_delta = streams, int(delta[0])
+
+    def _position_streams(self, req: Request, s: int, e: int) -> torch.Tensor:
+        """[3, e - s] rotary positions of context tokens [s, e): the prompt's streams, then index + offset."""
+        n_in = len(req.input_ids)
+        tail = torch.arange(max(s, n_in), max(e, s, n_in)).expand(3, -1) + req.rope_delta
+        if req.mm_positions is None:
+            return torch.arange(s, e).expand(3, -1)
+        if s >= n_in:
+            return tail
+        return torch.cat([req.mm_positions[:, s : min(e, n_in)], tail], dim=1)
 
     # ------------------------------------------------------ prefill / decode disaggregation
     def export_kv(self, req: Request):
@@ -394,6 +458,8 @@ class Engine:
         L = r.seq_len
         r.slot, r.decode_from_step, r.harvested = b, self.step_no, self.step_no
         self.slot_req[b] = r
+        if self.runner.rope_delta is not None:
+            self.runner.rope_delta[b] = r.rope_delta
         if self.runner.has_gdn:
             self.runner.load_gdn_state(b, r.gdn_state)
             r.gdn_state = None
@@ -610,6 +676,8 @@ class Engine:
 
     def _commit_pages(self, req: Request, ids):
         """Index every page that became full and whose KV is written (committed tokens only)."""
+        if req.mm is not None:
+            return
         ps = self.page_size
         while (req.committed_pages + 1) * ps <= req.num_computed and req.committed_pages < len(req.pages):
             ids = ids or (req.input_ids + req.output_ids)
@@ -696,6 +764,8 @@ class Engine:
                 if tag == "kv_cache":
                     self.abort(abort_all=True)
                     self.kv.release()
+                    if self.args.release_hicache and self.kv.allocator.host_tier is not None:
+                        self.kv.allocator.host_tier.release()  # the host pool goes too; without the switch it survives
                 elif tag == "cuda_graph":
                     self.runner.drop_graphs()
                 elif tag == "weights":
@@ -712,6 +782,8 @@ class Engine:
                     continue
                 if tag == "kv_cache":
                     self.kv.allocate()
+                    if self.kv.allocator.host_tier is not None:
+                        self.kv.allocator.host_tier.allocate()
                     if 0 in self.kv.allocator.free:
                         self.kv.allocator.free.remove(0)
                         self.kv.allocator.refcnt[0] = 1

@@ -33,9 +33,10 @@ from slime_b200.engine.request import SamplingParams
 
 
 class EngineServer:
-    def __init__(self, engine: Engine, host: str = "127.0.0.1", port: int = 30000, tokenizer=None):
+    def __init__(self, engine: Engine, host: str = "127.0.0.1", port: int = 30000, tokenizer=None, processor=None):
         self.engine, self.host, self.port = engine, host, port
         self.tokenizer = tokenizer or engine.tokenizer
+        self.processor = processor  # multimodal processor of the checkpoint, when it ships one
         self._stop = threading.Event()
         self._thread: threading.Thread | None = None
         self._loop: asyncio.AbstractEventLoop | None = None
@@ -65,11 +66,39 @@ class EngineServer:
                 self._wake.clear()
 
     # ---------------------------------------------------------------------------- handlers
+    def _vision_inputs(self, image_data, ids, text):
+        """``image_data`` (base64 / data URLs / paths, one request) -> (prompt ids with every image's placeholder run at
+        its full length, encoder inputs). With ``input_ids`` the prompt is taken as sent (already expanded by the caller's
+        processor, or one placeholder per image); with ``text`` it is tokenised here."""
+        from slime_b200.utils.image_processing import ImageProcessor, expand_image_placeholders
+        from slime_b200.utils.processing_utils import _load_image
+
+        cfg = self.engine.cfg
+        if cfg.vision is None or cfg.image_token_id is None:
+            raise ValueError("this model takes no images")
+        images = [_load_image(x) for x in (image_data if isinstance(image_data, list) else [image_data])]
+        ip = getattr(self.processor, "image_processor", None)
+        out = ip(images=images, return_tensors="pt") if ip is not None else ImageProcessor.from_vision_config(cfg.vision)(images)
+        mm = {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}
+        if ids is None:
+            if text is None or self.tokenizer is None:
+                raise ValueError("input_ids (or text with a tokenizer) required")
+            ids = self.tokenizer.encode(text, add_special_tokens=False)
+        merge = cfg.vision.get("spatial_merge_size", 2) ** 2
+        counts = [int(t * h * w) // merge for t, h, w in mm["image_grid_thw"].tolist()]
+        return expand_image_placeholders(list(ids), cfg.image_token_id, counts), mm
+
     async def _generate(self, request):
         from aiohttp import web
 
         body = await request.json()
         ids = body.get("input_ids")
+        mm = None
+        if body.get("image_data"):
+            try:
+                ids, mm = self._vision_inputs(body["image_data"], ids, body.get("text"))
+            except Exception as e:  # noqa: BLE001  a bad image or a prompt that does not match its images
+                return web.json_response({"error": f"image inputs: {e}"}, status=400)
         if ids is None:
             text = body.get("text")
             if text is None or self.tokenizer is None:
@@ -105,7 +134,7 @@ class EngineServer:
                 p, SamplingParams.from_dict(s), rid=body.get("rid"), return_logprob=bool(body.get("return_logprob", False)),
                 logprob_start_len=int(body.get("logprob_start_len", -1) if body.get("return_logprob") else -1),
                 return_routed_experts=bool(body.get("return_routed_experts", False)), stream=stream,
-                on_token=on_token if stream else None, done_event=_Done(ev), prefill_only=prefill_only,
+                on_token=on_token if stream else None, done_event=_Done(ev), prefill_only=prefill_only, mm=mm,
             )  # fmt: skip
             if req.finished():
                 ev.set()
@@ -617,7 +646,12 @@ def launch_server(server_args, model_config=None, tokenizer=None, weights_loader
 
         reader = SafetensorReader(server_args.model_path)
         engine.update_weights(((n, reader.get(n)) for n in reader.keys() if not n.endswith("_scale_inv")))
-    return EngineServer(engine, server_args.host, server_args.port, tokenizer).start(block=block)
+    processor = None
+    if cfg.vision is not None and server_args.model_path:
+        from slime_b200.utils.processing_utils import load_processor
+
+        processor = load_processor(server_args.tokenizer_path or server_args.model_path)
+    return EngineServer(engine, server_args.host, server_args.port, tokenizer, processor).start(block=block)
 
 
 if __name__ == "__main__":

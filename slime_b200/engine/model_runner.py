@@ -64,6 +64,11 @@ class EngineWeights:
                 return quant.Fp8Weight(*shape, device=device)
             return e(*shape)
 
+        self.vision = None  # image encoder, replicated on every rank of the engine
+        if cfg.vision is not None:
+            from slime_b200.models.vision import VisionConfig, VisionTower
+
+            self.vision = VisionTower(VisionConfig.from_dict(cfg.vision), dtype, device).requires_grad_(False)
         self.embed = e(self.vocab_local, h)
         self.lm_head = self.embed if cfg.tie_word_embeddings else e(self.vocab_local, h)
         self.final_norm = e(h)
@@ -163,6 +168,8 @@ class EngineWeights:
         yield self.embed
         yield self.lm_head
         yield self.final_norm
+        if self.vision is not None:
+            yield from self.vision.parameters()
         for L in self.layers + self.draft:
             for v in L.values():
                 if v is None or isinstance(v, (str, int)):  # absent buffers, the layer's kind tag, the indexer's source layer
@@ -179,6 +186,16 @@ class EngineWeights:
 
     def load_weight(self, name: str, t: torch.Tensor):
         cfg, d = self.cfg, self.cfg.head_dim
+        if name.startswith("model.visual."):  # the image encoder keeps the checkpoint's parameter names
+            if self.vision is None:
+                return True
+            target = dict(self.vision.named_parameters()).get(name[len("model.visual.") :])
+            if target is None:
+                return False
+            target.data.copy_(t.to(self.device, target.dtype))
+            return True
+        if name.startswith("model.language_model."):  # checkpoints with a vision tower nest the language model
+            name = "model." + name[len("model.language_model.") :]
         raw = t
         t = t.to(self.device, self.dtype, non_blocking=True)
         if name == "model.embed_tokens.weight":
@@ -441,7 +458,11 @@ class ModelRunner:
                 if L["kind"] == "gdn":
                     self.gdn_S[li] = torch.zeros(max_batch, hv, dk, dv, dtype=torch.float32, device=self.device)
                     self.gdn_conv[li] = torch.zeros(max_batch, K - 1, C, dtype=weights.dtype, device=self.device)
-        self._composed_attention = cfg.rotary_percent < 1.0 or cfg.rotary_interleaved or cfg.qk_layernorm_full
+        self._composed_attention = cfg.rotary_percent < 1.0 or cfg.rotary_interleaved or cfg.qk_layernorm_full or bool(cfg.mrope_section)
+        # vision inputs: decode positions are the token index plus a per-request offset (an image advances the position
+        # by its larger grid side only), prefill positions are three streams
+        self.rope_delta = torch.zeros(max_batch, dtype=torch.int32, device=self.device) if cfg.mrope_section else None
+        self._mrope_axes = None
         rot = int(cfg.head_dim * cfg.rotary_percent) // 2 * 2
         self.rope = ops.rope_cos_sin(max_context + 1, rot, cfg.rotary_base, device=self.device,
                                      scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
@@ -579,12 +600,24 @@ class ModelRunner:
                 q = mixers._rms(q.view(T, hq, d), L["q_norm"], cfg.norm_epsilon).view(T, -1)
                 k = mixers._rms(k.view(T, hkv, d), L["k_norm"], cfg.norm_epsilon).view(T, -1)
         if self.rope.shape[1] > 0:
-            cos, sin = mixers.rotary_cos_sin(self.rope, positions)
+            cos, sin = mixers.rotary_cos_sin(self.rope, positions, self._band_axes() if positions.dim() == 2 else None)
             q = mixers.apply_rotary(q.view(T, hq, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
             k = mixers.apply_rotary(k.view(T, hkv, d), cos, sin, cfg.rotary_interleaved).view(T, -1)
         k, v = k.contiguous(), v.contiguous()
         ops.kv_write(k, v, slots, self.kv.k[self.kv_of[li]], self.kv.v[self.kv_of[li]])
         return torch.cat([q, k, v], dim=-1)
+
+    def _band_axes(self):
+        if self._mrope_axes is None:
+            from slime_b200.models.vision import mrope_band_axes
+
+            self._mrope_axes = mrope_band_axes(self.cfg.mrope_section, self.rope.shape[1] // 2, self.cfg.mrope_interleaved, self.device)
+        return self._mrope_axes
+
+    @torch.no_grad()
+    def encode_images(self, pixel_values, grid_thw):
+        """Image encoder outputs [placeholder tokens, H] for one request's images."""
+        return self.w.vision(pixel_values.to(self.device), grid_thw.to(self.device)).to(self.w.dtype)
 
     def _full_norm(self, t, w):
         """RMSNorm over all heads of the model: the sum of squares crosses the tensor-parallel ranks."""
@@ -774,7 +807,8 @@ class ModelRunner:
 
     # --------------------------------------------------------------------- prefill
     @torch.no_grad()
-    def prefill(self, ids, positions, slots, cu_q, kv_gather_slots, cu_k, max_q, max_k, last_rows, fresh: bool, gdn_states=None):
+    def prefill(self, ids, positions, slots, cu_q, kv_gather_slots, cu_k, max_q, max_k, last_rows, fresh: bool, gdn_states=None,
+                embed_rows=None):
         """Extend pass over packed new tokens.
 
         ids/positions/slots: [T] for the new tokens; ``cu_q`` their per-request boundaries.
@@ -783,10 +817,14 @@ class ModelRunner:
         ``[len(last_rows), V/tp]`` fp32 for the requested rows and, when ``last_rows`` is None, all rows.
         Models with delta-net layers: ``gdn_states[i]`` is request i's recurrent state from its earlier chunks (or
         None); the states after this pass are left in ``last_gdn_states``.
+        Vision inputs: ``positions`` may be ``[3, T]`` (temporal / height / width streams) and ``embed_rows`` = (rows,
+        vectors) replaces the embeddings of image placeholder tokens by the encoder's outputs.
         """
         cfg, w, d = self.cfg, self.w, self.cfg.head_dim
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
+        if embed_rows is not None:
+            x = x.index_copy(0, embed_rows[0], embed_rows[1].to(x.dtype))
         res = None
         T = ids.numel()
         if self.has_gdn:
@@ -948,6 +986,8 @@ class ModelRunner:
                 P(ds["seq_lens"]), P(ds["slots"]), n, ps, W, _lib.stream()), "sb_decode_prepare")  # fmt: skip
         else:
             self._prepare_reference(n)
+        if self.rope_delta is not None:
+            pos = pos + self.rope_delta[:n]  # rotary position of a request that carries images
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
         if self._fused_tp is not None:

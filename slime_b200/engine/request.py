@@ -63,6 +63,7 @@ class Request:
     prefill_only: bool = False  # prefill / decode disaggregation: stop after the first token and export the prompt's KV
     kv_export: Any = None  # (k, v) [layers, tokens, kv heads, head dim] of a finished prefill-only request
     gdn_state: Any = None  # {layer: (recurrent state, convolution history)} between prefill chunks, until a decode slot takes it
+    mm: dict | None = None  # vision inputs: pixel_values + image_grid_thw (and the video pair) for the placeholder tokens of input_ids
     extra_meta: dict = field(default_factory=dict)  # added verbatim to meta_info (e.g. the pd_* transfer figures)
     # ---- engine state ----
     state: ReqState = ReqState.WAITING
@@ -95,6 +96,10 @@ class Request:
     end_step: int | None = None
     end_reason: dict | None = None
     # speculative decoding (engine/speculative.py): guesses for the tokens after the last one, the draft head's stream
+    mm_rows: Any = None  # positions of the placeholder tokens in input_ids (long tensor) ...
+    mm_embeds: Any = None  # ... and the encoder's vector for each, computed at the first prefill pass
+    mm_positions: Any = None  # [3, len(input_ids)] temporal / height / width position streams of the prompt
+    rope_delta: int = 0  # rotary position of a generated token = its index + rope_delta
     spec_draft: list[int] = field(default_factory=list)
     spec_hidden: Any = None
 

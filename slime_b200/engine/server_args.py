@@ -78,6 +78,9 @@ class ServerArgs:
     nsa_prefill_backend: str | None = None
     nsa_decode_backend: str | None = None
     mamba_scheduler_strategy: str | None = None
+    enable_hierarchical_cache: bool = False  # evicted prefix pages move to pinned host memory instead of being dropped
+    hicache_ratio: float = 2.0  # host pages per device page
+    hicache_size: int = 0  # host pool in GB (overrides the ratio when > 0)
     release_hicache: bool = False
     weight_version: str = "default"
     load_format: str = "auto"  # auto | dummy (random init)

@@ -64,7 +64,7 @@ class SpeculativeDecoder:
         eng = self.eng
         pos, slots, cu_q, cu_k, gather, max_q, max_k = [], [], [0], [0], [], 0, 0
         for r, s, n in spans:
-            pos += list(range(s, s + n))
+            pos += [p + r.rope_delta for p in range(s, s + n)]  # (a request with images rotates by index + offset)
             slots += eng._slots(r, s, s + n)
             cu_q.append(cu_q[-1] + n)
             cu_k.append(cu_k[-1] + s + n)

@@ -12,6 +12,9 @@ import os
 from dataclasses import dataclass
 
 
+VISION_FIELDS = ("vision", "image_token_id", "video_token_id", "mrope_section", "mrope_interleaved")
+
+
 @dataclass
 class ModelConfig:
     num_layers: int
@@ -153,6 +156,13 @@ class ModelConfig:
             else:
                 total += 3 * h * self.ffn_hidden_size
         total += self.vocab_size * h * (1 if self.tie_word_embeddings else 2) + h
+        if self.vision:
+            v = self.vision
+            d, inter, big = v["hidden_size"], v["intermediate_size"], v["hidden_size"] * v.get("spatial_merge_size", 2) ** 2
+            patch = v.get("in_channels", 3) * v.get("temporal_patch_size", 2) * v["patch_size"] ** 2
+            total += d * patch + d + v.get("num_position_embeddings", 0) * d  # patch embedding, learned positions
+            total += v["depth"] * (4 * d + 4 * d * d + 4 * d + 2 * d * inter + inter + d)  # norms, qkv + proj, mlp
+            total += 2 * d + big * big + big + v.get("out_hidden_size", h) * big + v.get("out_hidden_size", h)  # merger
         return total
 
     # -- constructors ---------------------------------------------------------
@@ -167,6 +177,15 @@ class ModelConfig:
                 raise ValueError(f"--{req.replace('_', '-')} is required (or give --hf-checkpoint with a config.json)")
         kw.setdefault("num_query_groups", kw["num_attention_heads"])
         kw.setdefault("ffn_hidden_size", 4 * kw["hidden_size"])
+        # the image encoder has no flags of its own: it is described by the checkpoint's config (or the preset)
+        hf = getattr(args, "hf_checkpoint", None)
+        if "vision" not in kw and isinstance(hf, str) and (hf.startswith("preset:") or os.path.exists(os.path.join(hf, "config.json"))):
+            try:
+                src = cls.from_hf(hf)
+            except (KeyError, ValueError, OSError):
+                src = None
+            if src is not None and src.vision is not None:
+                kw.update({f: getattr(src, f) for f in VISION_FIELDS})
         return cls(**kw)
 
     @classmethod

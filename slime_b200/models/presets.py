@@ -129,19 +129,24 @@ MORE_PRESETS.update({
                               num_experts=256, moe_ffn_hidden_size=512, moe_router_topk=8,
                               moe_shared_expert_intermediate_size=512, moe_shared_expert_gate=True, **_gdn(16, 32)),
 })  # fmt: skip
+# the same language model with its image / video encoder (27 blocks of width 1152, 16 x 16 pixel patches joined 2 x 2) and
+# three-stream rotary positions; the placeholder token ids are the tokenizer's (a real config.json overrides them)
+MORE_PRESETS["qwen3.5-35b-a3b-vl"] = dict(
+    MORE_PRESETS["qwen3.5-35b-a3b"], model_arch="Qwen3_5MoeForConditionalGeneration", mrope_section=[11, 11, 10], mrope_interleaved=True,
+    image_token_id=248056, video_token_id=248057,
+    vision=dict(depth=27, hidden_size=1152, num_heads=16, intermediate_size=4304, in_channels=3, patch_size=16, temporal_patch_size=2,
+                spatial_merge_size=2, out_hidden_size=2048, num_position_embeddings=2304, hidden_act="gelu_pytorch_tanh"))  # fmt: skip
 
 # name -> what is missing. The numbers of these families are in the recipes they come from; they are not repeated here
 # because a preset that cannot be instantiated correctly is worse than none.
-UNSUPPORTED: dict[str, str] = {
-    "qwen3.5-35b-a3b-vl": "the vision tower (image / video patches into the token stream) is not implemented",
-}
+UNSUPPORTED: dict[str, str] = {}
 
 ALIASES = {"qwen2.5-0.5b": "qwen2.5-0.5b", "llama3.2-3b-instruct-amd": "llama3.2-3b-instruct"}
 
 
 def to_flags(cfg) -> list[str]:
     """The preset as the command-line flags ``slime_b200.utils.arguments`` parses (Megatron names)."""
-    from slime_b200.models.config import ModelConfig
+    from slime_b200.models.config import VISION_FIELDS, ModelConfig
 
     base = {f.name: f.default for f in dataclasses.fields(ModelConfig)}
     out: list[str] = ["--swiglu", "--normalization", "RMSNorm", "--use-rotary-position-embeddings", "--disable-bias-linear"]
@@ -155,6 +160,8 @@ def to_flags(cfg) -> list[str]:
                       "index_topk_freq", "index_skip_topk_offset", "rotary_scaling_type", "rotary_original_max_position",
                       "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim") and v == base[f.name]:  # fmt: skip
             continue
+        if f.name in VISION_FIELDS:
+            continue  # no flags: the trainer reads the image encoder's description from --hf-checkpoint
         flag = "--" + f.name.replace("_", "-")
         if isinstance(v, bool):
             if v:

@@ -142,9 +142,10 @@ async def generate(args: Namespace, sample: Sample, sampling_params: dict[str, A
     images = sample.multimodal_inputs.get("images") if sample.multimodal_inputs else None
     if images:
         payload["image_data"] = [encode_image_for_rollout_engine(im) for im in images]
-        payload["text"] = sample.prompt
+    if images and state.processor is None:
+        payload["text"] = sample.prompt  # no processor on this side: the engine tokenises and sizes the placeholder runs
     else:
-        payload["input_ids"] = prompt_ids
+        payload["input_ids"] = prompt_ids  # (with images: already expanded by the processor, one run per image)
     if not sample.tokens:
         sample.tokens = prompt_ids
     headers = None

@@ -319,3 +319,48 @@ def test_router_runs_prefill_and_decode_on_different_servers():
         router.shutdown()
         for s in servers:
             s.shutdown()
+
+
+def test_evicted_prefix_pages_come_back_from_the_host_tier():
+    """Few device pages, a host tier behind them: a prompt whose pages were pushed out by other traffic is served from
+    the host copy (same tokens and log-probs as a cold run), counted as cached tokens; without the tier it is recomputed."""
+    from slime_b200.engine.kv_cache import HostKVTier
+
+    cfg = get_preset("tiny")
+    mk = lambda **kw: Engine(cfg, ServerArgs(page_size=4, max_running_requests=2, context_length=128, disable_cuda_graph=True, **kw),
+                             device="cpu", num_pages=24)  # noqa: E731
+    plain, tiered = mk(), mk(enable_hierarchical_cache=True, hicache_ratio=4.0)
+    for e in (plain, tiered):
+        e.weights.init_random(0, std=0.2)
+    tier = tiered.kv.allocator.host_tier
+    assert isinstance(tier, HostKVTier) and tier.num_pages == 96 and plain.kv.allocator.host_tier is None
+    sp = dict(max_new_tokens=4, temperature=0, ignore_eos=True)
+    first = list(range(1, 42))
+    others = [[100 + 50 * j + i for i in range(41)] for j in range(4)]
+    ref = plain.generate([first], [sp])[0]
+    for e in (plain, tiered):
+        e.generate([first], [sp])
+        for o in others:  # enough traffic to evict every page of the first prompt
+            e.generate([o], [sp])
+    assert tiered.kv.allocator.stats()["host_stores"] >= 10
+    again_plain, again = plain.generate([first], [sp])[0], tiered.generate([first], [sp])[0]
+    assert again_plain.num_cached_tokens == 0  # gone without the tier
+    assert again.num_cached_tokens == 40 and tiered.kv.allocator.stats()["host_hits"] == 10
+    assert again.output_ids == ref.output_ids and np.abs(np.array(again.output_logprobs) - np.array(ref.output_logprobs)).max() < 1e-5
+    # a weight update makes host copies stale too; releasing the cache keeps the host pool unless asked otherwise
+    tiered.update_weights([], flush_cache=True)
+    assert tiered.kv.allocator.stats()["host_cached"] == 0
+    tiered.generate([first], [sp])
+    for o in others:
+        tiered.generate([o], [sp])
+    assert tiered.kv.allocator.stats()["host_cached"] > 0
+    tiered.release_memory_occupation(["kv_cache"])
+    tiered.resume_memory_occupation(["kv_cache"])
+    assert tiered.kv.allocator.host_tier is tier and tier.k is not None
+    back = tiered.generate([first], [sp])[0]
+    assert back.num_cached_tokens > 0 and back.output_ids == ref.output_ids  # the device cache was dropped, the host copies were not
+    freeing = mk(enable_hierarchical_cache=True, release_hicache=True)
+    freeing.release_memory_occupation(["kv_cache"])
+    assert freeing.kv.allocator.host_tier.k is None and freeing.kv.allocator.host_tier.num_bytes() == 0
+    freeing.resume_memory_occupation(["kv_cache"])
+    assert freeing.kv.allocator.host_tier.k is not None

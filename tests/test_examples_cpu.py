@@ -326,3 +326,77 @@ def test_message_level_agent_keeps_the_exact_token_trajectory(engine):
 
     a, b = asyncio.run(bad_tools())
     assert a.startswith("Error: unknown tool") and b.startswith("Error: TypeError")
+
+
+def test_multi_turn_vision_rollout_collects_images_and_masks_environment_tokens(engine, monkeypatch):
+    import torch
+    from PIL import Image
+
+    from examples.geo3k_vlm_multi_turn import env_geo3k
+    from examples.geo3k_vlm_multi_turn import rollout as ex
+
+    args, state, tok = engine
+
+    def template(messages, tools=None, tokenize=False, add_generation_prompt=True, **kw):
+        parts = []
+        for m in messages:
+            c = m["content"]
+            body = c if isinstance(c, str) else " ".join("<image>" if p["type"] == "image" else p["text"] for p in c)
+            parts.append(f"<|{m['role']}|> {body}")
+        return " ".join(parts) + (" <|assistant|>" if add_generation_prompt else "")
+
+    tok.apply_chat_template = template
+    tok.bos_token_id = None
+
+    class FakeProcessor:
+        """Expands every <image> word into 4 placeholder tokens and emits one 4 x 4 grid of pixel rows per image."""
+
+        def __call__(self, text, images=None, return_tensors="pt", **kw):
+            ids = []
+            for w in text.split():
+                ids += tok.encode("<image>") * 4 if w == "<image>" else tok.encode(w)
+            out = {"input_ids": torch.tensor([ids]), "attention_mask": torch.ones(1, len(ids))}
+            if images:
+                out["pixel_values"] = torch.cat([torch.full((16, 8), float(im.size[0])) for im in images])
+                out["image_grid_thw"] = torch.tensor([[1, 4, 4]] * len(images))
+            return out
+
+    monkeypatch.setattr(sglang_rollout, "load_processor", lambda *a, **k: FakeProcessor())
+    sglang_rollout.GenerateState.clear_instances()
+    args.max_turns, args.rollout_interaction_env_path, args.apply_chat_template = 3, None, True
+    args.apply_chat_template_kwargs, args.rollout_max_context_len = None, 400
+
+    replies = iter(['I think <tool_call> {"name":"calc_score","arguments":{"answer":"7"}} </tool_call>',
+                    'Then <tool_call> {"name":"calc_score","arguments":{"answer":"12"}} </tool_call>',
+                    "So the answer is \\boxed{12}"])
+    state["script"] = lambda prompt: next(replies)
+    img = Image.new("RGB", (24, 24))
+    s = Sample(index=0, prompt="<|user|> <image> What is x ? <|assistant|>", label="12", multimodal_inputs={"images": [img]})
+    out = asyncio.run(ex.generate(args, s, {"max_new_tokens": 64, "temperature": 1.0}))
+    assert out.status == Sample.Status.COMPLETED
+    assert len(out.loss_mask) == out.response_length == len(out.rollout_log_probs)
+    trained = tok.decode([t for t, m in zip(out.tokens[-out.response_length:], out.loss_mask) if m])
+    context = tok.decode([t for t, m in zip(out.tokens[-out.response_length:], out.loss_mask) if not m])
+    assert "calc_score" in trained and "\\boxed{12}" in trained and "does not match" not in trained
+    assert "does not match the reference" in context and "matches the reference" in context and "helpful assistant" not in context
+    # the first image travelled with every call; its processor outputs reach the trainer; the prompt's placeholders are expanded
+    assert all(len(c) == 2 for c in state["calls"]) and len(state["calls"]) == 3
+    assert out.tokens.count(tok.encode("<image>")[0]) == 4
+    assert out.multimodal_train_inputs["pixel_values"].shape == (16, 8) and out.multimodal_train_inputs["image_grid_thw"].tolist() == [[1, 4, 4]]
+    # budget = context limit minus what is there: it shrinks from call to call
+    budgets = [c[1]["max_new_tokens"] for c in state["calls"]]
+    assert budgets[0] == 400 - (len(out.tokens) - out.response_length) and budgets[0] > budgets[1] > budgets[2]
+
+    # the environment by itself
+    env = env_geo3k.Geo3kEnv("12", max_turns=3)
+    obs, done, info = env.step('<tool_call>{"name": "calc_score", "arguments": {"answer": "\\\\boxed{12}"}}</tool_call>')
+    assert obs["tool_score"] == 1.0 and not done and info["tool_executed"]
+    obs, done, info = env.step('<tool_call>{"function": {"name": "calc_geo3k_reward", "arguments": "{\\"answer\\": \\"5\\"}"}}</tool_call>')
+    assert obs["tool_score"] == 0.0 and "one chance left" in obs["obs_str"] and not done
+    obs, done, info = env.step('<tool_call>{"name": "other", "arguments": {}}</tool_call>')
+    assert "not supported" in obs["obs_str"] and done  # third of three turns
+    assert env.step("no call here")[1] is True and env_geo3k.parse_tool_call("<tool_call>{broken</tool_call>") is None
+    msg = env.format_observation({"obs_str": "look", "multi_modal_data": {"image": [img]}})
+    assert [p["type"] for p in msg["content"]] == ["image", "text"]
+    ids, image_data, images, train = ex.encode_observation(tok, FakeProcessor(), msg, None, True, None)
+    assert tok.decode(ids).startswith("<|user|> <image> <image> <image> <image> look") and len(image_data) == 1 and train["pixel_values"].shape[0] == 16

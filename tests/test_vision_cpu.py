@@ -122,3 +122,137 @@ def test_image_encoder_receives_gradients_and_names_round_trip(pair):
     assert set(out) == set(sd), (sorted(set(out) - set(sd))[:5], sorted(set(sd) - set(out))[:5])
     for k in sd:
         assert torch.allclose(out[k], sd[k], atol=1e-6), k
+
+
+def _engine(pair, **kw):
+    from slime_b200.engine.engine import Engine
+    from slime_b200.engine.server_args import ServerArgs
+
+    _, hf, cfg, _ = pair
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=4, context_length=128, disable_cuda_graph=True, **kw), device="cpu", num_pages=96)
+    missing = e.weights.load_weights(list(hf.state_dict().items()))  # the checkpoint's own names, language model nested
+    assert not missing, missing
+    return e
+
+
+@pytest.mark.parametrize("chunk", [8192, 5])
+def test_engine_with_images_reproduces_the_trainer(pair, chunk):
+    """Prompt log-probs (prefill, also when an image spans several chunks) and greedy decode log-probs of a request with
+    two images equal the trainer's teacher-forced ones; a text-only request next to it is unaffected."""
+    import numpy as np
+
+    _, _, cfg, ours = pair
+    e = _engine(pair, chunked_prefill_size=chunk)
+    ids = [5, 6, VSTART] + [IMG] * 6 + [VEND, 7, 8, VSTART] + [IMG] * 8 + [VEND, 9, 10, 11]
+    px, grid = _image_inputs([[1, 4, 6], [1, 8, 4]], seed=3)
+    mm = dict(pixel_values=px, image_grid_thw=grid)
+
+    def trainer_logprobs(tokens):
+        with torch.no_grad():
+            lg = ours(torch.tensor(tokens), pixel_values=px, image_grid_thw=grid)[0]
+        return lg.log_softmax(-1)[:-1].gather(-1, torch.tensor(tokens[1:])[:, None]).squeeze(-1).numpy()
+
+    r = e.generate([ids], [dict(max_new_tokens=0)], logprob_start_len=0, mm=mm)[0]
+    assert np.abs(np.array(r.input_logprobs[1:]) - trainer_logprobs(ids)).max() < 2e-4
+    text = [5, 6, 7, 8, 9, 10, 11, 12]
+    a = e.add_request(ids, dict(max_new_tokens=7, temperature=0, ignore_eos=True), mm=mm)
+    b = e.add_request(text, dict(max_new_tokens=7, temperature=0, ignore_eos=True))
+    while e.has_work():
+        e.step()
+    assert a.rope_delta == (3 - 6) + (4 - 8)  # an image of 2 x 3 (4 x 2) merged patches advances the position by 3 (4), not by 6 (8)
+    ref = trainer_logprobs(ids + a.output_ids)[len(ids) - 1 :]
+    assert np.abs(np.array(a.output_logprobs) - ref).max() < 2e-4, np.abs(np.array(a.output_logprobs) - ref).max()
+    with torch.no_grad():
+        lg = ours(torch.tensor(text + b.output_ids))[0].log_softmax(-1)
+    ref_b = lg[len(text) - 1 : -1].gather(-1, torch.tensor(b.output_ids)[:, None]).squeeze(-1).numpy()
+    assert np.abs(np.array(b.output_logprobs) - ref_b).max() < 2e-4
+    # prompts with images neither offer nor reuse cached prefixes (placeholder ids do not identify the image)
+    again = e.generate([ids], [dict(max_new_tokens=2, temperature=0, ignore_eos=True)], mm=dict(pixel_values=px * 0.5, image_grid_thw=grid))[0]
+    assert again.num_cached_tokens == 0 and again.output_logprobs != a.output_logprobs[:2]
+
+
+def test_generate_endpoint_takes_images(pair):
+    import base64
+    import io
+
+    import numpy as np
+    import requests
+    from PIL import Image
+
+    from slime_b200.engine.http_server import EngineServer
+    from slime_b200.utils.image_processing import ImageProcessor, expand_image_placeholders
+
+    _, _, cfg, _ = pair
+    e = _engine(pair)
+    srv = EngineServer(e, port=0).start(block=False)
+    try:
+        url = f"http://127.0.0.1:{srv.port}"
+        rng = np.random.default_rng(0)
+        imgs = [Image.fromarray(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8)), Image.fromarray(rng.integers(0, 255, (32, 16, 3), dtype=np.uint8))]
+
+        def b64(im):
+            buf = io.BytesIO()
+            im.save(buf, format="PNG")
+            return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+        short = [5, VSTART, IMG, VEND, 7, VSTART, IMG, VEND, 9]  # one placeholder per image, as a chat template writes them
+        body = {"input_ids": short, "image_data": [b64(i) for i in imgs], "return_logprob": True,
+                "sampling_params": {"max_new_tokens": 5, "temperature": 0, "ignore_eos": True}}  # fmt: skip
+        out = requests.post(url + "/generate", json=body, timeout=60).json()
+        ip = ImageProcessor.from_vision_config(cfg.vision)
+        mm = ip(imgs)
+        counts = [ip.tokens_for(g) for g in mm["image_grid_thw"].tolist()]  # small images are scaled up to the minimum area
+        full = expand_image_placeholders(short, IMG, counts)
+        assert out["meta_info"]["prompt_tokens"] == len(full) == len(short) + sum(counts) - 2
+        want = e.generate([full], [dict(max_new_tokens=5, temperature=0, ignore_eos=True)], mm=mm)[0]
+        assert out["output_ids"] == want.output_ids
+        # an already expanded prompt is taken as it is; a prompt whose runs do not fit its images is refused
+        out2 = requests.post(url + "/generate", json=dict(body, input_ids=full), timeout=60).json()
+        assert out2["output_ids"] == want.output_ids
+        bad = requests.post(url + "/generate", json=dict(body, input_ids=short[:4]), timeout=60)
+        assert bad.status_code == 400 and "image" in bad.json()["error"]
+    finally:
+        srv.shutdown()
+
+
+def test_image_processor_matches_the_library_patch_layout():
+    import numpy as np
+    from PIL import Image
+    from transformers.models.qwen2_vl.image_processing_qwen2_vl import Qwen2VLImageProcessor
+
+    from slime_b200.utils.image_processing import ImageProcessor, smart_resize
+
+    rng = np.random.default_rng(0)
+    exact = [Image.fromarray(rng.integers(0, 255, (32, 48, 3), dtype=np.uint8))]  # already a multiple of patch * merge: no resize
+    odd = [Image.fromarray(rng.integers(0, 255, (37, 61, 3), dtype=np.uint8)), Image.fromarray(rng.integers(0, 255, (64, 32, 3), dtype=np.uint8))]
+    kw = dict(patch_size=4, temporal_patch_size=2, merge_size=2, min_pixels=16 * 16, max_pixels=64 * 64)
+    hf, mine = Qwen2VLImageProcessor(**kw), ImageProcessor(**kw)
+    a, b = hf(images=exact, return_tensors="pt"), mine(exact)
+    assert a["image_grid_thw"].tolist() == b["image_grid_thw"].tolist() == [[1, 8, 12]]
+    assert (a["pixel_values"] - b["pixel_values"]).abs().max() < 1e-5
+    a, b = hf(images=odd, return_tensors="pt"), mine(odd)
+    assert a["image_grid_thw"].tolist() == b["image_grid_thw"].tolist()
+    assert (a["pixel_values"] - b["pixel_values"]).abs().max() < 0.05  # resampling filters differ by a grey level
+    assert smart_resize(1000, 3000, 32, 56 * 56, 64 * 64 * 4)[0] * smart_resize(1000, 3000, 32, 56 * 56, 64 * 64 * 4)[1] <= 64 * 64 * 4
+    assert mine.tokens_for([1, 8, 12]) == 24
+
+
+def test_micro_batch_concatenates_processor_outputs_in_stream_order(pair):
+    """Samples with and without images in one micro-batch: the model kwargs are the per-sample tensors joined in order."""
+    from slime_b200.backends.train.data import DataIterator, get_batch
+
+    _, _, cfg, ours = pair
+    a = [5, VSTART] + [IMG] * 4 + [VEND, 7, 8]
+    b = [9, 10, 11]
+    c = [6, VSTART] + [IMG] * 6 + [VEND, 12]
+    pa, ga = _image_inputs([[1, 4, 4]], seed=1)
+    pc, gc = _image_inputs([[1, 4, 6]], seed=2)
+    data = {"tokens": [torch.tensor(a), torch.tensor(b), torch.tensor(c)],
+            "multimodal_train_inputs": [dict(pixel_values=pa, image_grid_thw=ga), None, dict(pixel_values=pc, image_grid_thw=gc)]}  # fmt: skip
+    batch = get_batch(DataIterator(data, [[0, 1, 2]]), ["tokens", "multimodal_train_inputs"], pad_multiplier=1)
+    mm = batch["multimodal"]
+    assert torch.equal(mm["pixel_values"], torch.cat([pa, pc])) and mm["image_grid_thw"].tolist() == [[1, 4, 4], [1, 4, 6]]
+    with torch.no_grad():
+        packed = ours(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"], **mm)[0]
+        alone = ours(torch.tensor(c), pixel_values=pc, image_grid_thw=gc)[0]
+    assert (packed[len(a) + len(b) :] - alone).abs().max() < 1e-4
