@@ -82,6 +82,8 @@ class Engine:
         self.stats = {"prefill_tokens": 0, "decode_tokens": 0, "cached_tokens": 0, "steps": 0, "aborted": 0,
                       "h2d_bytes": 0, "d2h_bytes": 0, "decode_steps": 0}  # fmt: skip
         self._init_decode_state()
+        if self.args.enable_deterministic_inference:
+            ops.set_batch_invariant(True)  # process-wide: an engine process serves one configuration
         self.spec = None  # host-driven speculative rounds instead of the slot-based decode loop
         if self.args.speculative_algorithm:
             from slime_b200.engine.speculative import SpeculativeDecoder

@@ -68,9 +68,24 @@ def _pick_bn(M: int, N: int, sms: int = 148) -> int:
     return 256 if cost256 <= cost128 else 128
 
 
+BATCH_INVARIANT = False
+
+
+def set_batch_invariant(on: bool = True):
+    """A row's result must not depend on what else is in the batch (``--sglang-enable-deterministic-inference``): no
+    split-K (its slices are summed by reduce-adds in arrival order, and the slice count follows the row count) and a
+    decode-attention split count that follows the cache geometry only. Tile widths still follow the shape: every output
+    element accumulates its K blocks in the same order whatever the tile. Same purpose as the batch-invariant operators
+    of docker/patch/latest/sglang-deterministic.patch:276-375 in the reference."""
+    global BATCH_INVARIANT
+    BATCH_INVARIANT = bool(on)
+
+
 def _pick_splitk(M: int, N: int, K: int, bn: int, sms: int = 148) -> int:
     """K slices for a GEMM whose output tiles cannot fill the machine (small weight gradients over many tokens,
     skinny decode projections with a long K): enough slices to occupy the SMs, at least 8 k-blocks of 64 each."""
+    if BATCH_INVARIANT:
+        return 1
     tiles = -(-M // 128) * -(-N // bn)
     kb = -(-K // 64)
     if tiles * 2 > sms or kb < 16:
@@ -472,6 +487,10 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
         # softmax sinks take the plain form
         return reference.paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size, scale, sinks)
     caller_splits = splits
+    if splits is None and BATCH_INVARIANT:
+        # the partial results of the splits are merged in split order: fix their number by the table width alone
+        tiles = -(-block_table.shape[1] * page_size // 128)
+        caller_splits = splits = max(1, min(16, -(-tiles // 16)))
     if splits is None:
         ctas = B * Hkv
         splits = 1 if ctas >= _lib.sm_count(q.device) else min(16, max(1, (2 * _lib.sm_count(q.device)) // max(ctas, 1)))
@@ -489,7 +508,7 @@ def paged_decode_attention(q, k_cache, v_cache, block_table, seq_lens, page_size
     # requests; below half an item per SM the two-chain kernel stays. SLIME_B200_DECODE_ATTN_WS=1 / 0 forces it on / off.
     ws_env = os.environ.get("SLIME_B200_DECODE_ATTN_WS", "")
     ws_ok = use_tensor_cores and D == 64 and Hq % Hkv == 0 and Hq // Hkv <= 8 and same_layout and ws_env != "0"
-    if ws_ok and (ws_env == "1" or 2 * B * Hkv >= _lib.sm_count(q.device)):
+    if ws_ok and (ws_env == "1" or (not BATCH_INVARIANT and 2 * B * Hkv >= _lib.sm_count(q.device))):  # one kernel for every batch size
         ns = splits
         if caller_splits is None:
             # its own split rule: enough items for the 4 x SMs groups, at least 8 tiles of 128 tokens per split

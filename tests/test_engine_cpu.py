@@ -364,3 +364,21 @@ def test_evicted_prefix_pages_come_back_from_the_host_tier():
     assert freeing.kv.allocator.host_tier.k is None and freeing.kv.allocator.host_tier.num_bytes() == 0
     freeing.resume_memory_occupation(["kv_cache"])
     assert freeing.kv.allocator.host_tier.k is not None
+
+
+def test_deterministic_inference_switch_removes_batch_dependent_choices():
+    from slime_b200 import ops
+
+    try:
+        assert ops._pick_splitk(8, 1024, 8192, 128) > 1
+        e = Engine(get_preset("tiny"), ServerArgs(page_size=4, max_running_requests=2, context_length=64, disable_cuda_graph=True,
+                                                  enable_deterministic_inference=True), device="cpu", num_pages=24)  # fmt: skip
+        assert ops.BATCH_INVARIANT and ops._pick_splitk(8, 1024, 8192, 128) == 1 == ops._pick_splitk(4096, 128, 65536, 128)
+        e.weights.init_random(0, std=0.2)
+        sp = dict(max_new_tokens=6, temperature=1.0, ignore_eos=True, sampling_seed=7)
+        alone = e.generate([[1, 2, 3, 4, 5]], [sp])[0]
+        crowd = e.generate([[1, 2, 3, 4, 5], [9, 8, 7], [4, 4, 4, 4, 4, 4, 4]], [sp, dict(sp, sampling_seed=1), dict(sp, sampling_seed=2)])[0]
+        # (bit equality is a property of the GPU kernels; the CPU reference matmul may differ in the last bit)
+        assert alone.output_ids == crowd.output_ids and np.abs(np.array(alone.output_logprobs) - np.array(crowd.output_logprobs)).max() < 1e-5
+    finally:
+        ops.set_batch_invariant(False)
