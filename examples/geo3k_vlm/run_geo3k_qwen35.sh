@@ -5,7 +5,7 @@
 # sides (trainer: inside the model; engine: `image_data`); other towers come in through --custom-model-provider-path.
 source "$(dirname -- "${BASH_SOURCE[0]}")/../../recipes/common.sh"
 launch train.py \
-  --hf-checkpoint "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-4B}" ${VLM_PROVIDER:+--custom-model-provider-path "${VLM_PROVIDER}"} \
+  --hf-checkpoint "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-35B-A3B}" ${VLM_PROVIDER:+--custom-model-provider-path "${VLM_PROVIDER}"} \
   --prompt-data "${DATA_DIR}/geo3k/train.parquet" --input-key problem --label-key answer \
   --multimodal-keys '{"image": "images"}' --apply-chat-template --rollout-shuffle --rm-type math \
   --num-rollout 300 --rollout-batch-size 32 --n-samples-per-prompt 8 --rollout-max-response-len 4096 \

@@ -4,7 +4,7 @@
 source "$(dirname -- "${BASH_SOURCE[0]}")/../../recipes/common.sh"
 HERE="$(dirname -- "${BASH_SOURCE[0]}")"
 launch train.py \
-  --hf-checkpoint "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-4B}" --ref-load "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-4B}" \
+  --hf-checkpoint "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-35B-A3B}" --ref-load "${CKPT_DIR}/${VLM_MODEL:-Qwen3.5-35B-A3B}" \
   --prompt-data "${DATA_DIR}/geo3k_imgurl/train.parquet" --input-key problem --label-key answer \
   --multimodal-keys '{"image": "images"}' --apply-chat-template --rollout-shuffle --rm-type math \
   --custom-generate-function-path examples.geo3k_vlm_multi_turn.rollout.generate \
