@@ -215,6 +215,8 @@ class EngineWeights:
         if name == "model.norm.weight":
             self.final_norm.copy_(t + plus1)
             return True
+        if name.startswith("mtp."):
+            return True  # Qwen3-Next / Qwen3.5 draft block: their recurrent trunks are not speculated on, the block is not kept
         mimo = _MIMO_DRAFT_RE.match(name)
         if mimo is not None:
             # MiMo stores its draft head outside the layer list, the joining projection's halves as (hidden, embedding)

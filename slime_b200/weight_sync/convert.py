@@ -23,6 +23,8 @@ from slime_b200.models.config import ModelConfig
 _LAYER = re.compile(r"^decoder\.layers\.(\d+)\.(.+)$")
 _EXPERT = re.compile(r"^mlp\.experts\.linear_fc([12])\.weight(\d+)$")
 _MTP = re.compile(r"^mtp\.layers\.(\d+)\.(.+)$")
+_QWEN_MTP = {"enorm.weight": "mtp.pre_fc_norm_embedding.weight", "hnorm.weight": "mtp.pre_fc_norm_hidden.weight",
+             "final_layernorm.weight": "mtp.norm.weight"}  # fmt: skip
 _MIMO_MTP = {"enorm.weight": "token_layernorm.weight", "hnorm.weight": "hidden_layernorm.weight",
              "final_layernorm.weight": "final_layernorm.weight"}  # fmt: skip
 
@@ -166,6 +168,21 @@ def _text_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str,
                 return [(f"{p}.{_MIMO_MTP[sub]}", t)]
             assert sub.startswith("transformer_layer."), name
             return [(n.replace(f"model.layers.{k}.", f"{p}.", 1), x) for n, x in _layer_to_hf(cfg, str(k), sub[len("transformer_layer.") :], t)]
+        if _family(cfg) in ("qwen3next", "qwen3_5"):
+            # Qwen3-Next / Qwen3.5 layout: a top-level ``mtp`` block; its norms are stored minus one like all norms of the
+            # family, Qwen3-Next keeps the joining projection's halves as (hidden, embedding)
+            # (slime/backends/megatron_utils/megatron_to_hf/qwen3_next.py:6-41, qwen3_5.py:6-31 in the reference)
+            if sub in _QWEN_MTP:
+                return [(_QWEN_MTP[sub], t - 1)]
+            if sub == "eh_proj.weight":
+                if _family(cfg) == "qwen3next":
+                    e_half, h_half = t.chunk(2, dim=1)
+                    t = torch.cat([h_half, e_half], dim=1)
+                return [("mtp.fc.weight", t)]
+            assert sub.startswith("transformer_layer."), name
+            out = _layer_to_hf(cfg, str(k), sub[len("transformer_layer.") :], t)
+            out = [(n, x - 1 if n.endswith(_ZERO_CENTRED) and ".linear_attn." not in n else x) for n, x in out]
+            return [(n.replace(f"model.layers.{k}.", f"mtp.layers.{k}.", 1), x) for n, x in out]
         # DeepSeek-V3 layout: draft depth k is checkpoint layer num_layers + k, with its own norms and projection
         i = str(cfg.num_layers + k)
         p = f"model.layers.{i}"
@@ -313,6 +330,13 @@ def _text_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
                 return [f"{p}.{_MIMO_MTP[sub]}"], "copy"
             names, rule = _text_sources_for(cfg, f"decoder.layers.{k}.{sub[len('transformer_layer.'):]}")
             return [n.replace(f"model.layers.{k}.", f"{p}.", 1) for n in names], rule
+        if _family(cfg) in ("qwen3next", "qwen3_5"):
+            if sub in _QWEN_MTP:
+                return [_QWEN_MTP[sub]], "copy+1"
+            if sub == "eh_proj.weight":
+                return ["mtp.fc.weight"], "swap_halves" if _family(cfg) == "qwen3next" else "copy"
+            names, rule = _text_sources_for(cfg, f"decoder.layers.{k}.{sub[len('transformer_layer.'):]}")
+            return [n.replace(f"model.layers.{k}.", f"mtp.layers.{k}.", 1) for n in names], rule
         p = f"model.layers.{cfg.num_layers + k}"
         own = {"enorm.weight": "enorm.weight", "hnorm.weight": "hnorm.weight", "eh_proj.weight": "eh_proj.weight",
                "final_layernorm.weight": "shared_head.norm.weight"}  # fmt: skip

@@ -413,3 +413,24 @@ def test_delta_rule_and_conv_continue_from_saved_state():
     state = hist.clone()[None]
     for t in range(cut, T):
         assert torch.allclose(mixers.short_conv_step(x[t][None], w, state)[0], ref[t], atol=1e-6), t
+
+
+def test_qwen_family_draft_block_names_round_trip():
+    from slime_b200.weight_sync import convert
+
+    """Qwen3-Next / Qwen3.5 keep the draft head in a top-level ``mtp`` block: norms minus one, Qwen3-Next's joining
+    projection with swapped halves, the inner layer under mtp.layers.k."""
+    for arch, swapped in (("Qwen3NextForCausalLM", True), ("Qwen3_5ForCausalLM", False)):
+        cfg = _tiny(mtp_num_layers=1, model_arch=arch, qk_layernorm=True)
+        model = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=2)
+        named = {n: p for n, p in model.named_parameters() if n.startswith("mtp.")}
+        hf = dict(x for n, p in named.items() for x in convert.convert_to_hf(cfg, n, p.detach()))
+        assert {"mtp.pre_fc_norm_embedding.weight", "mtp.pre_fc_norm_hidden.weight", "mtp.norm.weight", "mtp.fc.weight",
+                "mtp.layers.0.self_attn.q_proj.weight", "mtp.layers.0.input_layernorm.weight"} <= set(hf), sorted(hf)  # fmt: skip
+        assert torch.equal(hf["mtp.norm.weight"], named["mtp.layers.0.final_layernorm.weight"] - 1)
+        w = named["mtp.layers.0.eh_proj.weight"]
+        h = w.shape[1] // 2
+        assert torch.equal(hf["mtp.fc.weight"], torch.cat([w[:, h:], w[:, :h]], dim=1) if swapped else w)
+        for n, p in named.items():
+            names, rule = convert.hf_sources_for(cfg, n)
+            assert torch.allclose(convert.merge_hf_sources(rule, [hf[x] for x in names], cfg), p), n

@@ -256,3 +256,18 @@ def test_micro_batch_concatenates_processor_outputs_in_stream_order(pair):
         packed = ours(batch["tokens"], batch["position_ids"], packed_seq_params=batch["packed_seq_params"], **mm)[0]
         alone = ours(torch.tensor(c), pixel_values=pc, image_grid_thw=gc)[0]
     assert (packed[len(a) + len(b) :] - alone).abs().max() < 1e-4
+
+
+def test_position_streams_golden_vector_and_packed_reset():
+    """Two identical samples [start, 4 image tokens of a 4 x 4 grid merged 2 x 2, end, text]: temporal stays, height and
+    width spread over the 2 x 2 grid, text continues after the larger side; every packed sample restarts at zero."""
+    ids = torch.tensor([99, 10, 10, 10, 10, 98, 7, 99, 10, 10, 10, 10, 98, 8])
+    got, delta = vision.mrope_position_ids(ids, [0, 7, 14], torch.tensor([[1, 4, 4], [1, 4, 4]]), None, image_token_id=10, video_token_id=20)
+    want = torch.tensor([[0, 1, 1, 1, 1, 3, 4], [0, 1, 1, 2, 2, 3, 4], [0, 1, 2, 1, 2, 3, 4]])
+    assert torch.equal(got[:, :7], want) and torch.equal(got[:, 7:], want) and delta == [-2, -2]
+    with pytest.raises(ValueError, match="more grids"):
+        vision.mrope_position_ids(torch.tensor([1, 2, 3]), [0, 3], torch.tensor([[1, 4, 4]]), None, image_token_id=10, video_token_id=20)
+    # a two-frame video is two one-frame runs, each between its own markers
+    vid = torch.tensor([99, 20, 20, 20, 20, 98, 99, 20, 20, 20, 20, 98, 5])
+    got, _ = vision.mrope_position_ids(vid, [0, 13], None, torch.tensor([[2, 4, 4]]), image_token_id=10, video_token_id=20)
+    assert got[0].tolist() == [0, 1, 1, 1, 1, 3, 4, 5, 5, 5, 5, 7, 8] and got[2].tolist() == [0, 1, 2, 1, 2, 3, 4, 5, 6, 5, 6, 7, 8]
