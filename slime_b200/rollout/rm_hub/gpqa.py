@@ -34,11 +34,18 @@ def extract_letter(response: str, letters=DEFAULT_LETTERS) -> str | None:
     return tail[-1] if tail else None
 
 
+# the reference's names for the same things (plug-ins import them)
+DEFAULT_VALID_LETTERS = DEFAULT_LETTERS
+_extract_letter_from_response = extract_letter
+
+
 def compute_gpqa_reward(response: str, label, metadata: dict | None = None) -> float:
     md = metadata or {}
     choices = md.get("choices")
     letters = md.get("valid_letters") or (DEFAULT_LETTERS[: len(choices)] if choices else DEFAULT_LETTERS)
     correct = md.get("correct_letter")
+    if isinstance(correct, str):
+        correct = correct.strip().upper() or None
     if correct is None and label is not None:
         if isinstance(label, int):
             correct = letters[label] if 0 <= label < len(letters) else None

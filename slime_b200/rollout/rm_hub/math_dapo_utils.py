@@ -7,14 +7,23 @@ from __future__ import annotations
 
 import re
 
-from slime_b200.rollout.rm_hub.math_utils import last_boxed_only_string, remove_boxed
+from slime_b200.rollout.rm_hub.math_utils import last_boxed_only_string
+from slime_b200.rollout.rm_hub.math_utils import remove_boxed as _remove_boxed_or_none
+
+
+def remove_boxed(s: str) -> str:
+    """Content of ``\\boxed{...}``; unlike the lenient version of ``math_utils`` a string that is not a box is an error."""
+    out = _remove_boxed_or_none(s)
+    assert out is not None, f"box error: {s}"
+    return out
+
 
 _SUBS = [("an ", ""), ("a ", ""), (".$", "$"), ("\\$", ""), (r"\ ", ""), (" ", ""), ("mbox", "text"),
          (",\\text{and}", ","), ("\\text{and}", ","), ("\\text{m}", "\\text{}")]  # fmt: skip
 _REMOVED = ["square", "ways", "integers", "dollars", "mph", "inches", "hours", "km", "units", "\\ldots", "sue", "points",
             "feet", "minutes", "digits", "cents", "degrees", "cm", "gm", "pounds", "meters", "meals", "edges", "students",
             "childrentickets", "multiples", "\\text{s}", "\\text{.}", "\\text{\ns}", "\\text{}^2", "\\text{}^3", "\\text{\n}",
-            "\\text{}", r"\mathrm{th}", r"^\circ", r"^{\circ}", r"\;", r",\!", "{,}", '"', "\\dots"]  # fmt: skip
+            "\\text{}", r"\mathrm{th}", r"^\circ", r"^{\circ}", r"\;", r",\!", "{,}", '"', "\\dots", "<|im_end|>", "<|endoftext|>"]  # fmt: skip
 
 
 def normalize_final_answer(final_answer: str) -> str:
@@ -41,7 +50,7 @@ def is_correct_minerva(solution_str: str, gt: str, gt_need_extract: bool = False
     m = re.findall(answer_pattern, solution_str)
     pred = normalize_final_answer(m[-1]) if m else "[INVALID]"
     if gt_need_extract:
-        gt = normalize_final_answer(remove_boxed(last_boxed_only_string(gt)) or "")
+        gt = normalize_final_answer(_remove_boxed_or_none(last_boxed_only_string(gt)) or "")
     else:
         gt = normalize_final_answer(gt)
     return pred == gt, pred

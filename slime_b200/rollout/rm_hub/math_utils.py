@@ -32,6 +32,8 @@ def last_boxed_only_string(s: str) -> str | None:
 
 
 def remove_boxed(s: str) -> str | None:
+    if not isinstance(s, str):
+        return None
     for left in ("\\boxed{", "\\fbox{"):
         if s.startswith(left) and s.endswith("}"):
             return s[len(left) : -1]
@@ -130,6 +132,20 @@ def _split_tuple(s: str) -> list[str]:
     return [s]
 
 
+def _plain_fraction(s: str) -> str | None:
+    """``a/b`` for an answer that is nothing but a fraction of integer literals (``\frac{a}{b}`` or ``a/b``)."""
+    s = re.sub(r"^\\[dt]?frac\{(-?\d+)\}\{(\d+)\}$", r"\1/\2", s.replace(" ", ""))
+    return s if re.fullmatch(r"-?\d+/0*[1-9]\d*", s) else None
+
+
+def _is_integer_literal(s: str) -> bool:
+    try:
+        x = float(re.sub(r"(\d),(\d{3})\b", r"\1\2", s.strip()))
+        return abs(x - round(x)) <= 1e-7
+    except ValueError:
+        return False
+
+
 def grade_answer_sympy(given: str, truth: str) -> bool:
     if given is None or truth is None:
         return False
@@ -143,6 +159,13 @@ def grade_answer_sympy(given: str, truth: str) -> bool:
             continue
         if re.search(r"[a-zA-Z]{3,}", x) and not re.search(r"(sqrt|pi|frac)", x):
             return False  # free text never equals a different free text
+        fx, fy = _plain_fraction(x), _plain_fraction(y)
+        if fx is not None and fy is not None:
+            if fx != fy:
+                return False  # an unreduced fraction is not the reduced one: no simplification between two plain fractions
+            continue
+        if _is_integer_literal(x) != _is_integer_literal(y):
+            return False  # an integer answer must be given as that integer, not as an expression that evaluates to it
         if not _sympy_equal(x, y):
             return False
     return True
