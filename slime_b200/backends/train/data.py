@@ -48,7 +48,41 @@ def get_data_iterator(args, model_chunks, rollout_data):
     return [DataIterator(rollout_data, rollout_data["micro_batch_indices"]) for _ in range(n)]
 
 
-def get_batch(data_iterator: DataIterator, keys, pad_multiplier: int = 128, pad_token_id: int = 0, device=None):
+def _get_batch_allgather_cp(batch, tokens_list, pad_multiplier, pad_token_id, device):
+    """All-gather context parallelism: the samples are concatenated first, the stream is padded so that it divides into
+    equal pieces that are multiples of ``tp * pad_multiplier``, and CP rank r takes the r-th contiguous piece. The
+    cumulative lengths describe the whole stream; positions are the tokens' true in-sequence positions
+    (slime/backends/megatron_utils/data.py:55-73,117-128 in the reference)."""
+    cp, r = mpu.get_context_parallel_world_size(), mpu.get_context_parallel_rank()
+    tp = mpu.get_tensor_model_parallel_world_size()
+    cu = [0]
+    for t in tokens_list:
+        cu.append(cu[-1] + t.numel())
+    tokens = torch.cat(tokens_list)
+    positions = torch.cat([torch.arange(t.numel(), device=device, dtype=torch.int32) for t in tokens_list])
+    mult = cp * tp * pad_multiplier
+    pad = (-tokens.numel()) % mult
+    if pad:
+        tokens = F.pad(tokens, (0, pad), value=pad_token_id)
+        positions = torch.cat([positions, torch.arange(pad, device=device, dtype=torch.int32)])
+        cu.append(cu[-1] + pad)
+    local = tokens.numel() // cp
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=device)
+    max_len = max(b - a for a, b in zip(cu[:-1], cu[1:]))
+    piece = slice(r * local, (r + 1) * local)
+    batch["packed_seq_params"] = PackedSeqParams(cu_t, max_len, positions[piece])
+    batch["packed_seq_params"].local_cu_seqlens = cu_t
+    batch["tokens"] = tokens[piece].unsqueeze(0)
+    batch["position_ids"] = positions[piece].unsqueeze(0)
+    if batch.get("loss_masks") is not None:
+        full = [F.pad(m.to(torch.float32), (tl - rl - 1, 1)) for m, tl, rl in zip(batch["loss_masks"], batch["total_lengths"], batch["response_lengths"])]
+        fm = F.pad(torch.cat(full), (0, pad))
+        batch["full_loss_masks"] = fm[piece].unsqueeze(0)
+    return batch
+
+
+def get_batch(data_iterator: DataIterator, keys, pad_multiplier: int = 128, pad_token_id: int = 0, device=None,
+              allgather_cp: bool = False):
     """Build one packed micro-batch.
 
     Returns a dict with ``tokens`` [1, T_pad], ``position_ids`` [1, T_pad], ``packed_seq_params``,
@@ -62,6 +96,10 @@ def get_batch(data_iterator: DataIterator, keys, pad_multiplier: int = 128, pad_
     cp = mpu.get_context_parallel_world_size()
     tp = mpu.get_tensor_model_parallel_world_size()
     batch["unconcat_tokens"] = tokens_list
+    if allgather_cp and cp > 1:
+        if batch.get("multimodal_train_inputs") and any(batch["multimodal_train_inputs"]):
+            raise NotImplementedError("vision inputs with context parallelism")
+        return _get_batch_allgather_cp(batch, tokens_list, pad_multiplier, pad_token_id, device)
 
     pieces, pos_pieces, cu = [], [], [0]
     for t in tokens_list:

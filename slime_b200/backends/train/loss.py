@@ -19,12 +19,14 @@ from typing import Any
 
 import torch
 import torch.distributed as dist
+import torch.nn.functional as F
 
 from slime_b200.backends.train.cp_utils import (
     ZigZag,
     all_gather_with_cp,
     get_sum_of_sample_mean,
     local_loss_masks,
+    slice_log_prob_with_cp,
 )
 from slime_b200.parallel import state as mpu
 from slime_b200.utils.misc import load_function
@@ -75,6 +77,12 @@ def get_responses(logits, *, args, unconcat_tokens, total_lengths, response_leng
     if temp != 1.0:
         logits = logits / temp
     cp = mpu.get_context_parallel_world_size()
+    if cp > 1 and getattr(args, "allgather_cp", False):
+        # this rank holds one contiguous piece of the concatenated stream: a sample's local rows are one interval
+        for (r0, r1, s0, s1), tokens, tl, rl in zip(allgather_cp_rows(total_lengths, response_lengths, logits.shape[0]),
+                                                      unconcat_tokens, total_lengths, response_lengths):  # fmt: skip
+            yield logits[r0:r1], tokens[tl - rl + s0 : tl - rl + s1]
+        return
     end = 0
     for i, (tokens, tl, rl) in enumerate(zip(unconcat_tokens, total_lengths, response_lengths)):
         if cp == 1:
@@ -93,6 +101,43 @@ def get_responses(logits, *, args, unconcat_tokens, total_lengths, response_leng
             t1 = tokens[z.tokens[1][0] : z.tokens[1][1]]
             end += 2 * z.chunk_size
             yield torch.cat([rows0, rows1], dim=0), torch.cat([t0, t1], dim=0)
+
+
+def allgather_cp_rows(total_lengths, response_lengths, local_len: int):
+    """Per sample ``(first local row, end local row, first response position, end response position)``: which rows of
+    this rank's contiguous piece (``local_len`` rows of the concatenated stream) predict response tokens of the sample, and
+    which response positions those are. Empty intervals are ``(0, 0, 0, 0)``."""
+    lo = mpu.get_context_parallel_rank() * local_len
+    hi = lo + local_len
+    out, start = [], 0
+    for tl, rl in zip(total_lengths, response_lengths):
+        g0, g1 = start + tl - rl - 1, start + tl - 1  # stream rows whose next token is a response token
+        s, e = max(g0, lo), min(g1, hi)
+        out.append((s - lo, e - lo, s - g0, e - g0) if e > s else (0, 0, 0, 0))
+        start += tl
+    return out
+
+
+def redistribute_allgather_cp(res: dict, total_lengths, response_lengths, local_len: int) -> None:
+    """Per-sample response tensors computed on contiguous pieces -> the zig-zag pieces every reducer downstream expects:
+    each rank places what it has into a zero vector of the sample's response length, one differentiable sum over the
+    context-parallel group rebuilds the whole vectors, each rank then keeps its zig-zag rows. In place. (Same device as
+    slime/backends/megatron_utils/loss.py:194-271 in the reference.)"""
+    from slime_b200.backends.train.cp_utils import _AllReduceSum
+
+    spans = allgather_cp_rows(total_lengths, response_lengths, local_len)
+    for key, values in res.items():
+        if not values or all(v is None for v in values):
+            continue
+        ref = next(v for v in values if v is not None)
+        full = []
+        for v, (_r0, _r1, s0, s1), rl in zip(values, spans, response_lengths):
+            if v is None or s1 <= s0:
+                full.append(ref.new_zeros(rl))
+            else:
+                full.append(F.pad(v, (s0, rl - s1)))
+        whole = _AllReduceSum.apply(torch.cat(full), mpu.get_context_parallel_group())
+        res[key] = [slice_log_prob_with_cp(x, tl, rl) for x, tl, rl in zip(whole.split(list(response_lengths)), total_lengths, response_lengths)]
 
 
 def get_rollout_top_p_logprob_kwargs(args, batch) -> dict:
@@ -139,6 +184,9 @@ def get_log_probs_and_entropy(
     """Per-sample response log-probs (and entropies) from packed vocab-parallel logits."""
     tp_group = mpu.get_tensor_model_parallel_group()
     tp_rank = mpu.get_tensor_model_parallel_rank()
+    allgather = mpu.get_context_parallel_world_size() > 1 and getattr(args, "allgather_cp", False)
+    local_len = (logits.shape[1] if logits.dim() == 3 else logits.shape[0]) if allgather else 0
+    spans = allgather_cp_rows(total_lengths, response_lengths, local_len) if allgather else None
     lps, ents = [], []
     for i, (rows, toks) in enumerate(
         get_responses(logits, args=args, unconcat_tokens=unconcat_tokens, total_lengths=total_lengths,
@@ -147,7 +195,10 @@ def get_log_probs_and_entropy(
         keep = None
         if rollout_top_p_token_ids is not None:
             rl, tl = response_lengths[i], total_lengths[i]
-            slices = (slice(0, rl),) if mpu.get_context_parallel_world_size() == 1 else ZigZag.plan(tl, rl).response_slices()
+            if allgather:
+                slices = (slice(spans[i][2], spans[i][3]),)
+            else:
+                slices = (slice(0, rl),) if mpu.get_context_parallel_world_size() == 1 else ZigZag.plan(tl, rl).response_slices()
             vp = rows.shape[-1]
             keep = _keep_mask_rows(rollout_top_p_token_ids[i], rollout_top_p_token_offsets[i], slices, tp_rank * vp, vp,
                                    rows.device)  # fmt: skip
@@ -161,6 +212,8 @@ def get_log_probs_and_entropy(
     res = {"log_probs": lps}
     if with_entropy:
         res["entropy"] = ents
+    if allgather:
+        redistribute_allgather_cp(res, total_lengths, response_lengths, local_len)
     return torch.empty(0, device=logits.device), res
 
 
@@ -172,7 +225,10 @@ def get_values(logits, *, args, unconcat_tokens, total_lengths, response_lengths
     for rows, _t in get_responses(logits, args=a, unconcat_tokens=unconcat_tokens, total_lengths=total_lengths,
                                   response_lengths=response_lengths, max_seq_lens=max_seq_lens):  # fmt: skip
         vals.append(rows.squeeze(-1).float())
-    return torch.empty(0, device=logits.device), {"values": vals}
+    res = {"values": vals}
+    if mpu.get_context_parallel_world_size() > 1 and getattr(args, "allgather_cp", False):
+        redistribute_allgather_cp(res, total_lengths, response_lengths, logits.shape[1] if logits.dim() == 3 else logits.shape[0])
+    return torch.empty(0, device=logits.device), res
 
 
 # ------------------------------------------------------------------- advantages

@@ -42,6 +42,10 @@ class TrainModel:
         self.args, self.role = args, role
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
         self.cfg = ModelConfig.from_args(args)
+        if getattr(args, "allgather_cp", False):
+            from slime_b200.models import mixers
+
+            mixers.set_allgather_cp(True)
         if getattr(args, "max_tokens_per_gpu", None):
             from slime_b200.parallel import fused_tp
 

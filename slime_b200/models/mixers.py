@@ -86,27 +86,77 @@ def _rms(x, w, eps):
     return (y * w.float()).to(x.dtype)
 
 
-def dense_causal_attention(q, k, v, cu_seqlens, scale, allowed=None):
-    """Per-sequence causal attention with explicit matrices: q / k [T, H, Dqk], v [T, H, Dv] (query / key and value
-    widths may differ), ``allowed`` [T, Lmax] bool optional extra mask per query row over the keys of ITS sequence
-    (column j = j-th token of the sequence). fp32 math; meant for correctness, not for long sequences."""
-    out = torch.zeros(q.shape[0], q.shape[1], v.shape[-1], dtype=torch.float32, device=q.device)
+def dense_causal_attention(q, k, v, cu_seqlens, scale, allowed=None, q_offset: int = 0):
+    """Per-sequence causal attention with explicit matrices: q [Tq, H, Dqk], k [T, H, Dqk], v [T, H, Dv] (query / key and
+    value widths may differ), ``allowed`` [Tq, Lmax] bool optional extra mask per query row over the keys of ITS sequence
+    (column j = j-th token of the sequence). The query rows are rows ``q_offset .. q_offset + Tq`` of the packed stream
+    that ``k`` / ``v`` / ``cu_seqlens`` describe (all of it by default; a contiguous window under all-gather context
+    parallelism). fp32 math; meant for correctness, not for long sequences."""
+    Tq = q.shape[0]
+    out = torch.zeros(Tq, q.shape[1], v.shape[-1], dtype=torch.float32, device=q.device)
     pieces = []
     cu = cu_seqlens.tolist()
     for a, b in zip(cu[:-1], cu[1:]):
-        n = b - a
-        if n <= 0:
+        lo, hi = max(a, q_offset), min(b, q_offset + Tq)  # this sequence's rows inside the window
+        if hi <= lo:
             continue
-        qs, ks, vs = (t[a:b].float().transpose(0, 1) for t in (q, k, v))
+        qs = q[lo - q_offset : hi - q_offset].float().transpose(0, 1)
+        ks, vs = (t[a:hi].float().transpose(0, 1) for t in (k, v))  # keys up to the window's last row of the sequence
         att = (qs @ ks.transpose(-1, -2)) * scale
-        mask = torch.ones(n, n, dtype=torch.bool, device=q.device).tril()
+        mask = torch.arange(a, hi, device=q.device)[None, :] <= torch.arange(lo, hi, device=q.device)[:, None]
         if allowed is not None:
-            mask = mask & allowed[a:b, :n]
+            mask = mask & allowed[lo - q_offset : hi - q_offset, : hi - a]
         att = att.masked_fill(~mask, float("-inf"))
-        pieces.append((a, b, (att.softmax(-1) @ vs).transpose(0, 1)))
+        pieces.append((lo - q_offset, hi - q_offset, (att.softmax(-1) @ vs).transpose(0, 1)))
     for a, b, o in pieces:
-        out = out + F.pad(o, (0, 0, 0, 0, a, q.shape[0] - b))
+        out = out + F.pad(o, (0, 0, 0, 0, a, Tq - b))
     return out.to(q.dtype)
+
+
+# ------------------------------------------------------------------------------------- all-gather context parallelism
+ALLGATHER_CP = False
+
+
+def set_allgather_cp(on: bool):
+    """``--allgather-cp``: the packed stream of a micro-batch is cut into contiguous pieces, one per context-parallel rank;
+    latent-attention layers compute their own rows against keys / values gathered from all ranks (every other layer is
+    token-local). Same role as the all-gather mode of slime_plugins/models/glm5/glm5.py:850-852,921-928 in the reference."""
+    global ALLGATHER_CP
+    ALLGATHER_CP = bool(on)
+
+
+def allgather_cp_active() -> bool:
+    return ALLGATHER_CP and mpu.get_context_parallel_world_size() > 1
+
+
+class _GatherFromContextParallel(torch.autograd.Function):
+    """Rank-major concatenation of equally sized pieces along dim 0; the gradient of a rank's piece is the sum over ranks
+    of the gradients of that slice."""
+
+    @staticmethod
+    def forward(ctx, x):
+        group = mpu.get_context_parallel_group()
+        n = mpu.get_context_parallel_world_size()
+        out = torch.empty(n * x.shape[0], *x.shape[1:], dtype=x.dtype, device=x.device)
+        torch.distributed.all_gather_into_tensor(out, x.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        group = mpu.get_context_parallel_group()
+        n, r = mpu.get_context_parallel_world_size(), mpu.get_context_parallel_rank()
+        g = g.contiguous()
+        rows = g.shape[0] // n
+        if torch.distributed.get_backend(group) == "nccl":
+            out = torch.empty(rows, *g.shape[1:], dtype=g.dtype, device=g.device)
+            torch.distributed.reduce_scatter_tensor(out, g, group=group)
+            return out
+        torch.distributed.all_reduce(g, group=group)
+        return g[r * rows : (r + 1) * rows].clone()
+
+
+def gather_from_context_parallel(x):
+    return _GatherFromContextParallel.apply(x)
 
 
 # -------------------------------------------------------------------------------------------- attention variants
@@ -478,7 +528,7 @@ class MLASelfAttention(nn.Module):
         k = torch.cat([k_nope, k_pe.expand(T, self.hq, self.dr)], dim=-1)
         return q, k, v, q_latent, (cos, sin)
 
-    def _allowed(self, inp, q_latent, rope, packed):
+    def _allowed(self, inp, q_latent, rope, packed, q_offset=0):
         return None
 
     def forward(self, x, residual, rope_table, packed):
@@ -486,7 +536,13 @@ class MLASelfAttention(nn.Module):
         normed, residual = ops.rmsnorm(x, self.input_layernorm.weight, cfg.norm_epsilon, residual)
         inp = tp.gather_from_sequence_parallel_region_no_reduce(normed) if self.sp else normed
         q, k, v, q_latent, rope = self._qkv(inp, packed)
-        ctx = dense_causal_attention(q, k, v, packed.cu_seqlens, self.scale, self._allowed(inp, q_latent, rope, packed))
+        q_offset = 0
+        if allgather_cp_active():  # this rank's rows against every rank's keys and values
+            q_offset = mpu.get_context_parallel_rank() * inp.shape[0]
+            k, v = gather_from_context_parallel(k), gather_from_context_parallel(v)
+        elif mpu.get_context_parallel_world_size() > 1:
+            raise NotImplementedError("latent attention under context parallelism needs --allgather-cp")
+        ctx = dense_causal_attention(q, k, v, packed.cu_seqlens, self.scale, self._allowed(inp, q_latent, rope, packed, q_offset), q_offset)
         out = F.linear(ctx.reshape(inp.shape[0], -1), self.linear_proj.weight)
         return (tp.scatter_to_sequence_parallel_region(out) if self.sp else out), residual
 
@@ -497,25 +553,27 @@ def indexer_logits(q_idx, k_idx, weights):
     return torch.einsum("thd,sd->ths", q_idx.float(), k_idx.float()).relu_().mul_(weights.float()[:, :, None]).sum(1)
 
 
-def select_topk_keys(logits_fn, cu_seqlens, T: int, topk: int, device) -> torch.Tensor:
+def select_topk_keys(logits_fn, cu_seqlens, T: int, topk: int, device, q_offset: int = 0) -> torch.Tensor:
     """Per query row the ``topk`` best-scoring keys among the causally visible ones of its own sequence, as a boolean
-    matrix [T, Lmax] over in-sequence key positions (rows with fewer visible keys keep all of them).
-    ``logits_fn(a, b)`` returns the [b - a, b - a] score block of one sequence."""
+    matrix [T, Lmax] over in-sequence key positions (rows with fewer visible keys keep all of them). The ``T`` query rows
+    are rows ``q_offset .. q_offset + T`` of the packed stream. ``logits_fn(q0, q1, k0, k1)`` returns the score block of
+    query rows ``q0 .. q1`` (counted inside the window) against keys ``k0 .. k1`` (counted in the whole stream)."""
     cu = cu_seqlens.tolist()
     lmax = max((b - a for a, b in zip(cu[:-1], cu[1:])), default=0)
     allowed = torch.zeros(T, lmax, dtype=torch.bool, device=device)
     for a, b in zip(cu[:-1], cu[1:]):
-        n = b - a
-        if n <= 0:
+        lo, hi = max(a, q_offset), min(b, q_offset + T)
+        if hi <= lo:
             continue
-        causal = torch.ones(n, n, dtype=torch.bool, device=device).tril()
+        n = hi - a  # keys the window's last row of this sequence can see
+        causal = torch.arange(a, hi, device=device)[None, :] <= torch.arange(lo, hi, device=device)[:, None]
         if n <= topk:
-            allowed[a:b, :n] = causal
+            allowed[lo - q_offset : hi - q_offset, :n] = causal
             continue
-        scores = logits_fn(a, b).masked_fill(~causal, float("-inf"))
+        scores = logits_fn(lo - q_offset, hi - q_offset, a, hi).masked_fill(~causal, float("-inf"))
         idx = scores.topk(topk, dim=-1).indices
-        pick = torch.zeros(n, n, dtype=torch.bool, device=device).scatter_(1, idx, True)
-        allowed[a:b, :n] = pick & causal
+        pick = torch.zeros(hi - lo, n, dtype=torch.bool, device=device).scatter_(1, idx, True)
+        allowed[lo - q_offset : hi - q_offset, :n] = pick & causal
     return allowed
 
 
@@ -547,7 +605,7 @@ class DSASelfAttention(MLASelfAttention):
             self.k_norm.weight, self.k_norm.bias = mk(self.di, ones=True), mk(self.di, std=0.0)
             self.weights_proj.weight = mk(self.hi, cfg.hidden_size, std=cfg.init_method_std)
 
-    def _allowed(self, inp, q_latent, rope, packed):
+    def _allowed(self, inp, q_latent, rope, packed, q_offset=0):
         holder = getattr(packed, self._HOLDER, None)
         if holder is None:
             holder = {}
@@ -564,8 +622,10 @@ class DSASelfAttention(MLASelfAttention):
             k_idx = F.layer_norm(F.linear(inp, self.wk.weight).float(), (self.di,), self.k_norm.weight.float(), self.k_norm.bias.float())
             k_idx = apply_rotary(k_idx.view(T, 1, self.di), cos, sin, cfg.rotary_interleaved).view(T, self.di)
             w = F.linear(inp, self.weights_proj.weight).float() * (self.hi**-0.5) * (self.di**-0.5)
-            allowed = select_topk_keys(lambda a, b: indexer_logits(q_idx[a:b], k_idx[a:b], w[a:b]), packed.cu_seqlens, T,
-                                       cfg.index_topk, inp.device)  # fmt: skip
+            if allgather_cp_active():  # the indexer's keys of every rank (no gradient flows through the choice)
+                k_idx = gather_from_context_parallel(k_idx)
+            allowed = select_topk_keys(lambda q0, q1, k0, k1: indexer_logits(q_idx[q0:q1], k_idx[k0:k1], w[q0:q1]),
+                                       packed.cu_seqlens, T, cfg.index_topk, inp.device, q_offset)  # fmt: skip
         holder[self.layer_number] = allowed
         return allowed
 

@@ -55,7 +55,8 @@ def _get_batch(model, data_iterator, args):
     from slime_b200.backends.train.model import BATCH_KEYS
 
     keys = [k for k in BATCH_KEYS if k in data_iterator.rollout_data]
-    return get_batch(data_iterator, keys, getattr(args, "data_pad_size_multiplier", 128), device=model.device)
+    return get_batch(data_iterator, keys, getattr(args, "data_pad_size_multiplier", 128), device=model.device,
+                     allgather_cp=getattr(args, "allgather_cp", False))
 
 
 def _run_interleaved(model, data_iterator, num_microbatches: int, forward_step, args, forward_only: bool) -> list[dict]:

@@ -465,6 +465,9 @@ def backend_validate_args(args) -> None:
     if args.allgather_cp and not (getattr(args, "index_topk", None)
                                   or str(getattr(args, "model_arch", "")).lower().startswith(("deepseekv32", "glmmoedsa"))):
         raise ValueError("--allgather-cp is only supported for DSA (DeepSeek-V3.2 / GLM-5) models")
+    if args.allgather_cp and getattr(args, "context_parallel_size", 1) > 1 and (
+            getattr(args, "use_rollout_routing_replay", False) or getattr(args, "enable_mtp_training", False)):
+        raise ValueError("--allgather-cp: rollout routing replay and draft-head training still assume the zig-zag token layout")
     if args.virtual_pipeline_model_parallel_size is None and args.num_layers_per_virtual_pipeline_stage:
         per_stage = args.num_layers // args.pipeline_model_parallel_size
         args.virtual_pipeline_model_parallel_size = per_stage // args.num_layers_per_virtual_pipeline_stage

@@ -39,3 +39,15 @@ def test_colocated_moe_with_fp8_engine_and_rollout_routing_replay():
                         "127.0.0.1", "--master-port", "29699", os.path.join(ROOT, "tests/multigpu/colocated_moe_check.py")],
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=400)  # fmt: skip
     assert r.returncode == 0 and "RESULT ok world=2 ep=2" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("kind,port", [("dsa", 29745), ("mla", 29746)])
+def test_allgather_context_parallelism_of_latent_attention(kind, port):
+    """Two gloo ranks hold the two contiguous halves of a micro-batch's stream; keys, values and indexer keys are gathered
+    inside the attention layers. Logits, summed gradients, redistributed response log-probs / entropies / values and the
+    rows of a top-p keep mask equal the single-rank run."""
+    env = dict(os.environ, ALLGATHER_CP_MODEL=kind, MASTER_ADDR="127.0.0.1", OMP_NUM_THREADS="1")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+                        "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests/multigpu/allgather_cp_check.py")],
+                       env=env, cwd=ROOT, capture_output=True, text=True, timeout=280)  # fmt: skip
+    assert r.returncode == 0 and f"RESULT ok world=2 model={kind}" in r.stdout, r.stdout[-1500:] + r.stderr[-3000:]
