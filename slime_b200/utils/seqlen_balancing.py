@@ -69,8 +69,9 @@ def greedy_partition(seqlen_list: list[int], k_partitions: int, equal_size: bool
 def get_seqlen_balanced_partitions(seqlen_list: list[int], k_partitions: int, equal_size: bool) -> list[list[int]]:
     """Partition indices into ``k_partitions`` lists with near-equal weight sums.
 
-    Every index appears exactly once; no part is empty; parts are ordered by
-    their smallest index so the output is deterministic.
+    Every index appears exactly once; no part is empty; parts come heaviest first (ties: more items first, then the
+    smaller first index), each part's indices ascending: the same sample-to-rank assignment as the reference's
+    partitioner (slime/utils/seqlen_balancing.py:20-110), so a run can be compared rank by rank.
     """
     assert len(seqlen_list) >= k_partitions, f"{len(seqlen_list)} items < {k_partitions} partitions"
     parts = karmarkar_karp(seqlen_list, k_partitions, equal_size)
@@ -79,7 +80,8 @@ def get_seqlen_balanced_partitions(seqlen_list: list[int], k_partitions: int, eq
     seen = sorted(i for p in parts for i in p)
     assert seen == list(range(len(seqlen_list)))
     assert all(parts), "empty partition"
-    return sorted(parts, key=lambda p: p[0])
+    parts = [sorted(p) for p in parts]
+    return sorted(parts, key=lambda p: (-sum(seqlen_list[i] for i in p), -len(p), p[0]))
 
 
 def first_fit_pack(total_lengths, max_tokens_per_bin: int) -> list[list[int]]:

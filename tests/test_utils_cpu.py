@@ -211,3 +211,63 @@ def test_debug_mode_catches_bad_indices_before_any_launch(monkeypatch):
         attention.segment_attention(torch.randn(6, 2, 4), torch.randn(6, 1, 4), torch.randn(6, 1, 4), torch.tensor([[0, 3, 2, 7]], dtype=torch.int32))
     monkeypatch.setenv("SLIME_B200_CHECKS", "0")
     _checks.index_range("x", "y", torch.tensor([5]), upper=2)  # switched off: no check, no cost
+
+
+def test_dp_schedule_fixed_cases():
+    """Static / balanced / dynamic / interleaved-pipeline / grouped-rollout schedules on fixed inputs: every rank's
+    micro-batches tile its partition, partitions are disjoint and cover what is expected, a micro-batch above the token cap
+    holds a single sample. The FLOPs-balanced split of [1, 2, 3, 4, 5, 7, 9, 10] over two ranks is [[1, 2, 5, 6], [0, 3, 4, 7]]
+    (heavier part first), as in the reference's tests/test_dp_schedule.py."""
+    from types import SimpleNamespace
+
+    def A(**k):
+        d = dict(micro_batch_size=1, use_dynamic_batch_size=False, max_tokens_per_gpu=None, balance_data=False, balance_by_flops=False,
+                 hidden_size=16, num_attention_heads=2, num_query_groups=2, vocab_size=32, ffn_hidden_size=64, num_experts=None,
+                 num_layers=2, kv_channels=8)  # fmt: skip
+        d.update(k)
+        return SimpleNamespace(**d)
+
+    def P(dp=1, vpp=1, group=1):
+        return {"dp_size": dp, "cp_size": 1, "vpp_size": vpp, "microbatch_group_size_per_vp_stage": group}
+
+    def check(parts, mbi, nmb, dp, expect, lengths, cap=None):
+        seen = set()
+        for r in range(dp):
+            assert len(mbi[r]) == sum(nmb) and [i for m in mbi[r] for i in m] == list(range(len(parts[r])))
+            assert seen.isdisjoint(parts[r])
+            seen.update(parts[r])
+            for m in mbi[r]:
+                assert cap is None or sum(lengths[parts[r][i]] for i in m) <= cap or len(m) == 1
+        assert seen == set(expect)
+
+    tl = [10] * 16
+    p, m, n, g = build_dp_schedule(A(micro_batch_size=2), P(4), tl, global_batch_size=16, rollout_indices=list(range(16)))
+    assert n == [2] and g == [16]
+    check(p, m, n, 4, range(16), tl)
+    tl = [1, 2, 3, 4, 5, 6, 7, 8, 8, 7, 6, 5, 4, 3, 2, 1]
+    p, m, n, g = build_dp_schedule(A(micro_batch_size=2, balance_data=True), P(2), tl, global_batch_size=8, rollout_indices=list(range(16)))
+    assert n == [2, 2] and g == [8, 8]
+    check(p, m, n, 2, range(16), tl)
+    p, m, n, g = build_dp_schedule(A(balance_data=True), P(2), [1, 2, 3, 4, 5, 7, 9, 10], global_batch_size=8, rollout_indices=list(range(8)))
+    assert p == [[1, 2, 5, 6], [0, 3, 4, 7]] and n == [4] and g == [8]
+    dyn = A(use_dynamic_batch_size=True, max_tokens_per_gpu=10)
+    tl = [15, 3, 3, 3, 3, 3, 3, 3]  # the oversized sample gets a micro-batch of its own
+    p, m, n, g = build_dp_schedule(dyn, P(2), tl, global_batch_size=8, rollout_indices=list(range(8)))
+    check(p, m, n, 2, range(8), tl, cap=10)
+    tl = [4] * 32
+    p, m, n, g = build_dp_schedule(A(use_dynamic_batch_size=True, max_tokens_per_gpu=8), P(2, vpp=2, group=2), tl, global_batch_size=16,
+                                   rollout_indices=list(range(32)))  # fmt: skip
+    assert all(x % 2 == 0 for x in n)
+    check(p, m, n, 2, range(32), tl, cap=8)
+    dyn = A(use_dynamic_batch_size=True, max_tokens_per_gpu=12)
+    p, m, n, g = build_dp_schedule(dyn, P(1), [3] * 9, global_batch_size=1, rollout_indices=[0, 0, 0, 1, 1, 2, 2, 2, 2])
+    assert g == [1, 1, 1]  # a rollout's samples stay in one step
+    cur = 0
+    for step, k in enumerate(n):
+        assert sorted(p[0][j] for mb in m[0][cur : cur + k] for j in mb) == [[0, 1, 2], [3, 4], [5, 6, 7, 8]][step]
+        cur += k
+    p, m, n, g = build_dp_schedule(dyn, P(1), [3] * 8, global_batch_size=2, rollout_indices=[0, 0, 1, 2, 2, 3, 4, 4])
+    assert g == [2, 2]  # the fifth rollout does not fill a step and is dropped
+    check(p, m, n, 1, range(6), [3] * 8, cap=12)
+    with pytest.raises(AssertionError, match="num_rollouts"):
+        build_dp_schedule(dyn, P(1), [3] * 6, global_batch_size=4, rollout_indices=[0, 0, 1, 1, 2, 2])
