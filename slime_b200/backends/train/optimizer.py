@@ -206,10 +206,11 @@ class DistributedOptimizer:
 
 class StatelessAdam(torch.optim.Optimizer):
     """Adam whose moments start from zero every step: ``p -= lr * g / (|g| + eps')`` up to bias terms.
-    Keeps no state tensors, so it costs no optimizer memory."""
+    Keeps no state tensors, so it costs no optimizer memory. Every step equals the first step of a freshly created
+    ``torch.optim.AdamW`` (``adam_w_mode``, decoupled decay) or ``torch.optim.Adam`` (decay added to the gradient)."""
 
-    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0):
-        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay))
+    def __init__(self, params, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, adam_w_mode: bool = True):
+        super().__init__(params, dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, adam_w_mode=adam_w_mode))
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -219,11 +220,13 @@ class StatelessAdam(torch.optim.Optimizer):
             for p in group["params"]:
                 if p.grad is None:
                     continue
-                g = p.grad.float()
+                g = p.grad if p.grad.dtype == torch.float64 else p.grad.float()
+                if group["weight_decay"] and group["adam_w_mode"]:
+                    p.mul_(1 - group["lr"] * group["weight_decay"])
+                elif group["weight_decay"]:
+                    g = g + group["weight_decay"] * p.to(g.dtype)
                 m = (1 - b1) * g
                 v = (1 - b2) * g * g
-                if group["weight_decay"]:
-                    p.mul_(1 - group["lr"] * group["weight_decay"])
                 upd = (m / (1 - b1)) / ((v / (1 - b2)).sqrt() + group["eps"])
                 p.add_(upd.to(p.dtype), alpha=-group["lr"])
         return loss

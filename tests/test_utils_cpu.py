@@ -148,6 +148,23 @@ def test_stateless_adam_is_a_sign_like_step_and_keeps_no_state():
     q = torch.nn.Parameter(torch.ones(2))
     StatelessAdam([q], lr=0.1, weight_decay=0.5).step()  # no gradient: untouched, decay included
     assert torch.equal(q.detach(), torch.ones(2))
+    # every step is the first step of a freshly created torch optimizer, with decoupled or coupled weight decay
+    for decoupled, cls in ((True, torch.optim.AdamW), (False, torch.optim.Adam)):
+        torch.manual_seed(0)
+        start = torch.randn(8, dtype=torch.float64)
+        grads = [torch.randn_like(start) for _ in range(4)]
+        ours, kw = start.clone(), dict(lr=0.03, betas=(0.9, 0.98), eps=1e-6, weight_decay=0.1)
+        opt = StatelessAdam([ours], adam_w_mode=decoupled, **kw)
+        ref = start.clone()
+        for g in grads:
+            ours.grad = g.clone()
+            opt.step()
+            opt.zero_grad()
+            ref = ref.detach().requires_grad_(True)
+            fresh = cls([ref], **kw)
+            ref.grad = g.clone()
+            fresh.step()
+        assert torch.allclose(ours, ref.detach(), atol=1e-12) and opt.state_dict()["state"] == {}
 
 
 # ------------------------------------------------------------------------------------------------ quantisation
