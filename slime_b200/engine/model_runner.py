@@ -196,6 +196,10 @@ class EngineWeights:
             return True
         if name.startswith("model.language_model."):  # checkpoints with a vision tower nest the language model
             name = "model." + name[len("model.language_model.") :]
+        if ".block_sparse_moe." in name:  # MiniMax-M2 spelling of the expert tensors
+            from slime_b200.weight_sync.convert import family_name_to_generic
+
+            name = family_name_to_generic(name)
         raw = t
         t = t.to(self.device, self.dtype, non_blocking=True)
         if name == "model.embed_tokens.weight":

@@ -220,10 +220,11 @@ class ModelConfig:
             qk_layernorm=a.startswith("qwen3"),
             model_arch=arch,
         )
-        if c.get("num_experts") or c.get("n_routed_experts"):
+        n_experts = c.get("num_experts") or c.get("n_routed_experts") or c.get("num_local_experts")
+        if n_experts:
             kw.update(
-                num_experts=c.get("num_experts") or c.get("n_routed_experts"),
-                moe_ffn_hidden_size=c.get("moe_intermediate_size"),
+                num_experts=n_experts,
+                moe_ffn_hidden_size=c.get("moe_intermediate_size") or c.get("intermediate_size"),
                 moe_router_topk=c.get("num_experts_per_tok", 2),
                 norm_topk_prob=c.get("norm_topk_prob", True),
             )
@@ -234,8 +235,12 @@ class ModelConfig:
             if c.get("first_k_dense_replace"):
                 k0 = c["first_k_dense_replace"]
                 kw["moe_layer_freq"] = [0] * k0 + [1] * (c["num_hidden_layers"] - k0)
-            if c.get("scoring_func") == "sigmoid":
-                kw.update(moe_router_score_function="sigmoid", moe_router_enable_expert_bias=c.get("topk_method") == "noaux_tc"
+            # GLM-4.5 / 4.7 / 5, DeepSeek-V3 and MiniMax-M2 always score with a sigmoid and a correction bias; configs
+            # written by older tools say so (scoring_func / topk_method), newer ones leave it to the architecture
+            fixed = (a.startswith("glm") and "moe" in a) or a.startswith("deepseekv3") or "minimaxm2" in a
+            if c.get("scoring_func", "sigmoid" if fixed else None) == "sigmoid":
+                kw.update(moe_router_score_function="sigmoid", moe_router_pre_softmax=True,
+                          moe_router_enable_expert_bias=(fixed and "topk_method" not in c) or c.get("topk_method") == "noaux_tc"
                           or bool(c.get("use_routing_bias")))  # fmt: skip
             if c.get("routed_scaling_factor"):
                 kw["moe_router_topk_scaling_factor"] = c["routed_scaling_factor"]
@@ -245,6 +250,8 @@ class ModelConfig:
                 kw["moe_shared_expert_gate"] = True
         if c.get("partial_rotary_factor") and c["partial_rotary_factor"] < 1.0:
             kw["rotary_percent"] = c["partial_rotary_factor"]
+        elif c.get("rotary_dim") and c.get("head_dim") and c["rotary_dim"] < c["head_dim"]:
+            kw["rotary_percent"] = c["rotary_dim"] / c["head_dim"]
         if a.startswith("glm4") or a.startswith("glm"):
             kw["rotary_interleaved"] = not a.startswith("glm4moe") and "moe" not in a
             kw["post_self_attn_layernorm"] = kw["post_mlp_layernorm"] = a.startswith("glm4for")
@@ -260,8 +267,9 @@ class ModelConfig:
                       qk_layernorm=False)  # fmt: skip
             if c.get("index_topk"):
                 kw.update(index_topk=c["index_topk"], index_n_heads=c["index_n_heads"], index_head_dim=c["index_head_dim"])
-            kw["rotary_interleaved"] = True  # DeepSeek-style checkpoints rotate (2i, 2i + 1) pairs of the rotary part
-        rs = c.get("rope_scaling") or {}
+            # DeepSeek-style checkpoints rotate (2i, 2i + 1) pairs of the rotary part unless the config says otherwise
+            kw["rotary_interleaved"] = bool(c.get("rope_interleave", True))
+        rs = c.get("rope_scaling") or (rp if rp.get("rope_type", rp.get("type")) not in (None, "default") else {})
         if rs.get("type", rs.get("rope_type")) == "yarn":
             kw.update(rotary_scaling_type="yarn", rotary_scaling_factor=float(rs["factor"]),
                       rotary_original_max_position=int(rs.get("original_max_position_embeddings", 4096)),

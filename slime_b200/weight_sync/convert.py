@@ -139,12 +139,35 @@ def _vl_name(cfg: ModelConfig, hf_name: str) -> str:
     return hf_name
 
 
+_MINIMAX_MOE = (("mlp.gate.e_score_correction_bias", "block_sparse_moe.e_score_correction_bias"), ("mlp.gate.weight", "block_sparse_moe.gate.weight"),
+                ("gate_proj.weight", "w1.weight"), ("up_proj.weight", "w3.weight"), ("down_proj.weight", "w2.weight"),
+                ("mlp.experts.", "block_sparse_moe.experts."))  # fmt: skip
+
+
+def _family_name(cfg: ModelConfig, hf_name: str) -> str:
+    """Checkpoint spelling of a family whose files name the same tensors differently: MiniMax-M2 keeps its experts under
+    ``block_sparse_moe`` as w1 (gate) / w3 (up) / w2 (down)
+    (slime/backends/megatron_utils/megatron_to_hf/minimax_m2.py:31-84 in the reference)."""
+    if _family(cfg) == "minimax" and (".mlp.experts." in hf_name or ".mlp.gate." in hf_name):
+        for a, b in _MINIMAX_MOE:
+            hf_name = hf_name.replace(a, b)
+    return _vl_name(cfg, hf_name)
+
+
+def family_name_to_generic(hf_name: str) -> str:
+    """Inverse of the family spellings above (what an engine that only knows the generic names calls it)."""
+    if ".block_sparse_moe." in hf_name:
+        for a, b in reversed(_MINIMAX_MOE):
+            hf_name = hf_name.replace(b, a)
+    return hf_name
+
+
 def convert_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
     """One gathered trainer tensor -> HF (name, tensor) pairs. Names not handled raise."""
     name = name.removeprefix("module.").removeprefix("module.")
     if name.startswith("vision."):  # the image encoder keeps the checkpoint's own parameter names
         return [("model.visual." + name[len("vision.") :], t)]
-    return [(_vl_name(cfg, n), x) for n, x in _text_to_hf(cfg, name, t)]
+    return [(_family_name(cfg, n), x) for n, x in _text_to_hf(cfg, name, t)]
 
 
 def _text_to_hf(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]]:
@@ -307,7 +330,7 @@ def hf_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
     if name.startswith("vision."):
         return ["model.visual." + name[len("vision.") :]], "copy"
     names, rule = _text_sources_for(cfg, name)
-    return [_vl_name(cfg, n) for n in names], rule
+    return [_family_name(cfg, n) for n in names], rule
 
 
 def _text_sources_for(cfg: ModelConfig, name: str) -> tuple[list[str], str]:
