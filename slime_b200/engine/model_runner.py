@@ -470,8 +470,7 @@ class ModelRunner:
         self.rope_delta = torch.zeros(max_batch, dtype=torch.int32, device=self.device) if cfg.mrope_section else None
         self._mrope_axes = None
         rot = int(cfg.head_dim * cfg.rotary_percent) // 2 * 2
-        self.rope = ops.rope_cos_sin(max_context + 1, rot, cfg.rotary_base, device=self.device,
-                                     scaling_factor=cfg.rotary_scaling_factor)  # fmt: skip
+        self.rope = ops.rope_table(cfg, max_context + 1, rot, self.device)
         self.scale = 1.0 / math.sqrt(cfg.head_dim)
         if cfg.multi_latent_attention:
             from slime_b200.models import mixers

@@ -27,7 +27,9 @@ class ModelConfig:
     norm_epsilon: float = 1e-6
     rotary_base: float = 10000.0
     rotary_scaling_factor: float = 1.0
-    rotary_scaling_type: str = "linear"  # linear (positions divided by the factor) | yarn
+    rotary_scaling_type: str = "linear"  # linear (positions divided by the factor) | llama3 | yarn
+    rope_low_freq_factor: float = 1.0  # llama3: bands with a wavelength above original / low are slowed by the factor ...
+    rope_high_freq_factor: float = 4.0  # ... bands below original / high are kept, the rest blend
     rotary_original_max_position: int = 4096  # yarn: the context length the frequencies were trained at
     yarn_beta_fast: float = 32.0
     yarn_beta_slow: float = 1.0
@@ -277,6 +279,10 @@ class ModelConfig:
                       mscale=float(rs.get("mscale", 1.0)), mscale_all_dim=float(rs.get("mscale_all_dim", 0.0)))  # fmt: skip
         elif rs.get("type", rs.get("rope_type")) == "linear":
             kw["rotary_scaling_factor"] = float(rs["factor"])
+        elif rs.get("type", rs.get("rope_type")) == "llama3":
+            kw.update(rotary_scaling_type="llama3", rotary_scaling_factor=float(rs["factor"]),
+                      rotary_original_max_position=int(rs.get("original_max_position_embeddings", 8192)),
+                      rope_low_freq_factor=float(rs.get("low_freq_factor", 1.0)), rope_high_freq_factor=float(rs.get("high_freq_factor", 4.0)))  # fmt: skip
         if "minimax" in a:
             kw.update(qk_layernorm=False, qk_layernorm_full=bool(c.get("use_qk_norm", True)))
         section = rp.get("mrope_section") or rs.get("mrope_section")

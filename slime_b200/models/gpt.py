@@ -334,8 +334,7 @@ class GPTModel(nn.Module):
     def rope_table(self, device, need: int):
         if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
             n = max(need, 4096)
-            self._rope = ops.rope_cos_sin(n, self.cfg.head_dim, self.cfg.rotary_base, device=device,
-                                          scaling_factor=self.cfg.rotary_scaling_factor)  # fmt: skip
+            self._rope = ops.rope_table(self.cfg, n, self.cfg.head_dim, device)
         return self._rope
 
     def output_weight(self):

@@ -204,8 +204,7 @@ class GeneralSelfAttention(nn.Module):
 
     def _table(self, device, need: int):
         if self._rope is None or self._rope.shape[0] < need or self._rope.device != torch.device(device):
-            self._rope = ops.rope_cos_sin(max(need, 4096), self.rot, self.cfg.rotary_base, device=device,
-                                          scaling_factor=self.cfg.rotary_scaling_factor)  # fmt: skip
+            self._rope = ops.rope_table(self.cfg, max(need, 4096), self.rot, device)
         return self._rope
 
     def _full_norm(self, t, w, eps):

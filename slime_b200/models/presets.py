@@ -42,9 +42,11 @@ MORE_PRESETS: dict[str, dict] = {
     "qwen3-4b-instruct-2507": _dense(36, 2560, 9728, 32, 8, 151936, kv=128, rope=5e6, tied=True, qk=True,
                                      arch="Qwen3ForCausalLM"),
     "llama3.1-8b-instruct": _dense(32, 4096, 14336, 32, 8, 128256, kv=128, rope=5e5, eps=1e-5, arch="LlamaForCausalLM",
-                                   rotary_scaling_factor=8.0, max_position_embeddings=131072),
+                                   rotary_scaling_factor=8.0, rotary_scaling_type="llama3", rotary_original_max_position=8192,
+                                   max_position_embeddings=131072),
     "llama3.2-3b-instruct": _dense(28, 3072, 8192, 24, 8, 128256, kv=128, rope=5e5, eps=1e-5, tied=True,
-                                   arch="LlamaForCausalLM", rotary_scaling_factor=32.0, max_position_embeddings=131072),
+                                   arch="LlamaForCausalLM", rotary_scaling_factor=32.0, rotary_scaling_type="llama3",
+                                   rotary_original_max_position=8192, max_position_embeddings=131072),
     "mimo-7b-rl": _dense(36, 4096, 11008, 32, 8, 151680, rope=6.4e5, eps=1e-5, bias=True, mtp_num_layers=1,
                          arch="MiMoForCausalLM"),
     "qwen3-235b-a22b": _moe(0, 94, **_dense(94, 4096, 12288, 64, 4, 151936, kv=128, qk=True, arch="Qwen3MoeForCausalLM",
@@ -158,7 +160,7 @@ def to_flags(cfg) -> list[str]:
             continue
         if f.name in ("rotary_scaling_factor", "mtp_num_layers", "norm_topk_prob", "rotary_percent", "linear_conv_kernel_dim",
                       "index_topk_freq", "index_skip_topk_offset", "rotary_scaling_type", "rotary_original_max_position",
-                      "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim") and v == base[f.name]:  # fmt: skip
+                      "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim", "rope_low_freq_factor", "rope_high_freq_factor") and v == base[f.name]:  # fmt: skip
             continue
         if f.name in VISION_FIELDS:
             continue  # no flags: the trainer reads the image encoder's description from --hf-checkpoint

@@ -266,6 +266,19 @@ def rope_cos_sin(max_pos, dim, base, device=None, scaling_factor=1.0):
     return reference.rope_cos_sin(max_pos, dim, base, device=device, scaling_factor=scaling_factor)
 
 
+def rope_table(cfg, max_pos: int, dim: int, device=None):
+    """``[max_pos, dim]`` = ``[cos | sin]`` for a model's ordinary (not latent-attention) rotary layers, with the
+    frequency scaling its config names: none / linear (positions divided by the factor), ``llama3`` or ``yarn``."""
+    kind = cfg.rotary_scaling_type if cfg.rotary_scaling_factor and cfg.rotary_scaling_factor != 1.0 else None
+    if kind == "llama3":
+        return reference.rope_cos_sin_llama3(max_pos, dim, cfg.rotary_base, cfg.rotary_scaling_factor, cfg.rotary_original_max_position,
+                                             cfg.rope_low_freq_factor, cfg.rope_high_freq_factor, device=device)  # fmt: skip
+    if kind == "yarn":
+        return reference.rope_cos_sin_yarn(max_pos, dim, cfg.rotary_base, cfg.rotary_scaling_factor, cfg.rotary_original_max_position,
+                                           cfg.yarn_beta_fast, cfg.yarn_beta_slow, cfg.mscale, cfg.mscale_all_dim, device=device)  # fmt: skip
+    return reference.rope_cos_sin(max_pos, dim, cfg.rotary_base, device=device, scaling_factor=cfg.rotary_scaling_factor or 1.0)
+
+
 def _rope_launch(x, out, positions, cos_sin, nw, rstd, nheads, head0, D, eps, sign):
     T = x.shape[0]
     rc = _lib.lib().sb_rope(P(x), P(out), P(positions), P(cos_sin), P(nw), P(rstd), T, nheads, head0, x.stride(0),

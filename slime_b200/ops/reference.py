@@ -37,6 +37,22 @@ def rope_cos_sin(max_pos: int, dim: int, base: float, device=None, scaling_facto
     return torch.cat([ang.cos(), ang.sin()], dim=-1).float()
 
 
+def rope_cos_sin_llama3(max_pos: int, dim: int, base: float, factor: float, original_max_position: int, low_freq_factor: float = 1.0,
+                        high_freq_factor: float = 4.0, device=None) -> torch.Tensor:
+    """Table with Llama-3.1 style frequencies: bands whose wavelength exceeds ``original / low_freq_factor`` are slowed
+    by ``factor``, bands shorter than ``original / high_freq_factor`` are kept, the ones in between blend linearly in
+    ``original / wavelength`` (what ``--use-rope-scaling --rope-scaling-factor`` selects in the reference's trainer)."""
+    import math
+
+    inv = 1.0 / (base ** (torch.arange(0, dim, 2, dtype=torch.float64) / dim))
+    wavelen = 2 * math.pi / inv
+    smooth = ((original_max_position / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)).clamp(0, 1)
+    inv = (1 - smooth) * inv / factor + smooth * inv  # smooth = 0 for long waves, 1 for short ones
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    out = torch.cat([ang.cos(), ang.sin()], dim=-1).float()
+    return out.to(device) if device is not None else out
+
+
 def yarn_inv_freq(dim: int, base: float, factor: float, original_max_position: int, beta_fast: float = 32.0,
                   beta_slow: float = 1.0) -> torch.Tensor:
     """YaRN frequencies: dimensions that turn more than ``beta_fast`` times over the original context keep their

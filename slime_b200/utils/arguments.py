@@ -231,7 +231,8 @@ _MODEL = [
     _f("--qk-pos-emb-head-dim", type=int, default=None), _f("--v-head-dim", type=int, default=None),
     _f("--mscale", type=float, default=1.0), _f("--mscale-all-dim", type=float, default=0.0),
     _f("--qk-layernorm-full", action=_T), _f("--softmax-sinks", action=_T),
-    _f("--rotary-scaling-type", type=str, default="linear", choices=["linear", "yarn"]),
+    _f("--rotary-scaling-type", type=str, default="linear", choices=["linear", "llama3", "yarn"]),
+    _f("--rope-low-freq-factor", type=float, default=1.0), _f("--rope-high-freq-factor", type=float, default=4.0),
     _f("--rotary-original-max-position", type=int, default=4096), _f("--yarn-beta-fast", type=float, default=32.0),
     _f("--yarn-beta-slow", type=float, default=1.0),
     _f("--full-attention-interval", type=int, default=None), _f("--linear-num-key-heads", type=int, default=None),
@@ -459,6 +460,11 @@ def backend_validate_args(args) -> None:
             args.moe_layer_freq = eval(args.moe_layer_freq, {"__builtins__": {}})  # "[0]*3+[1]*45" style
     if args.moe_layer_freq is None and hasattr(args, "moe_layer_freq"):
         delattr(args, "moe_layer_freq")
+    if getattr(args, "use_rope_scaling", False) and args.rotary_scaling_type == "linear" and not getattr(args, "multi_latent_attention", False):
+        # the Llama-3.1 frequency scaling (as in the reference's trainer), trained at 8192 positions unless said otherwise
+        args.rotary_scaling_type = "llama3"
+        if getattr(args, "rotary_original_max_position", None) in (None, 4096):
+            args.rotary_original_max_position = 8192
     if args.vocab_size is not None and args.padded_vocab_size is None:
         mult = args.make_vocab_size_divisible_by * args.tensor_model_parallel_size
         args.padded_vocab_size = -(-args.vocab_size // mult) * mult

@@ -16,6 +16,9 @@ BASE = dict(num_layers=2, hidden_size=64, num_attention_heads=4, num_query_group
 FAMILIES = {
     "qwen2": dict(add_qkv_bias=True, model_arch="Qwen2ForCausalLM"),
     "qwen3": dict(qk_layernorm=True, model_arch="Qwen3ForCausalLM"),
+    "llama31": dict(model_arch="LlamaForCausalLM", rotary_scaling_type="llama3", rotary_scaling_factor=8.0, rotary_original_max_position=16),
+    "qwen3_yarn": dict(qk_layernorm=True, model_arch="Qwen3ForCausalLM", rotary_scaling_type="yarn", rotary_scaling_factor=4.0,
+                       rotary_original_max_position=16),
     "qwen3_moe": dict(qk_layernorm=True, num_experts=4, moe_ffn_hidden_size=32, moe_router_topk=2, model_arch="Qwen3MoeForCausalLM"),
     "glm4": dict(add_qkv_bias=True, post_self_attn_layernorm=True, post_mlp_layernorm=True, rotary_percent=0.5,
                  rotary_interleaved=True, model_arch="Glm4ForCausalLM"),

@@ -22,6 +22,9 @@ CASES = {
     "qwen2": ("qwen2", "Qwen2Config", "Qwen2ForCausalLM", dict(BASE)),
     "qwen3": ("qwen3", "Qwen3Config", "Qwen3ForCausalLM", dict(BASE, head_dim=16)),
     "llama": ("llama", "LlamaConfig", "LlamaForCausalLM", dict(BASE)),
+    "llama31": ("llama", "LlamaConfig", "LlamaForCausalLM",
+                dict(BASE, max_position_embeddings=512, rope_parameters=dict(rope_type="llama3", rope_theta=10000.0, factor=8.0, low_freq_factor=1.0,
+                                                                             high_freq_factor=4.0, original_max_position_embeddings=64))),
     "qwen3_moe": ("qwen3_moe", "Qwen3MoeConfig", "Qwen3MoeForCausalLM",
                   dict(BASE, head_dim=16, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
                        decoder_sparse_step=1, mlp_only_layers=[])),
