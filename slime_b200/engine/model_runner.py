@@ -657,9 +657,10 @@ class ModelRunner:
             hi, di = cfg.index_n_heads, cfg.index_head_dim
             if "idx_wk" in L:
                 q_latent = mixers._rms(ops.gemm(x, L["q_a"]), L["q_a_ln"], cfg.norm_epsilon)
-                qi = mixers.apply_rotary(ops.gemm(q_latent, L["idx_wq_b"]).view(T, hi, di), cos, sin, cfg.rotary_interleaved)
+                il = cfg.rotary_interleaved if cfg.index_rotary_interleaved is None else cfg.index_rotary_interleaved
+                qi = mixers.apply_rotary(ops.gemm(q_latent, L["idx_wq_b"]).view(T, hi, di), cos, sin, il)
                 ki = torch.nn.functional.layer_norm(ops.gemm(x, L["idx_wk"]).float(), (di,), L["idx_k_norm_w"].float(), L["idx_k_norm_b"].float())
-                ki = mixers.apply_rotary(ki.view(T, 1, di), cos, sin, cfg.rotary_interleaved).view(T, di)
+                ki = mixers.apply_rotary(ki.view(T, 1, di), cos, sin, il).view(T, di)
                 wi = ops.gemm(x, L["idx_weights"]).float() * (hi**-0.5) * (di**-0.5)
                 index_q = (qi.float(), wi)
                 parts.append(ki.to(x.dtype))

@@ -62,6 +62,9 @@ class ModelConfig:
     attention_output_gate: bool = False  # Qwen3-Next: q projection carries a sigmoid gate for the attention output
     qk_layernorm_full: bool = False  # MiniMax-M2: RMSNorm over all heads of q (and of k) at once instead of per head
     softmax_sinks: bool = False  # learnable per-head sink logit in the softmax denominator
+    # rotary convention of the sparse-attention indexer: None = the attention's own (``rotary_interleaved``), as the
+    # reference's trainer does; DeepSeek-V3.2's released inference code rotates the indexer half-split (False)
+    index_rotary_interleaved: bool | None = None
     # vision inputs (models/vision.py): the encoder's own config, the placeholder token ids, and multi-axis rotary positions
     vision: dict | None = None
     image_token_id: int | None = None
@@ -269,6 +272,8 @@ class ModelConfig:
                       qk_layernorm=False)  # fmt: skip
             if c.get("index_topk"):
                 kw.update(index_topk=c["index_topk"], index_n_heads=c["index_n_heads"], index_head_dim=c["index_head_dim"])
+                if c.get("index_rope_interleave") is not None:
+                    kw["index_rotary_interleaved"] = bool(c["index_rope_interleave"])
             # DeepSeek-style checkpoints rotate (2i, 2i + 1) pairs of the rotary part unless the config says otherwise
             kw["rotary_interleaved"] = bool(c.get("rope_interleave", True))
         rs = c.get("rope_scaling") or (rp if rp.get("rope_type", rp.get("type")) not in (None, "default") else {})

@@ -617,9 +617,10 @@ class DSASelfAttention(MLASelfAttention):
         cfg, T = self.cfg, inp.shape[0]
         cos, sin = rope
         with torch.no_grad():  # the choice is discrete: no gradient reaches the indexer through it
-            q_idx = apply_rotary(F.linear(q_latent, self.wq_b.weight).view(T, self.hi, self.di), cos, sin, cfg.rotary_interleaved)
+            il = cfg.rotary_interleaved if cfg.index_rotary_interleaved is None else cfg.index_rotary_interleaved
+            q_idx = apply_rotary(F.linear(q_latent, self.wq_b.weight).view(T, self.hi, self.di), cos, sin, il)
             k_idx = F.layer_norm(F.linear(inp, self.wk.weight).float(), (self.di,), self.k_norm.weight.float(), self.k_norm.bias.float())
-            k_idx = apply_rotary(k_idx.view(T, 1, self.di), cos, sin, cfg.rotary_interleaved).view(T, self.di)
+            k_idx = apply_rotary(k_idx.view(T, 1, self.di), cos, sin, il).view(T, self.di)
             w = F.linear(inp, self.weights_proj.weight).float() * (self.hi**-0.5) * (self.di**-0.5)
             if allgather_cp_active():  # the indexer's keys of every rank (no gradient flows through the choice)
                 k_idx = gather_from_context_parallel(k_idx)

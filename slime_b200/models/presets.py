@@ -160,7 +160,7 @@ def to_flags(cfg) -> list[str]:
             continue
         if f.name in ("rotary_scaling_factor", "mtp_num_layers", "norm_topk_prob", "rotary_percent", "linear_conv_kernel_dim",
                       "index_topk_freq", "index_skip_topk_offset", "rotary_scaling_type", "rotary_original_max_position",
-                      "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim", "rope_low_freq_factor", "rope_high_freq_factor") and v == base[f.name]:  # fmt: skip
+                      "yarn_beta_fast", "yarn_beta_slow", "mscale", "mscale_all_dim", "rope_low_freq_factor", "rope_high_freq_factor", "index_rotary_interleaved") and v == base[f.name]:  # fmt: skip
             continue
         if f.name in VISION_FIELDS:
             continue  # no flags: the trainer reads the image encoder's description from --hf-checkpoint

@@ -240,6 +240,7 @@ _MODEL = [
     _f("--linear-value-head-dim", type=int, default=None), _f("--linear-conv-kernel-dim", type=int, default=4),
     _f("--index-topk", type=int, default=None), _f("--index-n-heads", type=int, default=None),
     _f("--index-head-dim", type=int, default=None), _f("--index-topk-freq", type=int, default=1),
+    _f("--index-rotary-interleaved", type=lambda v: str(v).lower() in ("1", "true", "yes"), default=None),
     _f("--index-skip-topk-offset", type=int, default=0),
     _f("--spec", type=str, nargs="*", default=None), _f("--enable-experimental", action=_T),
     _f("--no-masked-softmax-fusion", action=_T), _f("--no-gradient-accumulation-fusion", action=_T),
