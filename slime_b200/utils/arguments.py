@@ -469,9 +469,9 @@ def backend_validate_args(args) -> None:
     if args.vocab_size is not None and args.padded_vocab_size is None:
         mult = args.make_vocab_size_divisible_by * args.tensor_model_parallel_size
         args.padded_vocab_size = -(-args.vocab_size // mult) * mult
-    if args.allgather_cp and not (getattr(args, "index_topk", None)
+    if args.allgather_cp and getattr(args, "context_parallel_size", 1) > 1 and not (getattr(args, "index_topk", None)
                                   or str(getattr(args, "model_arch", "")).lower().startswith(("deepseekv32", "glmmoedsa"))):
-        raise ValueError("--allgather-cp is only supported for DSA (DeepSeek-V3.2 / GLM-5) models")
+        raise ValueError("--allgather-cp is only supported for DSA attention models (DeepSeek-V3.2 / GLM-5)")
     if args.allgather_cp and getattr(args, "context_parallel_size", 1) > 1 and (
             getattr(args, "use_rollout_routing_replay", False) or getattr(args, "enable_mtp_training", False)):
         raise ValueError("--allgather-cp: rollout routing replay and draft-head training still assume the zig-zag token layout")

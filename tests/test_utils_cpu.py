@@ -288,3 +288,38 @@ def test_dp_schedule_fixed_cases():
     check(p, m, n, 1, range(6), [3] * 8, cap=12)
     with pytest.raises(AssertionError, match="num_rollouts"):
         build_dp_schedule(dyn, P(1), [3] * 6, global_batch_size=4, rollout_indices=[0, 0, 1, 1, 2, 2])
+
+
+# ------------------------------------------------------------------------------------------------ argument validation
+_ARGV = ["--rollout-batch-size", "4", "--num-rollout", "2", "--hf-checkpoint", "preset:qwen2.5-0.5b", "--rollout-num-gpus", "4"]
+
+
+@pytest.mark.parametrize("extra,message", [
+    (["--update-weight-transport", "disk"], "update-weight-disk-dir"),
+    (["--save-debug-rollout-data", "/tmp/d_{rollout_id}.pt", "--save-debug-train-data", "/tmp/d_{rollout_id}.pt"], "--save-debug-train-data must not be equal"),
+    (["--rollout-temperature", "0.0"], "--rollout-temperature must be > 0"),
+    (["--rollout-temperature", "-0.1"], "--rollout-temperature must be > 0"),
+    (["--update-weight-mode", "delta", "--update-weight-transport", "nccl", "--update-weight-local-checkpoint-dir", "/l"], "requires --update-weight-transport=disk"),
+    (["--update-weight-mode", "delta", "--update-weight-transport", "disk", "--update-weight-disk-dir", "/s", "--update-weight-local-checkpoint-dir", "/l",
+      "--colocate"], "not supported with --colocate"),
+    (["--update-weight-mode", "delta", "--update-weight-transport", "disk", "--update-weight-disk-dir", "/s"], "requires --update-weight-local-checkpoint-dir"),
+    (["--allgather-cp", "--context-parallel-size", "2"], "only supported for DSA attention models"),
+])  # fmt: skip
+def test_argument_combinations_that_are_refused(extra, message):
+    from slime_b200.utils.arguments import parse_args
+
+    with pytest.raises(ValueError, match=message):
+        parse_args(_ARGV + extra)
+
+
+def test_argument_defaults_that_are_kept_or_filled():
+    from slime_b200.utils.arguments import parse_args
+
+    assert parse_args(_ARGV + ["--start-rollout-id", "100"]).start_rollout_id == 100 and parse_args(_ARGV).start_rollout_id == 0
+    a = parse_args(_ARGV[:-2] + ["--colocate", "--rollout-num-gpus", "0"])
+    assert a.rollout_num_gpus == 0 and a.offload_train is True and a.offload_rollout is True
+    a = parse_args(_ARGV[:-2] + ["--colocate", "--actor-num-gpus-per-node", "8", "--actor-num-nodes", "1", "--rollout-num-gpus", "12"])
+    assert a.rollout_num_gpus == 12 and a.offload_train and a.offload_rollout
+    a = parse_args(_ARGV[:-2] + ["--rollout-num-gpus", "0"])
+    assert (a.rollout_num_gpus, a.actor_num_gpus_per_node, a.actor_num_nodes, a.offload_train, a.offload_rollout) == (0, 8, 1, False, False)
+    assert parse_args(_ARGV + ["--allgather-cp"]).allgather_cp  # without context parallelism the flag has nothing to refuse
