@@ -400,3 +400,82 @@ def test_multi_turn_vision_rollout_collects_images_and_masks_environment_tokens(
     assert [p["type"] for p in msg["content"]] == ["image", "text"]
     ids, image_data, images, train = ex.encode_observation(tok, FakeProcessor(), msg, None, True, None)
     assert tok.decode(ids).startswith("<|user|> <image> <image> <image> <image> look") and len(image_data) == 1 and train["pixel_values"].shape[0] == 16
+
+
+def test_token_delta_survives_templates_that_rewrite_history():
+    import re
+
+    from examples.tau_bench.token_delta import get_context_delta, get_token_delta
+
+    class Tok:
+        """Byte-level tokenizer whose template hides the reasoning of assistant turns that precede the last user turn."""
+
+        def apply_chat_template(self, messages, *, add_generation_prompt, tokenize):
+            assert tokenize is False
+            last_user = max((i for i, m in enumerate(messages) if m["role"] == "user"), default=-1)
+            out = []
+            for i, m in enumerate(messages):
+                c = re.sub(r"<think>.*?</think>", "", m["content"], flags=re.DOTALL) if m["role"] == "assistant" and i < last_user else m["content"]
+                out.append(f"<{m['role']}>{c}</{m['role']}>")
+            return "".join(out) + ("<assistant>" if add_generation_prompt else "")
+
+        def encode(self, text, *, add_special_tokens):
+            return list(text.encode())
+
+        def decode(self, ids):
+            return bytes(ids).decode()
+
+    class Merging(Tok):
+        """'>' followed by a newline is one token: the end of the generation prompt merges with the answer's first byte."""
+
+        def encode(self, text, *, add_special_tokens):
+            raw, out, i = text.encode(), [], 0
+            while i < len(raw):
+                if raw[i : i + 2] == b">\n":
+                    out.append(1000)
+                    i += 2
+                else:
+                    out.append(raw[i])
+                    i += 1
+            return out
+
+    tok = Tok()
+    first = [{"role": "user", "content": "first user"}, {"role": "assistant", "content": "<think>first reasoning</think>first answer"}]
+    ids, mask = get_token_delta(tok, first + [{"role": "user", "content": "second user must remain complete"}])
+    assert tok.decode(ids) == "<user>second user must remain complete</user>" and mask == [0] * len(ids)
+    ids, mask = get_token_delta(tok, [{"role": "user", "content": "q"}, {"role": "assistant", "content": "<think>r</think>a"}])
+    assert tok.decode(ids) == "<think>r</think>a</assistant>" and mask == [1] * len(ids)
+    assert tok.decode(get_context_delta(tok, first + [{"role": "user", "content": "again"}])) == "<user>again</user><assistant>"
+    # six turns accumulated message by message: every user span is context, every answer is trained on, every
+    # generation prompt is context
+    messages = [{"role": "user", "content": "user 1"}]
+    ids = tok.encode(tok.apply_chat_template(messages, add_generation_prompt=True, tokenize=False), add_special_tokens=False)
+    mask = [0] * len(ids)
+    for turn in range(1, 7):
+        messages.append({"role": "assistant", "content": f"<think>reasoning {turn}</think>answer {turn}"})
+        d, m = get_token_delta(tok, messages, include_generation_prompt=turn > 1)
+        ids, mask = ids + d, mask + m
+        if turn < 6:
+            messages.append({"role": "user", "content": f"user {turn + 1}"})
+            d, m = get_token_delta(tok, messages)
+            ids, mask = ids + d, mask + m
+    text = tok.decode(ids)
+    assert text.count("<assistant>") == 6 == text.count("</assistant>")
+    for turn in range(1, 7):
+        span = f"<user>user {turn}</user>"
+        at = text.index(span)
+        assert mask[at : at + len(span)] == [0] * len(span)
+        span = f"<think>reasoning {turn}</think>answer {turn}</assistant>"
+        at = text.index(span)
+        assert mask[at : at + len(span)] == [1] * len(span)
+        prompt_at = text.rfind("<assistant>", 0, at)
+        assert mask[prompt_at:at] == [0] * (at - prompt_at)
+    # a token that spans the end of the generation prompt and the start of the answer is kept whole and masked with the prompt
+    mt = Merging()
+    ids, mask = get_token_delta(mt, first + [{"role": "user", "content": "second user"}, {"role": "assistant", "content": "\nsecond answer"}],
+                                include_generation_prompt=True)  # fmt: skip
+    want = mt.encode("<assistant>\nsecond answer</assistant>", add_special_tokens=False)
+    n = len(mt.encode("<assistant>", add_special_tokens=False))
+    assert ids == want and 1000 in ids and mask == [0] * n + [1] * (len(want) - n)
+    with pytest.raises(ValueError, match="empty conversation"):
+        get_token_delta(tok, [])
