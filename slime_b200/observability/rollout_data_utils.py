@@ -18,6 +18,29 @@ from slime_b200.utils.types import Sample
 logger = logging.getLogger(__name__)
 
 
+def validate_rollout_routed_experts_for_replay(routed_experts, args) -> None:
+    """Refuse expert-route records that rollout routing replay cannot use: a wrong shape, no rows, or a mixture-of-experts
+    layer whose routes are zero for every token (an engine stage that did not report its layers: replaying that would send
+    every token to expert 0). Dense layers are zero by construction. Parity:
+    slime/observability/rollout_data_utils.py:55-89 in the reference."""
+    if not routed_experts:
+        raise ValueError("R3 is enabled but no rollout routed-experts tensors were returned.")
+    layers, topk = int(args.num_layers), int(args.moe_router_topk)
+    freq = getattr(args, "moe_layer_freq", None)
+    moe_layers = [i for i, f in enumerate(freq[:layers]) if int(f) != 0] if isinstance(freq, (list, tuple)) else list(range(layers))
+    for n, routes in enumerate(routed_experts):
+        routes = torch.as_tensor(routes)
+        if routes.ndim != 3 or tuple(routes.shape[1:]) != (layers, topk):
+            raise ValueError(f"Invalid rollout routed-experts shape for R3: sample={n}, got={tuple(routes.shape)}, expected=(*, {layers}, {topk}).")
+        if routes.shape[0] == 0:
+            raise ValueError(f"R3 sample {n} has no routed-experts rows.")
+        if topk > 1:  # with one route per token "all zero" can be a real answer
+            missing = [i for i in moe_layers if not torch.count_nonzero(routes[:, i, :])]
+            if missing:
+                raise ValueError(f"R3 routed-experts capture is all zero for MoE layers {missing} in sample {n}: the rollout "
+                                 "engine's stages did not report these layers; refusing to replay expert 0 everywhere.")  # fmt: skip
+
+
 def validate_rollout_id_annotated(node, depth: int = 0) -> None:
     """A rollout function may return one rollout as several training samples (``list[list[list[Sample]]]``).
     Such sibling lists (depth >= 2, more than one element) must carry one shared non-None ``rollout_id`` so the

@@ -115,6 +115,10 @@ def convert_samples_to_train_data(args, samples: list[Sample]) -> dict:
         data["rollout_top_p_token_offsets"] = [s.rollout_top_p_token_offsets for s in samples]
     if first.rollout_routed_experts is not None:
         data["rollout_routed_experts"] = [torch.as_tensor(s.rollout_routed_experts) for s in samples]
+        if getattr(args, "use_rollout_routing_replay", False):
+            from slime_b200.observability.rollout_data_utils import validate_rollout_routed_experts_for_replay
+
+            validate_rollout_routed_experts_for_replay(data["rollout_routed_experts"], args)
     if first.train_metadata is not None:
         data["metadata"] = [s.train_metadata for s in samples]
     if any(s.multimodal_train_inputs is not None for s in samples):
@@ -137,6 +141,12 @@ def tensorize_rollout_data_for_training(rollout_data: dict, pin: bool = False) -
             t = v.to(dtype) if torch.is_tensor(v) else torch.tensor(v, dtype=dtype)
             out.append(t.pin_memory() if pin and not t.is_pinned() and t.numel() else t)
         rollout_data[key] = out
+    if rollout_data.get("multimodal_train_inputs"):  # processor outputs travel as plain CPU tensors (no autograd history)
+        rollout_data["multimodal_train_inputs"] = [
+            d if d is None else {k: (v.detach().cpu() if torch.is_tensor(v) else v) for k, v in d.items()}
+            for d in rollout_data["multimodal_train_inputs"]]  # fmt: skip
+    if "rollout_mask_sums" in rollout_data and not torch.is_tensor(rollout_data["rollout_mask_sums"]):
+        rollout_data["rollout_mask_sums"] = torch.as_tensor([float(x) for x in rollout_data["rollout_mask_sums"]], dtype=torch.float32)
     return rollout_data
 
 

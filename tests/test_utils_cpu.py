@@ -323,3 +323,39 @@ def test_argument_defaults_that_are_kept_or_filled():
     a = parse_args(_ARGV[:-2] + ["--rollout-num-gpus", "0"])
     assert (a.rollout_num_gpus, a.actor_num_gpus_per_node, a.actor_num_nodes, a.offload_train, a.offload_rollout) == (0, 8, 1, False, False)
     assert parse_args(_ARGV + ["--allgather-cp"]).allgather_cp  # without context parallelism the flag has nothing to refuse
+
+
+def test_route_records_are_validated_and_rollout_payloads_normalised(tmp_path):
+    import numpy as np
+
+    from slime_b200.observability.rollout_data_utils import (
+        load_debug_rollout_data, save_debug_rollout_data, validate_rollout_routed_experts_for_replay)
+    from slime_b200.rollout.train_data import tensorize_rollout_data_for_training
+
+    args = Namespace(num_layers=6, moe_router_topk=2, moe_layer_freq=[0, 0, 0, 1, 1, 1])
+    routes = torch.zeros((4, 6, 2), dtype=torch.uint8)
+    routes[:, 3:, 1] = 7
+    validate_rollout_routed_experts_for_replay([routes], args)  # dense layers are zero by construction
+    routes = torch.zeros((4, 6, 2), dtype=torch.uint8)
+    routes[:, 3, 1] = 7
+    with pytest.raises(ValueError, match=r"all zero.*\[4, 5\]"):  # an engine stage that did not report its layers
+        validate_rollout_routed_experts_for_replay([routes], args)
+    with pytest.raises(ValueError, match="Invalid rollout routed-experts shape"):
+        validate_rollout_routed_experts_for_replay([torch.zeros((4, 5, 2), dtype=torch.uint8)], args)
+    with pytest.raises(ValueError, match="no rollout routed-experts"):
+        validate_rollout_routed_experts_for_replay([], args)
+    frozen = np.array([1, 2, 3])
+    frozen.flags.writeable = False
+    data = {"tokens": [frozen], "loss_masks": [[1, 0]], "rollout_mask_sums": [2],
+            "multimodal_train_inputs": [{"pixel_values": torch.tensor([1.0], requires_grad=True), "metadata": "unchanged"}]}  # fmt: skip
+    tensorize_rollout_data_for_training(data)
+    assert data["tokens"][0].dtype == torch.long and data["loss_masks"][0].dtype == torch.int and data["rollout_mask_sums"].dtype == torch.float32
+    mm = data["multimodal_train_inputs"][0]
+    assert mm["metadata"] == "unchanged" and not mm["pixel_values"].requires_grad
+    template = str(tmp_path / "rollout_{rollout_id}.pt")
+    save_debug_rollout_data(template, [Sample(index=1, rollout_id=3, prompt="question", response="answer", response_length=1)], rollout_id=3, evaluation=False)
+    back = load_debug_rollout_data(template, rollout_id=3)
+    assert (len(back), back[0].index, back[0].rollout_id, back[0].prompt, back[0].response) == (1, 1, 3, "question", "answer")
+    save_debug_rollout_data(template, {"math": {"samples": [Sample(index=1)]}, "code": {"samples": [Sample(index=2)]}}, rollout_id=4, evaluation=True)
+    saved = torch.load(tmp_path / "rollout_eval_4.pt", weights_only=False)
+    assert saved["rollout_id"] == 4 and [s["index"] for s in saved["samples"]] == [1, 2]
