@@ -51,6 +51,9 @@ _current_rollout_id = -1
 def set_current_rollout_id(rollout_id: int):
     global _current_rollout_id
     _current_rollout_id = rollout_id
+    from slime_b200.rollout import sample_hooks
+
+    sample_hooks.set_current_rollout_id(rollout_id)  # what sample hooks receive as ``rollout_id``
 
 
 def get_current_rollout_id() -> int:
@@ -258,6 +261,14 @@ def start_rollout_servers(args, pg) -> tuple[dict[str, RolloutServer], list]:
         for gc in m.server_groups:
             n_engines = 0 if gc.worker_type == "placeholder" else gc.num_gpus // gc.num_gpus_per_engine
             nodes_per = max(1, gc.num_gpus_per_engine // args.num_gpus_per_node)
+            if pg is not None and hasattr(pg, "count"):
+                from slime_b200.runtime.rollout_validation import validate_server_group_gpu_indices
+
+                validate_server_group_gpu_indices(
+                    worker_type=gc.worker_type, gpu_offset=gpu_offset, num_gpus_per_engine=gc.num_gpus_per_engine,
+                    num_gpus_per_engine_on_node=min(gc.num_gpus_per_engine, args.num_gpus_per_node), num_engines=n_engines,
+                    num_available_gpus=pg.count, rollout_num_gpus=getattr(args, "rollout_num_gpus", None),
+                    rollout_num_gpus_per_engine=getattr(args, "rollout_num_gpus_per_engine", None))  # fmt: skip
             g = ServerGroup(args=args, pg=pg, all_engines=[None] * (n_engines * nodes_per),
                             num_gpus_per_engine=gc.num_gpus_per_engine, worker_type=gc.worker_type,
                             rank_offset=rank_offset, gpu_offset=gpu_offset, overrides=dict(gc.overrides),

@@ -44,7 +44,7 @@ def test_generate_rm_filter_and_hook_shapes():
     assert isinstance(out, DynamicFilterOutput) and out.keep is False
     assert flt(None, [Sample(reward=1.0), Sample(reward=0.0)]).keep is True
     hooks = load_function("slime.rollout.sample_hooks.apply_rollout_sample_hooks")
-    assert inspect.iscoroutinefunction(hooks) and params(hooks)[0] == "args" and "rollout_id" in params(hooks)
+    assert inspect.iscoroutinefunction(hooks) and params(hooks)[:2] == ["args", "samples"]  # the rest is free-form context
 
 
 def test_data_source_and_buffer_filter_contract():
@@ -82,3 +82,54 @@ def test_moved_modules_are_the_same_objects():
     assert a.Sample is b.Sample and R1 is R2
     with pytest.raises(ImportError):
         load_function("slime.does_not_exist.fn")
+
+
+def test_sample_hooks_receive_the_context_they_name(monkeypatch):
+    import asyncio
+    import sys
+    import types
+
+    from slime_b200.rollout.sample_hooks import apply_rollout_sample_hooks, set_current_rollout_id
+    from slime_b200.utils.types import Sample
+
+    def sync_hook(args, sample, *, rollout_id=None):
+        sample.metadata["sync_hook"] = (args.marker, rollout_id)
+
+    async def async_hook(args, sample, *, evaluation=False):
+        sample.metadata["async_hook"] = evaluation
+        return sample
+
+    def bare_hook(args, sample):
+        sample.metadata["bare"] = True
+
+    def invalid_hook(args, sample):
+        return {"sample": sample}
+
+    mod = types.ModuleType("_sample_hook_cases")
+    for f in (sync_hook, async_hook, bare_hook, invalid_hook):
+        setattr(mod, f.__name__, f)
+    monkeypatch.setitem(sys.modules, "_sample_hook_cases", mod)
+    args = types.SimpleNamespace(marker="seen", rollout_sample_hook_path=[f"_sample_hook_cases.{n}" for n in ("sync_hook", "async_hook", "bare_hook")])
+    samples = [[Sample(index=0, metadata={})], [Sample(index=1, metadata={})]]
+    set_current_rollout_id(7)
+    out = asyncio.run(apply_rollout_sample_hooks(args, samples, evaluation=True, ignored="value"))
+    assert out is not samples and [[s.index for s in g] for g in out] == [[0], [1]]
+    assert all(g[0].metadata == {"sync_hook": ("seen", 7), "async_hook": True, "bare": True} for g in out)
+    with pytest.raises(TypeError, match="expected Sample or None"):
+        asyncio.run(apply_rollout_sample_hooks(types.SimpleNamespace(rollout_sample_hook_path=["_sample_hook_cases.invalid_hook"]), Sample(index=0)))
+    one = Sample(index=0)
+    assert asyncio.run(apply_rollout_sample_hooks(types.SimpleNamespace(rollout_sample_hook_path=[]), one)) is one
+    set_current_rollout_id(None)
+
+
+def test_server_group_gpu_ranges_are_checked_with_context():
+    from slime_b200.runtime.rollout_validation import validate_server_group_gpu_indices as check
+
+    common = dict(num_gpus_per_engine_on_node=1, num_available_gpus=4, rollout_num_gpus=4)
+    check(worker_type="regular", gpu_offset=2, num_gpus_per_engine=1, num_engines=2, rollout_num_gpus_per_engine=1, **common)
+    check(worker_type="placeholder", gpu_offset=4, num_gpus_per_engine=1, num_engines=0, rollout_num_gpus_per_engine=1, **common)
+    with pytest.raises(ValueError) as e:
+        check(worker_type="regular", gpu_offset=3, num_gpus_per_engine=2, num_engines=1, rollout_num_gpus_per_engine=2, **{**common, "num_gpus_per_engine_on_node": 2})
+    for part in ("worker_type=regular", "gpu_offset=3", "num_gpus_per_engine=2", "num_engines=1", "required_gpu_slots=5", "len(reordered_gpu_ids)=4",
+                 "rollout_num_gpus=4", "rollout_num_gpus_per_engine=2"):  # fmt: skip
+        assert part in str(e.value)
