@@ -48,6 +48,8 @@ def _layout(args) -> tuple[int, int, int]:
     rollout = args.rollout_num_gpus or 0
     if args.debug_train_only:
         return actor, 0, 0
+    if getattr(args, "rollout_external", False):  # engines started elsewhere take no GPU of this placement
+        return (actor, 0, 0) if args.debug_rollout_only else (actor, actor, 0)
     if args.debug_rollout_only:
         return rollout, 0, rollout
     if args.colocate:
