@@ -253,7 +253,7 @@ class Engine:
         fresh, max_q, max_k = True, 0, 0
         want_all_rows = any(r.logprob_start_len >= 0 for r, _ in batch)
         mrope = self.cfg.mrope_section is not None and any(r.mm is not None for r, _ in batch)
-        streams, emb_rows, emb_vecs = [], [], []
+        streams, emb_rows, emb_vecs, emb_deep = [], [], [], []
         for req, n in batch:
             s, e = req.num_computed, req.num_computed + n
             ids += req.ctx_ids[s:e]
@@ -264,6 +264,7 @@ class Engine:
                 if bool(inside.any()):
                     emb_rows.append(req.mm_rows[inside] - s + cu_q[-1])
                     emb_vecs.append(req.mm_embeds[inside])
+                    emb_deep.append([d[inside] for d in req.mm_deepstack])
             if mrope:
                 streams.append(self._position_streams(req, s, e))
             slots += self._slots(req, s, e)
@@ -282,7 +283,10 @@ class Engine:
         states = [getattr(req, "gdn_state", None) for req, _ in batch] if self.runner.has_gdn else None
         dev_pos = torch.cat(streams, dim=1).to(self.device, torch.int32) if mrope else t(pos)
         dev_in = (t(ids), dev_pos, t(slots), t(cu_q), None if fresh else t(gather, torch.long), t(cu_k))
-        embed_rows = (torch.cat(emb_rows).to(self.device), torch.cat(emb_vecs)) if emb_rows else None
+        embed_rows = None
+        if emb_rows:
+            deep = [torch.cat([d[k] for d in emb_deep]) for k in range(len(emb_deep[0]))]
+            embed_rows = (torch.cat(emb_rows).to(self.device), torch.cat(emb_vecs), deep)
         logits = self.runner.prefill(*dev_in, max_q, max_k, rows, fresh, gdn_states=states, embed_rows=embed_rows)
         if self.runner.has_gdn:
             for (req, _), st in zip(batch, self.runner.last_gdn_states):
@@ -337,19 +341,22 @@ class Engine:
         if self.weights.vision is None:
             raise ValueError("this model has no image encoder")
         ids = torch.tensor(req.input_ids)
-        rows, vecs = [], []
+        rows, vecs, deep = [], [], []
         for values, grids, tok in ((mm.get("pixel_values"), mm.get("image_grid_thw"), cfg.image_token_id),
                                    (mm.get("pixel_values_videos"), mm.get("video_grid_thw"), cfg.video_token_id)):  # fmt: skip
             if values is None:
                 continue
             where = (ids == tok).nonzero(as_tuple=False).flatten()
-            out = self.runner.encode_images(torch.as_tensor(values), torch.as_tensor(grids))
+            out, extras = self.runner.encode_images(torch.as_tensor(values), torch.as_tensor(grids))
             if where.numel() != out.shape[0]:
                 raise ValueError(f"{where.numel()} placeholder tokens for {out.shape[0]} encoder vectors")
             rows.append(where)
             vecs.append(out)
+            deep.append(extras)
         order = torch.cat(rows).argsort()
-        req.mm_rows, req.mm_embeds = torch.cat(rows)[order], torch.cat(vecs)[order.to(vecs[0].device)]
+        dev_order = order.to(vecs[0].device)
+        req.mm_rows, req.mm_embeds = torch.cat(rows)[order], torch.cat(vecs)[dev_order]
+        req.mm_deepstack = [torch.cat([d[k] for d in deep])[dev_order] for k in range(len(deep[0]))]
         if cfg.mrope_section:
             merge = (cfg.vision or {}).get("spatial_merge_size", 2)
             g = lambda k: None if mm.get(k) is None else torch.as_tensor(mm[k])  # noqa: E731

@@ -621,8 +621,10 @@ class ModelRunner:
 
     @torch.no_grad()
     def encode_images(self, pixel_values, grid_thw):
-        """Image encoder outputs [placeholder tokens, H] for one request's images."""
-        return self.w.vision(pixel_values.to(self.device), grid_thw.to(self.device)).to(self.w.dtype)
+        """Image encoder outputs [placeholder tokens, H] for one request's images, and the list of same-shaped vectors
+        that join the stream after the first layers (empty unless the encoder has deepstack outputs)."""
+        out, extras = self.w.vision(pixel_values.to(self.device), grid_thw.to(self.device), with_deepstack=True)
+        return out.to(self.w.dtype), [e.to(self.w.dtype) for e in extras]
 
     def _full_norm(self, t, w):
         """RMSNorm over all heads of the model: the sum of squares crosses the tensor-parallel ranks."""
@@ -829,8 +831,10 @@ class ModelRunner:
         cfg, w, d = self.cfg, self.w, self.cfg.head_dim
         x = ops.embedding(ids, w.embed, w.rank * w.vocab_local)
         x = self._tp_reduce(x) if w.tp > 1 else x
+        deepstack = []
         if embed_rows is not None:
             x = x.index_copy(0, embed_rows[0], embed_rows[1].to(x.dtype))
+            deepstack = embed_rows[2] if len(embed_rows) > 2 else []
         res = None
         T = ids.numel()
         if self.has_gdn:
@@ -839,6 +843,8 @@ class ModelRunner:
             in_call = positions_from_cu_seqlens(cu_q, T)  # position inside this pass (a later chunk starts at 0 again)
             self.last_gdn_states = [dict() for _ in range(cu_q.numel() - 1)]
         for li, L in enumerate(w.layers):
+            if 0 < li <= len(deepstack):  # vision vectors that join the stream after layer li - 1 (stream = x + res)
+                x = x.index_add(0, embed_rows[0], deepstack[li - 1].to(x.dtype))
             normed, res = ops.rmsnorm(x, L["ln1"], cfg.norm_epsilon, res)
             if L["kind"] == "gdn":
                 x = self._gdn_prefill(L, li, normed, in_call, cu_q, gdn_states, self.last_gdn_states)

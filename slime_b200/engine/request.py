@@ -98,6 +98,7 @@ class Request:
     # speculative decoding (engine/speculative.py): guesses for the tokens after the last one, the draft head's stream
     mm_rows: Any = None  # positions of the placeholder tokens in input_ids (long tensor) ...
     mm_embeds: Any = None  # ... and the encoder's vector for each, computed at the first prefill pass
+    mm_deepstack: Any = None  # vectors of the same rows that join the stream after the first layers (list, often empty)
     mm_positions: Any = None  # [3, len(input_ids)] temporal / height / width position streams of the prompt
     rope_delta: int = 0  # rotary position of a generated token = its index + rope_delta
     spec_draft: list[int] = field(default_factory=list)

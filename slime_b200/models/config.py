@@ -168,6 +168,8 @@ class ModelConfig:
             total += d * patch + d + v.get("num_position_embeddings", 0) * d  # patch embedding, learned positions
             total += v["depth"] * (4 * d + 4 * d * d + 4 * d + 2 * d * inter + inter + d)  # norms, qkv + proj, mlp
             total += 2 * d + big * big + big + v.get("out_hidden_size", h) * big + v.get("out_hidden_size", h)  # merger
+            # deepstack mergers: the same two linears behind a norm over the joined patches
+            total += len(v.get("deepstack_visual_indexes") or []) * (2 * big + big * big + big + v.get("out_hidden_size", h) * (big + 1))
         return total
 
     # -- constructors ---------------------------------------------------------
@@ -220,7 +222,9 @@ class ModelConfig:
             norm_epsilon=c.get("rms_norm_eps", 1e-6),
             rotary_base=c.get("rope_theta", 10000.0),
             max_position_embeddings=c.get("max_position_embeddings", 32768),
-            tie_word_embeddings=c.get("tie_word_embeddings", False),
+            # a nested configuration: the output layer belongs to the outer model, whose setting decides
+            tie_word_embeddings=top.get("tie_word_embeddings", c.get("tie_word_embeddings", False)) if "text_config" in top
+            else c.get("tie_word_embeddings", False),
             add_qkv_bias=c.get("attention_bias", a.startswith("qwen2")),
             qk_layernorm=a.startswith("qwen3"),
             model_arch=arch,

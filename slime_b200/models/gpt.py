@@ -359,6 +359,8 @@ class GPTModel(nn.Module):
                 x = tp.reduce_from_tensor_model_parallel_region(x)
             if vision_rows is not None:
                 x = x.index_put((vision_rows[0],), vision_rows[1].to(x.dtype))
+                if len(vision_rows) > 2 and vision_rows[2] and (self.sequence_parallel or mpu.get_pipeline_model_parallel_world_size() > 1):
+                    raise NotImplementedError("deepstack vision features with sequence or pipeline parallelism")
             if self.sequence_parallel:
                 x = tp.scatter_to_sequence_parallel_region(x)
             residual = None
@@ -366,11 +368,14 @@ class GPTModel(nn.Module):
             x, residual = self.input_tensor[0], self.input_tensor[1]
         packed.position_ids = position_ids
         table = self.rope_table(x.device, int(packed.max_seqlen) + 1)
-        for layer in self.decoder.layers:
+        deepstack = vision_rows[2] if vision_rows is not None and len(vision_rows) > 2 else []
+        for li, layer in enumerate(self.decoder.layers):
             if self.recompute and torch.is_grad_enabled():
                 x, residual = torch.utils.checkpoint.checkpoint(layer, x, residual, table, packed, use_reentrant=False)
             else:
                 x, residual = layer(x, residual, table, packed)
+            if li < len(deepstack):  # the stream is x + residual: adding to x adds to the stream
+                x = x.index_add(0, vision_rows[0], deepstack[li].to(x.dtype))
         if not self.post_process:
             if residual is None:
                 residual = torch.zeros_like(x)
@@ -429,22 +434,27 @@ class GPTModel(nn.Module):
         cfg = self.cfg
         if mpu.get_context_parallel_world_size() > 1:
             raise NotImplementedError("vision inputs with context parallelism: the placeholder rows of a rank's slices are not mapped yet")
-        rows, vecs = [], []
+        rows, vecs, deep = [], [], []
         for values, grids, tok in ((pixel_values, image_grid_thw, cfg.image_token_id), (pixel_values_videos, video_grid_thw, cfg.video_token_id)):
             if values is None:
                 continue
             assert grids is not None and tok is not None and self.vision is not None, "pixel values need their grids, a placeholder id and an encoder"
             where = (ids == tok).nonzero(as_tuple=False).flatten()
-            out = self.vision(values.to(ids.device), grids)
+            out, extras = self.vision(values.to(ids.device), grids, with_deepstack=True)
             if where.numel() != out.shape[0]:
                 raise ValueError(f"{where.numel()} placeholder tokens for {out.shape[0]} encoder vectors")
             rows.append(where)
             vecs.append(out)
+            deep.append(extras)
         if cfg.mrope_section:
             merge = (cfg.vision or {}).get("spatial_merge_size", 2)
             packed.mrope_positions, _ = mrope_position_ids(ids, packed.cu_seqlens, image_grid_thw, video_grid_thw, image_token_id=cfg.image_token_id,
                                                            video_token_id=cfg.video_token_id, spatial_merge_size=merge)  # fmt: skip
-        return (torch.cat(rows), torch.cat(vecs)) if rows else None
+        if not rows:
+            return None
+        # per early layer, the extra vectors of all placeholder rows (images then videos, like the rows themselves)
+        extras = [torch.cat([d[k] for d in deep]) for k in range(len(deep[0]))]
+        return torch.cat(rows), torch.cat(vecs), extras
 
     def forward(self, input_ids, position_ids=None, attention_mask=None, labels=None, packed_seq_params=None,
                 loss_mask=None, return_hidden=False, pixel_values=None, image_grid_thw=None, pixel_values_videos=None,

@@ -139,6 +139,17 @@ MORE_PRESETS["qwen3.5-35b-a3b-vl"] = dict(
     vision=dict(depth=27, hidden_size=1152, num_heads=16, intermediate_size=4304, in_channels=3, patch_size=16, temporal_patch_size=2,
                 spatial_merge_size=2, out_hidden_size=2048, num_position_embeddings=2304, hidden_act="gelu_pytorch_tanh"))  # fmt: skip
 
+# Qwen3-VL-8B: the Qwen3-8B language model (rotary base 5e6) with the same kind of encoder, three of whose blocks (8, 16,
+# 24) also feed the first three language layers through mergers of their own
+MORE_PRESETS["qwen3-vl-8b"] = dict(
+    num_layers=36, hidden_size=4096, num_attention_heads=32, num_query_groups=8, kv_channels=128, ffn_hidden_size=12288,
+    vocab_size=151936, tie_word_embeddings=False, qk_layernorm=True,
+    model_arch="Qwen3VLForConditionalGeneration", rotary_base=5e6, mrope_section=[24, 20, 20], mrope_interleaved=True,
+    image_token_id=151655, video_token_id=151656,
+    vision=dict(depth=27, hidden_size=1152, num_heads=16, intermediate_size=4304, in_channels=3, patch_size=16, temporal_patch_size=2,
+                spatial_merge_size=2, out_hidden_size=4096, num_position_embeddings=2304, hidden_act="gelu_pytorch_tanh",
+                deepstack_visual_indexes=[8, 16, 24]))  # fmt: skip
+
 # name -> what is missing. The numbers of these families are in the recipes they come from; they are not repeated here
 # because a preset that cannot be instantiated correctly is worse than none.
 UNSUPPORTED: dict[str, str] = {}

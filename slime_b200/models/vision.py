@@ -47,10 +47,7 @@ class VisionConfig:
     @classmethod
     def from_dict(cls, d: dict) -> "VisionConfig":
         names = {f.name for f in cls.__dataclass_fields__.values()}
-        cfg = cls(**{k: v for k, v in d.items() if k in names})
-        if cfg.deepstack_visual_indexes:
-            raise NotImplementedError("vision towers whose intermediate layers feed the language model (deepstack) are not built")
-        return cfg
+        return cls(**{k: v for k, v in d.items() if k in names})
 
     @property
     def patch_dim(self) -> int:
@@ -137,6 +134,15 @@ class VisionTower(nn.Module):
         self.merger.norm = _Affine(d, dtype=dtype, device=device, ones=True)
         self.merger.linear_fc1 = _Affine(big, big, dtype=dtype, device=device)
         self.merger.linear_fc2 = _Affine(c.out_hidden_size, big, dtype=dtype, device=device)
+        # "deepstack" (Qwen3-VL): the outputs of some intermediate blocks, each through a merger of its own (normalised
+        # after the neighbourhoods are joined), are added to the language model's stream after its first layers
+        self.deepstack_merger_list = nn.ModuleList()
+        for _ in c.deepstack_visual_indexes:
+            m = nn.Module()
+            m.norm = _Affine(big, dtype=dtype, device=device, ones=True)
+            m.linear_fc1 = _Affine(big, big, dtype=dtype, device=device)
+            m.linear_fc2 = _Affine(c.out_hidden_size, big, dtype=dtype, device=device)
+            self.deepstack_merger_list.append(m)
         self.side = int(math.isqrt(c.num_position_embeddings))
 
     @property
@@ -171,8 +177,9 @@ class VisionTower(nn.Module):
         ang = torch.cat([ang, ang], dim=-1)
         return torch.cat(pos), ang.cos(), ang.sin()
 
-    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor) -> torch.Tensor:
-        """``pixel_values`` [patches, C * tp * p * p], ``grid_thw`` [images, 3] -> [patches / merge**2, out_hidden]."""
+    def forward(self, pixel_values: torch.Tensor, grid_thw: torch.Tensor, with_deepstack: bool = False):
+        """``pixel_values`` [patches, C * tp * p * p], ``grid_thw`` [images, 3] -> [patches / merge**2, out_hidden]; with
+        ``with_deepstack`` also the list of same-shaped vectors for the language model's first layers."""
         c = self.c
         grid = [[int(v) for v in row] for row in grid_thw.tolist()]
         assert pixel_values.shape[0] == sum(t * h * w for t, h, w in grid), "pixel rows do not match the grids"
@@ -181,12 +188,20 @@ class VisionTower(nn.Module):
         pos, cos, sin = self._positions(grid, x.device)
         x = x + pos
         frames = [h * w for t, h, w in grid for _ in range(t)]
-        for blk in self.blocks:
+        big = c.hidden_size * c.spatial_merge_size**2
+        extras = []
+        for i, blk in enumerate(self.blocks):
             x = blk(x, cos, sin, frames)
+            if i in c.deepstack_visual_indexes:
+                m = self.deepstack_merger_list[c.deepstack_visual_indexes.index(i)]
+                y = F.layer_norm(x.reshape(-1, big), (big,), m.norm.weight, m.norm.bias, 1e-6)
+                y = F.gelu(F.linear(y, m.linear_fc1.weight, m.linear_fc1.bias))
+                extras.append(F.linear(y, m.linear_fc2.weight, m.linear_fc2.bias))
         x = F.layer_norm(x, (c.hidden_size,), self.merger.norm.weight, self.merger.norm.bias, 1e-6)
-        x = x.reshape(-1, c.hidden_size * c.spatial_merge_size**2)
+        x = x.reshape(-1, big)
         x = F.gelu(F.linear(x, self.merger.linear_fc1.weight, self.merger.linear_fc1.bias))
-        return F.linear(x, self.merger.linear_fc2.weight, self.merger.linear_fc2.bias)
+        out = F.linear(x, self.merger.linear_fc2.weight, self.merger.linear_fc2.bias)
+        return (out, extras) if with_deepstack else out
 
 
 # ----------------------------------------------------------------------------------------- multi-axis rotary positions

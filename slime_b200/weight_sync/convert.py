@@ -123,7 +123,7 @@ def _gated_q_from_hf(cfg: ModelConfig, qg: torch.Tensor):
 
 
 def _family(cfg: ModelConfig) -> str:
-    a = (cfg.model_arch or "").lower()
+    a = (cfg.model_arch or "").lower().replace("vlmoe", "moe").replace("vl", "")  # Qwen3-VL(-MoE): the text model's family
     for key in ("qwen3_5", "qwen3next", "qwen3moe", "qwen2moe", "qwen3", "qwen2", "glm4moe", "glm4", "llama", "mimo",
                 "deepseek", "minimax"):  # fmt: skip
         if key in a.replace("_", "").replace("-", "") or key in a:

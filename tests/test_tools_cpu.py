@@ -136,6 +136,7 @@ def test_model_presets_round_trip_through_flags():
             assert a == b, (name, f.name, a, b)
     vl = get_preset("qwen3.5-35b-a3b-vl")
     assert vl.vision["depth"] == 27 and vl.mixer(3) == "general_attention" and vl.num_params() - get_preset("qwen3.5-35b-a3b").num_params() > 4e8
+    assert abs(get_preset("qwen3-vl-8b").num_params() / 1e9 - 8.77) < 0.01  # the published size, deepstack mergers included
     assert get_preset("qwen3-235b-a22b").num_params() > 2.3e11
     # the parameter counts of the latent-attention and hybrid families agree with the published sizes
     for name, billions in (("deepseek-v3", 671), ("kimi-k2", 1026), ("glm5-744b-a40b", 744), ("qwen3-next-80b-a3b", 80),
