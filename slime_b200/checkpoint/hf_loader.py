@@ -40,7 +40,10 @@ class SafetensorReader:
         return self.index.keys()
 
     def __contains__(self, name):
-        return name in self.index
+        if name in self.index:
+            return True
+        stacked = convert.stacked_expert_source(name)  # files that keep a layer's experts in one tensor
+        return stacked is not None and stacked[0] in self.index
 
     def _file(self, name):
         fn = self.index[name]
@@ -48,7 +51,14 @@ class SafetensorReader:
             self._handles[fn] = self._open(os.path.join(self.path, fn), framework="pt")
         return self._handles[fn]
 
-    def get(self, name: str) -> torch.Tensor:
+    def get(self, name: str, cfg=None) -> torch.Tensor:
+        if name not in self.index:
+            stacked, e, part = convert.stacked_expert_source(name)
+            if cfg is None:
+                raise KeyError(f"{name} is held in the stacked tensor {stacked}: pass the model configuration to slice it")
+            sl = self._file(stacked).get_slice(stacked)
+            one = sl[e : e + 1]  # one expert's block only: the stack of a layer can be gigabytes
+            return dict(convert.split_stacked_experts(cfg, stacked, one))[name.replace(f".experts.{e}.", ".experts.0.")].contiguous()
         t = self._file(name).get_tensor(name)
         scale_name = name + "_scale_inv"
         if t.dtype == torch.float8_e4m3fn and scale_name in self.index:
@@ -89,7 +99,7 @@ def load_hf_weights(path: str, model) -> list[str]:
         if not all(s in reader for s in sources):
             missing.append(name)
             continue
-        full = convert.merge_hf_sources(rule, [reader.get(s) for s in sources], cfg)
+        full = convert.merge_hf_sources(rule, [reader.get(s, cfg) for s in sources], cfg)
         if name in ("embedding.word_embeddings.weight", "output_layer.weight"):
             full = convert.pad_vocab(full, cfg.padded_vocab_size)
         if getattr(p, "tensor_model_parallel", False) and tp > 1 and not getattr(p, "is_expert", False):

@@ -196,6 +196,10 @@ class EngineWeights:
             return True
         if name.startswith("model.language_model."):  # checkpoints with a vision tower nest the language model
             name = "model." + name[len("model.language_model.") :]
+        if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")):  # a layer's experts in one stacked tensor
+            from slime_b200.weight_sync.convert import split_stacked_experts
+
+            return all([self.load_weight(n, w) for n, w in split_stacked_experts(cfg, name, t)])
         if ".block_sparse_moe." in name:  # MiniMax-M2 spelling of the expert tensors
             from slime_b200.weight_sync.convert import family_name_to_generic
 

@@ -131,9 +131,45 @@ def _family(cfg: ModelConfig) -> str:
     return "qwen2"
 
 
+def split_stacked_experts(cfg: ModelConfig, name: str, t: torch.Tensor) -> list[tuple[str, torch.Tensor]] | None:
+    """Qwen3-VL-MoE files keep a layer's experts in two stacked tensors, ``mlp.experts.gate_up_proj`` of shape
+    [experts, hidden, 2 x width] and ``mlp.experts.down_proj`` of shape [experts, width, hidden] (the operands of
+    ``x @ W``, i.e. the transposes of linear-layer weights). Returns the per-expert ``gate_proj`` / ``up_proj`` /
+    ``down_proj`` linear weights every consumer here names, or None for any other tensor. A stack that already has the
+    linear-layer orientation is taken as it is; where hidden = 2 x width makes the two indistinguishable, the files'
+    orientation is assumed."""
+    if t.dim() != 3 or not name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")):
+        return None
+    h, w = cfg.hidden_size, cfg.moe_ffn_hidden_size
+    out = []
+    if name.endswith("gate_up_proj"):
+        base = name[: -len("gate_up_proj")]
+        if tuple(t.shape[1:]) != (h, 2 * w):
+            assert tuple(t.shape[1:]) == (2 * w, h), (name, tuple(t.shape))
+            t = t.transpose(1, 2)
+        for e in range(t.shape[0]):
+            out += [(f"{base}{e}.gate_proj.weight", t[e, :, :w].t()), (f"{base}{e}.up_proj.weight", t[e, :, w:].t())]
+    else:
+        base = name[: -len("down_proj")]
+        if tuple(t.shape[1:]) != (w, h):
+            assert tuple(t.shape[1:]) == (h, w), (name, tuple(t.shape))
+            t = t.transpose(1, 2)
+        out = [(f"{base}{e}.down_proj.weight", t[e].t()) for e in range(t.shape[0])]
+    return out
+
+
+def stacked_expert_source(name: str) -> tuple[str, int, str] | None:
+    """For a per-expert name ``....mlp.experts.<e>.<gate|up|down>_proj.weight``: the stacked tensor that would hold it in
+    a file of the layout above, the expert index and the part."""
+    m = re.match(r"(.*\.mlp\.experts\.)(\d+)\.(gate|up|down)_proj\.weight$", name)
+    if m is None:
+        return None
+    return m.group(1) + ("down_proj" if m.group(3) == "down" else "gate_up_proj"), int(m.group(2)), m.group(3)
+
+
 def _vl_name(cfg: ModelConfig, hf_name: str) -> str:
     """Checkpoints of models with vision inputs keep the language model under ``model.language_model`` (next to
-    ``model.visual``)."""
+    ``model.visual``, whose tensors keep their names). Parity: slime/backends/megatron_utils/megatron_to_hf/qwen3_vl.py:5-25."""
     if cfg.vision is not None and hf_name.startswith("model.") and not hf_name.startswith(("model.visual.", "model.language_model.")):
         return "model.language_model." + hf_name[len("model.") :]
     return hf_name

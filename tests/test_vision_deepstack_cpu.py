@@ -132,3 +132,35 @@ def test_engine_adds_the_side_outputs_after_the_first_layers(pair, chunk):
     a = e.generate([ids], [dict(max_new_tokens=6, temperature=0, ignore_eos=True)], mm=mm)[0]
     ref = trainer_logprobs(ids + a.output_ids)[len(ids) - 1 :]
     assert np.abs(np.array(a.output_logprobs) - ref).max() < 3e-4, np.abs(np.array(a.output_logprobs) - ref).max()
+
+
+def test_files_with_stacked_experts_load_into_trainer_and_engine(pair, tmp_path):
+    """Qwen3-VL-MoE files hold a layer's experts as [experts, hidden, 2 x width] and [experts, width, hidden] stacks."""
+    from safetensors.torch import save_file
+
+    from slime_b200.checkpoint.hf_loader import SafetensorReader, load_hf_weights
+    from slime_b200.engine.engine import Engine
+    from slime_b200.engine.server_args import ServerArgs
+
+    hf, cfg, ours, sd = pair
+    if not cfg.num_experts:
+        pytest.skip("dense model: nothing is stacked")
+    files = {k: (v.transpose(1, 2) if k.endswith(("experts.gate_up_proj", "experts.down_proj")) else v).contiguous().clone()
+             for k, v in hf.state_dict().items()}  # fmt: skip
+    assert files["model.language_model.layers.0.mlp.experts.down_proj"].shape == (4, 32, 64)
+    parts = dict(x for k, v in files.items() for x in (convert.split_stacked_experts(cfg, k, v) or [(k, v)]))
+    assert set(parts) == set(sd) and all(torch.equal(parts[k], sd[k]) for k in sd)
+    save_file(files, str(tmp_path / "model.safetensors"))
+    reader = SafetensorReader(str(tmp_path))
+    name = "model.language_model.layers.1.mlp.experts.2.up_proj.weight"
+    assert name in reader and torch.equal(reader.get(name, cfg), sd[name])
+    fresh = GPTModel(cfg, dtype=torch.float32, device="cpu", seed=7)
+    assert not load_hf_weights(str(tmp_path), fresh)
+    for (n, a), (_, b) in zip(fresh.named_parameters(), ours.named_parameters()):
+        assert torch.equal(a, b), n
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=2, context_length=64, disable_cuda_graph=True), device="cpu", num_pages=32)
+    assert not e.weights.load_weights(list(files.items()))
+    f = Engine(cfg, ServerArgs(page_size=4, max_running_requests=2, context_length=64, disable_cuda_graph=True), device="cpu", num_pages=32)
+    assert not f.weights.load_weights(list(sd.items()))
+    for a, b in zip(e.weights.tensors(), f.weights.tensors()):
+        assert torch.equal(a, b)
