@@ -66,27 +66,43 @@ class EngineServer:
                 self._wake.clear()
 
     # ---------------------------------------------------------------------------- handlers
-    def _vision_inputs(self, image_data, ids, text):
-        """``image_data`` (base64 / data URLs / paths, one request) -> (prompt ids with every image's placeholder run at
-        its full length, encoder inputs). With ``input_ids`` the prompt is taken as sent (already expanded by the caller's
-        processor, or one placeholder per image); with ``text`` it is tokenised here."""
+    def _vision_inputs(self, image_data, ids, text, video_data=None):
+        """``image_data`` (base64 / data URLs / paths, one request) and ``video_data`` (a list of clips, each a list of
+        frames given the same way) -> (prompt ids with every placeholder run at its full length, encoder inputs). With
+        ``input_ids`` the prompt is taken as sent (already expanded by the caller's processor, or one placeholder per
+        image and per frame group of a clip, each group between its own markers); with ``text`` it is tokenised here."""
         from slime_b200.utils.image_processing import ImageProcessor, expand_image_placeholders
         from slime_b200.utils.processing_utils import _load_image
 
         cfg = self.engine.cfg
         if cfg.vision is None or cfg.image_token_id is None:
             raise ValueError("this model takes no images")
-        images = [_load_image(x) for x in (image_data if isinstance(image_data, list) else [image_data])]
-        ip = getattr(self.processor, "image_processor", None)
-        out = ip(images=images, return_tensors="pt") if ip is not None else ImageProcessor.from_vision_config(cfg.vision)(images)
-        mm = {"pixel_values": out["pixel_values"], "image_grid_thw": out["image_grid_thw"]}
+        if video_data and cfg.video_token_id is None:
+            raise ValueError("this model takes no videos")
+        images = [_load_image(x) for x in (image_data if isinstance(image_data, list) else [image_data])] if image_data else []
+        videos = [[_load_image(f) for f in clip] for clip in (video_data or [])]
+        own = ImageProcessor.from_vision_config(cfg.vision)
+        mm = {}
+        if images:
+            ip = getattr(self.processor, "image_processor", None)
+            out = ip(images=images, return_tensors="pt") if ip is not None else own(images)
+            mm.update(pixel_values=out["pixel_values"], image_grid_thw=out["image_grid_thw"])
+        if videos:
+            vp = getattr(self.processor, "video_processor", None)
+            out = vp(videos=videos, return_tensors="pt") if vp is not None else own(videos=videos)
+            mm.update(pixel_values_videos=out["pixel_values_videos"], video_grid_thw=out["video_grid_thw"])
         if ids is None:
             if text is None or self.tokenizer is None:
                 raise ValueError("input_ids (or text with a tokenizer) required")
             ids = self.tokenizer.encode(text, add_special_tokens=False)
         merge = cfg.vision.get("spatial_merge_size", 2) ** 2
-        counts = [int(t * h * w) // merge for t, h, w in mm["image_grid_thw"].tolist()]
-        return expand_image_placeholders(list(ids), cfg.image_token_id, counts), mm
+        ids = list(ids)
+        if images:
+            ids = expand_image_placeholders(ids, cfg.image_token_id, [int(t * h * w) // merge for t, h, w in mm["image_grid_thw"].tolist()])
+        if videos:  # one run per frame group
+            counts = [int(h * w) // merge for t, h, w in mm["video_grid_thw"].tolist() for _ in range(int(t))]
+            ids = expand_image_placeholders(ids, cfg.video_token_id, counts)
+        return ids, mm
 
     async def _generate(self, request):
         from aiohttp import web
@@ -94,11 +110,11 @@ class EngineServer:
         body = await request.json()
         ids = body.get("input_ids")
         mm = None
-        if body.get("image_data"):
+        if body.get("image_data") or body.get("video_data"):
             try:
-                ids, mm = self._vision_inputs(body["image_data"], ids, body.get("text"))
+                ids, mm = self._vision_inputs(body.get("image_data"), ids, body.get("text"), body.get("video_data"))
             except Exception as e:  # noqa: BLE001  a bad image or a prompt that does not match its images
-                return web.json_response({"error": f"image inputs: {e}"}, status=400)
+                return web.json_response({"error": f"vision inputs: {e}"}, status=400)
         if ids is None:
             text = body.get("text")
             if text is None or self.tokenizer is None:

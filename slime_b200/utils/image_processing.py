@@ -74,9 +74,39 @@ class ImageProcessor:
         x = x.permute(2, 5, 3, 6, 1, 0, 4, 7)  # block row, block col, in-block row, in-block col, C, tp, p, p
         return x.reshape(gh * gw, 3 * tp * p * p).contiguous(), [1, gh, gw]
 
-    def __call__(self, images) -> dict:
-        rows, grids = zip(*(self.one(im) for im in images))
-        return {"pixel_values": torch.cat(rows), "image_grid_thw": torch.tensor(grids, dtype=torch.long)}
+    def video(self, frames) -> tuple[torch.Tensor, list[int]]:
+        """Frames of one clip -> rows of flattened patches, each spanning ``temporal_patch_size`` consecutive frames (the
+        last frame repeats to fill the final group), and the grid [frame groups, patch rows, patch columns]. Every frame
+        takes the size chosen for the first one."""
+        from PIL import Image
+
+        frames = [f if hasattr(f, "convert") else Image.fromarray(np.asarray(f)) for f in frames]
+        if not frames:
+            raise ValueError("a video needs at least one frame")
+        p, m, tp = self.patch_size, self.merge_size, self.temporal_patch_size
+        h, w = smart_resize(frames[0].height, frames[0].width, p * m, self.min_pixels, self.max_pixels)
+        frames = frames + [frames[-1]] * (-len(frames) % tp)
+        xs = []
+        for f in frames:
+            f = f.convert("RGB")
+            if (h, w) != (f.height, f.width):
+                f = f.resize((w, h), resample=Image.BICUBIC)
+            xs.append(torch.from_numpy(np.asarray(f, dtype=np.float32) / 255.0).permute(2, 0, 1))
+        x = (torch.stack(xs) - torch.tensor(self.mean)[:, None, None]) / torch.tensor(self.std)[:, None, None]  # [T, C, H, W]
+        gt, gh, gw = len(frames) // tp, h // p, w // p
+        x = x.reshape(gt, tp, 3, gh // m, m, p, gw // m, m, p)
+        x = x.permute(0, 3, 6, 4, 7, 2, 1, 5, 8)  # group, block row, block col, in-block row, in-block col, C, tp, p, p
+        return x.reshape(gt * gh * gw, 3 * tp * p * p).contiguous(), [gt, gh, gw]
+
+    def __call__(self, images=None, videos=None) -> dict:
+        out = {}
+        if images:
+            rows, grids = zip(*(self.one(im) for im in images))
+            out.update(pixel_values=torch.cat(rows), image_grid_thw=torch.tensor(grids, dtype=torch.long))
+        if videos:
+            rows, grids = zip(*(self.video(v) for v in videos))
+            out.update(pixel_values_videos=torch.cat(rows), video_grid_thw=torch.tensor(grids, dtype=torch.long))
+        return out
 
 
 def expand_image_placeholders(ids: list[int], token: int, counts: list[int]) -> list[int]:

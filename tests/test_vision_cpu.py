@@ -271,3 +271,77 @@ def test_position_streams_golden_vector_and_packed_reset():
     vid = torch.tensor([99, 20, 20, 20, 20, 98, 99, 20, 20, 20, 20, 98, 5])
     got, _ = vision.mrope_position_ids(vid, [0, 13], None, torch.tensor([[2, 4, 4]]), image_token_id=10, video_token_id=20)
     assert got[0].tolist() == [0, 1, 1, 1, 1, 3, 4, 5, 5, 5, 5, 7, 8] and got[2].tolist() == [0, 1, 2, 1, 2, 3, 4, 5, 6, 5, 6, 7, 8]
+
+
+def test_generate_endpoint_takes_video_frames(pair):
+    """A clip arrives as a list of frames; frame pairs form one temporal patch each, every pair has its own placeholder
+    run, and the engine's answer equals the direct call's and the trainer's."""
+    import base64
+    import io
+
+    import numpy as np
+    import requests
+    from PIL import Image
+
+    from slime_b200.engine.http_server import EngineServer
+    from slime_b200.utils.image_processing import ImageProcessor
+
+    _, _, cfg, ours = pair
+    ip = ImageProcessor.from_vision_config(cfg.vision, min_pixels=16 * 16, max_pixels=64 * 64)
+    rng = np.random.default_rng(1)
+    frames = [Image.fromarray(rng.integers(0, 255, (16, 24, 3), dtype=np.uint8)) for _ in range(3)]
+    rows, grid = ip.video(frames)
+    assert grid == [2, 4, 6] and rows.shape == (48, 3 * 2 * 4 * 4)
+    still, g1 = ip.one(frames[2])
+    assert g1 == [1, 4, 6] and torch.equal(rows[24:], still)  # the odd last frame repeats, like a still image
+    pair01 = rows[:24].reshape(24, 3, 2, 16)
+    assert torch.equal(pair01[:, :, 0], ip.one(frames[0])[0].reshape(24, 3, 2, 16)[:, :, 0])
+    assert torch.equal(pair01[:, :, 1], ip.one(frames[1])[0].reshape(24, 3, 2, 16)[:, :, 0])
+
+    e = _engine(pair)
+    srv = EngineServer(e, port=0).start(block=False)
+    try:
+        def b64(im):
+            buf = io.BytesIO()
+            im.save(buf, format="PNG")
+            return "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+
+        short = [5, VSTART, VID, VEND, 6, VSTART, VID, VEND, 9]  # one placeholder per frame pair, each between its own markers
+        body = {"input_ids": short, "video_data": [[b64(f) for f in frames]], "return_logprob": True,
+                "sampling_params": {"max_new_tokens": 4, "temperature": 0, "ignore_eos": True}}  # fmt: skip
+        out = requests.post(f"http://127.0.0.1:{srv.port}/generate", json=body, timeout=60).json()
+        own = ImageProcessor.from_vision_config(cfg.vision)(videos=[frames])
+        n = int(own["video_grid_thw"][0, 1] * own["video_grid_thw"][0, 2]) // 4
+        full = [5, VSTART] + [VID] * n + [VEND, 6, VSTART] + [VID] * n + [VEND, 9]
+        assert out["meta_info"]["prompt_tokens"] == len(full)
+        want = e.generate([full], [dict(max_new_tokens=4, temperature=0, ignore_eos=True)], mm=own)[0]
+        assert out["output_ids"] == want.output_ids
+        with torch.no_grad():
+            toks = full + want.output_ids
+            lg = ours(torch.tensor(toks), pixel_values_videos=own["pixel_values_videos"], video_grid_thw=own["video_grid_thw"])[0]
+        ref = lg.log_softmax(-1)[len(full) - 1 : -1].gather(-1, torch.tensor(want.output_ids)[:, None]).squeeze(-1)
+        assert (torch.tensor(want.output_logprobs) - ref).abs().max() < 2e-4
+        bad = requests.post(f"http://127.0.0.1:{srv.port}/generate", json=dict(body, input_ids=short[:4]), timeout=60)
+        assert bad.status_code == 400 and "vision inputs" in bad.json()["error"]
+    finally:
+        srv.shutdown()
+
+
+def test_video_patch_layout_matches_the_library_processor():
+    import numpy as np
+
+    from slime_b200.utils.image_processing import ImageProcessor
+
+    vp_mod = pytest.importorskip("transformers.models.qwen3_vl.video_processing_qwen3_vl")
+    try:
+        vp = vp_mod.Qwen3VLVideoProcessor(patch_size=4, temporal_patch_size=2, merge_size=2, do_sample_frames=False,
+                                          size={"shortest_edge": 16 * 16, "longest_edge": 64 * 64 * 8})  # fmt: skip
+    except ImportError as e:  # the library's processor wants torchvision
+        pytest.skip(str(e))
+    clip = np.random.default_rng(0).integers(0, 255, (4, 32, 48, 3), dtype=np.uint8)
+    want = vp(videos=[torch.from_numpy(clip).permute(0, 3, 1, 2)], return_tensors="pt")
+    ip = ImageProcessor(patch_size=4, temporal_patch_size=2, merge_size=2, min_pixels=16 * 16, max_pixels=64 * 64,
+                        mean=tuple(vp.image_mean), std=tuple(vp.image_std))  # fmt: skip
+    rows, grid = ip.video(list(clip))
+    assert grid == want["video_grid_thw"][0].tolist() == [2, 8, 12]
+    assert (rows - want["pixel_values_videos"]).abs().max() < 1e-6
