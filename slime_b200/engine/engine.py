@@ -332,22 +332,34 @@ class Engine:
         """First pass of a request with images: run the encoder once, locate the placeholder tokens, lay out the three
         position streams of the prompt. (``image_data`` of ``/generate``: slime/rollout/sglang_rollout.py:158-203 and
         examples/geo3k_vlm_multi_turn/rollout.py:192-209 in the reference send processor-expanded ``input_ids`` plus the
-        images.)"""
+        images.) ``image_embeds`` / ``video_embeds`` (with ``*_deepstack_embeds`` where the encoder has such outputs) in
+        place of pixel values skip the encoder: the precomputed-embedding path of engines that split encoder and language
+        model."""
         if req.mm_embeds is not None:
             return
         from slime_b200.models.vision import mrope_position_ids
 
         cfg, mm = self.cfg, req.mm
-        if self.weights.vision is None:
-            raise ValueError("this model has no image encoder")
         ids = torch.tensor(req.input_ids)
         rows, vecs, deep = [], [], []
-        for values, grids, tok in ((mm.get("pixel_values"), mm.get("image_grid_thw"), cfg.image_token_id),
-                                   (mm.get("pixel_values_videos"), mm.get("video_grid_thw"), cfg.video_token_id)):  # fmt: skip
-            if values is None:
+        n_deep = len((cfg.vision or {}).get("deepstack_visual_indexes") or [])
+        for kind, grids, tok in (("image", mm.get("image_grid_thw"), cfg.image_token_id),
+                                 ("video", mm.get("video_grid_thw"), cfg.video_token_id)):  # fmt: skip
+            values = mm.get("pixel_values" if kind == "image" else "pixel_values_videos")
+            ready = mm.get(f"{kind}_embeds")  # encoder outputs computed elsewhere (an encoder-only worker, a cache)
+            if values is None and ready is None:
                 continue
             where = (ids == tok).nonzero(as_tuple=False).flatten()
-            out, extras = self.runner.encode_images(torch.as_tensor(values), torch.as_tensor(grids))
+            if ready is not None:
+                dev, dt = self.runner.device, self.weights.dtype
+                out = torch.as_tensor(ready).to(dev, dt)
+                extras = [torch.as_tensor(x).to(dev, dt) for x in (mm.get(f"{kind}_deepstack_embeds") or [])]
+                if len(extras) != n_deep or any(x.shape != out.shape for x in extras):
+                    raise ValueError(f"{kind}_embeds of this model come with {n_deep} same-shaped {kind}_deepstack_embeds")
+            else:
+                if self.weights.vision is None:
+                    raise ValueError("this model has no image encoder")
+                out, extras = self.runner.encode_images(torch.as_tensor(values), torch.as_tensor(grids))
             if where.numel() != out.shape[0]:
                 raise ValueError(f"{where.numel()} placeholder tokens for {out.shape[0]} encoder vectors")
             rows.append(where)

@@ -164,3 +164,26 @@ def test_files_with_stacked_experts_load_into_trainer_and_engine(pair, tmp_path)
     assert not f.weights.load_weights(list(sd.items()))
     for a, b in zip(e.weights.tensors(), f.weights.tensors()):
         assert torch.equal(a, b)
+
+
+def test_engine_takes_encoder_outputs_computed_elsewhere(pair):
+    """``image_embeds`` + ``image_deepstack_embeds`` in place of pixel values skip the engine's encoder and give the same
+    tokens and log-probs; a request that leaves the deepstack vectors out is refused."""
+    from slime_b200.engine.engine import Engine
+    from slime_b200.engine.server_args import ServerArgs
+
+    hf, cfg, ours, sd = pair
+    e = Engine(cfg, ServerArgs(page_size=4, max_running_requests=4, context_length=128, disable_cuda_graph=True), device="cpu", num_pages=96)
+    assert not e.weights.load_weights(list(sd.items()))
+    ids, px, grid = _inputs()
+    ids = ids[0].tolist()
+    sp = dict(max_new_tokens=5, temperature=0, ignore_eos=True)
+    want = e.generate([ids], [sp], mm=dict(pixel_values=px, image_grid_thw=grid))[0]
+    with torch.no_grad():
+        out, extras = ours.vision(px, grid, with_deepstack=True)
+    e.weights.vision = None  # the language-model side of a split deployment holds no encoder
+    got = e.generate([ids], [sp], mm=dict(image_embeds=out, image_deepstack_embeds=extras, image_grid_thw=grid))[0]
+    assert got.output_ids == want.output_ids
+    assert max(abs(a - b) for a, b in zip(got.output_logprobs, want.output_logprobs)) < 1e-5
+    with pytest.raises(Exception, match="deepstack_embeds"):
+        e.generate([ids], [sp], mm=dict(image_embeds=out, image_grid_thw=grid))
