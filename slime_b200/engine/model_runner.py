@@ -877,7 +877,8 @@ class ModelRunner:
             x = self._post_norm(x, L["post_attn_ln"])
             normed, res = ops.rmsnorm(x, L["ln2"], cfg.norm_epsilon, res)
             x = self._post_norm(self._mlp(L, normed), L["post_mlp_ln"])
-        h, self.last_hidden = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
+        h, hidden = ops.rmsnorm(x, w.final_norm, cfg.norm_epsilon, res)
+        self.last_hidden = hidden if w.draft else None  # kept for a draft head only: a chunk's stream is tens of megabytes
         if last_rows is not None:
             h = h.index_select(0, last_rows)
         return self._gather_logits(ops.gemm(h, w.lm_head, out_dtype=torch.float32))
